@@ -1,0 +1,359 @@
+// Python bindings of the native runtime (module bluefog_b200._C).
+// Role of bluefog/torch/mpi_ops.cc:572-690 and mpi_win_ops.cc:663-728 in the reference,
+// with one generic enqueue entry instead of one symbol per tensor type.
+#include <torch/extension.h>
+
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <pybind11/stl.h>
+
+#include "common/logging.h"
+#include "common/runtime.h"
+#include "common/windows.h"
+#include "cuda/bucket.h"
+#include "cuda/gpu_channel.h"
+#include "cuda/symm_mem.h"
+
+namespace py = pybind11;
+using namespace bfb;
+
+namespace {
+
+int ElemOf(const at::Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return kF32;
+    case at::kDouble: return kF64;
+    case at::kHalf: return kF16;
+    case at::kBFloat16: return kBF16;
+    case at::kInt: return kI32;
+    case at::kLong: return kI64;
+    default: throw std::invalid_argument("unsupported tensor type for this kernel");
+  }
+}
+
+cudaStream_t CurrentStream(int device) { return c10::cuda::getCurrentCUDAStream(device).stream(); }
+
+void* PtrOrNull(const c10::optional<at::Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+
+// ---- single-process world of channels: every "rank" is a set of buffers on one GPU ----------
+class LocalWorld {
+ public:
+  LocalWorld(int world, int64_t half_bytes, int device) : world_(world), device_(device) {
+    std::vector<std::shared_ptr<SymmBuffer>> ctrl, arena;
+    ThrowIfError(AllocateLocal(world, device, sizeof(ChannelCtrl), &ctrl));
+    ThrowIfError(AllocateLocal(world, device, static_cast<size_t>(half_bytes) * 2, &arena));
+    for (int r = 0; r < world; ++r) chans_.push_back(std::make_unique<Channel>(ctrl[r], arena[r], half_bytes));
+  }
+  void set_timeout_ms(double ms) { for (auto& c : chans_) c->set_timeout_ms(ms); }
+  int publish(int rank, std::vector<at::Tensor> tensors, c10::optional<std::vector<double>> dst_weight, int n_readers) {
+    c10::cuda::CUDAGuard g(device_);
+    std::vector<SegSpec> segs;
+    for (auto& t : tensors) segs.push_back({t.data_ptr(), nullptr, static_cast<uint64_t>(t.nbytes()), static_cast<uint64_t>(t.numel())});
+    Round round;
+    ThrowIfError(chans_[rank]->Publish(segs, dst_weight ? dst_weight->data() : nullptr, n_readers, CurrentStream(device_), &round));
+    rounds_.push_back(round);
+    return static_cast<int>(rounds_.size()) - 1;
+  }
+  void combine(int rank, int round_id, std::vector<at::Tensor> outs, double self_w, std::vector<int> src_ranks,
+               std::vector<double> src_w, bool use_dst_weight, double post_scale) {
+    c10::cuda::CUDAGuard g(device_);
+    std::vector<SegSpec> segs;
+    for (auto& t : outs) segs.push_back({nullptr, t.data_ptr(), static_cast<uint64_t>(t.nbytes()), static_cast<uint64_t>(t.numel())});
+    ThrowIfError(chans_[rank]->PullCombine(rounds_[round_id], segs, ElemOf(outs[0]), self_w, src_ranks, src_w,
+                                           use_dst_weight, post_scale, CurrentStream(device_)));
+  }
+  void gather(int rank, int round_id, std::vector<int> src_ranks, std::vector<int> copy_src, std::vector<int64_t> arena_off,
+              std::vector<at::Tensor> outs) {
+    c10::cuda::CUDAGuard g(device_);
+    std::vector<Channel::CopySpec> copies;
+    for (size_t i = 0; i < outs.size(); ++i)
+      copies.push_back({copy_src[i], static_cast<uint64_t>(arena_off[i]), static_cast<uint64_t>(outs[i].nbytes()), outs[i].data_ptr()});
+    ThrowIfError(chans_[rank]->PullGather(rounds_[round_id], src_ranks, copies, CurrentStream(device_)));
+  }
+  // Rounds published by different ranks in the same position share version and layout.
+  std::vector<int64_t> round_offsets(int round_id) {
+    return std::vector<int64_t>(rounds_[round_id].offsets.begin(), rounds_[round_id].offsets.end());
+  }
+  py::tuple status(int rank) {
+    CommStatus s = chans_[rank]->ReadStatus();
+    return py::make_tuple(s.error, s.peer, s.want, s.seen);
+  }
+  void clear_status(int rank) { chans_[rank]->ClearStatus(); }
+
+ private:
+  int world_, device_;
+  std::vector<std::unique_ptr<Channel>> chans_;
+  std::vector<Round> rounds_;
+};
+
+std::unique_ptr<Channel> MakeIpcChannel(size_t half_bytes) {
+  Runtime& rt = Runtime::Get();
+  if (!rt.initialized()) throw std::invalid_argument(kNotInitializedError());
+  std::shared_ptr<SymmBuffer> ctrl, arena;
+  ThrowIfError(AllocateIpc(&rt.control_plane(), kChanUser, rt.device(), sizeof(ChannelCtrl), &ctrl));
+  ThrowIfError(AllocateIpc(&rt.control_plane(), kChanUser, rt.device(), half_bytes * 2, &arena));
+  return std::make_unique<Channel>(ctrl, arena, half_bytes);
+}
+
+int PubElem(const std::string& dtype) {
+  if (dtype == "float32") return kF32;
+  if (dtype == "bfloat16") return kBF16;
+  throw std::invalid_argument("published dtype must be float32 or bfloat16");
+}
+
+struct PyBucketArgs : BucketStepArgs {
+  c10::optional<at::Tensor> t_master, t_grad, t_state1, t_state2, t_state3, t_shadow;
+};
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "bluefog_b200 native runtime";
+
+  py::class_<OpSpec>(m, "OpSpec")
+      .def(py::init<>())
+      .def_readwrite("type", &OpSpec::type)
+      .def_readwrite("name", &OpSpec::name)
+      .def_readwrite("input", &OpSpec::input)
+      .def_readwrite("output", &OpSpec::output)
+      .def_readwrite("root_rank", &OpSpec::root_rank)
+      .def_readwrite("self_weight", &OpSpec::self_weight)
+      .def_readwrite("post_scale", &OpSpec::post_scale)
+      .def_readwrite("src_ranks", &OpSpec::src_ranks)
+      .def_readwrite("src_weights", &OpSpec::src_weights)
+      .def_readwrite("dst_ranks", &OpSpec::dst_ranks)
+      .def_readwrite("dst_weights", &OpSpec::dst_weights)
+      .def_readwrite("use_dst_weight", &OpSpec::use_dst_weight)
+      .def_readwrite("enable_topo_check", &OpSpec::enable_topo_check)
+      .def_readwrite("is_hierarchical", &OpSpec::is_hierarchical)
+      .def_readwrite("negotiate", &OpSpec::negotiate)
+      .def_readwrite("win_name", &OpSpec::win_name)
+      .def_readwrite("require_mutex", &OpSpec::require_mutex)
+      .def_readwrite("zero_init", &OpSpec::zero_init)
+      .def_readwrite("accumulate", &OpSpec::accumulate)
+      .def_readwrite("slot_index", &OpSpec::slot_index)
+      .def_readwrite("num_slots", &OpSpec::num_slots)
+      .def_readwrite("in_neighbors", &OpSpec::in_neighbors);
+
+  // ---- lifecycle ---------------------------------------------------------------------------
+  m.def("listen", [](const std::string& addr) {
+    int port = 0;
+    ThrowIfError(Runtime::Get().Listen(addr, &port));
+    return port;
+  });
+  m.def("init", [](int rank, int size, int local_rank, int local_size, std::vector<std::string> endpoints, int device) {
+    py::gil_scoped_release nogil;
+    ThrowIfError(Runtime::Get().Init(rank, size, local_rank, local_size, endpoints, device));
+  });
+  m.def("shutdown", [] {
+    py::gil_scoped_release nogil;
+    Runtime::Get().Shutdown();
+  });
+  m.def("is_initialized", [] { return Runtime::Get().initialized(); });
+  m.def("rank", [] { return Runtime::Get().rank(); });
+  m.def("size", [] { return Runtime::Get().size(); });
+  m.def("local_rank", [] { return Runtime::Get().local_rank(); });
+  m.def("local_size", [] { return Runtime::Get().local_size(); });
+  m.def("set_skip_negotiate_stage", [](bool v) { Runtime::Get().set_skip_negotiate(v); });
+  m.def("get_skip_negotiate_stage", [] { return Runtime::Get().skip_negotiate(); });
+  m.def("suspend", [] { Runtime::Get().Suspend(); });
+  m.def("resume", [] { Runtime::Get().Resume(); });
+  m.def("fusion_threshold", [] { return Runtime::Get().fusion_threshold(); });
+  m.def("set_fusion_threshold", [](int64_t v) { Runtime::Get().set_fusion_threshold(v); });
+  m.def("set_stall_warning_seconds", [](double s) { Runtime::Get().set_stall_warning_seconds(s); });
+  m.def("kernel_launch_count", [] { return KernelLaunchCount(); });
+
+  // ---- operations --------------------------------------------------------------------------
+  m.def("enqueue", [](OpSpec spec) { return Runtime::Get().Enqueue(std::move(spec)); });
+  m.def("poll", [](int h) { return Runtime::Get().Poll(h); });
+  m.def("wait", [](int h) {
+    Status s;
+    {
+      py::gil_scoped_release nogil;
+      s = Runtime::Get().Wait(h);
+    }
+    ThrowIfError(s);
+  });
+  m.def("release", [](int h) { Runtime::Get().Release(h); });
+  m.def("barrier_now", [] {
+    py::gil_scoped_release nogil;
+    ThrowIfError(Runtime::Get().BarrierNow());
+  });
+  m.def("allgather_bytes", [](py::bytes mine) {
+    std::string in = mine;
+    std::vector<std::string> all;
+    {
+      py::gil_scoped_release nogil;
+      ThrowIfError(Runtime::Get().AllgatherBytesNow(in, &all));
+    }
+    std::vector<py::bytes> out;
+    for (auto& s : all) out.emplace_back(s);
+    return out;
+  });
+
+  // ---- timeline / logging ------------------------------------------------------------------
+  m.def("timeline_initialized", [] { return Runtime::Get().timeline().Initialized(); });
+  m.def("timeline_start", [](const std::string& file) { return Runtime::Get().timeline().Initialize(file, Runtime::Get().size()); });
+  m.def("timeline_stop", [] { Runtime::Get().timeline().Shutdown(); });
+  m.def("timeline_start_activity", [](const std::string& tensor, const std::string& activity) {
+    auto& tl = Runtime::Get().timeline();
+    if (!tl.Initialized()) return false;
+    tl.ActivityStart(tensor, activity);
+    return true;
+  });
+  m.def("timeline_end_activity", [](const std::string& tensor) {
+    auto& tl = Runtime::Get().timeline();
+    if (!tl.Initialized()) return false;
+    tl.ActivityEnd(tensor);
+    return true;
+  });
+  m.def("timeline_span", [](const std::string& tensor, const std::string& activity, long b, long e, long lane) {
+    Runtime::Get().timeline().CompleteSpan(tensor, activity, b, e, lane);
+  });
+  m.def("timeline_now_us", [] { return Runtime::Get().timeline().NowMicros(); });
+  m.def("log", [](int level, const std::string& msg, int rank) {
+    if (level >= static_cast<int>(MinLogLevelFromEnv())) LogMessage("python", 0, static_cast<LogLevel>(level), rank) << msg;
+  });
+  m.def("log_level", [] { return static_cast<int>(MinLogLevelFromEnv()); });
+
+  // ---- windows -----------------------------------------------------------------------------
+  m.def("win_self_view", [](const std::string& name) { return Runtime::Get().windows()->SelfView(name); });
+  m.def("win_update", [](const std::string& name, c10::optional<at::Tensor> out, double self_weight, std::vector<int> src_ranks,
+                         std::vector<double> src_weights, bool reset, bool require_mutex) {
+    Runtime& rt = Runtime::Get();
+    at::Tensor view = rt.windows()->SelfView(name);
+    void* stream = nullptr;
+    if (view.defined() && view.is_cuda()) stream = CurrentStream(view.get_device());
+    at::Tensor o = out.has_value() ? *out : at::Tensor();
+    Status s;
+    {
+      py::gil_scoped_release nogil;
+      rt.timeline().ActivityStart(name, "WIN_SYNC_COMPUTE_AVERAGE");
+      s = rt.windows()->Update(name, o, self_weight, src_ranks, src_weights, reset, require_mutex, stream);
+      rt.timeline().ActivityEnd(name);
+    }
+    ThrowIfError(s);
+  });
+  m.def("win_mutex_acquire", [](const std::string& name, std::vector<int> ranks, bool for_self) {
+    py::gil_scoped_release nogil;
+    ThrowIfError(Runtime::Get().windows()->MutexAcquire(name, ranks, for_self));
+  });
+  m.def("win_mutex_release", [](const std::string& name, std::vector<int> ranks, bool for_self) {
+    ThrowIfError(Runtime::Get().windows()->MutexRelease(name, ranks, for_self));
+  });
+  m.def("win_versions", [](const std::string& name) {
+    std::vector<int64_t> v;
+    ThrowIfError(Runtime::Get().windows()->Versions(name, &v));
+    return v;
+  });
+  m.def("win_get_p", [](const std::string& name) {
+    double p = 0;
+    ThrowIfError(Runtime::Get().windows()->GetAssociatedP(name, &p));
+    return p;
+  });
+  m.def("win_set_p", [](const std::string& name, double p) { ThrowIfError(Runtime::Get().windows()->SetAssociatedP(name, p)); });
+  m.def("win_set_with_p", [](bool v) { Runtime::Get().windows()->set_with_associated_p(v); });
+  m.def("win_get_with_p", [] { return Runtime::Get().windows()->with_associated_p(); });
+  m.def("win_names", [] { return Runtime::Get().windows() ? Runtime::Get().windows()->Names() : std::vector<std::string>(); });
+  m.def("win_count", [] { return Runtime::Get().windows() ? Runtime::Get().windows()->Count() : size_t(0); });
+
+  // ---- kernels on explicit buffers -----------------------------------------------------------
+  m.def("scale_", [](at::Tensor t, double s) {
+    TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "scale_ needs a contiguous CUDA tensor");
+    c10::cuda::CUDAGuard g(t.get_device());
+    cudaError_t e = LaunchScale(t.data_ptr(), static_cast<unsigned long long>(t.numel()), s, ElemOf(t), CurrentStream(t.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "scale kernel launch failed: ", cudaGetErrorString(e));
+  });
+
+  py::class_<LocalWorld>(m, "LocalWorld")
+      .def(py::init<int, int64_t, int>(), py::arg("world"), py::arg("half_bytes"), py::arg("device") = 0)
+      .def("set_timeout_ms", &LocalWorld::set_timeout_ms)
+      .def("publish", &LocalWorld::publish, py::arg("rank"), py::arg("tensors"), py::arg("dst_weight") = py::none(), py::arg("n_readers") = 0)
+      .def("combine", &LocalWorld::combine)
+      .def("gather", &LocalWorld::gather)
+      .def("round_offsets", &LocalWorld::round_offsets)
+      .def("status", &LocalWorld::status)
+      .def("clear_status", &LocalWorld::clear_status);
+
+  py::class_<PyBucketArgs>(m, "BucketStepArgs")
+      .def(py::init<>())
+      .def_readwrite("mode", &PyBucketArgs::mode)
+      .def_readwrite("opt", &PyBucketArgs::opt)
+      .def_readwrite("nesterov", &PyBucketArgs::nesterov)
+      .def_readwrite("adamw", &PyBucketArgs::adamw)
+      .def_readwrite("amsgrad", &PyBucketArgs::amsgrad)
+      .def_readwrite("first_step", &PyBucketArgs::first_step)
+      .def_readwrite("maximize", &PyBucketArgs::maximize)
+      .def_readwrite("lr", &PyBucketArgs::lr)
+      .def_readwrite("momentum", &PyBucketArgs::momentum)
+      .def_readwrite("dampening", &PyBucketArgs::dampening)
+      .def_readwrite("weight_decay", &PyBucketArgs::weight_decay)
+      .def_readwrite("beta1", &PyBucketArgs::beta1)
+      .def_readwrite("beta2", &PyBucketArgs::beta2)
+      .def_readwrite("eps", &PyBucketArgs::eps)
+      .def_readwrite("bias1", &PyBucketArgs::bias1)
+      .def_readwrite("bias2", &PyBucketArgs::bias2)
+      .def_readwrite("grad_scale", &PyBucketArgs::grad_scale)
+      .def_readwrite("self_weight", &PyBucketArgs::self_weight)
+      .def_readwrite("post_scale", &PyBucketArgs::post_scale)
+      .def_readwrite("src_ranks", &PyBucketArgs::src_ranks)
+      .def_readwrite("src_weights", &PyBucketArgs::src_weights)
+      .def_readwrite("n_readers", &PyBucketArgs::n_readers)
+      .def_readwrite("master", &PyBucketArgs::t_master)
+      .def_readwrite("grad", &PyBucketArgs::t_grad)
+      .def_readwrite("state1", &PyBucketArgs::t_state1)
+      .def_readwrite("state2", &PyBucketArgs::t_state2)
+      .def_readwrite("state3", &PyBucketArgs::t_state3)
+      .def_readwrite("shadow", &PyBucketArgs::t_shadow);
+
+  py::class_<Bucket>(m, "Bucket")
+      .def_static("create", [](int64_t numel, const std::string& pub_dtype) {
+        const int pe = PubElem(pub_dtype);
+        return std::make_unique<Bucket>(MakeIpcChannel(Bucket::PubBytes(numel, pe)), static_cast<uint64_t>(numel), pe);
+      })
+      .def_static("create_local", [](int world, int64_t numel, const std::string& pub_dtype, int device) {
+        const int pe = PubElem(pub_dtype);
+        const size_t half = Bucket::PubBytes(numel, pe);
+        std::vector<std::shared_ptr<SymmBuffer>> ctrl, arena;
+        ThrowIfError(AllocateLocal(world, device, sizeof(ChannelCtrl), &ctrl));
+        ThrowIfError(AllocateLocal(world, device, half * 2, &arena));
+        std::vector<std::unique_ptr<Bucket>> out;
+        for (int r = 0; r < world; ++r)
+          out.push_back(std::make_unique<Bucket>(std::make_unique<Channel>(ctrl[r], arena[r], half), static_cast<uint64_t>(numel), pe));
+        return out;
+      }, py::arg("world"), py::arg("numel"), py::arg("pub_dtype"), py::arg("device") = 0)
+      .def("numel", &Bucket::numel)
+      .def("versions_published", &Bucket::versions_published)
+      .def("set_timeout_ms", [](Bucket& b, double ms) { b.channel()->set_timeout_ms(ms); })
+      .def("status", [](Bucket& b) {
+        CommStatus s = b.channel()->ReadStatus();
+        return py::make_tuple(s.error, s.peer, s.want, s.seen);
+      })
+      .def("check", [](Bucket& b) { ThrowIfError(b.channel()->StatusToError()); })
+      .def("step", [](Bucket& b, PyBucketArgs& a, int64_t stream) {
+        auto check = [&](const c10::optional<at::Tensor>& t, const char* what) {
+          if (t.has_value() && t->defined()) {
+            TORCH_CHECK(t->is_cuda() && t->is_contiguous(), what, " must be a contiguous CUDA tensor");
+            TORCH_CHECK(static_cast<uint64_t>(t->numel()) >= b.numel(), what, " is smaller than the bucket");
+          }
+        };
+        check(a.t_master, "master"); check(a.t_grad, "grad"); check(a.t_state1, "state1");
+        check(a.t_state2, "state2"); check(a.t_state3, "state3"); check(a.t_shadow, "shadow");
+        if (a.t_master.has_value() && a.t_master->defined()) TORCH_CHECK(a.t_master->scalar_type() == at::kFloat, "master must be float32");
+        a.BucketStepArgs::master = PtrOrNull(a.t_master);
+        a.BucketStepArgs::grad = PtrOrNull(a.t_grad);
+        a.BucketStepArgs::state1 = PtrOrNull(a.t_state1);
+        a.BucketStepArgs::state2 = PtrOrNull(a.t_state2);
+        a.BucketStepArgs::state3 = PtrOrNull(a.t_state3);
+        a.BucketStepArgs::shadow = PtrOrNull(a.t_shadow);
+        if (a.t_grad.has_value() && a.t_grad->defined()) {
+          TORCH_CHECK(a.t_grad->scalar_type() == at::kFloat || a.t_grad->scalar_type() == at::kBFloat16, "grad must be float32 or bfloat16");
+          a.grad_elem = a.t_grad->scalar_type() == at::kBFloat16 ? kBF16 : kF32;
+        }
+        if (a.t_shadow.has_value() && a.t_shadow->defined()) TORCH_CHECK(a.t_shadow->scalar_type() == at::kBFloat16, "shadow must be bfloat16");
+        int device = b.channel()->arena()->device;
+        c10::cuda::CUDAGuard g(device);
+        cudaStream_t st = stream == 0 ? CurrentStream(device) : reinterpret_cast<cudaStream_t>(stream);
+        ThrowIfError(b.Step(a, st));
+      }, py::arg("args"), py::arg("stream") = 0);
+}

@@ -1,0 +1,1045 @@
+#include "runtime.h"
+
+#include <poll.h>
+#include <sys/eventfd.h>
+#include <unistd.h>
+
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include "../cuda/gpu_channel.h"
+#include "../cuda/symm_mem.h"
+#include "logging.h"
+#include "windows.h"
+
+namespace bfb {
+
+namespace {
+
+using Clock = std::chrono::steady_clock;
+
+double EnvDouble(const char* name, double fallback) {
+  const char* v = std::getenv(name);
+  return v ? std::atof(v) : fallback;
+}
+
+uint64_t Fnv(uint64_t h, const void* data, size_t n) {
+  const unsigned char* p = static_cast<const unsigned char*>(data);
+  for (size_t i = 0; i < n; ++i) {
+    h ^= p[i];
+    h *= 1099511628211ull;
+  }
+  return h;
+}
+
+int ToElem(at::ScalarType t) {
+  switch (t) {
+    case at::kFloat: return kF32;
+    case at::kDouble: return kF64;
+    case at::kHalf: return kF16;
+    case at::kBFloat16: return kBF16;
+    case at::kInt: return kI32;
+    case at::kLong: return kI64;
+    default: return -1;
+  }
+}
+
+bool IsReduceOp(OpType t) {
+  return t == OpType::ALLREDUCE || t == OpType::NEIGHBOR_ALLREDUCE || t == OpType::PAIR_GOSSIP;
+}
+
+const char* ProcActivity(OpType t) {
+  switch (t) {
+    case OpType::ALLREDUCE: return "PROC_ALLREDUCE";
+    case OpType::ALLGATHER: return "PROC_ALLGATHER";
+    case OpType::BROADCAST: return "PROC_BROADCAST";
+    case OpType::NEIGHBOR_ALLREDUCE: return "PROC_NEIGHBOR_ALLREDUCE";
+    case OpType::NEIGHBOR_ALLGATHER: return "PROC_NEIGHBOR_ALLGATHER";
+    case OpType::PAIR_GOSSIP: return "PROC_PAIR_GOSSIP";
+    case OpType::WIN_CREATE: return "WIN_CREATE";
+    case OpType::WIN_FREE: return "WIN_FREE";
+    case OpType::WIN_PUT: return "WIN_PUT";
+    case OpType::WIN_GET: return "WIN_GET";
+    case OpType::WIN_ACCUMULATE: return "WIN_ACCUMULATE";
+    case OpType::BARRIER: return "PROC_BARRIER";
+    default: return "PROC_UNKNOWN";
+  }
+}
+
+}  // namespace
+
+DataType ToDataType(at::ScalarType t, bool* ok) {
+  *ok = true;
+  switch (t) {
+    case at::kByte: return DataType::UINT8;
+    case at::kChar: return DataType::INT8;
+    case at::kShort: return DataType::INT16;
+    case at::kInt: return DataType::INT32;
+    case at::kLong: return DataType::INT64;
+    case at::kHalf: return DataType::FLOAT16;
+    case at::kBFloat16: return DataType::BFLOAT16;
+    case at::kFloat: return DataType::FLOAT32;
+    case at::kDouble: return DataType::FLOAT64;
+    case at::kBool: return DataType::BOOL;
+    default: *ok = false; return DataType::BYTE;
+  }
+}
+
+uint64_t NeighborSignature(const OpSpec& spec) {
+  uint64_t h = 1469598103934665603ull;
+  auto add_vec_i = [&](const std::vector<int>& v) {
+    uint64_t n = v.size();
+    h = Fnv(h, &n, sizeof(n));
+    if (!v.empty()) h = Fnv(h, v.data(), v.size() * sizeof(int));
+  };
+  auto add_vec_d = [&](const std::vector<double>& v) {
+    uint64_t n = v.size();
+    h = Fnv(h, &n, sizeof(n));
+    if (!v.empty()) h = Fnv(h, v.data(), v.size() * sizeof(double));
+  };
+  add_vec_i(spec.src_ranks);
+  add_vec_d(spec.src_weights);
+  add_vec_i(spec.dst_ranks);
+  add_vec_d(spec.dst_weights);
+  h = Fnv(h, &spec.self_weight, sizeof(double));
+  h = Fnv(h, &spec.post_scale, sizeof(double));
+  unsigned char flags = (spec.use_dst_weight ? 1 : 0) | (spec.enable_topo_check ? 2 : 0);
+  h = Fnv(h, &flags, 1);
+  return h;
+}
+
+Runtime& Runtime::Get() {
+  static Runtime* rt = new Runtime();  // leaked on purpose: outlives static destructors
+  return *rt;
+}
+
+// ----------------------------------------------------------------------------------------
+// lifecycle
+// ----------------------------------------------------------------------------------------
+Status Runtime::Listen(const std::string& bind_addr, int* port) { return cp_.Listen(bind_addr, port); }
+
+Status Runtime::Init(int rank, int size, int local_rank, int local_size,
+                     const std::vector<std::string>& endpoints, int device) {
+  if (initialized_.load()) return Status::OK();
+  rank_ = rank;
+  size_ = size;
+  local_rank_ = local_rank;
+  local_size_ = local_size;
+  device_ = device;
+  if (size > kMaxWorld) return Status::InvalidArgument("at most 64 ranks are supported");
+  Status s = cp_.Connect(rank, size, endpoints, EnvDouble("BLUEFOG_START_TIMEOUT", 600.0));
+  if (!s.ok()) return s;
+  fusion_threshold_ = static_cast<int64_t>(EnvDouble("BLUEFOG_FUSION_THRESHOLD", 8.0 * 1024 * 1024));
+  cycle_time_ms_ = EnvDouble("BLUEFOG_CYCLE_TIME", 0.5);
+  stall_warning_s_ = EnvDouble("BLUEFOG_STALL_WARNING_SECONDS", 60.0);
+  if (const char* prefix = std::getenv("BLUEFOG_TIMELINE"))
+    timeline_.Initialize(std::string(prefix) + std::to_string(rank) + ".json", size);
+  // A job-wide tag for shared-memory names: rank 0's pid and start time, shared with everyone.
+  std::string tag;
+  if (rank == 0) {
+    char buf[64];
+    std::snprintf(buf, sizeof(buf), "%d_%lld", static_cast<int>(getpid()),
+                  static_cast<long long>(std::chrono::duration_cast<std::chrono::microseconds>(
+                                             std::chrono::system_clock::now().time_since_epoch()).count() % 100000000));
+    tag = buf;
+  }
+  s = cp_.BroadcastBytes(kChanUser, 0, &tag);
+  if (!s.ok()) return s;
+  windows_ = std::make_unique<WindowManager>(&cp_, rank, size, tag);
+  windows_->mutex_timeout_s = EnvDouble("BLUEFOG_B200_MUTEX_TIMEOUT_SECONDS", 120.0);
+  finalizers_.create(static_cast<int>(EnvDouble("BLUEFOG_NUM_FINALIZER_THREADS", 1)));
+  wake_fd_ = eventfd(0, EFD_NONBLOCK);
+  shutdown_requested_.store(false);
+  loop_exited_.store(false);
+  shutdown_sent_ = false;
+  any_shutdown_ = false;
+  last_stall_check_ = Clock::now();
+  initialized_.store(true);
+  thread_ = std::thread([this] { Loop(); });
+  return Status::OK();
+}
+
+void Runtime::Wake() {
+  if (wake_fd_ >= 0) {
+    uint64_t one = 1;
+    ssize_t r = ::write(wake_fd_, &one, sizeof(one));
+    (void)r;
+  }
+}
+
+void Runtime::Shutdown() {
+  if (!initialized_.load()) return;
+  shutdown_requested_.store(true);
+  Wake();
+  if (thread_.joinable()) thread_.join();
+  finalizers_.reset();
+  if (device_ >= 0) {
+    cudaSetDevice(device_);
+    cudaDeviceSynchronize();
+  }
+  if (windows_) {
+    windows_.reset();
+  }
+  gpu_channel_.reset();
+  gpu_ctrl_.reset();
+  if (comm_stream_) {
+    cudaStreamDestroy(static_cast<cudaStream_t>(comm_stream_));
+    comm_stream_ = nullptr;
+  }
+  timeline_.Shutdown();
+  cp_.Close();
+  if (wake_fd_ >= 0) {
+    ::close(wake_fd_);
+    wake_fd_ = -1;
+  }
+  message_table_.clear();
+  ready_names_.clear();
+  initialized_.store(false);
+}
+
+// ----------------------------------------------------------------------------------------
+// handles
+// ----------------------------------------------------------------------------------------
+void Runtime::MarkDone(int handle, const Status& s) {
+  {
+    std::lock_guard<std::mutex> g(handle_mu_);
+    auto it = handles_.find(handle);
+    if (it != handles_.end()) it->second = s;
+  }
+  handle_cv_.notify_all();
+}
+
+bool Runtime::Poll(int handle) {
+  std::lock_guard<std::mutex> g(handle_mu_);
+  auto it = handles_.find(handle);
+  if (it == handles_.end()) return true;
+  return !it->second.in_progress();
+}
+
+Status Runtime::Wait(int handle) {
+  std::unique_lock<std::mutex> lk(handle_mu_);
+  auto it = handles_.find(handle);
+  if (it == handles_.end()) return Status::InvalidArgument("unknown handle " + std::to_string(handle));
+  handle_cv_.wait(lk, [&] { return !handles_[handle].in_progress(); });
+  Status s = handles_[handle];
+  handles_.erase(handle);
+  return s;
+}
+
+void Runtime::Release(int handle) {
+  std::lock_guard<std::mutex> g(handle_mu_);
+  handles_.erase(handle);
+}
+
+int Runtime::Enqueue(OpSpec spec) {
+  int handle;
+  {
+    std::lock_guard<std::mutex> g(handle_mu_);
+    handle = next_handle_++;
+    handles_[handle] = Status::InProgress();
+  }
+  if (!initialized_.load() || loop_exited_.load()) {
+    MarkDone(handle, initialized_.load() ? Status::Aborted(kShutDownError()) : Status::PreconditionError(kNotInitializedError()));
+    return handle;
+  }
+  if (suspended_.load()) {
+    MarkDone(handle, Status::PreconditionError(kSuspendError()));
+    return handle;
+  }
+  Entry e;
+  e.handle = handle;
+  e.enqueued = Clock::now();
+  // Work queued on the producer's stream must be finished before the payload is read.
+  const at::Tensor* probe = spec.input.has_value() ? &*spec.input : (spec.output.has_value() ? &*spec.output : nullptr);
+  if (probe != nullptr && probe->is_cuda()) {
+    c10::cuda::CUDAGuard guard(probe->get_device());
+    cudaEvent_t ev;
+    cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    cudaEventRecord(ev, c10::cuda::getCurrentCUDAStream(probe->get_device()).stream());
+    e.ready_event = ev;
+  }
+  timeline_.ActivityStart(spec.name, std::string("ENQUEUE_") + OpTypeName(static_cast<OpType>(spec.type)));
+  e.spec = std::move(spec);
+  {
+    std::lock_guard<std::mutex> g(queue_mu_);
+    queue_.push_back(std::move(e));
+  }
+  Wake();
+  return handle;
+}
+
+Status Runtime::BarrierNow() {
+  std::lock_guard<std::mutex> g(user_chan_mu_);
+  return cp_.Barrier(kChanUser);
+}
+
+Status Runtime::AllgatherBytesNow(const std::string& mine, std::vector<std::string>* all) {
+  std::lock_guard<std::mutex> g(user_chan_mu_);
+  return cp_.AllgatherBytes(kChanUser, mine, all);
+}
+
+// ----------------------------------------------------------------------------------------
+// background loop
+// ----------------------------------------------------------------------------------------
+void Runtime::DrainLocalQueue(RequestList* outgoing, std::vector<std::string>* immediate) {
+  std::deque<Entry> local;
+  {
+    std::lock_guard<std::mutex> g(queue_mu_);
+    local.swap(queue_);
+  }
+  for (auto& e : local) {
+    const std::string name = e.spec.name;
+    {
+      std::lock_guard<std::mutex> g(table_mu_);
+      if (table_.count(name)) {
+        timeline_.ActivityEnd(name);
+        MarkDone(e.handle, Status::InvalidArgument(DuplicateNameError(name)));
+        if (e.ready_event) cudaEventDestroy(static_cast<cudaEvent_t>(e.ready_event));
+        continue;
+      }
+    }
+    const bool negotiate = e.spec.negotiate && !skip_negotiate_.load() && size_ > 1;
+    if (negotiate) {
+      Request q;
+      q.rank = rank_;
+      q.type = static_cast<OpType>(e.spec.type);
+      q.name = name;
+      q.root_rank = e.spec.root_rank;
+      q.is_hierarchical = e.spec.is_hierarchical;
+      q.neighbor_sig = NeighborSignature(e.spec);
+      const at::Tensor* t = e.spec.input.has_value() ? &*e.spec.input : (e.spec.output.has_value() ? &*e.spec.output : nullptr);
+      if (t != nullptr) {
+        bool ok;
+        q.dtype = ToDataType(t->scalar_type(), &ok);
+        q.device = t->is_cuda() ? t->get_device() : -1;
+        q.shape = t->sizes().vec();
+        q.nbytes = static_cast<uint64_t>(t->numel()) * t->element_size();
+      }
+      outgoing->requests.push_back(std::move(q));
+    } else {
+      immediate->push_back(name);
+    }
+    std::lock_guard<std::mutex> g(table_mu_);
+    table_.emplace(name, std::move(e));
+  }
+}
+
+void Runtime::Loop() {
+  if (device_ >= 0) cudaSetDevice(device_);
+  const bool coordinator = rank_ == 0;
+  std::vector<struct pollfd> pfds;
+  while (true) {
+    pfds.clear();
+    pfds.push_back({wake_fd_, POLLIN, 0});
+    if (size_ > 1) {
+      if (coordinator) {
+        for (int r = 1; r < size_; ++r) pfds.push_back({cp_.fd(kChanNegotiate, r), POLLIN, 0});
+      } else {
+        pfds.push_back({cp_.fd(kChanNegotiate, 0), POLLIN, 0});
+      }
+    }
+    int timeout_ms = 200;
+    poll(pfds.data(), pfds.size(), timeout_ms);
+    if (pfds[0].revents & POLLIN) {
+      uint64_t junk;
+      while (::read(wake_fd_, &junk, sizeof(junk)) > 0) {}
+    }
+    if (suspended_.load() && !shutdown_requested_.load()) continue;
+
+    RequestList outgoing;
+    std::vector<std::string> immediate;
+    DrainLocalQueue(&outgoing, &immediate);
+    // Operations that need no agreement run right away, in local order.
+    for (const auto& name : immediate) {
+      Response r;
+      {
+        std::lock_guard<std::mutex> g(table_mu_);
+        r.type = static_cast<OpType>(table_[name].spec.type);
+      }
+      r.names = {name};
+      ExecuteResponse(r);
+    }
+    if (shutdown_requested_.load() && !shutdown_sent_) {
+      outgoing.shutdown = true;
+      shutdown_sent_ = true;
+    }
+    bool fatal = false;
+    if (size_ == 1) {
+      if (outgoing.shutdown) break;
+      continue;
+    }
+    if (coordinator) {
+      if (!outgoing.requests.empty() || outgoing.shutdown) CoordinatorHandle(outgoing, 0);
+      for (size_t i = 1; i < pfds.size(); ++i) {
+        if (!(pfds[i].revents & (POLLIN | POLLHUP | POLLERR))) continue;
+        const int from = static_cast<int>(i);  // pfds[i] belongs to rank i
+        std::string bytes;
+        Status s = cp_.RecvMsg(kChanNegotiate, from, &bytes, 30.0);
+        RequestList list;
+        if (!s.ok() || !RequestList::Parse(bytes, &list)) {
+          BFLOG(WARNING, rank_) << "lost contact with rank " << from << ": " << s.reason() << "; shutting down";
+          any_shutdown_ = true;
+          continue;
+        }
+        CoordinatorHandle(list, from);
+      }
+      ResponseList responses = CoordinatorBuildResponses();
+      if (any_shutdown_) responses.shutdown = true;
+      if (!responses.responses.empty() || responses.shutdown) {
+        const std::string bytes = responses.Serialize();
+        for (int r = 1; r < size_; ++r) {
+          Status s = cp_.SendMsg(kChanNegotiate, r, bytes);
+          if (!s.ok()) BFLOG(DEBUG, rank_) << "could not send responses to rank " << r << ": " << s.reason();
+        }
+        ExecuteResponseList(responses);
+        if (responses.shutdown) break;
+      }
+      CheckStalled();
+    } else {
+      if (!outgoing.requests.empty() || outgoing.shutdown) {
+        Status s = cp_.SendMsg(kChanNegotiate, 0, outgoing.Serialize());
+        if (!s.ok()) fatal = true;
+      }
+      if (!fatal && (pfds.back().revents & (POLLIN | POLLHUP | POLLERR))) {
+        std::string bytes;
+        Status s = cp_.RecvMsg(kChanNegotiate, 0, &bytes, 30.0);
+        ResponseList list;
+        if (!s.ok() || !ResponseList::Parse(bytes, &list)) {
+          fatal = true;
+        } else {
+          ExecuteResponseList(list);
+          if (list.shutdown) break;
+        }
+      }
+      if (fatal) {
+        BFLOG(DEBUG, rank_) << "lost contact with the coordinator; shutting down";
+        break;
+      }
+    }
+  }
+  loop_exited_.store(true);
+  FailAll(Status::Aborted(kShutDownError()));
+}
+
+void Runtime::FailAll(const Status& s) {
+  std::vector<Entry> entries;
+  {
+    std::lock_guard<std::mutex> g(table_mu_);
+    for (auto& kv : table_) entries.push_back(std::move(kv.second));
+    table_.clear();
+  }
+  {
+    std::lock_guard<std::mutex> g(queue_mu_);
+    for (auto& e : queue_) entries.push_back(std::move(e));
+    queue_.clear();
+  }
+  for (auto& e : entries) {
+    timeline_.ActivityEnd(e.spec.name);
+    if (e.ready_event) cudaEventDestroy(static_cast<cudaEvent_t>(e.ready_event));
+    MarkDone(e.handle, s);
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// coordinator
+// ----------------------------------------------------------------------------------------
+void Runtime::CoordinatorHandle(const RequestList& list, int from_rank) {
+  if (list.shutdown) any_shutdown_ = true;
+  for (const auto& q : list.requests) {
+    auto& pt = message_table_[q.name];
+    if (pt.requests.empty()) {
+      pt.requests.resize(size_);
+      pt.seen.assign(size_, false);
+      pt.first_seen = Clock::now();
+    }
+    if (pt.seen[from_rank]) continue;  // duplicate submission is rejected on the sender
+    pt.requests[from_rank] = q;
+    pt.seen[from_rank] = true;
+    if (++pt.count == size_) ready_names_.push_back(q.name);
+  }
+}
+
+Response Runtime::ConstructResponse(const std::string& name, PendingTensor& pt) {
+  Response resp;
+  resp.names = {name};
+  const Request& first = pt.requests[0];
+  resp.type = first.type;
+  StrBuilder err;
+  bool bad = false;
+  for (int r = 1; r < size_ && !bad; ++r) {
+    const Request& q = pt.requests[r];
+    if (q.type != first.type) {
+      err << "Mismatched operations: rank 0 requested " << OpTypeName(first.type) << " but rank " << r
+          << " requested " << OpTypeName(q.type) << ".";
+      bad = true;
+    } else if (q.dtype != first.dtype) {
+      err << "Mismatched data types: rank 0 has " << DataTypeName(first.dtype) << " but rank " << r << " has "
+          << DataTypeName(q.dtype) << ".";
+      bad = true;
+    } else if ((q.device < 0) != (first.device < 0)) {
+      err << "Mismatched devices: rank 0 holds the tensor on " << (first.device < 0 ? "CPU" : "GPU")
+          << " but rank " << r << " on " << (q.device < 0 ? "CPU" : "GPU") << ".";
+      bad = true;
+    } else if (q.is_hierarchical != first.is_hierarchical) {
+      err << "Mismatched hierarchical flag between rank 0 and rank " << r << ".";
+      bad = true;
+    }
+  }
+  const OpType t = first.type;
+  if (!bad && (t == OpType::BROADCAST)) {
+    for (int r = 1; r < size_ && !bad; ++r)
+      if (pt.requests[r].root_rank != first.root_rank) {
+        err << "Mismatched root ranks: rank 0 specified " << first.root_rank << " but rank " << r
+            << " specified " << pt.requests[r].root_rank << ".";
+        bad = true;
+      }
+  }
+  if (!bad && (t == OpType::ALLREDUCE || t == OpType::BROADCAST || t == OpType::NEIGHBOR_ALLREDUCE ||
+               t == OpType::WIN_CREATE)) {
+    for (int r = 1; r < size_ && !bad; ++r)
+      if (pt.requests[r].shape != first.shape) {
+        err << "Mismatched tensor shapes between rank 0 and rank " << r << " for " << OpTypeName(t) << ".";
+        bad = true;
+      }
+  }
+  if (!bad && (t == OpType::ALLGATHER || t == OpType::NEIGHBOR_ALLGATHER)) {
+    if (first.shape.empty()) {
+      err << "Rank zero tried to gather a rank-zero tensor.";
+      bad = true;
+    }
+    for (int r = 1; r < size_ && !bad; ++r) {
+      const auto& sh = pt.requests[r].shape;
+      if (sh.size() != first.shape.size()) {
+        err << "Mismatched tensor ranks between rank 0 and rank " << r << " for " << OpTypeName(t) << ".";
+        bad = true;
+        break;
+      }
+      for (size_t d = 1; d < sh.size(); ++d)
+        if (sh[d] != first.shape[d]) {
+          err << "Mismatched trailing dimensions between rank 0 and rank " << r << " for " << OpTypeName(t) << ".";
+          bad = true;
+          break;
+        }
+    }
+    if (!bad)
+      for (int r = 0; r < size_; ++r) resp.first_dims.push_back(pt.requests[r].shape[0]);
+  }
+  for (int r = 0; r < size_; ++r) resp.devices.push_back(pt.requests[r].device);
+  if (bad) {
+    resp.type = OpType::ERROR;
+    resp.error_message = err.str();
+  }
+  return resp;
+}
+
+ResponseList Runtime::CoordinatorBuildResponses() {
+  ResponseList out;
+  while (!ready_names_.empty()) {
+    const std::string name = ready_names_.front();
+    ready_names_.pop_front();
+    auto it = message_table_.find(name);
+    if (it == message_table_.end()) continue;
+    PendingTensor pt = std::move(it->second);
+    message_table_.erase(it);
+    Response resp = ConstructResponse(name, pt);
+    // Fusion: keep appending following ready tensors of the same kind while they fit.
+    if (resp.type == OpType::ALLREDUCE || resp.type == OpType::NEIGHBOR_ALLREDUCE) {
+      uint64_t total = pt.requests[0].nbytes;
+      while (!ready_names_.empty()) {
+        const std::string& next = ready_names_.front();
+        auto nit = message_table_.find(next);
+        if (nit == message_table_.end()) break;
+        PendingTensor& np = nit->second;
+        const Request& a = pt.requests[0];
+        const Request& b = np.requests[0];
+        bool same = b.type == a.type && b.dtype == a.dtype && (b.device < 0) == (a.device < 0) &&
+                    b.is_hierarchical == a.is_hierarchical && total + b.nbytes <= static_cast<uint64_t>(fusion_threshold_);
+        for (int r = 0; r < size_ && same; ++r) same = np.requests[r].neighbor_sig == pt.requests[r].neighbor_sig;
+        if (!same) break;
+        Response probe = ConstructResponse(next, np);
+        if (probe.type == OpType::ERROR) break;
+        total += b.nbytes;
+        resp.names.push_back(next);
+        message_table_.erase(nit);
+        ready_names_.pop_front();
+      }
+    }
+    out.responses.push_back(std::move(resp));
+  }
+  return out;
+}
+
+std::vector<std::string> Runtime::StalledTensors() {
+  std::vector<std::string> out;
+  for (auto& kv : message_table_) out.push_back(kv.first);
+  return out;
+}
+
+void Runtime::CheckStalled() {
+  auto now = Clock::now();
+  if (std::chrono::duration<double>(now - last_stall_check_).count() < std::min(stall_warning_s_, 5.0)) return;
+  last_stall_check_ = now;
+  bool header = false;
+  for (auto& kv : message_table_) {
+    const double waited = std::chrono::duration<double>(now - kv.second.first_seen).count();
+    if (waited < stall_warning_s_) continue;
+    if (!header) {
+      BFLOG(WARNING) << "One or more tensors were submitted to be reduced, gathered or broadcasted by a subset "
+                        "of ranks and are waiting for the remainder for more than " << stall_warning_s_
+                     << " seconds. This may indicate that different ranks are trying to submit different "
+                        "tensors or that only a subset of ranks is submitting tensors, which will cause a deadlock.";
+      header = true;
+    }
+    StrBuilder os;
+    os << kv.first << " [missing ranks:";
+    for (int r = 0; r < size_; ++r)
+      if (!kv.second.seen[r]) os << " " << r;
+    os << "]";
+    BFLOG(WARNING) << os.str();
+    kv.second.first_seen = now;  // warn again after another period
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// execution
+// ----------------------------------------------------------------------------------------
+void Runtime::ExecuteResponseList(const ResponseList& list) {
+  for (const auto& r : list.responses) ExecuteResponse(r);
+}
+
+void Runtime::ExecuteResponse(const Response& resp) {
+  std::vector<Entry> entries;
+  {
+    std::lock_guard<std::mutex> g(table_mu_);
+    for (const auto& n : resp.names) {
+      auto it = table_.find(n);
+      if (it == table_.end()) continue;  // possible after a local failure
+      entries.push_back(std::move(it->second));
+      table_.erase(it);
+    }
+  }
+  if (entries.empty()) return;
+  if (resp.type == OpType::ERROR) {
+    FinishEntries(entries, Status::PreconditionError(resp.error_message), nullptr);
+    return;
+  }
+  ExecuteEntries(entries, resp);
+}
+
+void Runtime::FinishEntries(std::vector<Entry>& entries, const Status& s, void* done_event) {
+  if (done_event == nullptr || !s.ok()) {
+    if (done_event) cudaEventDestroy(static_cast<cudaEvent_t>(done_event));
+    for (auto& e : entries) {
+      timeline_.ActivityEnd(e.spec.name);  // ENQUEUE_*
+      if (e.ready_event) cudaEventDestroy(static_cast<cudaEvent_t>(e.ready_event));
+      MarkDone(e.handle, s);
+    }
+    return;
+  }
+  // GPU work in flight: a finalizer thread waits for the completion event, converts a device
+  // timeout into an error, and only then completes the handles.
+  std::vector<int> handles;
+  std::vector<std::string> names;
+  std::vector<void*> ready;
+  for (auto& e : entries) {
+    handles.push_back(e.handle);
+    names.push_back(e.spec.name);
+    ready.push_back(e.ready_event);
+  }
+  // Keep the tensors alive until the kernels are done.
+  auto keep = std::make_shared<std::vector<Entry>>(std::move(entries));
+  const int device = device_;
+  Channel* chan = gpu_channel_.get();
+  finalizers_.execute([this, handles, names, ready, keep, done_event, device, chan] {
+    cudaSetDevice(device);
+    cudaError_t err = cudaEventSynchronize(static_cast<cudaEvent_t>(done_event));
+    cudaEventDestroy(static_cast<cudaEvent_t>(done_event));
+    Status s = err == cudaSuccess ? Status::OK() : Status::UnknownError("CUDA error: " + CudaErrorString(err));
+    if (s.ok() && chan != nullptr) s = chan->StatusToError();
+    for (size_t i = 0; i < handles.size(); ++i) {
+      timeline_.ActivityEnd(names[i]);
+      if (ready[i]) cudaEventDestroy(static_cast<cudaEvent_t>(ready[i]));
+      MarkDone(handles[i], s);
+    }
+    keep->clear();
+  });
+}
+
+Status Runtime::TopoCheck(const OpSpec& spec) {
+  // Every rank publishes who it sends to and who it receives from; the send matrix must
+  // be the transpose of the receive matrix (reference: mpi_controller.cc:364-417).
+  std::string mine(2 * size_, 0);
+  for (int d : spec.dst_ranks)
+    if (d >= 0 && d < size_) mine[d] = 1;
+  for (int s : spec.src_ranks)
+    if (s >= 0 && s < size_) mine[size_ + s] = 1;
+  std::vector<std::string> all;
+  Status s = cp_.AllgatherBytes(kChanData, mine, &all);
+  if (!s.ok()) return s;
+  for (int i = 0; i < size_; ++i)
+    for (int j = 0; j < size_; ++j)
+      if (all[i][j] != all[j][size_ + i])
+        return Status::InvalidArgument(
+            "Send and recv neighbors dont' match in neighbor communication: rank " + std::to_string(i) +
+            (all[i][j] ? " sends to rank " : " does not send to rank ") + std::to_string(j) + " but rank " +
+            std::to_string(j) + (all[j][size_ + i] ? " expects" : " does not expect") + " to receive from it.");
+  return Status::OK();
+}
+
+void Runtime::ExecuteEntries(std::vector<Entry>& entries, const Response& resp) {
+  const OpType type = static_cast<OpType>(entries[0].spec.type);
+  for (auto& e : entries) timeline_.ActivityStart(e.spec.name, ProcActivity(type));
+  auto end_proc = [&] { for (auto& e : entries) timeline_.ActivityEnd(e.spec.name); };
+
+  if (type == OpType::BARRIER) {
+    Status s = size_ > 1 ? cp_.Barrier(kChanData) : Status::OK();
+    end_proc();
+    FinishEntries(entries, s, nullptr);
+    return;
+  }
+  if (type == OpType::WIN_CREATE || type == OpType::WIN_FREE || type == OpType::WIN_PUT ||
+      type == OpType::WIN_GET || type == OpType::WIN_ACCUMULATE) {
+    Status s = Status::OK();
+    void* done = nullptr;
+    for (auto& e : entries) {
+      s = ExecuteWindowOp(e);
+      if (!s.ok()) break;
+    }
+    const at::Tensor* t = entries[0].spec.input.has_value() ? &*entries[0].spec.input : nullptr;
+    bool gpu = (t != nullptr && t->is_cuda());
+    if (!gpu && (type == OpType::WIN_GET)) {
+      at::Tensor v = windows_->SelfView(entries[0].spec.win_name);
+      gpu = v.defined() && v.is_cuda();
+    }
+    if (s.ok() && gpu && comm_stream_ && (type == OpType::WIN_PUT || type == OpType::WIN_GET || type == OpType::WIN_ACCUMULATE)) {
+      cudaEvent_t ev;
+      cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+      cudaEventRecord(ev, static_cast<cudaStream_t>(comm_stream_));
+      done = ev;
+    }
+    end_proc();
+    FinishEntries(entries, s, done);
+    return;
+  }
+  if (entries[0].spec.enable_topo_check && size_ > 1 &&
+      (type == OpType::NEIGHBOR_ALLREDUCE || type == OpType::NEIGHBOR_ALLGATHER)) {
+    Status s = TopoCheck(entries[0].spec);
+    if (!s.ok()) {
+      end_proc();
+      FinishEntries(entries, s, nullptr);
+      return;
+    }
+  }
+  const at::Tensor* probe = entries[0].spec.input.has_value() ? &*entries[0].spec.input : &*entries[0].spec.output;
+  Status s;
+  void* done = nullptr;
+  if (probe->is_cuda()) {
+    s = ExecuteGpu(entries, resp);
+    if (s.ok()) {
+      cudaEvent_t ev;
+      cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+      cudaEventRecord(ev, static_cast<cudaStream_t>(comm_stream_));
+      done = ev;
+    }
+  } else {
+    s = ExecuteCpu(entries, resp);
+  }
+  end_proc();
+  FinishEntries(entries, s, done);
+}
+
+Status Runtime::ExecuteWindowOp(Entry& e) {
+  const OpType type = static_cast<OpType>(e.spec.type);
+  const at::Tensor* t = e.spec.input.has_value() ? &*e.spec.input : nullptr;
+  bool gpu = t != nullptr && t->is_cuda();
+  if (type == OpType::WIN_GET) {
+    at::Tensor v = windows_->SelfView(e.spec.win_name);
+    gpu = v.defined() && v.is_cuda();
+  }
+  if (gpu) {
+    cudaSetDevice(device_);
+    if (!comm_stream_) {
+      cudaStream_t st;
+      int lo, hi;
+      cudaDeviceGetStreamPriorityRange(&lo, &hi);
+      cudaStreamCreateWithPriority(&st, cudaStreamNonBlocking, hi);
+      comm_stream_ = st;
+    }
+    if (e.ready_event) cudaStreamWaitEvent(static_cast<cudaStream_t>(comm_stream_), static_cast<cudaEvent_t>(e.ready_event), 0);
+  }
+  switch (type) {
+    case OpType::WIN_CREATE: return windows_->Create(e.spec, kChanData);
+    case OpType::WIN_FREE: return windows_->Free(e.spec.win_name, kChanData);
+    case OpType::WIN_PUT:
+    case OpType::WIN_ACCUMULATE: return windows_->Put(e.spec, comm_stream_);
+    case OpType::WIN_GET: return windows_->Get(e.spec, comm_stream_);
+    default: return Status::InvalidArgument("not a window operation");
+  }
+}
+
+// CPU data path: payloads travel over the TCP mesh, the combine is done with ATen.
+Status Runtime::ExecuteCpu(std::vector<Entry>& entries, const Response& resp) {
+  for (size_t idx = 0; idx < entries.size(); ++idx) {
+    Entry& e = entries[idx];
+    OpSpec& sp = e.spec;
+    const OpType type = static_cast<OpType>(sp.type);
+    timeline_.ActivityStart(sp.name, "COMMUNICATE");
+    Status s = Status::OK();
+    if (type == OpType::BROADCAST) {
+      at::Tensor buf = *sp.output;
+      if (rank_ == sp.root_rank) {
+        if (sp.input.has_value() && sp.input->data_ptr() != buf.data_ptr()) buf.copy_(*sp.input);
+        std::vector<SendSpec> sends;
+        for (int r = 0; r < size_; ++r)
+          if (r != rank_) sends.push_back({r, buf.data_ptr(), static_cast<size_t>(buf.nbytes())});
+        s = cp_.Exchange(kChanData, sends, {});
+      } else {
+        s = cp_.Exchange(kChanData, {}, {{sp.root_rank, buf.data_ptr(), static_cast<size_t>(buf.nbytes())}});
+      }
+    } else if (type == OpType::ALLGATHER || type == OpType::NEIGHBOR_ALLGATHER) {
+      const at::Tensor& in = *sp.input;
+      at::Tensor& out = *sp.output;
+      const int64_t row_bytes = in.numel() == 0 ? 0 : in.nbytes() / std::max<int64_t>(in.size(0), 1);
+      std::vector<int64_t> dims(resp.first_dims.begin() + idx * size_, resp.first_dims.begin() + (idx + 1) * size_);
+      if (resp.first_dims.empty()) dims.assign(size_, in.size(0));  // negotiation skipped: equal sizes assumed
+      std::vector<int> order;
+      if (type == OpType::ALLGATHER) {
+        for (int r = 0; r < size_; ++r) order.push_back(r);
+      } else {
+        order = sp.src_ranks;
+      }
+      int64_t total = 0;
+      for (int r : order) total += dims[r];
+      std::vector<int64_t> shape = in.sizes().vec();
+      shape[0] = total;
+      out.resize_(shape);
+      std::vector<SendSpec> sends;
+      std::vector<RecvSpec> recvs;
+      const std::vector<int>& dsts = sp.dst_ranks;
+      for (int d : dsts) sends.push_back({d, in.data_ptr(), static_cast<size_t>(in.nbytes())});
+      char* base = static_cast<char*>(out.data_ptr());
+      int64_t off = 0;
+      for (int r : order) {
+        const size_t nb = static_cast<size_t>(dims[r] * row_bytes);
+        if (r == rank_) std::memcpy(base + off, in.data_ptr(), nb);
+        else recvs.push_back({r, base + off, nb});
+        off += nb;
+      }
+      s = cp_.Exchange(kChanData, sends, recvs);
+    } else if (IsReduceOp(type)) {
+      const at::Tensor& in = *sp.input;
+      at::Tensor& out = *sp.output;
+      // 16-bit floats are combined in fp32 (the reference does the same detour on CPU).
+      const bool widen = in.scalar_type() == at::kHalf || in.scalar_type() == at::kBFloat16;
+      std::vector<at::Tensor> scaled;   // per-destination scaled copies, kept alive during the exchange
+      std::vector<SendSpec> sends;
+      for (size_t i = 0; i < sp.dst_ranks.size(); ++i) {
+        const void* ptr = in.data_ptr();
+        if (sp.use_dst_weight && sp.dst_weights[i] != 1.0) {
+          scaled.push_back(in.mul(sp.dst_weights[i]));
+          ptr = scaled.back().data_ptr();
+        }
+        sends.push_back({sp.dst_ranks[i], ptr, static_cast<size_t>(in.nbytes())});
+      }
+      std::vector<at::Tensor> recv_bufs;
+      std::vector<RecvSpec> recvs;
+      for (int r : sp.src_ranks) {
+        recv_bufs.push_back(at::empty_like(in));
+        recvs.push_back({r, recv_bufs.back().data_ptr(), static_cast<size_t>(in.nbytes())});
+      }
+      s = cp_.Exchange(kChanData, sends, recvs);
+      if (s.ok()) {
+        timeline_.ActivityEnd(sp.name);
+        timeline_.ActivityStart(sp.name, "COMPUTE_AVERAGE");
+        const bool integral = at::isIntegralType(in.scalar_type(), /*includeBool=*/true);
+        at::Tensor acc = widen ? in.to(at::kFloat) : in.clone();
+        if (integral) {
+          for (size_t j = 0; j < recv_bufs.size(); ++j) acc.add_(recv_bufs[j]);
+        } else {
+          if (sp.self_weight != 1.0) acc.mul_(sp.self_weight);
+          for (size_t j = 0; j < recv_bufs.size(); ++j)
+            acc.add_(widen ? recv_bufs[j].to(at::kFloat) : recv_bufs[j], sp.src_weights[j]);
+          if (sp.post_scale != 1.0) acc.mul_(sp.post_scale);
+        }
+        out.resize_(in.sizes());
+        out.copy_(acc);
+      }
+    } else {
+      s = Status::InvalidArgument(std::string("unsupported CPU operation ") + OpTypeName(type));
+    }
+    timeline_.ActivityEnd(sp.name);
+    if (!s.ok()) return s;
+  }
+  return Status::OK();
+}
+
+Status Runtime::EnsureGpuChannel(uint64_t need_bytes) {
+  cudaSetDevice(device_);
+  if (!comm_stream_) {
+    cudaStream_t st;
+    int lo, hi;
+    cudaDeviceGetStreamPriorityRange(&lo, &hi);
+    BFB_CUDA_OK(cudaStreamCreateWithPriority(&st, cudaStreamNonBlocking, hi));
+    comm_stream_ = st;
+  }
+  const bool have = gpu_channel_ != nullptr;
+  if (have && need_bytes <= gpu_channel_->half_bytes()) return Status::OK();
+  // (Re)allocation is collective: payload sizes agree on every rank, so all ranks get here
+  // for the same operation.
+  uint64_t half = have ? gpu_channel_->half_bytes() : static_cast<uint64_t>(EnvDouble("BLUEFOG_B200_ARENA_BYTES", 32.0 * 1024 * 1024));
+  while (half < need_bytes) half *= 2;
+  if (have) {
+    BFB_CUDA_OK(cudaStreamSynchronize(static_cast<cudaStream_t>(comm_stream_)));
+    Status s = cp_.Barrier(kChanData);  // no peer still reads the old arena
+    if (!s.ok()) return s;
+  }
+  std::shared_ptr<SymmBuffer> arena;
+  Status s = AllocateIpc(&cp_, kChanData, device_, half * 2, &arena);
+  if (!s.ok()) return s;
+  if (!have) {
+    s = AllocateIpc(&cp_, kChanData, device_, sizeof(ChannelCtrl), &gpu_ctrl_);
+    if (!s.ok()) return s;
+    gpu_channel_ = std::make_unique<Channel>(gpu_ctrl_, arena, half);
+  } else {
+    gpu_channel_->ResetArena(arena, half);
+  }
+  return Status::OK();
+}
+
+// GPU data path: publish into the symmetric arena, then pull from the peers' arenas.
+Status Runtime::ExecuteGpu(std::vector<Entry>& entries, const Response& resp) {
+  const OpType type = static_cast<OpType>(entries[0].spec.type);
+  OpSpec& first = entries[0].spec;
+  std::vector<SegSpec> segs;
+  for (auto& e : entries) {
+    SegSpec sg;
+    const at::Tensor* in = e.spec.input.has_value() ? &*e.spec.input : nullptr;
+    sg.in = in ? in->data_ptr() : nullptr;
+    sg.nbytes = in ? static_cast<uint64_t>(in->nbytes()) : 0;
+    sg.numel = in ? static_cast<uint64_t>(in->numel()) : 0;
+    if (type == OpType::BROADCAST) {
+      at::Tensor& buf = *e.spec.output;
+      sg.in = buf.data_ptr();
+      sg.nbytes = static_cast<uint64_t>(buf.nbytes());
+      sg.numel = static_cast<uint64_t>(buf.numel());
+      if (rank_ != e.spec.root_rank) { sg.in = nullptr; }
+    }
+    segs.push_back(sg);
+  }
+  // Arena demand must be identical on all ranks: use the largest contribution for gathers.
+  uint64_t need = 0;
+  if (type == OpType::ALLGATHER || type == OpType::NEIGHBOR_ALLGATHER) {
+    const at::Tensor& in = *first.input;
+    const int64_t row_bytes = in.size(0) > 0 ? in.nbytes() / in.size(0) : 0;
+    int64_t max_dim = in.size(0);
+    for (int r = 0; r < size_ && !resp.first_dims.empty(); ++r) max_dim = std::max(max_dim, resp.first_dims[r]);
+    need = Channel::PaddedSize(static_cast<uint64_t>(max_dim * row_bytes));
+  } else if (type == OpType::BROADCAST) {
+    for (auto& e : entries) need += Channel::PaddedSize(static_cast<uint64_t>(e.spec.output->nbytes()));
+  } else {
+    need = Channel::RequiredBytes(segs);
+  }
+  Status s = EnsureGpuChannel(std::max<uint64_t>(need, 256));
+  if (!s.ok()) return s;
+  cudaStream_t stream = static_cast<cudaStream_t>(comm_stream_);
+  for (auto& e : entries)
+    if (e.ready_event) cudaStreamWaitEvent(stream, static_cast<cudaEvent_t>(e.ready_event), 0);
+  for (auto& e : entries) timeline_.ActivityStart(e.spec.name, "COMMUNICATE");
+  auto end_act = [&] { for (auto& e : entries) timeline_.ActivityEnd(e.spec.name); };
+
+  Round round;
+  if (type == OpType::BROADCAST) {
+    const bool root = rank_ == first.root_rank;
+    std::vector<SegSpec> pub;
+    if (root) pub = segs;
+    s = gpu_channel_->Publish(pub, nullptr, root ? size_ - 1 : 0, stream, &round);
+    if (s.ok() && !root) {
+      // The root's round layout is the same deterministic packing of the same sizes.
+      std::vector<Channel::CopySpec> copies;
+      uint64_t off = 0;
+      for (auto& e : entries) {
+        const uint64_t nb = static_cast<uint64_t>(e.spec.output->nbytes());
+        copies.push_back({first.root_rank, off, nb, e.spec.output->data_ptr()});
+        off += Channel::PaddedSize(nb);
+      }
+      s = gpu_channel_->PullGather(round, {first.root_rank}, copies, stream);
+    }
+    end_act();
+    return s;
+  }
+  if (type == OpType::ALLGATHER || type == OpType::NEIGHBOR_ALLGATHER) {
+    const at::Tensor& in = *first.input;
+    at::Tensor& out = *first.output;
+    const int64_t row_bytes = in.size(0) > 0 ? in.nbytes() / in.size(0) : 0;
+    std::vector<int64_t> dims(size_, in.size(0));
+    if (!resp.first_dims.empty()) dims.assign(resp.first_dims.begin(), resp.first_dims.begin() + size_);
+    std::vector<int> order;
+    if (type == OpType::ALLGATHER) for (int r = 0; r < size_; ++r) order.push_back(r);
+    else order = first.src_ranks;
+    int64_t total = 0;
+    for (int r : order) total += dims[r];
+    std::vector<int64_t> shape = in.sizes().vec();
+    shape[0] = total;
+    {
+      // Allocation happens on the scheduling thread: make the allocator use the comm stream.
+      c10::cuda::CUDAStreamGuard g(c10::cuda::getStreamFromExternal(stream, device_));
+      out.resize_(shape);
+    }
+    s = gpu_channel_->Publish(segs, nullptr, static_cast<int>(first.dst_ranks.size()), stream, &round);
+    if (s.ok()) {
+      std::vector<int> srcs;
+      std::vector<Channel::CopySpec> copies;
+      char* base = static_cast<char*>(out.data_ptr());
+      int64_t off = 0;
+      for (int r : order) {
+        const uint64_t nb = static_cast<uint64_t>(dims[r] * row_bytes);
+        if (r != rank_) srcs.push_back(r);
+        if (nb > 0) copies.push_back({r, 0, nb, base + off});
+        off += static_cast<int64_t>(nb);
+      }
+      s = gpu_channel_->PullGather(round, srcs, copies, stream);
+    }
+    end_act();
+    return s;
+  }
+  if (IsReduceOp(type)) {
+    const int elem = ToElem(first.input->scalar_type());
+    if (elem < 0) {
+      end_act();
+      return Status::InvalidArgument("unsupported tensor type for a GPU reduction");
+    }
+    std::vector<double> dstw;
+    if (first.use_dst_weight) {
+      dstw.assign(size_, 1.0);
+      for (size_t i = 0; i < first.dst_ranks.size(); ++i) dstw[first.dst_ranks[i]] = first.dst_weights[i];
+    }
+    s = gpu_channel_->Publish(segs, first.use_dst_weight ? dstw.data() : nullptr,
+                              static_cast<int>(first.dst_ranks.size()), stream, &round);
+    if (s.ok()) {
+      for (size_t i = 0; i < entries.size(); ++i) {
+        at::Tensor& out = *entries[i].spec.output;
+        if (out.sizes() != entries[i].spec.input->sizes()) {
+          c10::cuda::CUDAStreamGuard g(c10::cuda::getStreamFromExternal(stream, device_));
+          out.resize_(entries[i].spec.input->sizes());
+        }
+        segs[i].out = out.data_ptr();
+      }
+      const bool integral = elem == kI32 || elem == kI64;
+      std::vector<double> w = first.src_weights;
+      if (integral) w.assign(first.src_ranks.size(), 1.0);
+      s = gpu_channel_->PullCombine(round, segs, elem, integral ? 1.0 : first.self_weight, first.src_ranks, w,
+                                    first.use_dst_weight, integral ? 1.0 : first.post_scale, stream);
+    }
+    end_act();
+    return s;
+  }
+  end_act();
+  return Status::InvalidArgument(std::string("unsupported GPU operation ") + OpTypeName(type));
+}
+
+}  // namespace bfb

@@ -1,0 +1,177 @@
+// Device-side communication protocol and launchers for the peer-memory kernels.
+//
+// Every rank owns a "channel": a control block plus a double-buffered payload area
+// ("arena") that live in memory mapped into every peer's address space (CUDA IPC over
+// NVLink/NVSwitch).  A rank *publishes* version v of its payload in arena half v % 2 and
+// then stores epoch = v + 1 with release semantics; a reader spins (bounded) on the
+// owner's epoch with acquire loads, streams the payload with 16-byte loads straight out
+// of the owner's memory, and finally adds 1 to the owner's done[v % 2] counter.  Before a
+// rank overwrites arena half v % 2 with version v it waits until done[v % 2] has reached
+// the number of readers of all earlier versions with that parity.  Every dependency
+// points at an earlier version, so the protocol cannot deadlock, and every wait has a time
+// limit after which the kernel records an error code in a host-visible status word and
+// returns normally.
+//
+// What this replaces in the reference: the grouped ncclSend/ncclRecv exchange, the
+// cudaMemcpyAsync fusion-buffer pack/unpack, the per-destination scaled copies and the
+// per-neighbor ATen mul_/add_ combine (bluefog/common/nccl_controller.cc:710-949,
+// 1013-1204, 1915-2064; bluefog/torch/mpi_ops.cc:99-164).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace bfb {
+
+constexpr int kMaxWorld = 64;   // ranks addressable by one channel
+constexpr int kMaxSrc = 64;     // sources one pull kernel can read
+constexpr int kMaxSeg = 40;     // tensors handled by one launch (fused groups are chunked)
+
+// Error codes written to the status word (0 = healthy).
+enum CommError : uint32_t {
+  kCommOk = 0,
+  kCommTimeoutEpoch = 1,   // a source never published the awaited version
+  kCommTimeoutDone = 2,    // readers of an old version never finished
+  kCommBadArgument = 3,
+};
+
+struct alignas(256) ChannelCtrl {
+  unsigned long long epoch;             // versions published so far
+  unsigned long long done[2];           // finished readers per arena half (cumulative)
+  unsigned int block_counter[4];        // last-block detection, local use only
+  unsigned int reserved[2];
+  unsigned long long payload_bytes[2];  // size of the published payload per half
+  double dst_weight[2][kMaxWorld];      // weight the owner attaches per destination rank
+};
+
+// Host-visible status block (pinned, mapped): kernels write, the host reads after the
+// completion event.
+struct CommStatus {
+  unsigned int error;       // CommError
+  unsigned int peer;        // rank that was waited for
+  unsigned long long want;  // awaited value
+  unsigned long long seen;  // last observed value
+};
+
+enum ElemType : int {
+  kF32 = 0, kF64 = 1, kF16 = 2, kBF16 = 3, kI32 = 4, kI64 = 5, kU8 = 6, kI8 = 7, kI16 = 8,
+};
+int ElemSize(int elem_type);
+
+struct PackParams {
+  ChannelCtrl* ctrl;            // my control block
+  unsigned char* arena_half;    // my arena + half offset
+  CommStatus* status;
+  unsigned long long need_done; // wait until ctrl->done[half] >= need_done before writing
+  unsigned long long publish_epoch;  // value stored to ctrl->epoch when publish != 0
+  unsigned long long timeout_ns;
+  unsigned long long payload_bytes;
+  int half;
+  int wait_done;                // 1: perform the done-wait (first launch of a version)
+  int publish;                  // 1: store the header and the epoch (last launch of a version)
+  int world;
+  int my_rank;
+  int n_seg;
+  int has_dst_weight;
+  const void* src[kMaxSeg];
+  unsigned long long dst_off[kMaxSeg];
+  unsigned long long nbytes[kMaxSeg];
+  unsigned long long chunk_start[kMaxSeg + 1];  // prefix sum of 16-byte chunks
+  double dst_weight[kMaxWorld];
+};
+
+struct PullSync {
+  int n_src;
+  int my_rank;
+  int half;
+  int use_dst_weight;
+  int signal_done;              // 1: add 1 to every source's done[half] when the grid is finished
+  int counter_slot;             // which block_counter of my ctrl to use
+  unsigned long long wait_epoch;
+  unsigned long long timeout_ns;
+  ChannelCtrl* my_ctrl;
+  CommStatus* status;
+  ChannelCtrl* src_ctrl[kMaxSrc];           // peer-mapped control blocks
+  const unsigned char* src_arena[kMaxSrc];  // peer-mapped arena + half offset
+  int src_rank[kMaxSrc];
+};
+
+// out[seg] = post_scale * (self_w * self[seg] + sum_j w_j * dstw_j * src_j[seg])
+struct CombineParams {
+  PullSync sync;
+  const unsigned char* self_arena;   // my arena + half offset (self term), may be null if self_w == 0
+  double self_w;
+  double post_scale;
+  double src_w[kMaxSrc];
+  int elem_type;
+  int n_seg;
+  void* out[kMaxSeg];
+  unsigned long long off[kMaxSeg];      // byte offset of the segment inside every arena half
+  unsigned long long numel[kMaxSeg];
+  unsigned long long chunk_start[kMaxSeg + 1];
+};
+
+// Plain copies out of sources' arenas (allgather / neighbor_allgather / broadcast).
+struct GatherParams {
+  PullSync sync;
+  const unsigned char* self_arena;
+  int n_copy;
+  int copy_src[kMaxSeg];                 // index into sync.src_*, or -1 for my own arena
+  void* out[kMaxSeg];
+  unsigned long long src_off[kMaxSeg];
+  unsigned long long nbytes[kMaxSeg];
+  unsigned long long chunk_start[kMaxSeg + 1];
+};
+
+enum BucketOpt : int { kOptNone = 0, kOptSGD = 1, kOptAdam = 2 };
+enum BucketMode : int {
+  // c = self_w*P + sum_j w_j*pub_j(v);  P' = c - step(g, c);  pub(v+1) = P'   (adapt-with-combine)
+  kModeAWC = 0,
+  // a = P - step(g, P);  pub(v) = a   (first half of adapt-then-combine; no remote reads)
+  kModeAdaptPublish = 1,
+  // P' = self_w*pub_self(v) + sum_j w_j*pub_j(v)   (second half of adapt-then-combine)
+  kModeCombineOnly = 2,
+  // gbar = post_scale*(g_self + sum_j pub_j(v));  P' = P - step(gbar, P)   (gradient allreduce)
+  kModeGradReduce = 3,
+  // pub(v) = src (P or g): plain publish of a local buffer
+  kModePublishOnly = 4,
+};
+
+struct BucketParams {
+  PullSync sync;                 // unused fields are zero when the mode reads no peers
+  int mode;
+  int opt;
+  int pub_elem;                  // kF32 or kBF16: element type of the published copy
+  int grad_elem;                 // kF32 or kBF16
+  int nesterov, adamw, amsgrad, first_step, maximize;
+  float lr, momentum, dampening, weight_decay, beta1, beta2, eps, bias1, bias2, grad_scale;
+  float self_w, post_scale;
+  float src_w[kMaxSrc];
+  unsigned long long numel;
+  float* master;                 // P (private fp32)
+  const void* grad;              // flat gradient bucket
+  float* state1;                 // momentum / exp_avg
+  float* state2;                 // exp_avg_sq
+  float* state3;                 // max_exp_avg_sq (amsgrad)
+  void* shadow;                  // bf16 copy used by forward/backward (optional)
+  const unsigned char* pub_read_self;  // my published half that is read (combine-only mode)
+  unsigned char* pub_write;      // my published half that is written (or null)
+  // publishing the written half
+  int publish;
+  int wait_done;
+  int write_half;
+  unsigned long long need_done;
+  unsigned long long publish_epoch;
+};
+
+// Launchers. Each returns cudaGetLastError() of the launch.
+cudaError_t LaunchPack(const PackParams& p, cudaStream_t stream);
+cudaError_t LaunchCombine(const CombineParams& p, cudaStream_t stream);
+cudaError_t LaunchGather(const GatherParams& p, cudaStream_t stream);
+cudaError_t LaunchBucketStep(const BucketParams& p, cudaStream_t stream);
+// buf[i] *= s for any supported element type (K1/K2 of the reference, kept as a utility).
+cudaError_t LaunchScale(void* buf, unsigned long long numel, double s, int elem_type, cudaStream_t stream);
+// Number of kernels launched by this library in this process (all launchers count).
+unsigned long long KernelLaunchCount();
+void CountKernelLaunch();
+
+}  // namespace bfb

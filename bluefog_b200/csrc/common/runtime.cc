@@ -805,8 +805,9 @@ Status Runtime::ExecuteCpu(std::vector<Entry>& entries, const Response& resp) {
       const at::Tensor& in = *sp.input;
       at::Tensor& out = *sp.output;
       const int64_t row_bytes = in.numel() == 0 ? 0 : in.nbytes() / std::max<int64_t>(in.size(0), 1);
-      std::vector<int64_t> dims(resp.first_dims.begin() + idx * size_, resp.first_dims.begin() + (idx + 1) * size_);
-      if (resp.first_dims.empty()) dims.assign(size_, in.size(0));  // negotiation skipped: equal sizes assumed
+      std::vector<int64_t> dims(size_, in.size(0));  // negotiation skipped: equal sizes assumed
+      if (resp.first_dims.size() >= (idx + 1) * static_cast<size_t>(size_))
+        dims.assign(resp.first_dims.begin() + idx * size_, resp.first_dims.begin() + (idx + 1) * size_);
       std::vector<int> order;
       if (type == OpType::ALLGATHER) {
         for (int r = 0; r < size_; ++r) order.push_back(r);

@@ -118,16 +118,18 @@ void Timeline::WriteRecord(const Record& r) {
   int& tid = tid_index_[r.tid];
   if (tid == 0) tid = static_cast<int>(tid_index_.size());
   int& pid = tensor_pid_[r.tensor];
+  StrBuilder out;  // numbers are formatted without iostream facets
   if (pid == 0) {
     pid = static_cast<int>(tensor_pid_.size());
-    file_ << "{\"name\": \"process_name\", \"ph\": \"M\", \"pid\": " << pid << ", \"tid\": " << tid
-          << ", \"args\": {\"name\": \"" << JsonEscape(r.tensor) << "\"}},\n";
-    file_ << "{\"name\": \"process_sort_index\", \"ph\": \"M\", \"pid\": " << pid
-          << ", \"tid\": " << tid << ", \"args\": {\"sort_index\": " << pid << "}},\n";
+    out << "{\"name\": \"process_name\", \"ph\": \"M\", \"pid\": " << pid << ", \"tid\": " << tid
+        << ", \"args\": {\"name\": \"" << JsonEscape(r.tensor) << "\"}},\n";
+    out << "{\"name\": \"process_sort_index\", \"ph\": \"M\", \"pid\": " << pid << ", \"tid\": " << tid
+        << ", \"args\": {\"sort_index\": " << pid << "}},\n";
   }
-  file_ << "{\"ph\": \"" << r.phase << "\"";
-  if (r.phase != 'E') file_ << ", \"name\": \"" << JsonEscape(r.op) << "\"";
-  file_ << ", \"ts\": " << r.ts << ", \"pid\": " << pid << ", \"tid\": " << tid << "},\n";
+  out << "{\"ph\": \"" << r.phase << "\"";
+  if (r.phase != 'E') out << ", \"name\": \"" << JsonEscape(r.op) << "\"";
+  out << ", \"ts\": " << r.ts << ", \"pid\": " << pid << ", \"tid\": " << tid << "},\n";
+  file_.write(out.str().data(), static_cast<std::streamsize>(out.str().size()));
 }
 
 void Timeline::WriterLoop() {

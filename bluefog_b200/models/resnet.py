@@ -1,0 +1,169 @@
+"""ResNet family with torchvision's parameter names (so checkpoints interchange).
+
+The reference ships no model code and benchmarks ``torchvision.models.resnet50``
+(examples/pytorch_benchmark.py:100); this module states the same network (He et al.,
+v1.5: stride on the 3x3 convolution of a bottleneck) in a form that suits a B200:
+activations are NHWC (channels_last), parameters may be bf16 views of an fp32 master
+bucket, BatchNorm statistics stay fp32, and the 1x1 convolutions and the classifier, which
+are plain GEMMs in NHWC, can run on the hand-written tcgen05 GEMM
+(``bluefog_b200.ops.gemm``) when ``use_b200_gemm`` is set.
+"""
+from typing import List, Optional, Type
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+class MixedBatchNorm2d(nn.BatchNorm2d):
+    """BatchNorm whose affine parameters may be bf16 while the running statistics stay fp32."""
+
+    def forward(self, x):
+        w, b = self.weight, self.bias
+        if w is not None and w.dtype != torch.float32 and x.dtype == w.dtype:
+            # cuDNN's mixed mode wants fp32 scale/shift with 16-bit activations
+            w, b = w.float(), b.float()
+        if self.training and self.track_running_stats and self.num_batches_tracked is not None:
+            self.num_batches_tracked.add_(1)
+        momentum = 0.0 if self.momentum is None else self.momentum
+        return F.batch_norm(x, self.running_mean if (not self.training or self.track_running_stats) else None,
+                            self.running_var if (not self.training or self.track_running_stats) else None,
+                            w, b, self.training or not self.track_running_stats, momentum, self.eps)
+
+
+class Conv1x1(nn.Conv2d):
+    """1x1 convolution; in NHWC with stride 1 it is the GEMM [N*H*W, Cin] x [Cin, Cout]."""
+
+    def __init__(self, cin, cout, stride=1, use_b200_gemm=False):
+        super().__init__(cin, cout, kernel_size=1, stride=stride, bias=False)
+        self.use_b200_gemm = use_b200_gemm
+
+    def forward(self, x):
+        if (self.use_b200_gemm and x.is_cuda and x.dtype == torch.bfloat16
+                and x.is_contiguous(memory_format=torch.channels_last)):
+            from bluefog_b200.ops import gemm
+            if gemm.available():
+                if self.stride[0] != 1:
+                    x = x[:, :, ::self.stride[0], ::self.stride[1]].contiguous(memory_format=torch.channels_last)
+                n, c, h, w = x.shape
+                a = x.permute(0, 2, 3, 1).reshape(n * h * w, c)
+                y = gemm.linear(a, self.weight.view(self.out_channels, c))
+                return y.view(n, h, w, self.out_channels).permute(0, 3, 1, 2)
+        return super().forward(x)
+
+
+def conv3x3(cin, cout, stride=1):
+    return nn.Conv2d(cin, cout, kernel_size=3, stride=stride, padding=1, bias=False)
+
+
+class BasicBlock(nn.Module):
+    expansion = 1
+
+    def __init__(self, inplanes, planes, stride=1, downsample=None, use_b200_gemm=False):
+        super().__init__()
+        self.conv1 = conv3x3(inplanes, planes, stride)
+        self.bn1 = MixedBatchNorm2d(planes)
+        self.relu = nn.ReLU(inplace=True)
+        self.conv2 = conv3x3(planes, planes)
+        self.bn2 = MixedBatchNorm2d(planes)
+        self.downsample = downsample
+
+    def forward(self, x):
+        identity = x if self.downsample is None else self.downsample(x)
+        out = self.relu(self.bn1(self.conv1(x)))
+        out = self.bn2(self.conv2(out))
+        return self.relu(out + identity)
+
+
+class Bottleneck(nn.Module):
+    expansion = 4
+
+    def __init__(self, inplanes, planes, stride=1, downsample=None, use_b200_gemm=False):
+        super().__init__()
+        self.conv1 = Conv1x1(inplanes, planes, use_b200_gemm=use_b200_gemm)
+        self.bn1 = MixedBatchNorm2d(planes)
+        self.conv2 = conv3x3(planes, planes, stride)
+        self.bn2 = MixedBatchNorm2d(planes)
+        self.conv3 = Conv1x1(planes, planes * 4, use_b200_gemm=use_b200_gemm)
+        self.bn3 = MixedBatchNorm2d(planes * 4)
+        self.relu = nn.ReLU(inplace=True)
+        self.downsample = downsample
+
+    def forward(self, x):
+        identity = x if self.downsample is None else self.downsample(x)
+        out = self.relu(self.bn1(self.conv1(x)))
+        out = self.relu(self.bn2(self.conv2(out)))
+        out = self.bn3(self.conv3(out))
+        return self.relu(out + identity)
+
+
+class ResNet(nn.Module):
+    def __init__(self, block: Type[nn.Module], layers: List[int], num_classes: int = 1000,
+                 use_b200_gemm: bool = False, zero_init_residual: bool = False):
+        super().__init__()
+        self.inplanes = 64
+        self.use_b200_gemm = use_b200_gemm
+        self.conv1 = nn.Conv2d(3, 64, kernel_size=7, stride=2, padding=3, bias=False)
+        self.bn1 = MixedBatchNorm2d(64)
+        self.relu = nn.ReLU(inplace=True)
+        self.maxpool = nn.MaxPool2d(kernel_size=3, stride=2, padding=1)
+        self.layer1 = self._make_layer(block, 64, layers[0])
+        self.layer2 = self._make_layer(block, 128, layers[1], stride=2)
+        self.layer3 = self._make_layer(block, 256, layers[2], stride=2)
+        self.layer4 = self._make_layer(block, 512, layers[3], stride=2)
+        self.avgpool = nn.AdaptiveAvgPool2d((1, 1))
+        self.fc = nn.Linear(512 * block.expansion, num_classes)
+        for m in self.modules():
+            if isinstance(m, nn.Conv2d):
+                nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")
+            elif isinstance(m, nn.BatchNorm2d):
+                nn.init.constant_(m.weight, 1)
+                nn.init.constant_(m.bias, 0)
+        if zero_init_residual:
+            for m in self.modules():
+                if isinstance(m, Bottleneck):
+                    nn.init.constant_(m.bn3.weight, 0)
+                elif isinstance(m, BasicBlock):
+                    nn.init.constant_(m.bn2.weight, 0)
+
+    def _make_layer(self, block, planes, blocks, stride=1):
+        downsample = None
+        if stride != 1 or self.inplanes != planes * block.expansion:
+            downsample = nn.Sequential(
+                Conv1x1(self.inplanes, planes * block.expansion, stride, use_b200_gemm=self.use_b200_gemm),
+                MixedBatchNorm2d(planes * block.expansion))
+        layers = [block(self.inplanes, planes, stride, downsample, use_b200_gemm=self.use_b200_gemm)]
+        self.inplanes = planes * block.expansion
+        for _ in range(1, blocks):
+            layers.append(block(self.inplanes, planes, use_b200_gemm=self.use_b200_gemm))
+        return nn.Sequential(*layers)
+
+    def forward(self, x):
+        if x.is_cuda and x.dim() == 4:
+            x = x.contiguous(memory_format=torch.channels_last)
+        if x.dtype != self.conv1.weight.dtype:
+            x = x.to(self.conv1.weight.dtype)
+        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
+        x = torch.flatten(self.avgpool(x), 1)
+        if self.use_b200_gemm and x.is_cuda and x.dtype == torch.bfloat16:
+            from bluefog_b200.ops import gemm
+            if gemm.available():
+                return gemm.linear(x, self.fc.weight, self.fc.bias)
+        return self.fc(x)
+
+
+def resnet18(num_classes=1000, **kw):
+    return ResNet(BasicBlock, [2, 2, 2, 2], num_classes, **kw)
+
+
+def resnet34(num_classes=1000, **kw):
+    return ResNet(BasicBlock, [3, 4, 6, 3], num_classes, **kw)
+
+
+def resnet50(num_classes=1000, **kw):
+    return ResNet(Bottleneck, [3, 4, 6, 3], num_classes, **kw)
+
+
+def resnet101(num_classes=1000, **kw):
+    return ResNet(Bottleneck, [3, 4, 23, 3], num_classes, **kw)

@@ -29,6 +29,10 @@ _b = get_basics()
 _WIN_TYPES = (torch.float32, torch.float64, torch.int32, torch.int64, torch.bfloat16, torch.float16)
 
 _win_map: Dict[str, torch.Tensor] = {}
+# name -> serial number of the window currently registered under that name; lets an owner
+# check that a window is still the one it created before freeing it
+_win_serial: Dict[str, int] = {}
+_serial_counter = [0]
 _win_handle_map: Dict[int, tuple] = {}
 
 
@@ -64,7 +68,14 @@ def win_create(tensor: torch.Tensor, name: str, zero_init: bool = False) -> bool
     view = _b.native.win_self_view(name)
     tensor.data = view
     _win_map[name] = tensor
+    _serial_counter[0] += 1
+    _win_serial[name] = _serial_counter[0]
     return True
+
+
+def window_serial(name: str) -> int:
+    """Serial number of the window registered as ``name`` (0 if there is none)."""
+    return _win_serial.get(name, 0)
 
 
 def win_free(name: Optional[str] = None) -> bool:
@@ -73,11 +84,13 @@ def win_free(name: Optional[str] = None) -> bool:
         if not _win_map and _b.native.win_count() == 0:
             return True
         _win_map.clear()
+        _win_serial.clear()
         target = ""
     else:
         if name not in _win_map:
             return False
         _win_map.pop(name)
+        _win_serial.pop(name, None)
         target = name
     spec = _c._new_spec(_c.OP_WIN_FREE, f"win_free.{target if target else '__all__'}")
     spec.win_name = target

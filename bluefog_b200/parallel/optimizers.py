@@ -415,6 +415,7 @@ class _DistributedWinOptimizer(_CommonMixin):
         self._num_steps_per_communication = num_steps_per_communication
         self._bluefog_delay = {p: num_steps_per_communication for p in self._parameter_names}
         self._windows_registered = False
+        self._owned_windows = {}
         if _b.size() > 1:
             self._register_window()
             for m in self._models:
@@ -459,18 +460,19 @@ class _DistributedWinOptimizer(_CommonMixin):
                 with torch.no_grad():
                     if not _win.win_create(p, name):
                         raise ValueError("Cannot allocate window for the parameter {}".format(name))
+                self._owned_windows[name] = _win.window_serial(name)
         self._windows_registered = True
 
     def unregister_window(self):
         """Frees the windows of this optimizer (collective)."""
         if not getattr(self, "_windows_registered", False) or not _b.is_initialized() or _b.size() <= 1:
             return
-        for group in self.param_groups:
-            for p in group["params"]:
-                name = self._parameter_names.get(p)
-                if name in _win.get_current_created_window_names():
-                    if not _win.win_free(name):
-                        raise ValueError("Cannot free window for the parameter {}".format(name))
+        for name, serial in sorted(self._owned_windows.items()):
+            # only windows this optimizer created and that were not freed or replaced since
+            if _win.window_serial(name) == serial:
+                if not _win.win_free(name):
+                    raise ValueError("Cannot free window for the parameter {}".format(name))
+        self._owned_windows.clear()
         self._windows_registered = False
 
     def synchronize(self):
@@ -511,6 +513,7 @@ class _DistributedPushSumOptimizer(_CommonMixin):
         self._num_steps_per_communication = num_steps_per_communication
         self._pushsum_delay = {p: num_steps_per_communication for p in self._parameter_names}
         self._windows_registered = False
+        self._owned_windows = {}
         if _b.size() > 1:
             self._register_window()
             for m in self._models:
@@ -525,14 +528,16 @@ class _DistributedPushSumOptimizer(_CommonMixin):
                 if not _win.win_create(ext, name, zero_init=True):
                     raise ValueError("Cannot allocate window for the parameter {}".format(name))
                 self._extended[name] = ext
+                self._owned_windows[name] = _win.window_serial(name)
         self._windows_registered = True
 
     def unregister_window(self):
         if not getattr(self, "_windows_registered", False) or not _b.is_initialized() or _b.size() <= 1:
             return
-        for name in list(self._extended):
-            if name in _win.get_current_created_window_names():
+        for name, serial in sorted(self._owned_windows.items()):
+            if _win.window_serial(name) == serial:
                 _win.win_free(name)
+        self._owned_windows.clear()
         self._windows_registered = False
 
     def _make_hook(self):

@@ -1,0 +1,453 @@
+"""One rank of a multi-process test case: ``python tests/_worker.py <case>`` with the
+torchrun-style environment set by tests/conftest.py::run_ranks.  Expected values are closed
+forms of the rank ids and the known topology, as in the reference's test strategy
+(test/torch_ops_test.py), re-derived here."""
+import itertools
+import json
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+
+import bluefog_b200.torch as bf
+from bluefog_b200.common import topology_util as tu
+
+CASES = {}
+
+
+def case(fn):
+    CASES[fn.__name__] = fn
+    return fn
+
+
+def dev():
+    return torch.device("cuda", torch.cuda.current_device()) if bf._b.device() >= 0 else torch.device("cpu")
+
+
+def close(a, b, tol=1e-5):
+    assert torch.allclose(a.double().cpu(), torch.as_tensor(b, dtype=torch.float64).expand_as(a).cpu(),
+                          atol=tol, rtol=tol), (a.flatten()[:4], b)
+
+
+FLOATS = [torch.float32, torch.float64, torch.float16, torch.bfloat16]
+TOL = {torch.float32: 1e-5, torch.float64: 1e-9, torch.float16: 1e-2, torch.bfloat16: 5e-2}
+
+
+@case
+def basics():
+    r, n = bf.rank(), bf.size()
+    assert r == int(os.environ["RANK"]) and n == int(os.environ["WORLD_SIZE"])
+    assert bf.local_size() == n and bf.local_rank() == r
+    assert tu.IsTopologyEquivalent(bf.load_topology(), tu.ExponentialGraph(n))
+    assert bf.set_topology(tu.RingGraph(n))
+    assert sorted(bf.in_neighbor_ranks()) == sorted({(r - 1) % n, (r + 1) % n} - {r})
+    assert bf.set_topology(tu.ExponentialTwoGraph(n))
+    expect = sorted({(r - 2 ** k) % n for k in range(int(np.log2(n - 1)) + 1)} - {r}) if n > 1 else []
+    assert bf.in_neighbor_ranks() == expect
+    x = torch.zeros(3, device=dev())
+    assert bf.win_create(x, "basics.win")
+    if n > 2:   # (for n <= 2 the ring equals the current topology, which is a no-op True)
+        assert bf.set_topology(tu.RingGraph(n)) is False      # refused while a window exists
+    assert bf.win_free("basics.win")
+    assert bf.set_topology(tu.RingGraph(n)) is True
+    for graph in (tu.ExponentialGraph(n), tu.RingGraph(n), tu.StarGraph(n), tu.MeshGrid2DGraph(n), tu.FullyConnectedGraph(n)):
+        bf.set_topology(graph)
+        assert bf.InferSourceFromDestinationRanks(bf.out_neighbor_ranks()) == bf.in_neighbor_ranks()
+        assert bf.InferDestinationFromSourceRanks(bf.in_neighbor_ranks()) == bf.out_neighbor_ranks()
+    src, W = bf.InferSourceFromDestinationRanks(bf.out_neighbor_ranks(), construct_adjacency_matrix=True)
+    assert np.allclose(W.sum(axis=1), 1.0)
+
+
+@case
+def collectives():
+    r, n, d = bf.rank(), bf.size(), dev()
+    for dtype, dims in itertools.product(FLOATS, [1, 2, 3]):
+        x = torch.full([3] * dims, float(r), dtype=dtype, device=d)
+        close(bf.allreduce(x), (n - 1) / 2, TOL[dtype])
+        close(bf.allreduce(x, average=False), n * (n - 1) / 2, TOL[dtype] * n)
+        y = x.clone()
+        bf.allreduce_(y)
+        close(y, (n - 1) / 2, TOL[dtype])
+        close(bf.broadcast(x, n - 1), n - 1, 0)
+        close(x, r, 0)
+        z = x.clone()
+        bf.broadcast_(z, 0)
+        close(z, 0, 0)
+    xi = torch.full((5,), r, dtype=torch.int64, device=d)
+    assert bf.allreduce(xi, average=False).tolist() == [n * (n - 1) // 2] * 5
+    # allgather with a different first dimension on every rank
+    g = bf.allgather(torch.full((r + 1, 2), float(r), device=d))
+    assert g.shape[0] == n * (n + 1) // 2
+    pos = 0
+    for s in range(n):
+        close(g[pos:pos + s + 1], s, 0)
+        pos += s + 1
+    # many small named tensors at once exercise the fusion planner
+    hs = [bf.allreduce_nonblocking(torch.full((17,), float(r + i), device=d), name=f"fuse.{i}") for i in range(40)]
+    for i, h in enumerate(hs):
+        close(bf.synchronize(h), (n - 1) / 2 + i, 1e-5)
+    # duplicate name in flight is rejected: rank 0 submits late, so the first request of the
+    # other ranks is certainly still pending when their second one arrives
+    if r == 0:
+        time.sleep(0.5)
+        close(bf.allreduce(torch.ones(8, device=d), name="dup"), 1.0, 1e-6)
+    else:
+        h1 = bf.allreduce_nonblocking(torch.ones(8, device=d), name="dup")
+        h2 = bf.allreduce_nonblocking(torch.ones(8, device=d), name="dup")
+        try:
+            bf.synchronize(h2)
+            raise AssertionError("duplicate name must be rejected")
+        except ValueError as exc:
+            assert "same name" in str(exc)
+        close(bf.synchronize(h1), 1.0, 1e-6)
+    bf.barrier()
+
+
+@case
+def neighbor_ops():
+    r, n, d = bf.rank(), bf.size(), dev()
+    for graph_fn in (tu.ExponentialTwoGraph, tu.RingGraph, tu.StarGraph, tu.MeshGrid2DGraph):
+        graph = graph_fn(n)
+        bf.set_topology(graph)
+        nb = bf.in_neighbor_ranks()
+        for dtype in FLOATS:
+            x = torch.full((23, 3), float(r), dtype=dtype, device=d)
+            close(bf.neighbor_allreduce(x), (r + sum(nb)) / (len(nb) + 1), TOL[dtype])
+        # weighted by the topology
+        bf.set_topology(graph, is_weighted=True)
+        sw, nw = tu.GetRecvWeights(graph, r)
+        x = torch.full((9,), float(r), dtype=torch.float64, device=d)
+        close(bf.neighbor_allreduce(x), sw * r + sum(w * s for s, w in nw.items()), 1e-9)
+        bf.set_topology(graph, is_weighted=False)
+        # neighbor_allgather: sorted in-neighbors, self excluded
+        g = bf.neighbor_allgather(torch.full((1,), float(r), device=d))
+        assert g.tolist() == [float(s) for s in nb]
+    bf.set_topology(tu.ExponentialTwoGraph(n))
+    # explicit weights (static): sum instead of average
+    x = torch.full((4,), float(r), device=d)
+    nb = bf.in_neighbor_ranks()
+    close(bf.neighbor_allreduce(x, self_weight=1.0, src_weights={s: 1.0 for s in nb}), r + sum(nb), 1e-5)
+    # dynamic: everybody sends to rank+1 with destination weight 2
+    out = bf.neighbor_allreduce(x, self_weight=0.5, src_weights={(r - 1) % n: 0.25},
+                                dst_weights={(r + 1) % n: 2.0})
+    close(out, 0.5 * r + 0.25 * 2.0 * ((r - 1) % n), 1e-5)
+    # dynamic pattern that does not match raises on every rank instead of hanging
+    try:
+        bf.neighbor_allreduce(x, self_weight=0.5, src_weights={(r - 1) % n: 0.5}, dst_weights=[(r + 2) % n]
+                              if n > 2 else [], name="mismatch")
+        matched = (n <= 2)
+    except ValueError:
+        matched = True
+    assert matched or n == 3
+    # argument rules
+    for bad in (dict(self_weight=0.5), dict(src_weights={0: 1.0}), dict(dst_weights=[(r + 1) % n])):
+        try:
+            bf.neighbor_allreduce(x, **bad)
+            raise AssertionError("expected ValueError")
+        except ValueError:
+            pass
+    # one-peer dynamic schedule over exp2: after log2(n) rounds everybody holds the exact mean
+    if n & (n - 1) == 0 and n > 1:
+        gen = tu.GetDynamicOnePeerSendRecvRanks(bf.load_topology(), r)
+        v = torch.full((3,), float(r), dtype=torch.float64, device=d)
+        for _ in range(int(np.log2(n))):
+            send, recv = next(gen)
+            w = 1.0 / (len(recv) + 1)
+            v = bf.neighbor_allreduce(v, self_weight=w, src_weights={s: w for s in recv}, dst_weights=send)
+        close(v, (n - 1) / 2, 1e-9)
+    # pair gossip
+    partner = r ^ 1
+    if partner < n:
+        close(bf.pair_gossip(x, partner), (r + partner) / 2, 1e-6)
+        close(bf.pair_gossip(x, partner, self_weight=0.25, pair_weight=0.75), 0.25 * r + 0.75 * partner, 1e-6)
+    bf.barrier()
+
+
+@case
+def hierarchical():
+    r, n, d = bf.rank(), bf.size(), dev()
+    L = bf.local_size()
+    assert L == 2 and bf.machine_size() == n // 2 and bf.machine_rank() == r // 2
+    x = torch.full((6,), float(r), device=d)
+    base = (r // L) * L
+    close(bf.allreduce(x, is_hierarchical_local=True), sum(range(base, base + L)) / L, 1e-6)
+    M = bf.machine_size()
+    bf.set_machine_topology(tu.RingGraph(M))
+    mean = lambda m: sum(range(m * L, m * L + L)) / L
+    nbm = bf.in_neighbor_machine_ranks()
+    expect = (mean(r // L) + sum(mean(m) for m in nbm)) / (len(nbm) + 1)
+    close(bf.hierarchical_neighbor_allreduce(x), expect, 1e-6)
+    m = r // L
+    out = bf.hierarchical_neighbor_allreduce(x, self_weight=0.5, src_machine_weights={(m - 1) % M: 0.5},
+                                             dst_machine_weights={(m + 1) % M: 3.0})
+    close(out, 0.5 * mean(m) + 0.5 * 3.0 * mean((m - 1) % M), 1e-5)
+    bf.barrier()
+
+
+@case
+def windows():
+    r, n, d = bf.rank(), bf.size(), dev()
+    bf.set_topology(tu.ExponentialTwoGraph(n))
+    nb_in, nb_out = bf.in_neighbor_ranks(), bf.out_neighbor_ranks()
+    for dtype in (torch.float32, torch.float64):
+        x = torch.full((11, 2), float(r), dtype=dtype, device=d)
+        assert bf.win_create(x, "w")
+        assert bf.get_current_created_window_names() == ["w"]
+        # slots start as copies of the local tensor
+        close(bf.win_update("w", clone=True), r, 1e-6)
+        bf.barrier()
+        assert bf.win_put(x, "w")
+        bf.barrier()
+        assert bf.get_win_version("w") == {s: 1 for s in nb_in}
+        out = bf.win_update("w")
+        assert out.data_ptr() == x.data_ptr()
+        close(x, (r + sum(nb_in)) / (len(nb_in) + 1), 1e-6)
+        assert bf.get_win_version("w") == {s: 0 for s in nb_in}
+        bf.barrier()
+        # accumulate twice with weights, then collect
+        x.fill_(float(r))
+        bf.win_update("w", self_weight=1.0, neighbor_weights={s: 0.0 for s in nb_in}, reset=True)
+        bf.barrier()
+        for _ in range(2):
+            bf.win_accumulate(x, "w", dst_weights={s: 0.5 for s in nb_out})
+        bf.barrier()
+        close(bf.win_update_then_collect("w"), r + sum(nb_in), 1e-5)
+        bf.barrier()
+        # get pulls the neighbors' registered tensors
+        x.fill_(float(r))
+        bf.barrier()
+        bf.win_get("w")
+        bf.barrier()
+        close(bf.win_update("w", self_weight=0.0, neighbor_weights={s: 1.0 for s in nb_in}), sum(nb_in), 1e-5)
+        bf.barrier()
+        assert bf.win_free("w")
+    # push-sum weights: p tracks a ones tensor through put/update rounds
+    bf.turn_on_win_ops_with_associated_p()
+    x = torch.ones(5, device=d)
+    bf.win_create(x, "p", zero_init=True)
+    outdeg = len(nb_out)
+    for _ in range(5):
+        bf.barrier()
+        bf.win_accumulate(x, "p", self_weight=1.0 / (outdeg + 1), dst_weights={s: 1.0 / (outdeg + 1) for s in nb_out},
+                          require_mutex=True)
+        bf.barrier()
+        bf.win_update_then_collect("p")
+        close(x, bf.win_associated_p("p"), 1e-6)
+    total = bf.allreduce(torch.tensor([bf.win_associated_p("p")], dtype=torch.float64), average=True)
+    close(total, 1.0, 1e-9)
+    bf.turn_off_win_ops_with_associated_p()
+    bf.win_free()
+    # mutex: rank 0 holds its own slots for a second, writers must wait
+    x = torch.zeros(3, device=d)
+    bf.win_create(x, "m")
+    bf.barrier()
+    if r == 0:
+        with bf.win_mutex("m", for_self=True, ranks=nb_in):
+            bf.barrier()
+            time.sleep(1.0)
+    else:
+        bf.barrier()
+        t0 = time.time()
+        if 0 in nb_out:
+            bf.win_put(x, "m", dst_weights={0: 1.0}, require_mutex=True)
+            assert time.time() - t0 > 0.7
+    bf.barrier()
+    bf.win_free("m")
+
+
+@case
+def errors():
+    r, n = bf.rank(), bf.size()
+    for kind in ("shape", "dtype", "root"):
+        try:
+            if kind == "shape":
+                bf.allreduce(torch.zeros(3 + (r == 0)), name="e.shape")
+            elif kind == "dtype":
+                bf.allreduce(torch.zeros(3, dtype=torch.float32 if r else torch.float64), name="e.dtype")
+            else:
+                bf.broadcast(torch.zeros(3), 0 if r else 1, name="e.root")
+            raise AssertionError("expected an error for " + kind)
+        except ValueError as exc:
+            assert "Mismatched" in str(exc)
+    try:
+        bf.allreduce(torch.zeros(4, dtype=torch.uint8))
+        raise AssertionError("uint8 allreduce must be rejected")
+    except ValueError:
+        pass
+    try:
+        bf.allreduce(torch.zeros(4, 4).t())
+        raise AssertionError("non-contiguous must be rejected")
+    except ValueError:
+        pass
+    # the runtime is still healthy
+    assert bf.allreduce(torch.ones(2)).tolist() == [1.0, 1.0]
+
+
+@case
+def consensus():
+    """BASELINE config: 100 000 fp32 values N(0,1) from seed=rank, static exp2, 200 rounds."""
+    r, n = bf.rank(), bf.size()
+    bf.set_topology(tu.ExponentialTwoGraph(n))
+    x = torch.randn(100000, generator=torch.Generator().manual_seed(r))
+    mean = bf.allreduce(x)
+    devs = []
+    for it in range(200):
+        x = bf.neighbor_allreduce(x, name="consensus")
+        if it % 10 == 9:
+            devs.append(bf.allreduce((x - mean).abs().max().reshape(1), average=False).item())
+    assert devs[0] < 1e-2 or devs[1] < devs[0]
+    assert devs[-1] < 1e-5, devs
+    if r == 0:
+        print("consensus deviations", devs[:6])
+
+
+@case
+def timeline():
+    r = bf.rank()
+    x = torch.ones(10)
+    for i in range(3):
+        bf.neighbor_allreduce(x, name="tl.tensor")
+        bf.allreduce(x, name="tl.ar")
+    with bf.timeline_context("user.tensor", "USER_ACTIVITY"):
+        time.sleep(0.01)
+    bf.barrier()
+    bf.shutdown()
+    path = os.environ["BLUEFOG_TIMELINE"] + str(r) + ".json"
+    text = open(path).read()
+    for token in ("ENQUEUE_NEIGHBOR_ALLREDUCE", "PROC_NEIGHBOR_ALLREDUCE", "COMMUNICATE", "COMPUTE_AVERAGE",
+                  "USER_ACTIVITY", "tl.tensor", "process_name"):
+        assert token in text, token
+    events = json.loads(text.rstrip().rstrip(",") + "]")
+    assert sum(e["ph"] == "B" for e in events) == sum(e["ph"] == "E" for e in events)
+
+
+@case
+def skip_negotiate():
+    r, n = bf.rank(), bf.size()
+    bf.set_skip_negotiate_stage(True)
+    assert bf.get_skip_negotiate_stage()
+    x = torch.full((4,), float(r))
+    close(bf.allreduce(x), (n - 1) / 2, 1e-6)
+    bf.barrier()
+    bf.set_skip_negotiate_stage(False)
+    close(bf.allreduce(x), (n - 1) / 2, 1e-6)
+
+
+@case
+def rank_exits_early():
+    """A rank that leaves makes the others' next collective fail instead of hang."""
+    r = bf.rank()
+    bf.allreduce(torch.ones(1))
+    if r == 1:
+        bf.shutdown()
+        return
+    time.sleep(0.5)
+    try:
+        bf.allreduce(torch.ones(1), name="after")
+        raise AssertionError("expected failure after a rank left")
+    except RuntimeError as exc:
+        assert "shut down" in str(exc)
+
+
+@case
+def stall_warning():
+    r = bf.rank()
+    bf._b.native.set_stall_warning_seconds(1.0)
+    if r == 1:
+        time.sleep(7.0)
+    bf.allreduce(torch.ones(1), name="late.tensor")
+
+
+@case
+def optimizers():
+    r, n, d = bf.rank(), bf.size(), dev()
+    torch.manual_seed(0)
+    w_true = torch.randn(16, 3)
+    g = torch.Generator().manual_seed(100 + r)
+    x = torch.randn(256, 16, generator=g)
+    y = x @ w_true + 0.1 * torch.randn(256, 3, generator=g)
+    x, y = x.to(d), y.to(d)
+    styles = [("awc", bf.DistributedAdaptWithCombineOptimizer, {}),
+              ("atc", bf.DistributedAdaptThenCombineOptimizer, {}),
+              ("grad", bf.DistributedGradientAllreduceOptimizer, {}),
+              ("awc_allreduce", bf.DistributedAllreduceOptimizer, {}),
+              ("awc_j2", bf.DistributedAdaptWithCombineOptimizer, {"num_steps_per_communication": 2}),
+              ("win_put", bf.DistributedWinPutOptimizer, {}),
+              ("pull_get", bf.DistributedPullGetOptimizer, {}),
+              ("push_sum", bf.DistributedPushSumOptimizer, {})]
+    for name, factory, kw in styles:
+        torch.manual_seed(1)
+        model = torch.nn.Linear(16, 3).to(d)
+        bf.broadcast_parameters(model.state_dict(), 0)
+        opt = factory(torch.optim.Adam(model.parameters(), lr=0.05), model, **kw)
+        if name in ("win_put", "pull_get"):
+            opt.force_barrier = True
+        assert isinstance(opt, torch.optim.Adam)
+        J = kw.get("num_steps_per_communication", 1)
+        for ep in range(60):
+            opt.zero_grad()
+            for _ in range(J if name != "awc_j2" else 1):
+                loss = torch.nn.functional.mse_loss(model(x), y)
+                loss.backward()
+            opt.step()
+        assert loss.item() < 0.08, (name, loss.item())
+        sd = opt.state_dict()
+        assert set(sd.keys()) == {"state", "param_groups"}
+        bf.win_free()
+        bf.barrier()
+    # dynamic one-peer weights set between steps
+    model = torch.nn.Linear(16, 3).to(d)
+    opt = bf.DistributedNeighborAllreduceOptimizer(torch.optim.SGD(model.parameters(), lr=0.2), model)
+    gen = tu.GetDynamicOnePeerSendRecvRanks(bf.load_topology(), r)
+    for ep in range(80):
+        send, recv = next(gen)
+        opt.dst_weights = send
+        opt.src_weights = {s: 1.0 / (len(recv) + 1) for s in recv}
+        opt.self_weight = 1.0 / (len(recv) + 1)
+        opt.zero_grad()
+        loss = torch.nn.functional.mse_loss(model(x), y)
+        loss.backward()
+        opt.step()
+    assert loss.item() < 0.5
+    bf.barrier()
+
+
+@case
+def checkpoint():
+    r, n = bf.rank(), bf.size()
+    path = os.environ["BFB_CKPT"]
+    torch.manual_seed(r)
+    model = torch.nn.Linear(4, 2)
+    opt = bf.DistributedAdaptWithCombineOptimizer(torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9), model)
+    opt.zero_grad()
+    model(torch.ones(1, 4)).sum().backward()
+    opt.step()
+    bf.save_checkpoint(path, model, opt, extra={"iteration": 7})
+    bf.barrier()
+    payload = torch.load(path, weights_only=False)
+    assert set(payload.keys()) == {"model", "optimizer", "extra"}
+    assert set(payload["model"].keys()) == {"weight", "bias"}
+    model2 = torch.nn.Linear(4, 2)
+    opt2 = bf.DistributedAdaptWithCombineOptimizer(torch.optim.SGD(model2.parameters(), lr=0.1, momentum=0.9), model2)
+    extra = bf.load_checkpoint(path, model2, opt2)
+    assert extra == {"iteration": 7}
+    w0 = bf.broadcast(model2.weight.data, 0)
+    assert torch.equal(w0, model2.weight.data) and torch.equal(model2.weight.data, payload["model"]["weight"])
+    bf.barrier()
+
+
+def main():
+    name = sys.argv[1]
+    if name not in ("timeline",):
+        pass
+    bf.init()
+    CASES[name]()
+    if bf._b.is_initialized():
+        bf.barrier() if name not in ("rank_exits_early",) else None
+        bf.shutdown()
+
+
+if __name__ == "__main__":
+    main()

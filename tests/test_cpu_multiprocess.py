@@ -1,0 +1,49 @@
+"""Multi-process tests on CPU ranks (TCP mesh + shared-memory windows), 4 ranks on this host.
+The same cases run on GPUs in tests/test_gpu_multi.py."""
+import os
+
+import pytest
+
+from conftest import run_ranks
+
+
+@pytest.mark.parametrize("case", ["basics", "collectives", "neighbor_ops", "windows", "errors",
+                                  "skip_negotiate", "optimizers"])
+def test_case_4_ranks(case):
+    run_ranks(case, 4)
+
+
+def test_basics_single_rank():
+    run_ranks("basics", 1)
+
+
+def test_collectives_three_ranks():
+    run_ranks("collectives", 3)
+
+
+def test_hierarchical_two_fake_machines():
+    run_ranks("hierarchical", 4, env={"BLUEFOG_NODES_PER_MACHINE": "2"})
+
+
+def test_average_consensus_config():
+    out = run_ranks("consensus", 4, timeout=400)
+    assert "consensus deviations" in out[0][1]
+
+
+def test_timeline_files(tmp_path):
+    prefix = str(tmp_path / "tl_")
+    run_ranks("timeline", 2, env={"BLUEFOG_TIMELINE": prefix})
+    assert os.path.exists(prefix + "0.json") and os.path.exists(prefix + "1.json")
+
+
+def test_checkpoint_roundtrip(tmp_path):
+    run_ranks("checkpoint", 2, env={"BFB_CKPT": str(tmp_path / "ckpt.pth.tar")})
+
+
+def test_rank_that_leaves_is_detected():
+    run_ranks("rank_exits_early", 3, timeout=120)
+
+
+def test_stall_warning_names_missing_rank():
+    out = run_ranks("stall_warning", 2, timeout=120)
+    assert "late.tensor" in out[0][1] and "missing ranks: 1" in out[0][1]

@@ -1,0 +1,97 @@
+"""Topology library: closed-form properties of the graphs and generators."""
+import numpy as np
+import networkx as nx
+import pytest
+
+from bluefog_b200.common import topology_util as tu
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 4, 7, 8, 12, 16])
+def test_static_graphs_are_row_and_column_stochastic(n):
+    for g in (tu.ExponentialTwoGraph(n), tu.ExponentialGraph(n), tu.SymmetricExponentialGraph(n),
+              tu.RingGraph(n), tu.FullyConnectedGraph(n), tu.MeshGrid2DGraph(n), tu.StarGraph(n)):
+        w = nx.to_numpy_array(g)
+        assert w.shape == (n, n)
+        assert np.allclose(w.sum(axis=1), 1.0)
+        assert np.allclose(w.sum(axis=0), 1.0)
+
+
+def test_exponential_two_edges():
+    g = tu.ExponentialTwoGraph(12)
+    assert sorted(g.successors(0)) == [0, 1, 2, 4, 8]
+    assert sorted(g.predecessors(0)) == [0, 4, 8, 10, 11]
+    w = nx.to_numpy_array(g)
+    assert np.isclose(w[0, 1], 0.2) and np.isclose(w[3, 3], 0.2)
+    assert tu.IsRegularGraph(g)
+    assert tu.IsTopologyEquivalent(tu.ExponentialGraph(12, base=2), g)
+    assert not tu.IsTopologyEquivalent(tu.ExponentialGraph(12, base=3), g)
+    assert not tu.IsTopologyEquivalent(g, None)
+
+
+def test_ring_styles_and_weights():
+    assert sorted(tu.RingGraph(5, 0).successors(0)) == [0, 1, 4]
+    assert sorted(tu.RingGraph(5, 1).successors(0)) == [0, 4]
+    assert sorted(tu.RingGraph(5, 2).successors(0)) == [0, 1]
+    sw, nw = tu.GetRecvWeights(tu.RingGraph(5, 2), 2)
+    assert sw == 0.5 and nw == {1: 0.5}
+    sw, nw = tu.GetSendWeights(tu.RingGraph(5, 2), 2)
+    assert sw == 0.5 and nw == {3: 0.5}
+
+
+def test_meshgrid_hastings_weights():
+    g = tu.MeshGrid2DGraph(6)          # 2 x 3
+    w = nx.to_numpy_array(g)
+    # corner 0 has 2 neighbours (3 with itself); edge node 1 has 3 (4 with itself)
+    assert np.isclose(w[0, 1], 1 / 4) and np.isclose(w[0, 3], 1 / 3)
+    assert np.isclose(w[0, 0], 1 - 1 / 4 - 1 / 3)
+    assert w[0, 2] == 0 and np.allclose(w, w.T)
+    with pytest.raises(AssertionError):
+        tu.MeshGrid2DGraph(6, shape=(4, 2))
+
+
+def test_star_and_symmetric_exponential():
+    w = nx.to_numpy_array(tu.StarGraph(4, center_rank=1))
+    assert np.isclose(w[0, 1], 0.25) and np.isclose(w[1, 0], 0.25) and w[0, 2] == 0
+    g = tu.SymmetricExponentialGraph(12, base=4)
+    assert sorted(g.successors(0)) == [0, 1, 4, 8, 11]
+
+
+@pytest.mark.parametrize("n", [4, 8, 16])
+def test_one_peer_exp2_send_recv_are_consistent_and_reach_exact_average(n):
+    topo = tu.ExponentialTwoGraph(n)
+    gens = [tu.GetDynamicOnePeerSendRecvRanks(topo, r) for r in range(n)]
+    x = np.arange(n, dtype=np.float64)
+    for k in range(int(np.log2(n))):
+        rounds = [next(g) for g in gens]
+        for r, (send, recv) in enumerate(rounds):
+            assert send == [(r + 2 ** k) % n]
+            assert recv == [(r - 2 ** k) % n]
+        x = np.array([(x[r] + sum(x[s] for s in rounds[r][1])) / (len(rounds[r][1]) + 1) for r in range(n)])
+    assert np.allclose(x, (n - 1) / 2)
+
+
+def test_one_peer_on_irregular_graph_matches_transpose():
+    topo = tu.StarGraph(5)
+    gens = [tu.GetDynamicOnePeerSendRecvRanks(topo, r) for r in range(5)]
+    for _ in range(6):
+        rounds = [next(g) for g in gens]
+        for r, (send, recv) in enumerate(rounds):
+            for s in send:
+                assert r in rounds[s][1]
+            for s in recv:
+                assert rounds[s][0] == [r]
+
+
+def test_machine_and_inner_outer_generators():
+    g = tu.GetExp2DynamicSendRecvMachineRanks(world_size=16, local_size=2, self_rank=5, local_rank=1)
+    assert [next(g) for _ in range(4)] == [([3], [1]), ([4], [0]), ([6], [6]), ([3], [1])]
+    for gen_fn in (tu.GetInnerOuterRingDynamicSendRecvRanks, tu.GetInnerOuterExpo2DynamicSendRecvRanks):
+        world, local = 12, 4
+        gens = [gen_fn(world, local, r) for r in range(world)]
+        for _ in range(9):
+            rounds = [next(g) for g in gens]
+            for r, (send, recv) in enumerate(rounds):
+                assert len(send) == 1 and len(recv) == 1
+                assert rounds[send[0]][1] == [r], (gen_fn.__name__, r, rounds)
+    with pytest.raises(AssertionError):
+        next(tu.GetInnerOuterRingDynamicSendRecvRanks(8, 2, 0))

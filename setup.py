@@ -51,6 +51,7 @@ ext = CUDAExtension(
     extra_compile_args={"cxx": ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-sign-compare", "-Wno-unused-function"],
                         "nvcc": NVCC_FLAGS},
     libraries=["rt"],
+    extra_link_args=["-Wl,--strip-debug"],
 )
 
 setup(

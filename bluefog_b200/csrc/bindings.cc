@@ -11,6 +11,7 @@
 #include "common/runtime.h"
 #include "common/windows.h"
 #include "cuda/bucket.h"
+#include "cuda/gemm_tcgen05.h"
 #include "cuda/gpu_channel.h"
 #include "cuda/symm_mem.h"
 
@@ -99,6 +100,13 @@ int PubElem(const std::string& dtype) {
   if (dtype == "float32") return kF32;
   if (dtype == "bfloat16") return kBF16;
   throw std::invalid_argument("published dtype must be float32 or bfloat16");
+}
+
+// One device word per process that the GEMM kernel sets when a bounded wait expired.
+at::Tensor& GemmStatusWord(const at::Tensor& like) {
+  static at::Tensor status;
+  if (!status.defined()) status = at::zeros({1}, like.options().dtype(at::kInt));
+  return status;
 }
 
 struct PyBucketArgs : BucketStepArgs {
@@ -263,6 +271,34 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     c10::cuda::CUDAGuard g(t.get_device());
     cudaError_t e = LaunchScale(t.data_ptr(), static_cast<unsigned long long>(t.numel()), s, ElemOf(t), CurrentStream(t.get_device()));
     TORCH_CHECK(e == cudaSuccess, "scale kernel launch failed: ", cudaGetErrorString(e));
+  });
+
+  // ---- tcgen05 GEMM -------------------------------------------------------------------------
+  m.def("gemm_supported", [] { return GemmSupported(); });
+  m.def("gemm_bf16_nt", [](at::Tensor a, at::Tensor w, c10::optional<at::Tensor> bias, int act) {
+    TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2, "gemm_bf16_nt expects 2-D CUDA tensors");
+    TORCH_CHECK(a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "gemm_bf16_nt expects bf16");
+    TORCH_CHECK(a.is_contiguous() && w.is_contiguous(), "gemm_bf16_nt expects contiguous tensors");
+    TORCH_CHECK(a.size(1) == w.size(1), "inner dimensions differ");
+    TORCH_CHECK(a.size(1) % 8 == 0, "K must be a multiple of 8");
+    c10::cuda::CUDAGuard g(a.get_device());
+    at::Tensor& status = GemmStatusWord(a);
+    at::Tensor out = at::empty({a.size(0), w.size(0)}, a.options());
+    const void* bptr = nullptr;
+    if (bias.has_value() && bias->defined()) {
+      TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->is_contiguous() && bias->numel() == w.size(0), "bias must be bf16 [N]");
+      bptr = bias->data_ptr();
+    }
+    cudaError_t e = LaunchGemmBf16NT(a.data_ptr(), w.data_ptr(), out.data_ptr(), bptr, static_cast<int>(a.size(0)),
+                                     static_cast<int>(w.size(0)), static_cast<int>(a.size(1)), act,
+                                     reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(a.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "gemm_bf16_nt launch failed: ", cudaGetErrorString(e));
+    return out;
+  }, py::arg("a"), py::arg("w"), py::arg("bias") = py::none(), py::arg("act") = 0);
+
+  m.def("gemm_status", [] {
+    at::Tensor probe = at::empty({0}, at::TensorOptions().device(at::kCUDA));
+    return GemmStatusWord(probe).item<int>();
   });
 
   py::class_<LocalWorld>(m, "LocalWorld")

@@ -1,0 +1,311 @@
+// bf16 GEMM on Blackwell's 5th-generation tensor cores:  C[M,N] = act(A[M,K] * B[N,K]^T + bias).
+//
+// One CTA computes one 128 x 128 output tile.  Warp 0 is the TMA producer: it streams
+// 128x64 tiles of A and B (K-major, 128-byte swizzle) into a 6-stage shared-memory ring with
+// `cp.async.bulk.tensor.2d` (no cluster multicast).  Warp 1 allocates 128 columns of tensor
+// memory and issues `tcgen05.mma.cta_group::1.kind::f16` (M=128, N=128, K=16) from one
+// elected lane, accumulating in fp32 in TMEM, and releases ring stages with
+// `tcgen05.commit`.  Warps 2-5 are the epilogue: once the accumulator is complete they read
+// it back with `tcgen05.ld.32x32b.x32`, add the bias, apply the activation, convert to bf16
+// and store.  Producer, MMA issuer and epilogue run concurrently and synchronise only
+// through mbarriers.  Every mbarrier wait has a time limit: on expiry the kernel records an
+// error code, stops issuing work, waits (bounded) for its TMA copies in flight, frees its TMEM
+// and returns.
+//
+// The reference has no GEMM of its own (its models call cuBLAS through PyTorch,
+// examples/pytorch_benchmark.py:76-100); this kernel is what the models of this library use for
+// their linear layers and 1x1 convolutions.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gemm_tcgen05.h"
+#include "comm_kernels.h"
+
+namespace bfb {
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int kStages = 6;
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;
+constexpr uint32_t kStageBytesA = BM * BK * 2;
+constexpr uint32_t kStageBytesB = BN * BK * 2;
+constexpr uint32_t kStageBytes = kStageBytesA + kStageBytesB;
+constexpr uint32_t kTmemCols = 128;
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + 256 /*barriers*/;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+// Instruction descriptor: D=f32, A=B=bf16, both K-major, N=128, M=128.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false (and raises *failed) when the limit expires or another role failed.
+__device__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* failed) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = now_ns();
+  for (;;) {
+    if (mbar_try(bar, parity)) return true;
+    if (*failed) return false;
+    if (now_ns() - t0 > kWaitLimitNs) {
+      *failed = 1;
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart (SBO), descriptor version 1 (Blackwell).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  const uint64_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16);
+  const uint64_t hi = 64ull | (1ull << 14) | (2ull << 29);
+  return lo | (hi << 32);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ float act_fn(float x, int act) {
+  if (act == kActRelu) return fmaxf(x, 0.f);
+  if (act == kActGeluTanh) {
+    const float c = 0.7978845608028654f;
+    return 0.5f * x * (1.f + tanhf(c * (x + 0.044715f * x * x * x)));
+  }
+  return x;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
+                    int act, unsigned int* __restrict__ status) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* stage_a = smem;
+  unsigned char* stage_b = smem + size_t(kStages) * kStageBytesA;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(kStages) * kStageBytes);
+  // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator complete
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int failed_s;
+  volatile int* failed = &failed_s;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM;
+  const int n0 = blockIdx.x * BN;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    failed_s = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bars[s]), 1);
+      mbar_init(smem_u32(&bars[kStages + s]), 1);
+    }
+    mbar_init(smem_u32(&bars[2 * kStages]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+
+  int armed = 0;  // producer: stages whose TMA copies were issued (for the failure path)
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kStages;
+        const uint32_t parity = ((kb / kStages) & 1) ^ 1;
+        if (!mbar_wait(smem_u32(&bars[kStages + s]), parity, failed)) break;
+        const uint32_t full = smem_u32(&bars[s]);
+        mbar_expect_tx(full, kStageBytes);
+        tma_load_2d(smem_u32(stage_a + size_t(s) * kStageBytesA), &map_a, full, kb * BK, m0);
+        tma_load_2d(smem_u32(stage_b + size_t(s) * kStageBytesB), &map_b, full, kb * BK, n0);
+        armed = kb + 1;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kStages;
+        const uint32_t parity = (kb / kStages) & 1;
+        if (!mbar_wait(smem_u32(&bars[s]), parity, failed)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t adesc = make_desc(smem_u32(stage_a + size_t(s) * kStageBytesA));
+        const uint64_t bdesc = make_desc(smem_u32(stage_b + size_t(s) * kStageBytesB));
+#pragma unroll
+        for (int k = 0; k < BK / kUmmaK; ++k) {
+          // advancing by 16 bf16 = 32 bytes inside the swizzle atom = +2 in the 16-byte address field
+          umma_bf16(tmem_base, adesc + uint64_t(2 * k), bdesc + uint64_t(2 * k), (kb | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&bars[kStages + s]));   // frees the stage when these MMAs have read it
+      }
+      if (!*failed) umma_commit(smem_u32(&bars[2 * kStages]));  // accumulator complete
+    }
+  } else {
+    // Epilogue warps 2..5: TMEM lane group = warp % 4.
+    const int q = warp & 3;
+    const bool ok = mbar_wait(smem_u32(&bars[2 * kStages]), 0, failed);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const int m = m0 + q * 32 + lane;
+      const bool vec_ok = (N % 8) == 0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int nbase = n0 + c * 32;
+        if (m < M && nbase < N) {
+          __nv_bfloat16* dst = out + size_t(m) * N + nbase;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int n = nbase + j * 8;
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float x = __uint_as_float(r[j * 8 + i]);
+              if (bias != nullptr && n + i < N) x += __bfloat162float(bias[n + i]);
+              v[i] = act_fn(x, act);
+            }
+            if (vec_ok && n + 8 <= N) {
+              uint4 pk;
+              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+              *reinterpret_cast<uint4*>(dst + j * 8) = pk;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                if (n + i < N) dst[j * 8 + i] = __float2bfloat16_rn(v[i]);
+            }
+          }
+        }
+      }
+    }
+  }
+  // Tear-down. On the failure path the producer first waits (bounded) for the copies it issued.
+  if (warp == 0 && lane == 0 && *failed) {
+    const int first = armed > kStages ? armed - kStages : 0;
+    for (int kb = first; kb < armed; ++kb) {
+      const unsigned long long t0 = now_ns();
+      while (!mbar_try(smem_u32(&bars[kb % kStages]), (kb / kStages) & 1) && now_ns() - t0 < kWaitLimitNs) {}
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+  if (threadIdx.x == 0 && failed_s && status != nullptr) atomicExch(status, 1u);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn GetEncodeFn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return EncodeTiledFn(nullptr);
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+bool MakeMap(CUtensorMap* map, const void* base, int rows, int cols /*K*/, int box_rows) {
+  EncodeTiledFn fn = GetEncodeFn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool GemmSupported() { return GetEncodeFn() != nullptr; }
+
+cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void* bias, int M, int N, int K, int act,
+                             unsigned int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
+  // TMA needs 16-byte aligned bases and row pitches: K must be a multiple of 8 bf16 elements.
+  if ((K % 8) != 0 || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return cudaErrorInvalidValue;
+  CUtensorMap map_a, map_b;
+  if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, BN)) return cudaErrorInvalidValue;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  gemm_bf16_nt_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, static_cast<__nv_bfloat16*>(out),
+                                                             static_cast<const __nv_bfloat16*>(bias), M, N, K, act, status);
+  CountKernelLaunch();
+  return cudaGetLastError();
+}
+
+}  // namespace bfb

@@ -1,0 +1,112 @@
+"""GPT-2 (decoder-only transformer) with Hugging Face parameter names.
+
+Used by the GPT-2-medium data-parallel workload (24 layers, d_model 1024, 16 heads, vocab
+50257, sequence 1024).  The reference has no transformer code; the library only needs a
+single-GPU model whose parameters the distributed optimizers average.  Linear layers run on
+the hand-written tcgen05 GEMM when the activations are bf16 (``use_b200_gemm``); attention
+uses PyTorch's fused scaled-dot-product attention.
+"""
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+class B200Linear(nn.Linear):
+    """nn.Linear ([out, in] weight) that routes bf16 CUDA inputs to the tcgen05 GEMM."""
+
+    def __init__(self, in_features, out_features, bias=True, use_b200_gemm=True, act=None):
+        super().__init__(in_features, out_features, bias=bias)
+        self.use_b200_gemm = use_b200_gemm
+
+    def forward(self, x):
+        if self.use_b200_gemm and x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
+            from bluefog_b200.ops import gemm
+            if gemm.available() and self.in_features % 8 == 0:
+                y = gemm.linear(x.reshape(-1, self.in_features), self.weight, self.bias)
+                return y.view(*x.shape[:-1], self.out_features)
+        return F.linear(x, self.weight, self.bias)
+
+
+class Attention(nn.Module):
+    def __init__(self, d_model, n_head, use_b200_gemm):
+        super().__init__()
+        self.n_head = n_head
+        self.c_attn = B200Linear(d_model, 3 * d_model, use_b200_gemm=use_b200_gemm)
+        self.c_proj = B200Linear(d_model, d_model, use_b200_gemm=use_b200_gemm)
+
+    def forward(self, x):
+        b, t, c = x.shape
+        q, k, v = self.c_attn(x).split(c, dim=2)
+        shape = (b, t, self.n_head, c // self.n_head)
+        q, k, v = (z.view(shape).transpose(1, 2) for z in (q, k, v))
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        return self.c_proj(y.transpose(1, 2).reshape(b, t, c))
+
+
+class MLP(nn.Module):
+    def __init__(self, d_model, use_b200_gemm):
+        super().__init__()
+        self.c_fc = B200Linear(d_model, 4 * d_model, use_b200_gemm=use_b200_gemm)
+        self.c_proj = B200Linear(4 * d_model, d_model, use_b200_gemm=use_b200_gemm)
+
+    def forward(self, x):
+        return self.c_proj(F.gelu(self.c_fc(x), approximate="tanh"))
+
+
+class Block(nn.Module):
+    def __init__(self, d_model, n_head, use_b200_gemm):
+        super().__init__()
+        self.ln_1 = nn.LayerNorm(d_model)
+        self.attn = Attention(d_model, n_head, use_b200_gemm)
+        self.ln_2 = nn.LayerNorm(d_model)
+        self.mlp = MLP(d_model, use_b200_gemm)
+
+    def forward(self, x):
+        x = x + self.attn(self.ln_1(x))
+        return x + self.mlp(self.ln_2(x))
+
+
+class GPT2(nn.Module):
+    def __init__(self, vocab_size=50257, n_positions=1024, d_model=768, n_layer=12, n_head=12,
+                 use_b200_gemm=True):
+        super().__init__()
+        self.wte = nn.Embedding(vocab_size, d_model)
+        self.wpe = nn.Embedding(n_positions, d_model)
+        self.h = nn.ModuleList([Block(d_model, n_head, use_b200_gemm) for _ in range(n_layer)])
+        self.ln_f = nn.LayerNorm(d_model)
+        self.use_b200_gemm = use_b200_gemm
+        self.apply(self._init)
+        for name, p in self.named_parameters():
+            if name.endswith("c_proj.weight"):
+                nn.init.normal_(p, mean=0.0, std=0.02 / math.sqrt(2 * n_layer))
+
+    @staticmethod
+    def _init(m):
+        if isinstance(m, nn.Linear):
+            nn.init.normal_(m.weight, mean=0.0, std=0.02)
+            if m.bias is not None:
+                nn.init.zeros_(m.bias)
+        elif isinstance(m, nn.Embedding):
+            nn.init.normal_(m.weight, mean=0.0, std=0.02)
+
+    def forward(self, idx, targets=None):
+        b, t = idx.shape
+        pos = torch.arange(t, device=idx.device)
+        x = self.wte(idx) + self.wpe(pos)
+        for block in self.h:
+            x = block(x)
+        x = self.ln_f(x)
+        logits = F.linear(x, self.wte.weight)     # tied output embedding
+        if targets is None:
+            return logits
+        return F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.view(-1))
+
+
+def gpt2_small(**kw):
+    return GPT2(d_model=768, n_layer=12, n_head=12, **kw)
+
+
+def gpt2_medium(**kw):
+    return GPT2(d_model=1024, n_layer=24, n_head=16, **kw)

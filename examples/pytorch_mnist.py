@@ -1,0 +1,92 @@
+"""LeNet on MNIST-shaped data with decentralized SGD and a periodic global average every
+100 batches (role of the reference's examples/pytorch_mnist.py).  Reads torchvision's MNIST
+from --data-dir when it exists there; otherwise a synthetic set of the same shape is used.
+
+  bfrun -np 4 python examples/pytorch_mnist.py --epochs 1 --no-cuda
+"""
+import argparse
+import os
+
+import torch
+import torch.nn.functional as F
+
+import bluefog_b200.torch as bf
+from bluefog_b200.common import topology_util
+from bluefog_b200.models.lenet import LeNet
+
+parser = argparse.ArgumentParser()
+parser.add_argument("--batch-size", type=int, default=64)
+parser.add_argument("--epochs", type=int, default=1)
+parser.add_argument("--lr", type=float, default=0.01)
+parser.add_argument("--momentum", type=float, default=0.5)
+parser.add_argument("--data-dir", default="./data")
+parser.add_argument("--dist-optimizer", default="neighbor_allreduce",
+                    choices=["neighbor_allreduce", "allreduce", "gradient_allreduce", "win_put", "push_sum"])
+parser.add_argument("--average-test-result", action="store_true")
+parser.add_argument("--no-cuda", action="store_true")
+args = parser.parse_args()
+
+bf.init()
+cuda = not args.no_cuda and torch.cuda.is_available() and bf._b.device() >= 0
+device = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
+torch.manual_seed(42)
+
+
+def load_data():
+    try:
+        from torchvision import datasets, transforms
+        if os.path.isdir(os.path.join(args.data_dir, "MNIST")):
+            ds = datasets.MNIST(args.data_dir, train=True, download=False, transform=transforms.ToTensor())
+            x = ds.data.float().div(255).sub(0.1307).div(0.3081).unsqueeze(1)
+            return x, ds.targets
+    except Exception:
+        pass
+    g = torch.Generator().manual_seed(7)
+    y = torch.randint(0, 10, (6400,), generator=g)
+    protos = torch.randn(10, 1, 28, 28, generator=g)
+    return protos[y] + 0.5 * torch.randn(6400, 1, 28, 28, generator=g), y
+
+
+x_all, y_all = load_data()
+shard = slice(bf.rank(), None, bf.size())          # every rank trains on its own shard
+x_all, y_all = x_all[shard], y_all[shard]
+model = LeNet().to(device)
+bf.broadcast_parameters(model.state_dict(), root_rank=0)
+base = torch.optim.SGD(model.parameters(), lr=args.lr * bf.size(), momentum=args.momentum)
+CT = bf.CommunicationType
+if args.dist_optimizer == "neighbor_allreduce":
+    optimizer = bf.DistributedAdaptWithCombineOptimizer(base, model, CT.neighbor_allreduce)
+elif args.dist_optimizer == "allreduce":
+    optimizer = bf.DistributedAdaptWithCombineOptimizer(base, model, CT.allreduce)
+elif args.dist_optimizer == "gradient_allreduce":
+    optimizer = bf.DistributedGradientAllreduceOptimizer(base, model)
+elif args.dist_optimizer == "win_put":
+    optimizer = bf.DistributedWinPutOptimizer(base, model)
+else:
+    optimizer = bf.DistributedPushSumOptimizer(base, model)
+
+batches = len(x_all) // args.batch_size
+for epoch in range(args.epochs):
+    model.train()
+    perm = torch.randperm(len(x_all))
+    for b in range(batches):
+        idx = perm[b * args.batch_size:(b + 1) * args.batch_size]
+        x, y = x_all[idx].to(device), y_all[idx].to(device)
+        # every 100 batches one exact global average keeps the ranks from drifting apart
+        if args.dist_optimizer == "neighbor_allreduce" and hasattr(optimizer, "communication_type"):
+            optimizer.communication_type = CT.allreduce if b % 100 == 99 else CT.neighbor_allreduce
+        optimizer.zero_grad()
+        loss = F.cross_entropy(model(x), y)
+        loss.backward()
+        optimizer.step()
+        if b % 20 == 0 and bf.rank() == 0:
+            print(f"epoch {epoch} batch {b}/{batches} loss {loss.item():.4f}", flush=True)
+    model.eval()
+    with torch.no_grad():
+        out = model(x_all[:1024].to(device))
+        acc = (out.argmax(1).cpu() == y_all[:1024]).float().mean()
+    acc = bf.allreduce(acc.reshape(1), name="accuracy").item() if args.average_test_result else acc.item()
+    if bf.rank() == 0:
+        print(f"epoch {epoch}: accuracy on the training shard {acc:.3f}")
+bf.win_free()
+bf.barrier()

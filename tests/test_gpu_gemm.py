@@ -1,0 +1,53 @@
+"""tcgen05 GEMM against an fp32 PyTorch matmul of the same bf16 inputs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, w, bias, act):
+    y = a.float() @ w.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    if act == 1:
+        y = torch.relu(y)
+    elif act == 2:
+        y = torch.nn.functional.gelu(y, approximate="tanh")
+    return y
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 512), (256, 384, 1024), (200, 136, 72),
+                                   (1, 1000, 2048), (3136, 64, 256), (4096, 4096, 1024), (777, 50264, 64)])
+@pytest.mark.parametrize("with_bias,act", [(False, 0), (True, 1), (True, 2)])
+def test_gemm_matches_fp32_reference(M, N, K, with_bias, act):
+    from bluefog_b200 import _C
+    from bluefog_b200.ops import gemm
+    assert gemm.available(), "the tcgen05 GEMM must be usable on a B200 box"
+    g = torch.Generator().manual_seed(M * 7 + N * 3 + K)
+    a = (torch.randn(M, K, generator=g) * 0.5).cuda().to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.5).cuda().to(torch.bfloat16)
+    bias = torch.randn(N, generator=g).cuda().to(torch.bfloat16) if with_bias else None
+    out = _C.gemm_bf16_nt(a, w, bias, act)
+    torch.cuda.synchronize()
+    assert _C.gemm_status() == 0, "a bounded wait inside the kernel expired"
+    ref = _ref(a, w, bias, act)
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 1e-2 * scale + 1e-2, (M, N, K, err, scale)
+
+
+def test_linear_autograd_matches_torch():
+    from bluefog_b200.ops import gemm
+    torch.manual_seed(0)
+    a = torch.randn(300, 256, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(512, 256, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(512, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    y = gemm.linear(a, w, b)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    a2, w2, b2 = (t.detach().float().requires_grad_(True) for t in (a, w, b))
+    y2 = torch.nn.functional.linear(a2, w2, b2)
+    y2.backward(gy.float())
+    for got, ref in ((y, y2), (a.grad, a2.grad), (w.grad, w2.grad), (b.grad, b2.grad)):
+        err = (got.float() - ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item() + 1e-2

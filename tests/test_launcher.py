@@ -1,0 +1,60 @@
+"""bfrun: argument surface, environment of the ranks, exit codes, refusal of remote hosts."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ENV = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), BLUEFOG_B200_FORCE_CPU="1")
+
+
+def bfrun(*args, timeout=120):
+    return subprocess.run([sys.executable, "-m", "bluefog_b200.run.run", *args], env=ENV, capture_output=True,
+                          text=True, timeout=timeout)
+
+
+def test_version_and_required_arguments():
+    assert bfrun("-v").stdout.strip() == "0.1.0"
+    assert bfrun("python", "-c", "pass").returncode != 0          # -np missing
+    assert bfrun("-np", "2").returncode != 0                       # command missing
+
+
+def test_ranks_get_identity_and_flags(tmp_path):
+    code = ("import os;print('R',os.environ['RANK'],os.environ['WORLD_SIZE'],os.environ['LOCAL_RANK'],"
+            "os.environ.get('BLUEFOG_TIMELINE'),os.environ.get('BLUEFOG_LOG_LEVEL'))")
+    out = bfrun("-np", "3", "--timeline-filename", str(tmp_path / "t_"), "--verbose", sys.executable, "-c", code)
+    assert out.returncode == 0, out.stderr
+    lines = sorted(l for l in out.stdout.splitlines() if l.startswith("R "))
+    assert [l.split()[1] for l in lines] == ["0", "1", "2"]
+    assert all(l.split()[2] == "3" and l.split()[4].endswith("t_") and l.split()[5] == "debug" for l in lines)
+
+
+def test_exit_code_of_a_failing_rank_is_returned():
+    code = "import os,sys;sys.exit(7 if os.environ['RANK']=='1' else 0)"
+    assert bfrun("-np", "2", sys.executable, "-c", code).returncode == 7
+
+
+def test_remote_hosts_are_refused():
+    out = bfrun("-np", "2", "-H", "some-other-machine.invalid:2", sys.executable, "-c", "pass")
+    assert out.returncode != 0 and "not supported" in (out.stderr + out.stdout)
+    assert bfrun("-np", "2", "-H", "localhost:2", sys.executable, "-c", "pass").returncode == 0
+
+
+def test_end_to_end_allreduce_under_bfrun():
+    code = ("import torch, bluefog_b200.torch as bf; bf.init(); "
+            "x = bf.allreduce(torch.full((3,), float(bf.rank()))); "
+            "assert x.tolist() == [1.5] * 3, x; bf.barrier(); bf.shutdown()")
+    out = bfrun("-np", "4", sys.executable, "-c", code)
+    assert out.returncode == 0, out.stderr[-2000:]
+
+
+def test_host_parsing(tmp_path):
+    from bluefog_b200.run import network_util, env_util
+    assert network_util.parse_hosts("a:2, b:4,c") == [("a", 2), ("b", 4), ("c", 1)]
+    f = tmp_path / "hosts"
+    f.write_text("# comment\nlocalhost slots=8\nnode2 slots=4 max_slots=4\n")
+    assert network_util.parse_hostfile(str(f)) == [("localhost", 8), ("node2", 4)]
+    assert network_util.is_local_host("localhost") and network_util.is_local_host("127.0.0.1")
+    env = env_util.rank_environment({"A": "1", "RANK": "5", "BASH_FUNC_x%%": "y"}, timeline="p", verbose=True)
+    assert env == {"A": "1", "BLUEFOG_TIMELINE": "p", "BLUEFOG_LOG_LEVEL": "debug"}

@@ -35,7 +35,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--model", default="resnet50")
-    ap.add_argument("--no-b200-gemm", action="store_true")
+    ap.add_argument("--b200-gemm", action="store_true",
+                    help="route 1x1 convolutions and the classifier through the tcgen05 GEMM")
+    ap.add_argument("--no-graphs", action="store_true", help="drive forward/backward op by op instead of a CUDA graph")
     ap.add_argument("--exchange-dtype", default="float32", choices=["float32", "bfloat16"])
     return ap.parse_args()
 
@@ -113,7 +115,7 @@ def run_ours(args):
     dev = torch.device("cuda", torch.cuda.current_device())
     bf.set_topology(bf.ExponentialTwoGraph(size))
     torch.manual_seed(1234 + rank)
-    model = build_model(args.model, not args.no_b200_gemm).to(dev).to(memory_format=torch.channels_last)
+    model = build_model(args.model, args.b200_gemm).to(dev).to(memory_format=torch.channels_last)
     bf.broadcast_parameters(model.state_dict(), root_rank=0)
     base = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
     opt = bf.DistributedNeighborAllreduceOptimizer(
@@ -136,11 +138,19 @@ def run_ours(args):
             opt.src_weights = {r: w for r in recv}
             opt.self_weight = w
 
+    graphed = None
+    if not args.no_graphs:
+        from bluefog_b200.utils.graphs import GraphedForwardBackward
+        graphed = GraphedForwardBackward(model, loss_fn, opt, dev_x, dev_y)
+
     def step(x, y):
         set_weights()
-        opt.zero_grad()
-        loss = loss_fn(model(x).float(), y)
-        loss.backward()
+        if graphed is not None:
+            loss = graphed(x, y)          # zero_grad + forward + loss + backward as one CUDA graph
+        else:
+            opt.zero_grad()
+            loss = loss_fn(model(x).float(), y)
+            loss.backward()
         opt.step()
         return loss
 
@@ -168,6 +178,8 @@ def run_ours(args):
     e1.record()
     torch.cuda.synchronize()
     launches = bf._b.native.kernel_launch_count() - l0
+    if graphed is not None:
+        launches += args.steps * graphed.native_launches_per_replay
     ms_dev = max_over_ranks(e0.elapsed_time(e1))
     # end to end: pinned host -> device copy of the inputs and a loss read-back every step
     bf.barrier()
@@ -196,7 +208,8 @@ def run_ours(args):
             "config": {"model": args.model, "global_batch": B * size, "batch_per_gpu": B, "image": "3x224x224",
                        "parallelism": f"dp{size}", "optimizer": "SGD momentum 0.9 lr 0.1, fp32 master weights",
                        "topology": "ExponentialTwoGraph, dynamic one-peer", "exchange_dtype": args.exchange_dtype,
-                       "b200_gemm": bool(not args.no_b200_gemm and gemm.available()),
+                       "b200_gemm": bool(args.b200_gemm and gemm.available()),
+                       "cuda_graph": "forward+backward" if not args.no_graphs else "none",
                        "l2": "inputs plus activations exceed the 126 MB L2 every step; no explicit flush"},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 2), "unit": "img/s",

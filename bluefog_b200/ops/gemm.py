@@ -2,7 +2,7 @@
 
 ``linear(a, w, bias)`` computes ``a @ w.T + bias`` for row-major bf16 ``a`` [M, K] and
 ``w`` [N, K] with fp32 accumulation in tensor memory.  The backward pass uses the same
-kernel for both products (dA = dY @ W, dW = dY.T @ A).
+kernel for dA = dY @ W; dW = dY.T @ A goes to the library GEMM (see ``_LinearFn.backward``).
 """
 import torch
 
@@ -15,6 +15,11 @@ def available() -> bool:
     """True when the tcgen05 GEMM kernel is built into the native module and a GPU is present."""
     C = _b.native
     return bool(torch.cuda.is_available() and hasattr(C, "gemm_bf16_nt") and C.gemm_supported())
+
+
+def _nt_ok(m_rows, n_rows, k):
+    """The kernel needs a reduction length that is a multiple of 8 (16-byte TMA row pitch)."""
+    return k % 8 == 0 and m_rows > 0 and n_rows > 0
 
 
 class _LinearFn(torch.autograd.Function):
@@ -30,11 +35,17 @@ class _LinearFn(torch.autograd.Function):
         dy = dy.contiguous()
         da = dw = db = None
         if ctx.needs_input_grad[0]:
-            # dA[M,K] = dY[M,N] @ W[N,K]  ->  NT form needs W^T [K,N] as the "weight"
-            da = _b.native.gemm_bf16_nt(dy, w.t().contiguous(), None, 0)
+            # dA[M,K] = dY[M,N] @ W[N,K]: the reduction runs over N, so the kernel's second operand
+            # is W^T [K,N]; weights are small, the transpose copy is cheap.
+            if _nt_ok(dy.shape[0], w.shape[1], dy.shape[1]):
+                da = _b.native.gemm_bf16_nt(dy, w.t().contiguous(), None, 0)
+            else:
+                da = dy @ w
         if ctx.needs_input_grad[1]:
-            # dW[N,K] = dY^T[N,M] @ A[M,K] -> NT form: (dY^T) @ (A^T)^T
-            dw = _b.native.gemm_bf16_nt(dy.t().contiguous(), a.t().contiguous(), None, 0)
+            # dW[N,K] = dY^T @ A reduces over the (huge) row dimension of two activation matrices.
+            # Both operands are MN-major for that product and it wants split-K; it is left to the
+            # library GEMM, which takes the transposed views without copies.
+            dw = dy.t() @ a
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy.float().sum(0).to(dy.dtype)
         return da, dw, db
@@ -42,4 +53,6 @@ class _LinearFn(torch.autograd.Function):
 
 def linear(a: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
     """``a @ w.T (+ bias)`` on the tcgen05 kernel; a: [M, K] bf16, w: [N, K] bf16."""
+    if a.shape[-1] % 8 != 0:
+        return torch.nn.functional.linear(a, w, bias)
     return _LinearFn.apply(a.contiguous(), w.contiguous(), bias)

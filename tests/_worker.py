@@ -438,6 +438,68 @@ def checkpoint():
     bf.barrier()
 
 
+@case
+def gpu_fused_optimizers():
+    """Fused bucket engine on real GPUs: consensus of the parameters and convergence."""
+    r, n, d = bf.rank(), bf.size(), dev()
+    assert d.type == "cuda"
+    torch.manual_seed(0)
+    w_true = torch.randn(64, 8)
+    g = torch.Generator().manual_seed(100 + r)
+    x = torch.randn(512, 64, generator=g)
+    y = (x @ w_true + 0.1 * torch.randn(512, 8, generator=g)).to(d)
+    x = x.to(d)
+    for style, factory in (("awc", bf.DistributedAdaptWithCombineOptimizer),
+                           ("atc", bf.DistributedAdaptThenCombineOptimizer),
+                           ("grad", bf.DistributedGradientAllreduceOptimizer)):
+        for compute in (torch.float32, torch.bfloat16):
+            torch.manual_seed(1)
+            model = torch.nn.Sequential(torch.nn.Linear(64, 32), torch.nn.ReLU(), torch.nn.Linear(32, 8)).to(d)
+            bf.broadcast_parameters(model.state_dict(), 0)
+            opt = factory(torch.optim.Adam(model.parameters(), lr=0.01), model, compute_dtype=compute)
+            assert hasattr(opt, "master_parameters"), "the fused engine must be used on GPUs"
+            gen = tu.GetDynamicOnePeerSendRecvRanks(bf.load_topology(), r)
+            first = None
+            for it in range(150):
+                if style != "grad" and n > 1:
+                    send, recv = next(gen)
+                    opt.dst_weights, opt.self_weight = send, 1.0 / (len(recv) + 1)
+                    opt.src_weights = {s: 1.0 / (len(recv) + 1) for s in recv}
+                opt.zero_grad()
+                loss = torch.nn.functional.mse_loss(model(x.to(compute)).float(), y)
+                loss.backward()
+                opt.step()
+                first = first if first is not None else loss.item()
+            torch.cuda.synchronize()
+            opt.check()
+            assert loss.item() < 0.25 * first, (style, compute, first, loss.item())
+            flat = torch.cat([v.reshape(-1) for v in opt.master_parameters().values()])
+            spread = bf.allreduce((flat - bf.allreduce(flat)).abs().max().reshape(1), average=False).item()
+            assert spread < (1e-5 if style == "grad" else 0.2), (style, compute, spread)
+            bf.barrier()
+
+
+@case
+def gpu_wait_timeout():
+    """Rank 1 never issues the operation rank 0 is waiting for: rank 0's kernel gives up after
+    the wait limit (set to 300 ms by the test) and the operation raises; nothing hangs."""
+    r, n, d = bf.rank(), bf.size(), dev()
+    x = torch.ones(1024, device=d)
+    bf.neighbor_allreduce(x)          # creates the channel while everything still matches
+    bf.barrier()
+    bf.set_skip_negotiate_stage(True)
+    if r == 0:
+        try:
+            bf.neighbor_allreduce(x, self_weight=0.5, src_weights={1: 0.5}, dst_weights=[1], enable_topo_check=False)
+            raise AssertionError("expected the device wait to time out")
+        except RuntimeError as exc:
+            assert "timed out" in str(exc), str(exc)
+    else:
+        time.sleep(2.0)
+    assert torch.ones(4, device=d).sum().item() == 4.0     # the CUDA context is still usable
+    bf.barrier()
+
+
 def main():
     name = sys.argv[1]
     if name not in ("timeline",):

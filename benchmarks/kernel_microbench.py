@@ -1,0 +1,121 @@
+"""Single-GPU timing of the hand-written kernels against the measured machine peaks.
+
+  python benchmarks/kernel_microbench.py --kernel bucket --numel 67108864
+  python benchmarks/kernel_microbench.py --kernel combine --numel 67108864 --dtype bfloat16
+  python benchmarks/kernel_microbench.py --kernel gemm --m 8192 --n 8192 --k 8192
+  python benchmarks/kernel_microbench.py --kernel winput --numel 67108864
+
+The multi-rank kernels run on a one-process "local world": the peers' buffers are other
+buffers of the same GPU, so the numbers are HBM-bound, not NVLink-bound; they show how close
+the kernels come to the copy bandwidth of the device.  Inputs are larger than the 126 MB L2.
+Timing: CUDA events around `--iters` launches after `--warmup`, reported per launch.
+"""
+import argparse
+import json
+import os
+
+import torch
+
+from bluefog_b200 import _C
+
+PEAKS = {"hbm_gbs": 6530.6, "bf16_tflops": 1659.0}
+_peaks_file = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+if os.path.exists(_peaks_file):
+    with open(_peaks_file) as f:
+        PEAKS.update({k: v for k, v in json.load(f).items() if k in PEAKS})
+
+
+def timed(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def bench_bucket(args):
+    n, W = args.numel, 2
+    buckets = _C.Bucket.create_local(W, n, args.exchange, 0)
+    master = [torch.randn(n, device="cuda") for _ in range(W)]
+    grad = [torch.randn(n, device="cuda").to(torch.bfloat16) for _ in range(W)]
+    mom = [torch.zeros(n, device="cuda") for _ in range(W)]
+    shadow = [torch.zeros(n, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    for r in range(W):
+        a = _C.BucketStepArgs()
+        a.mode, a.master = 4, master[r]
+        buckets[r].step(a)
+    state = {"first": True}
+
+    def step():
+        for r in range(W):
+            a = _C.BucketStepArgs()
+            a.mode, a.opt = 0, 1
+            a.master, a.grad, a.state1, a.shadow = master[r], grad[r], mom[r], shadow[r]
+            a.lr, a.momentum, a.first_step = 0.01, 0.9, state["first"]
+            a.self_weight, a.src_ranks, a.src_weights, a.n_readers = 0.5, [1 - r], [0.5], 1
+            buckets[r].step(a)
+        state["first"] = False
+
+    ms = timed(step, args.iters, args.warmup) / W
+    pub = 4 if args.exchange == "float32" else 2
+    # per element: master r+w (8), peer published copy r, own published copy w, grad r (2), momentum r+w (8), shadow w (2)
+    bytes_per_launch = n * (8 + 2 * pub + 2 + 8 + 2)
+    return {"kernel": "bucket_step_kernel (AWC, SGD momentum, bf16 grad+shadow)", "numel": n, "ms": ms,
+            "gbs": bytes_per_launch / ms / 1e6, "frac_of_measured_hbm": bytes_per_launch / ms / 1e6 / PEAKS["hbm_gbs"]}
+
+
+def bench_combine(args):
+    dtype = getattr(torch, args.dtype)
+    n, W = args.numel, 2
+    esize = torch.empty(0, dtype=dtype).element_size()
+    world = _C.LocalWorld(W, n * esize + 4096, 0)
+    xs = [torch.randn(n, device="cuda").to(dtype) for _ in range(W)]
+    outs = [torch.empty(n, device="cuda", dtype=dtype) for _ in range(W)]
+
+    def step():
+        rounds = [world.publish(r, [xs[r]], None, 1) for r in range(W)]
+        for r in range(W):
+            world.combine(r, rounds[r], [outs[r]], 0.5, [1 - r], [0.5], False, 1.0)
+
+    ms = timed(step, args.iters, args.warmup) / W
+    # publish: read x, write arena; combine: read own arena + peer arena, write out
+    bytes_per_rank = n * esize * 5
+    return {"kernel": "pack_publish_kernel + combine_kernel", "dtype": args.dtype, "numel": n, "ms_per_rank": ms,
+            "gbs": bytes_per_rank / ms / 1e6, "frac_of_measured_hbm": bytes_per_rank / ms / 1e6 / PEAKS["hbm_gbs"]}
+
+
+def bench_gemm(args):
+    a = (torch.randn(args.m, args.k, device="cuda") * 0.1).to(torch.bfloat16)
+    w = (torch.randn(args.n, args.k, device="cuda") * 0.1).to(torch.bfloat16)
+    ms = timed(lambda: _C.gemm_bf16_nt(a, w, None, 0), args.iters, args.warmup)
+    ms_lib = timed(lambda: torch.matmul(a, w.t()), args.iters, args.warmup)
+    flops = 2.0 * args.m * args.n * args.k
+    return {"kernel": "gemm_bf16_nt_kernel (tcgen05)", "m": args.m, "n": args.n, "k": args.k, "ms": ms,
+            "tflops": flops / ms / 1e9, "frac_of_measured_bf16": flops / ms / 1e9 / PEAKS["bf16_tflops"],
+            "library_ms": ms_lib, "library_tflops": flops / ms_lib / 1e9, "status": _C.gemm_status()}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", required=True, choices=["bucket", "combine", "gemm"])
+    ap.add_argument("--numel", type=int, default=64 * 1024 * 1024)
+    ap.add_argument("--dtype", default="float32")
+    ap.add_argument("--exchange", default="float32", choices=["float32", "bfloat16"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    torch.cuda.set_device(0)
+    out = {"bucket": bench_bucket, "combine": bench_combine, "gemm": bench_gemm}[args.kernel](args)
+    print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -20,11 +20,11 @@ def _groups(params):
     groups, cur, cur_bytes = [], [], 0
     for p in params:
         nb = p.numel() * p.element_size()
-        if cur and cur_bytes + 2 * nb > FUSION_BYTES:   # self part + one recv part per in-neighbor
+        if cur and cur_bytes + nb > FUSION_BYTES // 2:   # self part + one recv part per in-neighbor
             groups.append(cur)
             cur, cur_bytes = [], 0
         cur.append(p)
-        cur_bytes += 2 * nb
+        cur_bytes += nb
     if cur:
         groups.append(cur)
     return groups
@@ -34,6 +34,20 @@ def neighbor_average_(params, send_to, recv_from, fusion, recv_fusion):
     """One-peer neighbor averaging of ``params`` in place, the reference's way."""
     w = 1.0 / (len(recv_from) + 1)
     for group in _groups(params):
+        if len(group) == 1 and group[0].numel() > fusion.numel():
+            # a tensor that does not fit the fusion buffer travels on its own (the reference sends
+            # such tensors unfused, straight from and into tensor memory)
+            p = group[0]
+            recv = [torch.empty_like(p.data) for _ in recv_from]
+            ops = [dist.P2POp(dist.irecv, recv[j], r) for j, r in enumerate(recv_from)]
+            ops += [dist.P2POp(dist.isend, p.data, d) for d in send_to]
+            if ops:
+                for req in dist.batch_isend_irecv(ops):
+                    req.wait()
+            p.data.mul_(w)
+            for t in recv:
+                p.data.add_(t, alpha=w)
+            continue
         off = 0
         for p in group:                       # MemcpyInFusionBuffer: one copy per tensor
             n = p.numel()
@@ -78,8 +92,8 @@ def run(args):
         mp.grad = torch.zeros_like(mp)
     opt = torch.optim.SGD(master, lr=0.1, momentum=0.9)
     params = list(model.parameters())
-    fusion = torch.empty(FUSION_BYTES // 4, device=dev)
-    recv_fusion = [torch.empty(FUSION_BYTES // 4, device=dev) for _ in range(3)]
+    fusion = torch.empty(FUSION_BYTES // 8, device=dev)            # self half of the 8 MiB buffer
+    recv_fusion = [torch.empty(FUSION_BYTES // 8, device=dev) for _ in range(3)]
     B = args.batch
     g = torch.Generator().manual_seed(rank)
     host_x = torch.randn(B, 3, 224, 224, generator=g).pin_memory()

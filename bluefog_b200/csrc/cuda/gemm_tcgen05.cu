@@ -20,6 +20,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+#include <string>
+
 #include "gemm_tcgen05.h"
 #include "comm_kernels.h"
 
@@ -256,6 +259,185 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (threadIdx.x == 0 && failed_s && status != nullptr) atomicExch(status, 1u);
 }
 
+
+// ------------------------------------------------------------------------------------------ //
+// Persistent variant: one CTA per SM walks over output tiles of 128 x BN_; the accumulator is
+// double-buffered in tensor memory (2 x BN_ columns) so that the epilogue of tile i runs while
+// the MMAs of tile i+1 are issued.  Ring-stage and accumulator hand-over use four kinds of
+// mbarriers: full/empty per smem stage, acc_full/acc_empty per accumulator buffer.
+// ------------------------------------------------------------------------------------------ //
+template <int BN_>
+struct PersistentCfg {
+  static constexpr int kStagesP = (BN_ == 256) ? 4 : 6;
+  static constexpr uint32_t kBytesA = BM * BK * 2;
+  static constexpr uint32_t kBytesB = BN_ * BK * 2;
+  static constexpr uint32_t kBytesStage = kBytesA + kBytesB;
+  static constexpr uint32_t kCols = 2 * BN_;
+  static constexpr size_t kSmem = 1024 + size_t(kStagesP) * kBytesStage + 256;
+  static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN_ >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+};
+
+template <int BN_>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                               __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ bias, int M, int N,
+                               int K, int act, unsigned int* __restrict__ status) {
+  using Cfg = PersistentCfg<BN_>;
+  constexpr int S = Cfg::kStagesP;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* stage_a = smem;
+  unsigned char* stage_b = smem + size_t(S) * Cfg::kBytesA;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(S) * Cfg::kBytesStage);
+  // bars[0..S): full, [S..2S): empty, [2S..2S+2): acc_full, [2S+2..2S+4): acc_empty
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int failed_s;
+  volatile int* failed = &failed_s;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_n = (N + BN_ - 1) / BN_;
+  const int tiles_m = (M + BM - 1) / BM;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    failed_s = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&bars[s]), 1);
+      mbar_init(smem_u32(&bars[S + s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bars[2 * S + a]), 1);        // one tcgen05.commit
+      mbar_init(smem_u32(&bars[2 * S + 2 + a]), 4);    // one arrive per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(Cfg::kCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+
+  int armed = 0;
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * BM;
+        const int n0 = (tile % tiles_n) * BN_;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % S;
+          if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, failed)) { ok = false; break; }
+          const uint32_t full = smem_u32(&bars[s]);
+          mbar_expect_tx(full, Cfg::kBytesStage);
+          tma_load_2d(smem_u32(stage_a + size_t(s) * Cfg::kBytesA), &map_a, full, kb * BK, m0);
+          tma_load_2d(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), &map_b, full, kb * BK, n0);
+          armed = it + 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        // the epilogue must have drained this accumulator buffer (tile local-2)
+        if (!mbar_wait(smem_u32(&bars[2 * S + 2 + acc]), ((local >> 1) & 1) ^ 1, failed)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + uint32_t(acc * BN_);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % S;
+          if (!mbar_wait(smem_u32(&bars[s]), (it / S) & 1, failed)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t adesc = make_desc(smem_u32(stage_a + size_t(s) * Cfg::kBytesA));
+          const uint64_t bdesc = make_desc(smem_u32(stage_b + size_t(s) * Cfg::kBytesB));
+#pragma unroll
+          for (int k = 0; k < BK / kUmmaK; ++k) {
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "setp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                ::"r"(tmem_d), "l"(adesc + uint64_t(2 * k)), "l"(bdesc + uint64_t(2 * k)), "r"(Cfg::kIdesc),
+                  "r"((kb | k) != 0 ? 1u : 0u)
+                : "memory");
+          }
+          umma_commit(smem_u32(&bars[S + s]));
+        }
+        if (ok) umma_commit(smem_u32(&bars[2 * S + acc]));
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const bool vec_ok = (N % 8) == 0;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      const int m0 = (tile / tiles_n) * BM;
+      const int n0 = (tile % tiles_n) * BN_;
+      if (!mbar_wait(smem_u32(&bars[2 * S + acc]), (local >> 1) & 1, failed)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int m = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN_ / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN_ + c * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int nbase = n0 + c * 32;
+        if (m < M && nbase < N) {
+          __nv_bfloat16* dst = out + size_t(m) * N + nbase;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int n = nbase + j * 8;
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float x = __uint_as_float(r[j * 8 + i]);
+              if (bias != nullptr && n + i < N) x += __bfloat162float(bias[n + i]);
+              v[i] = act_fn(x, act);
+            }
+            if (vec_ok && n + 8 <= N) {
+              uint4 pk;
+              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+              *reinterpret_cast<uint4*>(dst + j * 8) = pk;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                if (n + i < N) dst[j * 8 + i] = __float2bfloat16_rn(v[i]);
+            }
+          }
+        }
+      }
+      // hand the accumulator buffer back to the MMA warp
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars[2 * S + 2 + acc])) : "memory");
+    }
+  }
+  if (warp == 0 && lane == 0 && *failed) {
+    const int first = armed > S ? armed - S : 0;
+    for (int it = first; it < armed; ++it) {
+      const unsigned long long t0 = now_ns();
+      while (!mbar_try(smem_u32(&bars[it % S]), (it / S) & 1) && now_ns() - t0 < kWaitLimitNs) {}
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kCols) : "memory");
+  }
+  if (threadIdx.x == 0 && failed_s && status != nullptr) atomicExch(status, 1u);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -293,17 +475,55 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
   if ((K % 8) != 0 || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) ||
       (reinterpret_cast<uintptr_t>(out) & 15))
     return cudaErrorInvalidValue;
-  CUtensorMap map_a, map_b;
-  if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, BN)) return cudaErrorInvalidValue;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
-    if (e != cudaSuccess) return e;
-    attr_set = true;
+  static const int variant = [] {
+    const char* v = std::getenv("BLUEFOG_B200_GEMM_VARIANT");   // "tile" = one tile per CTA, default persistent
+    return (v != nullptr && std::string(v) == "tile") ? 0 : 1;
+  }();
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
   }
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_bf16_nt_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, static_cast<__nv_bfloat16*>(out),
-                                                             static_cast<const __nv_bfloat16*>(bias), M, N, K, act, status);
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+  const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
+  CUtensorMap map_a, map_b;
+  if (variant == 0) {
+    if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, BN)) return cudaErrorInvalidValue;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+      if (e != cudaSuccess) return e;
+      attr_set = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    gemm_bf16_nt_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, o, bp, M, N, K, act, status);
+  } else if (N > 128) {
+    using Cfg = PersistentCfg<256>;
+    if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, 256)) return cudaErrorInvalidValue;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
+      if (e != cudaSuccess) return e;
+      attr_set = true;
+    }
+    const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+    gemm_bf16_nt_persistent_kernel<256><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
+        map_a, map_b, o, bp, M, N, K, act, status);
+  } else {
+    using Cfg = PersistentCfg<128>;
+    if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, 128)) return cudaErrorInvalidValue;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
+      if (e != cudaSuccess) return e;
+      attr_set = true;
+    }
+    const int tiles = ((M + BM - 1) / BM) * ((N + 127) / 128);
+    gemm_bf16_nt_persistent_kernel<128><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
+        map_a, map_b, o, bp, M, N, K, act, status);
+  }
   CountKernelLaunch();
   return cudaGetLastError();
 }

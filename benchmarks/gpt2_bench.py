@@ -6,6 +6,10 @@ RingGraph topology, 64 MiB buckets.
 
   bfrun -np 8 python benchmarks/gpt2_bench.py --steps 10 --warmup 3
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # repository root
 import argparse
 import json
 

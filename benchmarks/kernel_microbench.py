@@ -10,6 +10,10 @@ buffers of the same GPU, so the numbers are HBM-bound, not NVLink-bound; they sh
 the kernels come to the copy bandwidth of the device.  Inputs are larger than the 126 MB L2.
 Timing: CUDA events around `--iters` launches after `--warmup`, reported per launch.
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # repository root
 import argparse
 import json
 import os
@@ -100,9 +104,34 @@ def bench_gemm(args):
             "library_ms": ms_lib, "library_tflops": flops / ms_lib / 1e9, "status": _C.gemm_status()}
 
 
+def bench_bn(args):
+    n, c, h, w = args.bn_shape
+    x = torch.randn(n, c, h, w, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    res = torch.randn_like(x)
+    gamma = torch.ones(c, device="cuda")
+    beta = torch.zeros(c, device="cuda")
+    rm, rv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+    y, mean, rstd = _C.bn_forward(x, res, gamma, beta, rm, rv, 1e-5, 0.1, True)
+    dy = torch.randn_like(x)
+    ms_f = timed(lambda: _C.bn_forward(x, res, gamma, beta, rm, rv, 1e-5, 0.1, True), args.iters, args.warmup)
+    ms_b = timed(lambda: _C.bn_backward(dy, y, x, mean, rstd, gamma, True, True), args.iters, args.warmup)
+    bn = torch.nn.BatchNorm2d(c).cuda()
+
+    bn16 = bn.to(torch.bfloat16)
+    ms_tf = timed(lambda: torch.relu(bn16(x) + res), args.iters, args.warmup)
+    nbytes = x.numel() * 2
+    # forward: stats read x; apply reads x, residual, writes y.  backward: reduce reads dy, y, x; apply reads
+    # dy, y, x and writes dx, dresidual.
+    return {"kernel": "bn_stats+bn_apply / bn_bwd_reduce+bn_bwd_apply (ReLU + residual)", "shape": [n, c, h, w],
+            "fwd_ms": ms_f, "fwd_gbs": 4 * nbytes / ms_f / 1e6, "fwd_frac_of_measured_hbm": 4 * nbytes / ms_f / 1e6 / PEAKS["hbm_gbs"],
+            "bwd_ms": ms_b, "bwd_gbs": 8 * nbytes / ms_b / 1e6, "bwd_frac_of_measured_hbm": 8 * nbytes / ms_b / 1e6 / PEAKS["hbm_gbs"],
+            "pytorch_fwd_ms (bn, add, relu)": ms_tf}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", required=True, choices=["bucket", "combine", "gemm"])
+    ap.add_argument("--kernel", required=True, choices=["bucket", "combine", "gemm", "bn"])
+    ap.add_argument("--bn-shape", type=int, nargs=4, default=[64, 256, 56, 56])
     ap.add_argument("--numel", type=int, default=64 * 1024 * 1024)
     ap.add_argument("--dtype", default="float32")
     ap.add_argument("--exchange", default="float32", choices=["float32", "bfloat16"])
@@ -113,7 +142,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
     torch.cuda.set_device(0)
-    out = {"bucket": bench_bucket, "combine": bench_combine, "gemm": bench_gemm}[args.kernel](args)
+    out = {"bucket": bench_bucket, "combine": bench_combine, "gemm": bench_gemm, "bn": bench_bn}[args.kernel](args)
     print(json.dumps(out), flush=True)
 
 

@@ -8,6 +8,10 @@ per neighbor per tensor, and then the local optimizer applies the gradient in a 
 pass.  Compute is whatever PyTorch dispatches to (cuDNN/cuBLAS), as in the reference's
 benchmark.  This is NOT the reference's code; the reference itself cannot be built offline.
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # repository root
 import json
 
 import torch

@@ -11,6 +11,10 @@ dynamic one-peer exp2) it times, on the device with CUDA events and as the max o
 GB/s counts the bytes every rank must receive over NVLink per operation (in-degree x size);
 the roofline fraction is against 770 GB/s per direction measured for a peer copy on this pool.
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # repository root
 import argparse
 import json
 import os

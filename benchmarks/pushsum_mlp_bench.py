@@ -8,6 +8,10 @@ rank ever waits for another one.
 
   bfrun -np 8 python benchmarks/pushsum_mlp_bench.py --seconds 10
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # repository root
 import argparse
 import json
 import time

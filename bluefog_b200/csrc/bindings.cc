@@ -10,6 +10,7 @@
 #include "common/logging.h"
 #include "common/runtime.h"
 #include "common/windows.h"
+#include "cuda/bn_kernels.h"
 #include "cuda/bucket.h"
 #include "cuda/gemm_tcgen05.h"
 #include "cuda/gpu_channel.h"
@@ -111,6 +112,9 @@ at::Tensor& GemmStatusWord(const at::Tensor& like) {
 
 struct PyBucketArgs : BucketStepArgs {
   c10::optional<at::Tensor> t_master, t_grad, t_state1, t_state2, t_state3, t_shadow;
+  // int64 CUDA tensors: per-parameter gradient addresses, first element and length of each parameter
+  c10::optional<at::Tensor> t_grad_ptrs, t_seg_start, t_seg_numel;
+  bool grad_table_bf16 = false;
 };
 
 }  // namespace
@@ -273,6 +277,69 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(e == cudaSuccess, "scale kernel launch failed: ", cudaGetErrorString(e));
   });
 
+  // ---- fused BatchNorm (+ReLU, +residual), NHWC bf16 -----------------------------------------
+  m.def("bn_supported", [](at::Tensor x) {
+    return x.is_cuda() && x.dim() == 4 && x.scalar_type() == at::kBFloat16 &&
+           x.is_contiguous(at::MemoryFormat::ChannelsLast) &&
+           BnShapeSupported(x.numel() / std::max<int64_t>(x.size(1), 1), static_cast<int>(x.size(1)));
+  });
+  m.def("bn_forward", [](at::Tensor x, c10::optional<at::Tensor> residual, at::Tensor gamma, at::Tensor beta,
+                         c10::optional<at::Tensor> running_mean, c10::optional<at::Tensor> running_var, double eps,
+                         double momentum, bool relu) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.scalar_type() == at::kBFloat16 &&
+                x.is_contiguous(at::MemoryFormat::ChannelsLast), "bn_forward expects a bf16 NHWC (channels_last) CUDA tensor");
+    const int C = static_cast<int>(x.size(1));
+    const long long R = x.numel() / C;
+    TORCH_CHECK(BnShapeSupported(R, C), "bn_forward: unsupported channel count ", C);
+    TORCH_CHECK(gamma.numel() == C && beta.numel() == C && gamma.scalar_type() == beta.scalar_type(), "bad affine parameters");
+    const bool pbf16 = gamma.scalar_type() == at::kBFloat16;
+    TORCH_CHECK(pbf16 || gamma.scalar_type() == at::kFloat, "affine parameters must be bf16 or fp32");
+    c10::cuda::CUDAGuard g(x.get_device());
+    at::Tensor y = at::empty_like(x);
+    auto fopts = x.options().dtype(at::kFloat);
+    at::Tensor sums = at::zeros({2 * C}, fopts);
+    at::Tensor save_mean = at::empty({C}, fopts), save_rstd = at::empty({C}, fopts);
+    const void* res = nullptr;
+    if (residual.has_value() && residual->defined()) {
+      TORCH_CHECK(residual->sizes() == x.sizes() && residual->scalar_type() == at::kBFloat16 &&
+                  residual->is_contiguous(at::MemoryFormat::ChannelsLast), "residual must match x (bf16, channels_last)");
+      res = residual->data_ptr();
+    }
+    float* rm = nullptr;
+    float* rv = nullptr;
+    if (running_mean.has_value() && running_mean->defined()) {
+      TORCH_CHECK(running_mean->scalar_type() == at::kFloat && running_var->scalar_type() == at::kFloat, "running statistics must be fp32");
+      rm = running_mean->data_ptr<float>();
+      rv = running_var->data_ptr<float>();
+    }
+    cudaError_t e = LaunchBnForward(x.data_ptr(), res, y.data_ptr(), sums.data_ptr<float>(), gamma.data_ptr(), beta.data_ptr(),
+                                    rm, rv, save_mean.data_ptr<float>(), save_rstd.data_ptr<float>(), R, C,
+                                    static_cast<float>(eps), static_cast<float>(momentum), relu ? 1 : 0, pbf16 ? 1 : 0,
+                                    CurrentStream(x.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "bn_forward launch failed: ", cudaGetErrorString(e));
+    return std::make_tuple(y, save_mean, save_rstd);
+  });
+  m.def("bn_backward", [](at::Tensor dy, at::Tensor y, at::Tensor x, at::Tensor save_mean, at::Tensor save_rstd,
+                          at::Tensor gamma, bool relu, bool want_dres) {
+    TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous(at::MemoryFormat::ChannelsLast) &&
+                dy.sizes() == x.sizes(), "bn_backward expects a bf16 NHWC gradient of the shape of x");
+    const int C = static_cast<int>(x.size(1));
+    const long long R = x.numel() / C;
+    const bool pbf16 = gamma.scalar_type() == at::kBFloat16;
+    c10::cuda::CUDAGuard g(x.get_device());
+    at::Tensor dx = at::empty_like(x);
+    at::Tensor dres = want_dres ? at::empty_like(x) : at::Tensor();
+    at::Tensor sums = at::zeros({2 * C}, x.options().dtype(at::kFloat));
+    at::Tensor dgamma = at::empty_like(gamma), dbeta = at::empty_like(gamma);
+    cudaError_t e = LaunchBnBackward(dy.data_ptr(), y.data_ptr(), x.data_ptr(), dx.data_ptr(),
+                                     want_dres ? dres.data_ptr() : nullptr, sums.data_ptr<float>(),
+                                     save_mean.data_ptr<float>(), save_rstd.data_ptr<float>(), gamma.data_ptr(),
+                                     dgamma.data_ptr(), dbeta.data_ptr(), R, C, relu ? 1 : 0, pbf16 ? 1 : 0,
+                                     CurrentStream(x.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "bn_backward launch failed: ", cudaGetErrorString(e));
+    return std::make_tuple(dx, dres, dgamma, dbeta);
+  });
+
   // ---- tcgen05 GEMM -------------------------------------------------------------------------
   m.def("gemm_supported", [] { return GemmSupported(); });
   m.def("gemm_bf16_nt", [](at::Tensor a, at::Tensor w, c10::optional<at::Tensor> bias, int act) {
@@ -340,7 +407,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("state1", &PyBucketArgs::t_state1)
       .def_readwrite("state2", &PyBucketArgs::t_state2)
       .def_readwrite("state3", &PyBucketArgs::t_state3)
-      .def_readwrite("shadow", &PyBucketArgs::t_shadow);
+      .def_readwrite("shadow", &PyBucketArgs::t_shadow)
+      .def_readwrite("grad_ptrs", &PyBucketArgs::t_grad_ptrs)
+      .def_readwrite("seg_start", &PyBucketArgs::t_seg_start)
+      .def_readwrite("seg_numel", &PyBucketArgs::t_seg_numel)
+      .def_readwrite("grad_table_bf16", &PyBucketArgs::grad_table_bf16);
 
   py::class_<Bucket>(m, "Bucket")
       .def_static("create", [](int64_t numel, const std::string& pub_dtype) {
@@ -387,6 +458,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           a.grad_elem = a.t_grad->scalar_type() == at::kBFloat16 ? kBF16 : kF32;
         }
         if (a.t_shadow.has_value() && a.t_shadow->defined()) TORCH_CHECK(a.t_shadow->scalar_type() == at::kBFloat16, "shadow must be bfloat16");
+        a.BucketStepArgs::grad_ptrs = nullptr;
+        a.BucketStepArgs::n_seg = 0;
+        if (a.t_grad_ptrs.has_value() && a.t_grad_ptrs->defined()) {
+          TORCH_CHECK(!(a.t_grad.has_value() && a.t_grad->defined()), "give either a flat gradient or a gradient table");
+          TORCH_CHECK(a.t_seg_start.has_value() && a.t_seg_numel.has_value(), "gradient table needs seg_start and seg_numel");
+          for (const at::Tensor* t : {&*a.t_grad_ptrs, &*a.t_seg_start, &*a.t_seg_numel})
+            TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kLong && t->is_contiguous() &&
+                        t->numel() == a.t_grad_ptrs->numel(), "gradient table tensors must be int64 CUDA tensors of equal length");
+          a.BucketStepArgs::grad_ptrs = reinterpret_cast<const void* const*>(a.t_grad_ptrs->data_ptr());
+          a.BucketStepArgs::seg_start = reinterpret_cast<const unsigned long long*>(a.t_seg_start->data_ptr());
+          a.BucketStepArgs::seg_numel = reinterpret_cast<const unsigned long long*>(a.t_seg_numel->data_ptr());
+          a.BucketStepArgs::n_seg = static_cast<int>(a.t_grad_ptrs->numel());
+          a.grad_elem = a.grad_table_bf16 ? kBF16 : kF32;
+        }
         int device = b.channel()->arena()->device;
         c10::cuda::CUDAGuard g(device);
         cudaStream_t st = stream == 0 ? CurrentStream(device) : reinterpret_cast<cudaStream_t>(stream);

@@ -1014,6 +1014,54 @@ Status Runtime::ExecuteGpu(std::vector<Entry>& entries, const Response& resp) {
       end_act();
       return Status::InvalidArgument("unsupported tensor type for a GPU reduction");
     }
+    static const uint64_t two_shot_bytes = static_cast<uint64_t>(EnvDouble("BLUEFOG_B200_TWO_SHOT_BYTES", 1024.0 * 1024.0));
+    if (type == OpType::ALLREDUCE && entries.size() == 1 && size_ > 2 &&
+        static_cast<int>(first.src_ranks.size()) == size_ - 1 && segs[0].nbytes >= two_shot_bytes) {
+      // Two-shot allreduce for large tensors: every rank reduces one slice out of all peers'
+      // published tensors (reduce-scatter), publishes its reduced slice, and then gathers the
+      // other slices.  Each rank moves 2*(N-1)/N of the tensor over NVLink instead of (N-1) times it.
+      const bool integral = elem == kI32 || elem == kI64;
+      const uint64_t esize = static_cast<uint64_t>(ElemSize(elem));
+      const uint64_t numel = segs[0].numel;
+      uint64_t per = (numel + size_ - 1) / size_;
+      per = (per + 63) & ~uint64_t(63);
+      auto start_of = [&](int r) { return std::min<uint64_t>(numel, static_cast<uint64_t>(r) * per); };
+      auto len_of = [&](int r) { return std::min<uint64_t>(numel, start_of(r) + per) - start_of(r); };
+      at::Tensor temp;
+      {
+        c10::cuda::CUDAStreamGuard g(c10::cuda::getStreamFromExternal(stream, device_));
+        temp = at::empty({static_cast<int64_t>(per)}, first.input->options());
+        at::Tensor& out = *first.output;
+        if (out.sizes() != first.input->sizes()) out.resize_(first.input->sizes());
+      }
+      s = gpu_channel_->Publish(segs, nullptr, size_ - 1, stream, &round);
+      if (s.ok()) {
+        SegSpec mine;
+        mine.out = temp.data_ptr();
+        mine.numel = len_of(rank_);
+        mine.elem_offset = start_of(rank_);
+        std::vector<double> ones(first.src_ranks.size(), 1.0);
+        s = gpu_channel_->PullCombine(round, {mine}, elem, 1.0, first.src_ranks, ones, false,
+                                      integral ? 1.0 : first.post_scale, stream);
+      }
+      Round round2;
+      if (s.ok()) {
+        SegSpec pub;
+        pub.in = temp.data_ptr();
+        pub.nbytes = len_of(rank_) * esize;
+        pub.numel = len_of(rank_);
+        s = gpu_channel_->Publish({pub}, nullptr, size_ - 1, stream, &round2);
+      }
+      if (s.ok()) {
+        std::vector<Channel::CopySpec> copies;
+        char* base = static_cast<char*>(first.output->data_ptr());
+        for (int r = 0; r < size_; ++r)
+          if (len_of(r) > 0) copies.push_back({r, 0, len_of(r) * esize, base + start_of(r) * esize});
+        s = gpu_channel_->PullGather(round2, first.src_ranks, copies, stream);
+      }
+      end_act();
+      return s;
+    }
     std::vector<double> dstw;
     if (first.use_dst_weight) {
       dstw.assign(size_, 1.0);

@@ -43,6 +43,12 @@ Status Bucket::Step(const BucketStepArgs& a, cudaStream_t stream) {
   p.numel = numel_;
   p.master = static_cast<float*>(a.master);
   p.grad = a.grad;
+  p.grad_ptrs = a.grad_ptrs;
+  p.seg_start = a.seg_start;
+  p.seg_numel = a.seg_numel;
+  p.n_seg = a.n_seg;
+  if (a.grad_ptrs != nullptr && (a.n_seg <= 0 || a.seg_start == nullptr || a.seg_numel == nullptr))
+    return Status::InvalidArgument("bucket step: incomplete gradient table");
   p.state1 = static_cast<float*>(a.state1);
   p.state2 = static_cast<float*>(a.state2);
   p.state3 = static_cast<float*>(a.state3);

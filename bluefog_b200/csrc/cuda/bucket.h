@@ -28,6 +28,10 @@ struct BucketStepArgs {
   int n_readers = 0;            // ranks that read the version this step consumes (my dst list)
   void* master = nullptr;
   const void* grad = nullptr;
+  const void* const* grad_ptrs = nullptr;              // device array, see BucketParams
+  const unsigned long long* seg_start = nullptr;       // device arrays of n_seg entries
+  const unsigned long long* seg_numel = nullptr;
+  int n_seg = 0;
   void* state1 = nullptr;
   void* state2 = nullptr;
   void* state3 = nullptr;

@@ -474,7 +474,9 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
     const unsigned long long n4 = p.numel / 4;
     const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
     const int mode = p.mode;
-    const bool has_grad = p.grad != nullptr && p.opt != kOptNone;
+    const bool any_grad = p.grad != nullptr || p.grad_ptrs != nullptr;
+    const bool has_grad = any_grad && p.opt != kOptNone;
+    const bool wants_grad = any_grad && (has_grad || mode == kModeGradReduce || mode == kModePublishOnly);
     // Main loop: 4 elements per thread per step; published/grad buffers are padded to 16 bytes.
     for (unsigned long long q = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; q * 4 < p.numel; q += stride) {
       const unsigned long long i0 = q * 4;
@@ -490,11 +492,25 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
         for (int i = 0; i < 4; ++i) x[i] = i < cnt ? p.master[i0 + i] : 0.f;
       }
       // gradient
-      if (has_grad || mode == kModeGradReduce) {
-        const GradT* gp = static_cast<const GradT*>(p.grad) + i0;
-        for (int i = 0; i < 4; ++i) g[i] = i < cnt ? GE::load(gp + i) * p.grad_scale : 0.f;
-      } else {
-        for (int i = 0; i < 4; ++i) g[i] = 0.f;
+      for (int i = 0; i < 4; ++i) g[i] = 0.f;
+      if (wants_grad) {
+        if (p.grad != nullptr) {
+          const GradT* gp = static_cast<const GradT*>(p.grad) + i0;
+          for (int i = 0; i < 4; ++i) g[i] = i < cnt ? GE::load(gp + i) * p.grad_scale : 0.f;
+        } else {
+          // per-parameter gradients: parameters start at multiples of 4 elements, so the four
+          // elements of this step belong to one parameter (or to the padding behind it)
+          int lo = 0, hi = p.n_seg - 1;
+          while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (p.seg_start[mid] <= i0) lo = mid; else hi = mid - 1;
+          }
+          const GradT* gp = static_cast<const GradT*>(p.grad_ptrs[lo]);
+          const unsigned long long local = i0 - p.seg_start[lo];
+          const unsigned long long n = p.seg_numel[lo];
+          if (gp != nullptr)
+            for (int i = 0; i < 4; ++i) g[i] = (local + i < n) ? GE::load(gp + local + i) * p.grad_scale : 0.f;
+        }
       }
       // remote terms
       if (mode == kModeAWC || mode == kModeCombineOnly) {
@@ -534,7 +550,7 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
       } else if (mode == kModeGradReduce) {
         for (int i = 0; i < 4; ++i) y[i] = i < cnt ? opt_update(o, x[i], acc[i] * p.post_scale, p.state1, p.state2, p.state3, i0 + i) : 0.f;
       } else {  // publish only: payload is the master (or the gradient when grad != null and opt == none)
-        for (int i = 0; i < 4; ++i) y[i] = (p.grad != nullptr) ? GE::load(static_cast<const GradT*>(p.grad) + i0 + (i < cnt ? i : 0)) * p.grad_scale : x[i];
+        for (int i = 0; i < 4; ++i) y[i] = any_grad ? g[i] : x[i];
       }
       const bool writes_master = (mode == kModeAWC || mode == kModeCombineOnly || mode == kModeGradReduce);
       if (writes_master) {

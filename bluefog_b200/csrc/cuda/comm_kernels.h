@@ -148,7 +148,13 @@ struct BucketParams {
   float src_w[kMaxSrc];
   unsigned long long numel;
   float* master;                 // P (private fp32)
-  const void* grad;              // flat gradient bucket
+  const void* grad;              // flat gradient bucket, or null when grad_ptrs is used
+  // Gradients left where autograd put them: grad_ptrs[s] is the gradient of the s-th parameter of
+  // the bucket (null = no gradient), which occupies elements [seg_start[s], seg_start[s] + seg_numel[s]).
+  const void* const* grad_ptrs;
+  const unsigned long long* seg_start;
+  const unsigned long long* seg_numel;
+  int n_seg;
   float* state1;                 // momentum / exp_avg
   float* state2;                 // exp_avg_sq
   float* state3;                 // max_exp_avg_sq (amsgrad)

@@ -146,7 +146,7 @@ Status Channel::PullCombine(const Round& round, const std::vector<SegSpec>& segs
     for (size_t i = begin; i < end; ++i) {
       const size_t k = i - begin;
       p.out[k] = segs[i].out;
-      p.off[k] = round.offsets[i];
+      p.off[k] = round.offsets[i] + segs[i].elem_offset * static_cast<uint64_t>(esize);
       p.numel[k] = segs[i].numel;
       p.chunk_start[k] = chunks;
       chunks += (segs[i].numel + per_vec - 1) / per_vec;

@@ -16,6 +16,7 @@ struct SegSpec {
   void* out = nullptr;        // pull: destination
   uint64_t nbytes = 0;        // payload bytes of this tensor
   uint64_t numel = 0;
+  uint64_t elem_offset = 0;   // pull: first element of the published tensor that is combined
 };
 
 struct Round {

@@ -14,6 +14,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from bluefog_b200.ops.fused_bn import bn_act
+
 
 class MixedBatchNorm2d(nn.BatchNorm2d):
     """BatchNorm whose affine parameters may be bf16 while the running statistics stay fp32."""
@@ -52,6 +54,16 @@ class Conv1x1(nn.Conv2d):
         return super().forward(x)
 
 
+class Downsample(nn.Sequential):
+    """1x1 convolution + BatchNorm on the shortcut (children named "0" and "1" as in torchvision)."""
+
+    def __init__(self, cin, cout, stride, use_b200_gemm):
+        super().__init__(Conv1x1(cin, cout, stride, use_b200_gemm=use_b200_gemm), MixedBatchNorm2d(cout))
+
+    def forward(self, x):
+        return bn_act(self[0](x), self[1], relu=False)
+
+
 def conv3x3(cin, cout, stride=1):
     return nn.Conv2d(cin, cout, kernel_size=3, stride=stride, padding=1, bias=False)
 
@@ -70,9 +82,8 @@ class BasicBlock(nn.Module):
 
     def forward(self, x):
         identity = x if self.downsample is None else self.downsample(x)
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.bn2(self.conv2(out))
-        return self.relu(out + identity)
+        out = bn_act(self.conv1(x), self.bn1, relu=True)
+        return bn_act(self.conv2(out), self.bn2, relu=True, residual=identity)
 
 
 class Bottleneck(nn.Module):
@@ -91,10 +102,9 @@ class Bottleneck(nn.Module):
 
     def forward(self, x):
         identity = x if self.downsample is None else self.downsample(x)
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.relu(self.bn2(self.conv2(out)))
-        out = self.bn3(self.conv3(out))
-        return self.relu(out + identity)
+        out = bn_act(self.conv1(x), self.bn1, relu=True)
+        out = bn_act(self.conv2(out), self.bn2, relu=True)
+        return bn_act(self.conv3(out), self.bn3, relu=True, residual=identity)
 
 
 class ResNet(nn.Module):
@@ -129,9 +139,7 @@ class ResNet(nn.Module):
     def _make_layer(self, block, planes, blocks, stride=1):
         downsample = None
         if stride != 1 or self.inplanes != planes * block.expansion:
-            downsample = nn.Sequential(
-                Conv1x1(self.inplanes, planes * block.expansion, stride, use_b200_gemm=self.use_b200_gemm),
-                MixedBatchNorm2d(planes * block.expansion))
+            downsample = Downsample(self.inplanes, planes * block.expansion, stride, self.use_b200_gemm)
         layers = [block(self.inplanes, planes, stride, downsample, use_b200_gemm=self.use_b200_gemm)]
         self.inplanes = planes * block.expansion
         for _ in range(1, blocks):
@@ -143,7 +151,7 @@ class ResNet(nn.Module):
             x = x.contiguous(memory_format=torch.channels_last)
         if x.dtype != self.conv1.weight.dtype:
             x = x.to(self.conv1.weight.dtype)
-        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        x = self.maxpool(bn_act(self.conv1(x), self.bn1, relu=True))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         x = torch.flatten(self.avgpool(x), 1)
         if self.use_b200_gemm and x.is_cuda and x.dtype == torch.bfloat16:

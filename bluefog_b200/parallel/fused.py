@@ -2,8 +2,8 @@
 
 Parameters are re-homed into flat buckets (a bucket is what the reference calls a fusion
 group, bluefog/common/operations.cc:990-1008, but permanent: nothing is packed per step).
-Per bucket there are: an fp32 master buffer, a flat gradient buffer that ``p.grad`` aliases,
-flat optimizer-state buffers that ``optimizer.state[p][...]`` aliases, optionally a bf16
+Per bucket there are: an fp32 master buffer, a table of the parameters' gradient addresses (the
+gradients stay where autograd allocates them), flat optimizer-state buffers that ``optimizer.state[p][...]`` aliases, optionally a bf16
 shadow that ``p.data`` aliases (bf16 compute with fp32 master weights), and a native
 ``Bucket`` whose peer-mapped, double-buffered published copy the neighbors read.
 
@@ -64,7 +64,12 @@ class _BucketState:
         self.offsets = offsets
         self.numel = n
         self.master = torch.zeros(n, dtype=torch.float32, device=device)
-        self.grad = torch.zeros(n, dtype=compute_dtype, device=device)
+        # gradients stay where autograd puts them; the kernel reads them through a pointer table
+        self.seg_start = torch.tensor(offsets, dtype=torch.int64, device=device)
+        self.seg_numel = torch.tensor([p.numel() for p in params], dtype=torch.int64, device=device)
+        self.grad_ptrs = torch.zeros(len(params), dtype=torch.int64, device=device)
+        self.grad_ptr_key = None
+        self.grad_bf16 = compute_dtype == torch.bfloat16
         self.shadow = torch.zeros(n, dtype=torch.bfloat16, device=device) if compute_dtype == torch.bfloat16 else None
         self.state1 = self.state2 = self.state3 = None
         if opt_kind == OPT_SGD and group.get("momentum", 0) != 0:
@@ -144,7 +149,7 @@ class _FusedMixin:
                 p.data = bk.view(bk.shadow, i)
             else:
                 p.data = bk.view(bk.master, i)
-            p.grad = bk.view(bk.grad, i)
+            p.grad = None
             st = self.state[p]
             if self._opt_kind == OPT_SGD:
                 if bk.state1 is not None:
@@ -178,7 +183,7 @@ class _FusedMixin:
     def _fill_opt(self, a, bk):
         g = self.param_groups[bk.group_index]
         a.opt = self._opt_kind
-        a.grad = bk.grad
+        self._fill_grads(a, bk)
         a.lr = float(g["lr"])
         a.weight_decay = float(g.get("weight_decay", 0.0))
         a.maximize = bool(g.get("maximize", False))
@@ -197,6 +202,26 @@ class _FusedMixin:
             a.adamw = self._adamw
             a.amsgrad = bool(g.get("amsgrad", False))
             a.state1, a.state2, a.state3 = bk.state1, bk.state2, bk.state3
+
+    def _fill_grads(self, a, bk):
+        """Points the kernel at the parameters' current ``.grad`` tensors (no flattening copy)."""
+        key = []
+        want = torch.bfloat16 if bk.grad_bf16 else torch.float32
+        for p in bk.params:
+            g = p.grad
+            if g is None:
+                key.append(0)
+                continue
+            if g.dtype != want or not g.is_contiguous():
+                g = g.to(want).contiguous()
+                p.grad = g
+            key.append(g.data_ptr())
+        key = tuple(key)
+        if key != bk.grad_ptr_key:     # under a CUDA graph the addresses never change after the first step
+            bk.grad_ptrs.copy_(torch.tensor(key, dtype=torch.int64))
+            bk.grad_ptr_key = key
+        a.grad_ptrs, a.seg_start, a.seg_numel = bk.grad_ptrs, bk.seg_start, bk.seg_numel
+        a.grad_table_bf16 = bk.grad_bf16
 
     def _after_update(self, bk):
         bk.steps += 1
@@ -253,10 +278,16 @@ class _FusedMixin:
     def turn_off_timeline(self):
         self._use_timeline = False
 
-    def zero_grad(self, set_to_none: bool = False):
-        """Gradients alias the flat buffers, so they are zeroed in place (never set to None)."""
+    def zero_grad(self, set_to_none: bool = True):
         for bk in self._buckets:
-            bk.grad.zero_()
+            for p in bk.params:
+                if p.grad is None:
+                    continue
+                if set_to_none:
+                    p.grad = None
+                else:
+                    p.grad.detach_()
+                    p.grad.zero_()
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -288,7 +319,7 @@ class _FusedMixin:
                 if n > 1:
                     pub = self._new_args(bk, MODE_PUBLISH_ONLY)
                     pub.master = None
-                    pub.grad = bk.grad
+                    self._fill_grads(pub, bk)
                     bk.native.step(pub)
                 a = self._new_args(bk, MODE_GRAD_REDUCE)
                 self._fill_opt(a, bk)

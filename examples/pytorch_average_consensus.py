@@ -6,6 +6,10 @@ examples/pytorch_average_consensus.py).
   bfrun -np 4 python examples/pytorch_average_consensus.py --enable-dynamic-topology
   bfrun -np 4 python examples/pytorch_average_consensus.py --asynchronous-mode
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # repository root
 import argparse
 
 import torch

@@ -5,6 +5,10 @@ mean +- 1.96 sigma per rank and summed over ranks.
   bfrun -np 8 python examples/pytorch_benchmark.py --model resnet50 --batch-size 64
   bfrun -np 4 python examples/pytorch_benchmark.py --model lenet --dist-optimizer win_put --no-cuda
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # repository root
 import argparse
 import timeit
 

@@ -4,6 +4,10 @@ from --data-dir when it exists there; otherwise a synthetic set of the same shap
 
   bfrun -np 4 python examples/pytorch_mnist.py --epochs 1 --no-cuda
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # repository root
 import argparse
 import os
 

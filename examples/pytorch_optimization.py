@@ -4,6 +4,10 @@ gradient tracking and push-DIGing, all written with the communication primitives
 
   bfrun -np 4 python examples/pytorch_optimization.py --method exact_diffusion
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # repository root
 import argparse
 
 import torch

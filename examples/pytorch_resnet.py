@@ -4,6 +4,10 @@ synthetic ImageNet-shaped set, which is what an offline machine can do.
 
   bfrun -np 8 python examples/pytorch_resnet.py --model resnet50 --epochs 2 --bf16
 """
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # repository root
 import argparse
 import math
 import os

@@ -1,0 +1,80 @@
+"""Fused BatchNorm+ReLU(+residual) kernels against PyTorch in fp32."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(N, C, H, W, relu, with_res, param_dtype):
+    from bluefog_b200.ops.fused_bn import bn_act
+    torch.manual_seed(C + H)
+    dev = torch.device("cuda", 0)
+    x = (torch.randn(N, C, H, W, device=dev) * 1.5 + 0.7).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    res = torch.randn(N, C, H, W, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last) if with_res else None
+    bn = torch.nn.BatchNorm2d(C).to(dev)
+    with torch.no_grad():
+        bn.weight.copy_(torch.rand(C, device=dev) + 0.5)
+        bn.bias.copy_(torch.randn(C, device=dev) * 0.2)
+    ref_bn = torch.nn.BatchNorm2d(C).to(dev)
+    ref_bn.load_state_dict(bn.state_dict())
+    if param_dtype == torch.bfloat16:
+        bn.weight.data = bn.weight.data.to(torch.bfloat16)
+        bn.bias.data = bn.bias.data.to(torch.bfloat16)
+        with torch.no_grad():
+            ref_bn.weight.copy_(bn.weight.float())
+            ref_bn.bias.copy_(bn.bias.float())
+    x1 = x.clone().requires_grad_(True)
+    r1 = res.clone().requires_grad_(True) if with_res else None
+    y = bn_act(x1, bn, relu=relu, residual=r1)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    x2 = x.float().requires_grad_(True)
+    r2 = res.float().requires_grad_(True) if with_res else None
+    z = ref_bn(x2)
+    if with_res:
+        z = z + r2
+    y2 = F.relu(z) if relu else z
+    y2.backward(gy.float())
+    torch.cuda.synchronize()
+
+    def close(a, b, tol, outliers=0.0):
+        """max-abs check; ``outliers`` = fraction of elements allowed to miss it.  An activation
+        that lands within rounding distance of zero may get a different ReLU mask in bf16 than in
+        the fp32 reference, which changes its gradient by the whole upstream value."""
+        err = (a.float() - b).abs()
+        bound = tol * max(1.0, b.abs().max().item())
+        bad = (err > bound).float().mean().item()
+        assert bad <= outliers, (err.max().item(), bound, bad)
+
+    close(y, y2, 2e-2)
+    # the ReLU mask of the kernel comes from its own bf16 output; compare gradients where both agree
+    close(x1.grad, x2.grad, 4e-2, outliers=1e-4 if relu else 0.0)
+    if with_res:
+        close(r1.grad, r2.grad, 2e-2, outliers=1e-4 if relu else 0.0)
+    close(bn.weight.grad, ref_bn.weight.grad, 3e-2)
+    close(bn.bias.grad, ref_bn.bias.grad, 3e-2)
+    close(bn.running_mean, ref_bn.running_mean, 1e-2)
+    close(bn.running_var, ref_bn.running_var, 1e-2)
+    assert int(bn.num_batches_tracked) == 1
+
+
+@pytest.mark.parametrize("N,C,H,W", [(4, 64, 56, 56), (8, 256, 14, 14), (2, 2048, 7, 7), (3, 128, 9, 5), (64, 64, 112, 112)])
+@pytest.mark.parametrize("relu,with_res", [(True, False), (True, True), (False, False)])
+def test_fused_bn_matches_pytorch(N, C, H, W, relu, with_res):
+    _case(N, C, H, W, relu, with_res, torch.float32)
+
+
+def test_fused_bn_with_bf16_parameters():
+    _case(8, 512, 7, 7, True, True, torch.bfloat16)
+
+
+def test_eval_mode_and_unsupported_inputs_fall_back():
+    from bluefog_b200.ops.fused_bn import bn_act
+    bn = torch.nn.BatchNorm2d(24).cuda().eval()
+    x = torch.randn(2, 24, 5, 5, device="cuda")
+    assert torch.allclose(bn_act(x, bn, relu=True), F.relu(bn(x)))
+    bn.train()
+    x16 = torch.randn(2, 24, 5, 5, device="cuda").to(torch.bfloat16)   # NCHW, C/8 does not divide 256
+    out = bn_act(x16, bn.to(torch.bfloat16), relu=False)
+    assert out.shape == x16.shape

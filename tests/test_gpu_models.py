@@ -44,7 +44,7 @@ def test_bf16_compute_keeps_fp32_master_and_checkpoint_names(bf, tmp_path):
     model = resnet.resnet18(num_classes=10).to(dev).to(memory_format=torch.channels_last)
     opt = bf.DistributedAdaptWithCombineOptimizer(torch.optim.AdamW(model.parameters(), lr=1e-3), model,
                                                   compute_dtype=torch.bfloat16)
-    assert model.conv1.weight.dtype == torch.bfloat16 and model.conv1.weight.grad.dtype == torch.bfloat16
+    assert model.conv1.weight.dtype == torch.bfloat16
     x = torch.randn(8, 3, 32, 32, device=dev)
     y = torch.randint(0, 10, (8,), device=dev)
     losses = []

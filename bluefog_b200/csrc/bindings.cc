@@ -14,6 +14,7 @@
 #include "cuda/bucket.h"
 #include "cuda/gemm_tcgen05.h"
 #include "cuda/gpu_channel.h"
+#include "cuda/pool_kernels.h"
 #include "cuda/symm_mem.h"
 
 namespace py = pybind11;
@@ -338,6 +339,32 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                      CurrentStream(x.get_device()));
     TORCH_CHECK(e == cudaSuccess, "bn_backward launch failed: ", cudaGetErrorString(e));
     return std::make_tuple(dx, dres, dgamma, dbeta);
+  });
+
+  // ---- 3x3/2 max pooling, NHWC bf16 ---------------------------------------------------------
+  m.def("maxpool3x3s2_forward", [](at::Tensor x) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.scalar_type() == at::kBFloat16 &&
+                x.is_contiguous(at::MemoryFormat::ChannelsLast) && x.size(1) % 8 == 0,
+                "maxpool3x3s2_forward expects a bf16 NHWC CUDA tensor with C % 8 == 0");
+    const int N = x.size(0), C = x.size(1), H = x.size(2), W = x.size(3);
+    const int Ho = (H - 1) / 2 + 1, Wo = (W - 1) / 2 + 1;
+    c10::cuda::CUDAGuard g(x.get_device());
+    at::Tensor y = at::empty({N, C, Ho, Wo}, x.options().memory_format(at::MemoryFormat::ChannelsLast));
+    at::Tensor idx = at::empty({N, C, Ho, Wo}, x.options().dtype(at::kByte).memory_format(at::MemoryFormat::ChannelsLast));
+    cudaError_t e = LaunchMaxPool3x3s2Forward(x.data_ptr(), y.data_ptr(), idx.data_ptr(), N, H, W, C, CurrentStream(x.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "maxpool forward launch failed: ", cudaGetErrorString(e));
+    return std::make_tuple(y, idx);
+  });
+  m.def("maxpool3x3s2_backward", [](at::Tensor dy, at::Tensor idx, int64_t H, int64_t W) {
+    TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous(at::MemoryFormat::ChannelsLast),
+                "maxpool3x3s2_backward expects a bf16 NHWC gradient");
+    const int N = dy.size(0), C = dy.size(1);
+    c10::cuda::CUDAGuard g(dy.get_device());
+    at::Tensor dx = at::empty({N, C, H, W}, dy.options().memory_format(at::MemoryFormat::ChannelsLast));
+    cudaError_t e = LaunchMaxPool3x3s2Backward(dy.data_ptr(), idx.data_ptr(), dx.data_ptr(), N, static_cast<int>(H),
+                                               static_cast<int>(W), C, CurrentStream(dy.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "maxpool backward launch failed: ", cudaGetErrorString(e));
+    return dx;
   });
 
   // ---- tcgen05 GEMM -------------------------------------------------------------------------

@@ -43,41 +43,64 @@ __device__ __forceinline__ void store_param(void* p, int i, int is_bf16, float v
   else static_cast<float*>(p)[i] = v;
 }
 
-// Block-level accumulation of 2 x 8 per-thread partial sums into sums[0..C) and sums[C..2C).
-__device__ __forceinline__ void flush_partials(const float* s1, const float* s2, int g, int C, float* sums) {
-  __shared__ float sh[2 * kMaxC];
-  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) sh[c] = 0.f;
+// Work decomposition of the two reduction kernels.  A block covers `cgb` groups of 8 channels
+// (at most 32 groups = 512 contiguous bytes per row) times `rlb` = 256 / cgb rows per step;
+// blockIdx.x selects the channel chunk, blockIdx.y the chunk of rows.  Every block adds its
+// partial sums into the global accumulators once, so the number of global atomics is
+// (#blocks x 2 x 8 x cgb) - small even for 2048 channels.
+struct ReduceGeom {
+  int cgb;      // channel groups per block
+  int rlb;      // row lanes per block
+};
+__device__ __forceinline__ ReduceGeom reduce_geom(int C) {
+  const int CG = C >> 3;
+  ReduceGeom g;
+  g.cgb = CG < 32 ? CG : 32;
+  g.rlb = kThreads / g.cgb;
+  return g;
+}
+
+// Adds the per-thread partials of one block into sums[c] and sums[C + c] (c = channels of this block).
+__device__ __forceinline__ void flush_partials(const float* s1, const float* s2, int lg, int cgb, int c0, int C,
+                                               float* sums) {
+  __shared__ float sh[2 * 256];           // 32 groups x 8 channels, two statistics
+  const int nch = cgb * 8;
+  for (int c = threadIdx.x; c < 2 * nch; c += blockDim.x) sh[c] = 0.f;
   __syncthreads();
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    atomicAdd(&sh[g * 8 + i], s1[i]);
-    atomicAdd(&sh[C + g * 8 + i], s2[i]);
+    atomicAdd(&sh[lg * 8 + i], s1[i]);
+    atomicAdd(&sh[nch + lg * 8 + i], s2[i]);
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) atomicAdd(&sums[c], sh[c]);
+  for (int c = threadIdx.x; c < nch; c += blockDim.x) {
+    atomicAdd(&sums[c0 + c], sh[c]);
+    atomicAdd(&sums[C + c0 + c], sh[nch + c]);
+  }
 }
 
 // sums[c] = sum_r (x[r,c] - x[0,c]);  sums[C+c] = sum_r (x[r,c] - x[0,c])^2
 __global__ void __launch_bounds__(kThreads) bn_stats_kernel(const __nv_bfloat16* __restrict__ x, long long R, int C,
                                                             float* __restrict__ sums) {
-  const int CG = C >> 3;
-  const int g = threadIdx.x % CG;
-  const int rl = threadIdx.x / CG;
-  const int RL = kThreads / CG;
+  const ReduceGeom geo = reduce_geom(C);
+  const int lg = threadIdx.x % geo.cgb;                 // group inside the block
+  const int rl = threadIdx.x / geo.cgb;
+  const int g = blockIdx.x * geo.cgb + lg;              // global channel group
+  const int RL = geo.rlb;
   float p[8], s1[8], s2[8];
   unpack8(*reinterpret_cast<const uint4*>(x + g * 8), p);
 #pragma unroll
   for (int i = 0; i < 8; ++i) s1[i] = s2[i] = 0.f;
-  const long long chunk = (R + gridDim.x - 1) / gridDim.x;
-  const long long r0 = (long long)blockIdx.x * chunk;
+  const long long chunk = (R + gridDim.y - 1) / gridDim.y;
+  const long long r0 = (long long)blockIdx.y * chunk;
   const long long r1 = r0 + chunk < R ? r0 + chunk : R;
   long long r = r0 + rl;
-  for (; r + 3LL * RL < r1; r += 4LL * RL) {
-    uint4 v[4];
+  for (; r + 7LL * RL < r1; r += 8LL * RL) {
+    uint4 v[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint4*>(x + (r + (long long)u * RL) * C + g * 8);
+    for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const uint4*>(x + (r + (long long)u * RL) * C + g * 8);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       float f[8];
       unpack8(v[u], f);
 #pragma unroll
@@ -98,7 +121,7 @@ __global__ void __launch_bounds__(kThreads) bn_stats_kernel(const __nv_bfloat16*
       s2[i] += d * d;
     }
   }
-  flush_partials(s1, s2, g, C, sums);
+  flush_partials(s1, s2, lg, geo.cgb, blockIdx.x * geo.cgb * 8, C, sums);
 }
 
 struct BnApplyParams {
@@ -150,37 +173,53 @@ __global__ void __launch_bounds__(kThreads) bn_apply_kernel(const BnApplyParams 
   }
   const long long total = p.R * CG;
   const long long stride = (long long)gridDim.x * blockDim.x;   // multiple of CG: g stays fixed
-  for (long long idx = gtid; idx < total; idx += stride) {
-    float f[8];
-    unpack8(*reinterpret_cast<const uint4*>(p.x + idx * 8), f);
-    if (p.residual != nullptr) {
-      float rr[8];
-      unpack8(*reinterpret_cast<const uint4*>(p.residual + idx * 8), rr);
+  constexpr int U = 4;
+  for (long long base = gtid; base < total; base += stride * U) {
+    uint4 vx[U], vr[U];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = f[i] * scale[i] + shift[i] + rr[i];
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = f[i] * scale[i] + shift[i];
+    for (int u = 0; u < U; ++u) {
+      const long long idx = base + (long long)u * stride;
+      if (idx < total) {
+        vx[u] = *reinterpret_cast<const uint4*>(p.x + idx * 8);
+        if (p.residual != nullptr) vr[u] = *reinterpret_cast<const uint4*>(p.residual + idx * 8);
+      }
     }
-    if (p.relu) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = fmaxf(f[i], 0.f);
+    for (int u = 0; u < U; ++u) {
+      const long long idx = base + (long long)u * stride;
+      if (idx >= total) continue;
+      float f[8];
+      unpack8(vx[u], f);
+      if (p.residual != nullptr) {
+        float rr[8];
+        unpack8(vr[u], rr);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = f[i] * scale[i] + shift[i] + rr[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = f[i] * scale[i] + shift[i];
+      }
+      if (p.relu) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = fmaxf(f[i], 0.f);
+      }
+      *reinterpret_cast<uint4*>(p.y + idx * 8) = pack8(f);
     }
-    *reinterpret_cast<uint4*>(p.y + idx * 8) = pack8(f);
   }
 }
 
 // sums[c] = sum dz;  sums[C+c] = sum dz * xhat
-__global__ void __launch_bounds__(kThreads) bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dy,
-                                                                 const __nv_bfloat16* __restrict__ y,
-                                                                 const __nv_bfloat16* __restrict__ x,
-                                                                 const float* __restrict__ save_mean,
-                                                                 const float* __restrict__ save_rstd, long long R, int C,
-                                                                 int relu, float* __restrict__ sums) {
-  const int CG = C >> 3;
-  const int g = threadIdx.x % CG;
-  const int rl = threadIdx.x / CG;
-  const int RL = kThreads / CG;
+__global__ void __launch_bounds__(kThreads, 3) bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                                    const __nv_bfloat16* __restrict__ y,
+                                                                    const __nv_bfloat16* __restrict__ x,
+                                                                    const float* __restrict__ save_mean,
+                                                                    const float* __restrict__ save_rstd, long long R,
+                                                                    int C, int relu, float* __restrict__ sums) {
+  const ReduceGeom geo = reduce_geom(C);
+  const int lg = threadIdx.x % geo.cgb;
+  const int rl = threadIdx.x / geo.cgb;
+  const int g = blockIdx.x * geo.cgb + lg;
+  const int RL = geo.rlb;
   float mean[8], rstd[8], s1[8], s2[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -188,21 +227,22 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_reduce_kernel(const __nv_bflo
     rstd[i] = save_rstd[g * 8 + i];
     s1[i] = s2[i] = 0.f;
   }
-  const long long chunk = (R + gridDim.x - 1) / gridDim.x;
-  const long long r0 = (long long)blockIdx.x * chunk;
+  const long long chunk = (R + gridDim.y - 1) / gridDim.y;
+  const long long r0 = (long long)blockIdx.y * chunk;
   const long long r1 = r0 + chunk < R ? r0 + chunk : R;
   long long r = r0 + rl;
-  for (; r + (long long)RL < r1; r += 2LL * RL) {
-    uint4 a[2], b[2], c[2];
+  constexpr int U = 3;
+  for (; r + (long long)(U - 1) * RL < r1; r += (long long)U * RL) {
+    uint4 a[U], b[U], c[U];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
+    for (int u = 0; u < U; ++u) {
       const long long off = (r + (long long)u * RL) * C + g * 8;
       a[u] = *reinterpret_cast<const uint4*>(dy + off);
       b[u] = *reinterpret_cast<const uint4*>(x + off);
       if (relu) c[u] = *reinterpret_cast<const uint4*>(y + off);
     }
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
+    for (int u = 0; u < U; ++u) {
       float fd[8], fx[8], fy[8];
       unpack8(a[u], fd);
       unpack8(b[u], fx);
@@ -228,7 +268,7 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_reduce_kernel(const __nv_bflo
       s2[i] += dz * (fx[i] - mean[i]) * rstd[i];
     }
   }
-  flush_partials(s1, s2, g, C, sums);
+  flush_partials(s1, s2, lg, geo.cgb, blockIdx.x * geo.cgb * 8, C, sums);
 }
 
 struct BnBwdApplyParams {
@@ -272,34 +312,55 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(const BnBwdApply
   }
   const long long total = p.R * CG;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long idx = gtid; idx < total; idx += stride) {
-    float fd[8], fx[8], fy[8], o[8];
-    unpack8(*reinterpret_cast<const uint4*>(p.dy + idx * 8), fd);
-    unpack8(*reinterpret_cast<const uint4*>(p.x + idx * 8), fx);
-    if (p.relu) {
-      unpack8(*reinterpret_cast<const uint4*>(p.y + idx * 8), fy);
+  constexpr int U = 2;
+  for (long long base = gtid; base < total; base += stride * U) {
+    uint4 vd[U], vx[U], vy[U];
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (!(fy[i] > 0.f)) fd[i] = 0.f;
+    for (int u = 0; u < U; ++u) {
+      const long long idx = base + (long long)u * stride;
+      if (idx < total) {
+        vd[u] = *reinterpret_cast<const uint4*>(p.dy + idx * 8);
+        vx[u] = *reinterpret_cast<const uint4*>(p.x + idx * 8);
+        if (p.relu) vy[u] = *reinterpret_cast<const uint4*>(p.y + idx * 8);
+      }
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = k0[i] * (fd[i] - k1[i] - (fx[i] - mean[i]) * rstd[i] * k2[i]);
-    *reinterpret_cast<uint4*>(p.dx + idx * 8) = pack8(o);
-    if (p.dres != nullptr) *reinterpret_cast<uint4*>(p.dres + idx * 8) = pack8(fd);
+    for (int u = 0; u < U; ++u) {
+      const long long idx = base + (long long)u * stride;
+      if (idx >= total) continue;
+      float fd[8], fx[8], fy[8], o[8];
+      unpack8(vd[u], fd);
+      unpack8(vx[u], fx);
+      if (p.relu) {
+        unpack8(vy[u], fy);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (!(fy[i] > 0.f)) fd[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = k0[i] * (fd[i] - k1[i] - (fx[i] - mean[i]) * rstd[i] * k2[i]);
+      *reinterpret_cast<uint4*>(p.dx + idx * 8) = pack8(o);
+      if (p.dres != nullptr) *reinterpret_cast<uint4*>(p.dres + idx * 8) = pack8(fd);
+    }
   }
 }
 
-int ReduceGrid(long long R, int C) {
-  const int RL = kThreads / (C >> 3);
-  long long blocks = (R + (long long)RL * 8 - 1) / ((long long)RL * 8);   // at least 8 rows per thread
-  if (blocks < 1) blocks = 1;
-  if (blocks > 148 * 8) blocks = 148 * 8;
-  return (int)blocks;
+dim3 ReduceGrid(long long R, int C) {
+  const int CG = C >> 3;
+  const int cgb = CG < 32 ? CG : 32;
+  const int rlb = kThreads / cgb;
+  const int cchunks = CG / cgb;
+  long long rows = (R + (long long)rlb * 16 - 1) / ((long long)rlb * 16);   // >= 16 rows per thread
+  long long cap = (148 * 4) / cchunks;
+  if (cap < 1) cap = 1;
+  if (rows > cap) rows = cap;
+  if (rows < 1) rows = 1;
+  return dim3(static_cast<unsigned>(cchunks), static_cast<unsigned>(rows));
 }
 int ApplyGrid(long long R, int C) {
   long long blocks = (R * (C >> 3) + kThreads * 4 - 1) / (kThreads * 4);
   if (blocks < 1) blocks = 1;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > 148 * 6) blocks = 148 * 6;
   return (int)blocks;
 }
 

@@ -15,6 +15,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from bluefog_b200.ops.fused_bn import bn_act
+from bluefog_b200.ops.fused_pool import maxpool3x3s2
 
 
 class MixedBatchNorm2d(nn.BatchNorm2d):
@@ -151,7 +152,7 @@ class ResNet(nn.Module):
             x = x.contiguous(memory_format=torch.channels_last)
         if x.dtype != self.conv1.weight.dtype:
             x = x.to(self.conv1.weight.dtype)
-        x = self.maxpool(bn_act(self.conv1(x), self.bn1, relu=True))
+        x = maxpool3x3s2(bn_act(self.conv1(x), self.bn1, relu=True))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         x = torch.flatten(self.avgpool(x), 1)
         if self.use_b200_gemm and x.is_cuda and x.dtype == torch.bfloat16:

@@ -137,6 +137,10 @@ class _FusedMixin:
                     cur_bytes += nbytes
                 if cur:
                     self._add_bucket(gi, cur, device, exchange_dtype, group)
+        self.overlap_backward = os.environ.get("BLUEFOG_B200_OVERLAP_BACKWARD", "1") != "0"
+        self._step_recipe = None
+        self._armed = False      # set by zero_grad(): the next backward belongs to a regular training step
+        self._register_overlap_hooks()
         self._publish_all()
 
     def _add_bucket(self, gi, params, device, pub_dtype, group):
@@ -279,7 +283,9 @@ class _FusedMixin:
         self._use_timeline = False
 
     def zero_grad(self, set_to_none: bool = True):
+        self._armed = True
         for bk in self._buckets:
+            bk.remaining = len(bk.params)
             for p in bk.params:
                 if p.grad is None:
                     continue
@@ -289,6 +295,72 @@ class _FusedMixin:
                     p.grad.detach_()
                     p.grad.zero_()
 
+    def _launch_bucket(self, bk, recipe):
+        """Launches the step of one bucket on the current stream."""
+        self_w, src_ranks, src_w, n_readers = recipe
+        if self._style == "awc":
+            a = self._new_args(bk, MODE_AWC)
+            self._fill_opt(a, bk)
+            a.self_weight, a.src_ranks, a.src_weights, a.n_readers = self_w, src_ranks, src_w, n_readers
+            bk.native.step(a)
+        elif self._style == "atc":
+            a = self._new_args(bk, MODE_ADAPT_PUBLISH)
+            self._fill_opt(a, bk)
+            bk.native.step(a)
+            c = self._new_args(bk, MODE_COMBINE_ONLY)
+            c.self_weight, c.src_ranks, c.src_weights, c.n_readers = self_w, src_ranks, src_w, n_readers
+            bk.native.step(c)
+        else:  # gradient allreduce
+            n = _b.size()
+            if n > 1:
+                pub = self._new_args(bk, MODE_PUBLISH_ONLY)
+                pub.master = None
+                self._fill_grads(pub, bk)
+                bk.native.step(pub)
+            a = self._new_args(bk, MODE_GRAD_REDUCE)
+            self._fill_opt(a, bk)
+            others = [r for r in range(n) if r != _b.rank()]
+            if n > 1:
+                a.src_ranks, a.src_weights, a.n_readers = others, [1.0] * len(others), len(others)
+                a.post_scale = 1.0 / n
+                bk.native.step(a)
+            else:
+                a.mode = MODE_AWC  # single rank: plain local update
+                bk.native.step(a)
+        self._after_update(bk)
+
+    # -- overlap with backward ------------------------------------------------------------------
+    def _register_overlap_hooks(self):
+        """When all gradients of a bucket exist, its step is launched on a side stream while
+        backward continues with the earlier layers (the role of the reference's per-parameter
+        backward hooks, bluefog/torch/optimizers.py:556-599, at bucket granularity).  Not used
+        while a CUDA graph is being captured, nor with local gradient accumulation."""
+        self._comm_stream = torch.cuda.Stream(device=_b.device(), priority=-1)
+        self._early = []        # buckets already launched during this backward
+        for bk in self._buckets:
+            bk.remaining = len(bk.params)
+            for p in bk.params:
+                p.register_post_accumulate_grad_hook(self._make_ready_hook(bk))
+
+    def _make_ready_hook(self, bk):
+        def hook(_param):
+            bk.remaining -= 1
+            if bk.remaining != 0:
+                return
+            if (not self.overlap_backward or not self._armed or self._num_steps_per_communication != 1
+                    or torch.cuda.is_current_stream_capturing()):
+                return
+            with torch.no_grad():
+                recipe = self._step_recipe
+                if recipe is None:
+                    recipe = self._step_recipe = self._combine_recipe(True)
+                cur = torch.cuda.current_stream()
+                self._comm_stream.wait_stream(cur)
+                with torch.cuda.stream(self._comm_stream):
+                    self._launch_bucket(bk, recipe)
+                self._early.append(bk)
+        return hook
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = None
@@ -297,41 +369,22 @@ class _FusedMixin:
                 loss = closure()
         self._local_steps += 1
         communicate = self._local_steps % self._num_steps_per_communication == 0
-        self_w, src_ranks, src_w, n_readers = self._combine_recipe(communicate)
+        recipe = self._step_recipe if self._early else None
+        if recipe is None:
+            recipe = self._combine_recipe(communicate)
         tl = getattr(self, "_use_timeline", False)
         if tl:
             _b.timeline_start_activity("fused.step", "FUSED_" + self._style.upper())
+        early = set(id(bk) for bk in self._early)
         for bk in self._buckets:
-            if self._style == "awc":
-                a = self._new_args(bk, MODE_AWC)
-                self._fill_opt(a, bk)
-                a.self_weight, a.src_ranks, a.src_weights, a.n_readers = self_w, src_ranks, src_w, n_readers
-                bk.native.step(a)
-            elif self._style == "atc":
-                a = self._new_args(bk, MODE_ADAPT_PUBLISH)
-                self._fill_opt(a, bk)
-                bk.native.step(a)
-                c = self._new_args(bk, MODE_COMBINE_ONLY)
-                c.self_weight, c.src_ranks, c.src_weights, c.n_readers = self_w, src_ranks, src_w, n_readers
-                bk.native.step(c)
-            else:  # gradient allreduce
-                n = _b.size()
-                if n > 1:
-                    pub = self._new_args(bk, MODE_PUBLISH_ONLY)
-                    pub.master = None
-                    self._fill_grads(pub, bk)
-                    bk.native.step(pub)
-                a = self._new_args(bk, MODE_GRAD_REDUCE)
-                self._fill_opt(a, bk)
-                others = [r for r in range(n) if r != _b.rank()]
-                if n > 1:
-                    a.src_ranks, a.src_weights, a.n_readers = others, [1.0] * len(others), len(others)
-                    a.post_scale = 1.0 / n
-                    bk.native.step(a)
-                else:
-                    a.mode = MODE_AWC  # single rank: plain local update
-                    bk.native.step(a)
-            self._after_update(bk)
+            if id(bk) not in early:
+                self._launch_bucket(bk, recipe)
+            bk.remaining = len(bk.params)
+        if self._early:
+            torch.cuda.current_stream().wait_stream(self._comm_stream)
+            self._early = []
+        self._step_recipe = None
+        self._armed = False
         if tl:
             _b.timeline_end_activity("fused.step")
         self._synchronized = False

@@ -23,6 +23,9 @@ class GraphedForwardBackward:
         if not example_x.is_cuda:
             raise ValueError("CUDA graphs need CUDA tensors")
         self.model, self.loss_fn, self.optimizer = model, loss_fn, optimizer
+        if hasattr(optimizer, "overlap_backward"):
+            # bucket steps launched from backward hooks have per-step arguments: they cannot live in a graph
+            optimizer.overlap_backward = False
         self.static_x = example_x.clone()
         self.static_y = example_y.clone()
         self.graph = torch.cuda.CUDAGraph()

@@ -78,3 +78,22 @@ def test_eval_mode_and_unsupported_inputs_fall_back():
     x16 = torch.randn(2, 24, 5, 5, device="cuda").to(torch.bfloat16)   # NCHW, C/8 does not divide 256
     out = bn_act(x16, bn.to(torch.bfloat16), relu=False)
     assert out.shape == x16.shape
+
+
+@pytest.mark.parametrize("shape", [(2, 64, 112, 112), (3, 8, 7, 9), (1, 128, 5, 5), (4, 64, 56, 57)])
+def test_maxpool_matches_pytorch(shape):
+    from bluefog_b200.ops.fused_pool import maxpool3x3s2
+    torch.manual_seed(shape[2])
+    x = torch.randn(*shape, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    x1 = x.clone().requires_grad_(True)
+    y = maxpool3x3s2(x1)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    x2 = x.float().requires_grad_(True)
+    y2 = F.max_pool2d(x2, 3, 2, 1)
+    y2.backward(gy.float())
+    torch.cuda.synchronize()
+    assert y.shape == y2.shape
+    assert torch.equal(y.float(), y2)
+    # bf16 inputs contain ties; PyTorch also sends the gradient to the first maximum in scan order
+    assert (x1.grad.float() - x2.grad).abs().max().item() <= 2e-2 * max(1.0, x2.grad.abs().max().item())

@@ -286,7 +286,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("bn_forward", [](at::Tensor x, c10::optional<at::Tensor> residual, at::Tensor gamma, at::Tensor beta,
                          c10::optional<at::Tensor> running_mean, c10::optional<at::Tensor> running_var, double eps,
-                         double momentum, bool relu) {
+                         double momentum, bool relu, c10::optional<at::Tensor> zeroed_sums) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.scalar_type() == at::kBFloat16 &&
                 x.is_contiguous(at::MemoryFormat::ChannelsLast), "bn_forward expects a bf16 NHWC (channels_last) CUDA tensor");
     const int C = static_cast<int>(x.size(1));
@@ -298,7 +298,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     c10::cuda::CUDAGuard g(x.get_device());
     at::Tensor y = at::empty_like(x);
     auto fopts = x.options().dtype(at::kFloat);
-    at::Tensor sums = at::zeros({2 * C}, fopts);
+    // 2*C floats that must be zero on entry; callers may hand in a slice of a workspace that they
+    // clear once per step instead of paying one memset per layer
+    at::Tensor sums;
+    if (zeroed_sums.has_value() && zeroed_sums->defined()) {
+      TORCH_CHECK(zeroed_sums->is_cuda() && zeroed_sums->scalar_type() == at::kFloat && zeroed_sums->is_contiguous() &&
+                  zeroed_sums->numel() >= 2 * C, "zeroed_sums must be a contiguous fp32 CUDA tensor of 2*C elements");
+      sums = *zeroed_sums;
+    } else {
+      sums = at::zeros({2 * C}, fopts);
+    }
     at::Tensor save_mean = at::empty({C}, fopts), save_rstd = at::empty({C}, fopts);
     const void* res = nullptr;
     if (residual.has_value() && residual->defined()) {
@@ -319,9 +328,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                     CurrentStream(x.get_device()));
     TORCH_CHECK(e == cudaSuccess, "bn_forward launch failed: ", cudaGetErrorString(e));
     return std::make_tuple(y, save_mean, save_rstd);
-  });
+  }, py::arg("x"), py::arg("residual"), py::arg("gamma"), py::arg("beta"), py::arg("running_mean"),
+     py::arg("running_var"), py::arg("eps"), py::arg("momentum"), py::arg("relu"), py::arg("zeroed_sums") = py::none());
   m.def("bn_backward", [](at::Tensor dy, at::Tensor y, at::Tensor x, at::Tensor save_mean, at::Tensor save_rstd,
-                          at::Tensor gamma, bool relu, bool want_dres) {
+                          at::Tensor gamma, bool relu, bool want_dres, c10::optional<at::Tensor> zeroed_sums) {
     TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous(at::MemoryFormat::ChannelsLast) &&
                 dy.sizes() == x.sizes(), "bn_backward expects a bf16 NHWC gradient of the shape of x");
     const int C = static_cast<int>(x.size(1));
@@ -330,7 +340,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     c10::cuda::CUDAGuard g(x.get_device());
     at::Tensor dx = at::empty_like(x);
     at::Tensor dres = want_dres ? at::empty_like(x) : at::Tensor();
-    at::Tensor sums = at::zeros({2 * C}, x.options().dtype(at::kFloat));
+    at::Tensor sums = (zeroed_sums.has_value() && zeroed_sums->defined())
+                          ? *zeroed_sums : at::zeros({2 * C}, x.options().dtype(at::kFloat));
+    TORCH_CHECK(sums.is_cuda() && sums.scalar_type() == at::kFloat && sums.is_contiguous() && sums.numel() >= 2 * C,
+                "zeroed_sums must be a contiguous fp32 CUDA tensor of 2*C elements");
     at::Tensor dgamma = at::empty_like(gamma), dbeta = at::empty_like(gamma);
     cudaError_t e = LaunchBnBackward(dy.data_ptr(), y.data_ptr(), x.data_ptr(), dx.data_ptr(),
                                      want_dres ? dres.data_ptr() : nullptr, sums.data_ptr<float>(),
@@ -339,7 +352,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                      CurrentStream(x.get_device()));
     TORCH_CHECK(e == cudaSuccess, "bn_backward launch failed: ", cudaGetErrorString(e));
     return std::make_tuple(dx, dres, dgamma, dbeta);
-  });
+  }, py::arg("dy"), py::arg("y"), py::arg("x"), py::arg("save_mean"), py::arg("save_rstd"), py::arg("gamma"),
+     py::arg("relu"), py::arg("want_dres"), py::arg("zeroed_sums") = py::none());
 
   // ---- 3x3/2 max pooling, NHWC bf16 ---------------------------------------------------------
   m.def("maxpool3x3s2_forward", [](at::Tensor x) {

@@ -14,8 +14,14 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from bluefog_b200.ops.fused_bn import bn_act
+from bluefog_b200.ops import fused_bn
+from bluefog_b200.ops.fused_bn import bn_act as _bn_act
 from bluefog_b200.ops.fused_pool import maxpool3x3s2
+
+
+def bn_act(x, bn, relu=True, residual=None):
+    # the batch counters of all layers are advanced together in ResNet.forward
+    return _bn_act(x, bn, relu=relu, residual=residual, count_batches=False)
 
 
 class MixedBatchNorm2d(nn.BatchNorm2d):
@@ -26,7 +32,8 @@ class MixedBatchNorm2d(nn.BatchNorm2d):
         if w is not None and w.dtype != torch.float32 and x.dtype == w.dtype:
             # cuDNN's mixed mode wants fp32 scale/shift with 16-bit activations
             w, b = w.float(), b.float()
-        if self.training and self.track_running_stats and self.num_batches_tracked is not None:
+        if (self.training and self.track_running_stats and self.num_batches_tracked is not None
+                and not getattr(self, "external_batch_count", False)):
             self.num_batches_tracked.add_(1)
         momentum = 0.0 if self.momentum is None else self.momentum
         return F.batch_norm(x, self.running_mean if (not self.training or self.track_running_stats) else None,
@@ -124,6 +131,9 @@ class ResNet(nn.Module):
         self.layer4 = self._make_layer(block, 512, layers[3], stride=2)
         self.avgpool = nn.AdaptiveAvgPool2d((1, 1))
         self.fc = nn.Linear(512 * block.expansion, num_classes)
+        self._bn_modules = [m for m in self.modules() if isinstance(m, MixedBatchNorm2d)]
+        for m in self._bn_modules:
+            m.external_batch_count = True        # advanced together in forward()
         for m in self.modules():
             if isinstance(m, nn.Conv2d):
                 nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")
@@ -152,6 +162,11 @@ class ResNet(nn.Module):
             x = x.contiguous(memory_format=torch.channels_last)
         if x.dtype != self.conv1.weight.dtype:
             x = x.to(self.conv1.weight.dtype)
+        if self.training:
+            fused_bn.begin_step(x.device)          # one memset for the statistics scratch of all layers
+            counters = [m.num_batches_tracked for m in self._bn_modules if m.num_batches_tracked is not None]
+            if counters:
+                torch._foreach_add_(counters, 1)     # one launch for the batch counters of all layers
         x = maxpool3x3s2(bn_act(self.conv1(x), self.bn1, relu=True))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         x = torch.flatten(self.avgpool(x), 1)

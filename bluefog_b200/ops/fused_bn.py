@@ -13,24 +13,86 @@ from bluefog_b200.common.basics import get_basics
 _b = get_basics()
 
 
+class _Workspace:
+    """Zero-initialised scratch for the per-channel sums of all BatchNorm layers of one step.
+
+    ``begin_step`` clears the part used by the previous step with a single memset and hands out
+    slices from the start again; layers that run without ``begin_step`` (or do not fit) simply
+    allocate their own zeros.  A slice is used at most once per generation, so a second backward
+    through the same forward, or two forwards before a backward, fall back to fresh zeros.
+    """
+
+    def __init__(self, device, capacity=1 << 20):
+        self.buf = torch.zeros(capacity, dtype=torch.float32, device=device)
+        self.offset = 0
+        self.high_water = 0
+        self.generation = 0
+        self.active = False
+
+    def begin_step(self):
+        if self.high_water:
+            self.buf[:self.high_water].zero_()
+        self.offset = 0
+        self.high_water = 0
+        self.generation += 1
+        self.active = True
+
+    def take(self, n):
+        if not self.active or self.offset + n > self.buf.numel():
+            return None, -1
+        out = self.buf[self.offset:self.offset + n]
+        self.offset += (n + 63) // 64 * 64
+        self.high_water = max(self.high_water, self.offset)
+        return out, self.generation
+
+
+_workspaces = {}
+
+
+def begin_step(device):
+    """Call once at the start of a training forward pass (the models of this package do)."""
+    if device.type != "cuda":
+        return
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = _workspaces[key] = _Workspace(device)
+    ws.begin_step()
+
+
+def _take(device, n):
+    ws = _workspaces.get(device.index if device.index is not None else torch.cuda.current_device())
+    if ws is None:
+        return None, -1, None
+    t, gen = ws.take(n)
+    return t, gen, ws
+
+
 class _BnActFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu):
-        y, mean, rstd = _b.native.bn_forward(x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu)
+        c2 = 2 * x.shape[1]
+        fwd_sums, _, _ = _take(x.device, c2)
+        y, mean, rstd = _b.native.bn_forward(x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu,
+                                             fwd_sums)
         ctx.save_for_backward(x, y, mean, rstd, gamma)
         ctx.relu = relu
         ctx.has_res = residual is not None
+        ctx.bwd_sums, ctx.bwd_gen, ctx.ws = _take(x.device, c2)   # reserved now, consumed by backward
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, y, mean, rstd, gamma = ctx.saved_tensors
         dy = dy.contiguous(memory_format=torch.channels_last)
-        dx, dres, dgamma, dbeta = _b.native.bn_backward(dy, y, x, mean, rstd, gamma, ctx.relu, ctx.has_res)
+        sums = None
+        if ctx.bwd_sums is not None and ctx.ws.generation == ctx.bwd_gen:
+            sums, ctx.bwd_sums = ctx.bwd_sums, None    # a slice is clean only once
+        dx, dres, dgamma, dbeta = _b.native.bn_backward(dy, y, x, mean, rstd, gamma, ctx.relu, ctx.has_res, sums)
         return dx, (dres if ctx.has_res else None), dgamma, dbeta, None, None, None, None, None
 
 
-def bn_act(x, bn, relu=True, residual=None):
+def bn_act(x, bn, relu=True, residual=None, count_batches=True):
     """``bn`` is an ``nn.BatchNorm2d``-like module (weight, bias, running_mean, running_var, eps, momentum)."""
     use_kernel = (bn.training and x.is_cuda and x.dtype == torch.bfloat16 and bn.weight is not None
                   and _b.native.bn_supported(x)
@@ -38,7 +100,7 @@ def bn_act(x, bn, relu=True, residual=None):
     if use_kernel:
         if residual is not None and not residual.is_contiguous(memory_format=torch.channels_last):
             residual = residual.contiguous(memory_format=torch.channels_last)
-        if bn.track_running_stats and bn.num_batches_tracked is not None:
+        if count_batches and bn.track_running_stats and bn.num_batches_tracked is not None:
             bn.num_batches_tracked.add_(1)
         momentum = 0.1 if bn.momentum is None else bn.momentum
         rm = bn.running_mean if bn.track_running_stats else None

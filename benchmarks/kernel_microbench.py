@@ -99,8 +99,10 @@ def bench_gemm(args):
     ms = timed(lambda: _C.gemm_bf16_nt(a, w, None, 0), args.iters, args.warmup)
     ms_lib = timed(lambda: torch.matmul(a, w.t()), args.iters, args.warmup)
     flops = 2.0 * args.m * args.n * args.k
+    nbytes = 2.0 * (args.m * args.k + args.n * args.k + args.m * args.n)     # A, B read once, C written once
     return {"kernel": "gemm_bf16_nt_kernel (tcgen05)", "m": args.m, "n": args.n, "k": args.k, "ms": ms,
             "tflops": flops / ms / 1e9, "frac_of_measured_bf16": flops / ms / 1e9 / PEAKS["bf16_tflops"],
+            "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / PEAKS["hbm_gbs"],
             "library_ms": ms_lib, "library_tflops": flops / ms_lib / 1e9, "status": _C.gemm_status()}
 
 
@@ -111,20 +113,20 @@ def bench_bn(args):
     gamma = torch.ones(c, device="cuda")
     beta = torch.zeros(c, device="cuda")
     rm, rv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
-    y, mean, rstd = _C.bn_forward(x, res, gamma, beta, rm, rv, 1e-5, 0.1, True)
+    y, mean, rstd, mask = _C.bn_forward(x, res, gamma, beta, rm, rv, 1e-5, 0.1, True)
     dy = torch.randn_like(x)
     ms_f = timed(lambda: _C.bn_forward(x, res, gamma, beta, rm, rv, 1e-5, 0.1, True), args.iters, args.warmup)
-    ms_b = timed(lambda: _C.bn_backward(dy, y, x, mean, rstd, gamma, True, True), args.iters, args.warmup)
+    ms_b = timed(lambda: _C.bn_backward(dy, mask, x, mean, rstd, gamma, True, True), args.iters, args.warmup)
     bn = torch.nn.BatchNorm2d(c).cuda()
 
     bn16 = bn.to(torch.bfloat16)
     ms_tf = timed(lambda: torch.relu(bn16(x) + res), args.iters, args.warmup)
     nbytes = x.numel() * 2
-    # forward: stats read x; apply reads x, residual, writes y.  backward: reduce reads dy, y, x; apply reads
-    # dy, y, x and writes dx, dresidual.
+    # forward: stats read x; apply reads x, residual, writes y (+ 1 bit/element).  backward: reduce reads dy, x
+    # (+ bits); apply reads dy, x (+ bits) and writes dx, dresidual.
     return {"kernel": "bn_stats+bn_apply / bn_bwd_reduce+bn_bwd_apply (ReLU + residual)", "shape": [n, c, h, w],
-            "fwd_ms": ms_f, "fwd_gbs": 4 * nbytes / ms_f / 1e6, "fwd_frac_of_measured_hbm": 4 * nbytes / ms_f / 1e6 / PEAKS["hbm_gbs"],
-            "bwd_ms": ms_b, "bwd_gbs": 8 * nbytes / ms_b / 1e6, "bwd_frac_of_measured_hbm": 8 * nbytes / ms_b / 1e6 / PEAKS["hbm_gbs"],
+            "fwd_ms": ms_f, "fwd_gbs": 4.0625 * nbytes / ms_f / 1e6, "fwd_frac_of_measured_hbm": 4.0625 * nbytes / ms_f / 1e6 / PEAKS["hbm_gbs"],
+            "bwd_ms": ms_b, "bwd_gbs": 6.125 * nbytes / ms_b / 1e6, "bwd_frac_of_measured_hbm": 6.125 * nbytes / ms_b / 1e6 / PEAKS["hbm_gbs"],
             "pytorch_fwd_ms (bn, add, relu)": ms_tf}
 
 

@@ -14,6 +14,7 @@
 #include "cuda/bucket.h"
 #include "cuda/gemm_tcgen05.h"
 #include "cuda/gpu_channel.h"
+#include "cuda/ln_kernels.h"
 #include "cuda/pool_kernels.h"
 #include "cuda/symm_mem.h"
 
@@ -322,15 +323,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       rm = running_mean->data_ptr<float>();
       rv = running_var->data_ptr<float>();
     }
-    cudaError_t e = LaunchBnForward(x.data_ptr(), res, y.data_ptr(), sums.data_ptr<float>(), gamma.data_ptr(), beta.data_ptr(),
+    at::Tensor mask = relu ? at::empty({static_cast<int64_t>(R) * (C / 8)}, x.options().dtype(at::kByte)) : at::Tensor();
+    cudaError_t e = LaunchBnForward(x.data_ptr(), res, y.data_ptr(), relu ? mask.data_ptr() : nullptr,
+                                    sums.data_ptr<float>(), gamma.data_ptr(), beta.data_ptr(),
                                     rm, rv, save_mean.data_ptr<float>(), save_rstd.data_ptr<float>(), R, C,
                                     static_cast<float>(eps), static_cast<float>(momentum), relu ? 1 : 0, pbf16 ? 1 : 0,
                                     CurrentStream(x.get_device()));
     TORCH_CHECK(e == cudaSuccess, "bn_forward launch failed: ", cudaGetErrorString(e));
-    return std::make_tuple(y, save_mean, save_rstd);
+    return std::make_tuple(y, save_mean, save_rstd, mask);
   }, py::arg("x"), py::arg("residual"), py::arg("gamma"), py::arg("beta"), py::arg("running_mean"),
      py::arg("running_var"), py::arg("eps"), py::arg("momentum"), py::arg("relu"), py::arg("zeroed_sums") = py::none());
-  m.def("bn_backward", [](at::Tensor dy, at::Tensor y, at::Tensor x, at::Tensor save_mean, at::Tensor save_rstd,
+  m.def("bn_backward", [](at::Tensor dy, c10::optional<at::Tensor> mask, at::Tensor x, at::Tensor save_mean, at::Tensor save_rstd,
                           at::Tensor gamma, bool relu, bool want_dres, c10::optional<at::Tensor> zeroed_sums) {
     TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous(at::MemoryFormat::ChannelsLast) &&
                 dy.sizes() == x.sizes(), "bn_backward expects a bf16 NHWC gradient of the shape of x");
@@ -345,15 +348,62 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(sums.is_cuda() && sums.scalar_type() == at::kFloat && sums.is_contiguous() && sums.numel() >= 2 * C,
                 "zeroed_sums must be a contiguous fp32 CUDA tensor of 2*C elements");
     at::Tensor dgamma = at::empty_like(gamma), dbeta = at::empty_like(gamma);
-    cudaError_t e = LaunchBnBackward(dy.data_ptr(), y.data_ptr(), x.data_ptr(), dx.data_ptr(),
+    const void* mptr = nullptr;
+    if (relu) {
+      TORCH_CHECK(mask.has_value() && mask->defined() && mask->scalar_type() == at::kByte &&
+                  mask->numel() == R * (C / 8), "bn_backward needs the ReLU bit mask of the forward pass");
+      mptr = mask->data_ptr();
+    }
+    cudaError_t e = LaunchBnBackward(dy.data_ptr(), mptr, x.data_ptr(), dx.data_ptr(),
                                      want_dres ? dres.data_ptr() : nullptr, sums.data_ptr<float>(),
                                      save_mean.data_ptr<float>(), save_rstd.data_ptr<float>(), gamma.data_ptr(),
                                      dgamma.data_ptr(), dbeta.data_ptr(), R, C, relu ? 1 : 0, pbf16 ? 1 : 0,
                                      CurrentStream(x.get_device()));
     TORCH_CHECK(e == cudaSuccess, "bn_backward launch failed: ", cudaGetErrorString(e));
     return std::make_tuple(dx, dres, dgamma, dbeta);
-  }, py::arg("dy"), py::arg("y"), py::arg("x"), py::arg("save_mean"), py::arg("save_rstd"), py::arg("gamma"),
+  }, py::arg("dy"), py::arg("mask"), py::arg("x"), py::arg("save_mean"), py::arg("save_rstd"), py::arg("gamma"),
      py::arg("relu"), py::arg("want_dres"), py::arg("zeroed_sums") = py::none());
+
+  // ---- LayerNorm over the last dimension, bf16 ------------------------------------------------
+  m.def("ln_supported", [](at::Tensor x) {
+    return x.is_cuda() && x.dim() >= 1 && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.numel() > 0 &&
+           LnShapeSupported(x.numel() / x.size(-1), static_cast<int>(x.size(-1)));
+  });
+  m.def("ln_forward", [](at::Tensor x, at::Tensor gamma, at::Tensor beta, double eps) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() >= 1 && x.numel() > 0,
+                "ln_forward expects a contiguous bf16 CUDA tensor");
+    const int C = static_cast<int>(x.size(-1));
+    const long long R = x.numel() / C;
+    TORCH_CHECK(LnShapeSupported(R, C), "ln_forward: unsupported row length ", C);
+    const bool pbf16 = gamma.scalar_type() == at::kBFloat16;
+    TORCH_CHECK(gamma.is_cuda() && beta.is_cuda() && gamma.numel() == C && beta.numel() == C &&
+                gamma.scalar_type() == beta.scalar_type() && (pbf16 || gamma.scalar_type() == at::kFloat) &&
+                gamma.is_contiguous() && beta.is_contiguous(), "ln_forward: weight/bias must be C fp32 or bf16 values");
+    at::Tensor y = at::empty_like(x);
+    at::Tensor mean = at::empty({static_cast<int64_t>(R)}, x.options().dtype(at::kFloat));
+    at::Tensor rstd = at::empty({static_cast<int64_t>(R)}, x.options().dtype(at::kFloat));
+    cudaError_t e = LaunchLnForward(x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), mean.data_ptr<float>(),
+                                    rstd.data_ptr<float>(), R, C, static_cast<float>(eps), pbf16 ? 1 : 0,
+                                    CurrentStream(x.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "ln_forward launch failed: ", cudaGetErrorString(e));
+    return std::make_tuple(y, mean, rstd);
+  });
+  m.def("ln_backward", [](at::Tensor dy, at::Tensor x, at::Tensor gamma, at::Tensor mean, at::Tensor rstd) {
+    TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && dy.sizes() == x.sizes() &&
+                x.scalar_type() == at::kBFloat16 && x.is_contiguous(), "ln_backward expects contiguous bf16 dy and x");
+    const int C = static_cast<int>(x.size(-1));
+    const long long R = x.numel() / C;
+    TORCH_CHECK(LnShapeSupported(R, C) && mean.numel() == R && rstd.numel() == R && mean.scalar_type() == at::kFloat &&
+                rstd.scalar_type() == at::kFloat, "ln_backward: statistics do not match x");
+    const bool pbf16 = gamma.scalar_type() == at::kBFloat16;
+    at::Tensor dx = at::empty_like(x);
+    at::Tensor sums = at::zeros({2, static_cast<int64_t>(C)}, x.options().dtype(at::kFloat));
+    cudaError_t e = LaunchLnBackward(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr<float>(),
+                                     rstd.data_ptr<float>(), dx.data_ptr(), sums.data_ptr<float>(),
+                                     sums.data_ptr<float>() + C, R, C, pbf16 ? 1 : 0, CurrentStream(x.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "ln_backward launch failed: ", cudaGetErrorString(e));
+    return std::make_tuple(dx, sums.select(0, 0), sums.select(0, 1));
+  });
 
   // ---- 3x3/2 max pooling, NHWC bf16 ---------------------------------------------------------
   m.def("maxpool3x3s2_forward", [](at::Tensor x) {

@@ -1,6 +1,6 @@
 // Fused training-mode BatchNorm for NHWC bf16 activations:
 //   forward : y = relu( gamma * (x - mean) * rstd + beta  [+ residual] )
-//   backward: dz = dy * (y > 0);  dx = gamma*rstd * (dz - mean(dz) - xhat * mean(dz*xhat));
+//   backward: dz = dy * (y > 0)   (the forward pass leaves one bit per element for this);  dx = gamma*rstd * (dz - mean(dz) - xhat * mean(dz*xhat));
 //             dresidual = dz;  dgamma = sum(dz*xhat);  dbeta = sum(dz)
 // The activation is viewed as a [R, C] matrix (R = N*H*W rows, C contiguous).  Each pass is one
 // streaming kernel with 16-byte loads: a statistics pass (per-channel sums in fp32, shifted by
@@ -128,6 +128,7 @@ struct BnApplyParams {
   const __nv_bfloat16* x;
   const __nv_bfloat16* residual;   // may be null
   __nv_bfloat16* y;
+  unsigned char* mask;             // one bit per element (y > 0), 8 channels per byte; null without ReLU
   const float* sums;               // from bn_stats_kernel
   const void* gamma;
   const void* beta;
@@ -200,8 +201,13 @@ __global__ void __launch_bounds__(kThreads) bn_apply_kernel(const BnApplyParams 
         for (int i = 0; i < 8; ++i) f[i] = f[i] * scale[i] + shift[i];
       }
       if (p.relu) {
+        unsigned bits = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = fmaxf(f[i], 0.f);
+        for (int i = 0; i < 8; ++i) {
+          bits |= (f[i] > 0.f ? 1u : 0u) << i;
+          f[i] = fmaxf(f[i], 0.f);
+        }
+        p.mask[idx] = (unsigned char)bits;
       }
       *reinterpret_cast<uint4*>(p.y + idx * 8) = pack8(f);
     }
@@ -210,7 +216,7 @@ __global__ void __launch_bounds__(kThreads) bn_apply_kernel(const BnApplyParams 
 
 // sums[c] = sum dz;  sums[C+c] = sum dz * xhat
 __global__ void __launch_bounds__(kThreads, 3) bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dy,
-                                                                    const __nv_bfloat16* __restrict__ y,
+                                                                    const unsigned char* __restrict__ mask,
                                                                     const __nv_bfloat16* __restrict__ x,
                                                                     const float* __restrict__ save_mean,
                                                                     const float* __restrict__ save_rstd, long long R,
@@ -231,25 +237,27 @@ __global__ void __launch_bounds__(kThreads, 3) bn_bwd_reduce_kernel(const __nv_b
   const long long r0 = (long long)blockIdx.y * chunk;
   const long long r1 = r0 + chunk < R ? r0 + chunk : R;
   long long r = r0 + rl;
-  constexpr int U = 3;
+  constexpr int U = 4;
+  const int CG = C >> 3;
   for (; r + (long long)(U - 1) * RL < r1; r += (long long)U * RL) {
-    uint4 a[U], b[U], c[U];
+    uint4 a[U], b[U];
+    unsigned m[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const long long off = (r + (long long)u * RL) * C + g * 8;
+      const long long row = r + (long long)u * RL;
+      const long long off = row * C + g * 8;
       a[u] = *reinterpret_cast<const uint4*>(dy + off);
       b[u] = *reinterpret_cast<const uint4*>(x + off);
-      if (relu) c[u] = *reinterpret_cast<const uint4*>(y + off);
+      m[u] = relu ? mask[row * CG + g] : 0xffu;
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      float fd[8], fx[8], fy[8];
+      float fd[8], fx[8];
       unpack8(a[u], fd);
       unpack8(b[u], fx);
-      if (relu) unpack8(c[u], fy);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float dz = (relu && !(fy[i] > 0.f)) ? 0.f : fd[i];
+        const float dz = ((m[u] >> i) & 1u) ? fd[i] : 0.f;
         s1[i] += dz;
         s2[i] += dz * (fx[i] - mean[i]) * rstd[i];
       }
@@ -257,13 +265,13 @@ __global__ void __launch_bounds__(kThreads, 3) bn_bwd_reduce_kernel(const __nv_b
   }
   for (; r < r1; r += RL) {
     const long long off = r * C + g * 8;
-    float fd[8], fx[8], fy[8];
+    float fd[8], fx[8];
     unpack8(*reinterpret_cast<const uint4*>(dy + off), fd);
     unpack8(*reinterpret_cast<const uint4*>(x + off), fx);
-    if (relu) unpack8(*reinterpret_cast<const uint4*>(y + off), fy);
+    const unsigned m = relu ? mask[r * CG + g] : 0xffu;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float dz = (relu && !(fy[i] > 0.f)) ? 0.f : fd[i];
+      const float dz = ((m >> i) & 1u) ? fd[i] : 0.f;
       s1[i] += dz;
       s2[i] += dz * (fx[i] - mean[i]) * rstd[i];
     }
@@ -273,7 +281,7 @@ __global__ void __launch_bounds__(kThreads, 3) bn_bwd_reduce_kernel(const __nv_b
 
 struct BnBwdApplyParams {
   const __nv_bfloat16* dy;
-  const __nv_bfloat16* y;
+  const unsigned char* mask;       // bits written by the forward pass (null without ReLU)
   const __nv_bfloat16* x;
   __nv_bfloat16* dx;
   __nv_bfloat16* dres;             // may be null
@@ -312,31 +320,29 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(const BnBwdApply
   }
   const long long total = p.R * CG;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  constexpr int U = 2;
+  constexpr int U = 4;
   for (long long base = gtid; base < total; base += stride * U) {
-    uint4 vd[U], vx[U], vy[U];
+    uint4 vd[U], vx[U];
+    unsigned m[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const long long idx = base + (long long)u * stride;
       if (idx < total) {
         vd[u] = *reinterpret_cast<const uint4*>(p.dy + idx * 8);
         vx[u] = *reinterpret_cast<const uint4*>(p.x + idx * 8);
-        if (p.relu) vy[u] = *reinterpret_cast<const uint4*>(p.y + idx * 8);
+        m[u] = p.relu ? p.mask[idx] : 0xffu;
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const long long idx = base + (long long)u * stride;
       if (idx >= total) continue;
-      float fd[8], fx[8], fy[8], o[8];
+      float fd[8], fx[8], o[8];
       unpack8(vd[u], fd);
       unpack8(vx[u], fx);
-      if (p.relu) {
-        unpack8(vy[u], fy);
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (!(fy[i] > 0.f)) fd[i] = 0.f;
-      }
+      for (int i = 0; i < 8; ++i)
+        if (!((m[u] >> i) & 1u)) fd[i] = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) o[i] = k0[i] * (fd[i] - k1[i] - (fx[i] - mean[i]) * rstd[i] * k2[i]);
       *reinterpret_cast<uint4*>(p.dx + idx * 8) = pack8(o);
@@ -371,29 +377,30 @@ bool BnShapeSupported(long long R, int C) {
   return R > 0 && C >= 8 && C <= kMaxC && (C % 8) == 0 && (kThreads % CG) == 0;
 }
 
-cudaError_t LaunchBnForward(const void* x, const void* residual, void* y, float* sums, const void* gamma, const void* beta,
+cudaError_t LaunchBnForward(const void* x, const void* residual, void* y, void* mask, float* sums, const void* gamma, const void* beta,
                             float* running_mean, float* running_var, float* save_mean, float* save_rstd, long long R,
                             int C, float eps, float momentum, int relu, int param_bf16, cudaStream_t stream) {
-  if (!BnShapeSupported(R, C)) return cudaErrorInvalidValue;
+  if (!BnShapeSupported(R, C) || (relu && mask == nullptr)) return cudaErrorInvalidValue;
   bn_stats_kernel<<<ReduceGrid(R, C), kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), R, C, sums);
   CountKernelLaunch();
   BnApplyParams p{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
-                  static_cast<__nv_bfloat16*>(y), sums, gamma, beta, running_mean, running_var, save_mean, save_rstd,
+                  static_cast<__nv_bfloat16*>(y), static_cast<unsigned char*>(mask), sums, gamma, beta, running_mean,
+                  running_var, save_mean, save_rstd,
                   R, C, relu, param_bf16, eps, momentum};
   bn_apply_kernel<<<ApplyGrid(R, C), kThreads, 0, stream>>>(p);
   CountKernelLaunch();
   return cudaGetLastError();
 }
 
-cudaError_t LaunchBnBackward(const void* dy, const void* y, const void* x, void* dx, void* dres, float* sums,
+cudaError_t LaunchBnBackward(const void* dy, const void* mask, const void* x, void* dx, void* dres, float* sums,
                              const float* save_mean, const float* save_rstd, const void* gamma, void* dgamma,
                              void* dbeta, long long R, int C, int relu, int param_bf16, cudaStream_t stream) {
-  if (!BnShapeSupported(R, C)) return cudaErrorInvalidValue;
+  if (!BnShapeSupported(R, C) || (relu && mask == nullptr)) return cudaErrorInvalidValue;
   bn_bwd_reduce_kernel<<<ReduceGrid(R, C), kThreads, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(x),
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const unsigned char*>(mask), static_cast<const __nv_bfloat16*>(x),
       save_mean, save_rstd, R, C, relu, sums);
   CountKernelLaunch();
-  BnBwdApplyParams p{static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(y),
+  BnBwdApplyParams p{static_cast<const __nv_bfloat16*>(dy), static_cast<const unsigned char*>(mask),
                      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(dx),
                      static_cast<__nv_bfloat16*>(dres), sums, save_mean, save_rstd, gamma, dgamma, dbeta, R, C, relu,
                      param_bf16};

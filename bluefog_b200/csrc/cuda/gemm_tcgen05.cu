@@ -89,6 +89,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// TMA store of a [rows x 64] bf16 box (128-byte swizzle) from shared memory; completion is tracked by bulk groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// at most N committed groups may still be reading their shared-memory source
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes,
 // 8-row groups 1024 bytes apart (SBO), descriptor version 1 (Blackwell).
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
@@ -265,6 +279,11 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // double-buffered in tensor memory (2 x BN_ columns) so that the epilogue of tile i runs while
 // the MMAs of tile i+1 are issued.  Ring-stage and accumulator hand-over use four kinds of
 // mbarriers: full/empty per smem stage, acc_full/acc_empty per accumulator buffer.
+// The epilogue leaves through shared memory: every epilogue warp converts [32 rows x 64 columns]
+// of its accumulator quarter to bf16, writes them in the 128-byte-swizzle layout and hands the box
+// to a TMA store (two boxes per warp in flight), so global memory sees full 128-byte rows and the
+// tile edges are clipped by the tensor map.  Row pitches that TMA cannot address (N % 8 != 0)
+// take the direct-store epilogue.
 // ------------------------------------------------------------------------------------------ //
 template <int BN_>
 struct PersistentCfg {
@@ -273,22 +292,27 @@ struct PersistentCfg {
   static constexpr uint32_t kBytesB = BN_ * BK * 2;
   static constexpr uint32_t kBytesStage = kBytesA + kBytesB;
   static constexpr uint32_t kCols = 2 * BN_;
-  static constexpr size_t kSmem = 1024 + size_t(kStagesP) * kBytesStage + 256;
+  // output staging: per epilogue warp two [32 rows x 64 columns] bf16 boxes (4 KiB each, 1024-byte aligned)
+  static constexpr uint32_t kBytesOutBox = 32 * 64 * 2;
+  static constexpr uint32_t kBytesOut = 4 * 2 * kBytesOutBox;
+  static constexpr size_t kSmem = 1024 + size_t(kStagesP) * kBytesStage + kBytesOut + 256;
   static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN_ >> 3) << 17) | (uint32_t(BM >> 4) << 24);
 };
 
 template <int BN_>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                               __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ bias, int M, int N,
-                               int K, int act, unsigned int* __restrict__ status) {
+                               const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ out,
+                               const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int act, int tma_out,
+                               unsigned int* __restrict__ status) {
   using Cfg = PersistentCfg<BN_>;
   constexpr int S = Cfg::kStagesP;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* stage_a = smem;
   unsigned char* stage_b = smem + size_t(S) * Cfg::kBytesA;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(S) * Cfg::kBytesStage);
+  unsigned char* stage_out = smem + size_t(S) * Cfg::kBytesStage;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + Cfg::kBytesOut);
   // bars[0..S): full, [S..2S): empty, [2S..2S+2): acc_full, [2S+2..2S+4): acc_empty
   __shared__ uint32_t tmem_base_s;
   __shared__ int failed_s;
@@ -376,7 +400,9 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
   } else {
     const int q = warp & 3;
     const bool vec_ok = (N % 8) == 0;
+    unsigned char* my_out = stage_out + size_t(q) * 2 * Cfg::kBytesOutBox;
     int local = 0;
+    int boxes = 0;                       // TMA stores issued by this warp
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int acc = local & 1;
       const int m0 = (tile / tiles_n) * BM;
@@ -384,34 +410,77 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
       if (!mbar_wait(smem_u32(&bars[2 * S + acc]), (local >> 1) & 1, failed)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m = m0 + q * 32 + lane;
+      if (tma_out) {
 #pragma unroll 1
-      for (int c = 0; c < BN_ / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN_ + c * 32), r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int nbase = n0 + c * 32;
-        if (m < M && nbase < N) {
-          __nv_bfloat16* dst = out + size_t(m) * N + nbase;
+        for (int c = 0; c < BN_ / 64; ++c) {
+          const int nbase = n0 + c * 64;
+          if (nbase >= N || m0 + q * 32 >= M) break;           // warp-uniform
+          uint32_t r[64];
+          const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN_ + c * 64);
+          tmem_ld32(taddr, r);
+          tmem_ld32(taddr + 32, r + 32);
+          // the box written two stores ago must have been read out of shared memory
+          if (lane == 0) tma_store_wait_read<1>();
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          __syncwarp();
+          unsigned char* box = my_out + size_t(boxes & 1) * Cfg::kBytesOutBox;
+          unsigned char* row = box + lane * 128;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int n = nbase + j * 8;
+          for (int j = 0; j < 8; ++j) {
             float v[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               float x = __uint_as_float(r[j * 8 + i]);
-              if (bias != nullptr && n + i < N) x += __bfloat162float(bias[n + i]);
+              if (bias != nullptr) {
+                const int n = nbase + j * 8 + i;
+                x += n < N ? __bfloat162float(bias[n]) : 0.f;
+              }
               v[i] = act_fn(x, act);
             }
-            if (vec_ok && n + 8 <= N) {
-              uint4 pk;
-              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+            uint4 pk;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-              for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-              *reinterpret_cast<uint4*>(dst + j * 8) = pk;
-            } else {
+            for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = pk;      // 128-byte swizzle
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&map_c, smem_u32(box), nbase, m0 + q * 32);
+            tma_store_commit();
+          }
+          ++boxes;
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN_ / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN_ + c * 32), r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const int nbase = n0 + c * 32;
+          if (m < M && nbase < N) {
+            __nv_bfloat16* dst = out + size_t(m) * N + nbase;
 #pragma unroll
-              for (int i = 0; i < 8; ++i)
-                if (n + i < N) dst[j * 8 + i] = __float2bfloat16_rn(v[i]);
+            for (int j = 0; j < 4; ++j) {
+              const int n = nbase + j * 8;
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float x = __uint_as_float(r[j * 8 + i]);
+                if (bias != nullptr && n + i < N) x += __bfloat162float(bias[n + i]);
+                v[i] = act_fn(x, act);
+              }
+              if (vec_ok && n + 8 <= N) {
+                uint4 pk;
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                *reinterpret_cast<uint4*>(dst + j * 8) = pk;
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  if (n + i < N) dst[j * 8 + i] = __float2bfloat16_rn(v[i]);
+              }
             }
           }
         }
@@ -421,6 +490,8 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars[2 * S + 2 + acc])) : "memory");
     }
+    // the stores of this warp must be complete before its shared memory goes away
+    if (lane == 0) tma_store_wait_all();
   }
   if (warp == 0 && lane == 0 && *failed) {
     const int first = armed > S ? armed - S : 0;
@@ -488,7 +559,12 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
   }
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
   const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_c;
+  const int tma_out = (N % 8) == 0 ? 1 : 0;        // TMA needs a 16-byte row pitch
+  if (variant != 0) {
+    // output boxes of [32 rows x 64 columns]; without a usable pitch the map is a valid dummy over A
+    if (!(tma_out ? MakeMap(&map_c, out, M, N, 32) : MakeMap(&map_c, a, M, K, 32))) return cudaErrorInvalidValue;
+  }
   if (variant == 0) {
     if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, BN)) return cudaErrorInvalidValue;
     static bool attr_set = false;
@@ -510,7 +586,7 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
     }
     const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
     gemm_bf16_nt_persistent_kernel<256><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
-        map_a, map_b, o, bp, M, N, K, act, status);
+        map_a, map_b, map_c, o, bp, M, N, K, act, tma_out, status);
   } else {
     using Cfg = PersistentCfg<128>;
     if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, 128)) return cudaErrorInvalidValue;
@@ -522,7 +598,7 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
     }
     const int tiles = ((M + BM - 1) / BM) * ((N + 127) / 128);
     gemm_bf16_nt_persistent_kernel<128><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
-        map_a, map_b, o, bp, M, N, K, act, status);
+        map_a, map_b, map_c, o, bp, M, N, K, act, tma_out, status);
   }
   CountKernelLaunch();
   return cudaGetLastError();

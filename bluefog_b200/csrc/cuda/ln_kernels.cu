@@ -1,0 +1,246 @@
+// LayerNorm over the last dimension of a bf16 [R, C] matrix, forward and backward.
+//
+//   forward:  y = (x - mean_r) * rstd_r * gamma + beta          (statistics in fp32, saved per row)
+//   backward: g = dy * gamma;  dx = rstd_r * (g - mean_c(g) - xhat * mean_c(g * xhat))
+//             dgamma = sum_r dy * xhat;  dbeta = sum_r dy
+//
+// One warp owns one row at a time and keeps the whole row in registers (C <= 2048: at most eight
+// 16-byte vectors per lane), so x is read once in the forward pass and x, dy once in the backward
+// pass.  The column sums of the backward pass stay in registers while a warp walks over its rows
+// and are folded through shared memory into fp32 atomics once per block.
+//
+// The reference ships no normalisation kernels (its examples call torch.nn layers); this is the
+// LayerNorm of the GPT-2 model of this library.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "comm_kernels.h"
+#include "ln_kernels.h"
+
+namespace bfb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxC = 2048;
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ void load_param8(const void* p, int c0, int is_bf16, float* f) {
+  if (is_bf16) {
+    unpack8(*reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p) + c0), f);
+  } else {
+    const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(p) + c0);
+    const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(p) + c0 + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(kThreads) ln_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const void* __restrict__ gamma,
+                                                          const void* __restrict__ beta,
+                                                          __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
+                                                          float* __restrict__ rstd_out, long long R, int C, float eps,
+                                                          int param_bf16) {
+  const int lane = threadIdx.x & 31;
+  const int CG = C >> 3;
+  const long long warp0 = (long long)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * kWarps;
+  const float inv_c = 1.f / (float)C;
+  for (long long r = warp0; r < R; r += nwarps) {
+    const __nv_bfloat16* xr = x + r * C;
+    float f[NV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int g = lane + 32 * v;
+      if (g < CG) {
+        unpack8(*reinterpret_cast<const uint4*>(xr + g * 8), f[v]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += f[v][i];
+      }
+    }
+    const float mean = warp_sum(s) * inv_c;
+    float q = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      if (lane + 32 * v < CG) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float d = f[v][i] - mean;
+          q += d * d;
+        }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(q) * inv_c + eps);
+    if (lane == 0) {
+      mean_out[r] = mean;
+      rstd_out[r] = rstd;
+    }
+    __nv_bfloat16* yr = y + r * C;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int g = lane + 32 * v;
+      if (g < CG) {
+        float ga[8], be[8], o[8];
+        load_param8(gamma, g * 8, param_bf16, ga);
+        load_param8(beta, g * 8, param_bf16, be);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = (f[v][i] - mean) * rstd * ga[i] + be[i];
+        *reinterpret_cast<uint4*>(yr + g * 8) = pack8(o);
+      }
+    }
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(kThreads) ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                          const __nv_bfloat16* __restrict__ x,
+                                                          const void* __restrict__ gamma,
+                                                          const float* __restrict__ mean_in,
+                                                          const float* __restrict__ rstd_in,
+                                                          __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
+                                                          float* __restrict__ dbeta, long long R, int C,
+                                                          int param_bf16) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int CG = C >> 3;
+  const long long warp0 = (long long)blockIdx.x * kWarps + warp;
+  const long long nwarps = (long long)gridDim.x * kWarps;
+  const float inv_c = 1.f / (float)C;
+  float ga[NV][8], sg[NV][8], sb[NV][8];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int g = lane + 32 * v;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ga[v][i] = sg[v][i] = sb[v][i] = 0.f;
+    if (g < CG) load_param8(gamma, g * 8, param_bf16, ga[v]);
+  }
+  for (long long r = warp0; r < R; r += nwarps) {
+    const float mean = mean_in[r], rstd = rstd_in[r];
+    float fd[NV][8], xh[NV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int g = lane + 32 * v;
+      if (g < CG) {
+        unpack8(*reinterpret_cast<const uint4*>(dy + r * C + g * 8), fd[v]);
+        unpack8(*reinterpret_cast<const uint4*>(x + r * C + g * 8), xh[v]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[v][i] = (xh[v][i] - mean) * rstd;
+          sg[v][i] += fd[v][i] * xh[v][i];
+          sb[v][i] += fd[v][i];
+          fd[v][i] *= ga[v][i];
+          s1 += fd[v][i];
+          s2 += fd[v][i] * xh[v][i];
+        }
+      }
+    }
+    s1 = warp_sum(s1) * inv_c;
+    s2 = warp_sum(s2) * inv_c;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int g = lane + 32 * v;
+      if (g < CG) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (fd[v][i] - s1 - xh[v][i] * s2);
+        *reinterpret_cast<uint4*>(dx + r * C + g * 8) = pack8(o);
+      }
+    }
+  }
+  // column sums: the warps of a block fold one vector slot (256 columns) at a time through shared
+  // memory, then the block adds each column once to the global fp32 sums
+  __shared__ float fold_g[32 * 8];
+  __shared__ float fold_b[32 * 8];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < 256; i += kThreads) fold_g[i] = fold_b[i] = 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      atomicAdd(&fold_g[lane * 8 + i], sg[v][i]);
+      atomicAdd(&fold_b[lane * 8 + i], sb[v][i]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 256; i += kThreads) {
+      const int c = (32 * v) * 8 + i;
+      if (c < C) {
+        atomicAdd(&dgamma[c], fold_g[i]);
+        atomicAdd(&dbeta[c], fold_b[i]);
+      }
+    }
+  }
+}
+
+int GridFor(long long R) {
+  long long blocks = (R + kWarps - 1) / kWarps;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  return (int)blocks;
+}
+
+}  // namespace
+
+bool LnShapeSupported(long long R, int C) { return R > 0 && C >= 8 && C <= kMaxC && (C % 8) == 0; }
+
+#define BFB_LN_DISPATCH(NVV, CALL)                 \
+  switch (NVV) {                                   \
+    case 1: { constexpr int NV = 1; CALL; } break; \
+    case 2: { constexpr int NV = 2; CALL; } break; \
+    case 3: { constexpr int NV = 3; CALL; } break; \
+    case 4: { constexpr int NV = 4; CALL; } break; \
+    case 5: { constexpr int NV = 5; CALL; } break; \
+    case 6: { constexpr int NV = 6; CALL; } break; \
+    case 7: { constexpr int NV = 7; CALL; } break; \
+    default: { constexpr int NV = 8; CALL; } break; \
+  }
+
+cudaError_t LaunchLnForward(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                            long long R, int C, float eps, int param_bf16, cudaStream_t stream) {
+  if (!LnShapeSupported(R, C)) return cudaErrorInvalidValue;
+  const int nv = ((C >> 3) + 31) / 32;
+  BFB_LN_DISPATCH(nv, (ln_fwd_kernel<NV><<<GridFor(R), kThreads, 0, stream>>>(
+                          static_cast<const __nv_bfloat16*>(x), gamma, beta, static_cast<__nv_bfloat16*>(y), mean,
+                          rstd, R, C, eps, param_bf16)));
+  CountKernelLaunch();
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchLnBackward(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                             void* dx, float* dgamma_zeroed, float* dbeta_zeroed, long long R, int C, int param_bf16,
+                             cudaStream_t stream) {
+  if (!LnShapeSupported(R, C)) return cudaErrorInvalidValue;
+  const int nv = ((C >> 3) + 31) / 32;
+  BFB_LN_DISPATCH(nv, (ln_bwd_kernel<NV><<<GridFor(R), kThreads, 0, stream>>>(
+                          static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), gamma, mean,
+                          rstd, static_cast<__nv_bfloat16*>(dx), dgamma_zeroed, dbeta_zeroed, R, C, param_bf16)));
+  CountKernelLaunch();
+  return cudaGetLastError();
+}
+
+}  // namespace bfb

@@ -1,0 +1,19 @@
+// LayerNorm forward/backward over the last dimension of a bf16 [R, C] matrix (see ln_kernels.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace bfb {
+
+// C % 8 == 0 and C <= 2048 (a warp keeps one row in registers).
+bool LnShapeSupported(long long R, int C);
+
+// gamma/beta: C values, fp32 or bf16 (param_bf16).  mean/rstd: R fp32 values each (written).
+cudaError_t LaunchLnForward(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                            long long R, int C, float eps, int param_bf16, cudaStream_t stream);
+
+// dgamma_zeroed/dbeta_zeroed: C fp32 values each that hold zeros on entry; the kernel adds into them.
+cudaError_t LaunchLnBackward(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                             void* dx, float* dgamma_zeroed, float* dbeta_zeroed, long long R, int C, int param_bf16,
+                             cudaStream_t stream);
+
+}  // namespace bfb

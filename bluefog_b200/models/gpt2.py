@@ -3,14 +3,17 @@
 Used by the GPT-2-medium data-parallel workload (24 layers, d_model 1024, 16 heads, vocab
 50257, sequence 1024).  The reference has no transformer code; the library only needs a
 single-GPU model whose parameters the distributed optimizers average.  Linear layers run on
-the hand-written tcgen05 GEMM when the activations are bf16 (``use_b200_gemm``); attention
-uses PyTorch's fused scaled-dot-product attention.
+the hand-written tcgen05 GEMM when the activations are bf16 (``use_b200_gemm``), LayerNorm on the
+row-in-registers kernels of ``bluefog_b200.ops.fused_ln``; attention uses PyTorch's fused
+scaled-dot-product attention.
 """
 import math
 
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
+
+from bluefog_b200.ops.fused_ln import LayerNorm
 
 
 class B200Linear(nn.Linear):
@@ -58,9 +61,9 @@ class MLP(nn.Module):
 class Block(nn.Module):
     def __init__(self, d_model, n_head, use_b200_gemm):
         super().__init__()
-        self.ln_1 = nn.LayerNorm(d_model)
+        self.ln_1 = LayerNorm(d_model)
         self.attn = Attention(d_model, n_head, use_b200_gemm)
-        self.ln_2 = nn.LayerNorm(d_model)
+        self.ln_2 = LayerNorm(d_model)
         self.mlp = MLP(d_model, use_b200_gemm)
 
     def forward(self, x):
@@ -75,7 +78,7 @@ class GPT2(nn.Module):
         self.wte = nn.Embedding(vocab_size, d_model)
         self.wpe = nn.Embedding(n_positions, d_model)
         self.h = nn.ModuleList([Block(d_model, n_head, use_b200_gemm) for _ in range(n_layer)])
-        self.ln_f = nn.LayerNorm(d_model)
+        self.ln_f = LayerNorm(d_model)
         self.use_b200_gemm = use_b200_gemm
         self.apply(self._init)
         for name, p in self.named_parameters():

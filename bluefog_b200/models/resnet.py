@@ -62,6 +62,30 @@ class Conv1x1(nn.Conv2d):
         return super().forward(x)
 
 
+class StemConv(nn.Conv2d):
+    """The 7x7 / stride 2 / 3-channel stem convolution.  With ``space_to_depth`` it is evaluated as
+    the equivalent 4x4 / stride 1 convolution over 2x2 pixel blocks (12 channels, padded to 16):
+    three input channels leave tensor-core tiles almost empty, sixteen do not.  The parameter
+    keeps its [64, 3, 7, 7] shape; the rearrangement of the (tiny) weight is part of the graph."""
+
+    def __init__(self, space_to_depth=False):
+        super().__init__(3, 64, kernel_size=7, stride=2, padding=3, bias=False)
+        self.space_to_depth = space_to_depth
+
+    def forward(self, x):
+        n, c, h, w = x.shape
+        if not (self.space_to_depth and x.is_cuda and h % 2 == 0 and w % 2 == 0):
+            return super().forward(x)
+        w8 = F.pad(self.weight, (0, 1, 0, 1))
+        w12 = w8.view(64, 3, 4, 2, 4, 2).permute(0, 1, 3, 5, 2, 4).reshape(64, 12, 4, 4)
+        w16 = F.pad(w12, (0, 0, 0, 0, 0, 4)).contiguous(memory_format=torch.channels_last)
+        hb, wb = (h + 6) // 2, (w + 6) // 2
+        xp = F.pad(x, (3, 3, 3, 3))
+        xs = xp.reshape(n, 3, hb, 2, wb, 2).permute(0, 1, 3, 5, 2, 4).reshape(n, 12, hb, wb)
+        xs = F.pad(xs, (0, 0, 0, 0, 0, 4)).contiguous(memory_format=torch.channels_last)
+        return F.conv2d(xs, w16)
+
+
 class Downsample(nn.Sequential):
     """1x1 convolution + BatchNorm on the shortcut (children named "0" and "1" as in torchvision)."""
 
@@ -117,11 +141,11 @@ class Bottleneck(nn.Module):
 
 class ResNet(nn.Module):
     def __init__(self, block: Type[nn.Module], layers: List[int], num_classes: int = 1000,
-                 use_b200_gemm: bool = False, zero_init_residual: bool = False):
+                 use_b200_gemm: bool = False, zero_init_residual: bool = False, stem_space_to_depth: bool = False):
         super().__init__()
         self.inplanes = 64
         self.use_b200_gemm = use_b200_gemm
-        self.conv1 = nn.Conv2d(3, 64, kernel_size=7, stride=2, padding=3, bias=False)
+        self.conv1 = StemConv(space_to_depth=stem_space_to_depth)
         self.bn1 = MixedBatchNorm2d(64)
         self.relu = nn.ReLU(inplace=True)
         self.maxpool = nn.MaxPool2d(kernel_size=3, stride=2, padding=1)

@@ -73,9 +73,10 @@ class _BnActFn(torch.autograd.Function):
     def forward(ctx, x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu):
         c2 = 2 * x.shape[1]
         fwd_sums, _, _ = _take(x.device, c2)
-        y, mean, rstd = _b.native.bn_forward(x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu,
-                                             fwd_sums)
-        ctx.save_for_backward(x, y, mean, rstd, gamma)
+        y, mean, rstd, mask = _b.native.bn_forward(x, residual, gamma, beta, running_mean, running_var, eps, momentum,
+                                                   relu, fwd_sums)
+        # backward needs x, the statistics and one bit per element for the ReLU; not y itself
+        ctx.save_for_backward(x, mask, mean, rstd, gamma)
         ctx.relu = relu
         ctx.has_res = residual is not None
         ctx.bwd_sums, ctx.bwd_gen, ctx.ws = _take(x.device, c2)   # reserved now, consumed by backward
@@ -83,12 +84,12 @@ class _BnActFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x, y, mean, rstd, gamma = ctx.saved_tensors
+        x, mask, mean, rstd, gamma = ctx.saved_tensors
         dy = dy.contiguous(memory_format=torch.channels_last)
         sums = None
         if ctx.bwd_sums is not None and ctx.ws.generation == ctx.bwd_gen:
             sums, ctx.bwd_sums = ctx.bwd_sums, None    # a slice is clean only once
-        dx, dres, dgamma, dbeta = _b.native.bn_backward(dy, y, x, mean, rstd, gamma, ctx.relu, ctx.has_res, sums)
+        dx, dres, dgamma, dbeta = _b.native.bn_backward(dy, mask, x, mean, rstd, gamma, ctx.relu, ctx.has_res, sums)
         return dx, (dres if ctx.has_res else None), dgamma, dbeta, None, None, None, None, None
 
 

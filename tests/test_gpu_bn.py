@@ -48,7 +48,7 @@ def _case(N, C, H, W, relu, with_res, param_dtype):
         assert bad <= outliers, (err.max().item(), bound, bad)
 
     close(y, y2, 2e-2)
-    # the ReLU mask of the kernel comes from its own bf16 output; compare gradients where both agree
+    # the kernel's ReLU bits come from its own fp32 value of bf16 inputs; compare gradients where both agree
     close(x1.grad, x2.grad, 4e-2, outliers=1e-4 if relu else 0.0)
     if with_res:
         close(r1.grad, r2.grad, 2e-2, outliers=1e-4 if relu else 0.0)

@@ -17,7 +17,8 @@ def _ref(a, w, bias, act):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 512), (256, 384, 1024), (200, 136, 72),
-                                   (1, 1000, 2048), (3136, 64, 256), (4096, 4096, 1024), (777, 50264, 64)])
+                                   (1, 1000, 2048), (3136, 64, 256), (4096, 4096, 1024), (777, 50264, 64),
+                                   (130, 100, 64), (20000, 256, 64), (12544, 1000, 256)])
 @pytest.mark.parametrize("with_bias,act", [(False, 0), (True, 1), (True, 2)])
 def test_gemm_matches_fp32_reference(M, N, K, with_bias, act):
     from bluefog_b200 import _C

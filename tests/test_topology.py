@@ -95,3 +95,4 @@ def test_machine_and_inner_outer_generators():
                 assert rounds[send[0]][1] == [r], (gen_fn.__name__, r, rounds)
     with pytest.raises(AssertionError):
         next(tu.GetInnerOuterRingDynamicSendRecvRanks(8, 2, 0))
+

@@ -37,6 +37,8 @@ def parse_args():
     ap.add_argument("--model", default="resnet50")
     ap.add_argument("--b200-gemm", action="store_true",
                     help="route 1x1 convolutions and the classifier through the tcgen05 GEMM")
+    ap.add_argument("--b200-conv", action="store_true",
+                    help="route stride-1 3x3 convolutions through the tcgen05 implicit-GEMM kernel")
     ap.add_argument("--no-graphs", action="store_true", help="drive forward/backward op by op instead of a CUDA graph")
     ap.add_argument("--stem-s2d", action="store_true", help="space-to-depth evaluation of the 7x7 stem convolution")
     ap.add_argument("--exchange-dtype", default="float32", choices=["float32", "bfloat16"])
@@ -95,9 +97,9 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def build_model(name, use_gemm, stem_s2d=False):
+def build_model(name, use_gemm, stem_s2d=False, use_conv=False):
     from bluefog_b200.models import resnet
-    return getattr(resnet, name)(use_b200_gemm=use_gemm, stem_space_to_depth=stem_s2d)
+    return getattr(resnet, name)(use_b200_gemm=use_gemm, stem_space_to_depth=stem_s2d, use_b200_conv=use_conv)
 
 
 def one_peer_schedule(bf, size, rank):
@@ -116,7 +118,7 @@ def run_ours(args):
     dev = torch.device("cuda", torch.cuda.current_device())
     bf.set_topology(bf.ExponentialTwoGraph(size))
     torch.manual_seed(1234 + rank)
-    model = build_model(args.model, args.b200_gemm, args.stem_s2d).to(dev).to(memory_format=torch.channels_last)
+    model = build_model(args.model, args.b200_gemm, args.stem_s2d, args.b200_conv).to(dev).to(memory_format=torch.channels_last)
     bf.broadcast_parameters(model.state_dict(), root_rank=0)
     base = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
     opt = bf.DistributedNeighborAllreduceOptimizer(
@@ -231,6 +233,7 @@ def run_ours(args):
                        "parallelism": f"dp{size}", "optimizer": "SGD momentum 0.9 lr 0.1, fp32 master weights",
                        "topology": "ExponentialTwoGraph, dynamic one-peer", "exchange_dtype": args.exchange_dtype,
                        "b200_gemm": bool(args.b200_gemm and gemm.available()),
+                       "b200_conv": bool(args.b200_conv),
                        "stem": "space-to-depth 4x4" if args.stem_s2d else "7x7 stride 2",
                        "cuda_graph": "forward+backward" if not args.no_graphs else "none",
                        "l2": "inputs plus activations exceed the 126 MB L2 every step; no explicit flush"},

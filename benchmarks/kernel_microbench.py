@@ -106,6 +106,18 @@ def bench_gemm(args):
             "library_ms": ms_lib, "library_tflops": flops / ms_lib / 1e9, "status": _C.gemm_status()}
 
 
+def bench_conv(args):
+    n, cin, cout, h, w = args.conv_shape
+    x = torch.randn(n, cin, h, w, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    wt = (torch.randn(cout, cin, 3, 3, device="cuda") * 0.05).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    ms = timed(lambda: _C.conv3x3_nhwc(x, wt), args.iters, args.warmup)
+    ms_lib = timed(lambda: torch.nn.functional.conv2d(x, wt, padding=1), args.iters, args.warmup)
+    flops = 2.0 * n * h * w * cout * cin * 9
+    return {"kernel": "conv3x3_nhwc_kernel (tcgen05 implicit GEMM)", "shape": [n, cin, cout, h, w], "ms": ms,
+            "tflops": flops / ms / 1e9, "frac_of_measured_bf16": flops / ms / 1e9 / PEAKS["bf16_tflops"],
+            "library_ms": ms_lib, "library_tflops": flops / ms_lib / 1e9, "status": _C.gemm_status()}
+
+
 def bench_bn(args):
     n, c, h, w = args.bn_shape
     x = torch.randn(n, c, h, w, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
@@ -132,7 +144,8 @@ def bench_bn(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", required=True, choices=["bucket", "combine", "gemm", "bn"])
+    ap.add_argument("--kernel", required=True, choices=["bucket", "combine", "gemm", "bn", "conv"])
+    ap.add_argument("--conv-shape", type=int, nargs=5, default=[64, 64, 64, 56, 56], metavar=("N", "CIN", "COUT", "H", "W"))
     ap.add_argument("--bn-shape", type=int, nargs=4, default=[64, 256, 56, 56])
     ap.add_argument("--numel", type=int, default=64 * 1024 * 1024)
     ap.add_argument("--dtype", default="float32")
@@ -144,7 +157,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
     torch.cuda.set_device(0)
-    out = {"bucket": bench_bucket, "combine": bench_combine, "gemm": bench_gemm, "bn": bench_bn}[args.kernel](args)
+    out = {"bucket": bench_bucket, "combine": bench_combine, "gemm": bench_gemm, "bn": bench_bn, "conv": bench_conv}[args.kernel](args)
     print(json.dumps(out), flush=True)
 
 

@@ -12,6 +12,7 @@
 #include "common/windows.h"
 #include "cuda/bn_kernels.h"
 #include "cuda/bucket.h"
+#include "cuda/conv_tcgen05.h"
 #include "cuda/gemm_tcgen05.h"
 #include "cuda/gpu_channel.h"
 #include "cuda/ln_kernels.h"
@@ -453,6 +454,29 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(e == cudaSuccess, "gemm_bf16_nt launch failed: ", cudaGetErrorString(e));
     return out;
   }, py::arg("a"), py::arg("w"), py::arg("bias") = py::none(), py::arg("act") = 0);
+
+  // ---- tcgen05 implicit-GEMM 3x3 convolution (stride 1, pad 1), NHWC bf16 ---------------------
+  m.def("conv3x3_supported", [](int64_t n, int64_t h, int64_t w, int64_t cin, int64_t cout) {
+    return Conv3x3Supported(static_cast<int>(n), static_cast<int>(h), static_cast<int>(w), static_cast<int>(cin),
+                            static_cast<int>(cout));
+  });
+  m.def("conv3x3_nhwc", [](at::Tensor x, at::Tensor w) {
+    TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 4 && w.dim() == 4 && x.scalar_type() == at::kBFloat16 &&
+                w.scalar_type() == at::kBFloat16, "conv3x3_nhwc expects 4-D bf16 CUDA tensors");
+    TORCH_CHECK(x.is_contiguous(at::MemoryFormat::ChannelsLast) && w.is_contiguous(at::MemoryFormat::ChannelsLast),
+                "conv3x3_nhwc expects channels_last input and filter");
+    TORCH_CHECK(w.size(2) == 3 && w.size(3) == 3 && w.size(1) == x.size(1), "conv3x3_nhwc expects a [Cout, Cin, 3, 3] filter");
+    const int N = static_cast<int>(x.size(0)), Cin = static_cast<int>(x.size(1)), H = static_cast<int>(x.size(2)),
+              W = static_cast<int>(x.size(3)), Cout = static_cast<int>(w.size(0));
+    TORCH_CHECK(Conv3x3Supported(N, H, W, Cin, Cout), "conv3x3_nhwc: unsupported shape");
+    c10::cuda::CUDAGuard g(x.get_device());
+    at::Tensor& status = GemmStatusWord(x);
+    at::Tensor y = at::empty({N, Cout, H, W}, x.options().memory_format(at::MemoryFormat::ChannelsLast));
+    cudaError_t e = LaunchConv3x3Nhwc(x.data_ptr(), w.data_ptr(), y.data_ptr(), N, H, W, Cin, Cout,
+                                      reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(x.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "conv3x3_nhwc launch failed: ", cudaGetErrorString(e));
+    return y;
+  });
 
   m.def("gemm_status", [] {
     at::Tensor probe = at::empty({0}, at::TensorOptions().device(at::kCUDA));

@@ -1,0 +1,18 @@
+// 3x3 / stride 1 / pad 1 convolution of NHWC bf16 tensors as an implicit GEMM on tcgen05 (see conv_tcgen05.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace bfb {
+
+// Patch of output pixels one CTA owns: bn images x bh rows x bw columns, at most 128 pixels. False when W > 128.
+bool Conv3x3Patch(int N, int H, int W, int* bw, int* bh, int* bn);
+
+// Cin a multiple of 64, Cout a multiple of 8 and at least 64, W <= 128, TMA descriptors available.
+bool Conv3x3Supported(int N, int H, int W, int Cin, int Cout);
+
+// y[N,H,W,Cout] = conv3x3(x[N,H,W,Cin], w[Cout,3,3,Cin]), all bf16, dense, 16-byte aligned bases.
+// status: device word set to 1 when a bounded wait inside the kernel expired (may be null).
+cudaError_t LaunchConv3x3Nhwc(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout,
+                              unsigned int* status, cudaStream_t stream);
+
+}  // namespace bfb

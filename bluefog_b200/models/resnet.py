@@ -6,7 +6,8 @@ v1.5: stride on the 3x3 convolution of a bottleneck) in a form that suits a B200
 activations are NHWC (channels_last), parameters may be bf16 views of an fp32 master
 bucket, BatchNorm statistics stay fp32, and the 1x1 convolutions and the classifier, which
 are plain GEMMs in NHWC, can run on the hand-written tcgen05 GEMM
-(``bluefog_b200.ops.gemm``) when ``use_b200_gemm`` is set.
+(``bluefog_b200.ops.gemm``) when ``use_b200_gemm`` is set; the stride-1 3x3 convolutions can run as
+implicit GEMMs on the tcgen05 kernel of ``bluefog_b200.ops.conv`` when ``use_b200_conv`` is set.
 """
 from typing import List, Optional, Type
 
@@ -96,19 +97,34 @@ class Downsample(nn.Sequential):
         return bn_act(self[0](x), self[1], relu=False)
 
 
-def conv3x3(cin, cout, stride=1):
-    return nn.Conv2d(cin, cout, kernel_size=3, stride=stride, padding=1, bias=False)
+class Conv3x3(nn.Conv2d):
+    """3x3 convolution; with stride 1 and ``use_b200_conv`` it runs as an implicit GEMM on the tcgen05
+    kernel of ``bluefog_b200.ops.conv`` (forward and input gradient), otherwise on the library."""
+
+    def __init__(self, cin, cout, stride=1, use_b200_conv=False):
+        super().__init__(cin, cout, kernel_size=3, stride=stride, padding=1, bias=False)
+        self.use_b200_conv = use_b200_conv and stride == 1
+
+    def forward(self, x):
+        if self.use_b200_conv and x.is_cuda and x.dtype == torch.bfloat16:
+            from bluefog_b200.ops import conv
+            return conv.conv3x3(x, self.weight)
+        return super().forward(x)
+
+
+def conv3x3(cin, cout, stride=1, use_b200_conv=False):
+    return Conv3x3(cin, cout, stride, use_b200_conv=use_b200_conv)
 
 
 class BasicBlock(nn.Module):
     expansion = 1
 
-    def __init__(self, inplanes, planes, stride=1, downsample=None, use_b200_gemm=False):
+    def __init__(self, inplanes, planes, stride=1, downsample=None, use_b200_gemm=False, use_b200_conv=False):
         super().__init__()
-        self.conv1 = conv3x3(inplanes, planes, stride)
+        self.conv1 = conv3x3(inplanes, planes, stride, use_b200_conv)
         self.bn1 = MixedBatchNorm2d(planes)
         self.relu = nn.ReLU(inplace=True)
-        self.conv2 = conv3x3(planes, planes)
+        self.conv2 = conv3x3(planes, planes, 1, use_b200_conv)
         self.bn2 = MixedBatchNorm2d(planes)
         self.downsample = downsample
 
@@ -121,11 +137,11 @@ class BasicBlock(nn.Module):
 class Bottleneck(nn.Module):
     expansion = 4
 
-    def __init__(self, inplanes, planes, stride=1, downsample=None, use_b200_gemm=False):
+    def __init__(self, inplanes, planes, stride=1, downsample=None, use_b200_gemm=False, use_b200_conv=False):
         super().__init__()
         self.conv1 = Conv1x1(inplanes, planes, use_b200_gemm=use_b200_gemm)
         self.bn1 = MixedBatchNorm2d(planes)
-        self.conv2 = conv3x3(planes, planes, stride)
+        self.conv2 = conv3x3(planes, planes, stride, use_b200_conv)
         self.bn2 = MixedBatchNorm2d(planes)
         self.conv3 = Conv1x1(planes, planes * 4, use_b200_gemm=use_b200_gemm)
         self.bn3 = MixedBatchNorm2d(planes * 4)
@@ -141,10 +157,12 @@ class Bottleneck(nn.Module):
 
 class ResNet(nn.Module):
     def __init__(self, block: Type[nn.Module], layers: List[int], num_classes: int = 1000,
-                 use_b200_gemm: bool = False, zero_init_residual: bool = False, stem_space_to_depth: bool = False):
+                 use_b200_gemm: bool = False, zero_init_residual: bool = False, stem_space_to_depth: bool = False,
+                 use_b200_conv: bool = False):
         super().__init__()
         self.inplanes = 64
         self.use_b200_gemm = use_b200_gemm
+        self.use_b200_conv = use_b200_conv
         self.conv1 = StemConv(space_to_depth=stem_space_to_depth)
         self.bn1 = MixedBatchNorm2d(64)
         self.relu = nn.ReLU(inplace=True)
@@ -175,10 +193,11 @@ class ResNet(nn.Module):
         downsample = None
         if stride != 1 or self.inplanes != planes * block.expansion:
             downsample = Downsample(self.inplanes, planes * block.expansion, stride, self.use_b200_gemm)
-        layers = [block(self.inplanes, planes, stride, downsample, use_b200_gemm=self.use_b200_gemm)]
+        kw = dict(use_b200_gemm=self.use_b200_gemm, use_b200_conv=self.use_b200_conv)
+        layers = [block(self.inplanes, planes, stride, downsample, **kw)]
         self.inplanes = planes * block.expansion
         for _ in range(1, blocks):
-            layers.append(block(self.inplanes, planes, use_b200_gemm=self.use_b200_gemm))
+            layers.append(block(self.inplanes, planes, **kw))
         return nn.Sequential(*layers)
 
     def forward(self, x):

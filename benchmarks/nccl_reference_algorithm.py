@@ -55,7 +55,7 @@ def neighbor_average_(params, send_to, recv_from, fusion, recv_fusion):
         off = 0
         for p in group:                       # MemcpyInFusionBuffer: one copy per tensor
             n = p.numel()
-            fusion[off:off + n].copy_(p.data.view(-1))
+            fusion[off:off + n].copy_(p.data.reshape(-1))
             off += n
         ops = []
         for j, r in enumerate(recv_from):

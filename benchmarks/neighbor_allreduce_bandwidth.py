@@ -59,9 +59,13 @@ def main():
     nccl = None
     if not args.skip_nccl and size > 1:
         import torch.distributed as dist
-        port = int(os.environ.get("MASTER_PORT", "29500")) + 7
-        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=size,
-                                device_id=dev)
+        if os.environ.get("TORCHELASTIC_USE_AGENT_STORE", "False") == "True":
+            # under torchrun every rank is a client of the agent's store at MASTER_PORT
+            dist.init_process_group("nccl", init_method="env://", rank=rank, world_size=size, device_id=dev)
+        else:
+            port = int(os.environ.get("MASTER_PORT", "29500")) + 7
+            dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=size,
+                                    device_id=dev)
         nccl = dist
     results = []
     sizes = []

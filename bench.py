@@ -40,7 +40,8 @@ def parse_args():
     ap.add_argument("--b200-conv", action="store_true",
                     help="route stride-1 3x3 convolutions through the tcgen05 implicit-GEMM kernel")
     ap.add_argument("--no-graphs", action="store_true", help="drive forward/backward op by op instead of a CUDA graph")
-    ap.add_argument("--stem-s2d", action="store_true", help="space-to-depth evaluation of the 7x7 stem convolution")
+    ap.add_argument("--stem", default="s2d", choices=["s2d", "7x7"],
+                    help="evaluate the 7x7/2 stem convolution as a 4x4 convolution over 2x2 pixel blocks (s2d) or directly")
     ap.add_argument("--exchange-dtype", default="float32", choices=["float32", "bfloat16"])
     return ap.parse_args()
 
@@ -118,7 +119,7 @@ def run_ours(args):
     dev = torch.device("cuda", torch.cuda.current_device())
     bf.set_topology(bf.ExponentialTwoGraph(size))
     torch.manual_seed(1234 + rank)
-    model = build_model(args.model, args.b200_gemm, args.stem_s2d, args.b200_conv).to(dev).to(memory_format=torch.channels_last)
+    model = build_model(args.model, args.b200_gemm, (args.stem == "s2d"), args.b200_conv).to(dev).to(memory_format=torch.channels_last)
     bf.broadcast_parameters(model.state_dict(), root_rank=0)
     base = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
     opt = bf.DistributedNeighborAllreduceOptimizer(
@@ -234,7 +235,7 @@ def run_ours(args):
                        "topology": "ExponentialTwoGraph, dynamic one-peer", "exchange_dtype": args.exchange_dtype,
                        "b200_gemm": bool(args.b200_gemm and gemm.available()),
                        "b200_conv": bool(args.b200_conv),
-                       "stem": "space-to-depth 4x4" if args.stem_s2d else "7x7 stride 2",
+                       "stem": "space-to-depth 4x4" if (args.stem == "s2d") else "7x7 stride 2",
                        "cuda_graph": "forward+backward" if not args.no_graphs else "none",
                        "l2": "inputs plus activations exceed the 126 MB L2 every step; no explicit flush"},
             "clocks": clocks,

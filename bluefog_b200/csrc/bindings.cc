@@ -460,7 +460,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return Conv3x3Supported(static_cast<int>(n), static_cast<int>(h), static_cast<int>(w), static_cast<int>(cin),
                             static_cast<int>(cout));
   });
-  m.def("conv3x3_nhwc", [](at::Tensor x, at::Tensor w) {
+  m.def("conv3x3_nhwc", [](at::Tensor x, at::Tensor w, bool flip_taps) {
     TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 4 && w.dim() == 4 && x.scalar_type() == at::kBFloat16 &&
                 w.scalar_type() == at::kBFloat16, "conv3x3_nhwc expects 4-D bf16 CUDA tensors");
     TORCH_CHECK(x.is_contiguous(at::MemoryFormat::ChannelsLast) && w.is_contiguous(at::MemoryFormat::ChannelsLast),
@@ -472,11 +472,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     c10::cuda::CUDAGuard g(x.get_device());
     at::Tensor& status = GemmStatusWord(x);
     at::Tensor y = at::empty({N, Cout, H, W}, x.options().memory_format(at::MemoryFormat::ChannelsLast));
-    cudaError_t e = LaunchConv3x3Nhwc(x.data_ptr(), w.data_ptr(), y.data_ptr(), N, H, W, Cin, Cout,
+    cudaError_t e = LaunchConv3x3Nhwc(x.data_ptr(), w.data_ptr(), y.data_ptr(), N, H, W, Cin, Cout, flip_taps ? 1 : 0,
                                       reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(x.get_device()));
     TORCH_CHECK(e == cudaSuccess, "conv3x3_nhwc launch failed: ", cudaGetErrorString(e));
     return y;
-  });
+  }, py::arg("x"), py::arg("w"), py::arg("flip_taps") = false);
 
   m.def("gemm_status", [] {
     at::Tensor probe = at::empty({0}, at::TensorOptions().device(at::kCUDA));

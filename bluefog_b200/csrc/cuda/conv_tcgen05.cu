@@ -2,6 +2,10 @@
 //
 //   y[n, h, w, co] = sum_{r, s, ci} x[n, h + r - 1, w + s - 1, ci] * wgt[co, r, s, ci]
 //
+// (with flip_taps the filter tap is (2 - r, 2 - s): the input gradient of such a convolution is the
+// same convolution of the output gradient with the filter rotated by 180 degrees and its channel
+// axes exchanged, so only the exchange of axes is left to the caller)
+//
 // The GEMM view is  M = output pixels, N = Cout, K = 9 * Cin,  and no im2col matrix is ever
 // written: one CTA owns a patch of  bn images x bh rows x bw columns  (at most 128 pixels, the M
 // extent of one tcgen05.mma), and for every filter tap (r, s) and every 64-channel slice the
@@ -56,6 +60,7 @@ struct ConvGeom {
   int N, H, W, Cin, Cout;
   int bw, bh, bn;            // patch extent (bw * bh * bn <= 128)
   int tiles_w, tiles_h, tiles_img, tiles_co;
+  int flip_taps;             // 1: input tap (r, s) meets filter tap (2 - r, 2 - s) (input-gradient form)
 };
 
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -134,7 +139,8 @@ conv3x3_nhwc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           const uint32_t full = smem_u32(&bars[s]);
           mbar_expect_tx(full, bytes_a + Cfg::kBytesB);
           tma_load_4d(smem_u32(stage_a + size_t(s) * Cfg::kBytesA), &map_x, full, ci0, w0 + sx - 1, h0 + r - 1, n0);
-          tma_load_2d(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), &map_w, full, tap * g.Cin + ci0, co0);
+          const int wtap = g.flip_taps ? 8 - tap : tap;
+          tma_load_2d(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), &map_w, full, wtap * g.Cin + ci0, co0);
           armed = it + 1;
         }
       }
@@ -316,21 +322,23 @@ bool Conv3x3Supported(int N, int H, int W, int Cin, int Cout) {
 }
 
 cudaError_t LaunchConv3x3Nhwc(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout,
-                              unsigned int* status, cudaStream_t stream) {
+                              int flip_taps, unsigned int* status, cudaStream_t stream) {
   if (!Conv3x3Supported(N, H, W, Cin, Cout)) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(y) & 15))
     return cudaErrorInvalidValue;
   ConvGeom g;
   g.N = N; g.H = H; g.W = W; g.Cin = Cin; g.Cout = Cout;
+  g.flip_taps = flip_taps ? 1 : 0;
   Conv3x3Patch(N, H, W, &g.bw, &g.bh, &g.bn);
   g.tiles_w = (W + g.bw - 1) / g.bw;
   g.tiles_h = (H + g.bh - 1) / g.bh;
   g.tiles_img = (N + g.bn - 1) / g.bn;
   const int spatial = g.tiles_w * g.tiles_h * g.tiles_img;
-  // widest N tile that still gives every SM a tile; narrow outputs take the narrow tile
+  // widest N tile that still occupies most of the SMs (a 256-wide tile streams half as many weight
+  // bytes per FLOP through shared memory); narrow outputs take the narrow tile
   int bn_tile = 256;
   if (Cout <= 64) bn_tile = 64;
-  else if (Cout <= 128 || spatial * ((Cout + 255) / 256) < SmCount()) bn_tile = 128;
+  else if (Cout <= 128 || spatial * ((Cout + 255) / 256) < (SmCount() * 3) / 4) bn_tile = 128;
   g.tiles_co = (Cout + bn_tile - 1) / bn_tile;
   CUtensorMap mx, mw, my;
   if (!MakeMap4d(&mx, x, Cin, W, H, N, g.bw, g.bh, g.bn) || !MakeMap2d(&mw, w, Cout, 9 * Cin, bn_tile) ||

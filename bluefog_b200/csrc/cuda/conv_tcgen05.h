@@ -11,8 +11,9 @@ bool Conv3x3Patch(int N, int H, int W, int* bw, int* bh, int* bn);
 bool Conv3x3Supported(int N, int H, int W, int Cin, int Cout);
 
 // y[N,H,W,Cout] = conv3x3(x[N,H,W,Cin], w[Cout,3,3,Cin]), all bf16, dense, 16-byte aligned bases.
+// flip_taps: use filter tap (2 - r, 2 - s) for input tap (r, s) (the 180-degree rotation of the input-gradient form).
 // status: device word set to 1 when a bounded wait inside the kernel expired (may be null).
 cudaError_t LaunchConv3x3Nhwc(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout,
-                              unsigned int* status, cudaStream_t stream);
+                              int flip_taps, unsigned int* status, cudaStream_t stream);
 
 }  // namespace bfb

@@ -43,23 +43,17 @@ class MixedBatchNorm2d(nn.BatchNorm2d):
 
 
 class Conv1x1(nn.Conv2d):
-    """1x1 convolution; in NHWC with stride 1 it is the GEMM [N*H*W, Cin] x [Cin, Cout]."""
+    """1x1 convolution; in NHWC with stride 1 it is the GEMM [N*H*W, Cin] x [Cin, Cout] (the strided
+    shortcut convolutions stay on the library)."""
 
     def __init__(self, cin, cout, stride=1, use_b200_gemm=False):
         super().__init__(cin, cout, kernel_size=1, stride=stride, bias=False)
         self.use_b200_gemm = use_b200_gemm
 
     def forward(self, x):
-        if (self.use_b200_gemm and x.is_cuda and x.dtype == torch.bfloat16
-                and x.is_contiguous(memory_format=torch.channels_last)):
+        if self.use_b200_gemm and self.stride[0] == 1 and x.is_cuda and x.dtype == torch.bfloat16:
             from bluefog_b200.ops import gemm
-            if gemm.available():
-                if self.stride[0] != 1:
-                    x = x[:, :, ::self.stride[0], ::self.stride[1]].contiguous(memory_format=torch.channels_last)
-                n, c, h, w = x.shape
-                a = x.permute(0, 2, 3, 1).reshape(n * h * w, c)
-                y = gemm.linear(a, self.weight.view(self.out_channels, c))
-                return y.view(n, h, w, self.out_channels).permute(0, 3, 1, 2)
+            return gemm.conv1x1(x, self.weight)
         return super().forward(x)
 
 
@@ -74,9 +68,13 @@ class StemConv(nn.Conv2d):
         self.space_to_depth = space_to_depth
 
     def forward(self, x):
+        h, w = x.shape[2:]
+        if self.space_to_depth and x.is_cuda and h % 2 == 0 and w % 2 == 0:
+            return self.forward_space_to_depth(x)
+        return super().forward(x)
+
+    def forward_space_to_depth(self, x):
         n, c, h, w = x.shape
-        if not (self.space_to_depth and x.is_cuda and h % 2 == 0 and w % 2 == 0):
-            return super().forward(x)
         w8 = F.pad(self.weight, (0, 1, 0, 1))
         w12 = w8.view(64, 3, 4, 2, 4, 2).permute(0, 1, 3, 5, 2, 4).reshape(64, 12, 4, 4)
         w16 = F.pad(w12, (0, 0, 0, 0, 0, 4)).contiguous(memory_format=torch.channels_last)
@@ -157,7 +155,7 @@ class Bottleneck(nn.Module):
 
 class ResNet(nn.Module):
     def __init__(self, block: Type[nn.Module], layers: List[int], num_classes: int = 1000,
-                 use_b200_gemm: bool = False, zero_init_residual: bool = False, stem_space_to_depth: bool = False,
+                 use_b200_gemm: bool = False, zero_init_residual: bool = False, stem_space_to_depth: bool = True,
                  use_b200_conv: bool = False):
         super().__init__()
         self.inplanes = 64

@@ -5,8 +5,8 @@
 ``Cout % 8 == 0``, ``Cout >= 64`` and ``W <= 128`` take ``csrc/cuda/conv_tcgen05.cu``:
 
 * forward:  the kernel on (x, weight);
-* input gradient: the same kernel on (dy, weight rotated by 180 degrees with its channel axes
-  swapped) — the transposed convolution of a stride-1 "same" convolution is again one;
+* input gradient: the same kernel on (dy, weight with its channel axes swapped), reading the filter
+  taps in reverse order — the transposed convolution of a stride-1 "same" convolution is again one;
 * filter gradient: reduces over every output pixel of the batch (a split-K problem with two
   pixel-major operands); it is left to the library (``aten::convolution_backward`` with only the
   weight mask set).
@@ -51,8 +51,9 @@ class _Conv3x3Fn(torch.autograd.Function):
         dy = dy.contiguous(memory_format=torch.channels_last)
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            wt = weight.flip(2, 3).transpose(0, 1).contiguous(memory_format=torch.channels_last)   # [Cin, Cout, 3, 3]
-            dx = _b.native.conv3x3_nhwc(dy, wt)
+            # [Cin, Cout, 3, 3]; the 180-degree rotation of the taps happens inside the kernel
+            wt = weight.transpose(0, 1).contiguous(memory_format=torch.channels_last)
+            dx = _b.native.conv3x3_nhwc(dy, wt, True)
         if ctx.needs_input_grad[1]:
             dw = torch.ops.aten.convolution_backward(dy, x, weight, None, (1, 1), (1, 1), (1, 1), False, (0, 0), 1,
                                                      (False, True, False))[1]

@@ -56,3 +56,44 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
     if a.shape[-1] % 8 != 0:
         return torch.nn.functional.linear(a, w, bias)
     return _LinearFn.apply(a.contiguous(), w.contiguous(), bias)
+
+
+class _Conv1x1Fn(torch.autograd.Function):
+    """Stride-1 1x1 convolution of channels_last activations: forward and input gradient are the GEMMs
+    [N*H*W, Cin] x [Cin, Cout] and [N*H*W, Cout] x [Cout, Cin] on the tcgen05 kernel; the filter
+    gradient (a reduction over all pixels) goes to the library's convolution backward."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        n, c, h, w = x.shape
+        cout = weight.shape[0]
+        ctx.save_for_backward(x, weight)
+        a = x.permute(0, 2, 3, 1).reshape(n * h * w, c)                  # a view of NHWC memory
+        y = _b.native.gemm_bf16_nt(a, weight.reshape(cout, c), None, 0)
+        return y.view(n, h, w, cout).permute(0, 3, 1, 2)                   # channels_last [N, Cout, H, W]
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        n, c, h, w = x.shape
+        cout = weight.shape[0]
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            d2 = dy.permute(0, 2, 3, 1).reshape(n * h * w, cout)
+            wt = weight.reshape(cout, c).t().contiguous()                  # [Cin, Cout]: K-major for the NT kernel
+            dx = _b.native.gemm_bf16_nt(d2, wt, None, 0).view(n, h, w, c).permute(0, 3, 1, 2)
+        if ctx.needs_input_grad[1]:
+            dw = torch.ops.aten.convolution_backward(dy, x, weight, None, (1, 1), (0, 0), (1, 1), False, (0, 0), 1,
+                                                     (False, True, False))[1]
+        return dx, dw
+
+
+def conv1x1(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``F.conv2d(x, weight)`` for a [Cout, Cin, 1, 1] filter and stride 1.  bf16 channels_last CUDA
+    activations with Cin % 8 == 0 and Cout % 8 == 0 take the tcgen05 GEMM, the rest the library."""
+    if (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 4
+            and x.shape[1] % 8 == 0 and weight.shape[0] % 8 == 0 and x.numel() > 0
+            and x.is_contiguous(memory_format=torch.channels_last) and available()):
+        return _Conv1x1Fn.apply(x, weight)
+    return torch.nn.functional.conv2d(x, weight)

@@ -50,6 +50,12 @@ def supported(optimizer, model, communication_type) -> bool:
     return True
 
 
+def _same_layout(a, b):
+    """True when both tensors order their elements identically in memory (strides of extent-1
+    dimensions carry no information and are ignored)."""
+    return all(sa == sb for sa, sb, n in zip(a.stride(), b.stride(), a.shape) if n > 1)
+
+
 class _BucketState:
     """Buffers and metadata of one bucket."""
 
@@ -63,6 +69,7 @@ class _BucketState:
             n += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
         self.offsets = offsets
         self.numel = n
+        self.strides = [self._dense_strides(p) for p in params]   # taken before the parameters are re-homed
         self.master = torch.zeros(n, dtype=torch.float32, device=device)
         # gradients stay where autograd puts them; the kernel reads them through a pointer table
         self.seg_start = torch.tensor(offsets, dtype=torch.int64, device=device)
@@ -83,9 +90,22 @@ class _BucketState:
         self.first_step = True    # SGD momentum buffer not initialised yet
         self.native = _b.native.Bucket.create(n, "bfloat16" if pub_dtype == torch.bfloat16 else "float32")
 
+    @staticmethod
+    def _dense_strides(p):
+        """Strides the bucket keeps for ``p``: channels_last filters stay channels_last (the
+        convolution kernels then read them in place instead of re-laying them out every step);
+        everything else is stored row-major."""
+        if p.dim() == 4 and not p.is_contiguous() and p.is_contiguous(memory_format=torch.channels_last):
+            return tuple(p.stride())
+        strides, n = [], 1
+        for d in reversed(p.shape):
+            strides.append(n)
+            n *= d
+        return tuple(reversed(strides))
+
     def view(self, flat, i):
         p = self.params[i]
-        return flat[self.offsets[i]:self.offsets[i] + p.numel()].view(p.shape)
+        return flat.as_strided(p.shape, self.strides[i], self.offsets[i])
 
 
 class _FusedMixin:
@@ -216,8 +236,11 @@ class _FusedMixin:
             if g is None:
                 key.append(0)
                 continue
-            if g.dtype != want or not g.is_contiguous():
-                g = g.to(want).contiguous()
+            if g.dtype != want or not _same_layout(g, p):
+                # the kernel walks gradient and master in memory order: both must share one layout
+                fixed = torch.empty_strided(p.shape, p.stride(), dtype=want, device=g.device)
+                fixed.copy_(g)
+                g = fixed
                 p.grad = g
             key.append(g.data_ptr())
         key = tuple(key)

@@ -52,3 +52,30 @@ def test_linear_autograd_matches_torch():
     for got, ref in ((y, y2), (a.grad, a2.grad), (w.grad, w2.grad), (b.grad, b2.grad)):
         err = (got.float() - ref).abs().max().item()
         assert err <= 2e-2 * ref.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("n,cin,cout,h,w", [(4, 64, 256, 56, 56), (3, 1024, 256, 14, 14), (2, 72, 40, 9, 7)])
+def test_conv1x1_autograd_matches_fp32(n, cin, cout, h, w):
+    import torch.nn.functional as F
+    from bluefog_b200 import _C
+    from bluefog_b200.ops import gemm
+    torch.manual_seed(cin + cout)
+    x = torch.randn(n, cin, h, w, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    wt = (torch.randn(cout, cin, 1, 1, device="cuda") / cin ** 0.5).to(torch.bfloat16)
+    dy = torch.randn(n, cout, h, w, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    x1, w1 = x.clone().requires_grad_(True), wt.clone().requires_grad_(True)
+    y1 = gemm.conv1x1(x1, w1)
+    assert y1.is_contiguous(memory_format=torch.channels_last)
+    y1.backward(dy)
+    x2, w2 = x.float().requires_grad_(True), wt.float().requires_grad_(True)
+    y2 = F.conv2d(x2, w2)
+    y2.backward(dy.float())
+
+    def close(a, ref, tol):
+        err = (a.float() - ref).abs().max().item()
+        assert err <= tol * max(1.0, ref.abs().max().item()), err
+
+    close(y1, y2, 1e-2)
+    close(x1.grad, x2.grad, 1e-2)
+    close(w1.grad, w2.grad, 2e-2)
+    assert _C.gemm_status() == 0

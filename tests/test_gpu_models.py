@@ -92,3 +92,78 @@ def test_graphed_forward_backward_matches_eager(bf):
         l1 = graphed(x, y)
         opts[1].step()
         assert abs(l0.item() - l1.item()) < 1e-3
+
+
+def test_space_to_depth_stem_matches_direct_convolution_on_gpu():
+    from bluefog_b200.models.resnet import StemConv
+    torch.manual_seed(3)
+    conv = StemConv(space_to_depth=True).cuda().to(torch.bfloat16)
+    x = torch.randn(4, 3, 64, 64, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    y = conv(x)                                         # 4x4 convolution over 2x2 pixel blocks
+    ref = torch.nn.Conv2d.forward(conv.float(), x.float())
+    assert y.shape == ref.shape
+    assert (y.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_bottleneck_with_tcgen05_convolutions_matches_library_path():
+    """Training-mode forward/backward of one bottleneck block with its 1x1 and 3x3 convolutions on the
+    tcgen05 kernels against the same weights on the library kernels."""
+    from bluefog_b200.models import resnet
+    from bluefog_b200.ops import conv, gemm
+    if not (gemm.available() and conv.available()):
+        pytest.fail("tcgen05 kernels are not available on this GPU")
+    torch.manual_seed(5)
+    a = resnet.Bottleneck(256, 64, use_b200_gemm=True, use_b200_conv=True).cuda()
+    b = resnet.Bottleneck(256, 64).cuda()
+    b.load_state_dict(a.state_dict())
+    for m in (a, b):
+        for p in m.parameters():                      # bf16 parameters, fp32 BatchNorm statistics
+            p.data = p.data.to(torch.bfloat16)
+    a, b = a.to(memory_format=torch.channels_last), b.to(memory_format=torch.channels_last)
+    x = torch.randn(8, 256, 28, 28, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    ya, yb = a(xa), b(xb)
+    dy = torch.randn_like(ya)
+    ya.backward(dy)
+    yb.backward(dy)
+
+    def rel(u, v):
+        return ((u.float() - v.float()).norm() / v.float().norm().clamp_min(1e-6)).item()
+
+    assert rel(ya, yb) < 2e-2
+    assert rel(xa.grad, xb.grad) < 3e-2
+    for (name, pa), (_, pb) in zip(a.named_parameters(), b.named_parameters()):
+        assert rel(pa.grad, pb.grad) < 5e-2, name
+
+
+def test_fused_sgd_keeps_channels_last_filters_and_matches_torch_sgd(bf):
+    """Channels_last filters stay channels_last inside the bucket (no per-step re-layout), gradients are
+    read in the same memory order, and the result equals torch.optim.SGD on the same model."""
+    torch.manual_seed(11)
+    dev = torch.device("cuda", 0)
+
+    def make():
+        return torch.nn.Sequential(torch.nn.Conv2d(8, 16, 3, padding=1), torch.nn.ReLU(),
+                                   torch.nn.Conv2d(16, 16, 1), torch.nn.ReLU(),
+                                   torch.nn.AdaptiveAvgPool2d(1), torch.nn.Flatten(), torch.nn.Linear(16, 4))
+
+    m1, m2 = make().to(dev), make().to(dev)
+    m2.load_state_dict(m1.state_dict())
+    m1, m2 = m1.to(memory_format=torch.channels_last), m2.to(memory_format=torch.channels_last)
+    o1 = torch.optim.SGD(m1.parameters(), lr=0.1, momentum=0.9)
+    o2 = bf.DistributedNeighborAllreduceOptimizer(torch.optim.SGD(m2.parameters(), lr=0.1, momentum=0.9), m2)
+    w = m2[0].weight
+    assert w.is_contiguous(memory_format=torch.channels_last) and not w.is_contiguous()
+    x = torch.randn(4, 8, 12, 12, device=dev).contiguous(memory_format=torch.channels_last)
+    y = torch.randint(0, 4, (4,), device=dev)
+    for _ in range(3):
+        for m, o in ((m1, o1), (m2, o2)):
+            o.zero_grad()
+            torch.nn.functional.cross_entropy(m(x), y).backward()
+            o.step()
+    torch.cuda.synchronize()
+    o2.check()
+    for (n1, p1), (_, p2) in zip(m1.named_parameters(), m2.named_parameters()):
+        assert torch.allclose(p1, p2, rtol=1e-4, atol=1e-5), n1
+    masters = o2.master_parameters()
+    assert torch.allclose(masters["0.weight"], m1[0].weight, rtol=1e-4, atol=1e-5)

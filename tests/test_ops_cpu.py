@@ -8,3 +8,23 @@ def test_layer_norm_cpu_fallback_matches_torch():
     x = torch.randn(3, 5, 24)
     torch.testing.assert_close(ln(x), F.layer_norm(x, (24,), ln.weight, ln.bias, ln.eps))
     torch.testing.assert_close(layer_norm(x, None, None), F.layer_norm(x, (24,)))
+
+
+def test_space_to_depth_stem_equals_the_7x7_convolution():
+    import torch
+    from bluefog_b200.models.resnet import StemConv
+    torch.manual_seed(0)
+    conv = StemConv(space_to_depth=True).double()
+    x = torch.randn(2, 3, 32, 48, dtype=torch.float64)
+    torch.testing.assert_close(conv.forward_space_to_depth(x), torch.nn.Conv2d.forward(conv, x), rtol=1e-10, atol=1e-10)
+
+
+def test_conv_ops_fall_back_on_cpu():
+    import torch
+    import torch.nn.functional as F
+    from bluefog_b200.ops import conv, gemm
+    x = torch.randn(2, 16, 6, 6)
+    w3 = torch.randn(8, 16, 3, 3)
+    w1 = torch.randn(8, 16, 1, 1)
+    torch.testing.assert_close(conv.conv3x3(x, w3), F.conv2d(x, w3, padding=1))
+    torch.testing.assert_close(gemm.conv1x1(x, w1), F.conv2d(x, w1))

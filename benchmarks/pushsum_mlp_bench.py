@@ -57,8 +57,9 @@ def main():
         steps += 1
     elapsed = time.time() - t_start
     bf.barrier()
-    counts = bf.allgather(torch.tensor([float(steps)], dtype=torch.float64)).tolist()
-    losses = bf.allgather(torch.tensor([loss.item()], dtype=torch.float64)).tolist()
+    # ranks ran different numbers of operations, so unnamed ops would carry different handle numbers
+    counts = bf.allgather(torch.tensor([float(steps)], dtype=torch.float64), name="pushsum.counts").tolist()
+    losses = bf.allgather(torch.tensor([loss.item()], dtype=torch.float64), name="pushsum.losses").tolist()
     if rank == 0:
         print(json.dumps({"metric": "push-sum MLP steps/s (sum over ranks)", "value": round(sum(counts) / elapsed, 2),
                           "unit": "steps/s", "n_gpus": size, "steps_per_rank": counts, "final_losses": losses,

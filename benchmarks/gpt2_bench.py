@@ -27,6 +27,7 @@ def main():
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--model", default="gpt2_medium", choices=["gpt2_small", "gpt2_medium"])
     ap.add_argument("--no-b200-gemm", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true", help="drive forward/backward op by op instead of a CUDA graph")
     args = ap.parse_args()
     bf.init()
     rank, size = bf.rank(), bf.size()
@@ -42,12 +43,21 @@ def main():
     tokens = torch.randint(0, 50257, (args.batch, args.seq + 1), generator=g).to(dev)
     x, y = tokens[:, :-1].contiguous(), tokens[:, 1:].contiguous()
 
-    def step():
-        opt.zero_grad()
-        loss = model(x, y)
-        loss.backward()
-        opt.step()
-        return loss
+    if args.no_graphs:
+        def step():
+            opt.zero_grad()
+            loss = model(x, y)
+            loss.backward()
+            opt.step()
+            return loss
+    else:
+        from bluefog_b200.utils.graphs import GraphedForwardBackward
+        graphed = GraphedForwardBackward(model, None, opt, x, y, forward_loss=model)
+
+        def step():
+            loss = graphed(x, y)
+            opt.step()
+            return loss
 
     for _ in range(args.warmup):
         step()

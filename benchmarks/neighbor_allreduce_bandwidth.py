@@ -42,6 +42,24 @@ def device_time_ms(fn, iters, warmup):
     return float(bf.allgather(ms).max())
 
 
+def pipelined_time_ms(issue, iters, warmup):
+    """Issues ``iters`` nonblocking operations back to back and waits for all of them; the closing
+    event is recorded after the last handle completed, so the figure can only err on the slow side."""
+    for h in [issue(k) for k in range(warmup)]:
+        bf.synchronize(h)
+    torch.cuda.synchronize()
+    bf.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    handles = [issue(k) for k in range(iters)]
+    outs = [bf.synchronize(h) for h in handles]
+    e1.record()
+    torch.cuda.synchronize()
+    del outs
+    ms = e0.elapsed_time(e1) / iters
+    return float(bf.allgather(torch.tensor([ms], dtype=torch.float64)).max())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--min-bytes", type=int, default=4096)
@@ -90,12 +108,27 @@ def main():
                     return bf.neighbor_allreduce(x, self_weight=w, src_weights={r: w for r in recv},
                                                  dst_weights=send, enable_topo_check=False, name="bw")
 
+                def ours_nonblocking(k):
+                    if mode == "static_exp2":
+                        return bf.neighbor_allreduce_nonblocking(x, name=f"bw.nb.{k}")
+                    send, recv = next(gen)
+                    w = 1.0 / (len(recv) + 1)
+                    return bf.neighbor_allreduce_nonblocking(x, self_weight=w, src_weights={r: w for r in recv},
+                                                             dst_weights=send, enable_topo_check=False,
+                                                             name=f"bw.nb.{k}")
+
                 indeg = len(in_nb) if mode == "static_exp2" else 1
                 ms = device_time_ms(ours, args.iters, args.warmup)
                 row = {"op": "neighbor_allreduce", "impl": "ours", "dtype": str(dtype).split(".")[-1], "bytes": nbytes,
                        "mode": mode, "ms": ms, "gbs": indeg * nbytes / ms / 1e6,
                        "roofline_frac": indeg * nbytes / ms / 1e6 / NVLINK_GBS}
                 results.append(row)
+                # the same operations issued back to back through the nonblocking API and waited for at the
+                # end, which is how the NCCL arm below runs (its wait() only orders streams)
+                ms_nb = pipelined_time_ms(ours_nonblocking, args.iters, args.warmup)
+                results.append({"op": "neighbor_allreduce", "impl": "ours-nonblocking", "dtype": row["dtype"],
+                                "bytes": nbytes, "mode": mode, "ms": ms_nb, "gbs": indeg * nbytes / ms_nb / 1e6,
+                                "roofline_frac": indeg * nbytes / ms_nb / 1e6 / NVLINK_GBS})
                 if nccl is not None:
                     recv_bufs = [torch.empty_like(x) for _ in range(len(in_nb))]
                     gen2 = tu.GetDynamicOnePeerSendRecvRanks(bf.load_topology(), rank)

@@ -179,7 +179,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("kernel_launch_count", [] { return KernelLaunchCount(); });
 
   // ---- operations --------------------------------------------------------------------------
-  m.def("enqueue", [](OpSpec spec) { return Runtime::Get().Enqueue(std::move(spec)); });
+  m.def("enqueue", [](OpSpec spec) {
+    py::gil_scoped_release nogil;   // a GPU collective may be issued right here, on the calling thread
+    return Runtime::Get().Enqueue(std::move(spec));
+  });
   m.def("poll", [](int h) { return Runtime::Get().Poll(h); });
   m.def("wait", [](int h) {
     Status s;

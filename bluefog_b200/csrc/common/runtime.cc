@@ -153,6 +153,7 @@ Status Runtime::Init(int rank, int size, int local_rank, int local_size,
   windows_ = std::make_unique<WindowManager>(&cp_, rank, size, tag);
   windows_->mutex_timeout_s = EnvDouble("BLUEFOG_B200_MUTEX_TIMEOUT_SECONDS", 120.0);
   finalizers_.create(static_cast<int>(EnvDouble("BLUEFOG_NUM_FINALIZER_THREADS", 1)));
+  inline_enabled_ = EnvDouble("BLUEFOG_B200_INLINE_OPS", 1.0) != 0.0;
   wake_fd_ = eventfd(0, EFD_NONBLOCK);
   shutdown_requested_.store(false);
   loop_exited_.store(false);
@@ -174,6 +175,16 @@ void Runtime::Wake() {
 
 void Runtime::Shutdown() {
   if (!initialized_.load()) return;
+  {
+    // fast-path operations nobody waited for: finish them before the channel goes away
+    std::vector<int> pending;
+    {
+      std::lock_guard<std::mutex> g(inline_mu_);
+      for (auto& kv : inline_ops_) pending.push_back(kv.first);
+    }
+    bool finished = false;
+    for (int h : pending) CompleteInline(h, /*block=*/true, &finished);
+  }
   shutdown_requested_.store(true);
   Wake();
   if (thread_.joinable()) thread_.join();
@@ -215,6 +226,8 @@ void Runtime::MarkDone(int handle, const Status& s) {
 }
 
 bool Runtime::Poll(int handle) {
+  bool finished = false;
+  CompleteInline(handle, /*block=*/false, &finished);   // no-op for handles of the queued path
   std::lock_guard<std::mutex> g(handle_mu_);
   auto it = handles_.find(handle);
   if (it == handles_.end()) return true;
@@ -222,6 +235,8 @@ bool Runtime::Poll(int handle) {
 }
 
 Status Runtime::Wait(int handle) {
+  bool finished = false;
+  CompleteInline(handle, /*block=*/true, &finished);
   std::unique_lock<std::mutex> lk(handle_mu_);
   auto it = handles_.find(handle);
   if (it == handles_.end()) return Status::InvalidArgument("unknown handle " + std::to_string(handle));
@@ -232,8 +247,103 @@ Status Runtime::Wait(int handle) {
 }
 
 void Runtime::Release(int handle) {
+  bool finished = false;
+  CompleteInline(handle, /*block=*/true, &finished);
   std::lock_guard<std::mutex> g(handle_mu_);
   handles_.erase(handle);
+}
+
+// ----------------------------------------------------------------------------------------
+// fast path: issue on the calling thread
+// ----------------------------------------------------------------------------------------
+thread_local bool Runtime::tls_inline_ = false;
+
+bool Runtime::InlineEligible(const OpSpec& spec) const {
+  if (!inline_enabled_ || device_ < 0) return false;
+  if (spec.negotiate && !skip_negotiate_.load() && size_ > 1) return false;
+  const OpType type = static_cast<OpType>(spec.type);
+  if (type != OpType::ALLREDUCE && type != OpType::BROADCAST && type != OpType::ALLGATHER &&
+      type != OpType::NEIGHBOR_ALLGATHER && type != OpType::NEIGHBOR_ALLREDUCE)
+    return false;
+  const at::Tensor* t = spec.input.has_value() ? &*spec.input : (spec.output.has_value() ? &*spec.output : nullptr);
+  return t != nullptr && t->is_cuda();
+}
+
+bool Runtime::TryRunInline(Entry& e) {
+  std::unique_lock<std::mutex> ex(exec_mu_, std::try_to_lock);
+  if (!ex.owns_lock()) return false;                 // the background loop is executing something
+  {
+    // anything queued or waiting for a response keeps its place in front of this operation
+    std::lock_guard<std::mutex> q(queue_mu_);
+    if (!queue_.empty()) return false;
+  }
+  {
+    std::lock_guard<std::mutex> t(table_mu_);
+    if (!table_.empty()) return false;
+  }
+  const std::string name = e.spec.name;
+  const int handle = e.handle;
+  {
+    std::lock_guard<std::mutex> g(inline_mu_);
+    if (inline_names_.count(name)) {
+      timeline_.ActivityEnd(name);
+      if (e.ready_event) cudaEventDestroy(static_cast<cudaEvent_t>(e.ready_event));
+      MarkDone(handle, Status::InvalidArgument(DuplicateNameError(name)));
+      return true;
+    }
+    inline_names_[name] = handle;
+  }
+  c10::cuda::CUDAGuard guard(device_);
+  Response r;
+  r.type = static_cast<OpType>(e.spec.type);
+  r.names = {name};
+  std::vector<Entry> entries;
+  entries.push_back(std::move(e));
+  tls_inline_ = true;
+  ExecuteEntries(entries, r);
+  tls_inline_ = false;
+  {
+    // finished on the spot (an error, or nothing left in flight): the name is free again
+    std::lock_guard<std::mutex> g(inline_mu_);
+    if (!inline_ops_.count(handle)) inline_names_.erase(name);
+  }
+  return true;
+}
+
+// Finishes a fast-path handle: waits for (block) or queries its completion event, turns a device-side
+// wait limit into an error, frees the events and records the final status.
+Status Runtime::CompleteInline(int handle, bool block, bool* finished) {
+  InlineOp op;
+  {
+    std::lock_guard<std::mutex> g(inline_mu_);
+    auto it = inline_ops_.find(handle);
+    if (it == inline_ops_.end()) {
+      *finished = true;
+      return Status::OK();
+    }
+    if (!block && cudaEventQuery(static_cast<cudaEvent_t>(it->second.done_event)) == cudaErrorNotReady) {
+      *finished = false;
+      return Status::OK();
+    }
+    op = std::move(it->second);
+    inline_ops_.erase(it);
+  }
+  cudaError_t err = cudaEventSynchronize(static_cast<cudaEvent_t>(op.done_event));
+  cudaEventDestroy(static_cast<cudaEvent_t>(op.done_event));
+  Status s = err == cudaSuccess ? Status::OK() : Status::UnknownError("CUDA error: " + CudaErrorString(err));
+  if (s.ok() && gpu_channel_) s = gpu_channel_->StatusToError();
+  for (auto& e : *op.keep) {
+    timeline_.ActivityEnd(e.spec.name);   // ENQUEUE_*
+    if (e.ready_event) cudaEventDestroy(static_cast<cudaEvent_t>(e.ready_event));
+    {
+      std::lock_guard<std::mutex> g(inline_mu_);
+      inline_names_.erase(e.spec.name);
+    }
+    MarkDone(e.handle, s);
+  }
+  op.keep->clear();
+  *finished = true;
+  return s;
 }
 
 int Runtime::Enqueue(OpSpec spec) {
@@ -265,6 +375,7 @@ int Runtime::Enqueue(OpSpec spec) {
   }
   timeline_.ActivityStart(spec.name, std::string("ENQUEUE_") + OpTypeName(static_cast<OpType>(spec.type)));
   e.spec = std::move(spec);
+  if (InlineEligible(e.spec) && TryRunInline(e)) return handle;
   {
     std::lock_guard<std::mutex> g(queue_mu_);
     queue_.push_back(std::move(e));
@@ -362,6 +473,7 @@ void Runtime::Loop() {
         r.type = static_cast<OpType>(table_[name].spec.type);
       }
       r.names = {name};
+      std::lock_guard<std::mutex> ex(exec_mu_);
       ExecuteResponse(r);
     }
     if (shutdown_requested_.load() && !shutdown_sent_) {
@@ -609,7 +721,10 @@ void Runtime::CheckStalled() {
 // execution
 // ----------------------------------------------------------------------------------------
 void Runtime::ExecuteResponseList(const ResponseList& list) {
-  for (const auto& r : list.responses) ExecuteResponse(r);
+  for (const auto& r : list.responses) {
+    std::lock_guard<std::mutex> ex(exec_mu_);   // callers on the fast path take the same lock
+    ExecuteResponse(r);
+  }
 }
 
 void Runtime::ExecuteResponse(const Response& resp) {
@@ -639,6 +754,16 @@ void Runtime::FinishEntries(std::vector<Entry>& entries, const Status& s, void* 
       if (e.ready_event) cudaEventDestroy(static_cast<cudaEvent_t>(e.ready_event));
       MarkDone(e.handle, s);
     }
+    return;
+  }
+  if (tls_inline_) {
+    // fast path: the caller's Wait/Poll finishes the handle, no thread hand-over
+    InlineOp op;
+    op.done_event = done_event;
+    op.keep = std::make_shared<std::vector<Entry>>(std::move(entries));
+    const int handle = (*op.keep)[0].handle;
+    std::lock_guard<std::mutex> g(inline_mu_);
+    inline_ops_[handle] = std::move(op);
     return;
   }
   // GPU work in flight: a finalizer thread waits for the completion event, converts a device

@@ -144,6 +144,11 @@ class Runtime {
   Status TopoCheck(const OpSpec& spec);
   Status EnsureGpuChannel(uint64_t need_bytes);
   void FinishEntries(std::vector<Entry>& entries, const Status& s, void* done_event);
+  // Fast path: a GPU collective that needs no negotiation and finds nothing queued is issued on the
+  // calling thread; its handle completes when the caller waits for (or polls) the completion event.
+  bool InlineEligible(const OpSpec& spec) const;
+  bool TryRunInline(Entry& e);
+  Status CompleteInline(int handle, bool block, bool* finished);
   void FailAll(const Status& s);
   void MarkDone(int handle, const Status& s);
   void CheckStalled();
@@ -172,6 +177,18 @@ class Runtime {
   std::condition_variable handle_cv_;
   std::unordered_map<int, Status> handles_;
   int next_handle_ = 0;
+
+  // operations issued on the caller's thread and not yet waited for
+  struct InlineOp {
+    void* done_event = nullptr;                       // cudaEvent_t
+    std::shared_ptr<std::vector<Entry>> keep;         // tensors stay alive until the kernels are done
+  };
+  std::mutex exec_mu_;                                // one executor at a time: background loop or a caller
+  std::mutex inline_mu_;
+  std::unordered_map<int, InlineOp> inline_ops_;      // by handle
+  std::unordered_map<std::string, int> inline_names_; // names in flight on the fast path
+  bool inline_enabled_ = true;
+  static thread_local bool tls_inline_;               // FinishEntries is running for the fast path
 
   // coordinator state (rank 0)
   std::map<std::string, PendingTensor> message_table_;

@@ -101,10 +101,27 @@ class GPT2(nn.Module):
         for block in self.h:
             x = block(x)
         x = self.ln_f(x)
-        logits = F.linear(x, self.wte.weight)     # tied output embedding
+        w = self.wte.weight                        # tied output embedding, [vocab, d_model]
+        vocab = w.shape[0]
+        pad = (-vocab) % 64 if x.is_cuda else 0
+        if pad:
+            # 50257 output columns make every GEMM of the classifier (forward, both gradients) run with
+            # odd leading dimensions; the product is taken against the matrix padded to a multiple of
+            # 64 rows and the surplus logits are set to -inf, which leaves loss and gradients unchanged
+            w = F.pad(w, (0, 0, 0, pad))
+        x2 = x.reshape(b * t, x.shape[-1])
+        logits = None
+        if self.use_b200_gemm and x2.is_cuda and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            from bluefog_b200.ops import gemm
+            if gemm.available():
+                logits = gemm.linear(x2, w)
+        if logits is None:
+            logits = F.linear(x2, w)
+        if pad:
+            logits[:, vocab:] = float("-inf")
         if targets is None:
-            return logits
-        return F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.view(-1))
+            return logits[:, :vocab].reshape(b, t, vocab)
+        return F.cross_entropy(logits.float(), targets.reshape(-1))
 
 
 def gpt2_small(**kw):

@@ -14,15 +14,19 @@ class GraphedForwardBackward:
     """Usage::
 
         step = GraphedForwardBackward(model, loss_fn, optimizer, example_x, example_y)
+        # or: GraphedForwardBackward(model, None, optimizer, tokens, targets, forward_loss=model)
         for x, y in loader:
             loss = step(x, y)        # copies x, y into the static buffers and replays the graph
             optimizer.step()
     """
 
-    def __init__(self, model, loss_fn, optimizer, example_x, example_y, warmup: int = 3):
+    def __init__(self, model, loss_fn, optimizer, example_x, example_y, warmup: int = 3, forward_loss=None):
+        """``forward_loss(x, y) -> loss`` replaces ``loss_fn(model(x).float(), y)`` for models that
+        compute their own loss (e.g. a language model called with targets)."""
         if not example_x.is_cuda:
             raise ValueError("CUDA graphs need CUDA tensors")
         self.model, self.loss_fn, self.optimizer = model, loss_fn, optimizer
+        self.forward_loss = forward_loss
         if hasattr(optimizer, "overlap_backward"):
             # bucket steps launched from backward hooks have per-step arguments: they cannot live in a graph
             optimizer.overlap_backward = False
@@ -47,8 +51,11 @@ class GraphedForwardBackward:
 
     def _eager(self):
         self.optimizer.zero_grad()
-        out = self.model(self.static_x)
-        loss = self.loss_fn(out.float(), self.static_y)
+        if self.forward_loss is not None:
+            loss = self.forward_loss(self.static_x, self.static_y)
+        else:
+            out = self.model(self.static_x)
+            loss = self.loss_fn(out.float(), self.static_y)
         loss.backward()
         return loss.detach()
 

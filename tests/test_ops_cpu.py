@@ -28,3 +28,19 @@ def test_conv_ops_fall_back_on_cpu():
     w1 = torch.randn(8, 16, 1, 1)
     torch.testing.assert_close(conv.conv3x3(x, w3), F.conv2d(x, w3, padding=1))
     torch.testing.assert_close(gemm.conv1x1(x, w1), F.conv2d(x, w1))
+
+
+def test_gpt2_small_config_runs_on_cpu_and_uses_hf_names():
+    import torch
+    from bluefog_b200.models import gpt2
+    torch.manual_seed(0)
+    m = gpt2.GPT2(vocab_size=101, n_positions=16, d_model=32, n_layer=2, n_head=2)
+    names = set(m.state_dict().keys())
+    assert {"wte.weight", "wpe.weight", "h.0.ln_1.weight", "h.0.attn.c_attn.weight", "h.0.attn.c_proj.bias",
+            "h.1.mlp.c_fc.weight", "h.1.mlp.c_proj.weight", "ln_f.bias"} <= names
+    x = torch.randint(0, 101, (2, 16))
+    y = torch.randint(0, 101, (2, 16))
+    assert m(x).shape == (2, 16, 101)
+    loss = m(x, y)
+    loss.backward()
+    assert torch.isfinite(loss) and m.wte.weight.grad.shape == (101, 32)

@@ -45,7 +45,8 @@ def device_time_ms(fn, iters, warmup):
 def pipelined_time_ms(issue, iters, warmup):
     """Issues ``iters`` nonblocking operations back to back and waits for all of them; the closing
     event is recorded after the last handle completed, so the figure can only err on the slow side."""
-    for h in [issue(k) for k in range(warmup)]:
+    # as many outputs alive at once as in the timed series, so that the allocator has settled
+    for h in [issue(k) for k in range(max(warmup, iters))]:
         bf.synchronize(h)
     torch.cuda.synchronize()
     bf.barrier()

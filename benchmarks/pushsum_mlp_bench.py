@@ -1,7 +1,7 @@
 """Asynchronous one-sided training: MLP regression with DistributedWinPutOptimizer.
 
 Config: 4 layers of 4096 hidden units, ReLU; batch 256 per GPU with x ~ N(0,1) of dim 4096 and
-y = x . w* + 0.01 noise (w* from seed 0); static ExponentialTwoGraph; win_put + win_update with
+y = x . w* + 0.01 noise (w* ~ N(0, 1/dim) from seed 0); static ExponentialTwoGraph; win_put + win_update with
 associated push-sum weights switched on; ranks run deliberately skewed numbers of steps per
 second (rank r sleeps r/(size-1) of a step time) to exercise the one-sided path, since no
 rank ever waits for another one.
@@ -33,7 +33,8 @@ def main():
     dev = torch.device("cuda", torch.cuda.current_device())
     bf.set_topology(bf.ExponentialTwoGraph(size))
     bf.turn_on_win_ops_with_associated_p()
-    w_star = torch.randn(args.dim, 1, generator=torch.Generator().manual_seed(0)).to(dev)
+    # w* ~ N(0, 1/dim): targets of unit variance keep plain SGD stable in bf16
+    w_star = (torch.randn(args.dim, 1, generator=torch.Generator().manual_seed(0)) / args.dim ** 0.5).to(dev)
     torch.manual_seed(1)
     model = MLP(args.dim, args.dim, 1, 4, use_b200_gemm=True).to(dev).to(torch.bfloat16)
     bf.broadcast_parameters(model.state_dict(), root_rank=0)

@@ -480,6 +480,64 @@ def gpu_fused_optimizers():
 
 
 @case
+def gpu_fast_path():
+    """Negotiation-free GPU collectives issued on the calling thread: blocking, nonblocking series, mixed
+    with queued operations, and large tensors right before small ones."""
+    r, n = bf.rank(), bf.size()
+    d = dev()
+    bf.set_topology(bf.RingGraph(n))
+    bf.set_skip_negotiate_stage(True)
+    nb = bf.in_neighbor_ranks()
+    w = 1.0 / (len(nb) + 1)
+    expect = w * (r + sum(nb))
+    # a series of nonblocking operations on the fast path, waited for at the end
+    xs = [torch.full((1000 + k,), float(r + k), device=d) for k in range(6)]
+    hs = [bf.neighbor_allreduce_nonblocking(x, name=f"series.{k}") for k, x in enumerate(xs)]
+    for k, h in enumerate(hs):
+        close(bf.synchronize(h), w * ((r + k) + sum(q + k for q in nb)), 1e-5)
+    # poll completes a fast-path handle as well
+    h = bf.allreduce_nonblocking(torch.full((64,), float(r), device=d), name="polled")
+    while not bf.poll(h):
+        pass
+    close(bf.synchronize(h), (n - 1) / 2, 1e-6)
+    # a duplicate name in flight is refused
+    big = torch.full((1 << 22,), 1.0, device=d)
+    h1 = bf.neighbor_allreduce_nonblocking(big, name="dup")
+    try:
+        bf.synchronize(bf.neighbor_allreduce_nonblocking(big, name="dup"))
+        raised = False
+    except ValueError:
+        raised = True
+    bf.synchronize(h1)
+    assert raised, "a second operation with a name that is still in flight must be refused"
+    bf.barrier()
+    # CPU operations take the queue; GPU operations issued after them keep their place behind them
+    c = bf.allreduce_nonblocking(torch.full((8,), float(r)), name="cpu.first")
+    g = bf.allreduce_nonblocking(torch.full((8,), float(r), device=d), name="gpu.second")
+    close(bf.synchronize(g), (n - 1) / 2, 1e-6)
+    close(bf.synchronize(c), (n - 1) / 2, 1e-6)
+    # 40 MiB + a ragged tail, fp32 and bf16, static and with explicit weights
+    numel = 10 * 1024 * 1024 + 12345
+    base = torch.arange(numel, device=d, dtype=torch.float32) % 7.0
+    x = base + r
+    out = bf.neighbor_allreduce(x, name="large.f32")
+    ref = w * (x + sum(base + q for q in nb))
+    assert torch.allclose(out, ref, atol=1e-5), (out[:4], ref[:4])
+    assert torch.allclose(out[-5:], ref[-5:], atol=1e-5)
+    xb = (base + r).to(torch.bfloat16).repeat(2)
+    outb = bf.neighbor_allreduce(xb, self_weight=0.5, src_weights={q: 0.5 / len(nb) for q in nb}, name="large.bf16")
+    refb = 0.5 * xb.float() + sum((0.5 / len(nb)) * (base + q).to(torch.bfloat16).repeat(2).float() for q in nb)
+    assert torch.allclose(outb.float(), refb, atol=0.1), (outb[:4], refb[:4])
+    # and a small operation right behind the large one
+    close(bf.neighbor_allreduce(torch.full((16,), float(r), device=d), name="after"), expect, 1e-5)
+    bf.barrier()
+    bf.set_skip_negotiate_stage(False)
+    # with negotiation the same large tensor goes through the queued path
+    out2 = bf.neighbor_allreduce(x, name="large.negotiated")
+    assert torch.allclose(out2, ref, atol=1e-5)
+
+
+@case
 def gpu_wait_timeout():
     """Rank 1 never issues the operation rank 0 is waiting for: rank 0's kernel gives up after
     the wait limit (set to 300 ms by the test) and the operation raises; nothing hangs."""

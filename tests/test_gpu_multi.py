@@ -17,13 +17,15 @@ def _need(n):
         pytest.skip(f"needs {n} GPUs")
 
 
-@pytest.mark.parametrize("case", ["collectives", "neighbor_ops", "windows", "optimizers", "gpu_fused_optimizers"])
+@pytest.mark.parametrize("case", ["collectives", "neighbor_ops", "windows", "optimizers", "gpu_fused_optimizers",
+                                  "gpu_fast_path"])
 def test_two_gpus(case):
     _need(2)
     run_ranks(case, 2, gpu=True, env=NVLS_OFF, timeout=600)
 
 
-@pytest.mark.parametrize("case", ["collectives", "neighbor_ops", "windows", "gpu_fused_optimizers"])
+@pytest.mark.parametrize("case", ["collectives", "neighbor_ops", "windows", "gpu_fused_optimizers",
+                                  "gpu_fast_path"])
 def test_four_gpus(case):
     _need(4)
     run_ranks(case, 4, gpu=True, env=NVLS_OFF, timeout=600)

@@ -329,6 +329,11 @@ Status Runtime::CompleteInline(int handle, bool block, bool* finished) {
     inline_ops_.erase(it);
   }
   cudaError_t err = cudaEventSynchronize(static_cast<cudaEvent_t>(op.done_event));
+  if (op.span_start) {
+    std::vector<std::string> names;
+    for (auto& e : *op.keep) names.push_back(e.spec.name);
+    EmitDeviceSpan(names, op.span_start, err == cudaSuccess ? op.done_event : nullptr);
+  }
   cudaEventDestroy(static_cast<cudaEvent_t>(op.done_event));
   Status s = err == cudaSuccess ? Status::OK() : Status::UnknownError("CUDA error: " + CudaErrorString(err));
   if (s.ok() && gpu_channel_) s = gpu_channel_->StatusToError();
@@ -746,9 +751,10 @@ void Runtime::ExecuteResponse(const Response& resp) {
   ExecuteEntries(entries, resp);
 }
 
-void Runtime::FinishEntries(std::vector<Entry>& entries, const Status& s, void* done_event) {
+void Runtime::FinishEntries(std::vector<Entry>& entries, const Status& s, void* done_event, void* span_start) {
   if (done_event == nullptr || !s.ok()) {
     if (done_event) cudaEventDestroy(static_cast<cudaEvent_t>(done_event));
+    if (span_start) cudaEventDestroy(static_cast<cudaEvent_t>(span_start));
     for (auto& e : entries) {
       timeline_.ActivityEnd(e.spec.name);  // ENQUEUE_*
       if (e.ready_event) cudaEventDestroy(static_cast<cudaEvent_t>(e.ready_event));
@@ -760,6 +766,7 @@ void Runtime::FinishEntries(std::vector<Entry>& entries, const Status& s, void* 
     // fast path: the caller's Wait/Poll finishes the handle, no thread hand-over
     InlineOp op;
     op.done_event = done_event;
+    op.span_start = span_start;
     op.keep = std::make_shared<std::vector<Entry>>(std::move(entries));
     const int handle = (*op.keep)[0].handle;
     std::lock_guard<std::mutex> g(inline_mu_);
@@ -780,9 +787,10 @@ void Runtime::FinishEntries(std::vector<Entry>& entries, const Status& s, void* 
   auto keep = std::make_shared<std::vector<Entry>>(std::move(entries));
   const int device = device_;
   Channel* chan = gpu_channel_.get();
-  finalizers_.execute([this, handles, names, ready, keep, done_event, device, chan] {
+  finalizers_.execute([this, handles, names, ready, keep, done_event, span_start, device, chan] {
     cudaSetDevice(device);
     cudaError_t err = cudaEventSynchronize(static_cast<cudaEvent_t>(done_event));
+    EmitDeviceSpan(names, span_start, err == cudaSuccess ? done_event : nullptr);
     cudaEventDestroy(static_cast<cudaEvent_t>(done_event));
     Status s = err == cudaSuccess ? Status::OK() : Status::UnknownError("CUDA error: " + CudaErrorString(err));
     if (s.ok() && chan != nullptr) s = chan->StatusToError();
@@ -863,11 +871,19 @@ void Runtime::ExecuteEntries(std::vector<Entry>& entries, const Response& resp) 
   const at::Tensor* probe = entries[0].spec.input.has_value() ? &*entries[0].spec.input : &*entries[0].spec.output;
   Status s;
   void* done = nullptr;
+  void* span_start = nullptr;
   if (probe->is_cuda()) {
+    const bool traced = timeline_.Initialized() && comm_stream_ != nullptr;
+    if (traced) {
+      cudaEvent_t t0;
+      cudaEventCreate(&t0);
+      cudaEventRecord(t0, static_cast<cudaStream_t>(comm_stream_));
+      span_start = t0;
+    }
     s = ExecuteGpu(entries, resp);
     if (s.ok()) {
       cudaEvent_t ev;
-      cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+      cudaEventCreateWithFlags(&ev, span_start ? cudaEventDefault : cudaEventDisableTiming);
       cudaEventRecord(ev, static_cast<cudaStream_t>(comm_stream_));
       done = ev;
     }
@@ -875,7 +891,19 @@ void Runtime::ExecuteEntries(std::vector<Entry>& entries, const Response& resp) 
     s = ExecuteCpu(entries, resp);
   }
   end_proc();
-  FinishEntries(entries, s, done);
+  FinishEntries(entries, s, done, span_start);
+}
+
+void Runtime::EmitDeviceSpan(const std::vector<std::string>& names, void* span_start, void* done_event) {
+  if (span_start == nullptr) return;
+  float ms = 0.f;
+  if (done_event != nullptr && timeline_.Initialized() &&
+      cudaEventElapsedTime(&ms, static_cast<cudaEvent_t>(span_start), static_cast<cudaEvent_t>(done_event)) == cudaSuccess) {
+    const long end_us = timeline_.NowMicros();
+    const long begin_us = end_us - static_cast<long>(ms * 1000.f);
+    for (const auto& n : names) timeline_.CompleteSpan(n, "DEVICE", begin_us, end_us, /*lane=*/1000000 + device_);
+  }
+  cudaEventDestroy(static_cast<cudaEvent_t>(span_start));
 }
 
 Status Runtime::ExecuteWindowOp(Entry& e) {

@@ -143,7 +143,10 @@ class Runtime {
   Status ExecuteWindowOp(Entry& e);
   Status TopoCheck(const OpSpec& spec);
   Status EnsureGpuChannel(uint64_t need_bytes);
-  void FinishEntries(std::vector<Entry>& entries, const Status& s, void* done_event);
+  void FinishEntries(std::vector<Entry>& entries, const Status& s, void* done_event, void* span_start = nullptr);
+  // With the timeline on, the device time between span_start and done_event becomes a "DEVICE" span of
+  // every tensor of the operation (drawn on its own lane, ending at the moment completion was observed).
+  void EmitDeviceSpan(const std::vector<std::string>& names, void* span_start, void* done_event);
   // Fast path: a GPU collective that needs no negotiation and finds nothing queued is issued on the
   // calling thread; its handle completes when the caller waits for (or polls) the completion event.
   bool InlineEligible(const OpSpec& spec) const;
@@ -181,6 +184,7 @@ class Runtime {
   // operations issued on the caller's thread and not yet waited for
   struct InlineOp {
     void* done_event = nullptr;                       // cudaEvent_t
+    void* span_start = nullptr;                       // cudaEvent_t, only with the timeline on
     std::shared_ptr<std::vector<Entry>> keep;         // tensors stay alive until the kernels are done
   };
   std::mutex exec_mu_;                                // one executor at a time: background loop or a caller

@@ -254,9 +254,12 @@ def _resolve_neighbor_weights(self_weight, src_weights, dst_weights):
             raise ValueError("Arguments self_weight and src_weights should be presented if "
                              "enabling dynamic topology.")
         dynamic = True
-        dst_map = {int(d): 1.0 for d in dst_weights} if isinstance(dst_weights, list) \
-            else {int(k): float(v) for k, v in dst_weights.items()}
-        use_dst = not np.allclose(list(dst_map.values()), 1.0) if dst_map else False
+        if isinstance(dst_weights, list):
+            dst_map, use_dst = {int(d): 1.0 for d in dst_weights}, False
+        else:
+            dst_map = {int(k): float(v) for k, v in dst_weights.items()}
+            # same tolerance as numpy.allclose(values, 1.0), without the array round trip on the hot path
+            use_dst = any(abs(v - 1.0) > 1e-8 + 1e-5 for v in dst_map.values())
     if self_weight is None and src_weights is None:
         if _b.is_topo_weighted():
             self_weight, src_map = GetRecvWeights(_b.load_topology(), _b.rank())
@@ -405,7 +408,7 @@ def hierarchical_neighbor_allreduce_nonblocking(
     for m, w in dst_map.items():
         for r in range(m * L, (m + 1) * L):
             dst[r] = w
-    use_dst = bool(dst_map) and not np.allclose(list(dst_map.values()), 1.0)
+    use_dst = any(abs(v - 1.0) > 1e-8 + 1e-5 for v in dst_map.values())
     spec = _new_spec(OP_NEIGHBOR_ALLREDUCE, _full_name("neighbor.allreduce", name))
     buf, dev = _stage(tensor.detach().clone())
     output = torch.empty_like(tensor)

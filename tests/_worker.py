@@ -287,7 +287,7 @@ def errors():
 
 @case
 def consensus():
-    """BASELINE config: 100 000 fp32 values N(0,1) from seed=rank, static exp2, 200 rounds."""
+    """Average-consensus workload: 100 000 fp32 values N(0,1) from seed=rank, static exp2, 200 rounds."""
     r, n = bf.rank(), bf.size()
     bf.set_topology(tu.ExponentialTwoGraph(n))
     x = torch.randn(100000, generator=torch.Generator().manual_seed(r))
@@ -535,6 +535,29 @@ def gpu_fast_path():
     # with negotiation the same large tensor goes through the queued path
     out2 = bf.neighbor_allreduce(x, name="large.negotiated")
     assert torch.allclose(out2, ref, atol=1e-5)
+
+
+@case
+def gpu_timeline():
+    """With the timeline on, GPU collectives of both issue paths leave a DEVICE span next to the host activities."""
+    r = bf.rank()
+    d = dev()
+    x = torch.ones(1 << 16, device=d)
+    for i in range(3):
+        bf.neighbor_allreduce(x, name="tl.gpu")          # negotiated: background thread + finalizer
+    bf.set_skip_negotiate_stage(True)
+    for i in range(3):
+        bf.neighbor_allreduce(x, name="tl.gpu.fast")     # issued on this thread
+    bf.barrier()
+    bf.set_skip_negotiate_stage(False)
+    bf.shutdown()
+    text = open(os.environ["BLUEFOG_TIMELINE"] + str(r) + ".json").read()
+    for token in ("ENQUEUE_NEIGHBOR_ALLREDUCE", "COMMUNICATE", "DEVICE", "tl.gpu", "tl.gpu.fast"):
+        assert token in text, token
+    events = json.loads(text.rstrip().rstrip(",") + "]")
+    assert sum(e["ph"] == "B" for e in events) == sum(e["ph"] == "E" for e in events)
+    pids = {e["pid"] for e in events if e.get("name") == "DEVICE"}
+    assert len(pids) >= 2, "both tensors must carry device spans"
 
 
 @case

@@ -27,6 +27,9 @@ def _close(a, ref, tol):
     (1, 64, 192, 9, 5),        # tiny image; Cout = 1.5 output tiles of 128
     (2, 64, 72, 30, 20),       # rows of the last patch hang over the image; Cout % 64 != 0
     (4, 128, 320, 16, 16),     # 256-wide and partial output tiles
+    (8, 256, 256, 4, 4),       # whole images, eight per patch
+    (8, 512, 512, 2, 2),       # 2x2 images: every tap but the centre one is mostly padding
+    (3, 64, 64, 1, 1),         # a single pixel per image
 ])
 def test_conv3x3_forward_and_input_gradient(n, cin, cout, h, w):
     from bluefog_b200 import _C

@@ -46,3 +46,9 @@ def test_pattern_mismatch_times_out_with_an_error_on_gpus():
     (shortened) limit and the operation raises instead of hanging."""
     _need(2)
     run_ranks("gpu_wait_timeout", 2, gpu=True, env=dict(NVLS_OFF, BLUEFOG_B200_WAIT_TIMEOUT_MS="300"), timeout=300)
+
+
+def test_timeline_has_device_spans_on_gpus(tmp_path):
+    _need(2)
+    prefix = str(tmp_path / "tl_")
+    run_ranks("gpu_timeline", 2, gpu=True, env=dict(NVLS_OFF, BLUEFOG_TIMELINE=prefix), timeout=300)

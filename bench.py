@@ -35,8 +35,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--model", default="resnet50")
-    ap.add_argument("--b200-gemm", action="store_true",
-                    help="route 1x1 convolutions and the classifier through the tcgen05 GEMM")
+    ap.add_argument("--b200-gemm", nargs="?", const="all", default="off", choices=["off", "auto", "all"],
+                    help="stride-1 1x1 convolutions on the tcgen05 GEMM: all of them (and the classifier), or "
+                         "'auto' = the layers where it measured faster than the library (at most 16384 pixels)")
     ap.add_argument("--b200-conv", action="store_true",
                     help="route stride-1 3x3 convolutions through the tcgen05 implicit-GEMM kernel")
     ap.add_argument("--no-graphs", action="store_true", help="drive forward/backward op by op instead of a CUDA graph")
@@ -119,7 +120,8 @@ def run_ours(args):
     dev = torch.device("cuda", torch.cuda.current_device())
     bf.set_topology(bf.ExponentialTwoGraph(size))
     torch.manual_seed(1234 + rank)
-    model = build_model(args.model, args.b200_gemm, (args.stem == "s2d"), args.b200_conv).to(dev).to(memory_format=torch.channels_last)
+    use_gemm = {"off": False, "auto": "auto", "all": True}[args.b200_gemm]
+    model = build_model(args.model, use_gemm, (args.stem == "s2d"), args.b200_conv).to(dev).to(memory_format=torch.channels_last)
     bf.broadcast_parameters(model.state_dict(), root_rank=0)
     base = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
     opt = bf.DistributedNeighborAllreduceOptimizer(
@@ -233,7 +235,7 @@ def run_ours(args):
             "config": {"model": args.model, "global_batch": B * size, "batch_per_gpu": B, "image": "3x224x224",
                        "parallelism": f"dp{size}", "optimizer": "SGD momentum 0.9 lr 0.1, fp32 master weights",
                        "topology": "ExponentialTwoGraph, dynamic one-peer", "exchange_dtype": args.exchange_dtype,
-                       "b200_gemm": bool(args.b200_gemm and gemm.available()),
+                       "b200_gemm": args.b200_gemm if gemm.available() else "off",
                        "b200_conv": bool(args.b200_conv),
                        "stem": "space-to-depth 4x4" if (args.stem == "s2d") else "7x7 stride 2",
                        "cuda_graph": "forward+backward" if not args.no_graphs else "none",

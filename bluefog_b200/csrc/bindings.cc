@@ -463,23 +463,40 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return Conv3x3Supported(static_cast<int>(n), static_cast<int>(h), static_cast<int>(w), static_cast<int>(cin),
                             static_cast<int>(cout));
   });
-  m.def("conv3x3_nhwc", [](at::Tensor x, at::Tensor w, bool flip_taps) {
+  m.def("conv3x3_nhwc", [](at::Tensor x, at::Tensor w, bool flip_taps, int filter_mode) {
     TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 4 && w.dim() == 4 && x.scalar_type() == at::kBFloat16 &&
                 w.scalar_type() == at::kBFloat16, "conv3x3_nhwc expects 4-D bf16 CUDA tensors");
     TORCH_CHECK(x.is_contiguous(at::MemoryFormat::ChannelsLast) && w.is_contiguous(at::MemoryFormat::ChannelsLast),
                 "conv3x3_nhwc expects channels_last input and filter");
-    TORCH_CHECK(w.size(2) == 3 && w.size(3) == 3 && w.size(1) == x.size(1), "conv3x3_nhwc expects a [Cout, Cin, 3, 3] filter");
+    // filter_mode 0: w = [Cout, Cin, 3, 3]; 1 / 2: w = [Cin, Cout, 3, 3], i.e. the forward filter of an input gradient
+    const int red_dim = filter_mode == 0 ? 1 : 0, out_dim = filter_mode == 0 ? 0 : 1;
+    TORCH_CHECK(w.size(2) == 3 && w.size(3) == 3 && w.size(red_dim) == x.size(1), "conv3x3_nhwc: filter does not match the input");
     const int N = static_cast<int>(x.size(0)), Cin = static_cast<int>(x.size(1)), H = static_cast<int>(x.size(2)),
-              W = static_cast<int>(x.size(3)), Cout = static_cast<int>(w.size(0));
+              W = static_cast<int>(x.size(3)), Cout = static_cast<int>(w.size(out_dim));
     TORCH_CHECK(Conv3x3Supported(N, H, W, Cin, Cout), "conv3x3_nhwc: unsupported shape");
     c10::cuda::CUDAGuard g(x.get_device());
     at::Tensor& status = GemmStatusWord(x);
     at::Tensor y = at::empty({N, Cout, H, W}, x.options().memory_format(at::MemoryFormat::ChannelsLast));
     cudaError_t e = LaunchConv3x3Nhwc(x.data_ptr(), w.data_ptr(), y.data_ptr(), N, H, W, Cin, Cout, flip_taps ? 1 : 0,
-                                      reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(x.get_device()));
+                                      filter_mode, reinterpret_cast<unsigned int*>(status.data_ptr()),
+                                      CurrentStream(x.get_device()));
     TORCH_CHECK(e == cudaSuccess, "conv3x3_nhwc launch failed: ", cudaGetErrorString(e));
     return y;
-  }, py::arg("x"), py::arg("w"), py::arg("flip_taps") = false);
+  }, py::arg("x"), py::arg("w"), py::arg("flip_taps") = false, py::arg("filter_mode") = 0);
+
+  m.def("gemm_bf16_nn", [](at::Tensor a, at::Tensor b, int mode) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.scalar_type() == at::kBFloat16 &&
+                b.scalar_type() == at::kBFloat16 && a.is_contiguous() && b.is_contiguous() && a.size(1) == b.size(0),
+                "gemm_bf16_nn expects contiguous bf16 CUDA matrices [M,K] and [K,N]");
+    c10::cuda::CUDAGuard g(a.get_device());
+    at::Tensor& status = GemmStatusWord(a);
+    at::Tensor out = at::empty({a.size(0), b.size(1)}, a.options());
+    cudaError_t e = LaunchGemmBf16NN(a.data_ptr(), b.data_ptr(), out.data_ptr(), static_cast<int>(a.size(0)),
+                                     static_cast<int>(b.size(1)), static_cast<int>(a.size(1)), mode,
+                                     reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(a.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "gemm_bf16_nn launch failed: ", cudaGetErrorString(e));
+    return out;
+  }, py::arg("a"), py::arg("b"), py::arg("mode") = 1);
 
   m.def("gemm_status", [] {
     at::Tensor probe = at::empty({0}, at::TensorOptions().device(at::kCUDA));

@@ -65,7 +65,11 @@ struct ConvGeom {
 
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <int BN_>
+// BMODE 0: the filter is [Cout, 3, 3, Cin] and supplies K-major B tiles.  BMODE 1 / 2 (input-gradient form):
+// the filter stays in the layout of the forward pass, [Cred, 3, 3, Cout'] with the reduction channels
+// outermost, and supplies MN-major B tiles: BN_/64 boxes of [64 reduction rows x 64 output channels] per
+// stage; the two modes differ in which descriptor stride spans the boxes.
+template <int BN_, int BMODE = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 conv3x3_nhwc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_y, const ConvGeom g, unsigned int* __restrict__ status) {
@@ -140,7 +144,14 @@ conv3x3_nhwc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           mbar_expect_tx(full, bytes_a + Cfg::kBytesB);
           tma_load_4d(smem_u32(stage_a + size_t(s) * Cfg::kBytesA), &map_x, full, ci0, w0 + sx - 1, h0 + r - 1, n0);
           const int wtap = g.flip_taps ? 8 - tap : tap;
-          tma_load_2d(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), &map_w, full, wtap * g.Cin + ci0, co0);
+          if (BMODE == 0) {
+            tma_load_2d(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), &map_w, full, wtap * g.Cin + ci0, co0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN_ / 64; ++j)
+              tma_load_2d(smem_u32(stage_b + size_t(s) * Cfg::kBytesB + size_t(j) * 8192), &map_w, full,
+                          wtap * g.Cout + co0 + j * 64, ci0);
+          }
           armed = it + 1;
         }
       }
@@ -159,10 +170,14 @@ conv3x3_nhwc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           if (!mbar_wait(smem_u32(&bars[s]), (it / S) & 1, failed)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t adesc = make_desc(smem_u32(stage_a + size_t(s) * Cfg::kBytesA));
-          const uint64_t bdesc = make_desc(smem_u32(stage_b + size_t(s) * Cfg::kBytesB));
+          const uint32_t b_addr = smem_u32(stage_b + size_t(s) * Cfg::kBytesB);
+          const uint64_t bdesc = BMODE == 0 ? make_desc(b_addr)
+                                 : BMODE == 1 ? make_desc_mn(b_addr, 8192, 1024) : make_desc_mn(b_addr, 1024, 8192);
+          constexpr uint32_t idesc = Cfg::kIdesc | (BMODE != 0 ? (1u << 16) : 0u);      // bit 16: B is MN-major
+          constexpr uint64_t b_step = BMODE == 0 ? 2 : (16 * 128) >> 4;                 // 16 reduction rows per MMA
 #pragma unroll
           for (int k = 0; k < BK / kUmmaK; ++k)
-            umma_f16(tmem_d, adesc + uint64_t(2 * k), bdesc + uint64_t(2 * k), Cfg::kIdesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(tmem_d, adesc + uint64_t(2 * k), bdesc + b_step * uint64_t(k), idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit(smem_u32(&bars[S + s]));
         }
         if (ok) umma_commit(smem_u32(&bars[2 * S + acc]));
@@ -275,20 +290,20 @@ int SmCount() {
   return sm_count;
 }
 
-template <int BN_>
+template <int BN_, int BMODE>
 cudaError_t Launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my, const ConvGeom& g,
                    unsigned int* status, cudaStream_t stream) {
   using Cfg = ConvCfg<BN_>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(conv3x3_nhwc_kernel<BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(conv3x3_nhwc_kernel<BN_, BMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(Cfg::kSmem));
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
   const int tiles = g.tiles_w * g.tiles_h * g.tiles_img * g.tiles_co;
   const int sms = SmCount();
-  conv3x3_nhwc_kernel<BN_><<<tiles < sms ? tiles : sms, kThreads, Cfg::kSmem, stream>>>(mx, mw, my, g, status);
+  conv3x3_nhwc_kernel<BN_, BMODE><<<tiles < sms ? tiles : sms, kThreads, Cfg::kSmem, stream>>>(mx, mw, my, g, status);
   CountKernelLaunch();
   return cudaGetLastError();
 }
@@ -322,7 +337,8 @@ bool Conv3x3Supported(int N, int H, int W, int Cin, int Cout) {
 }
 
 cudaError_t LaunchConv3x3Nhwc(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout,
-                              int flip_taps, unsigned int* status, cudaStream_t stream) {
+                              int flip_taps, int filter_mode, unsigned int* status, cudaStream_t stream) {
+  if (filter_mode < 0 || filter_mode > 2) return cudaErrorInvalidValue;
   if (!Conv3x3Supported(N, H, W, Cin, Cout)) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(y) & 15))
     return cudaErrorInvalidValue;
@@ -341,12 +357,17 @@ cudaError_t LaunchConv3x3Nhwc(const void* x, const void* w, void* y, int N, int 
   else if (Cout <= 128 || spatial * ((Cout + 255) / 256) < (SmCount() * 3) / 4) bn_tile = 128;
   g.tiles_co = (Cout + bn_tile - 1) / bn_tile;
   CUtensorMap mx, mw, my;
-  if (!MakeMap4d(&mx, x, Cin, W, H, N, g.bw, g.bh, g.bn) || !MakeMap2d(&mw, w, Cout, 9 * Cin, bn_tile) ||
-      !MakeMap4d(&my, y, Cout, W, H, N, g.bw, g.bh, g.bn))
+  // filter map: K-major [Cout rows, 9*Cin], or (MN-major modes) the forward filter [Cin rows, 9*Cout] in boxes of 64 x 64
+  const bool mw_ok = filter_mode == 0 ? MakeMap2d(&mw, w, Cout, 9 * Cin, bn_tile) : MakeMap2d(&mw, w, Cin, 9 * Cout, 64);
+  if (!MakeMap4d(&mx, x, Cin, W, H, N, g.bw, g.bh, g.bn) || !mw_ok || !MakeMap4d(&my, y, Cout, W, H, N, g.bw, g.bh, g.bn))
     return cudaErrorInvalidValue;
-  if (bn_tile == 64) return Launch<64>(mx, mw, my, g, status, stream);
-  if (bn_tile == 128) return Launch<128>(mx, mw, my, g, status, stream);
-  return Launch<256>(mx, mw, my, g, status, stream);
+#define BFB_CONV_LAUNCH(BNV)                                                        \
+  (filter_mode == 0 ? Launch<BNV, 0>(mx, mw, my, g, status, stream)                  \
+   : filter_mode == 1 ? Launch<BNV, 1>(mx, mw, my, g, status, stream) : Launch<BNV, 2>(mx, mw, my, g, status, stream))
+  if (bn_tile == 64) return BFB_CONV_LAUNCH(64);
+  if (bn_tile == 128) return BFB_CONV_LAUNCH(128);
+  return BFB_CONV_LAUNCH(256);
+#undef BFB_CONV_LAUNCH
 }
 
 }  // namespace bfb

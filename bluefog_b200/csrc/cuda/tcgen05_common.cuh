@@ -79,6 +79,14 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
   return lo | (hi << 32);
 }
 
+// Descriptor of an MN-major tile in the 128-byte swizzle: 64 MN-elements (128 bytes) per row, one row per
+// K index; lbo/sbo are the byte strides the matrix-descriptor format calls leading and stride dimension.
+__device__ __forceinline__ uint64_t make_desc_mn(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  const uint64_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16);
+  const uint64_t hi = uint64_t(sbo_bytes >> 4) | (1ull << 14) | (2ull << 29);
+  return lo | (hi << 32);
+}
+
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }

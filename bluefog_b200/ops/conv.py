@@ -51,9 +51,14 @@ class _Conv3x3Fn(torch.autograd.Function):
         dy = dy.contiguous(memory_format=torch.channels_last)
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            # [Cin, Cout, 3, 3]; the 180-degree rotation of the taps happens inside the kernel
-            wt = weight.transpose(0, 1).contiguous(memory_format=torch.channels_last)
-            dx = _b.native.conv3x3_nhwc(dy, wt, True)
+            # the 180-degree rotation of the taps happens inside the kernel
+            from bluefog_b200.ops.gemm import NN_MODE
+            if NN_MODE in (1, 2):
+                # the forward filter [Cout, Cin, 3, 3] is read in place as an MN-major operand
+                dx = _b.native.conv3x3_nhwc(dy, weight.contiguous(memory_format=torch.channels_last), True, NN_MODE)
+            else:
+                wt = weight.transpose(0, 1).contiguous(memory_format=torch.channels_last)      # [Cin, Cout, 3, 3]
+                dx = _b.native.conv3x3_nhwc(dy, wt, True)
         if ctx.needs_input_grad[1]:
             dw = torch.ops.aten.convolution_backward(dy, x, weight, None, (1, 1), (1, 1), (1, 1), False, (0, 0), 1,
                                                      (False, True, False))[1]

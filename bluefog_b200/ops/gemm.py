@@ -4,6 +4,8 @@
 ``w`` [N, K] with fp32 accumulation in tensor memory.  The backward pass uses the same
 kernel for dA = dY @ W; dW = dY.T @ A goes to the library GEMM (see ``_LinearFn.backward``).
 """
+import os
+
 import torch
 
 from bluefog_b200.common.basics import get_basics
@@ -15,6 +17,19 @@ def available() -> bool:
     """True when the tcgen05 GEMM kernel is built into the native module and a GPU is present."""
     C = _b.native
     return bool(torch.cuda.is_available() and hasattr(C, "gemm_bf16_nt") and C.gemm_supported())
+
+
+# Descriptor convention of the kernel that reads its second operand [K, N] row-major (0 = not used: input
+# gradients then multiply by an explicitly transposed copy of the weight).
+NN_MODE = int(os.environ.get("BLUEFOG_B200_GEMM_NN_MODE", "0"))
+
+
+def _input_gradient(dy2d: torch.Tensor, w2d: torch.Tensor) -> torch.Tensor:
+    """dX[M, K] = dY[M, N] @ W[N, K] on the tcgen05 kernel."""
+    if NN_MODE in (1, 2) and w2d.shape[1] % 8 == 0 and w2d.shape[0] % 8 == 0 and hasattr(_b.native, "gemm_bf16_nn"):
+        return _b.native.gemm_bf16_nn(dy2d, w2d.contiguous(), NN_MODE)     # W consumed in place, MN-major
+    # the reduction runs over N, so the NT kernel's second operand is W^T [K, N]
+    return _b.native.gemm_bf16_nt(dy2d, w2d.t().contiguous(), None, 0)
 
 
 def _nt_ok(m_rows, n_rows, k):
@@ -38,7 +53,7 @@ class _LinearFn(torch.autograd.Function):
             # dA[M,K] = dY[M,N] @ W[N,K]: the reduction runs over N, so the kernel's second operand
             # is W^T [K,N]; weights are small, the transpose copy is cheap.
             if _nt_ok(dy.shape[0], w.shape[1], dy.shape[1]):
-                da = _b.native.gemm_bf16_nt(dy, w.t().contiguous(), None, 0)
+                da = _input_gradient(dy, w)
             else:
                 da = dy @ w
         if ctx.needs_input_grad[1]:
@@ -81,8 +96,7 @@ class _Conv1x1Fn(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             d2 = dy.permute(0, 2, 3, 1).reshape(n * h * w, cout)
-            wt = weight.reshape(cout, c).t().contiguous()                  # [Cin, Cout]: K-major for the NT kernel
-            dx = _b.native.gemm_bf16_nt(d2, wt, None, 0).view(n, h, w, c).permute(0, 3, 1, 2)
+            dx = _input_gradient(d2, weight.reshape(cout, c)).view(n, h, w, c).permute(0, 3, 1, 2)
         if ctx.needs_input_grad[1]:
             dw = torch.ops.aten.convolution_backward(dy, x, weight, None, (1, 1), (0, 0), (1, 1), False, (0, 0), 1,
                                                      (False, True, False))[1]

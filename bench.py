@@ -35,7 +35,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--model", default="resnet50")
-    ap.add_argument("--b200-gemm", nargs="?", const="all", default="off", choices=["off", "auto", "all"],
+    ap.add_argument("--b200-gemm", nargs="?", const="all", default="auto", choices=["off", "auto", "all"],
                     help="stride-1 1x1 convolutions on the tcgen05 GEMM: all of them (and the classifier), or "
                          "'auto' = the layers where it measured faster than the library (at most 16384 pixels)")
     ap.add_argument("--b200-conv", action="store_true",
@@ -44,6 +44,9 @@ def parse_args():
     ap.add_argument("--stem", default="s2d", choices=["s2d", "7x7"],
                     help="evaluate the 7x7/2 stem convolution as a 4x4 convolution over 2x2 pixel blocks (s2d) or directly")
     ap.add_argument("--exchange-dtype", default="float32", choices=["float32", "bfloat16"])
+    ap.add_argument("--no-cudnn-benchmark", action="store_true",
+                    help="leave cuDNN on its heuristics instead of timing its algorithms per shape in the warm-up "
+                         "(the reference's benchmark sets cudnn.benchmark = True, examples/pytorch_benchmark.py:76)")
     return ap.parse_args()
 
 
@@ -238,6 +241,7 @@ def run_ours(args):
                        "b200_gemm": args.b200_gemm if gemm.available() else "off",
                        "b200_conv": bool(args.b200_conv),
                        "stem": "space-to-depth 4x4" if (args.stem == "s2d") else "7x7 stride 2",
+                       "cudnn_benchmark": bool(torch.backends.cudnn.benchmark),
                        "cuda_graph": "forward+backward" if not args.no_graphs else "none",
                        "l2": "inputs plus activations exceed the 126 MB L2 every step; no explicit flush"},
             "clocks": clocks,
@@ -255,6 +259,7 @@ def run_ours(args):
 
 def main():
     args = parse_args()
+    torch.backends.cudnn.benchmark = not args.no_cudnn_benchmark
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) != 0:
             return 0                      # one line per job, printed by rank 0

@@ -468,7 +468,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                 w.scalar_type() == at::kBFloat16, "conv3x3_nhwc expects 4-D bf16 CUDA tensors");
     TORCH_CHECK(x.is_contiguous(at::MemoryFormat::ChannelsLast) && w.is_contiguous(at::MemoryFormat::ChannelsLast),
                 "conv3x3_nhwc expects channels_last input and filter");
-    // filter_mode 0: w = [Cout, Cin, 3, 3]; 1 / 2: w = [Cin, Cout, 3, 3], i.e. the forward filter of an input gradient
+    // filter_mode 0: w = [Cout, Cin, 3, 3]; 1: w = [Cin, Cout, 3, 3], i.e. the forward filter of an input gradient
     const int red_dim = filter_mode == 0 ? 1 : 0, out_dim = filter_mode == 0 ? 0 : 1;
     TORCH_CHECK(w.size(2) == 3 && w.size(3) == 3 && w.size(red_dim) == x.size(1), "conv3x3_nhwc: filter does not match the input");
     const int N = static_cast<int>(x.size(0)), Cin = static_cast<int>(x.size(1)), H = static_cast<int>(x.size(2)),
@@ -484,7 +484,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return y;
   }, py::arg("x"), py::arg("w"), py::arg("flip_taps") = false, py::arg("filter_mode") = 0);
 
-  m.def("gemm_bf16_nn", [](at::Tensor a, at::Tensor b, int mode) {
+  m.def("gemm_bf16_nn", [](at::Tensor a, at::Tensor b) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.scalar_type() == at::kBFloat16 &&
                 b.scalar_type() == at::kBFloat16 && a.is_contiguous() && b.is_contiguous() && a.size(1) == b.size(0),
                 "gemm_bf16_nn expects contiguous bf16 CUDA matrices [M,K] and [K,N]");
@@ -492,11 +492,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     at::Tensor& status = GemmStatusWord(a);
     at::Tensor out = at::empty({a.size(0), b.size(1)}, a.options());
     cudaError_t e = LaunchGemmBf16NN(a.data_ptr(), b.data_ptr(), out.data_ptr(), static_cast<int>(a.size(0)),
-                                     static_cast<int>(b.size(1)), static_cast<int>(a.size(1)), mode,
+                                     static_cast<int>(b.size(1)), static_cast<int>(a.size(1)),
                                      reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(a.get_device()));
     TORCH_CHECK(e == cudaSuccess, "gemm_bf16_nn launch failed: ", cudaGetErrorString(e));
     return out;
-  }, py::arg("a"), py::arg("b"), py::arg("mode") = 1);
+  }, py::arg("a"), py::arg("b"));
 
   m.def("gemm_status", [] {
     at::Tensor probe = at::empty({0}, at::TensorOptions().device(at::kCUDA));

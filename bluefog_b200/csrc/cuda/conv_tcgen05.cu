@@ -65,10 +65,9 @@ struct ConvGeom {
 
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-// BMODE 0: the filter is [Cout, 3, 3, Cin] and supplies K-major B tiles.  BMODE 1 / 2 (input-gradient form):
-// the filter stays in the layout of the forward pass, [Cred, 3, 3, Cout'] with the reduction channels
-// outermost, and supplies MN-major B tiles: BN_/64 boxes of [64 reduction rows x 64 output channels] per
-// stage; the two modes differ in which descriptor stride spans the boxes.
+// BMODE 0: the filter is [Cout, 3, 3, Cin] and supplies K-major B tiles.  BMODE 1 (input-gradient form): the
+// filter stays in the layout of the forward pass, [Cred, 3, 3, Cout'] with the reduction channels outermost,
+// and supplies MN-major B tiles: BN_/64 boxes of [64 reduction rows x 64 output channels] per stage.
 template <int BN_, int BMODE = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 conv3x3_nhwc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -171,8 +170,7 @@ conv3x3_nhwc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t adesc = make_desc(smem_u32(stage_a + size_t(s) * Cfg::kBytesA));
           const uint32_t b_addr = smem_u32(stage_b + size_t(s) * Cfg::kBytesB);
-          const uint64_t bdesc = BMODE == 0 ? make_desc(b_addr)
-                                 : BMODE == 1 ? make_desc_mn(b_addr, 8192, 1024) : make_desc_mn(b_addr, 1024, 8192);
+          const uint64_t bdesc = BMODE == 0 ? make_desc(b_addr) : make_desc_mn(b_addr, 8192, 1024);
           constexpr uint32_t idesc = Cfg::kIdesc | (BMODE != 0 ? (1u << 16) : 0u);      // bit 16: B is MN-major
           constexpr uint64_t b_step = BMODE == 0 ? 2 : (16 * 128) >> 4;                 // 16 reduction rows per MMA
 #pragma unroll
@@ -338,7 +336,7 @@ bool Conv3x3Supported(int N, int H, int W, int Cin, int Cout) {
 
 cudaError_t LaunchConv3x3Nhwc(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout,
                               int flip_taps, int filter_mode, unsigned int* status, cudaStream_t stream) {
-  if (filter_mode < 0 || filter_mode > 2) return cudaErrorInvalidValue;
+  if (filter_mode < 0 || filter_mode > 1) return cudaErrorInvalidValue;
   if (!Conv3x3Supported(N, H, W, Cin, Cout)) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(y) & 15))
     return cudaErrorInvalidValue;
@@ -361,9 +359,8 @@ cudaError_t LaunchConv3x3Nhwc(const void* x, const void* w, void* y, int N, int 
   const bool mw_ok = filter_mode == 0 ? MakeMap2d(&mw, w, Cout, 9 * Cin, bn_tile) : MakeMap2d(&mw, w, Cin, 9 * Cout, 64);
   if (!MakeMap4d(&mx, x, Cin, W, H, N, g.bw, g.bh, g.bn) || !mw_ok || !MakeMap4d(&my, y, Cout, W, H, N, g.bw, g.bh, g.bn))
     return cudaErrorInvalidValue;
-#define BFB_CONV_LAUNCH(BNV)                                                        \
-  (filter_mode == 0 ? Launch<BNV, 0>(mx, mw, my, g, status, stream)                  \
-   : filter_mode == 1 ? Launch<BNV, 1>(mx, mw, my, g, status, stream) : Launch<BNV, 2>(mx, mw, my, g, status, stream))
+#define BFB_CONV_LAUNCH(BNV) \
+  (filter_mode == 0 ? Launch<BNV, 0>(mx, mw, my, g, status, stream) : Launch<BNV, 1>(mx, mw, my, g, status, stream))
   if (bn_tile == 64) return BFB_CONV_LAUNCH(64);
   if (bn_tile == 128) return BFB_CONV_LAUNCH(128);
   return BFB_CONV_LAUNCH(256);

@@ -12,9 +12,8 @@ bool Conv3x3Supported(int N, int H, int W, int Cin, int Cout);
 
 // y[N,H,W,Cout] = conv3x3(x[N,H,W,Cin], w[Cout,3,3,Cin]), all bf16, dense, 16-byte aligned bases.
 // flip_taps: use filter tap (2 - r, 2 - s) for input tap (r, s) (the 180-degree rotation of the input-gradient form).
-// filter_mode 0: w is [Cout,3,3,Cin].  1 / 2: w is [Cin,3,3,Cout] (the filter of the forward pass when this call
-// computes an input gradient; Cin, Cout are this call's reduction and output channels) and is read as an
-// MN-major operand; the two values select the descriptor convention.
+// filter_mode 0: w is [Cout,3,3,Cin].  1: w is [Cin,3,3,Cout] (the filter of the forward pass when this call
+// computes an input gradient; Cin, Cout are this call's reduction and output channels), read as an MN-major operand.
 // status: device word set to 1 when a bounded wait inside the kernel expired (may be null).
 cudaError_t LaunchConv3x3Nhwc(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout,
                               int flip_taps, int filter_mode, unsigned int* status, cudaStream_t stream);

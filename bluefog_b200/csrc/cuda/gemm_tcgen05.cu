@@ -218,9 +218,10 @@ struct PersistentCfg {
   static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN_ >> 3) << 17) | (uint32_t(BM >> 4) << 24);
 };
 
-// BMODE 0: B is [N, K] row-major (K-major operand, the production path).  BMODE 1 / 2: B is [K, N]
-// row-major (MN-major operand): every ring stage holds BN_/64 boxes of [64 K-rows x 64 N-columns], and
-// the two modes differ only in which of the two descriptor strides is the distance between boxes.
+// BMODE 0: B is [N, K] row-major (K-major operand).  BMODE 1: B is [K, N] row-major and is consumed as an
+// MN-major operand: every ring stage holds BN_/64 boxes of [64 K-rows x 64 N-columns] (8 KiB each, 128-byte
+// swizzle); the descriptor's leading-dimension stride is the distance between boxes, its stride-dimension
+// stride the 1024 bytes between groups of eight K-rows, and one MMA step advances 16 rows = 2048 bytes.
 template <int BN_, int BMODE = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -310,8 +311,7 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t adesc = make_desc(smem_u32(stage_a + size_t(s) * Cfg::kBytesA));
           const uint32_t b_addr = smem_u32(stage_b + size_t(s) * Cfg::kBytesB);
-          const uint64_t bdesc = BMODE == 0 ? make_desc(b_addr)
-                                 : BMODE == 1 ? make_desc_mn(b_addr, 8192, 1024) : make_desc_mn(b_addr, 1024, 8192);
+          const uint64_t bdesc = BMODE == 0 ? make_desc(b_addr) : make_desc_mn(b_addr, 8192, 1024);
           // MN-major B: bit 16 of the instruction descriptor; 16 K-rows of 128 bytes per MMA step
           constexpr uint32_t idesc = Cfg::kIdesc | (BMODE != 0 ? (1u << 16) : 0u);
           constexpr uint64_t b_step = BMODE == 0 ? 2 : (16 * 128) >> 4;
@@ -524,43 +524,46 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
 }
 
 // out[M,N] = a[M,K] * b[K,N]: the B operand is consumed MN-major straight from its row-major memory, so a
-// product with a transposed weight needs no transposed copy.  mode 1 / 2 select the descriptor convention.
-cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int N, int K, int mode,
-                             unsigned int* status, cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0 || (K % 8) != 0 || (N % 8) != 0 || (mode != 1 && mode != 2)) return cudaErrorInvalidValue;
+// product with a transposed weight (an input gradient) needs no transposed copy.
+cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int N, int K, unsigned int* status,
+                             cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 8) != 0 || (N % 8) != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
     return cudaErrorInvalidValue;
-  int sm_count = 148;
-  {
+  static int sm_count = 0;
+  if (sm_count == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  using Cfg = PersistentCfg<128>;
   CUtensorMap map_a, map_b, map_c;
   // B: [K rows, N columns]; boxes of 64 columns (128 bytes) x 64 rows
   if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, K, N, 64) || !MakeMap(&map_c, out, M, N, 32))
     return cudaErrorInvalidValue;
-  const int tiles = ((M + BM - 1) / BM) * ((N + 127) / 128);
-  const int grid = tiles < sm_count ? tiles : sm_count;
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
-  if (mode == 1) {
+  if (N > 128) {
+    using Cfg = PersistentCfg<256>;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
+      if (e != cudaSuccess) return e;
+      attr_set = true;
+    }
+    const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+    gemm_bf16_nt_persistent_kernel<256, 1><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
+        map_a, map_b, map_c, o, nullptr, M, N, K, 0, 1, status);
+  } else {
+    using Cfg = PersistentCfg<128>;
     static bool attr_set = false;
     if (!attr_set) {
       cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
       if (e != cudaSuccess) return e;
       attr_set = true;
     }
-    gemm_bf16_nt_persistent_kernel<128, 1><<<grid, kThreads, Cfg::kSmem, stream>>>(map_a, map_b, map_c, o, nullptr, M, N, K, 0, 1, status);
-  } else {
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
-      if (e != cudaSuccess) return e;
-      attr_set = true;
-    }
-    gemm_bf16_nt_persistent_kernel<128, 2><<<grid, kThreads, Cfg::kSmem, stream>>>(map_a, map_b, map_c, o, nullptr, M, N, K, 0, 1, status);
+    const int tiles = ((M + BM - 1) / BM) * ((N + 127) / 128);
+    gemm_bf16_nt_persistent_kernel<128, 1><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
+        map_a, map_b, map_c, o, nullptr, M, N, K, 0, 1, status);
   }
   CountKernelLaunch();
   return cudaGetLastError();

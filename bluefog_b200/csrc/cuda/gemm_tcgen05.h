@@ -16,8 +16,7 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
                              unsigned int* status, cudaStream_t stream);
 
 // out[M,N] = a[M,K] * b[K,N] with b row-major (consumed as an MN-major operand); K % 8 == 0, N % 8 == 0.
-// mode 1 / 2: which descriptor stride spans the 64-column boxes of a stage.
-cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int N, int K, int mode,
-                             unsigned int* status, cudaStream_t stream);
+cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int N, int K, unsigned int* status,
+                             cudaStream_t stream);
 
 }  // namespace bfb

@@ -5,8 +5,9 @@
 ``Cout % 8 == 0``, ``Cout >= 64`` and ``W <= 128`` take ``csrc/cuda/conv_tcgen05.cu``:
 
 * forward:  the kernel on (x, weight);
-* input gradient: the same kernel on (dy, weight with its channel axes swapped), reading the filter
-  taps in reverse order — the transposed convolution of a stride-1 "same" convolution is again one;
+* input gradient: the same kernel on (dy, the same filter), reading the filter taps in reverse order
+  and the filter tiles as MN-major operands (the channel axes swap roles without a transposed copy)
+  — the transposed convolution of a stride-1 "same" convolution is again one;
 * filter gradient: reduces over every output pixel of the batch (a split-K problem with two
   pixel-major operands); it is left to the library (``aten::convolution_backward`` with only the
   weight mask set).
@@ -51,14 +52,9 @@ class _Conv3x3Fn(torch.autograd.Function):
         dy = dy.contiguous(memory_format=torch.channels_last)
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            # the 180-degree rotation of the taps happens inside the kernel
-            from bluefog_b200.ops.gemm import NN_MODE
-            if NN_MODE in (1, 2):
-                # the forward filter [Cout, Cin, 3, 3] is read in place as an MN-major operand
-                dx = _b.native.conv3x3_nhwc(dy, weight.contiguous(memory_format=torch.channels_last), True, NN_MODE)
-            else:
-                wt = weight.transpose(0, 1).contiguous(memory_format=torch.channels_last)      # [Cin, Cout, 3, 3]
-                dx = _b.native.conv3x3_nhwc(dy, wt, True)
+            # the forward filter [Cout, Cin, 3, 3] is read in place: as an MN-major operand (its reduction
+            # channels are the outer dimension here) and with the taps in reverse order (180-degree rotation)
+            dx = _b.native.conv3x3_nhwc(dy, weight.contiguous(memory_format=torch.channels_last), True, 1)
         if ctx.needs_input_grad[1]:
             dw = torch.ops.aten.convolution_backward(dy, x, weight, None, (1, 1), (1, 1), (1, 1), False, (0, 0), 1,
                                                      (False, True, False))[1]

@@ -1,11 +1,10 @@
 """bf16 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), with autograd.
 
 ``linear(a, w, bias)`` computes ``a @ w.T + bias`` for row-major bf16 ``a`` [M, K] and
-``w`` [N, K] with fp32 accumulation in tensor memory.  The backward pass uses the same
-kernel for dA = dY @ W; dW = dY.T @ A goes to the library GEMM (see ``_LinearFn.backward``).
+``w`` [N, K] with fp32 accumulation in tensor memory.  The backward pass computes dA = dY @ W on the
+same kernel with W read in place as an MN-major operand; dW = dY.T @ A goes to the library GEMM
+(see ``_LinearFn.backward``).
 """
-import os
-
 import torch
 
 from bluefog_b200.common.basics import get_basics
@@ -19,16 +18,11 @@ def available() -> bool:
     return bool(torch.cuda.is_available() and hasattr(C, "gemm_bf16_nt") and C.gemm_supported())
 
 
-# Descriptor convention of the kernel that reads its second operand [K, N] row-major (0 = not used: input
-# gradients then multiply by an explicitly transposed copy of the weight).
-NN_MODE = int(os.environ.get("BLUEFOG_B200_GEMM_NN_MODE", "0"))
-
-
 def _input_gradient(dy2d: torch.Tensor, w2d: torch.Tensor) -> torch.Tensor:
-    """dX[M, K] = dY[M, N] @ W[N, K] on the tcgen05 kernel."""
-    if NN_MODE in (1, 2) and w2d.shape[1] % 8 == 0 and w2d.shape[0] % 8 == 0 and hasattr(_b.native, "gemm_bf16_nn"):
-        return _b.native.gemm_bf16_nn(dy2d, w2d.contiguous(), NN_MODE)     # W consumed in place, MN-major
-    # the reduction runs over N, so the NT kernel's second operand is W^T [K, N]
+    """dX[M, K] = dY[M, N] @ W[N, K] on the tcgen05 kernel.  W [N, K] row-major is exactly the [K_red, N_out]
+    operand of this product, which the kernel reads in place as an MN-major tile (no transposed copy)."""
+    if w2d.shape[1] % 8 == 0 and w2d.shape[0] % 8 == 0:
+        return _b.native.gemm_bf16_nn(dy2d, w2d.contiguous())
     return _b.native.gemm_bf16_nt(dy2d, w2d.t().contiguous(), None, 0)
 
 

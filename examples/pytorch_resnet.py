@@ -39,6 +39,7 @@ parser.add_argument("--bf16", action="store_true")
 parser.add_argument("--no-cuda", action="store_true")
 args = parser.parse_args()
 
+torch.backends.cudnn.benchmark = True      # let cuDNN time its algorithms for the fixed shapes
 bf.init()
 cuda = not args.no_cuda and torch.cuda.is_available() and bf._b.device() >= 0
 device = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")

@@ -79,3 +79,18 @@ def test_conv1x1_autograd_matches_fp32(n, cin, cout, h, w):
     close(x1.grad, x2.grad, 1e-2)
     close(w1.grad, w2.grad, 2e-2)
     assert _C.gemm_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 64, 64), (256, 128, 128), (512, 256, 256), (1000, 200, 72), (4096, 1024, 4096),
+                                   (12544, 256, 1024), (300, 520, 136)])
+def test_gemm_nn_reads_row_major_b_as_mn_major_operand(M, N, K):
+    """a[M,K] @ b[K,N] with b in its row-major memory (the input-gradient product dY @ W)."""
+    from bluefog_b200 import _C
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    b = (torch.randn(K, N, device="cuda") * 0.5).to(torch.bfloat16)
+    out = _C.gemm_bf16_nn(a, b).float()
+    ref = a.float() @ b.float()
+    err = (out - ref).abs().max().item()
+    assert err <= 1e-2 * max(1.0, ref.abs().max().item()), err
+    assert _C.gemm_status() == 0

@@ -36,15 +36,20 @@ def test_fused_sgd_single_rank_matches_torch_sgd(bf, exact_fp32_convolutions):
     assert type(o2).__name__ == "SGD" and isinstance(o2, torch.optim.SGD) and hasattr(o2, "master_parameters")
     x = torch.randn(4, 3, 32, 32, device=dev)
     y = torch.randint(0, 10, (4,), device=dev)
+    # Both optimizers get the SAME gradients (those of the fused model), so that the comparison is about
+    # the update arithmetic and not about which convolution algorithm the library picked for which copy.
     for _ in range(3):
-        for m, o in ((m1, o1), (m2, o2)):
-            o.zero_grad()
-            torch.nn.functional.cross_entropy(m(x), y).backward()
-            o.step()
-    torch.cuda.synchronize()
-    o2.check()
-    for (n1, p1), (n2, p2) in zip(m1.named_parameters(), m2.named_parameters()):
-        assert torch.allclose(p1, p2, rtol=1e-4, atol=1e-5), (n1, (p1 - p2).abs().max().item())
+        o1.zero_grad()
+        o2.zero_grad()
+        torch.nn.functional.cross_entropy(m2(x), y).backward()
+        for p1, p2 in zip(m1.parameters(), m2.parameters()):
+            p1.grad = p2.grad.detach().clone()
+        o1.step()
+        o2.step()
+        torch.cuda.synchronize()
+        o2.check()
+        for (n1, p1), (n2, p2) in zip(m1.named_parameters(), m2.named_parameters()):
+            assert torch.allclose(p1, p2, rtol=1e-5, atol=1e-6), (n1, (p1 - p2).abs().max().item())
     sd = o2.state_dict()
     assert "momentum_buffer" in sd["state"][0]
 
@@ -168,13 +173,16 @@ def test_fused_sgd_keeps_channels_last_filters_and_matches_torch_sgd(bf, exact_f
     x = torch.randn(4, 8, 12, 12, device=dev).contiguous(memory_format=torch.channels_last)
     y = torch.randint(0, 4, (4,), device=dev)
     for _ in range(3):
-        for m, o in ((m1, o1), (m2, o2)):
-            o.zero_grad()
-            torch.nn.functional.cross_entropy(m(x), y).backward()
-            o.step()
+        o1.zero_grad()
+        o2.zero_grad()
+        torch.nn.functional.cross_entropy(m2(x), y).backward()
+        for p1, p2 in zip(m1.parameters(), m2.parameters()):
+            p1.grad = p2.grad.detach().clone()            # same gradients for both optimizers
+        o1.step()
+        o2.step()
     torch.cuda.synchronize()
     o2.check()
     for (n1, p1), (_, p2) in zip(m1.named_parameters(), m2.named_parameters()):
-        assert torch.allclose(p1, p2, rtol=1e-4, atol=1e-5), n1
+        assert torch.allclose(p1, p2, rtol=1e-5, atol=1e-6), (n1, (p1 - p2).abs().max().item())
     masters = o2.master_parameters()
     assert torch.allclose(masters["0.weight"], m1[0].weight, rtol=1e-4, atol=1e-5)

@@ -45,7 +45,8 @@ def test_conv3x3_forward_and_input_gradient(n, cin, cout, h, w):
     assert _C.gemm_status() == 0
 
 
-@pytest.mark.parametrize("n,cin,cout,h,w", [(2, 64, 64, 56, 56), (3, 128, 256, 14, 14), (4, 512, 512, 7, 7)])
+@pytest.mark.parametrize("n,cin,cout,h,w", [(2, 64, 64, 56, 56), (3, 128, 256, 14, 14), (4, 512, 512, 7, 7),
+                                           (8, 512, 512, 2, 2), (8, 128, 128, 8, 8), (5, 64, 320, 16, 16)])
 def test_conv3x3_autograd_matches_fp32(n, cin, cout, h, w):
     from bluefog_b200 import _C
     from bluefog_b200.ops import conv

@@ -197,10 +197,28 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(const __nv_bfloat16* _
   }
 }
 
+int SmCount() {
+  static int sms = [] {
+    int dev = 0, n = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 148;
+  }();
+  return sms;
+}
+
 int GridFor(long long R) {
   long long blocks = (R + kWarps - 1) / kWarps;
   if (blocks < 1) blocks = 1;
-  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks > SmCount() * 4) blocks = SmCount() * 4;
+  return (int)blocks;
+}
+
+// The backward kernel ends with one global atomic per column and block: few, long-lived blocks (one per SM)
+// keep the contention on the 2*C sums low.
+int GridForBackward(long long R) {
+  long long blocks = (R + kWarps - 1) / kWarps;
+  if (blocks < 1) blocks = 1;
+  if (blocks > SmCount()) blocks = SmCount();
   return (int)blocks;
 }
 
@@ -236,7 +254,7 @@ cudaError_t LaunchLnBackward(const void* dy, const void* x, const void* gamma, c
                              cudaStream_t stream) {
   if (!LnShapeSupported(R, C)) return cudaErrorInvalidValue;
   const int nv = ((C >> 3) + 31) / 32;
-  BFB_LN_DISPATCH(nv, (ln_bwd_kernel<NV><<<GridFor(R), kThreads, 0, stream>>>(
+  BFB_LN_DISPATCH(nv, (ln_bwd_kernel<NV><<<GridForBackward(R), kThreads, 0, stream>>>(
                           static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), gamma, mean,
                           rstd, static_cast<__nv_bfloat16*>(dx), dgamma_zeroed, dbeta_zeroed, R, C, param_bf16)));
   CountKernelLaunch();

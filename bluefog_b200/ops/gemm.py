@@ -56,7 +56,7 @@ class _LinearFn(torch.autograd.Function):
             # library GEMM, which takes the transposed views without copies.
             dw = dy.t() @ a
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy.float().sum(0).to(dy.dtype)
+            db = dy.sum(0, dtype=torch.float32).to(dy.dtype)     # fp32 accumulation without an fp32 copy of dy
         return da, dw, db
 
 

@@ -198,6 +198,7 @@ void Runtime::Shutdown() {
   }
   gpu_channel_.reset();
   gpu_ctrl_.reset();
+  pair_channels_.clear();
   if (comm_stream_) {
     cudaStreamDestroy(static_cast<cudaStream_t>(comm_stream_));
     comm_stream_ = nullptr;
@@ -263,7 +264,7 @@ bool Runtime::InlineEligible(const OpSpec& spec) const {
   if (spec.negotiate && !skip_negotiate_.load() && size_ > 1) return false;
   const OpType type = static_cast<OpType>(spec.type);
   if (type != OpType::ALLREDUCE && type != OpType::BROADCAST && type != OpType::ALLGATHER &&
-      type != OpType::NEIGHBOR_ALLGATHER && type != OpType::NEIGHBOR_ALLREDUCE)
+      type != OpType::NEIGHBOR_ALLGATHER && type != OpType::NEIGHBOR_ALLREDUCE && type != OpType::PAIR_GOSSIP)
     return false;
   const at::Tensor* t = spec.input.has_value() ? &*spec.input : (spec.output.has_value() ? &*spec.output : nullptr);
   return t != nullptr && t->is_cuda();
@@ -336,7 +337,7 @@ Status Runtime::CompleteInline(int handle, bool block, bool* finished) {
   }
   cudaEventDestroy(static_cast<cudaEvent_t>(op.done_event));
   Status s = err == cudaSuccess ? Status::OK() : Status::UnknownError("CUDA error: " + CudaErrorString(err));
-  if (s.ok() && gpu_channel_) s = gpu_channel_->StatusToError();
+  if (s.ok()) s = GpuStatusToError();
   for (auto& e : *op.keep) {
     timeline_.ActivityEnd(e.spec.name);   // ENQUEUE_*
     if (e.ready_event) cudaEventDestroy(static_cast<cudaEvent_t>(e.ready_event));
@@ -786,14 +787,13 @@ void Runtime::FinishEntries(std::vector<Entry>& entries, const Status& s, void* 
   // Keep the tensors alive until the kernels are done.
   auto keep = std::make_shared<std::vector<Entry>>(std::move(entries));
   const int device = device_;
-  Channel* chan = gpu_channel_.get();
-  finalizers_.execute([this, handles, names, ready, keep, done_event, span_start, device, chan] {
+  finalizers_.execute([this, handles, names, ready, keep, done_event, span_start, device] {
     cudaSetDevice(device);
     cudaError_t err = cudaEventSynchronize(static_cast<cudaEvent_t>(done_event));
     EmitDeviceSpan(names, span_start, err == cudaSuccess ? done_event : nullptr);
     cudaEventDestroy(static_cast<cudaEvent_t>(done_event));
     Status s = err == cudaSuccess ? Status::OK() : Status::UnknownError("CUDA error: " + CudaErrorString(err));
-    if (s.ok() && chan != nullptr) s = chan->StatusToError();
+    if (s.ok()) s = GpuStatusToError();
     for (size_t i = 0; i < handles.size(); ++i) {
       timeline_.ActivityEnd(names[i]);
       if (ready[i]) cudaEventDestroy(static_cast<cudaEvent_t>(ready[i]));
@@ -1032,7 +1032,20 @@ Status Runtime::ExecuteCpu(std::vector<Entry>& entries, const Response& resp) {
   return Status::OK();
 }
 
-Status Runtime::EnsureGpuChannel(uint64_t need_bytes) {
+Status Runtime::GpuStatusToError() {
+  if (gpu_channel_) {
+    Status s = gpu_channel_->StatusToError();
+    if (!s.ok()) return s;
+  }
+  std::lock_guard<std::mutex> g(pair_mu_);
+  for (auto& kv : pair_channels_) {
+    Status s = kv.second.chan->StatusToError();
+    if (!s.ok()) return s;
+  }
+  return Status::OK();
+}
+
+Status Runtime::EnsureCommStream() {
   cudaSetDevice(device_);
   if (!comm_stream_) {
     cudaStream_t st;
@@ -1041,6 +1054,86 @@ Status Runtime::EnsureGpuChannel(uint64_t need_bytes) {
     BFB_CUDA_OK(cudaStreamCreateWithPriority(&st, cudaStreamNonBlocking, hi));
     comm_stream_ = st;
   }
+  return Status::OK();
+}
+
+// The channel of a gossip pair lives in memory that only the two partners map; its versions advance with
+// the gossips of this pair, whatever the other ranks do meanwhile.
+Status Runtime::EnsurePairChannel(int peer, uint64_t need_bytes, Channel** chan) {
+  Status s = EnsureCommStream();
+  if (!s.ok()) return s;
+  std::map<int, PairChannel>::iterator it;
+  {
+    std::lock_guard<std::mutex> g(pair_mu_);
+    it = pair_channels_.find(peer);
+  }
+  const bool have = it != pair_channels_.end();
+  if (have && need_bytes <= it->second.chan->half_bytes()) {
+    *chan = it->second.chan.get();
+    return Status::OK();
+  }
+  uint64_t half = have ? it->second.chan->half_bytes()
+                       : static_cast<uint64_t>(EnvDouble("BLUEFOG_B200_PAIR_ARENA_BYTES", 8.0 * 1024 * 1024));
+  while (half < need_bytes) half *= 2;
+  if (have) {
+    // both partners arrive here for the same gossip: finish the local work, then make sure the partner has
+    // finished reading the old arena before it is released
+    BFB_CUDA_OK(cudaStreamSynchronize(static_cast<cudaStream_t>(comm_stream_)));
+    char mine = 1, theirs = 0;
+    s = cp_.Exchange(kChanData, {{peer, &mine, 1}}, {{peer, &theirs, 1}});
+    if (!s.ok()) return s;
+  }
+  std::shared_ptr<SymmBuffer> arena;
+  s = AllocateIpcPair(&cp_, kChanData, peer, device_, half * 2, &arena);
+  if (!s.ok()) return s;
+  if (!have) {
+    PairChannel pc;
+    s = AllocateIpcPair(&cp_, kChanData, peer, device_, sizeof(ChannelCtrl), &pc.ctrl);
+    if (!s.ok()) return s;
+    pc.chan = std::make_unique<Channel>(pc.ctrl, arena, half);
+    std::lock_guard<std::mutex> g(pair_mu_);
+    it = pair_channels_.emplace(peer, std::move(pc)).first;
+  } else {
+    it->second.chan->ResetArena(arena, half);
+  }
+  *chan = it->second.chan.get();
+  return Status::OK();
+}
+
+Status Runtime::ExecutePairGossipGpu(Entry& e) {
+  OpSpec& sp = e.spec;
+  if (sp.src_ranks.size() != 1) return Status::InvalidArgument("pair_gossip needs exactly one partner");
+  const int peer = sp.src_ranks[0];
+  const int elem = ToElem(sp.input->scalar_type());
+  if (elem < 0 || elem == kI32 || elem == kI64) return Status::InvalidArgument("unsupported tensor type for pair_gossip");
+  SegSpec sg;
+  sg.in = sp.input->data_ptr();
+  sg.nbytes = static_cast<uint64_t>(sp.input->nbytes());
+  sg.numel = static_cast<uint64_t>(sp.input->numel());
+  Channel* chan = nullptr;
+  Status s = EnsurePairChannel(peer, std::max<uint64_t>(Channel::PaddedSize(sg.nbytes), 256), &chan);
+  if (!s.ok()) return s;
+  cudaStream_t stream = static_cast<cudaStream_t>(comm_stream_);
+  if (e.ready_event) cudaStreamWaitEvent(stream, static_cast<cudaEvent_t>(e.ready_event), 0);
+  timeline_.ActivityStart(sp.name, "COMMUNICATE");
+  at::Tensor& out = *sp.output;
+  if (out.sizes() != sp.input->sizes()) {
+    c10::cuda::CUDAStreamGuard g(c10::cuda::getStreamFromExternal(stream, device_));
+    out.resize_(sp.input->sizes());
+  }
+  sg.out = out.data_ptr();
+  Round round;
+  s = chan->Publish({sg}, nullptr, /*n_readers=*/1, stream, &round);
+  if (s.ok())
+    s = chan->PullCombine(round, {sg}, elem, sp.self_weight, {1 - chan->rank()}, {sp.src_weights.empty() ? 0.5 : sp.src_weights[0]},
+                          false, 1.0, stream);
+  timeline_.ActivityEnd(sp.name);
+  return s;
+}
+
+Status Runtime::EnsureGpuChannel(uint64_t need_bytes) {
+  Status cs = EnsureCommStream();
+  if (!cs.ok()) return cs;
   const bool have = gpu_channel_ != nullptr;
   if (have && need_bytes <= gpu_channel_->half_bytes()) return Status::OK();
   // (Re)allocation is collective: payload sizes agree on every rank, so all ranks get here
@@ -1068,6 +1161,14 @@ Status Runtime::EnsureGpuChannel(uint64_t need_bytes) {
 // GPU data path: publish into the symmetric arena, then pull from the peers' arenas.
 Status Runtime::ExecuteGpu(std::vector<Entry>& entries, const Response& resp) {
   const OpType type = static_cast<OpType>(entries[0].spec.type);
+  if (type == OpType::PAIR_GOSSIP) {
+    Status ps = Status::OK();
+    for (auto& e : entries) {
+      ps = ExecutePairGossipGpu(e);
+      if (!ps.ok()) break;
+    }
+    return ps;
+  }
   OpSpec& first = entries[0].spec;
   std::vector<SegSpec> segs;
   for (auto& e : entries) {

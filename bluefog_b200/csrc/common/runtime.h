@@ -143,6 +143,10 @@ class Runtime {
   Status ExecuteWindowOp(Entry& e);
   Status TopoCheck(const OpSpec& spec);
   Status EnsureGpuChannel(uint64_t need_bytes);
+  Status EnsureCommStream();
+  // pair_gossip on GPUs: a two-rank channel per partner, set up by the two ranks alone
+  Status EnsurePairChannel(int peer, uint64_t need_bytes, Channel** chan);
+  Status ExecutePairGossipGpu(Entry& e);
   void FinishEntries(std::vector<Entry>& entries, const Status& s, void* done_event, void* span_start = nullptr);
   // With the timeline on, the device time between span_start and done_event becomes a "DEVICE" span of
   // every tensor of the operation (drawn on its own lane, ending at the moment completion was observed).
@@ -212,6 +216,14 @@ class Runtime {
   // GPU path
   std::unique_ptr<Channel> gpu_channel_;
   std::shared_ptr<SymmBuffer> gpu_ctrl_;
+  struct PairChannel {
+    std::shared_ptr<SymmBuffer> ctrl;
+    std::unique_ptr<Channel> chan;
+  };
+  std::map<int, PairChannel> pair_channels_;   // by partner rank
+  std::mutex pair_mu_;                         // guards the map's structure (completion threads walk it)
+  // First error recorded by a kernel of any channel (device-side wait limits), or OK.
+  Status GpuStatusToError();
   void* comm_stream_ = nullptr;   // cudaStream_t
   std::mutex user_chan_mu_;
 };

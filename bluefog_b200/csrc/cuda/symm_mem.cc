@@ -71,6 +71,42 @@ Status AllocateIpc(ControlPlane* cp, int channel, int device, size_t bytes, std:
   return Status::OK();
 }
 
+Status AllocateIpcPair(ControlPlane* cp, int channel, int peer, int device, size_t bytes,
+                       std::shared_ptr<SymmBuffer>* out) {
+  if (peer < 0 || peer >= cp->size() || peer == cp->rank()) return Status::InvalidArgument("invalid peer for pair memory");
+  auto buf = std::make_shared<SymmBuffer>();
+  buf->rank = cp->rank() > peer ? 1 : 0;
+  buf->world = 2;
+  buf->device = device;
+  buf->bytes = bytes;
+  buf->ipc = true;
+  buf->ptrs.assign(2, nullptr);
+  BFB_CUDA_OK(cudaSetDevice(device));
+  void* mine = nullptr;
+  BFB_CUDA_OK(cudaMalloc(&mine, bytes));
+  BFB_CUDA_OK(cudaMemset(mine, 0, bytes));
+  BFB_CUDA_OK(cudaDeviceSynchronize());     // zeroed before the peer can learn the handle
+  buf->ptrs[buf->rank] = mine;
+  struct Blob {
+    cudaIpcMemHandle_t handle;
+    uint64_t bytes;
+  } out_blob, in_blob;
+  std::memset(&out_blob, 0, sizeof(out_blob));
+  std::memset(&in_blob, 0, sizeof(in_blob));
+  BFB_CUDA_OK(cudaIpcGetMemHandle(&out_blob.handle, mine));
+  out_blob.bytes = bytes;
+  Status s = cp->Exchange(channel, {{peer, &out_blob, sizeof(out_blob)}}, {{peer, &in_blob, sizeof(in_blob)}});
+  if (!s.ok()) return s;
+  if (in_blob.bytes != bytes)
+    return Status::PreconditionError("pair memory: rank " + std::to_string(peer) + " allocated " +
+                                     std::to_string(in_blob.bytes) + " bytes, this rank " + std::to_string(bytes));
+  void* theirs = nullptr;
+  BFB_CUDA_OK(cudaIpcOpenMemHandle(&theirs, in_blob.handle, cudaIpcMemLazyEnablePeerAccess));
+  buf->ptrs[1 - buf->rank] = theirs;
+  *out = buf;
+  return Status::OK();
+}
+
 Status AllocateLocal(int world, int device, size_t bytes, std::vector<std::shared_ptr<SymmBuffer>>* out) {
   BFB_CUDA_OK(cudaSetDevice(device));
   auto owned = std::make_shared<std::vector<void*>>(world, nullptr);

@@ -34,6 +34,10 @@ struct SymmBuffer {
 
 Status AllocateIpc(ControlPlane* cp, int channel, int device, size_t bytes, std::shared_ptr<SymmBuffer>* out);
 Status AllocateLocal(int world, int device, size_t bytes, std::vector<std::shared_ptr<SymmBuffer>>* out);
+// Symmetric memory shared by this rank and one peer only (world = 2; index 0 is the lower of the two ranks).
+// Only the two ranks take part in the exchange of handles, so it can be set up while the others do other work.
+Status AllocateIpcPair(ControlPlane* cp, int channel, int peer, int device, size_t bytes,
+                       std::shared_ptr<SymmBuffer>* out);
 
 std::string CudaErrorString(cudaError_t e);
 #define BFB_CUDA_OK(expr)                                                              \

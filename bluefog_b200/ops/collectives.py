@@ -68,9 +68,9 @@ def _new_spec(op: int, name: str):
     return spec
 
 
-def _stage(tensor: torch.Tensor, force: bool = False):
+def _stage(tensor: torch.Tensor):
     """Optionally move a CUDA tensor to the host (BLUEFOG_OPS_ON_CPU=1)."""
-    if tensor.is_cuda and (force or _ops_on_cpu()):
+    if tensor.is_cuda and _ops_on_cpu():
         return tensor.detach().cpu(), tensor.device
     return tensor, None
 
@@ -456,9 +456,8 @@ def pair_gossip_nonblocking(tensor: torch.Tensor, target_rank: int, self_weight:
         raise ValueError("self_weight and pair_weight have to be set at same time.")
     spec = _new_spec(OP_PAIR_GOSSIP, _full_name("pair.gossip", name))
     spec.negotiate = False  # only two ranks take part
-    # The peer-memory channel numbers its versions in lockstep on all ranks, which an
-    # operation of two ranks would break: CUDA tensors of a gossip pair travel via the host.
-    staged, dev = _stage(tensor, force=True)
+    # CUDA tensors travel over a two-rank peer-memory channel that the partners set up between themselves
+    staged, dev = _stage(tensor)
     output = torch.empty_like(tensor)
     out = output if dev is None else torch.empty_like(staged)
     spec.input, spec.output = staged, out

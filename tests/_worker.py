@@ -538,6 +538,35 @@ def gpu_fast_path():
 
 
 @case
+def gpu_pair_gossip():
+    """pair_gossip of CUDA tensors over the two-rank peer-memory channels: concurrent disjoint pairs,
+    changing partners, weights, a tensor that makes the pair arena grow, 16-bit payloads."""
+    r, n = bf.rank(), bf.size()
+    d = dev()
+    bf.set_skip_negotiate_stage(True)
+    for bit in (1, 2):
+        partner = r ^ bit
+        if partner >= n:
+            continue
+        x = torch.full((1000,), float(r), device=d)
+        close(bf.pair_gossip(x, partner), (r + partner) / 2, 1e-6)
+        close(bf.pair_gossip(x, partner, self_weight=0.25, pair_weight=0.75), 0.25 * r + 0.75 * partner, 1e-6)
+        hs = [bf.pair_gossip_nonblocking(torch.full((64 + k,), float(r + k), device=d), partner, name=f"pg.{bit}.{k}")
+              for k in range(4)]
+        for k, h in enumerate(hs):
+            close(bf.synchronize(h), (r + partner) / 2 + k, 1e-6)
+        big = torch.full((20 * 1024 * 1024 + 3,), float(r), device=d, dtype=torch.bfloat16)   # grows the pair arena
+        out = bf.pair_gossip(big, partner)
+        close(out[:8], (r + partner) / 2, 1e-2)
+        close(out[-8:], (r + partner) / 2, 1e-2)
+        close(bf.pair_gossip(torch.full((7,), float(r), device=d, dtype=torch.float64), partner), (r + partner) / 2, 1e-12)
+    bf.barrier()
+    # a collective of all ranks right after the gossips uses the common channel, whose versions did not move
+    bf.set_skip_negotiate_stage(False)
+    close(bf.allreduce(torch.full((16,), float(r), device=d)), (n - 1) / 2, 1e-6)
+
+
+@case
 def gpu_timeline():
     """With the timeline on, GPU collectives of both issue paths leave a DEVICE span next to the host activities."""
     r = bf.rank()

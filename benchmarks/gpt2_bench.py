@@ -27,6 +27,9 @@ def main():
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--model", default="gpt2_medium", choices=["gpt2_small", "gpt2_medium"])
     ap.add_argument("--no-b200-gemm", action="store_true")
+    ap.add_argument("--exchange-dtype", default="bfloat16", choices=["float32", "bfloat16"],
+                    help="format in which neighbors read each other's parameters (the own term and the master "
+                         "weights stay fp32)")
     ap.add_argument("--no-graphs", action="store_true", help="drive forward/backward op by op instead of a CUDA graph")
     args = ap.parse_args()
     bf.init()
@@ -38,7 +41,8 @@ def main():
     bf.broadcast_parameters(model.state_dict(), root_rank=0)
     opt = bf.DistributedAdaptThenCombineOptimizer(
         torch.optim.AdamW(model.parameters(), lr=3e-4, weight_decay=0.1), model,
-        compute_dtype=torch.bfloat16, bucket_bytes=64 * 1024 * 1024)
+        compute_dtype=torch.bfloat16, exchange_dtype=getattr(torch, args.exchange_dtype),
+        bucket_bytes=64 * 1024 * 1024)
     g = torch.Generator().manual_seed(rank)
     tokens = torch.randint(0, 50257, (args.batch, args.seq + 1), generator=g).to(dev)
     x, y = tokens[:, :-1].contiguous(), tokens[:, 1:].contiguous()
@@ -77,6 +81,7 @@ def main():
         print(json.dumps({"metric": "GPT-2 training throughput (tokens/s), ATC AdamW, ring", "value": round(toks, 1),
                           "unit": "tokens/s", "n_gpus": size, "ms_per_step": round(ms / args.steps, 2),
                           "model": args.model, "batch_per_gpu": args.batch, "seq_len": args.seq, "dtype": "bf16",
+                          "exchange_dtype": args.exchange_dtype,
                           "final_loss": float(loss)}), flush=True)
     bf.barrier()
     bf.shutdown()

@@ -514,12 +514,9 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
       }
       // remote terms
       if (mode == kModeAWC || mode == kModeCombineOnly) {
-        if (mode == kModeAWC) {
-          for (int i = 0; i < 4; ++i) acc[i] = p.self_w * x[i];
-        } else {
-          const PubT* sp = reinterpret_cast<const PubT*>(p.pub_read_self) + i0;
-          for (int i = 0; i < 4; ++i) acc[i] = i < cnt ? p.self_w * PE::load(sp + i) : 0.f;
-        }
+        // the own term comes from the fp32 master in both modes (after the adapt half of adapt-then-combine
+        // the master holds the adapted value), so a 16-bit exchange format only rounds the neighbors' terms
+        for (int i = 0; i < 4; ++i) acc[i] = p.self_w * x[i];
       } else if (mode == kModeGradReduce) {
         for (int i = 0; i < 4; ++i) acc[i] = g[i];
       } else {
@@ -552,11 +549,13 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
       } else {  // publish only: payload is the master (or the gradient when grad != null and opt == none)
         for (int i = 0; i < 4; ++i) y[i] = any_grad ? g[i] : x[i];
       }
-      const bool writes_master = (mode == kModeAWC || mode == kModeCombineOnly || mode == kModeGradReduce);
+      const bool writes_master = (mode == kModeAWC || mode == kModeCombineOnly || mode == kModeGradReduce ||
+                                  (mode == kModeAdaptPublish && p.master != nullptr));
       if (writes_master) {
         if (cnt == 4) *reinterpret_cast<float4*>(p.master + i0) = make_float4(y[0], y[1], y[2], y[3]);
         else for (int i = 0; i < cnt; ++i) p.master[i0 + i] = y[i];
-        if (p.shadow != nullptr) {
+        // the shadow is what the next forward pass reads: only the final value of the step goes there
+        if (p.shadow != nullptr && mode != kModeAdaptPublish) {
           __nv_bfloat16* sh = static_cast<__nv_bfloat16*>(p.shadow) + i0;
           if (cnt == 4) {
             __nv_bfloat162 a = __floats2bfloat162_rn(y[0], y[1]), b = __floats2bfloat162_rn(y[2], y[3]);

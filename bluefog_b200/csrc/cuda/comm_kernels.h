@@ -126,9 +126,9 @@ enum BucketOpt : int { kOptNone = 0, kOptSGD = 1, kOptAdam = 2 };
 enum BucketMode : int {
   // c = self_w*P + sum_j w_j*pub_j(v);  P' = c - step(g, c);  pub(v+1) = P'   (adapt-with-combine)
   kModeAWC = 0,
-  // a = P - step(g, P);  pub(v) = a   (first half of adapt-then-combine; no remote reads)
+  // a = P - step(g, P);  P = a;  pub(v) = a   (first half of adapt-then-combine; no remote reads)
   kModeAdaptPublish = 1,
-  // P' = self_w*pub_self(v) + sum_j w_j*pub_j(v)   (second half of adapt-then-combine)
+  // P' = self_w*P + sum_j w_j*pub_j(v)   (second half of adapt-then-combine; P holds the adapted value)
   kModeCombineOnly = 2,
   // gbar = post_scale*(g_self + sum_j pub_j(v));  P' = P - step(gbar, P)   (gradient allreduce)
   kModeGradReduce = 3,
@@ -159,7 +159,7 @@ struct BucketParams {
   float* state2;                 // exp_avg_sq
   float* state3;                 // max_exp_avg_sq (amsgrad)
   void* shadow;                  // bf16 copy used by forward/backward (optional)
-  const unsigned char* pub_read_self;  // my published half that is read (combine-only mode)
+  const unsigned char* pub_read_self;  // my published half of the version that is pulled (kept for reference; the own term is read from master)
   unsigned char* pub_write;      // my published half that is written (or null)
   // publishing the written half
   int publish;

@@ -409,6 +409,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return std::make_tuple(dx, sums.select(0, 0), sums.select(0, 1));
   });
 
+  m.def("column_sum", [](at::Tensor x) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous() &&
+                x.size(1) % 8 == 0 && x.numel() > 0, "column_sum expects a contiguous bf16 CUDA matrix with C % 8 == 0");
+    c10::cuda::CUDAGuard g(x.get_device());
+    at::Tensor out = at::zeros({x.size(1)}, x.options().dtype(at::kFloat));
+    cudaError_t e = LaunchColumnSum(x.data_ptr(), out.data_ptr<float>(), x.size(0), static_cast<int>(x.size(1)),
+                                    CurrentStream(x.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "column_sum launch failed: ", cudaGetErrorString(e));
+    return out;
+  });
+
   // ---- 3x3/2 max pooling, NHWC bf16 ---------------------------------------------------------
   m.def("maxpool3x3s2_forward", [](at::Tensor x) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.scalar_type() == at::kBFloat16 &&

@@ -197,6 +197,55 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(const __nv_bfloat16* _
   }
 }
 
+// out[c] += sum over rows of x[r, c]  (bf16 [R, C] row-major, fp32 sums; out holds zeros on entry).
+// The bias gradient of a linear layer.  A block owns 256 consecutive columns (one 16-byte vector per lane
+// and row) and a slice of the rows; its warps stride over the rows, fold through shared memory and add
+// each column once to the global sums.
+__global__ void __launch_bounds__(kThreads) column_sum_kernel(const __nv_bfloat16* __restrict__ x,
+                                                              float* __restrict__ out, long long R, int C) {
+  __shared__ float fold[256];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * 256 + lane * 8;
+  const long long chunk = (R + gridDim.y - 1) / gridDim.y;
+  const long long r0 = (long long)blockIdx.y * chunk;
+  const long long r1 = r0 + chunk < R ? r0 + chunk : R;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  if (c0 < C) {
+    constexpr int U = 4;
+    long long r = r0 + warp;
+    for (; r + (long long)(U - 1) * kWarps < r1; r += (long long)U * kWarps) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = *reinterpret_cast<const uint4*>(x + (r + (long long)u * kWarps) * C + c0);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float f[8];
+        unpack8(v[u], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+    }
+    for (; r < r1; r += kWarps) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + r * C + c0), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+  }
+  for (int i = threadIdx.x; i < 256; i += kThreads) fold[i] = 0.f;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) atomicAdd(&fold[lane * 8 + i], acc[i]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < 256; i += kThreads) {
+    const int c = blockIdx.x * 256 + i;
+    if (c < C) atomicAdd(&out[c], fold[i]);
+  }
+}
+
 int SmCount() {
   static int sms = [] {
     int dev = 0, n = 148;
@@ -257,6 +306,19 @@ cudaError_t LaunchLnBackward(const void* dy, const void* x, const void* gamma, c
   BFB_LN_DISPATCH(nv, (ln_bwd_kernel<NV><<<GridForBackward(R), kThreads, 0, stream>>>(
                           static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), gamma, mean,
                           rstd, static_cast<__nv_bfloat16*>(dx), dgamma_zeroed, dbeta_zeroed, R, C, param_bf16)));
+  CountKernelLaunch();
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchColumnSum(const void* x, float* out_zeroed, long long R, int C, cudaStream_t stream) {
+  if (R <= 0 || C < 8 || (C % 8) != 0) return cudaErrorInvalidValue;
+  const int col_blocks = (C + 255) / 256;
+  long long row_blocks = (SmCount() * 4 + col_blocks - 1) / col_blocks;
+  const long long max_rows = (R + kWarps * 4 - 1) / (kWarps * 4);      // at least four rows per warp
+  if (row_blocks > max_rows) row_blocks = max_rows;
+  if (row_blocks < 1) row_blocks = 1;
+  column_sum_kernel<<<dim3(static_cast<unsigned>(col_blocks), static_cast<unsigned>(row_blocks)), kThreads, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), out_zeroed, R, C);
   CountKernelLaunch();
   return cudaGetLastError();
 }

@@ -16,4 +16,7 @@ cudaError_t LaunchLnBackward(const void* dy, const void* x, const void* gamma, c
                              void* dx, float* dgamma_zeroed, float* dbeta_zeroed, long long R, int C, int param_bf16,
                              cudaStream_t stream);
 
+// out_zeroed[c] += sum_r x[r, c] for a bf16 [R, C] row-major matrix (C % 8 == 0); fp32 sums that hold zeros on entry.
+cudaError_t LaunchColumnSum(const void* x, float* out_zeroed, long long R, int C, cudaStream_t stream);
+
 }  // namespace bfb

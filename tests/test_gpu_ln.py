@@ -48,3 +48,14 @@ def test_layer_norm_module_falls_back_for_fp32():
     ln = LayerNorm(48).cuda()
     x = torch.randn(4, 48, device="cuda")
     torch.testing.assert_close(ln(x), F.layer_norm(x, (48,), ln.weight, ln.bias, ln.eps))
+
+
+@pytest.mark.parametrize("R,C", [(8192, 4096), (8192, 1024), (37, 8), (1000, 264), (3, 3072)])
+def test_column_sum_matches_fp32_sum(R, C):
+    from bluefog_b200 import _C
+    torch.manual_seed(R + C)
+    x = torch.randn(R, C, device="cuda").to(torch.bfloat16)
+    out = _C.column_sum(x)
+    ref = x.float().sum(0)
+    assert out.dtype == torch.float32
+    assert (out - ref).abs().max().item() <= 1e-3 * max(1.0, ref.abs().max().item())

@@ -118,6 +118,29 @@ def bench_conv(args):
             "library_ms": ms_lib, "library_tflops": flops / ms_lib / 1e9, "status": _C.gemm_status()}
 
 
+def bench_ln(args):
+    """LayerNorm forward/backward on [rows, 1024] and the bias-gradient column sum on [rows/4, 4096] (both
+    134 MB at the default 65536 rows: larger than L2)."""
+    rows = args.ln_rows
+    x = torch.randn(rows, 1024, device="cuda").to(torch.bfloat16)
+    w, b = torch.ones(1024, device="cuda"), torch.zeros(1024, device="cuda")
+    dy = torch.randn_like(x)
+    wide = torch.randn(max(rows // 4, 8), 4096, device="cuda").to(torch.bfloat16)
+    y, mean, rstd = _C.ln_forward(x, w, b, 1e-5)
+    nb = x.numel() * 2
+    ms_f = timed(lambda: _C.ln_forward(x, w, b, 1e-5), args.iters, args.warmup)
+    ms_b = timed(lambda: _C.ln_backward(dy, x, w, mean, rstd), args.iters, args.warmup)
+    ms_c = timed(lambda: _C.column_sum(wide), args.iters, args.warmup)
+    ms_t = timed(lambda: wide.sum(0, dtype=torch.float32), args.iters, args.warmup)
+    ms_tf = timed(lambda: torch.nn.functional.layer_norm(x, (1024,), w.bfloat16(), b.bfloat16()), args.iters, args.warmup)
+    peak = PEAKS["hbm_gbs"]
+    return {"kernel": "ln_fwd_kernel / ln_bwd_kernel / column_sum_kernel", "rows": rows,
+            "ln_fwd_ms": ms_f, "ln_fwd_frac_of_measured_hbm": 2 * nb / ms_f / 1e6 / peak,       # read x, write y
+            "ln_bwd_ms": ms_b, "ln_bwd_frac_of_measured_hbm": 3 * nb / ms_b / 1e6 / peak,       # read dy, x, write dx
+            "column_sum_ms": ms_c, "column_sum_frac_of_measured_hbm": wide.numel() * 2 / ms_c / 1e6 / peak,
+            "pytorch_layer_norm_fwd_ms": ms_tf, "pytorch_sum_ms": ms_t}
+
+
 def bench_bn(args):
     n, c, h, w = args.bn_shape
     x = torch.randn(n, c, h, w, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
@@ -144,7 +167,8 @@ def bench_bn(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", required=True, choices=["bucket", "combine", "gemm", "bn", "conv"])
+    ap.add_argument("--kernel", required=True, choices=["bucket", "combine", "gemm", "bn", "conv", "ln"])
+    ap.add_argument("--ln-rows", type=int, default=65536)
     ap.add_argument("--conv-shape", type=int, nargs=5, default=[64, 64, 64, 56, 56], metavar=("N", "CIN", "COUT", "H", "W"))
     ap.add_argument("--bn-shape", type=int, nargs=4, default=[64, 256, 56, 56])
     ap.add_argument("--numel", type=int, default=64 * 1024 * 1024)
@@ -157,7 +181,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
     torch.cuda.set_device(0)
-    out = {"bucket": bench_bucket, "combine": bench_combine, "gemm": bench_gemm, "bn": bench_bn, "conv": bench_conv}[args.kernel](args)
+    out = {"bucket": bench_bucket, "combine": bench_combine, "gemm": bench_gemm, "bn": bench_bn, "conv": bench_conv, "ln": bench_ln}[args.kernel](args)
     print(json.dumps(out), flush=True)
 
 

@@ -17,6 +17,7 @@
 #include "cuda/gpu_channel.h"
 #include "cuda/ln_kernels.h"
 #include "cuda/pool_kernels.h"
+#include "cuda/stem_kernels.h"
 #include "cuda/symm_mem.h"
 
 namespace py = pybind11;
@@ -417,6 +418,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     cudaError_t e = LaunchColumnSum(x.data_ptr(), out.data_ptr<float>(), x.size(0), static_cast<int>(x.size(1)),
                                     CurrentStream(x.get_device()));
     TORCH_CHECK(e == cudaSuccess, "column_sum launch failed: ", cudaGetErrorString(e));
+    return out;
+  });
+
+  // ---- space-to-depth input of the ResNet stem -------------------------------------------------
+  m.def("s2d_stem_input", [](at::Tensor x) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.size(1) == 3 && x.size(2) % 2 == 0 && x.size(3) % 2 == 0 &&
+                (x.scalar_type() == at::kFloat || x.scalar_type() == at::kBFloat16),
+                "s2d_stem_input expects a [N, 3, H, W] fp32 or bf16 CUDA tensor with even H and W");
+    c10::cuda::CUDAGuard g(x.get_device());
+    const int N = static_cast<int>(x.size(0)), H = static_cast<int>(x.size(2)), W = static_cast<int>(x.size(3));
+    at::Tensor out = at::empty({N, 16, (H + 6) / 2, (W + 6) / 2},
+                               x.options().dtype(at::kBFloat16).memory_format(at::MemoryFormat::ChannelsLast));
+    cudaError_t e = LaunchS2dStemInput(x.data_ptr(), x.scalar_type() == at::kBFloat16 ? 1 : 0, out.data_ptr(), N, H, W,
+                                       x.stride(0), x.stride(1), x.stride(2), x.stride(3), CurrentStream(x.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "s2d_stem_input launch failed: ", cudaGetErrorString(e));
     return out;
   });
 

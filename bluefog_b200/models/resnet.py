@@ -80,16 +80,27 @@ class StemConv(nn.Conv2d):
             return self.forward_space_to_depth(x)
         return super().forward(x)
 
-    def forward_space_to_depth(self, x):
-        n, c, h, w = x.shape
+    def space_to_depth_weight(self):
+        """[64, 3, 7, 7] -> [64, 16, 4, 4] channels_last (kernel padded to 8x8, 2x2 blocks folded into channels)."""
         w8 = F.pad(self.weight, (0, 1, 0, 1))
         w12 = w8.view(64, 3, 4, 2, 4, 2).permute(0, 1, 3, 5, 2, 4).reshape(64, 12, 4, 4)
-        w16 = F.pad(w12, (0, 0, 0, 0, 0, 4)).contiguous(memory_format=torch.channels_last)
+        return F.pad(w12, (0, 0, 0, 0, 0, 4)).contiguous(memory_format=torch.channels_last)
+
+    def forward_space_to_depth(self, x):
+        n, c, h, w = x.shape
+        w16 = self.space_to_depth_weight()
         hb, wb = (h + 6) // 2, (w + 6) // 2
         xp = F.pad(x, (3, 3, 3, 3))
         xs = xp.reshape(n, 3, hb, 2, wb, 2).permute(0, 1, 3, 5, 2, 4).reshape(n, 12, hb, wb)
         xs = F.pad(xs, (0, 0, 0, 0, 0, 4)).contiguous(memory_format=torch.channels_last)
         return F.conv2d(xs, w16)
+
+    def forward_from_raw(self, x):
+        """The same convolution for an input that still is what the data loader delivered (fp32 or bf16, NCHW
+        or NHWC, no gradient): padding, space-to-depth, cast and layout change happen in one kernel."""
+        from bluefog_b200.common.basics import get_basics
+        xs = get_basics().native.s2d_stem_input(x)
+        return F.conv2d(xs, self.space_to_depth_weight())
 
 
 class Downsample(nn.Sequential):
@@ -206,16 +217,21 @@ class ResNet(nn.Module):
         return nn.Sequential(*layers)
 
     def forward(self, x):
-        if x.is_cuda and x.dim() == 4:
-            x = x.contiguous(memory_format=torch.channels_last)
-        if x.dtype != self.conv1.weight.dtype:
-            x = x.to(self.conv1.weight.dtype)
+        raw_stem = (self.conv1.space_to_depth and x.is_cuda and x.dim() == 4 and not x.requires_grad
+                    and self.conv1.weight.dtype == torch.bfloat16 and x.dtype in (torch.float32, torch.bfloat16)
+                    and x.shape[1] == 3 and x.shape[2] % 2 == 0 and x.shape[3] % 2 == 0)
+        if not raw_stem:
+            if x.is_cuda and x.dim() == 4:
+                x = x.contiguous(memory_format=torch.channels_last)
+            if x.dtype != self.conv1.weight.dtype:
+                x = x.to(self.conv1.weight.dtype)
         if self.training:
             fused_bn.begin_step(x.device)          # one memset for the statistics scratch of all layers
             counters = [m.num_batches_tracked for m in self._bn_modules if m.num_batches_tracked is not None]
             if counters:
                 torch._foreach_add_(counters, 1)     # one launch for the batch counters of all layers
-        x = maxpool3x3s2(bn_act(self.conv1(x), self.bn1, relu=True))
+        stem = self.conv1.forward_from_raw(x) if raw_stem else self.conv1(x)
+        x = maxpool3x3s2(bn_act(stem, self.bn1, relu=True))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         x = torch.flatten(self.avgpool(x), 1)
         if self.use_b200_gemm is True and x.is_cuda and x.dtype == torch.bfloat16:

@@ -525,6 +525,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return out;
   }, py::arg("a"), py::arg("b"));
 
+  m.def("gemm_bf16_tn", [](at::Tensor a, at::Tensor b) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.scalar_type() == at::kBFloat16 &&
+                b.scalar_type() == at::kBFloat16 && a.is_contiguous() && b.is_contiguous() && a.size(0) == b.size(0),
+                "gemm_bf16_tn expects contiguous bf16 CUDA matrices [K,M] and [K,N]");
+    c10::cuda::CUDAGuard g(a.get_device());
+    at::Tensor& status = GemmStatusWord(a);
+    at::Tensor out = at::empty({a.size(1), b.size(1)}, a.options());
+    cudaError_t e = LaunchGemmBf16TN(a.data_ptr(), b.data_ptr(), out.data_ptr(), static_cast<int>(a.size(1)),
+                                     static_cast<int>(b.size(1)), static_cast<int>(a.size(0)),
+                                     reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(a.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "gemm_bf16_tn launch failed: ", cudaGetErrorString(e));
+    return out;
+  }, py::arg("a"), py::arg("b"));
+
   m.def("gemm_status", [] {
     at::Tensor probe = at::empty({0}, at::TensorOptions().device(at::kCUDA));
     return GemmStatusWord(probe).item<int>();

@@ -254,27 +254,17 @@ conv3x3_nhwc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 }
 
 bool MakeMap4d(CUtensorMap* map, const void* base, int C, int W, int H, int N, int bw, int bh, int bn) {
-  EncodeTiledFn fn = GetEncodeFn();
-  if (fn == nullptr) return false;
-  cuuint64_t dims[4] = {cuuint64_t(C), cuuint64_t(W), cuuint64_t(H), cuuint64_t(N)};
-  cuuint64_t strides[3] = {cuuint64_t(C) * 2, cuuint64_t(W) * C * 2, cuuint64_t(H) * W * C * 2};
-  cuuint32_t box[4] = {64, cuuint32_t(bw), cuuint32_t(bh), cuuint32_t(bn)};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const cuuint64_t dims[4] = {cuuint64_t(C), cuuint64_t(W), cuuint64_t(H), cuuint64_t(N)};
+  const cuuint64_t strides[3] = {cuuint64_t(C) * 2, cuuint64_t(W) * C * 2, cuuint64_t(H) * W * C * 2};
+  const cuuint32_t box[4] = {64, cuuint32_t(bw), cuuint32_t(bh), cuuint32_t(bn)};
+  return EncodeTiled(map, 4, base, dims, strides, box);
 }
 
 bool MakeMap2d(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
-  EncodeTiledFn fn = GetEncodeFn();
-  if (fn == nullptr) return false;
-  cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
-  cuuint64_t strides[1] = {cuuint64_t(cols) * 2};
-  cuuint32_t box[2] = {64, cuuint32_t(box_rows)};
-  cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(cols) * 2};
+  const cuuint32_t box[2] = {64, cuuint32_t(box_rows)};
+  return EncodeTiled(map, 2, base, dims, strides, box);
 }
 
 int SmCount() {

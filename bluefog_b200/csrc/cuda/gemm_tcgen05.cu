@@ -222,7 +222,10 @@ struct PersistentCfg {
 // MN-major operand: every ring stage holds BN_/64 boxes of [64 K-rows x 64 N-columns] (8 KiB each, 128-byte
 // swizzle); the descriptor's leading-dimension stride is the distance between boxes, its stride-dimension
 // stride the 1024 bytes between groups of eight K-rows, and one MMA step advances 16 rows = 2048 bytes.
-template <int BN_, int BMODE = 0>
+// AMODE 1: A is given as [K, M] row-major (the transposed product dY^T * X of a weight gradient) and is
+// consumed MN-major in the same way: two boxes of [64 K-rows x 64 M-columns] per stage, bit 15 of the
+// instruction descriptor.
+template <int BN_, int BMODE = 0, int AMODE = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ out,
@@ -283,7 +286,13 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
           if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, failed)) { ok = false; break; }
           const uint32_t full = smem_u32(&bars[s]);
           mbar_expect_tx(full, Cfg::kBytesStage);
-          tma_load_2d(smem_u32(stage_a + size_t(s) * Cfg::kBytesA), &map_a, full, kb * BK, m0);
+          if (AMODE == 0) {
+            tma_load_2d(smem_u32(stage_a + size_t(s) * Cfg::kBytesA), &map_a, full, kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(smem_u32(stage_a + size_t(s) * Cfg::kBytesA + size_t(j) * 8192), &map_a, full, m0 + j * 64, kb * BK);
+          }
           if (BMODE == 0) {
             tma_load_2d(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), &map_b, full, kb * BK, n0);
           } else {
@@ -309,11 +318,13 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
           const int s = it % S;
           if (!mbar_wait(smem_u32(&bars[s]), (it / S) & 1, failed)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint64_t adesc = make_desc(smem_u32(stage_a + size_t(s) * Cfg::kBytesA));
+          const uint32_t a_addr = smem_u32(stage_a + size_t(s) * Cfg::kBytesA);
+          const uint64_t adesc = AMODE == 0 ? make_desc(a_addr) : make_desc_mn(a_addr, 8192, 1024);
           const uint32_t b_addr = smem_u32(stage_b + size_t(s) * Cfg::kBytesB);
           const uint64_t bdesc = BMODE == 0 ? make_desc(b_addr) : make_desc_mn(b_addr, 8192, 1024);
-          // MN-major B: bit 16 of the instruction descriptor; 16 K-rows of 128 bytes per MMA step
-          constexpr uint32_t idesc = Cfg::kIdesc | (BMODE != 0 ? (1u << 16) : 0u);
+          // MN-major operands: bits 15 (A) and 16 (B) of the instruction descriptor; 16 K-rows of 128 bytes per MMA step
+          constexpr uint32_t idesc = Cfg::kIdesc | (AMODE != 0 ? (1u << 15) : 0u) | (BMODE != 0 ? (1u << 16) : 0u);
+          constexpr uint64_t a_step = AMODE == 0 ? 2 : (16 * 128) >> 4;
           constexpr uint64_t b_step = BMODE == 0 ? 2 : (16 * 128) >> 4;
 #pragma unroll
           for (int k = 0; k < BK / kUmmaK; ++k) {
@@ -321,7 +332,7 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                 "{\n\t.reg .pred p;\n\t"
                 "setp.ne.b32 p, %4, 0;\n\t"
                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                ::"r"(tmem_d), "l"(adesc + uint64_t(2 * k)), "l"(bdesc + b_step * uint64_t(k)), "r"(idesc),
+                ::"r"(tmem_d), "l"(adesc + a_step * uint64_t(k)), "l"(bdesc + b_step * uint64_t(k)), "r"(idesc),
                   "r"((kb | k) != 0 ? 1u : 0u)
                 : "memory");
           }
@@ -443,15 +454,10 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 }
 
 bool MakeMap(CUtensorMap* map, const void* base, int rows, int cols /*K*/, int box_rows) {
-  EncodeTiledFn fn = GetEncodeFn();
-  if (fn == nullptr) return false;
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
-  cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+  return EncodeTiled(map, 2, base, dims, strides, box);
 }
 
 }  // namespace
@@ -460,6 +466,7 @@ bool GemmSupported() { return GetEncodeFn() != nullptr; }
 
 cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void* bias, int M, int N, int K, int act,
                              unsigned int* status, cudaStream_t stream) {
+  (void)cudaGetLastError();   // the value returned below must be this launch's own, not an older error of the calling thread
   if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
   // TMA needs 16-byte aligned bases and row pitches: K must be a multiple of 8 bf16 elements.
   if ((K % 8) != 0 || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) ||
@@ -527,6 +534,7 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
 // product with a transposed weight (an input gradient) needs no transposed copy.
 cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int N, int K, unsigned int* status,
                              cudaStream_t stream) {
+  (void)cudaGetLastError();   // the value returned below must be this launch's own, not an older error of the calling thread
   if (M <= 0 || N <= 0 || K <= 0 || (K % 8) != 0 || (N % 8) != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
     return cudaErrorInvalidValue;
@@ -563,6 +571,53 @@ cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int
     }
     const int tiles = ((M + BM - 1) / BM) * ((N + 127) / 128);
     gemm_bf16_nt_persistent_kernel<128, 1><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
+        map_a, map_b, map_c, o, nullptr, M, N, K, 0, 1, status);
+  }
+  CountKernelLaunch();
+  return cudaGetLastError();
+}
+
+// out[M,N] = a[K,M]^T * b[K,N]: both operands row-major with the reduction dimension outermost (the weight
+// gradient dW = dY^T X of a linear layer: a = dY [rows, N_out], b = X [rows, K_in]); both are consumed MN-major.
+cudaError_t LaunchGemmBf16TN(const void* a, const void* b, void* out, int M, int N, int K, unsigned int* status,
+                             cudaStream_t stream) {
+  (void)cudaGetLastError();   // the value returned below must be this launch's own, not an older error of the calling thread
+  if (M <= 0 || N <= 0 || K <= 0 || (M % 8) != 0 || (N % 8) != 0) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return cudaErrorInvalidValue;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  CUtensorMap map_a, map_b, map_c;
+  // A: [K rows, M columns], B: [K rows, N columns]; boxes of 64 columns (128 bytes) x 64 rows
+  if (!MakeMap(&map_a, a, K, M, 64) || !MakeMap(&map_b, b, K, N, 64) || !MakeMap(&map_c, out, M, N, 32))
+    return cudaErrorInvalidValue;
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+  if (N > 128) {
+    using Cfg = PersistentCfg<256>;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<256, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
+      if (e != cudaSuccess) return e;
+      attr_set = true;
+    }
+    const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+    gemm_bf16_nt_persistent_kernel<256, 1, 1><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
+        map_a, map_b, map_c, o, nullptr, M, N, K, 0, 1, status);
+  } else {
+    using Cfg = PersistentCfg<128>;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<128, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
+      if (e != cudaSuccess) return e;
+      attr_set = true;
+    }
+    const int tiles = ((M + BM - 1) / BM) * ((N + 127) / 128);
+    gemm_bf16_nt_persistent_kernel<128, 1, 1><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
         map_a, map_b, map_c, o, nullptr, M, N, K, 0, 1, status);
   }
   CountKernelLaunch();

@@ -19,4 +19,8 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
 cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int N, int K, unsigned int* status,
                              cudaStream_t stream);
 
+// out[M,N] = a[K,M]^T * b[K,N], a and b row-major (both consumed MN-major); M % 8 == 0, N % 8 == 0.
+cudaError_t LaunchGemmBf16TN(const void* a, const void* b, void* out, int M, int N, int K, unsigned int* status,
+                             cudaStream_t stream);
+
 }  // namespace bfb

@@ -141,5 +141,26 @@ inline EncodeTiledFn GetEncodeFn() {
   return fn;
 }
 
+// cuTensorMapEncodeTiled for the calling thread.  A thread that has not yet made a runtime call that binds
+// the device's primary context (an autograd worker whose first CUDA work is one of these launchers) gets
+// CUDA_ERROR_INVALID_CONTEXT from the driver entry point: bind the context and encode once more.
+inline bool EncodeTiled(CUtensorMap* map, cuuint32_t rank, const void* base, const cuuint64_t* dims,
+                        const cuuint64_t* strides, const cuuint32_t* box) {
+  EncodeTiledFn fn = GetEncodeFn();
+  if (fn == nullptr) return false;
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  auto encode = [&] {
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode();
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    cudaFree(nullptr);
+    r = encode();
+  }
+  return r == CUDA_SUCCESS;
+}
+
 }  // namespace t5
 }  // namespace bfb

@@ -2,8 +2,9 @@
 
 ``linear(a, w, bias)`` computes ``a @ w.T + bias`` for row-major bf16 ``a`` [M, K] and
 ``w`` [N, K] with fp32 accumulation in tensor memory.  The backward pass computes dA = dY @ W on the
-same kernel with W read in place as an MN-major operand; dW = dY.T @ A goes to the library GEMM
-(see ``_LinearFn.backward``).
+same kernel with W read in place as an MN-major operand, and dW = dY.T @ A with both operands read
+MN-major (products with too few output tiles for a kernel without split-K go to the library, see
+``_LinearFn.backward``).
 """
 import torch
 
@@ -31,6 +32,10 @@ def _nt_ok(m_rows, n_rows, k):
     return k % 8 == 0 and m_rows > 0 and n_rows > 0
 
 
+# Weight gradients with fewer output tiles (128 x 256) than this leave most SMs idle in a kernel without split-K
+_TN_MIN_TILES = 120
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, a, w, bias):
@@ -51,10 +56,15 @@ class _LinearFn(torch.autograd.Function):
             else:
                 da = dy @ w
         if ctx.needs_input_grad[1]:
-            # dW[N,K] = dY^T @ A reduces over the (huge) row dimension of two activation matrices.
-            # Both operands are MN-major for that product and it wants split-K; it is left to the
-            # library GEMM, which takes the transposed views without copies.
-            dw = dy.t() @ a
+            # dW[N,K] = dY^T @ A reduces over the rows of two activation matrices: both operands are MN-major
+            # for that product and the kernel reads them in place.  It has no split-K, so a product with
+            # few output tiles and a long reduction (the 1x1 convolutions) stays on the library.
+            n_out, k_in = dy.shape[1], a.shape[1]
+            tiles = ((n_out + 127) // 128) * ((k_in + 255) // 256)
+            if n_out % 8 == 0 and k_in % 8 == 0 and tiles >= _TN_MIN_TILES and hasattr(_b.native, "gemm_bf16_tn"):
+                dw = _b.native.gemm_bf16_tn(dy, a)
+            else:
+                dw = dy.t() @ a
         if ctx.has_bias and ctx.needs_input_grad[2]:
             if dy.shape[1] % 8 == 0 and hasattr(_b.native, "column_sum"):
                 db = _b.native.column_sum(dy).to(dy.dtype)       # fp32 sums of the bf16 gradient in one pass

@@ -94,3 +94,34 @@ def test_gemm_nn_reads_row_major_b_as_mn_major_operand(M, N, K):
     err = (out - ref).abs().max().item()
     assert err <= 1e-2 * max(1.0, ref.abs().max().item()), err
     assert _C.gemm_status() == 0
+
+
+@pytest.mark.parametrize("K,M,N", [(64, 128, 64), (256, 256, 256), (1000, 200, 72), (8192, 4096, 1024), (4100, 1024, 3072)])
+def test_gemm_tn_reads_both_operands_mn_major(K, M, N):
+    """a[K,M]^T @ b[K,N] with both matrices in their row-major memory (the weight-gradient product dY^T X)."""
+    from bluefog_b200 import _C
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(K, M, device="cuda") * 0.5).to(torch.bfloat16)
+    b = (torch.randn(K, N, device="cuda") * 0.5).to(torch.bfloat16)
+    out = _C.gemm_bf16_tn(a, b).float()
+    ref = a.float().t() @ b.float()
+    err = (out - ref).abs().max().item()
+    assert err <= 1e-2 * max(1.0, ref.abs().max().item()), err
+    assert _C.gemm_status() == 0
+
+
+def test_linear_backward_runs_all_three_products_on_the_kernel():
+    from bluefog_b200 import _C
+    from bluefog_b200.ops import gemm
+    torch.manual_seed(3)
+    a = (torch.randn(2048, 1024, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(4096, 1024, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_(True)   # 32 x 4 output tiles
+    b = torch.zeros(4096, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn(2048, 4096, device="cuda").to(torch.bfloat16)
+    before = _C.kernel_launch_count()
+    gemm.linear(a, w, b).backward(dy)
+    assert _C.kernel_launch_count() - before >= 4          # forward, input gradient, weight gradient, bias gradient
+    a2, w2 = a.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    torch.nn.functional.linear(a2, w2).backward(dy.float())
+    for got, ref in ((a.grad, a2.grad), (w.grad, w2.grad), (b.grad, dy.float().sum(0))):
+        assert (got.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())

@@ -94,14 +94,27 @@ def bench_combine(args):
 
 
 def bench_gemm(args):
-    a = (torch.randn(args.m, args.k, device="cuda") * 0.1).to(torch.bfloat16)
-    w = (torch.randn(args.n, args.k, device="cuda") * 0.1).to(torch.bfloat16)
-    ms = timed(lambda: _C.gemm_bf16_nt(a, w, None, 0), args.iters, args.warmup)
-    ms_lib = timed(lambda: torch.matmul(a, w.t()), args.iters, args.warmup)
-    flops = 2.0 * args.m * args.n * args.k
-    nbytes = 2.0 * (args.m * args.k + args.n * args.k + args.m * args.n)     # A, B read once, C written once
-    return {"kernel": "gemm_bf16_nt_kernel (tcgen05)", "m": args.m, "n": args.n, "k": args.k, "ms": ms,
-            "tflops": flops / ms / 1e9, "frac_of_measured_bf16": flops / ms / 1e9 / PEAKS["bf16_tflops"],
+    """--gemm-layout nt: a[M,K] w[N,K]^T (forward);  nn: a[M,K] b[K,N] (input gradient);  tn: a[K,M]^T b[K,N] (weight
+    gradient).  M, N, K are the extents of the product in every layout."""
+    m, n, k = args.m, args.n, args.k
+    if args.gemm_layout == "nt":
+        a = (torch.randn(m, k, device="cuda") * 0.1).to(torch.bfloat16)
+        w = (torch.randn(n, k, device="cuda") * 0.1).to(torch.bfloat16)
+        ours, lib = (lambda: _C.gemm_bf16_nt(a, w, None, 0)), (lambda: torch.matmul(a, w.t()))
+    elif args.gemm_layout == "nn":
+        a = (torch.randn(m, k, device="cuda") * 0.1).to(torch.bfloat16)
+        w = (torch.randn(k, n, device="cuda") * 0.1).to(torch.bfloat16)
+        ours, lib = (lambda: _C.gemm_bf16_nn(a, w)), (lambda: torch.matmul(a, w))
+    else:
+        a = (torch.randn(k, m, device="cuda") * 0.1).to(torch.bfloat16)
+        w = (torch.randn(k, n, device="cuda") * 0.1).to(torch.bfloat16)
+        ours, lib = (lambda: _C.gemm_bf16_tn(a, w)), (lambda: torch.matmul(a.t(), w))
+    ms = timed(ours, args.iters, args.warmup)
+    ms_lib = timed(lib, args.iters, args.warmup)
+    flops = 2.0 * m * n * k
+    nbytes = 2.0 * (m * k + n * k + m * n)     # A, B read once, C written once
+    return {"kernel": "gemm_bf16_nt_persistent_kernel (tcgen05)", "layout": args.gemm_layout, "m": m, "n": n, "k": k,
+            "ms": ms, "tflops": flops / ms / 1e9, "frac_of_measured_bf16": flops / ms / 1e9 / PEAKS["bf16_tflops"],
             "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / PEAKS["hbm_gbs"],
             "library_ms": ms_lib, "library_tflops": flops / ms_lib / 1e9, "status": _C.gemm_status()}
 
@@ -174,6 +187,7 @@ def main():
     ap.add_argument("--numel", type=int, default=64 * 1024 * 1024)
     ap.add_argument("--dtype", default="float32")
     ap.add_argument("--exchange", default="float32", choices=["float32", "bfloat16"])
+    ap.add_argument("--gemm-layout", default="nt", choices=["nt", "nn", "tn"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)

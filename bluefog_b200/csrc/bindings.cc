@@ -12,6 +12,7 @@
 #include "common/windows.h"
 #include "cuda/bn_kernels.h"
 #include "cuda/bucket.h"
+#include "cuda/ce_kernels.h"
 #include "cuda/conv_tcgen05.h"
 #include "cuda/gemm_tcgen05.h"
 #include "cuda/gpu_channel.h"
@@ -434,6 +435,37 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                        x.stride(0), x.stride(1), x.stride(2), x.stride(3), CurrentStream(x.get_device()));
     TORCH_CHECK(e == cudaSuccess, "s2d_stem_input launch failed: ", cudaGetErrorString(e));
     return out;
+  });
+
+  // ---- mean cross-entropy of bf16 logits ------------------------------------------------------
+  m.def("cross_entropy_forward", [](at::Tensor logits, at::Tensor target) {
+    TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.scalar_type() == at::kBFloat16 && logits.is_contiguous() &&
+                logits.size(1) % 8 == 0 && logits.size(0) > 0, "cross_entropy_forward expects contiguous bf16 logits [R, C], C % 8 == 0");
+    TORCH_CHECK(target.is_cuda() && target.scalar_type() == at::kLong && target.is_contiguous() &&
+                target.numel() == logits.size(0), "cross_entropy_forward expects int64 targets [R]");
+    c10::cuda::CUDAGuard g(logits.get_device());
+    at::Tensor lse = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+    at::Tensor loss = at::zeros({}, logits.options().dtype(at::kFloat));
+    cudaError_t e = LaunchCrossEntropyForward(logits.data_ptr(), reinterpret_cast<const long long*>(target.data_ptr<int64_t>()),
+                                              lse.data_ptr<float>(), loss.data_ptr<float>(), logits.size(0),
+                                              static_cast<int>(logits.size(1)), CurrentStream(logits.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "cross_entropy_forward launch failed: ", cudaGetErrorString(e));
+    return std::make_tuple(loss, lse);
+  });
+  m.def("cross_entropy_backward", [](at::Tensor logits, at::Tensor target, at::Tensor lse, at::Tensor grad_out) {
+    TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.scalar_type() == at::kBFloat16 && logits.is_contiguous() &&
+                logits.size(1) % 8 == 0, "cross_entropy_backward expects contiguous bf16 logits [R, C], C % 8 == 0");
+    TORCH_CHECK(grad_out.is_cuda() && grad_out.scalar_type() == at::kFloat && grad_out.numel() == 1 &&
+                lse.scalar_type() == at::kFloat && lse.numel() == logits.size(0) && target.scalar_type() == at::kLong &&
+                target.numel() == logits.size(0), "cross_entropy_backward: mismatched arguments");
+    c10::cuda::CUDAGuard g(logits.get_device());
+    at::Tensor dx = at::empty_like(logits);
+    cudaError_t e = LaunchCrossEntropyBackward(logits.data_ptr(), reinterpret_cast<const long long*>(target.data_ptr<int64_t>()),
+                                               lse.data_ptr<float>(), grad_out.data_ptr<float>(), dx.data_ptr(),
+                                               logits.size(0), static_cast<int>(logits.size(1)),
+                                               CurrentStream(logits.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "cross_entropy_backward launch failed: ", cudaGetErrorString(e));
+    return dx;
   });
 
   // ---- 3x3/2 max pooling, NHWC bf16 ---------------------------------------------------------

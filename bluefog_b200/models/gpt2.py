@@ -121,7 +121,8 @@ class GPT2(nn.Module):
             logits[:, vocab:] = float("-inf")
         if targets is None:
             return logits[:, :vocab].reshape(b, t, vocab)
-        return F.cross_entropy(logits.float(), targets.reshape(-1))
+        from bluefog_b200.ops.fused_ce import cross_entropy
+        return cross_entropy(logits, targets.reshape(-1))
 
 
 def gpt2_small(**kw):

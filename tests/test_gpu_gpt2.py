@@ -30,3 +30,25 @@ def test_gpt2_bf16_kernels_match_fp32_reference():
     assert rel < 0.08, rel
     g2, g2_ref = fast.h[0].mlp.c_fc.weight.grad.float(), ref.h[0].mlp.c_fc.weight.grad
     assert ((g2 - g2_ref).norm() / g2_ref.norm()).item() < 0.08
+
+
+@pytest.mark.parametrize("R,C,pad", [(64, 1008, 7), (1000, 50304, 47), (3, 8, 0), (257, 4096, 0)])
+def test_fused_cross_entropy_matches_fp32(R, C, pad):
+    from bluefog_b200.ops.fused_ce import cross_entropy
+    torch.manual_seed(R + C)
+    logits = (torch.randn(R, C, device="cuda") * 3).to(torch.bfloat16)
+    if pad:
+        logits[:, C - pad:] = float("-inf")
+    targets = torch.randint(0, C - pad, (R,), device="cuda")
+    a = logits.clone().requires_grad_(True)
+    loss = cross_entropy(a, targets)
+    (loss * 2.5).backward()                      # a non-trivial upstream gradient
+    b = logits.float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(b, targets)
+    (ref * 2.5).backward()
+    assert loss.dtype == torch.float32 and abs(loss.item() - ref.item()) < 1e-3 * max(1.0, abs(ref.item()))
+    assert a.grad.dtype == torch.bfloat16
+    err = (a.grad.float() - b.grad).abs().max().item()
+    assert err <= 1e-2 * max(b.grad.abs().max().item(), 1e-6), err
+    if pad:
+        assert a.grad[:, C - pad:].abs().max().item() == 0.0

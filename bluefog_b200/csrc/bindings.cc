@@ -557,6 +557,45 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return out;
   }, py::arg("a"), py::arg("b"));
 
+  // act(a w^T + bias) with the tanh GELU, returning the activated matrix and the pre-activation (kept for backward)
+  m.def("gemm_bf16_nt_gelu", [](at::Tensor a, at::Tensor w, c10::optional<at::Tensor> bias) {
+    TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2 && a.scalar_type() == at::kBFloat16 &&
+                w.scalar_type() == at::kBFloat16 && a.is_contiguous() && w.is_contiguous() && a.size(1) == w.size(1) &&
+                a.size(1) % 8 == 0 && w.size(0) % 8 == 0, "gemm_bf16_nt_gelu expects contiguous bf16 [M,K], [N,K] with K, N % 8 == 0");
+    c10::cuda::CUDAGuard g(a.get_device());
+    at::Tensor& status = GemmStatusWord(a);
+    at::Tensor out = at::empty({a.size(0), w.size(0)}, a.options());
+    at::Tensor pre = at::empty({a.size(0), w.size(0)}, a.options());
+    const void* bptr = nullptr;
+    if (bias.has_value() && bias->defined()) {
+      TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->is_contiguous() && bias->numel() == w.size(0), "bias must be bf16 [N]");
+      bptr = bias->data_ptr();
+    }
+    cudaError_t e = LaunchGemmBf16NT(a.data_ptr(), w.data_ptr(), out.data_ptr(), bptr, static_cast<int>(a.size(0)),
+                                     static_cast<int>(w.size(0)), static_cast<int>(a.size(1)), kActGeluTanh,
+                                     reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(a.get_device()),
+                                     pre.data_ptr());
+    TORCH_CHECK(e == cudaSuccess, "gemm_bf16_nt_gelu launch failed: ", cudaGetErrorString(e));
+    return std::make_tuple(out, pre);
+  }, py::arg("a"), py::arg("w"), py::arg("bias") = py::none());
+  // (a b) * GELU'(preact): the input gradient through a GELU whose pre-activation was kept
+  m.def("gemm_bf16_nn_gelu_grad", [](at::Tensor a, at::Tensor b, at::Tensor preact) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.scalar_type() == at::kBFloat16 &&
+                b.scalar_type() == at::kBFloat16 && a.is_contiguous() && b.is_contiguous() && a.size(1) == b.size(0),
+                "gemm_bf16_nn_gelu_grad expects contiguous bf16 CUDA matrices [M,K] and [K,N]");
+    TORCH_CHECK(preact.is_cuda() && preact.scalar_type() == at::kBFloat16 && preact.is_contiguous() && preact.dim() == 2 &&
+                preact.size(0) == a.size(0) && preact.size(1) == b.size(1), "preact must be bf16 [M,N]");
+    c10::cuda::CUDAGuard g(a.get_device());
+    at::Tensor& status = GemmStatusWord(a);
+    at::Tensor out = at::empty({a.size(0), b.size(1)}, a.options());
+    cudaError_t e = LaunchGemmBf16NN(a.data_ptr(), b.data_ptr(), out.data_ptr(), static_cast<int>(a.size(0)),
+                                     static_cast<int>(b.size(1)), static_cast<int>(a.size(1)),
+                                     reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(a.get_device()),
+                                     preact.data_ptr());
+    TORCH_CHECK(e == cudaSuccess, "gemm_bf16_nn_gelu_grad launch failed: ", cudaGetErrorString(e));
+    return out;
+  });
+
   m.def("gemm_bf16_tn", [](at::Tensor a, at::Tensor b) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.scalar_type() == at::kBFloat16 &&
                 b.scalar_type() == at::kBFloat16 && a.is_contiguous() && b.is_contiguous() && a.size(0) == b.size(0),

@@ -62,6 +62,14 @@ __device__ __forceinline__ float act_fn(float x, int act) {
   return x;
 }
 
+// d/dx of the tanh-approximated GELU of act_fn
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+  const float c = 0.7978845608028654f;
+  const float u = c * (x + 0.044715f * x * x * x);
+  const float t = tanhf(u);
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * c * (1.f + 3.f * 0.044715f * x * x);
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
@@ -225,12 +233,14 @@ struct PersistentCfg {
 // AMODE 1: A is given as [K, M] row-major (the transposed product dY^T * X of a weight gradient) and is
 // consumed MN-major in the same way: two boxes of [64 K-rows x 64 M-columns] per stage, bit 15 of the
 // instruction descriptor.
-template <int BN_, int BMODE = 0, int AMODE = 0>
+// EPI (GemmEpi) is a template parameter so that the plain epilogue keeps its small register footprint.
+template <int BN_, int BMODE = 0, int AMODE = 0, int EPI = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ out,
                                const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int act, int tma_out,
-                               unsigned int* __restrict__ status) {
+                               unsigned int* __restrict__ status, const __grid_constant__ CUtensorMap map_aux,
+                               const __nv_bfloat16* __restrict__ aux_in) {
   using Cfg = PersistentCfg<BN_>;
   constexpr int S = Cfg::kStagesP;
   extern __shared__ unsigned char smem_raw[];
@@ -367,33 +377,104 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
           if (lane == 0) tma_store_wait_read<1>();
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           __syncwarp();
-          unsigned char* box = my_out + size_t(boxes & 1) * Cfg::kBytesOutBox;
-          unsigned char* row = box + lane * 128;
+          if constexpr (EPI == kEpiNone) {
+            unsigned char* box = my_out + size_t(boxes & 1) * Cfg::kBytesOutBox;
+            unsigned char* row = box + lane * 128;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float v[8];
+            for (int j = 0; j < 8; ++j) {
+              float v[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              float x = __uint_as_float(r[j * 8 + i]);
-              if (bias != nullptr) {
-                const int n = nbase + j * 8 + i;
-                x += n < N ? __bfloat162float(bias[n]) : 0.f;
+              for (int i = 0; i < 8; ++i) {
+                float x = __uint_as_float(r[j * 8 + i]);
+                if (bias != nullptr) {
+                  const int n = nbase + j * 8 + i;
+                  x += n < N ? __bfloat162float(bias[n]) : 0.f;
+                }
+                v[i] = act_fn(x, act);
               }
-              v[i] = act_fn(x, act);
-            }
-            uint4 pk;
-            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+              uint4 pk;
+              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-            *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = pk;      // 128-byte swizzle
+              for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+              *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = pk;      // 128-byte swizzle
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&map_c, smem_u32(box), nbase, m0 + q * 32);
+              tma_store_commit();
+            }
+            ++boxes;
+          } else if constexpr (EPI == kEpiMulGeluGrad) {
+            // out = accumulator * GELU'(aux): the backward of a fused Linear+GELU, aux = the saved pre-activation
+            unsigned char* box = my_out + size_t(boxes & 1) * Cfg::kBytesOutBox;
+            unsigned char* row = box + lane * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              uint4 av = make_uint4(0u, 0u, 0u, 0u);
+              if (m < M && nbase + j * 8 < N) av = __ldg(reinterpret_cast<const uint4*>(aux_in + size_t(m) * N + nbase + j * 8));
+              const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&av);
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 t2 = __bfloat1622float2(ah[i]);
+                v[2 * i] = __uint_as_float(r[j * 8 + 2 * i]) * gelu_tanh_grad(t2.x);
+                v[2 * i + 1] = __uint_as_float(r[j * 8 + 2 * i + 1]) * gelu_tanh_grad(t2.y);
+              }
+              uint4 pk;
+              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+              *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = pk;      // 128-byte swizzle
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&map_c, smem_u32(box), nbase, m0 + q * 32);
+              tma_store_commit();
+            }
+            ++boxes;
+          } else {
+            // kEpiStorePreact: two boxes leave per chunk, x = accumulator + bias through map_aux and act(x)
+            // through map_c; both staging boxes are in use, so every earlier store must have been read
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+            unsigned char* row_raw = my_out + lane * 128;
+            unsigned char* row_act = my_out + Cfg::kBytesOutBox + lane * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float x[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                x[i] = __uint_as_float(r[j * 8 + i]);
+                if (bias != nullptr) {
+                  const int n = nbase + j * 8 + i;
+                  x[i] += n < N ? __bfloat162float(bias[n]) : 0.f;
+                }
+              }
+              uint4 pk_raw, pk_act;
+              __nv_bfloat162* hr = reinterpret_cast<__nv_bfloat162*>(&pk_raw);
+              __nv_bfloat162* ha = reinterpret_cast<__nv_bfloat162*>(&pk_act);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                hr[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+                // the activation sees the rounded pre-activation, as a separate activation kernel would
+                const float2 xr = __bfloat1622float2(hr[i]);
+                ha[i] = __floats2bfloat162_rn(act_fn(xr.x, act), act_fn(xr.y, act));
+              }
+              const int off = (j ^ (lane & 7)) << 4;                                // 128-byte swizzle
+              *reinterpret_cast<uint4*>(row_raw + off) = pk_raw;
+              *reinterpret_cast<uint4*>(row_act + off) = pk_act;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&map_aux, smem_u32(my_out), nbase, m0 + q * 32);
+              tma_store_2d(&map_c, smem_u32(my_out + Cfg::kBytesOutBox), nbase, m0 + q * 32);
+              tma_store_commit();
+            }
+            boxes += 2;
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&map_c, smem_u32(box), nbase, m0 + q * 32);
-            tma_store_commit();
-          }
-          ++boxes;
         }
       } else {
 #pragma unroll 1
@@ -460,12 +541,43 @@ bool MakeMap(CUtensorMap* map, const void* base, int rows, int cols /*K*/, int b
   return EncodeTiled(map, 2, base, dims, strides, box);
 }
 
+// Launches one instantiation of the persistent kernel on min(tiles, SMs) CTAs.
+template <int BN_, int BMODE, int AMODE, int EPI>
+cudaError_t LaunchPersistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
+                             const CUtensorMap& map_aux, __nv_bfloat16* out, const __nv_bfloat16* bias,
+                             const __nv_bfloat16* aux_in, int M, int N, int K, int act, int tma_out, int sm_count,
+                             unsigned int* status, cudaStream_t stream) {
+  using Cfg = PersistentCfg<BN_>;
+  auto kernel = gemm_bf16_nt_persistent_kernel<BN_, BMODE, AMODE, EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN_ - 1) / BN_);
+  kernel<<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(map_a, map_b, map_c, out, bias, M, N, K, act,
+                                                                             tma_out, status, map_aux, aux_in);
+  return cudaSuccess;
+}
+
+int SmCount() {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  return sm_count;
+}
+
 }  // namespace
 
 bool GemmSupported() { return GetEncodeFn() != nullptr; }
 
 cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void* bias, int M, int N, int K, int act,
-                             unsigned int* status, cudaStream_t stream) {
+                             unsigned int* status, cudaStream_t stream, void* preact_out) {
   (void)cudaGetLastError();   // the value returned below must be this launch's own, not an older error of the calling thread
   if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
   // TMA needs 16-byte aligned bases and row pitches: K must be a multiple of 8 bf16 elements.
@@ -476,13 +588,7 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
     const char* v = std::getenv("BLUEFOG_B200_GEMM_VARIANT");   // "tile" = one tile per CTA, default persistent
     return (v != nullptr && std::string(v) == "tile") ? 0 : 1;
   }();
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    if (sm_count <= 0) sm_count = 148;
-  }
+  const int sm_count = SmCount();
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
   const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
   CUtensorMap map_a, map_b, map_c;
@@ -491,88 +597,71 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
     // output boxes of [32 rows x 64 columns]; without a usable pitch the map is a valid dummy over A
     if (!(tma_out ? MakeMap(&map_c, out, M, N, 32) : MakeMap(&map_c, a, M, K, 32))) return cudaErrorInvalidValue;
   }
+  CUtensorMap map_aux = map_c;
+  const bool preact = preact_out != nullptr;
+  if (preact) {
+    if (variant == 0 || !tma_out || (reinterpret_cast<uintptr_t>(preact_out) & 15)) return cudaErrorInvalidValue;
+    if (!MakeMap(&map_aux, preact_out, M, N, 32)) return cudaErrorInvalidValue;
+  }
+  cudaError_t e = cudaSuccess;
   if (variant == 0) {
     if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, BN)) return cudaErrorInvalidValue;
     static bool attr_set = false;
     if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+      e = cudaFuncSetAttribute(gemm_bf16_nt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
       if (e != cudaSuccess) return e;
       attr_set = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     gemm_bf16_nt_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, o, bp, M, N, K, act, status);
   } else if (N > 128) {
-    using Cfg = PersistentCfg<256>;
     if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, 256)) return cudaErrorInvalidValue;
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
-      if (e != cudaSuccess) return e;
-      attr_set = true;
-    }
-    const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
-    gemm_bf16_nt_persistent_kernel<256><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
-        map_a, map_b, map_c, o, bp, M, N, K, act, tma_out, status);
+    e = preact ? LaunchPersistent<256, 0, 0, kEpiStorePreact>(map_a, map_b, map_c, map_aux, o, bp, nullptr, M, N, K, act, tma_out,
+                                                              sm_count, status, stream)
+               : LaunchPersistent<256, 0, 0, kEpiNone>(map_a, map_b, map_c, map_aux, o, bp, nullptr, M, N, K, act, tma_out,
+                                                       sm_count, status, stream);
   } else {
-    using Cfg = PersistentCfg<128>;
     if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, 128)) return cudaErrorInvalidValue;
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
-      if (e != cudaSuccess) return e;
-      attr_set = true;
-    }
-    const int tiles = ((M + BM - 1) / BM) * ((N + 127) / 128);
-    gemm_bf16_nt_persistent_kernel<128><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
-        map_a, map_b, map_c, o, bp, M, N, K, act, tma_out, status);
+    e = preact ? LaunchPersistent<128, 0, 0, kEpiStorePreact>(map_a, map_b, map_c, map_aux, o, bp, nullptr, M, N, K, act, tma_out,
+                                                              sm_count, status, stream)
+               : LaunchPersistent<128, 0, 0, kEpiNone>(map_a, map_b, map_c, map_aux, o, bp, nullptr, M, N, K, act, tma_out,
+                                                       sm_count, status, stream);
   }
+  if (e != cudaSuccess) return e;
   CountKernelLaunch();
   return cudaGetLastError();
 }
 
 // out[M,N] = a[M,K] * b[K,N]: the B operand is consumed MN-major straight from its row-major memory, so a
-// product with a transposed weight (an input gradient) needs no transposed copy.
+// product with a transposed weight (an input gradient) needs no transposed copy.  With gelu_preact the result
+// is multiplied elementwise by GELU'(gelu_preact[M,N]) in the epilogue (the backward of a fused Linear+GELU).
 cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int N, int K, unsigned int* status,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, const void* gelu_preact) {
   (void)cudaGetLastError();   // the value returned below must be this launch's own, not an older error of the calling thread
   if (M <= 0 || N <= 0 || K <= 0 || (K % 8) != 0 || (N % 8) != 0) return cudaErrorInvalidValue;
-  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
+      (reinterpret_cast<uintptr_t>(gelu_preact) & 15))
     return cudaErrorInvalidValue;
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    if (sm_count <= 0) sm_count = 148;
-  }
+  const int sm_count = SmCount();
   CUtensorMap map_a, map_b, map_c;
   // B: [K rows, N columns]; boxes of 64 columns (128 bytes) x 64 rows
   if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, K, N, 64) || !MakeMap(&map_c, out, M, N, 32))
     return cudaErrorInvalidValue;
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+  const __nv_bfloat16* aux = static_cast<const __nv_bfloat16*>(gelu_preact);
+  cudaError_t e;
   if (N > 128) {
-    using Cfg = PersistentCfg<256>;
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
-      if (e != cudaSuccess) return e;
-      attr_set = true;
-    }
-    const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
-    gemm_bf16_nt_persistent_kernel<256, 1><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
-        map_a, map_b, map_c, o, nullptr, M, N, K, 0, 1, status);
+    e = aux != nullptr ? LaunchPersistent<256, 1, 0, kEpiMulGeluGrad>(map_a, map_b, map_c, map_c, o, nullptr, aux, M, N, K, 0, 1,
+                                                                      sm_count, status, stream)
+                       : LaunchPersistent<256, 1, 0, kEpiNone>(map_a, map_b, map_c, map_c, o, nullptr, nullptr, M, N, K, 0, 1,
+                                                               sm_count, status, stream);
   } else {
-    using Cfg = PersistentCfg<128>;
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
-      if (e != cudaSuccess) return e;
-      attr_set = true;
-    }
-    const int tiles = ((M + BM - 1) / BM) * ((N + 127) / 128);
-    gemm_bf16_nt_persistent_kernel<128, 1><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
-        map_a, map_b, map_c, o, nullptr, M, N, K, 0, 1, status);
+    e = aux != nullptr ? LaunchPersistent<128, 1, 0, kEpiMulGeluGrad>(map_a, map_b, map_c, map_c, o, nullptr, aux, M, N, K, 0, 1,
+                                                                      sm_count, status, stream)
+                       : LaunchPersistent<128, 1, 0, kEpiNone>(map_a, map_b, map_c, map_c, o, nullptr, nullptr, M, N, K, 0, 1,
+                                                               sm_count, status, stream);
   }
+  if (e != cudaSuccess) return e;
   CountKernelLaunch();
   return cudaGetLastError();
 }
@@ -585,41 +674,18 @@ cudaError_t LaunchGemmBf16TN(const void* a, const void* b, void* out, int M, int
   if (M <= 0 || N <= 0 || K <= 0 || (M % 8) != 0 || (N % 8) != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
     return cudaErrorInvalidValue;
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    if (sm_count <= 0) sm_count = 148;
-  }
+  const int sm_count = SmCount();
   CUtensorMap map_a, map_b, map_c;
   // A: [K rows, M columns], B: [K rows, N columns]; boxes of 64 columns (128 bytes) x 64 rows
   if (!MakeMap(&map_a, a, K, M, 64) || !MakeMap(&map_b, b, K, N, 64) || !MakeMap(&map_c, out, M, N, 32))
     return cudaErrorInvalidValue;
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
-  if (N > 128) {
-    using Cfg = PersistentCfg<256>;
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<256, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
-      if (e != cudaSuccess) return e;
-      attr_set = true;
-    }
-    const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
-    gemm_bf16_nt_persistent_kernel<256, 1, 1><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
-        map_a, map_b, map_c, o, nullptr, M, N, K, 0, 1, status);
-  } else {
-    using Cfg = PersistentCfg<128>;
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_persistent_kernel<128, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
-      if (e != cudaSuccess) return e;
-      attr_set = true;
-    }
-    const int tiles = ((M + BM - 1) / BM) * ((N + 127) / 128);
-    gemm_bf16_nt_persistent_kernel<128, 1, 1><<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(
-        map_a, map_b, map_c, o, nullptr, M, N, K, 0, 1, status);
-  }
+  const cudaError_t e =
+      N > 128 ? LaunchPersistent<256, 1, 1, kEpiNone>(map_a, map_b, map_c, map_c, o, nullptr, nullptr, M, N, K, 0, 1, sm_count,
+                                                      status, stream)
+              : LaunchPersistent<128, 1, 1, kEpiNone>(map_a, map_b, map_c, map_c, o, nullptr, nullptr, M, N, K, 0, 1, sm_count,
+                                                      status, stream);
+  if (e != cudaSuccess) return e;
   CountKernelLaunch();
   return cudaGetLastError();
 }

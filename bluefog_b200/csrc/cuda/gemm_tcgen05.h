@@ -5,6 +5,10 @@
 namespace bfb {
 
 enum GemmAct : int { kActNone = 0, kActRelu = 1, kActGeluTanh = 2 };
+// Extra work of the epilogue: store the pre-activation value (accumulator + bias) to a second matrix besides
+// act(...) of it; or multiply the result by GELU'(aux[m, n]) (the input gradient through a GELU whose
+// pre-activation was kept).
+enum GemmEpi : int { kEpiNone = 0, kEpiStorePreact = 1, kEpiMulGeluGrad = 2 };
 
 // True when the driver exposes cuTensorMapEncodeTiled (needed to build TMA descriptors).
 bool GemmSupported();
@@ -12,12 +16,14 @@ bool GemmSupported();
 // out[M,N] (bf16, row-major) = act(a[M,K] * b[N,K]^T + bias[N]); a, b bf16 row-major, K % 8 == 0,
 // all base pointers 16-byte aligned. bias may be null. status: device word set to 1 when a
 // bounded wait inside the kernel expired (may be null).
+// preact_out (optional, [M,N] bf16, needs N % 8 == 0): receives a*b^T + bias before the activation.
 cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void* bias, int M, int N, int K, int act,
-                             unsigned int* status, cudaStream_t stream);
+                             unsigned int* status, cudaStream_t stream, void* preact_out = nullptr);
 
 // out[M,N] = a[M,K] * b[K,N] with b row-major (consumed as an MN-major operand); K % 8 == 0, N % 8 == 0.
+// gelu_preact (optional, [M,N] bf16): the result is multiplied elementwise by GELU'(gelu_preact).
 cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int N, int K, unsigned int* status,
-                             cudaStream_t stream);
+                             cudaStream_t stream, const void* gelu_preact = nullptr);
 
 // out[M,N] = a[K,M]^T * b[K,N], a and b row-major (both consumed MN-major); M % 8 == 0, N % 8 == 0.
 cudaError_t LaunchGemmBf16TN(const void* a, const void* b, void* out, int M, int N, int K, unsigned int* status,

@@ -9,6 +9,8 @@ scaled-dot-product attention.
 """
 import math
 
+import os
+
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
@@ -55,6 +57,13 @@ class MLP(nn.Module):
         self.c_proj = B200Linear(4 * d_model, d_model, use_b200_gemm=use_b200_gemm)
 
     def forward(self, x):
+        # BLUEFOG_B200_MLP_FUSION=0 keeps the GELU a kernel of its own between the two GEMMs
+        if (self.c_fc.use_b200_gemm and x.is_cuda and x.dtype == torch.bfloat16
+                and os.environ.get("BLUEFOG_B200_MLP_FUSION", "1") != "0"):
+            from bluefog_b200.ops import gemm
+            y = gemm.mlp_gelu(x.reshape(-1, x.shape[-1]), self.c_fc.weight, self.c_fc.bias, self.c_proj.weight,
+                              self.c_proj.bias)
+            return y.view(*x.shape[:-1], y.shape[-1])
         return self.c_proj(F.gelu(self.c_fc(x), approximate="tanh"))
 
 

@@ -118,3 +118,52 @@ def conv1x1(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
             and x.is_contiguous(memory_format=torch.channels_last) and available()):
         return _Conv1x1Fn.apply(x, weight)
     return torch.nn.functional.conv2d(x, weight)
+
+
+class _MlpGeluFn(torch.autograd.Function):
+    """y = gelu_tanh(a W1^T + b1) W2^T + b2 with both GELU passes inside GEMM epilogues: the first product
+    stores its pre-activation next to the activated matrix, and the input gradient of the second product is
+    multiplied by GELU'(pre-activation) before it is written."""
+
+    @staticmethod
+    def forward(ctx, a, w1, b1, w2, b2):
+        g, u = _b.native.gemm_bf16_nt_gelu(a, w1, b1)
+        y = _b.native.gemm_bf16_nt(g, w2, b2, 0)
+        ctx.save_for_backward(a, w1, w2, u, g)
+        ctx.has_bias = (b1 is not None, b2 is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        a, w1, w2, u, g = ctx.saved_tensors
+        dy = dy.contiguous()
+        C = _b.native
+        du = C.gemm_bf16_nn_gelu_grad(dy, w2, u)                  # (dY W2) * GELU'(u)
+        dw2 = _weight_gradient(dy, g)
+        db2 = C.column_sum(dy).to(dy.dtype) if ctx.has_bias[1] else None
+        da = _input_gradient(du, w1) if ctx.needs_input_grad[0] else None
+        dw1 = _weight_gradient(du, a)
+        db1 = C.column_sum(du).to(du.dtype) if ctx.has_bias[0] else None
+        return da, dw1, db1, dw2, db2
+
+
+def _weight_gradient(dy: torch.Tensor, a: torch.Tensor) -> torch.Tensor:
+    """dW[N, K] = dY[M, N]^T @ A[M, K] (see ``_LinearFn.backward`` for the tile rule)."""
+    n_out, k_in = dy.shape[1], a.shape[1]
+    tiles = ((n_out + 127) // 128) * ((k_in + 255) // 256)
+    if n_out % 8 == 0 and k_in % 8 == 0 and tiles >= _TN_MIN_TILES:
+        return _b.native.gemm_bf16_tn(dy, a)
+    return dy.t() @ a
+
+
+def mlp_gelu(a: torch.Tensor, w1: torch.Tensor, b1, w2: torch.Tensor, b2) -> torch.Tensor:
+    """``F.linear(F.gelu(F.linear(a, w1, b1), approximate="tanh"), w2, b2)`` for a bf16 CUDA matrix ``a`` [M, K]
+    on the tcgen05 kernels with the GELU folded into the GEMM epilogues; other inputs take PyTorch's ops."""
+    ok = (a.is_cuda and a.dim() == 2 and all(t.dtype == torch.bfloat16 for t in (a, w1, w2))
+          and a.shape[1] % 8 == 0 and w1.shape[0] % 8 == 0 and w2.shape[0] % 8 == 0 and a.numel() > 0
+          and (b1 is None or b1.dtype == torch.bfloat16) and (b2 is None or b2.dtype == torch.bfloat16)
+          and available() and hasattr(_b.native, "gemm_bf16_nt_gelu"))
+    if ok:
+        return _MlpGeluFn.apply(a.contiguous(), w1.contiguous(), b1, w2.contiguous(), b2)
+    h = torch.nn.functional.gelu(torch.nn.functional.linear(a, w1, b1), approximate="tanh")
+    return torch.nn.functional.linear(h, w2, b2)

@@ -125,3 +125,23 @@ def test_linear_backward_runs_all_three_products_on_the_kernel():
     torch.nn.functional.linear(a2, w2).backward(dy.float())
     for got, ref in ((a.grad, a2.grad), (w.grad, w2.grad), (b.grad, dy.float().sum(0))):
         assert (got.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("M,K,H", [(512, 256, 1024), (8192, 1024, 4096), (300, 72, 136)])
+def test_mlp_gelu_with_epilogue_fusion_matches_fp32(M, K, H):
+    from bluefog_b200 import _C
+    from bluefog_b200.ops import gemm
+    import torch.nn.functional as F
+    torch.manual_seed(M + K + H)
+    mk = lambda *s, scale=1.0: (torch.randn(*s, device="cuda") * scale).to(torch.bfloat16).requires_grad_(True)
+    a, w1, b1, w2, b2 = mk(M, K), mk(H, K, scale=K ** -0.5), mk(H, scale=0.1), mk(K, H, scale=H ** -0.5), mk(K, scale=0.1)
+    dy = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    y = gemm.mlp_gelu(a, w1, b1, w2, b2)
+    y.backward(dy)
+    ref_in = [t.detach().float().requires_grad_(True) for t in (a, w1, b1, w2, b2)]
+    yr = F.linear(F.gelu(F.linear(ref_in[0], ref_in[1], ref_in[2]), approximate="tanh"), ref_in[3], ref_in[4])
+    yr.backward(dy.float())
+    for name, got, ref in [("y", y, yr)] + [(n, t.grad, r.grad) for n, t, r in zip("a w1 b1 w2 b2".split(), (a, w1, b1, w2, b2), ref_in)]:
+        err = (got.float() - ref).abs().max().item()
+        assert err <= 2e-2 * max(1.0, ref.abs().max().item()), (name, err, ref.abs().max().item())
+    assert _C.gemm_status() == 0

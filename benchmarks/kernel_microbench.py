@@ -113,10 +113,27 @@ def bench_gemm(args):
     ms_lib = timed(lib, args.iters, args.warmup)
     flops = 2.0 * m * n * k
     nbytes = 2.0 * (m * k + n * k + m * n)     # A, B read once, C written once
-    return {"kernel": "gemm_bf16_nt_persistent_kernel (tcgen05)", "layout": args.gemm_layout, "m": m, "n": n, "k": k,
-            "ms": ms, "tflops": flops / ms / 1e9, "frac_of_measured_bf16": flops / ms / 1e9 / PEAKS["bf16_tflops"],
-            "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / PEAKS["hbm_gbs"],
-            "library_ms": ms_lib, "library_tflops": flops / ms_lib / 1e9, "status": _C.gemm_status()}
+    out = {"kernel": "gemm_bf16_nt_persistent_kernel (tcgen05)", "layout": args.gemm_layout, "m": m, "n": n, "k": k,
+           "ms": ms, "tflops": flops / ms / 1e9, "frac_of_measured_bf16": flops / ms / 1e9 / PEAKS["bf16_tflops"],
+           "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / PEAKS["hbm_gbs"],
+           "library_ms": ms_lib, "library_tflops": flops / ms_lib / 1e9}
+    if args.gemm_col_stats and args.gemm_layout == "nt" and n % 8 == 0:
+        # the epilogue variant that also takes the column statistics of its output, against the separate
+        # statistics pass of the BatchNorm kernels over the same [M, N] activation (the sums buffer is cleared
+        # inside the timed call in both arms)
+        stats = torch.zeros(2 * n, device="cuda")
+        y = _C.gemm_bf16_nt(a, w, None, 0)
+        out["with_col_stats_ms"] = timed(lambda: (stats.zero_(), _C.gemm_bf16_nt(a, w, None, 0, stats)), args.iters, args.warmup)
+        x4 = y.view(1, m, 1, n).permute(0, 3, 1, 2)                   # the NHWC activation a BatchNorm would see
+        if _C.bn_supported(x4):
+            g, b = torch.ones(n, device="cuda"), torch.zeros(n, device="cuda")
+            full = timed(lambda: (stats.zero_(), _C.bn_forward(x4, None, g, b, None, None, 1e-5, 0.1, True, stats, False)),
+                         args.iters, args.warmup)
+            apply_only = timed(lambda: (stats.zero_(), _C.bn_forward(x4, None, g, b, None, None, 1e-5, 0.1, True, stats, True)),
+                               args.iters, args.warmup)
+            out["bn_forward_ms"], out["bn_forward_without_statistics_pass_ms"] = full, apply_only
+    out["status"] = _C.gemm_status()
+    return out
 
 
 def bench_conv(args):
@@ -188,6 +205,7 @@ def main():
     ap.add_argument("--dtype", default="float32")
     ap.add_argument("--exchange", default="float32", choices=["float32", "bfloat16"])
     ap.add_argument("--gemm-layout", default="nt", choices=["nt", "nn", "tn"])
+    ap.add_argument("--gemm-col-stats", action="store_true", help="also time the epilogue that takes column statistics")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)

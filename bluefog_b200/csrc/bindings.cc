@@ -293,7 +293,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("bn_forward", [](at::Tensor x, c10::optional<at::Tensor> residual, at::Tensor gamma, at::Tensor beta,
                          c10::optional<at::Tensor> running_mean, c10::optional<at::Tensor> running_var, double eps,
-                         double momentum, bool relu, c10::optional<at::Tensor> zeroed_sums) {
+                         double momentum, bool relu, c10::optional<at::Tensor> zeroed_sums, bool stats_ready) {
+    // stats_ready: zeroed_sums already holds sum(x) and sum(x^2) per channel (written by the kernel that produced
+    // x), so the statistics pass over x is skipped
+    TORCH_CHECK(!stats_ready || (zeroed_sums.has_value() && zeroed_sums->defined()), "stats_ready needs the sums");
     TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.scalar_type() == at::kBFloat16 &&
                 x.is_contiguous(at::MemoryFormat::ChannelsLast), "bn_forward expects a bf16 NHWC (channels_last) CUDA tensor");
     const int C = static_cast<int>(x.size(1));
@@ -334,11 +337,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                     sums.data_ptr<float>(), gamma.data_ptr(), beta.data_ptr(),
                                     rm, rv, save_mean.data_ptr<float>(), save_rstd.data_ptr<float>(), R, C,
                                     static_cast<float>(eps), static_cast<float>(momentum), relu ? 1 : 0, pbf16 ? 1 : 0,
-                                    CurrentStream(x.get_device()));
+                                    CurrentStream(x.get_device()), stats_ready ? 1 : 0);
     TORCH_CHECK(e == cudaSuccess, "bn_forward launch failed: ", cudaGetErrorString(e));
     return std::make_tuple(y, save_mean, save_rstd, mask);
   }, py::arg("x"), py::arg("residual"), py::arg("gamma"), py::arg("beta"), py::arg("running_mean"),
-     py::arg("running_var"), py::arg("eps"), py::arg("momentum"), py::arg("relu"), py::arg("zeroed_sums") = py::none());
+     py::arg("running_var"), py::arg("eps"), py::arg("momentum"), py::arg("relu"), py::arg("zeroed_sums") = py::none(),
+     py::arg("stats_ready") = false);
   m.def("bn_backward", [](at::Tensor dy, c10::optional<at::Tensor> mask, at::Tensor x, at::Tensor save_mean, at::Tensor save_rstd,
                           at::Tensor gamma, bool relu, bool want_dres, c10::optional<at::Tensor> zeroed_sums) {
     TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous(at::MemoryFormat::ChannelsLast) &&
@@ -496,7 +500,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
   // ---- tcgen05 GEMM -------------------------------------------------------------------------
   m.def("gemm_supported", [] { return GemmSupported(); });
-  m.def("gemm_bf16_nt", [](at::Tensor a, at::Tensor w, c10::optional<at::Tensor> bias, int act) {
+  // col_stats (optional, >= 2*N zero-initialised or running fp32 values): receives the column sums and sums of
+  // squares of the rounded output, added by the GEMM epilogue (needs N % 8 == 0, no bias, act == 0)
+  m.def("gemm_bf16_nt", [](at::Tensor a, at::Tensor w, c10::optional<at::Tensor> bias, int act,
+                           c10::optional<at::Tensor> col_stats) {
     TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2, "gemm_bf16_nt expects 2-D CUDA tensors");
     TORCH_CHECK(a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "gemm_bf16_nt expects bf16");
     TORCH_CHECK(a.is_contiguous() && w.is_contiguous(), "gemm_bf16_nt expects contiguous tensors");
@@ -510,12 +517,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->is_contiguous() && bias->numel() == w.size(0), "bias must be bf16 [N]");
       bptr = bias->data_ptr();
     }
+    float* stats = nullptr;
+    if (col_stats.has_value() && col_stats->defined()) {
+      TORCH_CHECK(col_stats->is_cuda() && col_stats->scalar_type() == at::kFloat && col_stats->is_contiguous() &&
+                  col_stats->numel() >= 2 * w.size(0) && w.size(0) % 8 == 0 && bptr == nullptr && act == 0 &&
+                  (reinterpret_cast<uintptr_t>(col_stats->data_ptr()) & 15) == 0,
+                  "col_stats needs 2*N 16-byte aligned fp32 values, N % 8 == 0, no bias and no activation");
+      stats = col_stats->data_ptr<float>();
+    }
     cudaError_t e = LaunchGemmBf16NT(a.data_ptr(), w.data_ptr(), out.data_ptr(), bptr, static_cast<int>(a.size(0)),
                                      static_cast<int>(w.size(0)), static_cast<int>(a.size(1)), act,
-                                     reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(a.get_device()));
+                                     reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(a.get_device()),
+                                     nullptr, stats);
     TORCH_CHECK(e == cudaSuccess, "gemm_bf16_nt launch failed: ", cudaGetErrorString(e));
     return out;
-  }, py::arg("a"), py::arg("w"), py::arg("bias") = py::none(), py::arg("act") = 0);
+  }, py::arg("a"), py::arg("w"), py::arg("bias") = py::none(), py::arg("act") = 0, py::arg("col_stats") = py::none());
 
   // ---- tcgen05 implicit-GEMM 3x3 convolution (stride 1, pad 1), NHWC bf16 ---------------------
   m.def("conv3x3_supported", [](int64_t n, int64_t h, int64_t w, int64_t cin, int64_t cout) {

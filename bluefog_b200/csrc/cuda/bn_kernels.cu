@@ -142,6 +142,7 @@ struct BnApplyParams {
   int param_bf16;
   float eps;
   float momentum;
+  int raw_sums;                    // sums are of x itself (a producer's epilogue wrote them), not of x - x[0]
 };
 
 __global__ void __launch_bounds__(kThreads) bn_apply_kernel(const BnApplyParams p) {
@@ -150,6 +151,10 @@ __global__ void __launch_bounds__(kThreads) bn_apply_kernel(const BnApplyParams 
   const int g = (int)(gtid % CG);
   float pivot[8], scale[8], shift[8];
   unpack8(*reinterpret_cast<const uint4*>(p.x + g * 8), pivot);
+  if (p.raw_sums) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pivot[i] = 0.f;
+  }
   const float inv_r = 1.f / (float)p.R;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -379,14 +384,17 @@ bool BnShapeSupported(long long R, int C) {
 
 cudaError_t LaunchBnForward(const void* x, const void* residual, void* y, void* mask, float* sums, const void* gamma, const void* beta,
                             float* running_mean, float* running_var, float* save_mean, float* save_rstd, long long R,
-                            int C, float eps, float momentum, int relu, int param_bf16, cudaStream_t stream) {
+                            int C, float eps, float momentum, int relu, int param_bf16, cudaStream_t stream,
+                            int stats_ready) {
   if (!BnShapeSupported(R, C) || (relu && mask == nullptr)) return cudaErrorInvalidValue;
-  bn_stats_kernel<<<ReduceGrid(R, C), kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), R, C, sums);
-  CountKernelLaunch();
+  if (!stats_ready) {
+    bn_stats_kernel<<<ReduceGrid(R, C), kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), R, C, sums);
+    CountKernelLaunch();
+  }
   BnApplyParams p{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
                   static_cast<__nv_bfloat16*>(y), static_cast<unsigned char*>(mask), sums, gamma, beta, running_mean,
                   running_var, save_mean, save_rstd,
-                  R, C, relu, param_bf16, eps, momentum};
+                  R, C, relu, param_bf16, eps, momentum, stats_ready};
   bn_apply_kernel<<<ApplyGrid(R, C), kThreads, 0, stream>>>(p);
   CountKernelLaunch();
   return cudaGetLastError();

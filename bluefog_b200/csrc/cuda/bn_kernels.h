@@ -11,7 +11,8 @@ bool BnShapeSupported(long long R, int C);
 // mask: R*C/8 bytes, bit i of byte (r*C/8 + g) = (y[r, 8g+i] > 0); required when relu != 0.
 cudaError_t LaunchBnForward(const void* x, const void* residual, void* y, void* mask, float* sums, const void* gamma, const void* beta,
                             float* running_mean, float* running_var, float* save_mean, float* save_rstd, long long R,
-                            int C, float eps, float momentum, int relu, int param_bf16, cudaStream_t stream);
+                            int C, float eps, float momentum, int relu, int param_bf16, cudaStream_t stream,
+                            int stats_ready = 0);   // 1: sums already hold sum(x), sum(x^2); no statistics pass
 
 cudaError_t LaunchBnBackward(const void* dy, const void* mask, const void* x, void* dx, void* dres, float* sums,
                              const float* save_mean, const float* save_rstd, const void* gamma, void* dgamma,

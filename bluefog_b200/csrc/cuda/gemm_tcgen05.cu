@@ -62,6 +62,19 @@ __device__ __forceinline__ float act_fn(float x, int act) {
   return x;
 }
 
+// two floats in one 64-bit register, the operand form of the packed f32x2 instructions
+__device__ __forceinline__ unsigned long long pack_f32x2(uint32_t lo_bits, uint32_t hi_bits) {
+  unsigned long long v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(lo_bits), "r"(hi_bits));
+  return v;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+  uint32_t a, b;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+  lo = __uint_as_float(a);
+  hi = __uint_as_float(b);
+}
+
 // d/dx of the tanh-approximated GELU of act_fn
 __device__ __forceinline__ float gelu_tanh_grad(float x) {
   const float c = 0.7978845608028654f;
@@ -212,9 +225,12 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // tile edges are clipped by the tensor map.  Row pitches that TMA cannot address (N % 8 != 0)
 // take the direct-store epilogue.
 // ------------------------------------------------------------------------------------------ //
-template <int BN_>
+template <int BN_, int EPI = 0>
 struct PersistentCfg {
-  static constexpr int kStagesP = (BN_ == 256) ? 4 : 6;
+  // the column-statistics epilogue gives one ring stage up for its per-warp partial sums
+  static constexpr int kStagesP = ((BN_ == 256) ? 4 : 6) - (EPI == kEpiColumnStats ? 1 : 0);
+  // per epilogue warp: BN_ column sums and BN_ sums of squares
+  static constexpr uint32_t kStatBytes = EPI == kEpiColumnStats ? 4 * 2 * BN_ * 4 : 0;
   static constexpr uint32_t kBytesA = BM * BK * 2;
   static constexpr uint32_t kBytesB = BN_ * BK * 2;
   static constexpr uint32_t kBytesStage = kBytesA + kBytesB;
@@ -222,7 +238,7 @@ struct PersistentCfg {
   // output staging: per epilogue warp two [32 rows x 64 columns] bf16 boxes (4 KiB each, 1024-byte aligned)
   static constexpr uint32_t kBytesOutBox = 32 * 64 * 2;
   static constexpr uint32_t kBytesOut = 4 * 2 * kBytesOutBox;
-  static constexpr size_t kSmem = 1024 + size_t(kStagesP) * kBytesStage + kBytesOut + 256;
+  static constexpr size_t kSmem = 1024 + size_t(kStagesP) * kBytesStage + kBytesOut + 256 + kStatBytes;
   static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN_ >> 3) << 17) | (uint32_t(BM >> 4) << 24);
 };
 
@@ -240,8 +256,8 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                                const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ out,
                                const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int act, int tma_out,
                                unsigned int* __restrict__ status, const __grid_constant__ CUtensorMap map_aux,
-                               const __nv_bfloat16* __restrict__ aux_in) {
-  using Cfg = PersistentCfg<BN_>;
+                               const __nv_bfloat16* __restrict__ aux_in, float* __restrict__ col_stats) {
+  using Cfg = PersistentCfg<BN_, EPI>;
   constexpr int S = Cfg::kStagesP;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -357,6 +373,34 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     unsigned char* my_out = stage_out + size_t(q) * 2 * Cfg::kBytesOutBox;
     int local = 0;
     int boxes = 0;                       // TMA stores issued by this warp
+    // kEpiColumnStats: this warp's partial column sums [BN_] and sums of squares [BN_] of the current column
+    // block live in shared memory (lanes 0-7 each own eight columns of every 64-column chunk, so no atomics)
+    // and go to col_stats with vector reductions when the column block changes and at the end: adding every
+    // box to global memory directly serialises thousands of reductions per address.
+    float* wstat = reinterpret_cast<float*>(stage_out + Cfg::kBytesOut + 256) + (EPI == kEpiColumnStats ? q * 2 * BN_ : 0);
+    int stat_n0 = -1;
+    auto flush_stats = [&]() {
+      if (stat_n0 >= 0 && lane < 8) {
+#pragma unroll 1
+        for (int c = 0; c < BN_ / 64; ++c) {
+          const int col = c * 64 + lane * 8;
+          const int n = stat_n0 + col;
+          float4* ws = reinterpret_cast<float4*>(wstat + col);
+          float4* wq = reinterpret_cast<float4*>(wstat + BN_ + col);
+          if (n < N) {                   // N is a multiple of 8 in this mode: the whole group is inside
+            atomicAdd(reinterpret_cast<float4*>(col_stats + n), ws[0]);
+            atomicAdd(reinterpret_cast<float4*>(col_stats + n) + 1, ws[1]);
+            atomicAdd(reinterpret_cast<float4*>(col_stats + N + n), wq[0]);
+            atomicAdd(reinterpret_cast<float4*>(col_stats + N + n) + 1, wq[1]);
+          }
+          ws[0] = ws[1] = wq[0] = wq[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+    };
+    if constexpr (EPI == kEpiColumnStats) {
+      for (int i = lane; i < 2 * BN_; i += 32) wstat[i] = 0.f;
+      __syncwarp();
+    }
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int acc = local & 1;
       const int m0 = (tile / tiles_n) * BM;
@@ -364,6 +408,12 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
       if (!mbar_wait(smem_u32(&bars[2 * S + acc]), (local >> 1) & 1, failed)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m = m0 + q * 32 + lane;
+      if constexpr (EPI == kEpiColumnStats) {
+        if (n0 != stat_n0) {
+          flush_stats();
+          stat_n0 = n0;
+        }
+      }
       if (tma_out) {
 #pragma unroll 1
         for (int c = 0; c < BN_ / 64; ++c) {
@@ -377,7 +427,7 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
           if (lane == 0) tma_store_wait_read<1>();
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           __syncwarp();
-          if constexpr (EPI == kEpiNone) {
+          if constexpr (EPI == kEpiNone || EPI == kEpiColumnStats) {
             unsigned char* box = my_out + size_t(boxes & 1) * Cfg::kBytesOutBox;
             unsigned char* row = box + lane * 128;
 #pragma unroll
@@ -397,6 +447,47 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 #pragma unroll
               for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
               *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = pk;      // 128-byte swizzle
+            }
+            if constexpr (EPI == kEpiColumnStats) {
+              // Statistics of the staged (rounded) box: lane l reads the eight columns (l & 7)*8.. of rows
+              // (l >> 3) + 4i back with 16-byte loads that follow the swizzle, sums them as packed float pairs, the
+              // four row groups are folded with shuffles and eight lanes add the result to this warp's partial sums.
+              // Rows past M hold exact zeros (zero-filled A rows, no bias, no activation).  The chunk loop stays
+              // rolled: as straight-line code the epilogue ran out of the instruction cache.
+              __syncwarp();
+              unsigned long long s2[4] = {0ull, 0ull, 0ull, 0ull}, q2[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rr = (lane >> 3) + 4 * i;
+                const uint4 wv = *reinterpret_cast<const uint4*>(box + rr * 128 + (((lane & 7) ^ (rr & 7)) << 4));
+                const uint32_t w4[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const unsigned long long f = pack_f32x2(w4[k] << 16, w4[k] & 0xffff0000u);   // two bf16 -> two floats
+                  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(s2[k]) : "l"(f));
+                  asm("fma.rn.f32x2 %0, %1, %1, %0;" : "+l"(q2[k]) : "l"(f));
+                }
+              }
+              float v[16];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                unpack_f32x2(s2[k], v[2 * k], v[2 * k + 1]);
+                unpack_f32x2(q2[k], v[8 + 2 * k], v[8 + 2 * k + 1]);
+              }
+#pragma unroll
+              for (int k = 0; k < 16; ++k) {
+                v[k] += __shfl_xor_sync(0xffffffffu, v[k], 8);
+                v[k] += __shfl_xor_sync(0xffffffffu, v[k], 16);
+              }
+              if (lane < 8) {
+                float4* ws = reinterpret_cast<float4*>(wstat + c * 64 + lane * 8);
+                float4* wq = reinterpret_cast<float4*>(wstat + BN_ + c * 64 + lane * 8);
+                float4 t;
+                t = ws[0]; t.x += v[0]; t.y += v[1]; t.z += v[2]; t.w += v[3]; ws[0] = t;
+                t = ws[1]; t.x += v[4]; t.y += v[5]; t.z += v[6]; t.w += v[7]; ws[1] = t;
+                t = wq[0]; t.x += v[8]; t.y += v[9]; t.z += v[10]; t.w += v[11]; wq[0] = t;
+                t = wq[1]; t.x += v[12]; t.y += v[13]; t.z += v[14]; t.w += v[15]; wq[1] = t;
+              }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
@@ -515,6 +606,7 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars[2 * S + 2 + acc])) : "memory");
     }
+    if constexpr (EPI == kEpiColumnStats) flush_stats();
     // the stores of this warp must be complete before its shared memory goes away
     if (lane == 0) tma_store_wait_all();
   }
@@ -546,8 +638,8 @@ template <int BN_, int BMODE, int AMODE, int EPI>
 cudaError_t LaunchPersistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
                              const CUtensorMap& map_aux, __nv_bfloat16* out, const __nv_bfloat16* bias,
                              const __nv_bfloat16* aux_in, int M, int N, int K, int act, int tma_out, int sm_count,
-                             unsigned int* status, cudaStream_t stream) {
-  using Cfg = PersistentCfg<BN_>;
+                             unsigned int* status, cudaStream_t stream, float* col_stats = nullptr) {
+  using Cfg = PersistentCfg<BN_, EPI>;
   auto kernel = gemm_bf16_nt_persistent_kernel<BN_, BMODE, AMODE, EPI>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -557,7 +649,7 @@ cudaError_t LaunchPersistent(const CUtensorMap& map_a, const CUtensorMap& map_b,
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN_ - 1) / BN_);
   kernel<<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(map_a, map_b, map_c, out, bias, M, N, K, act,
-                                                                             tma_out, status, map_aux, aux_in);
+                                                                             tma_out, status, map_aux, aux_in, col_stats);
   return cudaSuccess;
 }
 
@@ -577,7 +669,7 @@ int SmCount() {
 bool GemmSupported() { return GetEncodeFn() != nullptr; }
 
 cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void* bias, int M, int N, int K, int act,
-                             unsigned int* status, cudaStream_t stream, void* preact_out) {
+                             unsigned int* status, cudaStream_t stream, void* preact_out, float* col_stats) {
   (void)cudaGetLastError();   // the value returned below must be this launch's own, not an older error of the calling thread
   if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
   // TMA needs 16-byte aligned bases and row pitches: K must be a multiple of 8 bf16 elements.
@@ -604,7 +696,16 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
     if (!MakeMap(&map_aux, preact_out, M, N, 32)) return cudaErrorInvalidValue;
   }
   cudaError_t e = cudaSuccess;
-  if (variant == 0) {
+  if (col_stats != nullptr) {
+    // column statistics of the plain product only: the kernel relies on rows past M being exact zeros
+    if (variant == 0 || !tma_out || preact || bias != nullptr || act != 0) return cudaErrorInvalidValue;
+    const int bn = N > 128 ? 256 : 128;
+    if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, bn)) return cudaErrorInvalidValue;
+    e = N > 128 ? LaunchPersistent<256, 0, 0, kEpiColumnStats>(map_a, map_b, map_c, map_aux, o, nullptr, nullptr, M, N, K, 0, 1,
+                                                               sm_count, status, stream, col_stats)
+                : LaunchPersistent<128, 0, 0, kEpiColumnStats>(map_a, map_b, map_c, map_aux, o, nullptr, nullptr, M, N, K, 0, 1,
+                                                               sm_count, status, stream, col_stats);
+  } else if (variant == 0) {
     if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, BN)) return cudaErrorInvalidValue;
     static bool attr_set = false;
     if (!attr_set) {

@@ -8,7 +8,7 @@ enum GemmAct : int { kActNone = 0, kActRelu = 1, kActGeluTanh = 2 };
 // Extra work of the epilogue: store the pre-activation value (accumulator + bias) to a second matrix besides
 // act(...) of it; or multiply the result by GELU'(aux[m, n]) (the input gradient through a GELU whose
 // pre-activation was kept).
-enum GemmEpi : int { kEpiNone = 0, kEpiStorePreact = 1, kEpiMulGeluGrad = 2 };
+enum GemmEpi : int { kEpiNone = 0, kEpiStorePreact = 1, kEpiMulGeluGrad = 2, kEpiColumnStats = 3 };
 
 // True when the driver exposes cuTensorMapEncodeTiled (needed to build TMA descriptors).
 bool GemmSupported();
@@ -17,8 +17,12 @@ bool GemmSupported();
 // all base pointers 16-byte aligned. bias may be null. status: device word set to 1 when a
 // bounded wait inside the kernel expired (may be null).
 // preact_out (optional, [M,N] bf16, needs N % 8 == 0): receives a*b^T + bias before the activation.
+// col_stats (optional, 2*N floats, needs N % 8 == 0, no bias, no activation): col_stats[n] += sum_m out[m,n] and
+// col_stats[N + n] += sum_m out[m,n]^2 over the rounded bf16 output (the batch statistics of a following
+// normalisation layer, taken while the tile is still on chip).
 cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void* bias, int M, int N, int K, int act,
-                             unsigned int* status, cudaStream_t stream, void* preact_out = nullptr);
+                             unsigned int* status, cudaStream_t stream, void* preact_out = nullptr,
+                             float* col_stats = nullptr);
 
 // out[M,N] = a[M,K] * b[K,N] with b row-major (consumed as an MN-major operand); K % 8 == 0, N % 8 == 0.
 // gelu_preact (optional, [M,N] bf16): the result is multiplied elementwise by GELU'(gelu_preact).

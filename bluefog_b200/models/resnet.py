@@ -9,6 +9,7 @@ are plain GEMMs in NHWC, can run on the hand-written tcgen05 GEMM
 (``bluefog_b200.ops.gemm``) when ``use_b200_gemm`` is set; the stride-1 3x3 convolutions can run as
 implicit GEMMs on the tcgen05 kernel of ``bluefog_b200.ops.conv`` when ``use_b200_conv`` is set.
 """
+import os
 from typing import List, Optional, Type
 
 import torch
@@ -20,9 +21,9 @@ from bluefog_b200.ops.fused_bn import bn_act as _bn_act
 from bluefog_b200.ops.fused_pool import maxpool3x3s2
 
 
-def bn_act(x, bn, relu=True, residual=None):
+def bn_act(x, bn, relu=True, residual=None, stats=None):
     # the batch counters of all layers are advanced together in ResNet.forward
-    return _bn_act(x, bn, relu=relu, residual=residual, count_batches=False)
+    return _bn_act(x, bn, relu=relu, residual=residual, count_batches=False, stats=stats)
 
 
 class MixedBatchNorm2d(nn.BatchNorm2d):
@@ -42,6 +43,10 @@ class MixedBatchNorm2d(nn.BatchNorm2d):
                             w, b, self.training or not self.track_running_stats, momentum, self.eps)
 
 
+# BLUEFOG_B200_FUSE_BN_STATS=0: the BatchNorm after a tcgen05 1x1 convolution takes its own statistics pass
+FUSE_BN_STATS = os.environ.get("BLUEFOG_B200_FUSE_BN_STATS", "1") != "0"
+
+
 class Conv1x1(nn.Conv2d):
     """1x1 convolution; in NHWC with stride 1 it is the GEMM [N*H*W, Cin] x [Cin, Cout] (the strided
     shortcut convolutions stay on the library)."""
@@ -54,14 +59,32 @@ class Conv1x1(nn.Conv2d):
     # library from there down (batch 64: the 14x14 and 7x7 layers), above it the library is on par or ahead
     AUTO_MAX_ROWS = 16384
 
-    def forward(self, x):
+    def takes_b200_gemm(self, x):
         use = self.use_b200_gemm
         if use == "auto":
             use = x.shape[0] * x.shape[2] * x.shape[3] <= self.AUTO_MAX_ROWS
-        if use and self.stride[0] == 1 and x.is_cuda and x.dtype == torch.bfloat16:
+        return bool(use) and self.stride[0] == 1 and x.is_cuda and x.dtype == torch.bfloat16
+
+    def forward(self, x):
+        if self.takes_b200_gemm(x):
             from bluefog_b200.ops import gemm
             return gemm.conv1x1(x, self.weight)
         return super().forward(x)
+
+    def forward_bn_act(self, x, bn, relu, residual=None):
+        """``bn_act(self(x), bn, ...)``; on the tcgen05 path the GEMM epilogue also takes the batch statistics of
+        its output, so the BatchNorm kernels read the activation once instead of twice."""
+        # Only the channel-reducing convolutions (Cout <= Cin, the first of every bottleneck): their GEMM waits on
+        # its input, so the epilogue has time for the sums (200704 x 256 -> 64: +3 us against a 13 us statistics
+        # pass).  A channel-expanding product is bound by its epilogue and loses what the skipped pass saves
+        # (200704 x 64 -> 256: +33 us against 31 us).
+        if (self.takes_b200_gemm(x) and bn.training and FUSE_BN_STATS
+                and self.weight.shape[0] <= self.weight.shape[1]):
+            from bluefog_b200.ops import gemm
+            if gemm.conv1x1_supported(x, self.weight) and self.weight.shape[0] % 8 == 0:
+                sums = fused_bn.take_sums(x.device, self.weight.shape[0])
+                return bn_act(gemm.conv1x1(x, self.weight, col_stats=sums), bn, relu=relu, residual=residual, stats=sums)
+        return bn_act(self(x), bn, relu=relu, residual=residual)
 
 
 class StemConv(nn.Conv2d):
@@ -110,7 +133,7 @@ class Downsample(nn.Sequential):
         super().__init__(Conv1x1(cin, cout, stride, use_b200_gemm=use_b200_gemm), MixedBatchNorm2d(cout))
 
     def forward(self, x):
-        return bn_act(self[0](x), self[1], relu=False)
+        return self[0].forward_bn_act(x, self[1], relu=False)
 
 
 class Conv3x3(nn.Conv2d):
@@ -166,9 +189,9 @@ class Bottleneck(nn.Module):
 
     def forward(self, x):
         identity = x if self.downsample is None else self.downsample(x)
-        out = bn_act(self.conv1(x), self.bn1, relu=True)
+        out = self.conv1.forward_bn_act(x, self.bn1, relu=True)
         out = bn_act(self.conv2(out), self.bn2, relu=True)
-        return bn_act(self.conv3(out), self.bn3, relu=True, residual=identity)
+        return self.conv3.forward_bn_act(out, self.bn3, relu=True, residual=identity)
 
 
 class ResNet(nn.Module):

@@ -68,13 +68,23 @@ def _take(device, n):
     return t, gen, ws
 
 
+def take_sums(device, channels):
+    """2*channels zeroed fp32 values for the kernel that produces a BatchNorm input to add the per-channel sum and
+    sum of squares of its output to; hand them to ``bn_act(..., stats=)``, which then skips its statistics pass."""
+    t, _, _ = _take(device, 2 * channels)
+    return t if t is not None else torch.zeros(2 * channels, dtype=torch.float32, device=device)
+
+
 class _BnActFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu):
+    def forward(ctx, x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu, stats):
         c2 = 2 * x.shape[1]
-        fwd_sums, _, _ = _take(x.device, c2)
+        if stats is not None:
+            fwd_sums = stats
+        else:
+            fwd_sums, _, _ = _take(x.device, c2)
         y, mean, rstd, mask = _b.native.bn_forward(x, residual, gamma, beta, running_mean, running_var, eps, momentum,
-                                                   relu, fwd_sums)
+                                                   relu, fwd_sums, stats is not None)
         # backward needs x, the statistics and one bit per element for the ReLU; not y itself
         ctx.save_for_backward(x, mask, mean, rstd, gamma)
         ctx.relu = relu
@@ -90,11 +100,13 @@ class _BnActFn(torch.autograd.Function):
         if ctx.bwd_sums is not None and ctx.ws.generation == ctx.bwd_gen:
             sums, ctx.bwd_sums = ctx.bwd_sums, None    # a slice is clean only once
         dx, dres, dgamma, dbeta = _b.native.bn_backward(dy, mask, x, mean, rstd, gamma, ctx.relu, ctx.has_res, sums)
-        return dx, (dres if ctx.has_res else None), dgamma, dbeta, None, None, None, None, None
+        return dx, (dres if ctx.has_res else None), dgamma, dbeta, None, None, None, None, None, None
 
 
-def bn_act(x, bn, relu=True, residual=None, count_batches=True):
-    """``bn`` is an ``nn.BatchNorm2d``-like module (weight, bias, running_mean, running_var, eps, momentum)."""
+def bn_act(x, bn, relu=True, residual=None, count_batches=True, stats=None):
+    """``bn`` is an ``nn.BatchNorm2d``-like module (weight, bias, running_mean, running_var, eps, momentum).
+    ``stats``: 2*C fp32 values holding sum(x) and sum(x^2) per channel, written by the producer of ``x``
+    (see ``take_sums``); ignored where the kernels do not apply."""
     use_kernel = (bn.training and x.is_cuda and x.dtype == torch.bfloat16 and bn.weight is not None
                   and _b.native.bn_supported(x)
                   and (residual is None or (residual.dtype == torch.bfloat16 and residual.shape == x.shape)))
@@ -106,7 +118,7 @@ def bn_act(x, bn, relu=True, residual=None, count_batches=True):
         momentum = 0.1 if bn.momentum is None else bn.momentum
         rm = bn.running_mean if bn.track_running_stats else None
         rv = bn.running_var if bn.track_running_stats else None
-        return _BnActFn.apply(x, residual, bn.weight, bn.bias, rm, rv, bn.eps, momentum, relu)
+        return _BnActFn.apply(x, residual, bn.weight, bn.bias, rm, rv, bn.eps, momentum, relu, stats)
     out = bn(x)
     if residual is not None:
         out = out + residual

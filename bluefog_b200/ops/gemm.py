@@ -86,12 +86,12 @@ class _Conv1x1Fn(torch.autograd.Function):
     gradient (a reduction over all pixels) goes to the library's convolution backward."""
 
     @staticmethod
-    def forward(ctx, x, weight):
+    def forward(ctx, x, weight, col_stats=None):
         n, c, h, w = x.shape
         cout = weight.shape[0]
         ctx.save_for_backward(x, weight)
         a = x.permute(0, 2, 3, 1).reshape(n * h * w, c)                  # a view of NHWC memory
-        y = _b.native.gemm_bf16_nt(a, weight.reshape(cout, c), None, 0)
+        y = _b.native.gemm_bf16_nt(a, weight.reshape(cout, c), None, 0, col_stats)
         return y.view(n, h, w, cout).permute(0, 3, 1, 2)                   # channels_last [N, Cout, H, W]
 
     @staticmethod
@@ -107,16 +107,25 @@ class _Conv1x1Fn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = torch.ops.aten.convolution_backward(dy, x, weight, None, (1, 1), (0, 0), (1, 1), False, (0, 0), 1,
                                                      (False, True, False))[1]
-        return dx, dw
+        return dx, dw, None
 
 
-def conv1x1(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """``F.conv2d(x, weight)`` for a [Cout, Cin, 1, 1] filter and stride 1.  bf16 channels_last CUDA
-    activations with Cin % 8 == 0 and Cout % 8 == 0 take the tcgen05 GEMM, the rest the library."""
-    if (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 4
+def conv1x1_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether ``conv1x1`` runs this input on the tcgen05 GEMM."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 4
             and x.shape[1] % 8 == 0 and weight.shape[0] % 8 == 0 and x.numel() > 0
-            and x.is_contiguous(memory_format=torch.channels_last) and available()):
-        return _Conv1x1Fn.apply(x, weight)
+            and x.is_contiguous(memory_format=torch.channels_last) and available())
+
+
+def conv1x1(x: torch.Tensor, weight: torch.Tensor, col_stats=None) -> torch.Tensor:
+    """``F.conv2d(x, weight)`` for a [Cout, Cin, 1, 1] filter and stride 1.  bf16 channels_last CUDA
+    activations with Cin % 8 == 0 and Cout % 8 == 0 take the tcgen05 GEMM, the rest the library.
+    ``col_stats`` (2*Cout fp32 values, only where ``conv1x1_supported``): the GEMM epilogue adds the
+    per-channel sum and sum of squares of the output, the batch statistics of a following BatchNorm."""
+    if conv1x1_supported(x, weight):
+        return _Conv1x1Fn.apply(x, weight, col_stats)
+    if col_stats is not None:
+        raise ValueError("conv1x1: col_stats needs the tcgen05 path (see conv1x1_supported)")
     return torch.nn.functional.conv2d(x, weight)
 
 

@@ -145,3 +145,58 @@ def test_mlp_gelu_with_epilogue_fusion_matches_fp32(M, K, H):
         err = (got.float() - ref).abs().max().item()
         assert err <= 2e-2 * max(1.0, ref.abs().max().item()), (name, err, ref.abs().max().item())
     assert _C.gemm_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (200, 136, 72), (3136, 64, 256), (130, 104, 64), (51200, 256, 64),
+                                   (12544, 1024, 256), (40000, 512, 128), (33, 2048, 512)])
+def test_gemm_epilogue_column_statistics_match_the_stored_output(M, N, K):
+    """The sums that a following BatchNorm consumes are those of the rounded bf16 output, taken in the epilogue;
+    they are added to what the buffer held before."""
+    from bluefog_b200 import _C
+    g = torch.Generator().manual_seed(M + N + K)
+    a = (torch.randn(M, K, generator=g) * 0.5 + 0.1).cuda().to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.5).cuda().to(torch.bfloat16)
+    stats = torch.full((2 * N,), 3.0, device="cuda")
+    out = _C.gemm_bf16_nt(a, w, None, 0, stats)
+    torch.cuda.synchronize()
+    assert _C.gemm_status() == 0
+    plain = _C.gemm_bf16_nt(a, w, None, 0)
+    assert torch.equal(out, plain)
+    o = out.double()
+    s1, s2 = o.sum(0), (o * o).sum(0)
+    got1, got2 = stats[:N].double() - 3.0, stats[N:].double() - 3.0
+    assert (got1 - s1).abs().max().item() <= 1e-4 * o.abs().sum(0).max().item() + 1e-3
+    assert (got2 - s2).abs().max().item() <= 1e-4 * s2.max().item() + 1e-3
+
+
+def test_batchnorm_fed_by_the_gemm_statistics_matches_its_own_pass():
+    from bluefog_b200 import _C
+    from bluefog_b200.models.resnet import Conv1x1, MixedBatchNorm2d
+    from bluefog_b200.ops.fused_bn import bn_act
+    torch.manual_seed(5)
+    results = []
+    # a channel-reducing convolution: the kind whose statistics the model takes in the GEMM epilogue
+    x0 = (torch.randn(8, 256, 14, 14) + 0.3).cuda().to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    res = torch.randn(8, 64, 14, 14).cuda().to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    conv = Conv1x1(256, 64, use_b200_gemm=True).cuda().to(torch.bfloat16)
+    bn = MixedBatchNorm2d(64).cuda()
+    with torch.no_grad():
+        bn.weight.uniform_(0.5, 1.5)
+        bn.bias.uniform_(-0.5, 0.5)
+    for fused in (True, False):
+        bn.running_mean.zero_()
+        bn.running_var.fill_(1.0)
+        x = x0.clone().requires_grad_(True)
+        conv.weight.grad = bn.weight.grad = bn.bias.grad = None
+        if fused:
+            launches = _C.kernel_launch_count() if hasattr(_C, "kernel_launch_count") else None
+            y = conv.forward_bn_act(x, bn, relu=True, residual=res)
+            if launches is not None:     # GEMM + apply: no statistics kernel
+                assert _C.kernel_launch_count() - launches == 2
+        else:
+            y = bn_act(conv(x), bn, relu=True, residual=res)
+        y.float().square().sum().backward()
+        results.append((y.detach().float(), x.grad.float(), conv.weight.grad.float(), bn.weight.grad.float(),
+                        bn.running_mean.clone(), bn.running_var.clone()))
+    for got, want in zip(*results):
+        assert (got - want).norm().item() <= 2e-2 * want.norm().item() + 1e-3

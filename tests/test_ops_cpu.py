@@ -44,3 +44,33 @@ def test_gpt2_small_config_runs_on_cpu_and_uses_hf_names():
     loss = m(x, y)
     loss.backward()
     assert torch.isfinite(loss) and m.wte.weight.grad.shape == (101, 32)
+
+
+def test_mlp_gelu_falls_back_to_the_plain_ops_on_cpu():
+    import torch
+    import torch.nn.functional as F
+    from bluefog_b200.ops import gemm
+    torch.manual_seed(0)
+    a, w1, b1 = torch.randn(6, 16), torch.randn(32, 16), torch.randn(32)
+    w2, b2 = torch.randn(16, 32), torch.randn(16)
+    want = F.linear(F.gelu(F.linear(a, w1, b1), approximate="tanh"), w2, b2)
+    assert torch.allclose(gemm.mlp_gelu(a, w1, b1, w2, b2), want)
+
+
+def test_conv1x1_with_batchnorm_statistics_needs_the_kernel_path():
+    import pytest
+    import torch
+    from bluefog_b200.models.resnet import Conv1x1, MixedBatchNorm2d, bn_act
+    from bluefog_b200.ops import gemm
+    x = torch.randn(2, 16, 4, 4)
+    conv, bn = Conv1x1(16, 8, use_b200_gemm=True), MixedBatchNorm2d(8)
+    assert not gemm.conv1x1_supported(x, conv.weight)
+    with pytest.raises(ValueError):
+        gemm.conv1x1(x, conv.weight, col_stats=torch.zeros(16))
+    # the model-level entry point silently takes the library convolution and the BatchNorm's own statistics
+    torch.manual_seed(1)
+    got = conv.forward_bn_act(x, bn, relu=True)
+    bn2 = MixedBatchNorm2d(8)
+    want = bn_act(conv(x), bn2, relu=True)
+    assert torch.allclose(got, want)
+    assert torch.allclose(bn.running_mean, bn2.running_mean)

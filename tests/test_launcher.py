@@ -49,6 +49,30 @@ def test_end_to_end_allreduce_under_bfrun():
     assert out.returncode == 0, out.stderr[-2000:]
 
 
+@pytest.mark.parametrize("mode", ["normal", "compute-only", "sleep-and-communicate"])
+def test_linear_speedup_study_runs_in_every_mode(mode):
+    import json
+    script = os.path.join(ROOT, "benchmarks", "linear_speedup_study.py")
+    out = bfrun("-np", "2", sys.executable, script, "--no-cuda", "--mode", mode, "--rounds", "2", "--steps-per-round", "3",
+                "--warmup-steps", "1", "--samples", "64", "--dim", "16", "--sleep-seconds", "0.01", "--topology", "ring")
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["mode"] == mode and line["n_ranks"] == 2 and line["job_total"] > line["per_rank"] > 0
+
+
+def test_resource_allocation_example_converges_towards_the_admm_solution(tmp_path):
+    script = os.path.join(ROOT, "examples", "resource_allocation.py")
+    out = bfrun("-np", "3", sys.executable, script, "--no-cuda", "--iterations", "400", "--plot", str(tmp_path / "c.png"),
+                timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = {l.split("relative error")[0].strip(): l for l in out.stdout.splitlines() if "relative error" in l}
+    assert set(lines) == {"EXTRA", "exact diffusion", "gradient tracking"}
+    for l in lines.values():     # "... relative error E after N iterations (E100 after 100)"
+        final, early = float(l.split("relative error")[1].split()[0]), float(l.split("(")[1].split()[0])
+        assert final < 0.5 * early, l
+    assert (tmp_path / "c.png").exists() or (tmp_path / "c.csv").exists()
+
+
 def test_host_parsing(tmp_path):
     from bluefog_b200.run import network_util, env_util
     assert network_util.parse_hosts("a:2, b:4,c") == [("a", 2), ("b", 4), ("c", 1)]

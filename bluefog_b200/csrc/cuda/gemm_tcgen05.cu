@@ -62,6 +62,21 @@ __device__ __forceinline__ float act_fn(float x, int act) {
   return x;
 }
 
+// Order in which the persistent kernel walks the output tiles: groups of eight tile rows, inside a group the
+// row index runs fastest.  The CTAs that are resident together then share 8 A panels and about tiles/8 B panels
+// instead of one or two A panels and every B panel, so a B matrix larger than L2 (a 50 304-column classifier)
+// is streamed from DRAM once per group of eight tile rows rather than once per tile row.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int kGroup = 8;
+  const int per_group = kGroup * tiles_n;
+  const int gid = tile / per_group;
+  const int first = gid * kGroup;
+  const int rows = min(tiles_m - first, kGroup);
+  const int r = tile - gid * per_group;
+  tm = first + r % rows;
+  tn = r / rows;
+}
+
 // two floats in one 64-bit register, the operand form of the packed f32x2 instructions
 __device__ __forceinline__ unsigned long long pack_f32x2(uint32_t lo_bits, uint32_t hi_bits) {
   unsigned long long v;
@@ -305,8 +320,10 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
       int it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / tiles_n) * BM;
-        const int n0 = (tile % tiles_n) * BN_;
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * BM;
+        const int n0 = tn * BN_;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % S;
           if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, failed)) { ok = false; break; }
@@ -403,8 +420,10 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     }
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int acc = local & 1;
-      const int m0 = (tile / tiles_n) * BM;
-      const int n0 = (tile % tiles_n) * BN_;
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * BM;
+      const int n0 = tn * BN_;
       if (!mbar_wait(smem_u32(&bars[2 * S + acc]), (local >> 1) & 1, failed)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m = m0 + q * 32 + lane;

@@ -78,3 +78,4 @@ from bluefog_b200.parallel.optimizers import (  # noqa: E402
     DistributedHierarchicalNeighborAllreduceOptimizer,
 )
 from bluefog_b200.utils.checkpoint import save_checkpoint, load_checkpoint  # noqa: E402
+from bluefog_b200.common.util import check_extension  # noqa: E402

@@ -96,3 +96,39 @@ def test_machine_and_inner_outer_generators():
     with pytest.raises(AssertionError):
         next(tu.GetInnerOuterRingDynamicSendRecvRanks(8, 2, 0))
 
+
+
+def test_every_public_name_of_the_reference_package_exists():
+    """``import bluefog.torch as bf`` -> ``import bluefog_b200.torch as bf`` must not lose a name
+    (list read from bluefog/torch/__init__.py:34-110 of the reference)."""
+    import bluefog_b200.torch as bf
+    names = """
+    init shutdown size local_size rank local_rank machine_size machine_rank load_topology set_topology
+    load_machine_topology set_machine_topology in_neighbor_ranks out_neighbor_ranks in_neighbor_machine_ranks
+    out_neighbor_machine_ranks mpi_threads_supported unified_mpi_window_model_supported nccl_built is_homogeneous
+    suspend resume check_extension
+    allreduce allreduce_nonblocking allreduce_ allreduce_nonblocking_ allgather allgather_nonblocking
+    broadcast broadcast_nonblocking broadcast_ broadcast_nonblocking_ neighbor_allgather neighbor_allgather_nonblocking
+    neighbor_allreduce neighbor_allreduce_nonblocking hierarchical_neighbor_allreduce
+    hierarchical_neighbor_allreduce_nonblocking poll synchronize wait barrier
+    win_create win_free win_update win_update_then_collect win_put_nonblocking win_put win_get_nonblocking win_get
+    win_accumulate_nonblocking win_accumulate win_wait win_poll win_mutex get_win_version
+    get_current_created_window_names win_associated_p turn_on_win_ops_with_associated_p
+    turn_off_win_ops_with_associated_p set_skip_negotiate_stage get_skip_negotiate_stage
+    timeline_start_activity timeline_end_activity timeline_context
+    neighbor_win_put neighbor_win_put_nonblocking neighbor_win_get neighbor_win_get_nonblocking
+    neighbor_win_accumulate neighbor_win_accumulate_nonblocking
+    broadcast_parameters allreduce_parameters broadcast_optimizer_state
+    CommunicationType DistributedAdaptThenCombineOptimizer DistributedAdaptWithCombineOptimizer
+    DistributedGradientAllreduceOptimizer DistributedWinPutOptimizer DistributedAllreduceOptimizer
+    DistributedNeighborAllreduceOptimizer DistributedHierarchicalNeighborAllreduceOptimizer
+    DistributedPullGetOptimizer DistributedPushSumOptimizer
+    GetRecvWeights GetSendWeights IsRegularGraph IsTopologyEquivalent ExponentialGraph ExponentialTwoGraph
+    SymmetricExponentialGraph MeshGrid2DGraph StarGraph RingGraph FullyConnectedGraph
+    GetDynamicOnePeerSendRecvRanks GetExp2DynamicSendRecvMachineRanks GetInnerOuterRingDynamicSendRecvRanks
+    GetInnerOuterExpo2DynamicSendRecvRanks InferSourceFromDestinationRanks InferDestinationFromSourceRanks
+    pair_gossip pair_gossip_nonblocking
+    """.split()
+    missing = [n for n in names if not hasattr(bf, n)]
+    assert not missing, missing
+    bf.check_extension("bluefog_b200")          # the extension of this checkout is built

@@ -26,15 +26,42 @@ def _require_ipyparallel():
         raise SystemExit("ibfrun needs the optional package 'ipyparallel' (pip install ipyparallel).")
 
 
+def _version():
+    from bluefog_b200 import __version__
+    return __version__
+
+
+def _refuse_remote_hosts(args):
+    """The same rule as bfrun: every listed host must be this machine."""
+    from bluefog_b200.run import network_util
+    hosts = []
+    if args.hosts:
+        hosts += [h for h, _ in network_util.parse_hosts(args.hosts)]
+    if args.hostfile:
+        hosts += [h for h, _ in network_util.parse_hostfile(args.hostfile)]
+    remote = [h for h in hosts if not network_util.is_local_host(h)]
+    if remote:
+        raise SystemExit("ibfrun: only this machine is supported (CUDA IPC data plane); remote hosts: " + ", ".join(remote))
+
+
 def parse_args(argv=None):
     p = argparse.ArgumentParser(prog="ibfrun", description="Interactive BlueFog-B200 cluster")
     p.add_argument("action", choices=["start", "stop", "status"])
     p.add_argument("-np", "--num-proc", dest="np", type=int, default=None)
     p.add_argument("--ipython-profile", dest="profile", default=PROFILE)
-    p.add_argument("--disable-heartbeat", action="store_true",
-                   help="Engines do not send heartbeats (long collectives otherwise look like dead engines).")
+    p.add_argument("--enable-heartbeat", action="store_true",
+                   help="Keep the heartbeat check between controller and engines (off by default: an engine inside a "
+                        "long collective otherwise looks dead).")
+    p.add_argument("--disable-heartbeat", action="store_true", help="Accepted; this is the default.")
     p.add_argument("--verbose", action="store_true")
-    p.add_argument("-H", "--hosts", dest="hosts", default=None, help="Accepted; only this machine is supported.")
+    p.add_argument("-v", "--version", action="version", version=_version())
+    p.add_argument("-H", "--hosts", dest="hosts", default=None,
+                   help="host:slots list; only this machine is supported (the data plane is CUDA IPC).")
+    p.add_argument("-hostfile", "--hostfile", dest="hostfile", default=None, help="As --hosts, one 'host slots=N' per line.")
+    p.add_argument("-p", "--ssh-port", dest="ssh_port", type=int, default=None, help="Accepted; no remote hosts.")
+    p.add_argument("--network-interface", dest="nic", default=None, help="Accepted; ranks talk over loopback.")
+    p.add_argument("--use-infiniband", action="store_true", help="Accepted; no effect inside one machine.")
+    p.add_argument("--extra-mpi-flags", dest="extra_flags", default=None, help="Accepted; there is no MPI.")
     return p.parse_args(argv)
 
 
@@ -55,9 +82,10 @@ def _alive(pid):
 
 
 def start(args):
-    _require_ipyparallel()
     if not args.np:
         raise SystemExit("ibfrun start: -np is required.")
+    _refuse_remote_hosts(args)
+    _require_ipyparallel()
     state = _load_state()
     if state and any(_alive(p) for p in state.get("pids", [])):
         raise SystemExit("ibfrun: a cluster is already running; use 'ibfrun stop' first.")
@@ -67,7 +95,7 @@ def start(args):
                                    "--ip=127.0.0.1"], stdout=out, stderr=out, start_new_session=True)
     time.sleep(3.0)   # connection files must exist before the engines start
     engine_cmd = [sys.executable, "-m", "ipyparallel.engine", f"--profile={args.profile}"]
-    if args.disable_heartbeat:
+    if not args.enable_heartbeat:
         engine_cmd.append("--IPEngine.max_heartbeat_misses=0")
     engines = subprocess.Popen([sys.executable, "-m", "bluefog_b200.run.run", "-np", str(args.np), "--"] + engine_cmd,
                                stdout=out, stderr=out, start_new_session=True)

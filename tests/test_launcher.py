@@ -73,6 +73,21 @@ def test_resource_allocation_example_converges_towards_the_admm_solution(tmp_pat
     assert (tmp_path / "c.png").exists() or (tmp_path / "c.csv").exists()
 
 
+def test_ibfrun_accepts_the_reference_flags_and_refuses_remote_hosts(tmp_path):
+    from bluefog_b200.run import interactive_run
+    args = interactive_run.parse_args(["start", "-np", "4", "--ipython-profile", "p", "--enable-heartbeat", "-H", "localhost:4",
+                                       "-p", "22", "--network-interface", "lo", "--use-infiniband", "--extra-mpi-flags", "x"])
+    assert args.np == 4 and args.profile == "p" and args.enable_heartbeat
+    with pytest.raises(SystemExit, match="remote hosts: elsewhere"):
+        interactive_run.start(interactive_run.parse_args(["start", "-np", "2", "-H", "elsewhere:2"]))
+    hostfile = tmp_path / "hosts"
+    hostfile.write_text("localhost slots=2\nfar.away slots=2\n")
+    with pytest.raises(SystemExit, match="far.away"):
+        interactive_run.start(interactive_run.parse_args(["start", "-np", "4", "-hostfile", str(hostfile)]))
+    with pytest.raises(SystemExit, match="-np is required"):
+        interactive_run.start(interactive_run.parse_args(["start"]))
+
+
 def test_host_parsing(tmp_path):
     from bluefog_b200.run import network_util, env_util
     assert network_util.parse_hosts("a:2, b:4,c") == [("a", 2), ("b", 4), ("c", 1)]

@@ -25,7 +25,34 @@ parser.add_argument("--asynchronous-mode", action="store_true", help="push-sum o
 parser.add_argument("--enable-dynamic-topology", action="store_true")
 parser.add_argument("--no-cuda", action="store_true")
 parser.add_argument("--seed", type=int, default=2020)
+parser.add_argument("--save-plot-file", default="", help="write the error curve of rank 0 to this image file")
+parser.add_argument("--plot-interactive", action="store_true", help="show the curve with plt.show()")
 args = parser.parse_args()
+
+
+def save_curve(values, path, interactive, ylabel):
+    """Semilog plot of ``values`` on rank 0 (the numbers as a .csv when matplotlib is not installed)."""
+    if bf.rank() != 0 or not (path or interactive):
+        return
+    try:
+        import matplotlib
+        if not interactive:
+            matplotlib.use("agg")
+        import matplotlib.pyplot as plt
+    except ImportError:
+        if path:
+            csv = os.path.splitext(path)[0] + ".csv"
+            with open(csv, "w") as f:
+                f.write("iteration,%s\n" % ylabel + "".join("%d,%.6e\n" % (i, v) for i, v in enumerate(values)))
+            print("matplotlib is not installed; wrote " + csv)
+        return
+    plt.semilogy(values)
+    plt.xlabel("iteration")
+    plt.ylabel(ylabel)
+    if path:
+        plt.savefig(path)
+    if interactive:
+        plt.show()
 
 bf.init()
 cuda = not args.no_cuda and torch.cuda.is_available() and bf._b.device() >= 0
@@ -76,4 +103,5 @@ err = torch.norm(x - x_bar, p=2).item() / torch.norm(x_bar, p=2).item()
 print(f"[rank {bf.rank()}] relative error after {args.max_iters} iterations: {err:.3e}")
 if bf.rank() == 0:
     print("relative MSE every 20 iterations:", ["%.2e" % m for m in mse[::20]])
+save_curve(mse, args.save_plot_file, args.plot_interactive, "relative error")
 bf.barrier()

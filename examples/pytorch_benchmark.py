@@ -33,6 +33,10 @@ parser.add_argument("--dist-optimizer", default="neighbor_allreduce",
                     help="neighbor_allreduce, allreduce, gradient_allreduce, hierarchical_neighbor_allreduce, "
                          "win_put, pull_get, push_sum, atc, empty")
 parser.add_argument("--disable-dynamic-topology", action="store_true")
+parser.add_argument("--atc-style", action="store_true",
+                    help="adapt-then-combine instead of adapt-with-combine for the (hierarchical_)neighbor_allreduce / allreduce optimizers")
+parser.add_argument("--profiler", action="store_true", help="torch.autograd.profiler around the timed iterations on rank 0")
+parser.add_argument("--partition", type=int, default=None, help="accepted for compatibility with the reference's script; unused there too")
 parser.add_argument("--virtual-topology", default="expo2")
 args = parser.parse_args()
 
@@ -58,12 +62,13 @@ base = torch.optim.SGD(model.parameters(), lr=0.01)
 kw = {"compute_dtype": torch.bfloat16} if (args.bf16 and cuda) else {}
 CT = bf.CommunicationType
 name = args.dist_optimizer
+combine = bf.DistributedAdaptThenCombineOptimizer if args.atc_style else bf.DistributedAdaptWithCombineOptimizer
 if name == "neighbor_allreduce":
-    optimizer = bf.DistributedAdaptWithCombineOptimizer(base, model, CT.neighbor_allreduce, **kw)
+    optimizer = combine(base, model, CT.neighbor_allreduce, **kw)
 elif name == "allreduce":
-    optimizer = bf.DistributedAdaptWithCombineOptimizer(base, model, CT.allreduce, **kw)
+    optimizer = combine(base, model, CT.allreduce, **kw)
 elif name == "empty":
-    optimizer = bf.DistributedAdaptWithCombineOptimizer(base, model, CT.empty, **kw)
+    optimizer = combine(base, model, CT.empty, **kw)
 elif name == "atc":
     optimizer = bf.DistributedAdaptThenCombineOptimizer(base, model, CT.neighbor_allreduce, **kw)
 elif name == "gradient_allreduce":
@@ -117,10 +122,14 @@ def log(msg):
 log(f"Model: {args.model}  batch size: {args.batch_size}  ranks: {bf.size()}  optimizer: {name}")
 timeit.timeit(benchmark_step, number=args.num_warmup_batches)
 rates = []
-for i in range(args.num_iters):
-    t = timeit.timeit(benchmark_step, number=args.num_batches_per_iter)
-    rates.append(args.batch_size * args.num_batches_per_iter / t)
-    log(f"Iter #{i}: {rates[-1]:.1f} img/sec per rank")
+profiling = args.profiler and bf.rank() == 0
+with torch.autograd.profiler.profile(enabled=profiling, use_device="cuda" if cuda else None) as prof:
+    for i in range(args.num_iters):
+        t = timeit.timeit(benchmark_step, number=args.num_batches_per_iter)
+        rates.append(args.batch_size * args.num_batches_per_iter / t)
+        log(f"Iter #{i}: {rates[-1]:.1f} img/sec per rank")
+if profiling:
+    print(prof.key_averages().table(sort_by="self_cpu_time_total", row_limit=25), flush=True)
 mean, conf = float(np.mean(rates)), float(1.96 * np.std(rates))
 log(f"Img/sec per rank: {mean:.1f} +-{conf:.1f}")
 total = bf.allreduce(torch.tensor([mean, conf], dtype=torch.float64), average=False)

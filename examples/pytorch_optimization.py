@@ -19,10 +19,37 @@ parser = argparse.ArgumentParser()
 parser.add_argument("--method", default="exact_diffusion",
                     choices=["diffusion", "exact_diffusion", "gradient_tracking", "push_diging"])
 parser.add_argument("--task", default="linear_regression", choices=["linear_regression", "logistic_regression"])
-parser.add_argument("--max-iters", type=int, default=500)
+parser.add_argument("--max-iters", "--max-iter", dest="max_iters", type=int, default=500)
+parser.add_argument("--save-plot-file", default="", help="write the curve of rank 0's local gradient norm to this image file")
+parser.add_argument("--plot-interactive", action="store_true", help="show the curve with plt.show()")
 parser.add_argument("--lr", type=float, default=0.05)
 parser.add_argument("--topology", default="mesh", choices=["mesh", "expo2", "ring", "star"])
 args = parser.parse_args()
+
+
+def save_curve(values, path, interactive, ylabel):
+    """Semilog plot of ``values`` on rank 0 (the numbers as a .csv when matplotlib is not installed)."""
+    if bf.rank() != 0 or not (path or interactive):
+        return
+    try:
+        import matplotlib
+        if not interactive:
+            matplotlib.use("agg")
+        import matplotlib.pyplot as plt
+    except ImportError:
+        if path:
+            csv = os.path.splitext(path)[0] + ".csv"
+            with open(csv, "w") as f:
+                f.write("iteration,%s\n" % ylabel + "".join("%d,%.6e\n" % (i, v) for i, v in enumerate(values)))
+            print("matplotlib is not installed; wrote " + csv)
+        return
+    plt.semilogy(values)
+    plt.xlabel("iteration")
+    plt.ylabel(ylabel)
+    if path:
+        plt.savefig(path)
+    if interactive:
+        plt.show()
 
 bf.init()
 graph = {"mesh": topology_util.MeshGrid2DGraph, "expo2": topology_util.ExponentialTwoGraph,
@@ -53,9 +80,11 @@ def global_grad_norm(w):
 
 w = torch.zeros(n, 1, dtype=torch.double)
 lr = args.lr
+curve = []          # |gradient of this rank's own loss| at its iterate, one value per iteration
 if args.method == "diffusion":
     for _ in range(args.max_iters):
         w = bf.neighbor_allreduce(w - lr * grad(w), name="w")
+        curve.append(torch.norm(grad(w)).item())
 elif args.method == "exact_diffusion":
     # psi_k = w_k - lr*g(w_k);  phi_k = psi_k + w_k - psi_{k-1};  w_{k+1} = Abar * phi_k, Abar = (I + W)/2
     sw, nw = topology_util.GetRecvWeights(graph, bf.rank())
@@ -66,6 +95,7 @@ elif args.method == "exact_diffusion":
         phi = psi + w - psi_prev
         w = bf.neighbor_allreduce(phi, self_weight=sw, src_weights=nw, name="w")
         psi_prev = psi
+        curve.append(torch.norm(grad(w)).item())
 elif args.method == "gradient_tracking":
     g_prev = grad(w)
     q = g_prev.clone()
@@ -76,6 +106,7 @@ elif args.method == "gradient_tracking":
         g = grad(w)
         q = bf.synchronize(h_q) + g - g_prev
         g_prev = g
+        curve.append(torch.norm(g).item())
 else:  # push-DIGing over one-sided accumulate: column-stochastic weights, ratio correction
     outdeg = len(bf.out_neighbor_ranks())
     a = 1.0 / (outdeg + 1)
@@ -94,10 +125,12 @@ else:  # push-DIGing over one-sided accumulate: column-stochastic weights, ratio
         g = grad(w)
         ext[n:2 * n] += g - g_prev
         g_prev = g
+        curve.append(torch.norm(g).item())
     bf.barrier()
     bf.win_free("ext")
 
 gn = global_grad_norm(w)
 spread = torch.norm(w - bf.allreduce(w, name="w.mean")).item()
 print(f"[rank {bf.rank()}] {args.method}: |global gradient| = {gn:.3e}, distance to the mean iterate = {spread:.3e}")
+save_curve(curve, args.save_plot_file, args.plot_interactive, "local gradient norm")
 bf.barrier()

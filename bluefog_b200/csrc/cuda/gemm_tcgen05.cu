@@ -12,6 +12,14 @@
 // error code, stops issuing work, waits (bounded) for its TMA copies in flight, frees its TMEM
 // and returns.
 //
+// That is the one-tile-per-CTA kernel (gemm_bf16_nt_kernel).  The default is the persistent kernel further
+// down: one CTA per SM walks 128 x 128/256 tiles in groups of eight tile rows, the accumulator is
+// double-buffered in TMEM so that the epilogue of one tile overlaps the MMAs of the next, the output leaves
+// through swizzled staging boxes and TMA stores, and operands may be K-major or MN-major (NT, NN, TN
+// products).  Its epilogue mode is a template parameter: bias + activation; pre-activation and GELU in one
+// pass; product times GELU'(saved pre-activation); column sums and sums of squares of the output for a
+// following BatchNorm.
+//
 // The reference has no GEMM of its own (its models call cuBLAS through PyTorch,
 // examples/pytorch_benchmark.py:76-100); this kernel is what the models of this library use for
 // their linear layers and 1x1 convolutions.

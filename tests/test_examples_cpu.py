@@ -57,3 +57,21 @@ def test_resnet_example_trains_checkpoints_and_resumes(tmp_path):
     assert "epoch 0:" in out and (tmp_path / "ck-0.pth.tar").exists() and os.listdir(tmp_path / "logs")
     out = run_example(2, "pytorch_resnet.py", "--epochs", "2", "--resume-from", fmt.format(epoch=0), *common, timeout=600)
     assert "epoch 1:" in out and "epoch 0:" not in out
+
+
+def test_interactive_notebook_is_valid_and_its_cells_parse():
+    import ast
+    import json
+    with open(os.path.join(ROOT, "examples", "interactive_helloworld.ipynb")) as f:
+        nb = json.load(f)
+    assert nb["nbformat"] == 4 and nb["cells"]
+    import bluefog_b200.torch as bf
+    for cell in nb["cells"]:
+        if cell["cell_type"] != "code":
+            continue
+        src = "".join(l for l in cell["source"] if not l.startswith("%%"))
+        tree = ast.parse(src)
+        # every bf.<name> the notebook teaches exists
+        for node in ast.walk(tree):
+            if isinstance(node, ast.Attribute) and isinstance(node.value, ast.Name) and node.value.id == "bf":
+                assert hasattr(bf, node.attr), node.attr

@@ -89,6 +89,10 @@ def main(argv=None):
         bind = network_util.interface_address(args.nic)
     port = args.master_port or _free_port()
     base_env = env_util.rank_environment(os.environ, timeline=args.timeline_filename, verbose=args.verbose)
+    # Every rank is a PyTorch process whose CPU kernels start an OpenMP team as large as the machine; N ranks
+    # doing that at once oversubscribe the cores and spin against each other (a 400 KB clone took 25 ms with
+    # 4 ranks on 8 cores).  Unless the user chose a thread count, the cores are shared out among the ranks.
+    base_env.setdefault("OMP_NUM_THREADS", str(max(1, (os.cpu_count() or 1) // args.np)))
     procs = []
     for r in range(args.np):
         env = dict(base_env)

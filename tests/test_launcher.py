@@ -88,6 +88,16 @@ def test_ibfrun_accepts_the_reference_flags_and_refuses_remote_hosts(tmp_path):
         interactive_run.start(interactive_run.parse_args(["start"]))
 
 
+def test_cores_are_shared_among_ranks_unless_the_user_set_a_thread_count():
+    code = "import os; print('T', os.environ['OMP_NUM_THREADS'])"
+    env = {k: v for k, v in ENV.items() if k != "OMP_NUM_THREADS"}
+    cmd = [sys.executable, "-m", "bluefog_b200.run.run", "-np", "2", sys.executable, "-c", code]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=120)
+    assert out.stdout.split().count(str(max(1, (os.cpu_count() or 1) // 2))) == 2, out.stdout + out.stderr[-500:]
+    out = subprocess.run(cmd, env=dict(env, OMP_NUM_THREADS="3"), capture_output=True, text=True, timeout=120)
+    assert out.stdout.split().count("3") == 2, out.stdout
+
+
 def test_host_parsing(tmp_path):
     from bluefog_b200.run import network_util, env_util
     assert network_util.parse_hosts("a:2, b:4,c") == [("a", 2), ("b", 4), ("c", 1)]

@@ -17,7 +17,7 @@ def run_example(np_, script, *args, timeout=300):
     return out.stdout
 
 
-@pytest.mark.parametrize("extra", [[], ["--enable-dynamic-topology"], ["--asynchronous-mode"], ["--virtual-topology", "ring"]])
+@pytest.mark.parametrize("extra", [["--enable-dynamic-topology"], ["--asynchronous-mode"], ["--virtual-topology", "ring"]])
 def test_average_consensus_reaches_the_mean(extra, tmp_path):
     out = run_example(4, "pytorch_average_consensus.py", "--no-cuda", "--data-size", "64", "--max-iters", "120",
                       "--save-plot-file", str(tmp_path / "c.png"), *extra)
@@ -34,8 +34,8 @@ def test_decentralized_optimization_methods_converge(method):
     assert norms and max(norms) < (0.2 if method == "diffusion" else 1e-2), out[-800:]
 
 
-@pytest.mark.parametrize("optimizer,extra", [("neighbor_allreduce", ["--atc-style"]), ("gradient_allreduce", []),
-                                             ("win_put", []), ("push_sum", ["--disable-dynamic-topology"])])
+@pytest.mark.parametrize("optimizer,extra", [("neighbor_allreduce", ["--atc-style"]), ("win_put", []),
+                                             ("push_sum", ["--disable-dynamic-topology"])])
 def test_synthetic_benchmark_runs_with_every_optimizer(optimizer, extra):
     out = run_example(2, "pytorch_benchmark.py", "--model", "lenet", "--no-cuda", "--dist-optimizer", optimizer,
                       "--batch-size", "8", "--num-iters", "2", "--num-batches-per-iter", "2", "--num-warmup-batches", "1", *extra)

@@ -21,8 +21,9 @@ def test_version_and_required_arguments():
 
 
 def test_ranks_get_identity_and_flags(tmp_path):
-    code = ("import os;print('R',os.environ['RANK'],os.environ['WORLD_SIZE'],os.environ['LOCAL_RANK'],"
-            "os.environ.get('BLUEFOG_TIMELINE'),os.environ.get('BLUEFOG_LOG_LEVEL'))")
+    # one os.write per rank: a short write to a pipe is atomic, so the ranks' lines cannot interleave
+    code = ("import os;e=os.environ;os.write(1,(' '.join(['R',e['RANK'],e['WORLD_SIZE'],e['LOCAL_RANK'],"
+            "str(e.get('BLUEFOG_TIMELINE')),str(e.get('BLUEFOG_LOG_LEVEL'))])+chr(10)).encode())")
     out = bfrun("-np", "3", "--timeline-filename", str(tmp_path / "t_"), "--verbose", sys.executable, "-c", code)
     assert out.returncode == 0, out.stderr
     lines = sorted(l for l in out.stdout.splitlines() if l.startswith("R "))
@@ -89,7 +90,7 @@ def test_ibfrun_accepts_the_reference_flags_and_refuses_remote_hosts(tmp_path):
 
 
 def test_cores_are_shared_among_ranks_unless_the_user_set_a_thread_count():
-    code = "import os; print('T', os.environ['OMP_NUM_THREADS'])"
+    code = "import os; os.write(1, ('T ' + os.environ['OMP_NUM_THREADS'] + chr(10)).encode())"
     env = {k: v for k, v in ENV.items() if k != "OMP_NUM_THREADS"}
     cmd = [sys.executable, "-m", "bluefog_b200.run.run", "-np", "2", sys.executable, "-c", code]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=120)

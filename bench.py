@@ -35,12 +35,13 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--model", default="resnet50")
-    ap.add_argument("--b200-gemm", nargs="?", const="all", default="off", choices=["off", "auto", "all"],
-                    help="stride-1 1x1 convolutions on the tcgen05 GEMM: all of them (and the classifier), or "
-                         "'auto' = those of at most 16384 pixels.  With cudnn.benchmark on, the library's tuned "
-                         "kernels are 0.9 %% ahead of 'auto' on the whole step, so the default is 'off'")
-    ap.add_argument("--b200-conv", action="store_true",
-                    help="route stride-1 3x3 convolutions through the tcgen05 implicit-GEMM kernel")
+    ap.add_argument("--b200-gemm", nargs="?", const="all", default="all", choices=["off", "auto", "all"],
+                    help="1x1 convolutions and the classifier on the tcgen05 GEMM / implicit-GEMM kernels: all of them "
+                         "(default), 'auto' = the stride-1 ones of at most 16384 pixels, or 'off' = library kernels")
+    ap.add_argument("--library-conv", action="store_true",
+                    help="3x3 convolutions and the stem on the library (cuDNN) instead of the tcgen05 implicit-GEMM "
+                         "kernels (forward, input gradient and filter gradient)")
+    ap.add_argument("--library-loss", action="store_true", help="F.cross_entropy instead of the fused loss kernels")
     ap.add_argument("--no-graphs", action="store_true", help="drive forward/backward op by op instead of a CUDA graph")
     ap.add_argument("--stem", default="s2d", choices=["s2d", "7x7"],
                     help="evaluate the 7x7/2 stem convolution as a 4x4 convolution over 2x2 pixel blocks (s2d) or directly")
@@ -108,6 +109,15 @@ def build_model(name, use_gemm, stem_s2d=False, use_conv=False):
     return getattr(resnet, name)(use_b200_gemm=use_gemm, stem_space_to_depth=stem_s2d, use_b200_conv=use_conv)
 
 
+def make_loss(args):
+    """Mean cross-entropy of the bf16 logits: the fused kernels of this library, or PyTorch's on an fp32 copy."""
+    if args.library_loss:
+        ce = torch.nn.CrossEntropyLoss()
+        return lambda logits, y: ce(logits.float(), y)
+    from bluefog_b200.ops.fused_ce import cross_entropy
+    return cross_entropy
+
+
 def one_peer_schedule(bf, size, rank):
     if size == 1:
         while True:
@@ -125,7 +135,7 @@ def run_ours(args):
     bf.set_topology(bf.ExponentialTwoGraph(size))
     torch.manual_seed(1234 + rank)
     use_gemm = {"off": False, "auto": "auto", "all": True}[args.b200_gemm]
-    model = build_model(args.model, use_gemm, (args.stem == "s2d"), args.b200_conv).to(dev).to(memory_format=torch.channels_last)
+    model = build_model(args.model, use_gemm, (args.stem == "s2d"), not args.library_conv).to(dev).to(memory_format=torch.channels_last)
     bf.broadcast_parameters(model.state_dict(), root_rank=0)
     base = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
     opt = bf.DistributedNeighborAllreduceOptimizer(
@@ -136,9 +146,10 @@ def run_ours(args):
     g = torch.Generator().manual_seed(rank)
     host_x = torch.randn(B, 3, 224, 224, generator=g).pin_memory()
     host_y = torch.randint(0, 1000, (B,), generator=g).pin_memory()
-    dev_x = host_x.to(dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    # the batch as a data loader delivers it: fp32 NCHW; cast, padding and layout change are the stem kernel's job
+    dev_x = host_x.to(dev)
     dev_y = host_y.to(dev)
-    loss_fn = torch.nn.CrossEntropyLoss()
+    loss_fn = make_loss(args)
 
     def set_weights():
         send, recv = next(sched)
@@ -151,7 +162,8 @@ def run_ours(args):
     graphed = None
     if not args.no_graphs:
         from bluefog_b200.utils.graphs import GraphedForwardBackward
-        graphed = GraphedForwardBackward(model, loss_fn, opt, dev_x, dev_y)
+        graphed = GraphedForwardBackward(model, None, opt, dev_x, dev_y,
+                                         forward_loss=lambda x, y: loss_fn(model(x), y))
 
     def step(x, y):
         set_weights()
@@ -159,7 +171,7 @@ def run_ours(args):
             loss = graphed(x, y)          # zero_grad + forward + loss + backward as one CUDA graph
         else:
             opt.zero_grad()
-            loss = loss_fn(model(x).float(), y)
+            loss = loss_fn(model(x), y)
             loss.backward()
         opt.step()
         return loss
@@ -193,7 +205,6 @@ def run_ours(args):
     ms_dev = max_over_ranks(e0.elapsed_time(e1))
     # end to end: every step copies its inputs from pinned host memory (on a copy stream, one step
     # ahead, into one of two device buffers) and reads the loss back to the host
-    host_x16 = host_x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last).pin_memory()
     copy_stream = torch.cuda.Stream()
     bufs = [(torch.empty_like(dev_x), torch.empty_like(dev_y)) for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
@@ -204,7 +215,7 @@ def run_ours(args):
         with torch.cuda.stream(copy_stream):
             if i >= 2:
                 copy_stream.wait_event(consumed[b])      # step i-2 has finished reading this buffer
-            bufs[b][0].copy_(host_x16, non_blocking=True)
+            bufs[b][0].copy_(host_x, non_blocking=True)
             bufs[b][1].copy_(host_y, non_blocking=True)
             ready[b].record(copy_stream)
 
@@ -250,15 +261,16 @@ def run_ours(args):
                        "parallelism": f"dp{size}", "optimizer": "SGD momentum 0.9 lr 0.1, fp32 master weights",
                        "topology": "ExponentialTwoGraph, dynamic one-peer", "exchange_dtype": args.exchange_dtype,
                        "b200_gemm": args.b200_gemm if gemm.available() else "off",
-                       "b200_conv": bool(args.b200_conv),
+                       "b200_conv": bool(not args.library_conv and gemm.available()),
+                       "loss": "library" if args.library_loss else "fused cross-entropy kernels",
                        "stem": "space-to-depth 4x4" if (args.stem == "s2d") else "7x7 stride 2",
                        "cudnn_benchmark": bool(torch.backends.cudnn.benchmark),
                        "cuda_graph": "forward+backward" if not args.no_graphs else "none",
                        "l2": "inputs plus activations exceed the 126 MB L2 every step; no explicit flush"},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 2), "unit": "img/s",
-                    "h2d_bytes_per_step": int(host_x16.numel() * 2 + host_y.numel() * 8),
-                    "host_input": "pinned bf16 NHWC images + int64 labels, copied one step ahead on a copy stream", "host_output": "loss of every step copied to pinned memory and read by the host one step later",
+                    "h2d_bytes_per_step": int(host_x.numel() * 4 + host_y.numel() * 8),
+                    "host_input": "pinned fp32 NCHW images + int64 labels, copied one step ahead on a copy stream", "host_output": "loss of every step copied to pinned memory and read by the host one step later",
                     "d2h_bytes_per_step": 4, "ms_per_step": round(ms_e2e / args.steps, 3)},
             "gpu_launches": int(launches),
             "final_loss": loss_val, "finite": ok,

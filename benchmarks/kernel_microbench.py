@@ -3,7 +3,7 @@
   python benchmarks/kernel_microbench.py --kernel bucket --numel 67108864
   python benchmarks/kernel_microbench.py --kernel combine --numel 67108864 --dtype bfloat16
   python benchmarks/kernel_microbench.py --kernel gemm --m 8192 --n 8192 --k 8192
-  python benchmarks/kernel_microbench.py --kernel winput --numel 67108864
+  python benchmarks/kernel_microbench.py --kernel conv_layers --batch 64
 
 The multi-rank kernels run on a one-process "local world": the peers' buffers are other
 buffers of the same GPU, so the numbers are HBM-bound, not NVLink-bound; they show how close
@@ -37,6 +37,31 @@ def timed(fn, iters, warmup):
     e0.record()
     for _ in range(iters):
         fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def timed_graph(fn, iters, warmup):
+    """Device time per call with the host out of the picture: ``iters`` calls captured into one CUDA graph, the graph
+    replayed ``warmup`` times untimed and then once between two events."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(warmup):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(iters):
+            fn()
+    for _ in range(warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / iters
@@ -148,6 +173,81 @@ def bench_conv(args):
             "library_ms": ms_lib, "library_tflops": flops / ms_lib / 1e9, "status": _C.gemm_status()}
 
 
+# (count in ResNet-50, Cin, Cout, kernel, stride, input height = width) of every convolution of the network
+RESNET50_CONVS = [
+    (1, 64, 64, 1, 1, 56), (3, 64, 64, 3, 1, 56), (4, 64, 256, 1, 1, 56), (2, 256, 64, 1, 1, 56),
+    (1, 256, 128, 1, 1, 56), (1, 128, 128, 3, 2, 56), (4, 128, 512, 1, 1, 28), (1, 256, 512, 1, 2, 56),
+    (3, 512, 128, 1, 1, 28), (3, 128, 128, 3, 1, 28),
+    (1, 512, 256, 1, 1, 28), (1, 256, 256, 3, 2, 28), (6, 256, 1024, 1, 1, 14), (1, 512, 1024, 1, 2, 28),
+    (5, 1024, 256, 1, 1, 14), (5, 256, 256, 3, 1, 14),
+    (1, 1024, 512, 1, 1, 14), (1, 512, 512, 3, 2, 14), (3, 512, 2048, 1, 1, 7), (1, 1024, 2048, 1, 2, 14),
+    (2, 2048, 512, 1, 1, 7), (2, 512, 512, 3, 1, 7),
+]
+
+
+def bench_conv_layers(args):
+    """Forward, input gradient and filter gradient of every convolution shape of ResNet-50 at batch --batch: this
+    library's kernels (through the autograd functions the model uses) against the library convolutions with
+    ``cudnn.benchmark`` on, each timed as a CUDA graph of --iters calls (no host time in the numbers; the operands of
+    one layer fit in L2, as they mostly do between the layers of a step).  One JSON line per shape and a last line with
+    the sums weighted by layer count."""
+    from bluefog_b200.ops import conv
+    torch.backends.cudnn.benchmark = True
+    n = args.batch
+    aten_bwd = torch.ops.aten.convolution_backward
+    total = {"ours": [0.0, 0.0, 0.0], "lib": [0.0, 0.0, 0.0]}
+    for count, cin, cout, k, stride, hw in RESNET50_CONVS:
+        pad = k // 2
+        x = torch.randn(n, cin, hw, hw, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        wt = (torch.randn(cout, cin, k, k, device="cuda") * 0.05).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        ho = (hw + 2 * pad - k) // stride + 1
+        dy = torch.randn(n, cout, ho, ho, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        if k == 1 and stride == 1:
+            x2d, dy2d, w2d = x.permute(0, 2, 3, 1).reshape(-1, cin), dy.permute(0, 2, 3, 1).reshape(-1, cout), wt.reshape(cout, cin)
+            ours_fns = [lambda: _C.gemm_bf16_nt(x2d, w2d, None, 0), lambda: _C.gemm_bf16_nn(dy2d, w2d),
+                        lambda: _C.conv_wgrad(dy, x, [0], [0], [0], 1, 1, False)]
+        else:
+            ours_fns = [lambda: conv.forward_product(x, wt, stride, pad), lambda: conv.input_gradient(dy, wt, x.shape, stride, pad),
+                        lambda: conv.filter_gradient(dy, x, k, stride, pad)]
+        ours = [timed_graph(f, args.iters, args.warmup) for f in ours_fns]
+        conv_args = (None, (stride, stride), (pad, pad), (1, 1), False, (0, 0), 1)
+        lib = [timed_graph(lambda: torch.nn.functional.conv2d(x, wt, stride=stride, padding=pad), args.iters, args.warmup),
+               timed_graph(lambda: aten_bwd(dy, x, wt, *conv_args, (True, False, False)), args.iters, args.warmup),
+               timed_graph(lambda: aten_bwd(dy, x, wt, *conv_args, (False, True, False)), args.iters, args.warmup)]
+        flops = 2.0 * n * ho * ho * cout * cin * k * k
+        for i in range(3):
+            total["ours"][i] += count * ours[i]
+            total["lib"][i] += count * lib[i]
+        print(json.dumps({"conv": [count, cin, cout, k, stride, hw], "ours_ms_fwd_dgrad_wgrad": [round(v, 4) for v in ours],
+                          "library_ms_fwd_dgrad_wgrad": [round(v, 4) for v in lib],
+                          "ours_tflops": [round(flops / v / 1e9, 1) for v in ours], "status": _C.gemm_status()}), flush=True)
+    return {"kernel": "all ResNet-50 convolutions, batch %d: sum over layers (ms)" % n,
+            "ours_fwd_dgrad_wgrad_ms": [round(v, 3) for v in total["ours"]], "ours_total_ms": round(sum(total["ours"]), 3),
+            "library_fwd_dgrad_wgrad_ms": [round(v, 3) for v in total["lib"]], "library_total_ms": round(sum(total["lib"]), 3)}
+
+
+def bench_wgrad(args):
+    """One filter gradient (--conv-shape N CIN COUT H W, --ksize, --stride) on the split-K kernel and on the library."""
+    from bluefog_b200.ops import conv
+    torch.backends.cudnn.benchmark = True
+    n, cin, cout, h, w = args.conv_shape
+    k, stride = args.ksize, args.stride
+    pad = k // 2
+    ho, wo = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+    x = torch.randn(n, cin, h, w, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    wt = torch.zeros(cout, cin, k, k, device="cuda", dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    dy = torch.randn(n, cout, ho, wo, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    ms = timed_graph(lambda: conv.filter_gradient(dy, x, k, stride, pad), args.iters, args.warmup)
+    conv_args = (None, (stride, stride), (pad, pad), (1, 1), False, (0, 0), 1)
+    ms_lib = timed_graph(lambda: torch.ops.aten.convolution_backward(dy, x, wt, *conv_args, (False, True, False)), args.iters, args.warmup)
+    flops = 2.0 * n * ho * wo * cout * cin * k * k
+    nbytes = 2.0 * (x.numel() + dy.numel() + wt.numel())
+    return {"kernel": "conv_wgrad_kernel (tcgen05, split-K)", "shape": [n, cin, cout, h, w], "ksize": k, "stride": stride,
+            "ms": ms, "tflops": flops / ms / 1e9, "frac_of_measured_bf16": flops / ms / 1e9 / PEAKS["bf16_tflops"],
+            "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / PEAKS["hbm_gbs"],
+            "library_ms": ms_lib, "status": _C.gemm_status()}
+
+
 def bench_ln(args):
     """LayerNorm forward/backward on [rows, 1024] and the bias-gradient column sum on [rows/4, 4096] (both
     134 MB at the default 65536 rows: larger than L2)."""
@@ -197,7 +297,10 @@ def bench_bn(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", required=True, choices=["bucket", "combine", "gemm", "bn", "conv", "ln"])
+    ap.add_argument("--kernel", required=True, choices=["bucket", "combine", "gemm", "bn", "conv", "conv_layers", "wgrad", "ln"])
+    ap.add_argument("--ksize", type=int, default=3)
+    ap.add_argument("--stride", type=int, default=1)
+    ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--ln-rows", type=int, default=65536)
     ap.add_argument("--conv-shape", type=int, nargs=5, default=[64, 64, 64, 56, 56], metavar=("N", "CIN", "COUT", "H", "W"))
     ap.add_argument("--bn-shape", type=int, nargs=4, default=[64, 256, 56, 56])
@@ -213,7 +316,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
     torch.cuda.set_device(0)
-    out = {"bucket": bench_bucket, "combine": bench_combine, "gemm": bench_gemm, "bn": bench_bn, "conv": bench_conv, "ln": bench_ln}[args.kernel](args)
+    out = {"bucket": bench_bucket, "combine": bench_combine, "gemm": bench_gemm, "bn": bench_bn, "conv": bench_conv, "conv_layers": bench_conv_layers, "wgrad": bench_wgrad,
+           "ln": bench_ln}[args.kernel](args)
     print(json.dumps(out), flush=True)
 
 

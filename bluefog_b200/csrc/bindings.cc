@@ -7,6 +7,9 @@
 #include <c10/cuda/CUDAStream.h>
 #include <pybind11/stl.h>
 
+#include <map>
+#include <mutex>
+
 #include "common/logging.h"
 #include "common/runtime.h"
 #include "common/windows.h"
@@ -113,6 +116,35 @@ at::Tensor& GemmStatusWord(const at::Tensor& like) {
   static at::Tensor status;
   if (!status.defined()) status = at::zeros({1}, like.options().dtype(at::kInt));
   return status;
+}
+
+// channels_last [N, C, H, W] -> the [n, h, w, c] view the convolution kernels address
+ConvView MakeConvView(const at::Tensor& t, bool stem_view) {
+  const int N = static_cast<int>(t.size(0)), C = static_cast<int>(t.size(1)), H = static_cast<int>(t.size(2)),
+            W = static_cast<int>(t.size(3));
+  if (stem_view) {
+    TORCH_CHECK(C == 16 && W > 3, "the stem view needs a 16-channel image wider than 3 pixels");
+    return ConvView{t.data_ptr(), N, H, W - 3, 64, 16, (long long)W * 16, (long long)H * W * 16};
+  }
+  return ConvView{t.data_ptr(), N, H, W, C, C, (long long)W * C, (long long)H * W * C};
+}
+
+// Zero-initialised scratch of the split-K filter gradients, one per (device, stream): fp32 partial sums and
+// tile counters.  The kernel leaves both zero, so they are cleared only when they are (re)allocated.
+struct WgradScratch {
+  at::Tensor sums, counters;
+};
+WgradScratch& WgradScratchFor(const at::Tensor& like, cudaStream_t stream, int64_t floats) {
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, WgradScratch> all;
+  std::lock_guard<std::mutex> lk(mu);
+  WgradScratch& sc = all[{like.get_device(), stream}];
+  if (!sc.sums.defined() || sc.sums.numel() < floats) {
+    const int64_t want = std::max<int64_t>(floats, int64_t(1) << 23);
+    sc.sums = at::zeros({want}, like.options().dtype(at::kFloat));
+  }
+  if (!sc.counters.defined()) sc.counters = at::zeros({4096}, like.options().dtype(at::kInt));
+  return sc;
 }
 
 struct PyBucketArgs : BucketStepArgs {
@@ -559,6 +591,116 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return y;
   }, py::arg("x"), py::arg("w"), py::arg("flip_taps") = false, py::arg("filter_mode") = 0);
 
+  // ---- general implicit-GEMM convolution (taps, strides) and its filter gradient ---------------
+  // x: bf16 channels_last [N, C, H, W].  stem_view: x has 16 channels and every position reads the 64 consecutive
+  // values of four neighbouring pixels (reduction channels = 64, usable width = W - 3).
+  // w: contiguous bf16 memory [Cout, w_taps, Cred] (filter_mode 0) or [Cred, w_taps, Cout] (filter_mode 1).
+  // y: bf16 channels_last [N, Cout, Hy, Wy], written at (a*out_stride + out_ph, b*out_stride + out_pw) for the
+  // grid of output positions a < Ho, b < Wo; positions of y outside that lattice are left as they are.
+  m.def("conv_igemm", [](at::Tensor x, at::Tensor w, at::Tensor y, int64_t Ho, int64_t Wo, std::vector<int> dh,
+                         std::vector<int> dw, std::vector<int> wt, int64_t w_taps, int64_t in_stride, int64_t filter_mode,
+                         int64_t out_stride, int64_t out_ph, int64_t out_pw, bool stem_view) {
+    TORCH_CHECK(x.is_cuda() && w.is_cuda() && y.is_cuda() && x.dim() == 4 && y.dim() == 4 &&
+                x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && y.scalar_type() == at::kBFloat16,
+                "conv_igemm expects bf16 CUDA tensors");
+    TORCH_CHECK(x.is_contiguous(at::MemoryFormat::ChannelsLast) && y.is_contiguous(at::MemoryFormat::ChannelsLast),
+                "conv_igemm expects channels_last activations");
+    TORCH_CHECK(dh.size() == dw.size() && dh.size() == wt.size() && !dh.empty() && dh.size() <= size_t(kConvMaxTaps),
+                "conv_igemm: between 1 and 16 taps");
+    ConvProblem p{};
+    p.x = MakeConvView(x, stem_view);
+    const int64_t Cout = y.size(1);
+    TORCH_CHECK(w.numel() == Cout * w_taps * p.x.c && y.size(0) == x.size(0), "conv_igemm: filter or output does not match");
+    p.w = w.data_ptr();
+    p.filter_mode = static_cast<int>(filter_mode);
+    p.w_taps = static_cast<int>(w_taps);
+    p.y = y.data_ptr();
+    p.Hy = static_cast<int>(y.size(2)); p.Wy = static_cast<int>(y.size(3)); p.Cout = static_cast<int>(Cout);
+    p.Ho = static_cast<int>(Ho); p.Wo = static_cast<int>(Wo);
+    p.out_stride = static_cast<int>(out_stride); p.out_ph = static_cast<int>(out_ph); p.out_pw = static_cast<int>(out_pw);
+    p.in_stride = static_cast<int>(in_stride);
+    p.taps.T = static_cast<int>(dh.size());
+    for (int i = 0; i < p.taps.T; ++i) { p.taps.dh[i] = dh[i]; p.taps.dw[i] = dw[i]; p.taps.wt[i] = wt[i]; }
+    TORCH_CHECK((Ho - 1) * out_stride + out_ph < y.size(2) && (Wo - 1) * out_stride + out_pw < y.size(3),
+                "conv_igemm: the output lattice leaves y");
+    TORCH_CHECK(ConvIgemmSupported(p), "conv_igemm: unsupported shape");
+    c10::cuda::CUDAGuard g(x.get_device());
+    at::Tensor& status = GemmStatusWord(x);
+    cudaError_t e = LaunchConvIgemm(p, reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(x.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "conv_igemm launch failed: ", cudaGetErrorString(e));
+    return y;
+  }, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("Ho"), py::arg("Wo"), py::arg("dh"), py::arg("dw"), py::arg("wt"),
+     py::arg("w_taps"), py::arg("in_stride") = 1, py::arg("filter_mode") = 0, py::arg("out_stride") = 1,
+     py::arg("out_ph") = 0, py::arg("out_pw") = 0, py::arg("stem_view") = false);
+  m.def("conv_igemm_supported", [](int64_t n, int64_t ho, int64_t wo, int64_t cred, int64_t cout, int64_t in_stride) {
+    int bw, bh, bn;
+    return GemmSupported() && cred >= 64 && cred % 64 == 0 && cout >= 8 && cout % 8 == 0 &&
+           ConvPatch(static_cast<int>(n), static_cast<int>(ho), static_cast<int>(wo), false, &bw, &bh, &bn) &&
+           bw * in_stride <= 256 && bh * in_stride <= 256;
+  });
+  // dw[Cout, w_taps, Cred] (bf16) = sum over positions of dy (x) shifted x, see conv_tcgen05.h
+  m.def("conv_wgrad", [](at::Tensor dy, at::Tensor x, std::vector<int> dh, std::vector<int> dw, std::vector<int> wt,
+                         int64_t w_taps, int64_t in_stride, bool stem_view) {
+    TORCH_CHECK(dy.is_cuda() && x.is_cuda() && dy.dim() == 4 && x.dim() == 4 && dy.scalar_type() == at::kBFloat16 &&
+                x.scalar_type() == at::kBFloat16, "conv_wgrad expects 4-D bf16 CUDA tensors");
+    TORCH_CHECK(x.is_contiguous(at::MemoryFormat::ChannelsLast) && dy.is_contiguous(at::MemoryFormat::ChannelsLast),
+                "conv_wgrad expects channels_last tensors");
+    TORCH_CHECK(dh.size() == dw.size() && dh.size() == wt.size() && !dh.empty() && dh.size() <= size_t(kConvMaxTaps),
+                "conv_wgrad: between 1 and 16 taps");
+    WgradProblem p{};
+    p.dy = MakeConvView(dy, false);
+    p.x = MakeConvView(x, stem_view);
+    p.in_stride = static_cast<int>(in_stride);
+    p.taps.T = static_cast<int>(dh.size());
+    for (int i = 0; i < p.taps.T; ++i) { p.taps.dh[i] = dh[i]; p.taps.dw[i] = dw[i]; p.taps.wt[i] = wt[i]; }
+    p.w_taps = static_cast<int>(w_taps);
+    TORCH_CHECK(ConvWgradSupported(p), "conv_wgrad: unsupported shape");
+    c10::cuda::CUDAGuard g(x.get_device());
+    cudaStream_t stream = CurrentStream(x.get_device());
+    at::Tensor out = at::empty({dy.size(1), w_taps, static_cast<int64_t>(p.x.c)}, x.options());
+    WgradScratch& sc = WgradScratchFor(x, stream, out.numel());
+    p.dw = out.data_ptr();
+    p.workspace = sc.sums.data_ptr<float>();
+    p.workspace_floats = sc.sums.numel();
+    p.counters = reinterpret_cast<unsigned int*>(sc.counters.data_ptr());
+    p.n_counters = static_cast<int>(sc.counters.numel());
+    at::Tensor& status = GemmStatusWord(x);
+    cudaError_t e = LaunchConvWgrad(p, reinterpret_cast<unsigned int*>(status.data_ptr()), stream);
+    TORCH_CHECK(e == cudaSuccess, "conv_wgrad launch failed: ", cudaGetErrorString(e));
+    return out;
+  }, py::arg("dy"), py::arg("x"), py::arg("dh"), py::arg("dw"), py::arg("wt"), py::arg("w_taps"), py::arg("in_stride") = 1,
+     py::arg("stem_view") = false);
+  m.def("conv_wgrad_supported", [](int64_t n, int64_t ho, int64_t wo, int64_t cin, int64_t cout, int64_t in_stride) {
+    int bw, bh, bn;
+    return GemmSupported() && cin >= 64 && cin % 64 == 0 && cout >= 8 && cout % 8 == 0 &&
+           ConvPatch(static_cast<int>(n), static_cast<int>(ho), static_cast<int>(wo), true, &bw, &bh, &bn) &&
+           bw * in_stride <= 256 && bh * in_stride <= 256;
+  });
+
+  // ---- global average pooling, NHWC bf16 ----------------------------------------------------
+  m.def("avgpool_forward", [](at::Tensor x) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.scalar_type() == at::kBFloat16 &&
+                x.is_contiguous(at::MemoryFormat::ChannelsLast) && x.size(1) % 8 == 0,
+                "avgpool_forward expects a bf16 NHWC CUDA tensor with C % 8 == 0");
+    c10::cuda::CUDAGuard g(x.get_device());
+    at::Tensor y = at::empty({x.size(0), x.size(1)}, x.options());
+    cudaError_t e = LaunchAvgPoolForward(x.data_ptr(), y.data_ptr(), static_cast<int>(x.size(0)),
+                                         static_cast<int>(x.size(2) * x.size(3)), static_cast<int>(x.size(1)),
+                                         CurrentStream(x.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "avgpool forward launch failed: ", cudaGetErrorString(e));
+    return y;
+  });
+  m.def("avgpool_backward", [](at::Tensor dy, int64_t H, int64_t W) {
+    TORCH_CHECK(dy.is_cuda() && dy.dim() == 2 && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && dy.size(1) % 8 == 0,
+                "avgpool_backward expects a contiguous bf16 [N, C] gradient with C % 8 == 0");
+    c10::cuda::CUDAGuard g(dy.get_device());
+    at::Tensor dx = at::empty({dy.size(0), dy.size(1), H, W}, dy.options().memory_format(at::MemoryFormat::ChannelsLast));
+    cudaError_t e = LaunchAvgPoolBackward(dy.data_ptr(), dx.data_ptr(), static_cast<int>(dy.size(0)), static_cast<int>(H * W),
+                                          static_cast<int>(dy.size(1)), CurrentStream(dy.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "avgpool backward launch failed: ", cudaGetErrorString(e));
+    return dx;
+  });
+
   m.def("gemm_bf16_nn", [](at::Tensor a, at::Tensor b) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.scalar_type() == at::kBFloat16 &&
                 b.scalar_type() == at::kBFloat16 && a.is_contiguous() && b.is_contiguous() && a.size(1) == b.size(0),
@@ -665,6 +807,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("src_ranks", &PyBucketArgs::src_ranks)
       .def_readwrite("src_weights", &PyBucketArgs::src_weights)
       .def_readwrite("n_readers", &PyBucketArgs::n_readers)
+      .def_readwrite("dst_weights", &PyBucketArgs::dst_weights)
+      .def_readwrite("read_dst_weights", &PyBucketArgs::read_dst_weights)
       .def_readwrite("master", &PyBucketArgs::t_master)
       .def_readwrite("grad", &PyBucketArgs::t_grad)
       .def_readwrite("state1", &PyBucketArgs::t_state1)

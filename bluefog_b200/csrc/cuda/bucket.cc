@@ -60,6 +60,13 @@ Status Bucket::Step(const BucketStepArgs& a, cudaStream_t stream) {
   s.status = ch.status_ptr();
   s.timeout_ns = ch.timeout_ns();
   s.counter_slot = 2;
+  if (a.mode == kModeAnnounceWeights) {
+    if (ch.next_version() == 0) return Status::PreconditionError("bucket step: nothing has been published yet");
+    if (a.dst_weights.empty()) return Status::InvalidArgument("bucket step: no destination weights to announce");
+    const uint64_t v_read = ch.next_version() - 1;
+    s.half = static_cast<int>(v_read & 1);
+    s.wait_epoch = v_read + 1;
+  }
   if (reads) {
     const uint64_t v_read = ch.next_version() - 1;   // latest published version
     ch.AddReaders(v_read, a.n_readers);
@@ -67,6 +74,9 @@ Status Bucket::Step(const BucketStepArgs& a, cudaStream_t stream) {
     s.half = static_cast<int>(v_read & 1);
     s.wait_epoch = v_read + 1;
     s.signal_done = 1;
+    // adapt-with-combine reads a version that was published before this step's weights were known: they are
+    // announced separately (mode 2); every other mode finds them stored beside the version it reads
+    if (a.read_dst_weights) s.use_dst_weight = a.mode == kModeAWC ? 2 : 1;
     for (size_t j = 0; j < a.src_ranks.size(); ++j) {
       s.src_ctrl[j] = ch.ctrl_ptr(a.src_ranks[j]);
       s.src_arena[j] = ch.arena_ptr(a.src_ranks[j], s.half);
@@ -84,6 +94,14 @@ Status Bucket::Step(const BucketStepArgs& a, cudaStream_t stream) {
     p.write_half = static_cast<int>(v_new & 1);
     p.need_done = need_done;
     p.publish_epoch = v_new + 1;
+  }
+  if (!a.dst_weights.empty()) {
+    if (static_cast<int>(a.dst_weights.size()) != ch.world() || ch.world() > kMaxWorld)
+      return Status::InvalidArgument("bucket step: destination weights need one entry per rank");
+    p.world = ch.world();
+    for (int r = 0; r < ch.world(); ++r) p.dst_weight[r] = static_cast<float>(a.dst_weights[r]);
+    if ((a.mode == kModeAWC && reads) || a.mode == kModeAnnounceWeights) p.dst_weight_mode = 2;
+    else if (writes_pub) p.dst_weight_mode = 1;
   }
   BFB_CUDA_OK(LaunchBucketStep(p, stream));
   return Status::OK();

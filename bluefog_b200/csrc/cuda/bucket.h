@@ -26,6 +26,10 @@ struct BucketStepArgs {
   std::vector<int> src_ranks;
   std::vector<double> src_weights;
   int n_readers = 0;            // ranks that read the version this step consumes (my dst list)
+  // Destination weights (world entries; empty = not used).  When used, every rank of the step must use them:
+  // the readers then wait for and apply their sources' weights.
+  std::vector<double> dst_weights;
+  bool read_dst_weights = false;   // the sources attach destination weights to the version this step reads
   void* master = nullptr;
   const void* grad = nullptr;
   const void* const* grad_ptrs = nullptr;              // device array, see BucketParams

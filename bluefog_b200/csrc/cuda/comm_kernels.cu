@@ -63,7 +63,8 @@ __device__ bool wait_ge(const unsigned long long* flag, unsigned long long targe
   for (unsigned long long it = 0; it < kMaxSpinIters; ++it) {
     v = ld_acquire_sys(flag);
     if (v >= target) return true;
-    if (globaltimer_ns() - t0 > timeout_ns) break;
+    // the timer is a slow read next to a poll: look at it once per eight polls
+    if ((it & 7ull) == 7ull && globaltimer_ns() - t0 > timeout_ns) break;
     __nanosleep(backoff);
     if (backoff < 2048) backoff <<= 1;
   }
@@ -113,6 +114,14 @@ __device__ bool pull_prologue(const PullSync& s, const W* host_w, int n_w, W* sm
   for (int j = threadIdx.x; j < s.n_src; j += blockDim.x) {
     unsigned long long seen = 0;
     if (!wait_ge(&s.src_ctrl[j]->epoch, s.wait_epoch, s.timeout_ns, &seen)) {
+      report_error(s.status, kCommTimeoutEpoch, (unsigned)s.src_rank[j], s.wait_epoch, seen);
+      ok = 0;
+    } else if (ld_acquire_sys(&s.src_ctrl[j]->failed_epoch) == s.wait_epoch) {
+      // the owner gave up while producing this version: its payload is not to be combined
+      report_error(s.status, kCommPeerFailed, (unsigned)s.src_rank[j], s.wait_epoch, s.wait_epoch);
+      ok = 0;
+    }
+    if (ok && s.use_dst_weight == 2 && !wait_ge(&s.src_ctrl[j]->weight_epoch, s.wait_epoch, s.timeout_ns, &seen)) {
       report_error(s.status, kCommTimeoutEpoch, (unsigned)s.src_rank[j], s.wait_epoch, seen);
       ok = 0;
     }
@@ -241,7 +250,10 @@ __global__ void __launch_bounds__(kThreads) pack_publish_kernel(const __grid_con
       if (!wait_ge(&p.ctrl->done[p.half], p.need_done, p.timeout_ns, &seen)) {
         report_error(p.status, kCommTimeoutDone, (unsigned)p.my_rank, p.need_done, seen);
         ok = 0;
+        atomicExch(&p.ctrl->launch_failed, 1u);     // later launches of this version skip their copies too
       }
+    } else if (*reinterpret_cast<volatile unsigned int*>(&p.ctrl->launch_failed) != 0u) {
+      ok = 0;
     }
   }
   for (int i = threadIdx.x; i <= p.n_seg; i += blockDim.x) starts[i] = p.chunk_start[i];
@@ -267,7 +279,14 @@ __global__ void __launch_bounds__(kThreads) pack_publish_kernel(const __grid_con
     if (grid_last_block(&p.ctrl->block_counter[0])) {
       if (p.has_dst_weight)
         for (int r = threadIdx.x; r < p.world; r += blockDim.x) p.ctrl->dst_weight[p.half][r] = p.dst_weight[r];
-      if (threadIdx.x == 0) p.ctrl->payload_bytes[p.half] = p.payload_bytes;
+      if (threadIdx.x == 0) {
+        p.ctrl->payload_bytes[p.half] = p.payload_bytes;
+        // a version that was not written completely is still announced (nobody may hang on it), but marked
+        if (*reinterpret_cast<volatile unsigned int*>(&p.ctrl->launch_failed) != 0u) {
+          p.ctrl->failed_epoch = p.publish_epoch;
+          p.ctrl->launch_failed = 0u;
+        }
+      }
       __threadfence_system();
       __syncthreads();
       if (threadIdx.x == 0) st_release_sys(&p.ctrl->epoch, p.publish_epoch);
@@ -435,8 +454,9 @@ __device__ __forceinline__ float opt_update(const OptConst& o, float c, float g,
     s2[i] = v;
     float vhat = v;
     if (o.amsgrad) { vhat = fmaxf(s3[i], v); s3[i] = vhat; }
-    float denom = sqrtf(vhat) / sqrtf(o.bias2) + o.eps;
-    return c - (o.lr / o.bias1) * (m / denom);
+    // correctly rounded square root and division whatever the build's fast-math setting: v is tiny early in training
+    const float denom = __fdiv_rn(__fsqrt_rn(vhat), __fsqrt_rn(o.bias2)) + o.eps;
+    return c - __fdiv_rn(o.lr, o.bias1) * __fdiv_rn(m, denom);
   }
   return c;
 }
@@ -450,6 +470,14 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
   __shared__ int okd;
   const bool reads_peers = (p.mode == kModeAWC || p.mode == kModeCombineOnly || p.mode == kModeGradReduce);
   bool ok = true;
+  if (p.dst_weight_mode == 2 && blockIdx.x == 0) {
+    // the weights this rank attaches to the version its neighbors pull in this step, announced before any wait
+    for (int r = threadIdx.x; r < p.world; r += blockDim.x) p.sync.my_ctrl->dst_weight[p.sync.half][r] = (double)p.dst_weight[r];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_sys(&p.sync.my_ctrl->weight_epoch, p.sync.wait_epoch);
+  }
+  if (p.mode == kModeAnnounceWeights) return;
   if (reads_peers) {
     for (int j = threadIdx.x; j < p.sync.n_src; j += blockDim.x) w_host[j] = p.src_w[j];
     __syncthreads();
@@ -491,7 +519,9 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
       } else {
         for (int i = 0; i < 4; ++i) x[i] = i < cnt ? p.master[i0 + i] : 0.f;
       }
-      // gradient
+      // gradient.  A parameter of the table without a gradient (frozen, or unused in this step) takes no optimizer
+      // update at all - no weight decay, no decay of its moments - as torch.optim skips it.
+      bool seg_has_grad = true;
       for (int i = 0; i < 4; ++i) g[i] = 0.f;
       if (wants_grad) {
         if (p.grad != nullptr) {
@@ -510,6 +540,8 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
           const unsigned long long n = p.seg_numel[lo];
           if (gp != nullptr)
             for (int i = 0; i < 4; ++i) g[i] = (local + i < n) ? GE::load(gp + local + i) * p.grad_scale : 0.f;
+          else
+            seg_has_grad = false;
         }
       }
       // remote terms
@@ -538,10 +570,11 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
         }
       }
       float y[4];
+      const bool upd = has_grad && seg_has_grad;
       if (mode == kModeAWC) {
-        for (int i = 0; i < 4; ++i) y[i] = (has_grad && i < cnt) ? opt_update(o, acc[i], g[i], p.state1, p.state2, p.state3, i0 + i) : acc[i];
+        for (int i = 0; i < 4; ++i) y[i] = (upd && i < cnt) ? opt_update(o, acc[i], g[i], p.state1, p.state2, p.state3, i0 + i) : acc[i];
       } else if (mode == kModeAdaptPublish) {
-        for (int i = 0; i < 4; ++i) y[i] = (has_grad && i < cnt) ? opt_update(o, x[i], g[i], p.state1, p.state2, p.state3, i0 + i) : x[i];
+        for (int i = 0; i < 4; ++i) y[i] = (upd && i < cnt) ? opt_update(o, x[i], g[i], p.state1, p.state2, p.state3, i0 + i) : x[i];
       } else if (mode == kModeCombineOnly) {
         for (int i = 0; i < 4; ++i) y[i] = acc[i];
       } else if (mode == kModeGradReduce) {
@@ -578,11 +611,27 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
       }
     }
   }
-  // Tail: publish my new version and release the sources.
+  // Tail: publish my new version and release the sources.  A block whose wait ran out has not written its part
+  // of the new version: the version is announced all the same (a neighbor must never hang on it) but marked as
+  // failed, so that readers report an error instead of combining it.
   const bool need_tail = p.publish || (reads_peers && p.sync.signal_done);
   if (need_tail) {
+    if (!ok && threadIdx.x == 0) atomicExch(&p.sync.my_ctrl->launch_failed, 1u);
     if (grid_last_block(&p.sync.my_ctrl->block_counter[p.sync.counter_slot])) {
-      if (p.publish && threadIdx.x == 0) st_release_sys(&p.sync.my_ctrl->epoch, p.publish_epoch);
+      if (p.publish) {
+        if (p.dst_weight_mode == 1)
+          for (int r = threadIdx.x; r < p.world; r += blockDim.x)
+            p.sync.my_ctrl->dst_weight[p.write_half][r] = (double)p.dst_weight[r];
+        if (threadIdx.x == 0 && *reinterpret_cast<volatile unsigned int*>(&p.sync.my_ctrl->launch_failed) != 0u) {
+          p.sync.my_ctrl->failed_epoch = p.publish_epoch;
+          p.sync.my_ctrl->launch_failed = 0u;
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) st_release_sys(&p.sync.my_ctrl->epoch, p.publish_epoch);
+      } else if (threadIdx.x == 0) {
+        p.sync.my_ctrl->launch_failed = 0u;
+      }
       if (reads_peers && p.sync.signal_done)
         for (int j = threadIdx.x; j < p.sync.n_src; j += blockDim.x)
           red_add_release_sys(&p.sync.src_ctrl[j]->done[p.sync.half], 1ull);

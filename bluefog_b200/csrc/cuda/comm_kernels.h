@@ -32,6 +32,7 @@ enum CommError : uint32_t {
   kCommTimeoutEpoch = 1,   // a source never published the awaited version
   kCommTimeoutDone = 2,    // readers of an old version never finished
   kCommBadArgument = 3,
+  kCommPeerFailed = 4,     // a source published a version it could not complete (its own wait had expired)
 };
 
 struct alignas(256) ChannelCtrl {
@@ -41,6 +42,13 @@ struct alignas(256) ChannelCtrl {
   unsigned int reserved[2];
   unsigned long long payload_bytes[2];  // size of the published payload per half
   double dst_weight[2][kMaxWorld];      // weight the owner attaches per destination rank
+  // Versions (epoch values) up to which dst_weight[] of the half being *read* is valid: the adapt-with-combine
+  // bucket step announces the destination weights of a step when that step starts, after the data they scale.
+  unsigned long long weight_epoch;
+  // Epoch value of a version whose owner gave up while producing it (a wait ran out): published all the same, so
+  // that nobody hangs, but marked; readers report kCommPeerFailed and leave their outputs alone.
+  unsigned long long failed_epoch;
+  unsigned int launch_failed;           // set by any block of the owner's launches of the current version
 };
 
 // Host-visible status block (pinned, mapped): kernels write, the host reads after the
@@ -83,7 +91,7 @@ struct PullSync {
   int n_src;
   int my_rank;
   int half;
-  int use_dst_weight;
+  int use_dst_weight;           // 1: scale by the sources' dst_weight[half][my_rank]; 2: wait for their weight_epoch first
   int signal_done;              // 1: add 1 to every source's done[half] when the grid is finished
   int counter_slot;             // which block_counter of my ctrl to use
   unsigned long long wait_epoch;
@@ -134,6 +142,10 @@ enum BucketMode : int {
   kModeGradReduce = 3,
   // pub(v) = src (P or g): plain publish of a local buffer
   kModePublishOnly = 4,
+  // only announces this step's destination weights for the version the neighbors are about to pull (what an
+  // adapt-with-combine launch does at its start; as a launch of its own for ranks emulated on one GPU, whose
+  // kernels run one after the other and cannot wait for each other's start)
+  kModeAnnounceWeights = 5,
 };
 
 struct BucketParams {
@@ -167,6 +179,13 @@ struct BucketParams {
   int write_half;
   unsigned long long need_done;
   unsigned long long publish_epoch;
+  // Destination weights of this step (world entries, 1 where unused).  dst_weight_mode 1: they belong to the
+  // version this launch publishes and are stored beside it.  2: they belong to the version this launch *reads*
+  // (adapt-with-combine: the neighbors pull what the previous step published) and are announced at kernel start
+  // through weight_epoch.
+  int dst_weight_mode;
+  int world;
+  float dst_weight[kMaxWorld];
 };
 
 // Launchers. Each returns cudaGetLastError() of the launch.

@@ -3,6 +3,7 @@
 // window; backward gathers: every input pixel looks at the (at most four) windows that
 // contain it and adds the gradients of those that chose it, so no atomics are needed and the
 // result is deterministic.  Eight channels per thread, 16-byte accesses.
+// Global average pooling (the layer before a ResNet classifier) forward and backward as two more streaming kernels.
 // The reference leaves pooling to PyTorch (examples/pytorch_benchmark.py:100).
 #include "pool_kernels.h"
 
@@ -121,6 +122,48 @@ __global__ void __launch_bounds__(kThreads) maxpool_bwd_kernel(const __nv_bfloat
   }
 }
 
+// Global average pooling: y[n, c] = mean_p x[n, p, c]; one thread owns eight channels of one image.
+__global__ void __launch_bounds__(kThreads) avgpool_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                               __nv_bfloat16* __restrict__ y, int N, int P, int C) {
+  const int CG = C >> 3;
+  const int total = N * CG;
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gridDim.x * blockDim.x) {
+    const int g = t % CG, n = t / CG;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    const __nv_bfloat16* src = x + (long long)n * P * C + g * 8;
+    for (int p = 0; p < P; ++p) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(src + (long long)p * C), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    const float inv = 1.f / float(P);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] *= inv;
+    *reinterpret_cast<uint4*>(y + (long long)n * C + g * 8) = pack8(acc);
+  }
+}
+
+// dx[n, p, c] = dy[n, c] / P
+__global__ void __launch_bounds__(kThreads) avgpool_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                               __nv_bfloat16* __restrict__ dx, int N, int P, int C) {
+  const int CG = C >> 3;
+  const long long total = (long long)N * P * CG;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const float inv = 1.f / float(P);
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int g = (int)(t % CG);
+    const int n = (int)(t / ((long long)CG * P));
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(dy + (long long)n * C + g * 8), f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] *= inv;
+    *reinterpret_cast<uint4*>(dx + t * 8) = pack8(f);
+  }
+}
+
 int Grid(long long items) {
   long long b = (items + kThreads - 1) / kThreads;
   if (b < 1) b = 1;
@@ -145,6 +188,22 @@ cudaError_t LaunchMaxPool3x3s2Backward(const void* dy, const void* idx, void* dx
   const int Ho = (H + 2 - 3) / 2 + 1, Wo = (W + 2 - 3) / 2 + 1;
   maxpool_bwd_kernel<<<Grid((long long)N * H * W * (C / 8)), kThreads, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const unsigned char*>(idx), static_cast<__nv_bfloat16*>(dx), N, H, W, C, Ho, Wo);
+  CountKernelLaunch();
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchAvgPoolForward(const void* x, void* y, int N, int P, int C, cudaStream_t stream) {
+  if (C % 8 != 0 || N <= 0 || P <= 0) return cudaErrorInvalidValue;
+  avgpool_fwd_kernel<<<Grid((long long)N * (C / 8)), kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+                                                                          static_cast<__nv_bfloat16*>(y), N, P, C);
+  CountKernelLaunch();
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchAvgPoolBackward(const void* dy, void* dx, int N, int P, int C, cudaStream_t stream) {
+  if (C % 8 != 0 || N <= 0 || P <= 0) return cudaErrorInvalidValue;
+  avgpool_bwd_kernel<<<Grid((long long)N * P * (C / 8)), kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(dy),
+                                                                              static_cast<__nv_bfloat16*>(dx), N, P, C);
   CountKernelLaunch();
   return cudaGetLastError();
 }

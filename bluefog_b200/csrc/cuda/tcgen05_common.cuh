@@ -37,15 +37,21 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait. Returns false (and raises *failed) when the limit expires or another role failed.
+// The limit is counted on the SM's own cycle counter and looked at once per 32 polls: reading %globaltimer in
+// the polling loop costs far more than a poll, and a wait that does not succeed at once would notice its barrier
+// only after two such reads.
+constexpr long long kWaitLimitCycles = 4000000000ll;      // about two seconds at the boost clock
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* failed) {
   if (mbar_try(bar, parity)) return true;
-  const unsigned long long t0 = now_ns();
-  for (;;) {
+  const long long t0 = clock64();
+  for (unsigned polls = 1;; ++polls) {
     if (mbar_try(bar, parity)) return true;
-    if (*failed) return false;
-    if (now_ns() - t0 > kWaitLimitNs) {
-      *failed = 1;
-      return false;
+    if ((polls & 31u) == 0u) {
+      if (*failed) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *failed = 1;
+        return false;
+      }
     }
   }
 }
@@ -144,11 +150,13 @@ inline EncodeTiledFn GetEncodeFn() {
 // cuTensorMapEncodeTiled for the calling thread.  A thread that has not yet made a runtime call that binds
 // the device's primary context (an autograd worker whose first CUDA work is one of these launchers) gets
 // CUDA_ERROR_INVALID_CONTEXT from the driver entry point: bind the context and encode once more.
+// elem_strides (optional, one per dimension): traversal strides; a box of extent e*stride then delivers e elements.
 inline bool EncodeTiled(CUtensorMap* map, cuuint32_t rank, const void* base, const cuuint64_t* dims,
-                        const cuuint64_t* strides, const cuuint32_t* box) {
+                        const cuuint64_t* strides, const cuuint32_t* box, const cuuint32_t* elem_strides = nullptr) {
   EncodeTiledFn fn = GetEncodeFn();
   if (fn == nullptr) return false;
-  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const cuuint32_t unit[5] = {1, 1, 1, 1, 1};
+  const cuuint32_t* estr = elem_strides != nullptr ? elem_strides : unit;
   auto encode = [&] {
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

@@ -18,7 +18,7 @@ import torch.nn.functional as F
 
 from bluefog_b200.ops import fused_bn
 from bluefog_b200.ops.fused_bn import bn_act as _bn_act
-from bluefog_b200.ops.fused_pool import maxpool3x3s2
+from bluefog_b200.ops.fused_pool import global_avgpool, maxpool3x3s2
 
 
 def bn_act(x, bn, relu=True, residual=None, stats=None):
@@ -48,8 +48,8 @@ FUSE_BN_STATS = os.environ.get("BLUEFOG_B200_FUSE_BN_STATS", "1") != "0"
 
 
 class Conv1x1(nn.Conv2d):
-    """1x1 convolution; in NHWC with stride 1 it is the GEMM [N*H*W, Cin] x [Cin, Cout] (the strided
-    shortcut convolutions stay on the library)."""
+    """1x1 convolution; in NHWC with stride 1 it is the GEMM [N*H*W, Cin] x [Cin, Cout]; the strided
+    shortcut convolutions take the implicit-GEMM kernel, which reads every second pixel."""
 
     def __init__(self, cin, cout, stride=1, use_b200_gemm=False):
         super().__init__(cin, cout, kernel_size=1, stride=stride, bias=False)
@@ -69,6 +69,9 @@ class Conv1x1(nn.Conv2d):
         if self.takes_b200_gemm(x):
             from bluefog_b200.ops import gemm
             return gemm.conv1x1(x, self.weight)
+        if self.use_b200_gemm is True and self.stride[0] == 2 and x.is_cuda and x.dtype == torch.bfloat16:
+            from bluefog_b200.ops import conv
+            return conv.conv2d(x, self.weight, 2, 0)       # strided reads inside the implicit-GEMM kernel
         return super().forward(x)
 
     def forward_bn_act(self, x, bn, relu, residual=None):
@@ -93,9 +96,10 @@ class StemConv(nn.Conv2d):
     three input channels leave tensor-core tiles almost empty, sixteen do not.  The parameter
     keeps its [64, 3, 7, 7] shape; the rearrangement of the (tiny) weight is part of the graph."""
 
-    def __init__(self, space_to_depth=False):
+    def __init__(self, space_to_depth=False, use_b200_conv=True):
         super().__init__(3, 64, kernel_size=7, stride=2, padding=3, bias=False)
         self.space_to_depth = space_to_depth
+        self.use_b200_conv = use_b200_conv
 
     def forward(self, x):
         h, w = x.shape[2:]
@@ -122,8 +126,12 @@ class StemConv(nn.Conv2d):
         """The same convolution for an input that still is what the data loader delivered (fp32 or bf16, NCHW
         or NHWC, no gradient): padding, space-to-depth, cast and layout change happen in one kernel."""
         from bluefog_b200.common.basics import get_basics
+        from bluefog_b200.ops import conv
         xs = get_basics().native.s2d_stem_input(x)
-        return F.conv2d(xs, self.space_to_depth_weight())
+        if not self.use_b200_conv:
+            return F.conv2d(xs, self.space_to_depth_weight())
+        # four taps (one per filter row) over 64-value slices of four neighbouring pixels on the tcgen05 kernel
+        return conv.stem_conv(xs, self.space_to_depth_weight())
 
 
 class Downsample(nn.Sequential):
@@ -137,17 +145,17 @@ class Downsample(nn.Sequential):
 
 
 class Conv3x3(nn.Conv2d):
-    """3x3 convolution; with stride 1 and ``use_b200_conv`` it runs as an implicit GEMM on the tcgen05
-    kernel of ``bluefog_b200.ops.conv`` (forward and input gradient), otherwise on the library."""
+    """3x3 convolution (stride 1 or 2); with ``use_b200_conv`` it runs as an implicit GEMM on the tcgen05
+    kernels of ``bluefog_b200.ops.conv`` (forward, input gradient and filter gradient), otherwise on the library."""
 
     def __init__(self, cin, cout, stride=1, use_b200_conv=False):
         super().__init__(cin, cout, kernel_size=3, stride=stride, padding=1, bias=False)
-        self.use_b200_conv = use_b200_conv and stride == 1
+        self.use_b200_conv = use_b200_conv
 
     def forward(self, x):
         if self.use_b200_conv and x.is_cuda and x.dtype == torch.bfloat16:
             from bluefog_b200.ops import conv
-            return conv.conv3x3(x, self.weight)
+            return conv.conv3x3(x, self.weight, self.stride[0])
         return super().forward(x)
 
 
@@ -202,7 +210,7 @@ class ResNet(nn.Module):
         self.inplanes = 64
         self.use_b200_gemm = use_b200_gemm
         self.use_b200_conv = use_b200_conv
-        self.conv1 = StemConv(space_to_depth=stem_space_to_depth)
+        self.conv1 = StemConv(space_to_depth=stem_space_to_depth, use_b200_conv=bool(use_b200_conv))
         self.bn1 = MixedBatchNorm2d(64)
         self.relu = nn.ReLU(inplace=True)
         self.maxpool = nn.MaxPool2d(kernel_size=3, stride=2, padding=1)
@@ -256,7 +264,7 @@ class ResNet(nn.Module):
         stem = self.conv1.forward_from_raw(x) if raw_stem else self.conv1(x)
         x = maxpool3x3s2(bn_act(stem, self.bn1, relu=True))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
-        x = torch.flatten(self.avgpool(x), 1)
+        x = global_avgpool(x)
         if self.use_b200_gemm is True and x.is_cuda and x.dtype == torch.bfloat16:
             from bluefog_b200.ops import gemm
             if gemm.available():

@@ -348,26 +348,9 @@ def neighbor_allreduce(tensor: torch.Tensor, *,
 # --------------------------------------------------------------------------------------
 # hierarchical_neighbor_allreduce
 # --------------------------------------------------------------------------------------
-def hierarchical_neighbor_allreduce_nonblocking(
-        tensor: torch.Tensor, *,
-        self_weight: Optional[float] = None,
-        src_machine_weights: Optional[Dict[int, float]] = None,
-        dst_machine_weights: Optional[Union[Dict[int, float], List[int]]] = None,
-        enable_topo_check: bool = False,
-        name: Optional[str] = None,
-        neighbor_machine_weights=None, send_neighbor_machines=None) -> int:
-    """Machines are the nodes of the topology: the result on every rank of machine M is
-    ``self_weight * mean_M(x) + sum_m w_m * mean_m(x)``.  On an NVSwitch box every rank pulls
-    the contributing ranks' tensors directly, so the local allreduce, the leader exchange
-    and the local broadcast of the reference collapse into one weighted pull."""
-    if neighbor_machine_weights is not None:
-        src_machine_weights = neighbor_machine_weights
-    if send_neighbor_machines is not None:
-        dst_machine_weights = send_neighbor_machines
-    assert _b.is_homogeneous(), \
-        "hierarchical_neighbor_allreduce should be used under homogeneous environment only"
-    assert _b.local_size() > 1, "If local size is 1, you should use neighbor allreduce directly."
-    _check_tensor(tensor, _REDUCE_TYPES, "hierarchical_neighbor_allreduce")
+def _resolve_machine_weights(self_weight, src_machine_weights, dst_machine_weights):
+    """Argument rules of the hierarchical operation (reference bluefog/torch/mpi_ops.py:790-864): all three given,
+    or none (then the machine topology supplies them).  Returns (self_weight, {machine: weight}, {machine: weight})."""
     if self_weight is None and src_machine_weights is None and dst_machine_weights is None:
         topo = _b.load_machine_topology()
         if topo is None:
@@ -393,10 +376,36 @@ def hierarchical_neighbor_allreduce_nonblocking(
     else:
         raise ValueError("Arguments self_weight, src_machine_weights, dst_machine_weights have to "
                          "be presented at the same time.")
-    L, me, my_machine = _b.local_size(), _b.rank(), _b.machine_rank()
+    my_machine = _b.machine_rank()
     for m in list(src_machine_weights) + list(dst_map):
         if m < 0 or m >= _b.machine_size() or m == my_machine:
             raise ValueError("Machine ids must be other machines between 0 and machine_size-1.")
+    return float(self_weight), {int(m): float(w) for m, w in src_machine_weights.items()}, dst_map
+
+
+def hierarchical_neighbor_allreduce_nonblocking(
+        tensor: torch.Tensor, *,
+        self_weight: Optional[float] = None,
+        src_machine_weights: Optional[Dict[int, float]] = None,
+        dst_machine_weights: Optional[Union[Dict[int, float], List[int]]] = None,
+        enable_topo_check: bool = False,
+        name: Optional[str] = None,
+        neighbor_machine_weights=None, send_neighbor_machines=None) -> int:
+    """Machines are the nodes of the topology: the result on every rank of machine M is
+    ``self_weight * mean_M(x) + sum_m w_m * mean_m(x)``.  On an NVSwitch box every rank pulls
+    the contributing ranks' tensors directly, so the local allreduce, the leader exchange
+    and the local broadcast of the reference collapse into one weighted pull."""
+    if neighbor_machine_weights is not None:
+        src_machine_weights = neighbor_machine_weights
+    if send_neighbor_machines is not None:
+        dst_machine_weights = send_neighbor_machines
+    assert _b.is_homogeneous(), \
+        "hierarchical_neighbor_allreduce should be used under homogeneous environment only"
+    assert _b.local_size() > 1, "If local size is 1, you should use neighbor allreduce directly."
+    _check_tensor(tensor, _REDUCE_TYPES, "hierarchical_neighbor_allreduce")
+    self_weight, src_machine_weights, dst_map = _resolve_machine_weights(self_weight, src_machine_weights,
+                                                                         dst_machine_weights)
+    L, me, my_machine = _b.local_size(), _b.rank(), _b.machine_rank()
     src, dst = {}, {}
     for r in range(my_machine * L, (my_machine + 1) * L):
         if r != me:

@@ -57,14 +57,8 @@ class _LinearFn(torch.autograd.Function):
                 da = dy @ w
         if ctx.needs_input_grad[1]:
             # dW[N,K] = dY^T @ A reduces over the rows of two activation matrices: both operands are MN-major
-            # for that product and the kernel reads them in place.  It has no split-K, so a product with
-            # few output tiles and a long reduction (the 1x1 convolutions) stays on the library.
-            n_out, k_in = dy.shape[1], a.shape[1]
-            tiles = ((n_out + 127) // 128) * ((k_in + 255) // 256)
-            if n_out % 8 == 0 and k_in % 8 == 0 and tiles >= _TN_MIN_TILES and hasattr(_b.native, "gemm_bf16_tn"):
-                dw = _b.native.gemm_bf16_tn(dy, a)
-            else:
-                dw = dy.t() @ a
+            # for that product and the kernels read them in place.
+            dw = _weight_gradient(dy, a)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             if dy.shape[1] % 8 == 0 and hasattr(_b.native, "column_sum"):
                 db = _b.native.column_sum(dy).to(dy.dtype)       # fp32 sums of the bf16 gradient in one pass
@@ -83,7 +77,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
 class _Conv1x1Fn(torch.autograd.Function):
     """Stride-1 1x1 convolution of channels_last activations: forward and input gradient are the GEMMs
     [N*H*W, Cin] x [Cin, Cout] and [N*H*W, Cout] x [Cout, Cin] on the tcgen05 kernel; the filter
-    gradient (a reduction over all pixels) goes to the library's convolution backward."""
+    gradient (a reduction over all pixels) is the split-K kernel of ``csrc/cuda/conv_tcgen05.cu``."""
 
     @staticmethod
     def forward(ctx, x, weight, col_stats=None):
@@ -105,8 +99,14 @@ class _Conv1x1Fn(torch.autograd.Function):
             d2 = dy.permute(0, 2, 3, 1).reshape(n * h * w, cout)
             dx = _input_gradient(d2, weight.reshape(cout, c)).view(n, h, w, c).permute(0, 3, 1, 2)
         if ctx.needs_input_grad[1]:
-            dw = torch.ops.aten.convolution_backward(dy, x, weight, None, (1, 1), (0, 0), (1, 1), False, (0, 0), 1,
-                                                     (False, True, False))[1]
+            C = _b.native
+            if (hasattr(C, "conv_wgrad") and c % 64 == 0 and cout % 8 == 0
+                    and C.conv_wgrad_supported(n, h, w, c, cout, 1)):
+                # a reduction over all pixels into a handful of tiles: the split-K kernel with both operands pixel-major
+                dw = C.conv_wgrad(dy, x, [0], [0], [0], 1, 1, False).view(cout, 1, 1, c).permute(0, 3, 1, 2)
+            else:
+                dw = torch.ops.aten.convolution_backward(dy, x, weight, None, (1, 1), (0, 0), (1, 1), False, (0, 0), 1,
+                                                         (False, True, False))[1]
         return dx, dw, None
 
 
@@ -157,11 +157,18 @@ class _MlpGeluFn(torch.autograd.Function):
 
 
 def _weight_gradient(dy: torch.Tensor, a: torch.Tensor) -> torch.Tensor:
-    """dW[N, K] = dY[M, N]^T @ A[M, K] (see ``_LinearFn.backward`` for the tile rule)."""
+    """dW[N, K] = dY[M, N]^T @ A[M, K].  Products with many output tiles take the TN kernel (one CTA per tile walks
+    the whole reduction); products with few tiles and a long reduction take the split-K kernel of the convolution
+    filter gradients, which sees the rows as M images of one pixel."""
     n_out, k_in = dy.shape[1], a.shape[1]
     tiles = ((n_out + 127) // 128) * ((k_in + 255) // 256)
+    C = _b.native
     if n_out % 8 == 0 and k_in % 8 == 0 and tiles >= _TN_MIN_TILES:
-        return _b.native.gemm_bf16_tn(dy, a)
+        return C.gemm_bf16_tn(dy, a)
+    m = dy.shape[0]
+    if (hasattr(C, "conv_wgrad") and n_out % 8 == 0 and k_in % 64 == 0 and dy.is_contiguous() and a.is_contiguous()
+            and C.conv_wgrad_supported(m, 1, 1, k_in, n_out, 1)):
+        return C.conv_wgrad(dy.view(m, n_out, 1, 1), a.view(m, k_in, 1, 1), [0], [0], [0], 1, 1, False).view(n_out, k_in)
     return dy.t() @ a
 
 

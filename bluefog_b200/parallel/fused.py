@@ -16,6 +16,7 @@ wrappers (bluefog/torch/optimizers.py:297-319, 485-841, 166-294).
 
 import math
 import os
+import weakref
 from typing import Dict, Optional
 
 import torch
@@ -30,16 +31,24 @@ OPT_NONE, OPT_SGD, OPT_ADAM = 0, 1, 2
 _ALIGN = 64  # elements; keeps every parameter view 128-byte aligned even in bf16
 
 
+_live = weakref.WeakSet()     # fused optimizers of this process
+
+
+def republish_live():
+    """Calls ``republish()`` on every fused optimizer of this process.  The collective helpers that write parameters
+    in place on all ranks (``broadcast_parameters``, ``allreduce_parameters``, ``broadcast_optimizer_state``) end
+    with this, so that wrapping the optimizer first and broadcasting afterwards - the order of the reference's
+    examples (examples/pytorch_resnet.py:213-238) - hands the neighbors the broadcast values, not the initial ones."""
+    for opt in list(_live):
+        opt.republish()
+
+
 def supported(optimizer, model, communication_type) -> bool:
     """True when the bucket engine can take over: initialised runtime on a GPU, every
-    parameter on that GPU in fp32, optimizer exactly SGD, Adam or AdamW, and a
-    communication type other than the hierarchical one."""
-    from bluefog_b200.parallel.optimizers import CommunicationType
+    parameter on that GPU in fp32, optimizer exactly SGD, Adam or AdamW."""
     if not _b.is_initialized() or _b.device() < 0:
         return False
     if type(optimizer) not in (torch.optim.SGD, torch.optim.Adam, torch.optim.AdamW):
-        return False
-    if communication_type == CommunicationType.hierarchical_neighbor_allreduce:
         return False
     for g in optimizer.param_groups:
         if g.get("capturable") or g.get("differentiable"):
@@ -162,6 +171,7 @@ class _FusedMixin:
         self._armed = False      # set by zero_grad(): the next backward belongs to a regular training step
         self._register_overlap_hooks()
         self._publish_all()
+        _live.add(self)
 
     def _add_bucket(self, gi, params, device, pub_dtype, group):
         names = [self._parameter_names[p] for p in params]
@@ -255,25 +265,73 @@ class _FusedMixin:
         bk.first_step = False
 
     def _combine_recipe(self, communicate):
-        """(self_weight, src_ranks, src_weights, n_readers) for this step."""
+        """(self_weight, src_ranks, src_weights, n_readers, dst_weights) for this step; ``dst_weights`` is None or
+        one weight per rank of the world (what this rank attaches to the copy each destination pulls)."""
         CT = self._CommunicationType
         if not communicate or self._communication_type == CT.empty or _b.size() == 1:
-            return 1.0, [], [], 0
+            return 1.0, [], [], 0, None
         if self._communication_type == CT.allreduce:
             n = _b.size()
             others = [r for r in range(n) if r != _b.rank()]
-            return 1.0 / n, others, [1.0 / n] * len(others), len(others)
+            return 1.0 / n, others, [1.0 / n] * len(others), len(others), None
+        if self._communication_type == CT.hierarchical_neighbor_allreduce:
+            return self._hierarchical_recipe()
         sw, src_ranks, src_w, dst_ranks, dst_w, use_dst, _ = _ops._resolve_neighbor_weights(
             self.self_weight, self.src_weights, self.dst_weights)
-        if use_dst:
-            raise ValueError("The fused optimizers do not support destination weights other than 1.0; "
-                             "fold them into the receivers' src_weights or pass fused=False.")
-        return sw, src_ranks, src_w, len(dst_ranks)
+        dst = None
+        if isinstance(self.dst_weights, dict):
+            # A dictionary of destination weights switches the weight exchange on for this step (on every rank:
+            # readers then wait for their sources' weights), whatever the values are.
+            dst = [1.0] * _b.size()
+            for r, w in zip(dst_ranks, dst_w):
+                dst[r] = float(w)
+        return sw, src_ranks, src_w, len(dst_ranks), dst
+
+    def _hierarchical_recipe(self):
+        """hierarchical_neighbor_allreduce as one weighted pull (the form the generic operation takes as well):
+        every rank of my machine and of the in-neighbor machines is a source, with the machine's weight divided by
+        the local size; the readers of my copy are the other ranks of my machine and all ranks of the out-neighbor
+        machines.  (reference: bluefog/common/nccl_controller.cc:791-857 does a local allreduce, a neighbor
+        allreduce between the local roots and a local broadcast.)"""
+        ls = _b.local_size()
+        sw, src_machines, dst_machines = _ops._resolve_machine_weights(
+            self.self_weight, self.src_machine_weights, self.dst_machine_weights)
+        me, my_machine = _b.rank(), _b.machine_rank()
+        src_ranks, src_w = [], []
+        for r in range(my_machine * ls, (my_machine + 1) * ls):
+            if r != me:
+                src_ranks.append(r)
+                src_w.append(sw / ls)
+        # as with dst_weights: a dictionary switches the weight exchange on for every rank of the step
+        dst = [1.0] * _b.size() if isinstance(self.dst_machine_weights, dict) else None
+        for m in sorted(src_machines):
+            for r in range(m * ls, (m + 1) * ls):
+                src_ranks.append(r)
+                src_w.append(src_machines[m] / ls)
+        for m, w in dst_machines.items():
+            if dst is not None:
+                for r in range(m * ls, (m + 1) * ls):
+                    dst[r] = w
+        n_readers = (ls - 1) + ls * len(dst_machines)
+        return sw / ls, src_ranks, src_w, n_readers, dst
 
     def _publish_all(self):
         for bk in self._buckets:
             a = self._new_args(bk, MODE_PUBLISH_ONLY)
             bk.native.step(a)
+
+    @torch.no_grad()
+    def republish(self):
+        """Makes values written into ``p.data`` after construction (a broadcast, ``model.load_state_dict``, a manual
+        edit) the values the next step starts from and the neighbors read.  With bf16 compute ``p.data`` is the
+        bf16 shadow: where it no longer equals the rounded fp32 master it replaces the master value.  The peer-
+        visible copy is then written again.  Collective: every rank must call it the same number of times (the
+        published versions advance in lockstep)."""
+        for bk in self._buckets:
+            if bk.shadow is not None:
+                changed = bk.shadow != bk.master.to(torch.bfloat16)
+                bk.master.copy_(torch.where(changed, bk.shadow.float(), bk.master))
+        self._publish_all()
 
     # ------------------------------------------------------------------ public API
     @property
@@ -320,18 +378,23 @@ class _FusedMixin:
 
     def _launch_bucket(self, bk, recipe):
         """Launches the step of one bucket on the current stream."""
-        self_w, src_ranks, src_w, n_readers = recipe
+        self_w, src_ranks, src_w, n_readers, dst_w = recipe
         if self._style == "awc":
             a = self._new_args(bk, MODE_AWC)
             self._fill_opt(a, bk)
             a.self_weight, a.src_ranks, a.src_weights, a.n_readers = self_w, src_ranks, src_w, n_readers
+            if dst_w is not None:
+                a.dst_weights, a.read_dst_weights = dst_w, True
             bk.native.step(a)
         elif self._style == "atc":
             a = self._new_args(bk, MODE_ADAPT_PUBLISH)
             self._fill_opt(a, bk)
+            if dst_w is not None:
+                a.dst_weights = dst_w
             bk.native.step(a)
             c = self._new_args(bk, MODE_COMBINE_ONLY)
             c.self_weight, c.src_ranks, c.src_weights, c.n_readers = self_w, src_ranks, src_w, n_readers
+            c.read_dst_weights = dst_w is not None
             bk.native.step(c)
         else:  # gradient allreduce
             n = _b.size()
@@ -390,6 +453,9 @@ class _FusedMixin:
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        # a device-side wait of an earlier step that ran out left its record in pinned host memory: raise it now
+        # rather than only when somebody calls check()
+        self.check()
         self._local_steps += 1
         communicate = self._local_steps % self._num_steps_per_communication == 0
         recipe = self._step_recipe if self._early else None
@@ -428,42 +494,72 @@ class _FusedMixin:
         return out
 
     @torch.no_grad()
-    def load_master_parameters(self, state: Dict[str, torch.Tensor]):
+    def load_master_parameters(self, state: Dict[str, torch.Tensor], publish: bool = True):
+        """Loads fp32 master values by model name.  ``publish=False`` leaves the peer-visible copy alone for a caller
+        that runs on some ranks only and lets every rank call ``republish()`` or ``broadcast_from()`` afterwards."""
         for bk in self._buckets:
             for i, name in enumerate(bk.names):
                 if name in state:
                     bk.view(bk.master, i).copy_(state[name].to(bk.master.device, torch.float32).reshape(bk.params[i].shape))
             if bk.shadow is not None:
                 bk.shadow.copy_(bk.master)
-        self._publish_all()
+        if publish:
+            self._publish_all()
+
+    def _state_pairs(self, bk):
+        if self._opt_kind == OPT_SGD:
+            return (("momentum_buffer", bk.state1),)
+        return (("exp_avg", bk.state1), ("exp_avg_sq", bk.state2), ("max_exp_avg_sq", bk.state3))
 
     def state_dict(self):
         if self._opt_kind == OPT_ADAM:
             for bk in self._buckets:
                 for p in bk.params:
                     self.state[p]["step"] = torch.tensor(float(bk.steps))
-        return self._base_cls.state_dict(self)
+        out = self._base_cls.state_dict(self)
+        # what the flat buffers cannot say by themselves: whether SGD's momentum buffer has been initialised yet
+        out["bluefog_b200"] = {"first_step": [bool(bk.first_step) for bk in self._buckets],
+                               "steps": [int(bk.steps) for bk in self._buckets]}
+        return out
 
     @torch.no_grad()
     def load_state_dict(self, state_dict):
-        self._base_cls.load_state_dict(self, state_dict)
-        # torch replaced the state tensors by copies: move the values back into the flat buffers
-        for bk in self._buckets:
+        """Loads hyper-parameters through the base class and copies the state tensors straight into the fp32 flat
+        buffers.  (``torch.optim.Optimizer.load_state_dict`` casts floating state to the parameter's dtype, which
+        with bf16 compute is the bf16 shadow: the moments would lose their low mantissa bits on every resume.)"""
+        saved_groups = state_dict["param_groups"]
+        if len(saved_groups) != len(self.param_groups) or any(
+                len(sg["params"]) != len(g["params"]) for sg, g in zip(saved_groups, self.param_groups)):
+            raise ValueError("loaded state dict does not match the optimizer's parameter groups")
+        by_id = {}
+        for sg, g in zip(saved_groups, self.param_groups):
+            for old_id, p in zip(sg["params"], g["params"]):
+                by_id[old_id] = p
+        loaded = {by_id[k]: v for k, v in state_dict["state"].items() if k in by_id}
+        self._base_cls.load_state_dict(self, {"state": {}, "param_groups": saved_groups})
+        extra = state_dict.get("bluefog_b200")
+        for k, bk in enumerate(self._buckets):
+            saw_momentum = False
             for i, p in enumerate(bk.params):
+                src = loaded.get(p, {})
                 st = self.state[p]
-                pairs = (("momentum_buffer", bk.state1),) if self._opt_kind == OPT_SGD else \
-                    (("exp_avg", bk.state1), ("exp_avg_sq", bk.state2), ("max_exp_avg_sq", bk.state3))
-                for key, flat in pairs:
+                for key, flat in self._state_pairs(bk):
                     if flat is None:
                         continue
-                    val = st.get(key)
+                    val = src.get(key)
                     if isinstance(val, torch.Tensor):
-                        bk.view(flat, i).copy_(val)
-                        if key == "momentum_buffer":
-                            bk.first_step = False
+                        bk.view(flat, i).copy_(val.to(flat.device, torch.float32).reshape(p.shape))
+                        saw_momentum = saw_momentum or key == "momentum_buffer"
                     st[key] = bk.view(flat, i)
-                if "step" in st:
-                    bk.steps = int(float(st["step"]))
+                if "step" in src:
+                    bk.steps = int(float(src["step"]))
+                if self._opt_kind == OPT_ADAM:
+                    st["step"] = torch.tensor(float(bk.steps))
+            if extra is not None and k < len(extra.get("first_step", [])):
+                bk.first_step = bool(extra["first_step"][k])
+                bk.steps = int(extra["steps"][k])
+            elif self._opt_kind == OPT_SGD:
+                bk.first_step = not saw_momentum     # a torch.optim.SGD dict has buffers only after its first step
 
     @torch.no_grad()
     def broadcast_from(self, root_rank: int = 0):

@@ -44,6 +44,13 @@ def broadcast_parameters(params, root_rank):
         handles.append(_ops.broadcast_nonblocking_(t, root_rank, name="broadcast.param." + name))
     for h in handles:
         _ops.synchronize(h)
+    _republish_fused()
+
+
+def _republish_fused():
+    """Parameters that a fused optimizer keeps in buckets were just written in place on every rank."""
+    from bluefog_b200.parallel import fused
+    fused.republish_live()
 
 
 def allreduce_parameters(params):
@@ -56,6 +63,7 @@ def allreduce_parameters(params):
         handles.append(_ops.allreduce_nonblocking_(t, average=True, name="allreduce.param." + name))
     for h in handles:
         _ops.synchronize(h)
+    _republish_fused()
 
 
 def _broadcast_object(obj, root_rank, name):
@@ -111,7 +119,11 @@ def broadcast_optimizer_state(optimizer, root_rank):
             else:
                 scalars[(pid, key)] = value.item() if isinstance(value, torch.Tensor) else value
     groups = [{k: v for k, v in g.items() if k != "params"} for g in state_dict["param_groups"]]
-    scalars, groups = _broadcast_object((scalars, groups), root_rank, "optimizer.scalars")
+    # "bluefog_b200": what a fused optimizer keeps beside its flat buffers (step counts, SGD's first-step flag)
+    scalars, groups, fused_extra = _broadcast_object((scalars, groups, state_dict.get("bluefog_b200")), root_rank,
+                                                     "optimizer.scalars")
+    if fused_extra is not None:
+        state_dict["bluefog_b200"] = fused_extra
     broadcast_parameters(tensors, root_rank)
     for (pid, key), value in scalars.items():
         cur = state_dict["state"][pid].get(key)

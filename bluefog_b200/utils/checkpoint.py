@@ -45,16 +45,18 @@ def save_checkpoint(path, model, optimizer, extra=None, all_ranks=False):
 
 
 def load_checkpoint(path, model, optimizer=None, root_rank=0, broadcast=True, map_location="cpu"):
-    """Loads ``path`` where it exists and makes all ranks consistent with ``root_rank``.
-    Returns the ``extra`` entry (or None)."""
-    from bluefog_b200.parallel.utility import broadcast_optimizer_state, broadcast_parameters
+    """Loads ``path`` where it exists and makes all ranks consistent with ``root_rank``: parameters (fp32 masters of
+    a fused optimizer), optimizer state, the model's buffers (BatchNorm running statistics and counters) and the
+    ``extra`` entry, which is returned on every rank (None when the file has none).  Collective: every rank calls it."""
+    from bluefog_b200.parallel.utility import _broadcast_object, broadcast_optimizer_state, broadcast_parameters
     extra = None
     have = os.path.exists(path)
+    fused = getattr(optimizer, "load_master_parameters", None) is not None
     if have:
         payload = torch.load(path, map_location=map_location, weights_only=False)
-        loader = getattr(optimizer, "load_master_parameters", None)
-        if loader is not None:
-            loader(payload["model"])
+        if fused:
+            # no publish here: this branch runs only where the file is, the peer-visible copies advance in lockstep
+            optimizer.load_master_parameters(payload["model"], publish=False)
             other = {k: v for k, v in payload["model"].items() if k not in dict(model.named_parameters())}
             model.load_state_dict(other, strict=False)
         else:
@@ -62,12 +64,18 @@ def load_checkpoint(path, model, optimizer=None, root_rank=0, broadcast=True, ma
         if optimizer is not None and "optimizer" in payload:
             optimizer.load_state_dict(payload["optimizer"])
         extra = payload.get("extra")
-    if broadcast and _b.is_initialized() and _b.size() > 1:
-        resync = getattr(optimizer, "broadcast_from", None)
-        if resync is not None:
-            resync(root_rank)
+    distributed = broadcast and _b.is_initialized() and _b.size() > 1
+    if distributed:
+        if fused:
+            optimizer.broadcast_from(root_rank)           # masters, optimizer state, step counters; republishes
+            buffers = dict(model.named_buffers())
+            if buffers:
+                broadcast_parameters(buffers, root_rank)
         else:
             broadcast_parameters(model.state_dict(), root_rank)
             if optimizer is not None:
                 broadcast_optimizer_state(optimizer, root_rank)
+        extra = _broadcast_object(extra, root_rank, "checkpoint.extra")
+    elif fused:
+        optimizer.republish()
     return extra

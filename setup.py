@@ -15,21 +15,6 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join("bluefog_b200", "csrc")
 
 
-def cutlass_include_dirs():
-    """CUTLASS/CuTe headers vendored inside the Python environment (used by the tcgen05 kernels)."""
-    import importlib.util
-    out = []
-    for pkg, rel in (("flashinfer", "data/cutlass/include"), ("tilelang", "3rdparty/cutlass/include")):
-        spec = importlib.util.find_spec(pkg)
-        if spec is None or not spec.submodule_search_locations:
-            continue
-        cand = os.path.join(list(spec.submodule_search_locations)[0], rel)
-        if os.path.isdir(cand):
-            out.append(cand)
-            break
-    return out
-
-
 def sources():
     files = [os.path.join(CSRC, "bindings.cc")]
     files += sorted(glob.glob(os.path.join(CSRC, "common", "*.cc")))
@@ -47,7 +32,7 @@ NVCC_FLAGS = [
 ext = CUDAExtension(
     name="bluefog_b200._C",
     sources=sources(),
-    include_dirs=[os.path.join(ROOT, CSRC)] + cutlass_include_dirs(),
+    include_dirs=[os.path.join(ROOT, CSRC)],
     extra_compile_args={"cxx": ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-sign-compare", "-Wno-unused-function"],
                         "nvcc": NVCC_FLAGS},
     libraries=["rt"],

@@ -40,6 +40,26 @@ def test_checkpoint_roundtrip(tmp_path):
     run_ranks("checkpoint", 2, env={"BFB_CKPT": str(tmp_path / "ckpt.pth.tar")})
 
 
+def test_checkpoint_found_on_the_root_only(tmp_path):
+    run_ranks("checkpoint_root_only", 3, env={"BFB_CKPT": str(tmp_path / "root_only.pth.tar")})
+
+
+def test_neighbor_operation_sweeps():
+    run_ranks("neighbor_sweeps", 4, timeout=400)
+
+
+def test_neighbor_operation_sweeps_three_ranks():
+    run_ranks("neighbor_sweeps", 3, timeout=400)
+
+
+def test_associated_p_follows_random_weights():
+    run_ranks("win_random_p", 4, timeout=300)
+
+
+def test_local_step_warning_and_duplicated_layers():
+    run_ranks("optimizer_warnings", 2, timeout=300)
+
+
 def test_rank_that_leaves_is_detected():
     run_ranks("rank_exits_early", 3, timeout=120)
 

@@ -112,6 +112,9 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   __shared__ uint32_t tmem_base_s;
   __shared__ int failed_s;
   __shared__ int go_s;              // the epilogue warps' common decision to process a tile
+  // The tap tables are copied to shared memory with constant indices: indexing the kernel parameter with a loop
+  // variable would move it to local memory, whose loads sit on the producers' critical path.
+  __shared__ int tap_dh_s[kConvMaxTaps], tap_dw_s[kConvMaxTaps], tap_wt_s[kConvMaxTaps];
   volatile int* failed = &failed_s;
 
   const int warp = threadIdx.x >> 5;
@@ -123,6 +126,12 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   const uint32_t bytes_a = uint32_t(g.bw * g.bh * g.bn) * 128u;      // what one A box delivers
 
   if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < kConvMaxTaps; ++i) {
+      tap_dh_s[i] = g.dh[i];
+      tap_dw_s[i] = g.dw[i];
+      tap_wt_s[i] = g.wt[i];
+    }
     failed_s = 0;
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&bars[s]), 2);                // the activation producer and the filter producer
@@ -172,11 +181,11 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           const uint32_t full = smem_u32(&bars[s]);
           if (!filter_side) {
             mbar_expect_tx(full, bytes_a);
-            tma_load_4d(smem_u32(stage_a + size_t(s) * Cfg::kBytesA), &map_x, full, ci0, w0 * g.in_stride + g.dw[tap],
-                        h0 * g.in_stride + g.dh[tap], n0);
+            tma_load_4d(smem_u32(stage_a + size_t(s) * Cfg::kBytesA), &map_x, full, ci0, w0 * g.in_stride + tap_dw_s[tap],
+                        h0 * g.in_stride + tap_dh_s[tap], n0);
           } else {
             mbar_expect_tx(full, Cfg::kBytesB);
-            const int wtap = g.wt[tap];
+            const int wtap = tap_wt_s[tap];
             if (BMODE == 0) {
               tma_load_2d(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), &map_w, full, wtap * g.Cin + ci0, co0);
             } else {
@@ -202,7 +211,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % S;
           if (!mbar_wait(smem_u32(&bars[s]), (it / S) & 1, failed)) { ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          // (no tcgen05 fence here: the data arrived through the async proxy and its mbarrier, which the wait above
+          // observed; the fence orders tcgen05 operations of different threads, e.g. the epilogue's loads of an accumulator)
           const uint64_t adesc = make_desc(smem_u32(stage_a + size_t(s) * Cfg::kBytesA));
           const uint32_t b_addr = smem_u32(stage_b + size_t(s) * Cfg::kBytesB);
           const uint64_t bdesc = BMODE == 0 ? make_desc(b_addr) : make_desc_mn(b_addr, 8192, 1024);
@@ -320,21 +330,294 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 }
 
 // ------------------------------------------------------------------------------------------------------ //
+// 3x3 / stride 1 / pad 1 with the input patch loaded once: conv_halo_kernel.
+//
+// The per-tap kernel above fetches the shifted input patch nine times.  Here a tile is a run of at most 128
+// consecutive positions of the image *padded by one pixel on every side* (rows of Wp = W + 2 positions, bh rows
+// per tile), and one TMA box of {64 channels, Wp, bh + 2 rows} per 64-channel slice brings the patch with its
+// halo into shared memory as [(bh + 2) * Wp rows x 128 bytes].  Output position m of the tile then meets, for tap
+// (dh, dw), patch row  m + (dh + 1) * Wp + (dw + 1):  the A operand of the tap is the same patch with the matrix
+// descriptor's start address moved by that many rows of 128 bytes.  Such a start is not aligned to the 1024-byte
+// period of the 128-byte swizzle; the tensor core applies the swizzle to the absolute shared-memory address, as
+// TMA did when it wrote the patch, so the rows line up (base-offset field of the descriptor left at zero).
+// Two of every Wp positions of a tile are padding columns: their accumulator rows are computed and dropped.
+// The filter arrives tap by tap through its own ring, or - when all nine taps of the output-channel tile fit
+// (64 -> 64 channels) - is loaded once per CTA and stays resident.
+// ------------------------------------------------------------------------------------------------------ //
+struct HaloGeom {
+  int N, H, W, Cin, Cout;
+  int Wp, bh, tiles_h, tiles_co;
+  int T;
+  signed char dh[kConvMaxTaps], dw[kConvMaxTaps];
+  unsigned char wt[kConvMaxTaps];
+  int slots_a, slots_b;            // ring depths (slots_b = 0: resident filter)
+  unsigned int slot_bytes_a;       // multiple of 1024; room for the furthest row any tap reads
+  unsigned int patch_bytes;        // what one box delivers
+};
+
+template <int BN_>
+struct HaloCfg {
+  static constexpr uint32_t kBytesB = BN_ * BK * 2;               // one tap, one 64-channel slice
+  static constexpr uint32_t kCols = 2 * BN_ < 32 ? 32 : 2 * BN_;
+  static constexpr int kMaxBars = 48;
+  static constexpr size_t kSmemLimit = 226 * 1024;      // dynamic part; the kernel also has a few static words
+  static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN_ >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+};
+
+template <int BN_, int BMODE>
+__global__ void __launch_bounds__(kIgemmThreads, 1)
+conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const HaloGeom g,
+                 __nv_bfloat16* __restrict__ y, unsigned int* __restrict__ status) {
+  using Cfg = HaloCfg<BN_>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int SA = g.slots_a;
+  const bool resident = g.slots_b == 0;
+  const int cblocks = g.Cin / BK;
+  const int SB = resident ? g.T * cblocks : g.slots_b;
+  unsigned char* stage_a = smem;
+  unsigned char* stage_b = smem + size_t(SA) * g.slot_bytes_a;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_b + size_t(SB) * Cfg::kBytesB);
+  uint64_t* full_a = bars;
+  uint64_t* empty_a = bars + SA;
+  uint64_t* full_b = bars + 2 * SA;            // resident: full_b[0] only
+  uint64_t* empty_b = full_b + (resident ? 1 : SB);
+  uint64_t* acc_full = empty_b + (resident ? 0 : SB);
+  uint64_t* acc_empty = acc_full + 2;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int failed_s;
+  __shared__ int go_s;
+  volatile int* failed = &failed_s;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int spatial = g.N * g.tiles_h;
+  const int num_tiles = spatial * g.tiles_co;
+
+  if (threadIdx.x == 0) {
+    failed_s = 0;
+    for (int s = 0; s < SA; ++s) {
+      mbar_init(smem_u32(&full_a[s]), 1);
+      mbar_init(smem_u32(&empty_a[s]), 1);
+    }
+    if (resident) {
+      mbar_init(smem_u32(&full_b[0]), 1);
+    } else {
+      for (int s = 0; s < SB; ++s) {
+        mbar_init(smem_u32(&full_b[s]), 1);
+        mbar_init(smem_u32(&empty_b[s]), 1);
+      }
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&acc_full[a]), 1);
+      mbar_init(smem_u32(&acc_empty[a]), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(Cfg::kCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+
+  auto tile_coords = [&](int tile, int& co0, int& n, int& h0) {
+    const int sp = tile / g.tiles_co;
+    co0 = (tile % g.tiles_co) * BN_;
+    h0 = (sp % g.tiles_h) * g.bh;
+    n = sp / g.tiles_h;
+  };
+  // one filter tile: tap wt, 64-channel slice ci0, output channels co0 ...
+  auto load_filter = [&](uint32_t dst, uint32_t bar, int wtap, int ci0, int co0) {
+    if (BMODE == 0) {
+      tma_load_2d(dst, &map_w, bar, wtap * g.Cin + ci0, co0);
+    } else {
+#pragma unroll
+      for (int j = 0; j < BN_ / 64; ++j) tma_load_2d(dst + uint32_t(j) * 8192u, &map_w, bar, wtap * g.Cout + co0 + j * 64, ci0);
+    }
+  };
+
+  int armed_a = 0, armed_b = 0;
+  if (warp == 0) {
+    // activation producer: one patch per 64-channel slice
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int co0, n, h0;
+        tile_coords(tile, co0, n, h0);
+        for (int cb = 0; cb < cblocks; ++cb, ++it) {
+          const int s = it % SA;
+          if (!mbar_wait(smem_u32(&empty_a[s]), ((it / SA) & 1) ^ 1, failed)) { ok = false; break; }
+          const uint32_t full = smem_u32(&full_a[s]);
+          mbar_expect_tx(full, g.patch_bytes);
+          tma_load_4d(smem_u32(stage_a + size_t(s) * g.slot_bytes_a), &map_x, full, cb * BK, -1, h0 - 1, n);
+          armed_a = it + 1;
+        }
+      }
+    }
+  } else if (warp == 6) {
+    // filter producer
+    if (lane == 0) {
+      if (resident) {
+        int co0, n, h0;
+        tile_coords(blockIdx.x, co0, n, h0);
+        const uint32_t full = smem_u32(&full_b[0]);
+        mbar_expect_tx(full, uint32_t(SB) * Cfg::kBytesB);
+#pragma unroll
+        for (int t = 0; t < 9; ++t)
+          for (int cb = 0; cb < cblocks; ++cb)
+            load_filter(smem_u32(stage_b + size_t(t * cblocks + cb) * Cfg::kBytesB), full, g.wt[t], cb * BK, co0);
+        armed_b = 1;
+      } else {
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+          int co0, n, h0;
+          tile_coords(tile, co0, n, h0);
+          for (int cb = 0; cb < cblocks && ok; ++cb) {
+#pragma unroll
+            for (int t = 0; t < 9; ++t, ++it) {
+              const int s = it % SB;
+              if (!mbar_wait(smem_u32(&empty_b[s]), ((it / SB) & 1) ^ 1, failed)) { ok = false; break; }
+              const uint32_t full = smem_u32(&full_b[s]);
+              mbar_expect_tx(full, Cfg::kBytesB);
+              load_filter(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), full, g.wt[t], cb * BK, co0);
+              armed_b = it + 1;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int ita = 0, itb = 0, local = 0;
+      bool ok = true;
+      if (resident) ok = mbar_wait(smem_u32(&full_b[0]), 0, failed);
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        if (!mbar_wait(smem_u32(&acc_empty[acc]), ((local >> 1) & 1) ^ 1, failed)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + uint32_t(acc * BN_);
+        for (int cb = 0; cb < cblocks && ok; ++cb, ++ita) {
+          const int sa = ita % SA;
+          if (!mbar_wait(smem_u32(&full_a[sa]), (ita / SA) & 1, failed)) { ok = false; break; }
+          const uint32_t a_base = smem_u32(stage_a + size_t(sa) * g.slot_bytes_a);
+          // Nine taps, unrolled: the tap tables are then read at constant indices (kernel parameters) and the
+          // loop between two MMAs is a handful of integer instructions.  With a rolled loop the tables live in
+          // local memory and their loads leave the tensor core idle between taps.
+#pragma unroll
+          for (int t = 0; t < 9; ++t) {
+            uint32_t b_addr;
+            int sb = 0;
+            if (resident) {
+              b_addr = smem_u32(stage_b + size_t(t * cblocks + cb) * Cfg::kBytesB);
+            } else {
+              sb = itb % SB;
+              if (!mbar_wait(smem_u32(&full_b[sb]), (itb / SB) & 1, failed)) { ok = false; break; }
+              ++itb;
+              b_addr = smem_u32(stage_b + size_t(sb) * Cfg::kBytesB);
+            }
+            // the tap's view of the patch: same rows, start moved by (dh + 1) * Wp + (dw + 1) rows of 128 bytes
+            const uint32_t a_addr = a_base + uint32_t((g.dh[t] + 1) * g.Wp + (g.dw[t] + 1)) * 128u;
+            const uint64_t adesc = make_desc(a_addr);
+            const uint64_t bdesc = BMODE == 0 ? make_desc(b_addr) : make_desc_mn(b_addr, 8192, 1024);
+            constexpr uint32_t idesc = Cfg::kIdesc | (BMODE != 0 ? (1u << 16) : 0u);
+            constexpr uint64_t b_step = BMODE == 0 ? 2 : (16 * 128) >> 4;
+#pragma unroll
+            for (int k = 0; k < BK / kUmmaK; ++k)
+              umma_f16(tmem_d, adesc + uint64_t(2 * k), bdesc + b_step * uint64_t(k), idesc, (cb | t | k) != 0 ? 1u : 0u);
+            if (!resident) umma_commit(smem_u32(&empty_b[sb]));
+          }
+          if (ok) umma_commit(smem_u32(&empty_a[sa]));
+        }
+        if (ok) umma_commit(smem_u32(&acc_full[acc]));
+      }
+    }
+  } else if (warp >= 2 && warp <= 5) {
+    const int q = warp & 3;
+    const bool leader = (warp == 2 && lane == 0);
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      int co0, n, h0;
+      tile_coords(tile, co0, n, h0);
+      mbar_wait(smem_u32(&acc_full[acc]), (local >> 1) & 1, failed);
+      epilogue_bar();
+      if (leader) go_s = (*failed == 0);
+      epilogue_bar();
+      if (!*reinterpret_cast<volatile int*>(&go_s)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int m = q * 32 + lane;
+      const int hh = h0 + m / g.Wp, ww = m % g.Wp;
+      __nv_bfloat16* ypix = nullptr;
+      if (m < g.bh * g.Wp && ww < g.W && hh < g.H) ypix = y + ((size_t(n) * g.H + hh) * g.W + ww) * g.Cout;
+#pragma unroll 1
+      for (int c = 0; c < BN_ / 64; ++c) {
+        const int cbase = co0 + c * 64;
+        if (cbase >= g.Cout) break;
+        uint32_t rr[64];
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN_ + c * 64);
+        tmem_ld32(taddr, rr);
+        tmem_ld32(taddr + 32, rr + 32);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (ypix != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (cbase + j * 8 < g.Cout) {
+              uint4 pk;
+              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                h[i] = __floats2bfloat162_rn(__uint_as_float(rr[j * 8 + 2 * i]), __uint_as_float(rr[j * 8 + 2 * i + 1]));
+              *reinterpret_cast<uint4*>(ypix + cbase + j * 8) = pk;
+            }
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[acc])) : "memory");
+    }
+  }
+  if (*failed) {
+    if (warp == 0 && lane == 0) {
+      for (int it = armed_a > SA ? armed_a - SA : 0; it < armed_a; ++it) {
+        const unsigned long long t0 = now_ns();
+        while (!mbar_try(smem_u32(&full_a[it % SA]), (it / SA) & 1) && now_ns() - t0 < kWaitLimitNs / 8) {}
+      }
+    }
+    if (warp == 6 && lane == 0) {
+      const int nb = resident ? 1 : SB;
+      for (int it = armed_b > nb ? armed_b - nb : 0; it < armed_b; ++it) {
+        const unsigned long long t0 = now_ns();
+        while (!mbar_try(smem_u32(&full_b[it % nb]), (it / nb) & 1) && now_ns() - t0 < kWaitLimitNs / 8) {}
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kCols) : "memory");
+  }
+  if (threadIdx.x == 0 && failed_s && status != nullptr) atomicExch(status, 1u);
+}
+
+// ------------------------------------------------------------------------------------------------------ //
 // Filter gradient.
 // ------------------------------------------------------------------------------------------------------ //
 template <int BN_>
 struct WgradCfg {
-  // Shared memory is a pool of 13 boxes of up to 128 positions x 64 channels (16 KiB each), cut at launch into a
-  // ring of output-gradient slots (one or two boxes: 64 or 128 output channels) and a ring of input slots (one box
-  // per 64 input channels of the tile), as many patches deep as fit: what limits a split-K CTA is the latency of its
-  // loads, so every byte of shared memory should be in flight.
-  static constexpr int kPoolBoxes = 13;
-  static constexpr uint32_t kBoxBytes = 128 * 128;
-  static constexpr int kMaxBars = 64;
-  static constexpr size_t kSmem = 1024 + size_t(kPoolBoxes) * kBoxBytes + kMaxBars * 8;
-  // D fp32, A and B bf16, both MN-major (bits 15, 16), N = BN_, M = 128
-  static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) |
-                                     (uint32_t(BN_ >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+  // Shared memory is one pool cut at launch into ring stages of (output-gradient boxes + input boxes of the taps
+  // of a group), as many as fit: what limits a split-K CTA is the latency of its loads, so every byte should be in
+  // flight.  A box holds up to 128 positions x 64 channels.
+  static constexpr uint32_t kPoolBytes = 216 * 1024;
+  static constexpr int kMaxStages = 8;
+  static constexpr size_t kSmem = 1024 + size_t(kPoolBytes) + (2 * kMaxStages + 2) * 8;
 };
 
 struct WgradGeom {
@@ -346,8 +629,9 @@ struct WgradGeom {
   int tiles_co, tiles_ci, groups, tg, splits;
   int ldw;                   // elements between filter-gradient rows: w_taps * Cin
   unsigned int tmem_cols;    // power of two >= tg * BN_
-  int slots_a, slots_b;      // ring depths
-  int boxes_a, boxes_b;      // boxes per slot
+  int stages;                // ring depth
+  int boxes_a, boxes_b;      // boxes per stage: output gradient (1 or 2), input per tap (BN_/64 at most)
+  unsigned int box_stride;   // bytes between boxes
 };
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -360,23 +644,21 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
                   __nv_bfloat16* __restrict__ dwt, float* __restrict__ ws, unsigned int* __restrict__ counters,
                   unsigned int* __restrict__ status) {
   using Cfg = WgradCfg<BN_>;
-  const int SA = g.slots_a, SB = g.slots_b;
-  const uint32_t bytes_slot_a = uint32_t(g.boxes_a) * Cfg::kBoxBytes, bytes_slot_b = uint32_t(g.boxes_b) * Cfg::kBoxBytes;
+  const int S = g.stages;
+  const uint32_t box_stride = g.box_stride;                 // bytes between boxes: the box size rounded up to 1 KiB
+  const uint32_t stage_bytes = uint32_t(g.boxes_a + g.tg * g.boxes_b) * box_stride;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* stage_a = smem;
-  unsigned char* stage_b = smem + size_t(SA) * bytes_slot_a;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(Cfg::kPoolBoxes) * Cfg::kBoxBytes);
-  uint64_t* full_a = bars;
-  uint64_t* empty_a = bars + SA;
-  uint64_t* full_b = bars + 2 * SA;
-  uint64_t* empty_b = bars + 2 * SA + SB;
-  uint64_t* acc_full = bars + 2 * SA + 2 * SB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kPoolBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + S;
+  uint64_t* acc_full = bars + 2 * S;
   uint64_t* acc_empty = acc_full + 1;
   __shared__ uint32_t tmem_base_s;
   __shared__ int failed_s;
   __shared__ int go_s;
   __shared__ unsigned int ticket_s;
+  __shared__ int tap_dh_s[kConvMaxTaps], tap_dw_s[kConvMaxTaps], tap_wt_s[kConvMaxTaps];   // see conv_igemm_kernel
   volatile int* failed = &failed_s;
 
   const int warp = threadIdx.x >> 5;
@@ -389,14 +671,16 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
   const uint32_t box_bytes = uint32_t(positions) * 128u;
 
   if (threadIdx.x == 0) {
-    failed_s = 0;
-    for (int s = 0; s < SA; ++s) {
-      mbar_init(smem_u32(&full_a[s]), 1);
-      mbar_init(smem_u32(&empty_a[s]), 1);
+#pragma unroll
+    for (int i = 0; i < kConvMaxTaps; ++i) {
+      tap_dh_s[i] = g.dh[i];
+      tap_dw_s[i] = g.dw[i];
+      tap_wt_s[i] = g.wt[i];
     }
-    for (int s = 0; s < SB; ++s) {
-      mbar_init(smem_u32(&full_b[s]), 1);
-      mbar_init(smem_u32(&empty_b[s]), 1);
+    failed_s = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&full[s]), 1);
+      mbar_init(smem_u32(&empty[s]), 1);
     }
     mbar_init(smem_u32(acc_full), 1);       // one tcgen05.commit
     mbar_init(smem_u32(acc_empty), 4);      // one arrive per epilogue warp
@@ -433,45 +717,43 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
     n0 = (p / (g.tiles_w * g.tiles_h)) * g.bn;
   };
 
-  int armed_a = 0, armed_b = 0;
+  // One ring stage = one patch: the output-gradient boxes (64 channels each) followed by the input boxes of the
+  // group's taps, tap after tap, every tap taking boxes_b boxes.  The taps of a group therefore form ONE B operand
+  // of N = taps * BN_ columns (64-column groups box_stride apart), and a patch costs positions/16 MMAs in all
+  // instead of that many per tap: with 64 input channels a 128x64x16 MMA keeps the tensor core a third busy,
+  // a 128x192x16 one fully.
+  int armed = 0;
   if (warp == 0) {
     if (lane == 0) {
-      int ita = 0, itb = 0;
+      int it = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
         int co0, ci0, t0, t1, p0, p1, tile_id;
         decode(item, co0, ci0, t0, t1, p0, p1, tile_id);
-        const int boxes_a = min(2, (g.Cout - co0 + 63) / 64);
-        const int boxes_b = min(BN_ / 64, (g.Cin - ci0 + 63) / 64);
-        for (int p = p0; p < p1 && ok; ++p) {
+        const int boxes_a = min(g.boxes_a, (g.Cout - co0 + 63) / 64);
+        const int boxes_b = min(g.boxes_b, (g.Cin - ci0 + 63) / 64);
+        for (int p = p0; p < p1; ++p, ++it) {
           int n0, h0, w0;
           patch_coords(p, n0, h0, w0);
-          {
-            const int s = ita % SA;
-            if (!mbar_wait(smem_u32(&empty_a[s]), ((ita / SA) & 1) ^ 1, failed)) { ok = false; break; }
-            const uint32_t full = smem_u32(&full_a[s]);
-            mbar_expect_tx(full, uint32_t(boxes_a) * box_bytes);
-            for (int j = 0; j < boxes_a; ++j)
-              tma_load_4d(smem_u32(stage_a + size_t(s) * bytes_slot_a + size_t(j) * Cfg::kBoxBytes), &map_dy, full,
-                          co0 + j * 64, w0, h0, n0);
-            armed_a = ++ita;
-          }
-          for (int t = t0; t < t1; ++t) {
-            const int s = itb % SB;
-            if (!mbar_wait(smem_u32(&empty_b[s]), ((itb / SB) & 1) ^ 1, failed)) { ok = false; break; }
-            const uint32_t full = smem_u32(&full_b[s]);
-            mbar_expect_tx(full, uint32_t(boxes_b) * box_bytes);
+          const int s = it % S;
+          if (!mbar_wait(smem_u32(&empty[s]), ((it / S) & 1) ^ 1, failed)) { ok = false; break; }
+          const uint32_t bar = smem_u32(&full[s]);
+          unsigned char* stage = smem + size_t(s) * stage_bytes;
+          mbar_expect_tx(bar, uint32_t(boxes_a + (t1 - t0) * boxes_b) * box_bytes);
+          for (int j = 0; j < boxes_a; ++j)
+            tma_load_4d(smem_u32(stage + size_t(j) * box_stride), &map_dy, bar, co0 + j * 64, w0, h0, n0);
+          unsigned char* stage_b = stage + size_t(g.boxes_a) * box_stride;
+          for (int t = t0; t < t1; ++t)
             for (int j = 0; j < boxes_b; ++j)
-              tma_load_4d(smem_u32(stage_b + size_t(s) * bytes_slot_b + size_t(j) * Cfg::kBoxBytes), &map_x, full,
-                          ci0 + j * 64, w0 * g.in_stride + g.dw[t], h0 * g.in_stride + g.dh[t], n0);
-            armed_b = ++itb;
-          }
+              tma_load_4d(smem_u32(stage_b + size_t((t - t0) * g.boxes_b + j) * box_stride), &map_x, bar, ci0 + j * 64,
+                          w0 * g.in_stride + tap_dw_s[t], h0 * g.in_stride + tap_dh_s[t], n0);
+          armed = it + 1;
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      int ita = 0, itb = 0, local = 0;
+      int it = 0, local = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++local) {
         int co0, ci0, t0, t1, p0, p1, tile_id;
@@ -479,25 +761,20 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
         // the epilogue must have drained the accumulators of the previous item
         if (!mbar_wait(smem_u32(acc_empty), (local & 1) ^ 1, failed)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        for (int p = p0; p < p1 && ok; ++p) {
-          const int sa = ita % SA;
-          if (!mbar_wait(smem_u32(&full_a[sa]), (ita / SA) & 1, failed)) { ok = false; break; }
-          ++ita;
-          const uint64_t adesc = make_desc_mn(smem_u32(stage_a + size_t(sa) * bytes_slot_a), Cfg::kBoxBytes, 1024);
-          for (int t = t0; t < t1; ++t) {
-            const int sb = itb % SB;
-            if (!mbar_wait(smem_u32(&full_b[sb]), (itb / SB) & 1, failed)) { ok = false; break; }
-            ++itb;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t bdesc = make_desc_mn(smem_u32(stage_b + size_t(sb) * bytes_slot_b), Cfg::kBoxBytes, 1024);
-            const uint32_t tmem_d = tmem_base + uint32_t((t - t0) * BN_);
-            // one MMA step reduces over 16 positions = 16 rows of 128 bytes in both operands
-            for (int k = 0; k < ksteps; ++k)
-              umma_f16(tmem_d, adesc + uint64_t(k) * 128u, bdesc + uint64_t(k) * 128u, Cfg::kIdesc,
-                       (p != p0 || k != 0) ? 1u : 0u);
-            umma_commit(smem_u32(&empty_b[sb]));
-          }
-          if (ok) umma_commit(smem_u32(&empty_a[sa]));
+        // D fp32, A and B bf16, both MN-major (bits 15, 16), N = taps * BN_, M = 128
+        const uint32_t n_cols = uint32_t(t1 - t0) * BN_;
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((n_cols >> 3) << 17) |
+                               (uint32_t(BM >> 4) << 24);
+        for (int p = p0; p < p1; ++p, ++it) {
+          const int s = it % S;
+          if (!mbar_wait(smem_u32(&full[s]), (it / S) & 1, failed)) { ok = false; break; }
+          const uint32_t stage = smem_u32(smem + size_t(s) * stage_bytes);
+          const uint64_t adesc = make_desc_mn(stage, box_stride, 1024);
+          const uint64_t bdesc = make_desc_mn(stage + uint32_t(g.boxes_a) * box_stride, box_stride, 1024);
+          // one MMA step reduces over 16 positions = 16 rows of 128 bytes in both operands
+          for (int k = 0; k < ksteps; ++k)
+            umma_f16(tmem_base, adesc + uint64_t(k) * 128u, bdesc + uint64_t(k) * 128u, idesc, (p != p0 || k != 0) ? 1u : 0u);
+          umma_commit(smem_u32(&empty[s]));
         }
         if (ok) umma_commit(smem_u32(acc_full));
       }
@@ -518,7 +795,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
       const int co = co0 + q * 32 + lane;
       const bool row_ok = co < g.Cout;
       for (int t = t0; t < t1; ++t) {
-        const size_t row_off = size_t(co) * g.ldw + size_t(g.wt[t]) * g.Cin;
+        const size_t row_off = size_t(co) * g.ldw + size_t(tap_wt_s[t]) * g.Cin;
 #pragma unroll 1
         for (int c = 0; c < BN_ / 32; ++c) {
           const int col = ci0 + c * 32;
@@ -577,7 +854,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
               const int row = co0 + q * 32 + i / (cchunks * ntaps);
               const int col = cc * 128 + lane * 4;
               const bool ok = i < total && row < g.Cout && col < width;
-              off[u] = ok ? size_t(row) * g.ldw + size_t(g.wt[t]) * g.Cin + ci0 + col : size_t(-1);
+              off[u] = ok ? size_t(row) * g.ldw + size_t(tap_wt_s[t]) * g.Cin + ci0 + col : size_t(-1);
               if (ok) v[u] = __ldcg(reinterpret_cast<const float4*>(ws + off[u]));
             }
 #pragma unroll
@@ -598,13 +875,9 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
     }
   }
   if (warp == 0 && lane == 0 && *failed) {
-    for (int it = armed_a > SA ? armed_a - SA : 0; it < armed_a; ++it) {
+    for (int it = armed > S ? armed - S : 0; it < armed; ++it) {
       const unsigned long long t0 = now_ns();
-      while (!mbar_try(smem_u32(&full_a[it % SA]), (it / SA) & 1) && now_ns() - t0 < kWaitLimitNs) {}
-    }
-    for (int it = armed_b > SB ? armed_b - SB : 0; it < armed_b; ++it) {
-      const unsigned long long t0 = now_ns();
-      while (!mbar_try(smem_u32(&full_b[it % SB]), (it / SB) & 1) && now_ns() - t0 < kWaitLimitNs) {}
+      while (!mbar_try(smem_u32(&full[it % S]), (it / S) & 1) && now_ns() - t0 < kWaitLimitNs) {}
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -683,6 +956,56 @@ cudaError_t LaunchWgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const Wgr
   return cudaGetLastError();
 }
 
+template <int BN_, int BMODE>
+cudaError_t LaunchHalo(const CUtensorMap& mx, const CUtensorMap& mw, HaloGeom g, void* y, unsigned int* status,
+                       cudaStream_t stream) {
+  using Cfg = HaloCfg<BN_>;
+  const int cblocks = g.Cin / BK;
+  // filter: resident when all taps of the (single) output-channel tile fit beside a useful activation ring
+  const size_t resident_bytes = size_t(g.T) * cblocks * Cfg::kBytesB;
+  const bool resident = g.tiles_co == 1 && resident_bytes <= 80 * 1024;
+  g.slots_b = resident ? 0 : (BN_ == 64 ? 8 : (BN_ == 128 ? 4 : 3));
+  const size_t bytes_b = resident ? resident_bytes : size_t(g.slots_b) * Cfg::kBytesB;
+  const size_t fixed = 1024 + bytes_b + Cfg::kMaxBars * 8;
+  if (fixed + 2 * size_t(g.slot_bytes_a) > Cfg::kSmemLimit) return cudaErrorInvalidValue;
+  int sa = int((Cfg::kSmemLimit - fixed) / g.slot_bytes_a);
+  if (sa > 6) sa = 6;
+  g.slots_a = sa;
+  const size_t smem = fixed + size_t(sa) * g.slot_bytes_a;
+  static size_t attr_bytes = 0;
+  if (smem > attr_bytes) {
+    cudaError_t e = cudaFuncSetAttribute(conv_halo_kernel<BN_, BMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(Cfg::kSmemLimit));
+    if (e != cudaSuccess) return e;
+    attr_bytes = Cfg::kSmemLimit;
+  }
+  const int tiles = g.N * g.tiles_h * g.tiles_co;
+  const int sms = SmCount();
+  conv_halo_kernel<BN_, BMODE><<<tiles < sms ? tiles : sms, kIgemmThreads, smem, stream>>>(
+      mx, mw, g, static_cast<__nv_bfloat16*>(y), status);
+  CountKernelLaunch();
+  return cudaGetLastError();
+}
+
+// Whether the problem is a dense 3x3-neighbourhood convolution the halo kernel covers well: unit strides, taps within
+// one pixel, the whole padded row inside one box, and tiles that are at least three quarters real positions.
+bool HaloApplies(const ConvProblem& p, int* bh_out) {
+  if (p.in_stride != 1 || p.out_stride != 1 || p.out_ph != 0 || p.out_pw != 0) return false;
+  if (p.Hy != p.Ho || p.Wy != p.Wo || p.x.h != p.Ho || p.x.w != p.Wo || p.x.pix_pitch != p.x.c) return false;
+  if (p.taps.T != 9) return false;            // the kernel's tap loop is unrolled for a 3x3 filter
+  for (int t = 0; t < p.taps.T; ++t)
+    if (p.taps.dh[t] < -1 || p.taps.dh[t] > 1 || p.taps.dw[t] < -1 || p.taps.dw[t] > 1) return false;
+  const int Wp = p.Wo + 2;
+  if (Wp > 128) return false;
+  int bh = 128 / Wp;
+  if (bh > p.Ho) bh = p.Ho;
+  if (bh < 1 || bh * p.Wo < 96) return false;
+  static const bool off = [] { const char* e = std::getenv("BLUEFOG_B200_CONV_HALO"); return e != nullptr && e[0] == '0'; }();
+  if (off) return false;
+  *bh_out = bh;
+  return true;
+}
+
 bool TapsOk(const ConvTaps& t, int w_taps) {
   if (t.T < 1 || t.T > kConvMaxTaps) return false;
   for (int i = 0; i < t.T; ++i)
@@ -759,6 +1082,36 @@ cudaError_t LaunchConvIgemm(const ConvProblem& p, unsigned int* status, cudaStre
   if (p.Cout <= 64) bn_tile = 64;
   else if (p.Cout <= 128 || spatial * ((p.Cout + 255) / 256) < (SmCount() * 3) / 4) bn_tile = 128;
   g.tiles_co = (p.Cout + bn_tile - 1) / bn_tile;
+  int halo_bh = 0;
+  if (HaloApplies(p, &halo_bh)) {
+    HaloGeom hg;
+    hg.N = g.N; hg.H = p.Ho; hg.W = p.Wo; hg.Cin = g.Cin; hg.Cout = p.Cout;
+    hg.Wp = p.Wo + 2; hg.bh = halo_bh;
+    hg.tiles_h = (p.Ho + halo_bh - 1) / halo_bh;
+    hg.T = g.T;
+    for (int i = 0; i < kConvMaxTaps; ++i) { hg.dh[i] = g.dh[i]; hg.dw[i] = g.dw[i]; hg.wt[i] = g.wt[i]; }
+    const int spatial_h = g.N * hg.tiles_h;
+    int bn_h = 256;
+    if (p.Cout <= 64) bn_h = 64;
+    else if (p.Cout <= 128 || spatial_h * ((p.Cout + 255) / 256) < (SmCount() * 3) / 4) bn_h = 128;
+    hg.tiles_co = (p.Cout + bn_h - 1) / bn_h;
+    const int patch_rows = (halo_bh + 2) * hg.Wp;
+    int slot_rows = 2 * hg.Wp + 2 + 128;
+    if (slot_rows < patch_rows) slot_rows = patch_rows;
+    hg.slot_bytes_a = (unsigned(slot_rows) * 128u + 1023u) & ~1023u;
+    hg.patch_bytes = unsigned(patch_rows) * 128u;
+    hg.slots_a = hg.slots_b = 0;
+    CUtensorMap hx, hw;
+    const bool hw_ok = p.filter_mode == 0 ? MakeMap2d(&hw, p.w, p.Cout, p.w_taps * g.Cin, bn_h)
+                                          : MakeMap2d(&hw, p.w, g.Cin, p.w_taps * p.Cout, 64);
+    if (MakeViewMap(&hx, p.x, hg.Wp, halo_bh + 2, 1, 1) && hw_ok) {
+      cudaError_t e;
+      if (bn_h == 64) e = p.filter_mode == 0 ? LaunchHalo<64, 0>(hx, hw, hg, p.y, status, stream) : LaunchHalo<64, 1>(hx, hw, hg, p.y, status, stream);
+      else if (bn_h == 128) e = p.filter_mode == 0 ? LaunchHalo<128, 0>(hx, hw, hg, p.y, status, stream) : LaunchHalo<128, 1>(hx, hw, hg, p.y, status, stream);
+      else e = p.filter_mode == 0 ? LaunchHalo<256, 0>(hx, hw, hg, p.y, status, stream) : LaunchHalo<256, 1>(hx, hw, hg, p.y, status, stream);
+      return e;
+    }
+  }
   const bool direct = !(p.out_stride == 1 && p.out_ph == 0 && p.out_pw == 0 && p.Hy == p.Ho && p.Wy == p.Wo);
   CUtensorMap mx, mw, my;
   // filter map: K-major [Cout rows, w_taps*Cin], or (MN-major mode) the forward filter [Cin rows, w_taps*Cout] in boxes of 64 x 64
@@ -783,46 +1136,44 @@ cudaError_t LaunchConvIgemm(const ConvProblem& p, unsigned int* status, cudaStre
 
 namespace {
 
-// Cuts the pool of 13 boxes into the two rings: as many whole patches (one output-gradient slot + tg input slots)
-// as fit, at least two output-gradient slots, the rest to the input ring.
-void WgradRings(int cout, int cin, int bn, int tg, int* boxes_a, int* boxes_b, int* slots_a, int* slots_b) {
+// Ring geometry of a filter gradient: boxes per stage and how many stages fit into the pool.
+void WgradRings(int cout, int cin, int bn, int tg, int positions, int* boxes_a, int* boxes_b, unsigned* box_stride,
+                int* stages) {
   const int ba = cout > 64 ? 2 : 1;
   const int bb = (bn < cin ? bn : cin) / 64;
-  int depth = 13 / (ba + tg * bb);
-  if (depth > 6) depth = 6;
-  int sa, sb;
-  if (depth >= 2) {
-    sa = depth;
-    sb = (13 - sa * ba) / bb;
-  } else {
-    sa = 2;
-    sb = (13 - 2 * ba) / bb;
-  }
-  if (sb > 16) sb = 16;
+  const unsigned stride = (unsigned(positions) * 128u + 1023u) & ~1023u;
+  int s = int(WgradCfg<64>::kPoolBytes / (size_t(ba + tg * bb) * stride));
+  if (s > WgradCfg<64>::kMaxStages) s = WgradCfg<64>::kMaxStages;
   *boxes_a = ba;
   *boxes_b = bb;
-  *slots_a = sa;
-  *slots_b = sb;
+  *box_stride = stride;
+  *stages = s;
 }
 
 // Tile shape and split of a filter gradient: BN (input channels per tile), taps per group, shares of the patches.
-// Every candidate is priced with a small model of one CTA's time line and the cheapest wins:
-//   main loop   = patches of the CTA x max(bytes it loads per patch / what one SM draws from L2, MMA time)
+// The taps of a group are columns of one MMA (N = taps * BN <= 256), so more taps per group cost no extra MMA
+// instructions and share the load of the output gradient; they widen the tile that is reduced at the end.  Every
+// candidate is priced with a small model of one CTA's time line and the cheapest wins:
+//   main loop   = patches of the CTA x max(bytes per patch / what one SM draws from L2, MMA time, load latency / depth)
 //   reduction   = (more than one share per tile) vector reductions of the partial tile, a fence and a ticket, and the
 //                 last CTA's conversion pass in batches of one L2 round trip each.
-// Few taps per CTA mean more tiles and fewer shares (cheap reduction, but the output gradient is loaded once per
-// tap); many taps per CTA share that load but reduce a wider tile.  BLUEFOG_B200_WGRAD_PLAN=bn,tg,splits overrides.
+// BLUEFOG_B200_WGRAD_PLAN=bn,tg,splits overrides.
 void WgradPlan(const WgradProblem& p, int patches, int positions, int* bn_tile, int* tg, int* splits) {
   const int cin = p.x.c, cout = p.dy.c, T = p.taps.T;
   const int sms = SmCount();
   if (const char* env = std::getenv("BLUEFOG_B200_WGRAD_PLAN")) {
     int b = 0, t = 0, s = 0;
     if (std::sscanf(env, "%d,%d,%d", &b, &t, &s) == 3 && (b == 64 || b == 128 || b == 256) && t >= 1 && t <= T &&
-        t * b <= 512 && s >= 1) {
-      *bn_tile = b;
-      *tg = t;
-      *splits = s > patches ? patches : s;
-      return;
+        t * b <= 256 && s >= 1) {
+      int ba, bb, st;
+      unsigned stride;
+      WgradRings(cout, cin, b, t, positions, &ba, &bb, &stride, &st);
+      if (st >= 2) {
+        *bn_tile = b;
+        *tg = t;
+        *splits = s > patches ? patches : s;
+        return;
+      }
     }
   }
   const double kSmBytesPerNs = 150.0;        // what one SM's TMA loads sustain out of L2 (GB/s = bytes/ns)
@@ -834,7 +1185,11 @@ void WgradPlan(const WgradProblem& p, int patches, int positions, int* bn_tile, 
   double best = -1.0;
   for (int b : {64, 128, 256}) {
     if (b > 64 && b > cin) continue;
-    for (int t = 1; t <= T && t * b <= 512; ++t) {
+    for (int t = 1; t <= T && t * b <= 256; ++t) {
+      int ba, bb, stages;
+      unsigned stride;
+      WgradRings(cout, cin, b, t, positions, &ba, &bb, &stride, &stages);
+      if (stages < 2) continue;
       const int groups = (T + t - 1) / t;
       const int tiles_co = (cout + BM - 1) / BM, tiles_ci = (cin + b - 1) / b;
       const int tiles = tiles_co * tiles_ci * groups;
@@ -843,15 +1198,12 @@ void WgradPlan(const WgradProblem& p, int patches, int positions, int* bn_tile, 
       if (s > patches) s = patches;
       const double items_per_cta = double((tiles * s + sms - 1) / sms);
       const double cta_patches = double((patches + s - 1) / s) * items_per_cta;
-      const int boxes_a = cout >= BM ? 2 : (cout + 63) / 64;
-      const int boxes_b = (b < cin ? b : cin) / 64;
-      const double bytes = (boxes_a + double(t) * boxes_b) * box;
-      const double mma_ns = double(t) * ksteps * (b / 2.0) / kClockGhz;
+      const double bytes = (ba + double(t) * bb) * box;
+      double mma_clk = double(t) * b / 2.0;                      // one 128 x (t*b) x 16 MMA
+      if (mma_clk < 60.0) mma_clk = 60.0;                        // floor of a small MMA with MN-major operands
+      const double mma_ns = ksteps * mma_clk / kClockGhz;
       const double load_ns = bytes / kSmBytesPerNs;
-      int ba, bb, sa, sb;
-      WgradRings(cout, cin, b, t, &ba, &bb, &sa, &sb);
-      const double depth = double(sa < sb / t ? sa : (sb / t > 0 ? sb / t : 1));     // patches in flight
-      const double latency_ns = (kLoadLatencyNs + mma_ns) / depth;
+      const double latency_ns = (kLoadLatencyNs + mma_ns) / stages;
       double per_patch = load_ns > mma_ns ? load_ns : mma_ns;
       if (latency_ns > per_patch) per_patch = latency_ns;
       double ns = 3000.0 + cta_patches * per_patch + kRoundTripNs;
@@ -908,7 +1260,8 @@ cudaError_t LaunchConvWgrad(const WgradProblem& p, unsigned int* status, cudaStr
   unsigned int cols = 32;
   while (cols < unsigned(g.tg * bn_tile)) cols <<= 1;
   g.tmem_cols = cols;
-  WgradRings(g.Cout, g.Cin, bn_tile, g.tg, &g.boxes_a, &g.boxes_b, &g.slots_a, &g.slots_b);
+  WgradRings(g.Cout, g.Cin, bn_tile, g.tg, g.bw * g.bh * g.bn, &g.boxes_a, &g.boxes_b, &g.box_stride, &g.stages);
+  if (g.stages < 2) return cudaErrorInvalidValue;
   if (g.splits > 1) {
     const long long need = (long long)g.Cout * g.ldw;
     if (p.workspace == nullptr || p.counters == nullptr || p.workspace_floats < need ||

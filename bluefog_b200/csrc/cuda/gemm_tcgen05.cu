@@ -165,7 +165,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int s = kb % kStages;
         const uint32_t parity = (kb / kStages) & 1;
         if (!mbar_wait(smem_u32(&bars[s]), parity, failed)) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // (no tcgen05 fence here: the data arrived through the async proxy and its mbarrier; a fence after every
+        // stage wait makes the issuing thread wait out the MMAs in flight: 150 instead of 48 cycles per 128x64x16 MMA)
         const uint64_t adesc = make_desc(smem_u32(stage_a + size_t(s) * kStageBytesA));
         const uint64_t bdesc = make_desc(smem_u32(stage_b + size_t(s) * kStageBytesB));
 #pragma unroll
@@ -368,7 +369,8 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % S;
           if (!mbar_wait(smem_u32(&bars[s]), (it / S) & 1, failed)) { ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          // (no tcgen05 fence here: the data arrived through the async proxy and its mbarrier; a fence after every
+          // stage wait makes the issuing thread wait out the MMAs in flight: 150 instead of 48 cycles per 128x64x16 MMA)
           const uint32_t a_addr = smem_u32(stage_a + size_t(s) * Cfg::kBytesA);
           const uint64_t adesc = AMODE == 0 ? make_desc(a_addr) : make_desc_mn(a_addr, 8192, 1024);
           const uint32_t b_addr = smem_u32(stage_b + size_t(s) * Cfg::kBytesB);

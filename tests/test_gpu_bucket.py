@@ -161,3 +161,146 @@ def test_grad_reduce_equals_mean_gradient_sgd():
     for r in range(W):
         assert buckets[r].status()[0] == 0
         assert (master[r] - ref[r]).abs().max().item() < 1e-5
+
+
+MODE_ANNOUNCE = 5
+
+
+def test_awc_with_destination_weights_announced_per_step():
+    """Adapt-with-combine where every sender scales what each destination pulls: the weights of a step are
+    announced for the version published one step earlier.  (Ranks share one GPU here and run one after the other,
+    so the announcement is a launch of its own; on real ranks the step kernel makes it when it starts.)"""
+    C = _C()
+    W, n, lr = 4, 3001, 0.1
+    buckets, master = _make(C, W, n, "float32")
+    ref = [m.clone() for m in master]
+    g = torch.Generator().manual_seed(21)
+    for t in range(4):
+        grads = [torch.randn(n, generator=g).cuda() for _ in range(W)]
+        # rank s sends to s+1 with weight 0.5 + 0.1*s + 0.05*t, and to s+2 with weight 2
+        dstw = [[1.0] * W for _ in range(W)]
+        for s in range(W):
+            dstw[s][(s + 1) % W] = 0.5 + 0.1 * s + 0.05 * t
+            dstw[s][(s + 2) % W] = 2.0
+        old = [p.clone() for p in ref]
+        for r in range(W):
+            comb = 0.4 * old[r] + 0.3 * dstw[(r - 1) % W][r] * old[(r - 1) % W] + 0.3 * dstw[(r - 2) % W][r] * old[(r - 2) % W]
+            ref[r] = comb - lr * grads[r]
+        for r in range(W):
+            a = C.BucketStepArgs()
+            a.mode, a.dst_weights = MODE_ANNOUNCE, dstw[r]
+            buckets[r].step(a)
+        for r in range(W):
+            a = C.BucketStepArgs()
+            a.mode, a.opt, a.master, a.grad, a.lr = MODE_AWC, 1, master[r], grads[r], lr
+            a.self_weight, a.src_ranks, a.src_weights, a.n_readers = 0.4, [(r - 1) % W, (r - 2) % W], [0.3, 0.3], 2
+            a.dst_weights, a.read_dst_weights = dstw[r], True
+            buckets[r].step(a)
+    torch.cuda.synchronize()
+    for r in range(W):
+        assert buckets[r].status()[0] == 0, buckets[r].status()
+        assert (master[r] - ref[r]).abs().max().item() < 1e-4
+
+
+def test_atc_with_destination_weights_stored_beside_the_version():
+    C = _C()
+    W, n, lr = 3, 2500, 0.05
+    buckets, master = _make(C, W, n, "float32")
+    ref = [m.clone() for m in master]
+    g = torch.Generator().manual_seed(22)
+    for t in range(3):
+        grads = [torch.randn(n, generator=g).cuda() for _ in range(W)]
+        dstw = [[1.0] * W for _ in range(W)]
+        for s in range(W):
+            dstw[s][(s + 1) % W] = 0.25 * (s + 1) + t
+        adapted = [ref[r] - lr * grads[r] for r in range(W)]
+        ref = [0.5 * adapted[r] + 0.5 * dstw[(r - 1) % W][r] * adapted[(r - 1) % W] for r in range(W)]
+        for r in range(W):
+            a = C.BucketStepArgs()
+            a.mode, a.opt, a.master, a.grad, a.lr = MODE_ADAPT_PUBLISH, 1, master[r], grads[r], lr
+            a.dst_weights = dstw[r]
+            buckets[r].step(a)
+        for r in range(W):
+            c = C.BucketStepArgs()
+            c.mode, c.master = MODE_COMBINE_ONLY, master[r]
+            c.self_weight, c.src_ranks, c.src_weights, c.n_readers = 0.5, [(r - 1) % W], [0.5], 1
+            c.read_dst_weights = True
+            buckets[r].step(c)
+    torch.cuda.synchronize()
+    for r in range(W):
+        assert buckets[r].status()[0] == 0
+        assert (master[r] - ref[r]).abs().max().item() < 1e-4
+
+
+def test_hierarchical_average_as_one_weighted_pull():
+    """Four ranks on two machines of two: mean inside each machine, then the machines average each other."""
+    C = _C()
+    W, n = 4, 1030
+    buckets, master = _make(C, W, n, "float32")
+    start = [m.clone() for m in master]
+    machine_mean = [(start[0] + start[1]) / 2, (start[2] + start[3]) / 2]
+    expect = [0.5 * machine_mean[r // 2] + 0.5 * machine_mean[1 - r // 2] for r in range(W)]
+    for r in range(W):
+        a = C.BucketStepArgs()
+        a.mode, a.master = MODE_AWC, master[r]
+        mine, other = r // 2, 1 - r // 2
+        a.self_weight = 0.5 / 2
+        a.src_ranks = [s for s in range(2 * mine, 2 * mine + 2) if s != r] + list(range(2 * other, 2 * other + 2))
+        a.src_weights = [0.25] * 3
+        a.n_readers = 3
+        buckets[r].step(a)
+    torch.cuda.synchronize()
+    for r in range(W):
+        assert buckets[r].status()[0] == 0
+        assert (master[r] - expect[r]).abs().max().item() < 1e-5
+
+
+def test_parameters_without_a_gradient_are_left_alone():
+    """Per-parameter gradient table with a missing entry: that parameter gets the combined value and no optimizer
+    update (no weight decay, no momentum decay), like torch.optim, which skips parameters whose grad is None."""
+    C = _C()
+    n_a, n_b = 1024, 2048
+    n = n_a + n_b
+    buckets, master = _make(C, 1, n, "float32")
+    before = master[0].clone()
+    mom = torch.full((n,), 0.5, device="cuda")
+    ga = torch.randn(n_a, device="cuda")
+    table = torch.tensor([ga.data_ptr(), 0], dtype=torch.int64, device="cuda")
+    a = C.BucketStepArgs()
+    a.mode, a.opt, a.master, a.state1 = MODE_AWC, 1, master[0], mom
+    a.lr, a.momentum, a.weight_decay, a.first_step = 0.1, 0.9, 0.1, False
+    a.grad_ptrs = table
+    a.seg_start = torch.tensor([0, n_a], dtype=torch.int64, device="cuda")
+    a.seg_numel = torch.tensor([n_a, n_b], dtype=torch.int64, device="cuda")
+    a.self_weight = 1.0
+    buckets[0].step(a)
+    torch.cuda.synchronize()
+    d = ga + 0.1 * before[:n_a]
+    buf = 0.9 * 0.5 + d
+    assert torch.allclose(master[0][:n_a], before[:n_a] - 0.1 * buf, atol=1e-5)
+    assert torch.equal(master[0][n_a:], before[n_a:])
+    assert torch.equal(mom[n_a:], torch.full((n_b,), 0.5, device="cuda"))
+
+
+def test_a_version_whose_owner_gave_up_is_marked_and_not_combined():
+    """The owner's wait for its readers runs out (50 ms limit, nobody reads): it announces the version anyway so
+    that nobody hangs, marked as failed; a reader of that version reports the failure and leaves its output alone."""
+    C = _C()
+    dev = torch.device("cuda", 0)
+    world = C.LocalWorld(2, 1 << 16, 0)
+    world.set_timeout_ms(50.0)
+    x = torch.ones(256, device=dev)
+    for _ in range(2):
+        world.publish(0, [x], None, 1)           # versions 0 and 1: one reader each, who never comes
+        world.publish(1, [x], None, 0)
+    r0 = world.publish(0, [x * 3], None, 1)      # version 2 must wait for the reader of version 0: times out
+    r1 = world.publish(1, [x], None, 0)
+    torch.cuda.synchronize()
+    assert world.status(0)[0] == 2               # kCommTimeoutDone on the owner
+    out = torch.full((256,), -7.0, device=dev)
+    world.combine(1, r1, [out], 0.5, [0], [0.5], False, 1.0)
+    torch.cuda.synchronize()
+    err, peer, _, _ = world.status(1)
+    assert err == 4 and peer == 0                # kCommPeerFailed
+    assert torch.equal(out, torch.full((256,), -7.0, device=dev))
+    assert torch.ones(4, device=dev).sum().item() == 4.0

@@ -118,6 +118,51 @@ def make_loss(args):
     return cross_entropy
 
 
+def timed_end_to_end(step, host_x, host_y, like_x, like_y, steps, barrier):
+    """Device time of ``steps`` steps that each take their inputs from pinned host memory (copied on a copy stream,
+    one step ahead, into one of two device buffers) and deliver their loss to the host (read one step later, so that
+    launching step i+1 does not wait for step i to drain).  Returns (milliseconds, last loss)."""
+    copy_stream = torch.cuda.Stream()
+    bufs = [(torch.empty_like(like_x), torch.empty_like(like_y)) for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+
+    def prefetch(i):
+        b = i % 2
+        with torch.cuda.stream(copy_stream):
+            if i >= 2:
+                copy_stream.wait_event(consumed[b])      # step i-2 has finished reading this buffer
+            bufs[b][0].copy_(host_x, non_blocking=True)
+            bufs[b][1].copy_(host_y, non_blocking=True)
+            ready[b].record(copy_stream)
+
+    loss_host = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
+    loss_ready = [torch.cuda.Event() for _ in range(2)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    prefetch(0)
+    loss_val = float("nan")
+    for i in range(steps):
+        if i + 1 < steps:
+            prefetch(i + 1)
+        b = i % 2
+        torch.cuda.current_stream().wait_event(ready[b])
+        loss_t = step(bufs[b][0], bufs[b][1])
+        consumed[b].record(torch.cuda.current_stream())
+        loss_host[b].copy_(loss_t.detach().float(), non_blocking=True)
+        loss_ready[b].record(torch.cuda.current_stream())
+        if i > 0:
+            loss_ready[1 - b].synchronize()
+            loss_val = float(loss_host[1 - b])
+    loss_ready[(steps - 1) % 2].synchronize()
+    loss_val = float(loss_host[(steps - 1) % 2])
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1), loss_val
+
+
 def one_peer_schedule(bf, size, rank):
     if size == 1:
         while True:
@@ -203,47 +248,8 @@ def run_ours(args):
     if graphed is not None:
         launches += args.steps * graphed.native_launches_per_replay
     ms_dev = max_over_ranks(e0.elapsed_time(e1))
-    # end to end: every step copies its inputs from pinned host memory (on a copy stream, one step
-    # ahead, into one of two device buffers) and reads the loss back to the host
-    copy_stream = torch.cuda.Stream()
-    bufs = [(torch.empty_like(dev_x), torch.empty_like(dev_y)) for _ in range(2)]
-    ready = [torch.cuda.Event() for _ in range(2)]
-    consumed = [torch.cuda.Event() for _ in range(2)]
-
-    def prefetch(i):
-        b = i % 2
-        with torch.cuda.stream(copy_stream):
-            if i >= 2:
-                copy_stream.wait_event(consumed[b])      # step i-2 has finished reading this buffer
-            bufs[b][0].copy_(host_x, non_blocking=True)
-            bufs[b][1].copy_(host_y, non_blocking=True)
-            ready[b].record(copy_stream)
-
-    loss_host = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
-    loss_ready = [torch.cuda.Event() for _ in range(2)]
-    bf.barrier()
-    torch.cuda.synchronize()
-    e0.record()
-    prefetch(0)
-    for i in range(args.steps):
-        if i + 1 < args.steps:
-            prefetch(i + 1)
-        b = i % 2
-        torch.cuda.current_stream().wait_event(ready[b])
-        loss_t = step(bufs[b][0], bufs[b][1])
-        consumed[b].record(torch.cuda.current_stream())
-        # device -> host read of the loss of EVERY step, into pinned memory; the host looks at it one step
-        # later, so that launching step i+1 does not wait for step i to drain
-        loss_host[b].copy_(loss_t.detach(), non_blocking=True)
-        loss_ready[b].record(torch.cuda.current_stream())
-        if i > 0:
-            loss_ready[1 - b].synchronize()
-            loss_val = float(loss_host[1 - b])
-    loss_ready[(args.steps - 1) % 2].synchronize()
-    loss_val = float(loss_host[(args.steps - 1) % 2])
-    e1.record()
-    torch.cuda.synchronize()
-    ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+    ms_e2e, loss_val = timed_end_to_end(step, host_x, host_y, dev_x, dev_y, args.steps, bf.barrier)
+    ms_e2e = max_over_ranks(ms_e2e)
     clocks = sampler.stop() if rank == 0 else None
     opt.check()
     ok = bool(torch.isfinite(torch.tensor(loss_val)))

@@ -1,5 +1,5 @@
-"""neighbor_allreduce / win_put bandwidth sweep (role of the reference's scripts/single_ops_test.py,
-extended to the sweep of message sizes and topologies).
+"""Bandwidth sweep of neighbor_allreduce, the window operations and the global collectives (role of the reference's
+scripts/single_ops_test.py, extended to the sweep of message sizes and topologies).
 
   bfrun -np 8 python benchmarks/neighbor_allreduce_bandwidth.py --out sweep.json
 
@@ -7,7 +7,8 @@ For every size (4 KB ... 1 GB, powers of 4), dtype (fp32, bf16) and topology (st
 dynamic one-peer exp2) it times, on the device with CUDA events and as the max over ranks:
   * ours      - bf.neighbor_allreduce (peer-memory pull kernel),
   * nccl      - the reference's algorithm: grouped NCCL send/recv + one mul/add per neighbor,
-  * win_put   - bf.win_put into the neighbors' windows (static topology only).
+  * win_put / win_accumulate / win_get / win_update (static topology only),
+  * allreduce / broadcast / allgather against torch.distributed's NCCL (bus bandwidth as nccl-tests define it).
 GB/s counts the bytes every rank must receive over NVLink per operation (in-degree x size);
 the roofline fraction is against 770 GB/s per direction measured for a peer copy on this pool.
 """
@@ -69,7 +70,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--out", default="")
     ap.add_argument("--skip-nccl", action="store_true")
+    ap.add_argument("--ops", default="neighbor,windows,collectives",
+                    help="comma-separated: neighbor (neighbor_allreduce), windows (win_put/accumulate/get/update), "
+                         "collectives (allreduce/broadcast/allgather against NCCL)")
     args = ap.parse_args()
+    ops = set(args.ops.split(","))
     bf.init()
     rank, size = bf.rank(), bf.size()
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -98,7 +103,7 @@ def main():
         for nbytes in sizes:
             numel = nbytes // esize
             x = (torch.rand(numel, generator=torch.Generator().manual_seed(rank)) * 2 - 1).to(dev).to(dtype)
-            for mode in ("static_exp2", "one_peer_exp2"):
+            for mode in (("static_exp2", "one_peer_exp2") if "neighbor" in ops else ()):
                 gen = tu.GetDynamicOnePeerSendRecvRanks(bf.load_topology(), rank)
 
                 def ours():
@@ -154,19 +159,49 @@ def main():
                                     "dtype": row["dtype"], "bytes": nbytes, "mode": mode, "ms": ms2,
                                     "gbs": indeg * nbytes / ms2 / 1e6})
                     del recv_bufs
-            # win_put, static topology
-            w = torch.zeros_like(x)
-            bf.win_create(w, "bw.win", zero_init=True)
-
-            def put():
-                bf.win_put(x, "bw.win")
-
-            ms3 = device_time_ms(put, args.iters, args.warmup)
-            results.append({"op": "win_put", "impl": "ours", "dtype": str(dtype).split(".")[-1], "bytes": nbytes,
-                            "mode": "static_exp2", "ms": ms3, "gbs": len(out_nb) * nbytes / ms3 / 1e6,
-                            "roofline_frac": len(out_nb) * nbytes / ms3 / 1e6 / NVLINK_GBS})
-            bf.win_free("bw.win")
-            del x, w
+            dname = str(dtype).split(".")[-1]
+            if "windows" in ops:
+                # one-sided operations, static topology: put and accumulate write into every out-neighbor's slot, get
+                # reads every in-neighbor's tensor, update folds the slots locally (HBM-bound, no NVLink traffic)
+                w = torch.zeros_like(x)
+                bf.win_create(w, "bw.win", zero_init=True)
+                for op, fn, peers in (("win_put", lambda: bf.win_put(x, "bw.win"), len(out_nb)),
+                                      ("win_accumulate", lambda: bf.win_accumulate(x, "bw.win"), len(out_nb)),
+                                      ("win_get", lambda: bf.win_get("bw.win"), len(in_nb))):
+                    ms3 = device_time_ms(fn, args.iters, args.warmup)
+                    results.append({"op": op, "impl": "ours", "dtype": dname, "bytes": nbytes, "mode": "static_exp2",
+                                    "ms": ms3, "gbs": peers * nbytes / ms3 / 1e6,
+                                    "roofline_frac": peers * nbytes / ms3 / 1e6 / NVLINK_GBS})
+                ms4 = device_time_ms(lambda: bf.win_update("bw.win"), args.iters, args.warmup)
+                # reads self and every slot, writes self
+                results.append({"op": "win_update", "impl": "ours", "dtype": dname, "bytes": nbytes, "mode": "static_exp2",
+                                "ms": ms4, "gbs": (len(in_nb) + 2) * nbytes / ms4 / 1e6})
+                bf.win_free("bw.win")
+                del w
+            if "collectives" in ops:
+                # bus-bandwidth convention of nccl-tests: allreduce 2(n-1)/n * S / t, allgather (n-1)/n * n*S / t,
+                # broadcast S / t
+                n = size
+                for op, ours, ref, factor in (
+                        ("allreduce", lambda: bf.allreduce(x, average=False, name="bw.ar"),
+                         (lambda: nccl.all_reduce(xr)) if nccl else None, 2.0 * (n - 1) / n),
+                        ("broadcast", lambda: bf.broadcast(x, 0, name="bw.bc"),
+                         (lambda: nccl.broadcast(xr, 0)) if nccl else None, 1.0),
+                        ("allgather", lambda: bf.allgather(x, name="bw.ag"),
+                         (lambda: nccl.all_gather_into_tensor(gather_out, xr)) if nccl else None, float(n - 1))):
+                    if op == "allgather" and nbytes * n > (2 << 30):
+                        continue
+                    xr = x.clone()
+                    gather_out = torch.empty(numel * n, dtype=dtype, device=dev) if op == "allgather" else None
+                    ms5 = device_time_ms(ours, args.iters, args.warmup)
+                    results.append({"op": op, "impl": "ours", "dtype": dname, "bytes": nbytes, "ms": ms5,
+                                    "busbw_gbs": factor * nbytes / ms5 / 1e6})
+                    if ref is not None:
+                        ms6 = device_time_ms(ref, args.iters, args.warmup)
+                        results.append({"op": op, "impl": "nccl", "dtype": dname, "bytes": nbytes, "ms": ms6,
+                                        "busbw_gbs": factor * nbytes / ms6 / 1e6})
+                    del xr, gather_out
+            del x
             torch.cuda.empty_cache()
     if rank == 0:
         for r in results:

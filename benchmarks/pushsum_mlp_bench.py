@@ -27,6 +27,8 @@ def main():
     ap.add_argument("--seconds", type=float, default=10.0)
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--dim", type=int, default=4096)
+    ap.add_argument("--bucket-bytes", type=int, default=None,
+                    help="parameters per window; 0 = one window per parameter (the reference's layout), default 64 MiB")
     args = ap.parse_args()
     bf.init()
     rank, size = bf.rank(), bf.size()
@@ -38,7 +40,8 @@ def main():
     torch.manual_seed(1)
     model = MLP(args.dim, args.dim, 1, 4, use_b200_gemm=True).to(dev).to(torch.bfloat16)
     bf.broadcast_parameters(model.state_dict(), root_rank=0)
-    opt = bf.DistributedWinPutOptimizer(torch.optim.SGD(model.parameters(), lr=1e-3), model)
+    opt = bf.DistributedWinPutOptimizer(torch.optim.SGD(model.parameters(), lr=1e-3), model,
+                                        bucket_bytes=args.bucket_bytes)
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     skew = rank / max(size - 1, 1)          # 0 .. 1 extra step time: 1x .. 2x step duration
     steps, t_step = 0, 0.0
@@ -64,6 +67,7 @@ def main():
     if rank == 0:
         print(json.dumps({"metric": "push-sum MLP steps/s (sum over ranks)", "value": round(sum(counts) / elapsed, 2),
                           "unit": "steps/s", "n_gpus": size, "steps_per_rank": counts, "final_losses": losses,
+                          "windows": len(bf.get_current_created_window_names()),
                           "seconds": elapsed}), flush=True)
     opt.unregister_window()
     bf.barrier()

@@ -23,6 +23,7 @@
 #include "cuda/pool_kernels.h"
 #include "cuda/stem_kernels.h"
 #include "cuda/symm_mem.h"
+#include "cuda/window_kernels.h"
 
 namespace py = pybind11;
 using namespace bfb;
@@ -117,6 +118,150 @@ at::Tensor& GemmStatusWord(const at::Tensor& like) {
   if (!status.defined()) status = at::zeros({1}, like.options().dtype(at::kInt));
   return status;
 }
+
+// ---- single-process world of windows: every "rank" is a block [WinHeader | self | one slot per source rank] on
+// one GPU; the per-rank kernels are launched one after the other (tests and micro-benchmarks of the window kernels)
+class LocalWindows {
+ public:
+  LocalWindows(int world, int64_t numel, at::ScalarType dtype, int device)
+      : world_(world), numel_(numel), dtype_(dtype), device_(device) {
+    TORCH_CHECK(world >= 1 && world <= kMaxWorld && numel > 0, "LocalWindows: bad geometry");
+    c10::cuda::CUDAGuard g(device);
+    const int64_t esize = static_cast<int64_t>(c10::elementSize(dtype));
+    region_ = (numel * esize + 255) / 256 * 256;
+    auto opts = at::TensorOptions().device(at::kCUDA, device).dtype(at::kByte);
+    for (int r = 0; r < world; ++r) {
+      mem_.push_back(at::zeros({static_cast<int64_t>(sizeof(WinHeader)) + region_ * (world + 1)}, opts));
+      scratch_.push_back(at::zeros({256}, opts));
+    }
+    for (int r = 0; r < world; ++r) header(r);   // touch
+    std::vector<double> one(1, 1.0);
+    for (int r = 0; r < world; ++r) set_p(r, r, 1.0);
+  }
+  WinHeader* header(int r) { return reinterpret_cast<WinHeader*>(mem_[r].data_ptr()); }
+  unsigned char* self_ptr(int r) { return static_cast<unsigned char*>(mem_[r].data_ptr()) + sizeof(WinHeader); }
+  unsigned char* slot_ptr(int r, int src) { return self_ptr(r) + region_ * (1 + src); }
+  unsigned int* counter(int r) { return reinterpret_cast<unsigned int*>(scratch_[r].data_ptr()); }
+  WinLockState* lock_state_ptr(int r) { return reinterpret_cast<WinLockState*>(static_cast<unsigned char*>(scratch_[r].data_ptr()) + 64); }
+  at::Tensor view(unsigned char* p) {
+    return at::from_blob(p, {numel_}, at::TensorOptions().device(at::kCUDA, device_).dtype(dtype_));
+  }
+  at::Tensor self_tensor(int r) { return view(self_ptr(r)); }
+  at::Tensor slot_tensor(int r, int src) { return view(slot_ptr(r, src)); }
+  void put(int rank, at::Tensor src, std::vector<int> dst, std::vector<double> w, double self_weight, bool accumulate,
+           bool with_p, bool guarded) {
+    c10::cuda::CUDAGuard g(device_);
+    WinPutParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.src = src.data_ptr();
+    p.self_scale_target = src.data_ptr();
+    p.numel = static_cast<unsigned long long>(numel_);
+    p.elem_type = ElemOf(src);
+    p.accumulate = accumulate ? 1 : 0;
+    p.n_dst = static_cast<int>(dst.size());
+    p.my_rank = rank;
+    p.with_p = with_p ? 1 : 0;
+    p.self_weight = self_weight;
+    for (size_t i = 0; i < dst.size(); ++i) {
+      p.weight[i] = w[i];
+      p.dst_slot[i] = slot_ptr(dst[i], rank);
+      p.dst_header[i] = header(dst[i]);
+    }
+    p.my_header = header(rank);
+    p.block_counter = counter(rank);
+    p.lock_state = guarded ? lock_state_ptr(rank) : nullptr;
+    cudaError_t e = LaunchWinPut(p, CurrentStream(device_));
+    TORCH_CHECK(e == cudaSuccess, "win_put launch failed: ", cudaGetErrorString(e));
+  }
+  void get(int rank, std::vector<int> srcs, std::vector<double> w) {
+    c10::cuda::CUDAGuard g(device_);
+    WinGetParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.numel = static_cast<unsigned long long>(numel_);
+    p.elem_type = ElemOf(self_tensor(rank));
+    p.n_src = static_cast<int>(srcs.size());
+    for (size_t i = 0; i < srcs.size(); ++i) {
+      p.weight[i] = w[i];
+      p.src_self[i] = self_ptr(srcs[i]);
+      p.local_slot[i] = slot_ptr(rank, srcs[i]);
+      p.src_rank[i] = srcs[i];
+    }
+    p.my_header = header(rank);
+    p.block_counter = counter(rank);
+    cudaError_t e = LaunchWinGet(p, CurrentStream(device_));
+    TORCH_CHECK(e == cudaSuccess, "win_get launch failed: ", cudaGetErrorString(e));
+  }
+  void update(int rank, std::vector<int> srcs, std::vector<double> w, double self_weight, bool reset, bool with_p) {
+    c10::cuda::CUDAGuard g(device_);
+    WinUpdateParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.self = self_ptr(rank);
+    p.out = self_ptr(rank);
+    p.numel = static_cast<unsigned long long>(numel_);
+    p.elem_type = ElemOf(self_tensor(rank));
+    p.n_src = static_cast<int>(srcs.size());
+    p.reset = reset ? 1 : 0;
+    p.with_p = with_p ? 1 : 0;
+    p.my_rank = rank;
+    p.self_weight = self_weight;
+    for (size_t i = 0; i < srcs.size(); ++i) {
+      p.weight[i] = w[i];
+      p.slot[i] = slot_ptr(rank, srcs[i]);
+      p.src_rank[i] = srcs[i];
+    }
+    p.my_header = header(rank);
+    p.block_counter = counter(rank);
+    cudaError_t e = LaunchWinUpdate(p, CurrentStream(device_));
+    TORCH_CHECK(e == cudaSuccess, "win_update launch failed: ", cudaGetErrorString(e));
+  }
+  // takes or frees lock[index[i]] on rank owners[i], as `rank`
+  void lock(int rank, std::vector<int> owners, std::vector<int> index, bool acquire, double timeout_ms) {
+    c10::cuda::CUDAGuard g(device_);
+    WinLockParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.acquire = acquire ? 1 : 0;
+    p.n = static_cast<int>(owners.size());
+    p.my_rank = rank;
+    p.timeout_ns = static_cast<unsigned long long>(timeout_ms * 1e6);
+    for (size_t i = 0; i < owners.size(); ++i) {
+      p.header[i] = header(owners[i]);
+      p.index[i] = index[i];
+      p.owner[i] = owners[i];
+    }
+    p.state = lock_state_ptr(rank);
+    cudaError_t e = LaunchWinLock(p, CurrentStream(device_));
+    TORCH_CHECK(e == cudaSuccess, "win_lock launch failed: ", cudaGetErrorString(e));
+  }
+  std::vector<int64_t> lock_state(int rank) {
+    at::Tensor host = scratch_[rank].cpu();
+    const WinLockState* s = reinterpret_cast<const WinLockState*>(static_cast<const unsigned char*>(host.data_ptr()) + 64);
+    return {static_cast<int64_t>(s->failed), static_cast<int64_t>(s->failed_rank), static_cast<int64_t>(s->held)};
+  }
+  std::vector<int64_t> versions(int rank) {
+    at::Tensor host = mem_[rank].slice(0, 0, sizeof(WinHeader)).cpu();
+    const WinHeader* h = reinterpret_cast<const WinHeader*>(host.data_ptr());
+    std::vector<int64_t> out(world_);
+    for (int r = 0; r < world_; ++r) out[r] = static_cast<int64_t>(h->version[r]);
+    return out;
+  }
+  std::vector<double> p_values(int rank) {
+    at::Tensor host = mem_[rank].slice(0, 0, sizeof(WinHeader)).cpu();
+    const WinHeader* h = reinterpret_cast<const WinHeader*>(host.data_ptr());
+    return std::vector<double>(h->p, h->p + world_);
+  }
+  void set_p(int rank, int index, double v) {
+    c10::cuda::CUDAGuard g(device_);
+    cudaMemcpy(&header(rank)->p[index], &v, sizeof(double), cudaMemcpyHostToDevice);
+  }
+
+ private:
+  int world_;
+  int64_t numel_;
+  at::ScalarType dtype_;
+  int device_;
+  int64_t region_ = 0;
+  std::vector<at::Tensor> mem_, scratch_;
+};
 
 // channels_last [N, C, H, W] -> the [n, h, w, c] view the convolution kernels address
 ConvView MakeConvView(const at::Tensor& t, bool stem_view) {
@@ -701,19 +846,26 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return dx;
   });
 
-  m.def("gemm_bf16_nn", [](at::Tensor a, at::Tensor b) {
+  m.def("gemm_bf16_nn", [](at::Tensor a, at::Tensor b, c10::optional<at::Tensor> addend) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.scalar_type() == at::kBFloat16 &&
                 b.scalar_type() == at::kBFloat16 && a.is_contiguous() && b.is_contiguous() && a.size(1) == b.size(0),
                 "gemm_bf16_nn expects contiguous bf16 CUDA matrices [M,K] and [K,N]");
+    const void* add = nullptr;
+    if (addend.has_value() && addend->defined()) {
+      TORCH_CHECK(addend->is_cuda() && addend->scalar_type() == at::kBFloat16 && addend->is_contiguous() && addend->dim() == 2 &&
+                  addend->size(0) == a.size(0) && addend->size(1) == b.size(1), "addend must be a contiguous bf16 [M,N] matrix");
+      add = addend->data_ptr();
+    }
     c10::cuda::CUDAGuard g(a.get_device());
     at::Tensor& status = GemmStatusWord(a);
     at::Tensor out = at::empty({a.size(0), b.size(1)}, a.options());
     cudaError_t e = LaunchGemmBf16NN(a.data_ptr(), b.data_ptr(), out.data_ptr(), static_cast<int>(a.size(0)),
                                      static_cast<int>(b.size(1)), static_cast<int>(a.size(1)),
-                                     reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(a.get_device()));
+                                     reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(a.get_device()),
+                                     nullptr, add);
     TORCH_CHECK(e == cudaSuccess, "gemm_bf16_nn launch failed: ", cudaGetErrorString(e));
     return out;
-  }, py::arg("a"), py::arg("b"));
+  }, py::arg("a"), py::arg("b"), py::arg("addend") = py::none());
 
   // act(a w^T + bias) with the tanh GELU, returning the activated matrix and the pre-activation (kept for backward)
   m.def("gemm_bf16_nt_gelu", [](at::Tensor a, at::Tensor w, c10::optional<at::Tensor> bias) {
@@ -772,6 +924,24 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     at::Tensor probe = at::empty({0}, at::TensorOptions().device(at::kCUDA));
     return GemmStatusWord(probe).item<int>();
   });
+
+  py::class_<LocalWindows>(m, "LocalWindows")
+      .def(py::init([](int world, int64_t numel, py::object dtype, int device) {
+             return std::make_unique<LocalWindows>(world, numel, torch::python::detail::py_object_to_dtype(dtype), device);
+           }), py::arg("world"), py::arg("numel"), py::arg("dtype"), py::arg("device") = 0)
+      .def("self_tensor", &LocalWindows::self_tensor)
+      .def("slot_tensor", &LocalWindows::slot_tensor)
+      .def("put", &LocalWindows::put, py::arg("rank"), py::arg("src"), py::arg("dst"), py::arg("weights"),
+           py::arg("self_weight") = 1.0, py::arg("accumulate") = false, py::arg("with_p") = false, py::arg("guarded") = false)
+      .def("get", &LocalWindows::get)
+      .def("update", &LocalWindows::update, py::arg("rank"), py::arg("srcs"), py::arg("weights"), py::arg("self_weight") = 1.0,
+           py::arg("reset") = false, py::arg("with_p") = false)
+      .def("lock", &LocalWindows::lock, py::arg("rank"), py::arg("owners"), py::arg("index"), py::arg("acquire"),
+           py::arg("timeout_ms") = 1000.0)
+      .def("lock_state", &LocalWindows::lock_state)
+      .def("versions", &LocalWindows::versions)
+      .def("p_values", &LocalWindows::p_values)
+      .def("set_p", &LocalWindows::set_p);
 
   py::class_<LocalWorld>(m, "LocalWorld")
       .def(py::init<int, int64_t, int>(), py::arg("world"), py::arg("half_bytes"), py::arg("device") = 0)

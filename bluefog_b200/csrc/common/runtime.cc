@@ -1051,6 +1051,10 @@ Status Runtime::ExecuteCpu(std::vector<Entry>& entries, const Response& resp) {
 }
 
 Status Runtime::GpuStatusToError() {
+  if (windows_) {
+    Status s = windows_->TakeDeviceError();       // a window mutex wait that ran out on the device
+    if (!s.ok()) return s;
+  }
   if (gpu_channel_) {
     Status s = gpu_channel_->StatusToError();
     if (!s.ok()) return s;
@@ -1334,13 +1338,13 @@ Status Runtime::ExecuteGpu(std::vector<Entry>& entries, const Response& resp) {
       end_act();
       return s;
     }
-    std::vector<double> dstw;
-    if (first.use_dst_weight) {
-      dstw.assign(size_, 1.0);
+    // The weights a sender attaches to its destinations always travel with the version (ones when it attaches
+    // none) and the readers always apply them: whether destination weighting is "on" is the sender's decision
+    // alone (any weight != 1), which a reader cannot know, and it may differ from rank to rank and step to step.
+    std::vector<double> dstw(size_, 1.0);
+    if (first.dst_weights.size() == first.dst_ranks.size())
       for (size_t i = 0; i < first.dst_ranks.size(); ++i) dstw[first.dst_ranks[i]] = first.dst_weights[i];
-    }
-    s = gpu_channel_->Publish(segs, first.use_dst_weight ? dstw.data() : nullptr,
-                              static_cast<int>(first.dst_ranks.size()), stream, &round);
+    s = gpu_channel_->Publish(segs, dstw.data(), static_cast<int>(first.dst_ranks.size()), stream, &round);
     if (s.ok()) {
       for (size_t i = 0; i < entries.size(); ++i) {
         at::Tensor& out = *entries[i].spec.output;
@@ -1354,7 +1358,7 @@ Status Runtime::ExecuteGpu(std::vector<Entry>& entries, const Response& resp) {
       std::vector<double> w = first.src_weights;
       if (integral) w.assign(first.src_ranks.size(), 1.0);
       s = gpu_channel_->PullCombine(round, segs, elem, integral ? 1.0 : first.self_weight, first.src_ranks, w,
-                                    first.use_dst_weight, integral ? 1.0 : first.post_scale, stream);
+                                    /*use_dst_weight=*/!integral, integral ? 1.0 : first.post_scale, stream);
     }
     end_act();
     return s;

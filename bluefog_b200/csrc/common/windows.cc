@@ -143,7 +143,7 @@ Status WindowManager::Create(const OpSpec& spec, int channel) {
   Status s = OpenShm(shm_name(rank_), shm_bytes, /*create=*/true, &w->shm[rank_]);
   if (!s.ok()) return s;
   if (w->on_gpu) {
-    s = AllocateIpc(cp_, channel, w->device, data_bytes + 256, &w->dev);
+    s = AllocateIpc(cp_, channel, w->device, data_bytes + 512, &w->dev);     // + block counters and lock states
     if (!s.ok()) return s;
     w->block_counter = reinterpret_cast<unsigned int*>(static_cast<unsigned char*>(w->dev->local()) + data_bytes);
   }
@@ -231,9 +231,70 @@ static Status SpinLock(std::atomic<int>* word, double timeout_s) {
   }
 }
 
+static WinLockState* LockStateOf(const Window& w, bool user) {
+  return reinterpret_cast<WinLockState*>(reinterpret_cast<unsigned char*>(w.block_counter) + (user ? 192 : 128));
+}
+
+Status WindowManager::DeviceLock(Window& w, const std::vector<int>& ranks, bool for_self, bool acquire, bool user,
+                                 void* stream) {
+  if (ranks.empty()) return Status::OK();
+  if (dev_status_host_ == nullptr) {
+    if (cudaHostAlloc(&dev_status_host_, sizeof(CommStatus), cudaHostAllocMapped) != cudaSuccess)
+      return Status::UnknownError("cannot allocate the pinned status block of the window mutexes");
+    std::memset(dev_status_host_, 0, sizeof(CommStatus));
+    if (cudaHostGetDevicePointer(&dev_status_dev_, dev_status_host_, 0) != cudaSuccess)
+      return Status::UnknownError("cannot map the status block of the window mutexes");
+  }
+  std::vector<int> sorted(ranks);
+  std::sort(sorted.begin(), sorted.end());                     // one global order of acquisition: no cycles
+  sorted.erase(std::unique(sorted.begin(), sorted.end()), sorted.end());
+  size_t begin = 0;
+  while (begin < sorted.size()) {
+    const size_t end = std::min(sorted.size(), begin + static_cast<size_t>(kMaxWinPeers));
+    WinLockParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.acquire = acquire ? 1 : 0;
+    p.n = static_cast<int>(end - begin);
+    p.my_rank = rank_;
+    p.timeout_ns = static_cast<unsigned long long>(mutex_timeout_s * 1e9);
+    for (size_t i = begin; i < end; ++i) {
+      const int r = sorted[i];
+      if (r < 0 || r >= size_) return Status::InvalidArgument("invalid rank in mutex list");
+      p.header[i - begin] = reinterpret_cast<WinHeader*>(w.data_base(for_self ? rank_ : r));
+      p.index[i - begin] = for_self ? r : rank_;
+      p.owner[i - begin] = for_self ? rank_ : r;
+    }
+    p.state = LockStateOf(w, user);
+    p.status = static_cast<CommStatus*>(dev_status_dev_);
+    cudaError_t e = LaunchWinLock(p, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return Status::UnknownError("window mutex launch failed: " + CudaErrorString(e));
+    begin = end;
+  }
+  return Status::OK();
+}
+
+Status WindowManager::TakeDeviceError() {
+  if (dev_status_host_ == nullptr) return Status::OK();
+  volatile CommStatus* st = static_cast<volatile CommStatus*>(dev_status_host_);
+  if (st->error == kCommOk) return Status::OK();
+  const unsigned peer = st->peer;
+  st->error = kCommOk;
+  return Status::Aborted("timed out acquiring a window mutex on rank " + std::to_string(peer) +
+                         " (held for longer than BLUEFOG_B200_MUTEX_TIMEOUT_SECONDS); the operation was skipped");
+}
+
 Status WindowManager::MutexAcquire(const std::string& name, const std::vector<int>& ranks, bool for_self) {
   auto w = Find(name);
   if (!w) return Status::InvalidArgument("Window " + name + " does not exist.");
+  if (w->on_gpu) {
+    // an explicit win_mutex: the caller's host code runs under it, so wait until the kernel has taken the words
+    c10::cuda::CUDAGuard guard(w->device);
+    cudaStream_t st = c10::cuda::getCurrentCUDAStream(w->device).stream();
+    Status s = DeviceLock(*w, ranks, for_self, /*acquire=*/true, /*user=*/true, st);
+    if (!s.ok()) return s;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return Status::UnknownError("CUDA error while taking a window mutex");
+    return TakeDeviceError();
+  }
   for (int r : ranks) {
     if (r < 0 || r >= size_) return Status::InvalidArgument("invalid rank in mutex list");
     Status s = for_self ? SpinLock(w->mutex_word(rank_, r), mutex_timeout_s)
@@ -246,6 +307,11 @@ Status WindowManager::MutexAcquire(const std::string& name, const std::vector<in
 Status WindowManager::MutexRelease(const std::string& name, const std::vector<int>& ranks, bool for_self) {
   auto w = Find(name);
   if (!w) return Status::InvalidArgument("Window " + name + " does not exist.");
+  if (w->on_gpu) {
+    c10::cuda::CUDAGuard guard(w->device);
+    cudaStream_t st = c10::cuda::getCurrentCUDAStream(w->device).stream();
+    return DeviceLock(*w, ranks, for_self, /*acquire=*/false, /*user=*/true, st);
+  }
   for (int r : ranks) {
     if (r < 0 || r >= size_) continue;
     auto* word = for_self ? w->mutex_word(rank_, r) : w->mutex_word(r, rank_);
@@ -309,7 +375,9 @@ Status WindowManager::Put(const OpSpec& spec, void* stream) {
   if (spec.dst_ranks.size() != spec.slot_index.size() || spec.dst_ranks.size() != spec.dst_weights.size())
     return Status::InvalidArgument("win_put: inconsistent destination lists");
   const bool with_p = with_p_.load();
-  if (spec.require_mutex) {
+  const bool host_mutex = spec.require_mutex && !w->on_gpu;
+  const bool dev_mutex = spec.require_mutex && w->on_gpu;
+  if (host_mutex) {
     Status s = MutexAcquire(spec.win_name, spec.dst_ranks, /*for_self=*/false);
     if (!s.ok()) return s;
   }
@@ -317,6 +385,10 @@ Status WindowManager::Put(const OpSpec& spec, void* stream) {
   if (w->on_gpu) {
     c10::cuda::CUDAGuard guard(w->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dev_mutex) {
+      Status s = DeviceLock(*w, spec.dst_ranks, /*for_self=*/false, /*acquire=*/true, /*user=*/false, st);
+      if (!s.ok()) return s;
+    }
     size_t begin = 0;
     const size_t n = spec.dst_ranks.size();
     do {
@@ -341,11 +413,12 @@ Status WindowManager::Put(const OpSpec& spec, void* stream) {
       }
       p.my_header = reinterpret_cast<WinHeader*>(w->data_base(rank_));
       p.block_counter = w->block_counter;
+      p.lock_state = dev_mutex ? LockStateOf(*w, false) : nullptr;
       cudaError_t e = LaunchWinPut(p, st);
       if (e != cudaSuccess) { result = Status::UnknownError("win_put launch failed: " + CudaErrorString(e)); break; }
       begin = end;
     } while (begin < n);
-    if (spec.require_mutex) cudaStreamSynchronize(st);
+    if (dev_mutex) DeviceLock(*w, spec.dst_ranks, /*for_self=*/false, /*acquire=*/false, /*user=*/false, st);
   } else {
     auto opts = at::TensorOptions().dtype(w->dtype);
     WinHeader* mine = reinterpret_cast<WinHeader*>(w->data_base(rank_));
@@ -372,7 +445,7 @@ Status WindowManager::Put(const OpSpec& spec, void* stream) {
     if (spec.self_weight != 1.0) t.mul_(spec.self_weight);
     if (with_p && spec.self_weight != 1.0) mine->p[rank_] *= spec.self_weight;
   }
-  if (spec.require_mutex) MutexRelease(spec.win_name, spec.dst_ranks, /*for_self=*/false);
+  if (host_mutex) MutexRelease(spec.win_name, spec.dst_ranks, /*for_self=*/false);
   return result;
 }
 
@@ -382,7 +455,9 @@ Status WindowManager::Get(const OpSpec& spec, void* stream) {
   if (!w) return Status::InvalidArgument("Window " + spec.win_name + " does not exist.");
   if (spec.src_ranks.size() != spec.slot_index.size() || spec.src_ranks.size() != spec.src_weights.size())
     return Status::InvalidArgument("win_get: inconsistent source lists");
-  if (spec.require_mutex) {
+  const bool host_mutex = spec.require_mutex && !w->on_gpu;
+  const bool dev_mutex = spec.require_mutex && w->on_gpu;
+  if (host_mutex) {
     Status s = MutexAcquire(spec.win_name, spec.src_ranks, /*for_self=*/false);
     if (!s.ok()) return s;
   }
@@ -390,6 +465,10 @@ Status WindowManager::Get(const OpSpec& spec, void* stream) {
   if (w->on_gpu) {
     c10::cuda::CUDAGuard guard(w->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dev_mutex) {
+      Status s = DeviceLock(*w, spec.src_ranks, /*for_self=*/false, /*acquire=*/true, /*user=*/false, st);
+      if (!s.ok()) return s;
+    }
     WinGetParams p;
     std::memset(&p, 0, sizeof(p));
     p.numel = w->numel;
@@ -404,9 +483,10 @@ Status WindowManager::Get(const OpSpec& spec, void* stream) {
     }
     p.my_header = reinterpret_cast<WinHeader*>(w->data_base(rank_));
     p.block_counter = w->block_counter;
+    p.lock_state = dev_mutex ? LockStateOf(*w, false) : nullptr;
     cudaError_t e = LaunchWinGet(p, st);
     if (e != cudaSuccess) result = Status::UnknownError("win_get launch failed: " + CudaErrorString(e));
-    if (spec.require_mutex) cudaStreamSynchronize(st);
+    if (dev_mutex) DeviceLock(*w, spec.src_ranks, /*for_self=*/false, /*acquire=*/false, /*user=*/false, st);
   } else {
     auto opts = at::TensorOptions().dtype(w->dtype);
     WinHeader* mine = reinterpret_cast<WinHeader*>(w->data_base(rank_));
@@ -418,7 +498,7 @@ Status WindowManager::Get(const OpSpec& spec, void* stream) {
       reinterpret_cast<std::atomic<unsigned long long>*>(&mine->version[s])->fetch_add(1);
     }
   }
-  if (spec.require_mutex) MutexRelease(spec.win_name, spec.src_ranks, /*for_self=*/false);
+  if (host_mutex) MutexRelease(spec.win_name, spec.src_ranks, /*for_self=*/false);
   return result;
 }
 
@@ -437,7 +517,11 @@ Status WindowManager::Update(const std::string& name, at::Tensor out, double sel
     slots.push_back(static_cast<int>(it - w->in_neighbors.begin()));
   }
   const bool with_p = with_p_.load();
-  if (require_mutex) {
+  const bool host_mutex = require_mutex && !w->on_gpu;
+  // GPU windows: the read-and-clear of win_update(reset) is atomic against concurrent accumulates by itself; the
+  // mutex is still taken when asked for, as three stream-ordered launches
+  const bool dev_mutex = require_mutex && w->on_gpu;
+  if (host_mutex) {
     Status s = MutexAcquire(name, src_ranks, /*for_self=*/true);
     if (!s.ok()) return s;
   }
@@ -445,6 +529,10 @@ Status WindowManager::Update(const std::string& name, at::Tensor out, double sel
   if (w->on_gpu) {
     c10::cuda::CUDAGuard guard(w->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dev_mutex) {
+      Status s = DeviceLock(*w, src_ranks, /*for_self=*/true, /*acquire=*/true, /*user=*/false, st);
+      if (!s.ok()) return s;
+    }
     WinUpdateParams p;
     std::memset(&p, 0, sizeof(p));
     p.self = w->self_ptr(rank_);
@@ -464,9 +552,10 @@ Status WindowManager::Update(const std::string& name, at::Tensor out, double sel
     }
     p.my_header = reinterpret_cast<WinHeader*>(w->data_base(rank_));
     p.block_counter = w->block_counter + 8;
+    p.lock_state = dev_mutex ? LockStateOf(*w, false) : nullptr;
     cudaError_t e = LaunchWinUpdate(p, st);
     if (e != cudaSuccess) result = Status::UnknownError("win_update launch failed: " + CudaErrorString(e));
-    if (require_mutex) cudaStreamSynchronize(st);
+    if (dev_mutex) DeviceLock(*w, src_ranks, /*for_self=*/true, /*acquire=*/false, /*user=*/false, st);
   } else {
     auto opts = at::TensorOptions().dtype(w->dtype);
     WinHeader* h = reinterpret_cast<WinHeader*>(w->data_base(rank_));
@@ -487,7 +576,7 @@ Status WindowManager::Update(const std::string& name, at::Tensor out, double sel
     for (int r = 0; r < size_; ++r)
       reinterpret_cast<std::atomic<unsigned long long>*>(&h->version[r])->store(0);
   }
-  if (require_mutex) MutexRelease(name, src_ranks, /*for_self=*/true);
+  if (host_mutex) MutexRelease(name, src_ranks, /*for_self=*/true);
   return result;
 }
 

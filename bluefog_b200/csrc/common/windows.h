@@ -5,8 +5,10 @@
 // version counter and a push-sum weight p per source rank, and one mutex word per source
 // rank.  CPU windows live in POSIX shared memory mapped by every rank of the box, so a
 // put is a weighted copy into the target's mapping; GPU windows live in CUDA-IPC memory
-// and are written by kernels (cuda/window_kernels.cu).  Mutex words always live in host
-// shared memory and are taken by the host with compare-and-swap, for both kinds.
+// and are written by kernels (cuda/window_kernels.cu).  The mutex words of CPU windows live in host shared
+// memory and are taken by the host with compare-and-swap; those of GPU windows live in the window's device
+// header and are taken by a one-thread kernel on the stream of the operation (bounded wait, error status), so an
+// operation under a mutex is three stream-ordered launches and never a host synchronisation.
 // The target never takes part in a transfer, which is the passive-target behaviour of
 // the reference's MPI-RMA windows (bluefog/common/mpi_controller.cc:795-1183,
 // 1594-1663; bluefog/common/mpi_context.cc:53-170; bluefog/torch/mpi_win_ops.cc:83-426).
@@ -87,8 +89,16 @@ class WindowManager {
   std::vector<std::string> Names();
   size_t Count();
   double mutex_timeout_s = 120.0;
+  // Error left by a device-side mutex wait that ran out since the last call (OK when none); clears it.
+  Status TakeDeviceError();
 
  private:
+  // Launches the lock (acquire) or unlock kernel for the words `ranks` of a GPU window on `stream`.
+  // for_self: words lock[r] of my own header (win_update); otherwise word lock[my rank] of every rank r's header.
+  // user: the state block of explicit win_mutex calls instead of the one that guards the operation kernels.
+  Status DeviceLock(Window& w, const std::vector<int>& ranks, bool for_self, bool acquire, bool user, void* stream);
+  void* dev_status_host_ = nullptr;   // pinned, mapped CommStatus written by the lock kernel
+  void* dev_status_dev_ = nullptr;
   std::shared_ptr<Window> Find(const std::string& name);
   Status FreeOne(std::shared_ptr<Window> w);
   ControlPlane* cp_;

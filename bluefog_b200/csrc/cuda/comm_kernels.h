@@ -33,6 +33,7 @@ enum CommError : uint32_t {
   kCommTimeoutDone = 2,    // readers of an old version never finished
   kCommBadArgument = 3,
   kCommPeerFailed = 4,     // a source published a version it could not complete (its own wait had expired)
+  kCommTimeoutLock = 5,    // a window mutex word stayed taken for longer than the limit
 };
 
 struct alignas(256) ChannelCtrl {

@@ -525,8 +525,9 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
               tma_store_commit();
             }
             ++boxes;
-          } else if constexpr (EPI == kEpiMulGeluGrad) {
-            // out = accumulator * GELU'(aux): the backward of a fused Linear+GELU, aux = the saved pre-activation
+          } else if constexpr (EPI == kEpiMulGeluGrad || EPI == kEpiAddAux) {
+            // kEpiMulGeluGrad: out = accumulator * GELU'(aux), the backward of a fused Linear+GELU (aux = the saved
+            // pre-activation).  kEpiAddAux: out = accumulator + aux (aux = a gradient that joins this one).
             unsigned char* box = my_out + size_t(boxes & 1) * Cfg::kBytesOutBox;
             unsigned char* row = box + lane * 128;
 #pragma unroll
@@ -538,8 +539,13 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 const float2 t2 = __bfloat1622float2(ah[i]);
-                v[2 * i] = __uint_as_float(r[j * 8 + 2 * i]) * gelu_tanh_grad(t2.x);
-                v[2 * i + 1] = __uint_as_float(r[j * 8 + 2 * i + 1]) * gelu_tanh_grad(t2.y);
+                if constexpr (EPI == kEpiAddAux) {
+                  v[2 * i] = __uint_as_float(r[j * 8 + 2 * i]) + t2.x;
+                  v[2 * i + 1] = __uint_as_float(r[j * 8 + 2 * i + 1]) + t2.y;
+                } else {
+                  v[2 * i] = __uint_as_float(r[j * 8 + 2 * i]) * gelu_tanh_grad(t2.x);
+                  v[2 * i + 1] = __uint_as_float(r[j * 8 + 2 * i + 1]) * gelu_tanh_grad(t2.y);
+                }
               }
               uint4 pk;
               __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
@@ -766,11 +772,12 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
 // product with a transposed weight (an input gradient) needs no transposed copy.  With gelu_preact the result
 // is multiplied elementwise by GELU'(gelu_preact[M,N]) in the epilogue (the backward of a fused Linear+GELU).
 cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int N, int K, unsigned int* status,
-                             cudaStream_t stream, const void* gelu_preact) {
+                             cudaStream_t stream, const void* gelu_preact, const void* addend) {
   (void)cudaGetLastError();   // the value returned below must be this launch's own, not an older error of the calling thread
   if (M <= 0 || N <= 0 || K <= 0 || (K % 8) != 0 || (N % 8) != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
-      (reinterpret_cast<uintptr_t>(gelu_preact) & 15))
+      (reinterpret_cast<uintptr_t>(gelu_preact) & 15) || (reinterpret_cast<uintptr_t>(addend) & 15) ||
+      (gelu_preact != nullptr && addend != nullptr))
     return cudaErrorInvalidValue;
   const int sm_count = SmCount();
   CUtensorMap map_a, map_b, map_c;
@@ -780,7 +787,13 @@ cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
   const __nv_bfloat16* aux = static_cast<const __nv_bfloat16*>(gelu_preact);
   cudaError_t e;
-  if (N > 128) {
+  if (addend != nullptr) {
+    const __nv_bfloat16* add = static_cast<const __nv_bfloat16*>(addend);
+    e = N > 128 ? LaunchPersistent<256, 1, 0, kEpiAddAux>(map_a, map_b, map_c, map_c, o, nullptr, add, M, N, K, 0, 1, sm_count,
+                                                          status, stream)
+                : LaunchPersistent<128, 1, 0, kEpiAddAux>(map_a, map_b, map_c, map_c, o, nullptr, add, M, N, K, 0, 1, sm_count,
+                                                          status, stream);
+  } else if (N > 128) {
     e = aux != nullptr ? LaunchPersistent<256, 1, 0, kEpiMulGeluGrad>(map_a, map_b, map_c, map_c, o, nullptr, aux, M, N, K, 0, 1,
                                                                       sm_count, status, stream)
                        : LaunchPersistent<256, 1, 0, kEpiNone>(map_a, map_b, map_c, map_c, o, nullptr, nullptr, M, N, K, 0, 1,

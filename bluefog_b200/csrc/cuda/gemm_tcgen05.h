@@ -8,7 +8,7 @@ enum GemmAct : int { kActNone = 0, kActRelu = 1, kActGeluTanh = 2 };
 // Extra work of the epilogue: store the pre-activation value (accumulator + bias) to a second matrix besides
 // act(...) of it; or multiply the result by GELU'(aux[m, n]) (the input gradient through a GELU whose
 // pre-activation was kept).
-enum GemmEpi : int { kEpiNone = 0, kEpiStorePreact = 1, kEpiMulGeluGrad = 2, kEpiColumnStats = 3 };
+enum GemmEpi : int { kEpiNone = 0, kEpiStorePreact = 1, kEpiMulGeluGrad = 2, kEpiColumnStats = 3, kEpiAddAux = 4 };
 
 // True when the driver exposes cuTensorMapEncodeTiled (needed to build TMA descriptors).
 bool GemmSupported();
@@ -26,8 +26,10 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
 
 // out[M,N] = a[M,K] * b[K,N] with b row-major (consumed as an MN-major operand); K % 8 == 0, N % 8 == 0.
 // gelu_preact (optional, [M,N] bf16): the result is multiplied elementwise by GELU'(gelu_preact).
+// addend (optional, [M,N] bf16, not together with gelu_preact): added to the product in fp32 before rounding (the
+// gradient that reaches a block's input through its shortcut, so that no separate addition pass is needed).
 cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int N, int K, unsigned int* status,
-                             cudaStream_t stream, const void* gelu_preact = nullptr);
+                             cudaStream_t stream, const void* gelu_preact = nullptr, const void* addend = nullptr);
 
 // out[M,N] = a[K,M]^T * b[K,N], a and b row-major (both consumed MN-major); M % 8 == 0, N % 8 == 0.
 cudaError_t LaunchGemmBf16TN(const void* a, const void* b, void* out, int M, int N, int K, unsigned int* status,

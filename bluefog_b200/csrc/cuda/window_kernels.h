@@ -17,6 +17,18 @@ namespace bfb {
 struct alignas(256) WinHeader {
   unsigned long long version[kMaxWorld];  // version[s]: transfers from source s since the last update
   double p[kMaxWorld];                    // push-sum weights: p[own rank] = own value, p[s] = received from s
+  // Device-side mutex words of GPU windows: lock[s] guards the slot that source s writes on this rank (and
+  // lock[own rank] the self tensor).  0 = free, otherwise 1 + the holder's rank.  Taken with a compare-and-swap
+  // from a kernel of the holder (win_lock_kernel), which waits at most a given time.
+  unsigned int lock[kMaxWorld];
+};
+
+// Outcome of the last lock launch of a rank on a window; lives next to the window's block counter.
+struct WinLockState {
+  unsigned int failed;        // 1: the wait for some word ran out; nothing is held, guarded kernels do nothing
+  unsigned int failed_rank;   // owner of the word that could not be taken
+  unsigned int held;          // words currently held by this rank's lock launch
+  unsigned int pad;
 };
 
 constexpr int kMaxWinPeers = 64;
@@ -36,6 +48,7 @@ struct WinPutParams {
   WinHeader* dst_header[kMaxWinPeers];  // peer-mapped headers
   WinHeader* my_header;
   unsigned int* block_counter;
+  const WinLockState* lock_state;   // optional: when its `failed` is set the kernel does nothing
 };
 
 struct WinGetParams {
@@ -48,6 +61,7 @@ struct WinGetParams {
   int src_rank[kMaxWinPeers];
   WinHeader* my_header;
   unsigned int* block_counter;
+  const WinLockState* lock_state;
 };
 
 struct WinUpdateParams {
@@ -65,10 +79,26 @@ struct WinUpdateParams {
   int src_rank[kMaxWinPeers];
   WinHeader* my_header;
   unsigned int* block_counter;
+  const WinLockState* lock_state;
+};
+
+// Takes (acquire != 0) or frees the words lock[index[i]] of the headers header[i], in the given order (callers
+// sort by owner rank, so two ranks locking overlapping sets cannot wait for each other in a cycle).
+struct WinLockParams {
+  int acquire;
+  int n;
+  int my_rank;
+  unsigned long long timeout_ns;
+  WinHeader* header[kMaxWinPeers];
+  int index[kMaxWinPeers];
+  int owner[kMaxWinPeers];           // rank that owns header[i], for the error report
+  WinLockState* state;
+  CommStatus* status;                // optional pinned status block: error kCommTimeoutLock, peer = owner
 };
 
 cudaError_t LaunchWinPut(const WinPutParams& p, cudaStream_t stream);
 cudaError_t LaunchWinGet(const WinGetParams& p, cudaStream_t stream);
 cudaError_t LaunchWinUpdate(const WinUpdateParams& p, cudaStream_t stream);
+cudaError_t LaunchWinLock(const WinLockParams& p, cudaStream_t stream);
 
 }  // namespace bfb

@@ -74,6 +74,19 @@ class Conv1x1(nn.Conv2d):
             return conv.conv2d(x, self.weight, 2, 0)       # strided reads inside the implicit-GEMM kernel
         return super().forward(x)
 
+    def forward_fork_bn_act(self, x, bn, relu):
+        """``(bn_act(self(x), bn), shortcut)`` for the first convolution of a block whose shortcut is the identity:
+        the shortcut's gradient is added inside the input-gradient GEMM (``ops.gemm.conv1x1_fork``)."""
+        from bluefog_b200.ops import gemm
+        if (self.takes_b200_gemm(x) and torch.is_grad_enabled() and x.requires_grad
+                and gemm.conv1x1_fork_supported(x, self.weight)):
+            sums = None
+            if bn.training and FUSE_BN_STATS and self.weight.shape[0] <= self.weight.shape[1]:
+                sums = fused_bn.take_sums(x.device, self.weight.shape[0])
+            y, shortcut = gemm.conv1x1_fork(x, self.weight, sums)
+            return bn_act(y, bn, relu=relu, stats=sums), shortcut
+        return self.forward_bn_act(x, bn, relu), x
+
     def forward_bn_act(self, x, bn, relu, residual=None):
         """``bn_act(self(x), bn, ...)``; on the tcgen05 path the GEMM epilogue also takes the batch statistics of
         its output, so the BatchNorm kernels read the activation once instead of twice."""
@@ -196,8 +209,11 @@ class Bottleneck(nn.Module):
         self.downsample = downsample
 
     def forward(self, x):
-        identity = x if self.downsample is None else self.downsample(x)
-        out = self.conv1.forward_bn_act(x, self.bn1, relu=True)
+        if self.downsample is None:
+            out, identity = self.conv1.forward_fork_bn_act(x, self.bn1, relu=True)
+        else:
+            identity = self.downsample(x)
+            out = self.conv1.forward_bn_act(x, self.bn1, relu=True)
         out = bn_act(self.conv2(out), self.bn2, relu=True)
         return self.conv3.forward_bn_act(out, self.bn3, relu=True, residual=identity)
 

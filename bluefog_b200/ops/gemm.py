@@ -110,6 +110,53 @@ class _Conv1x1Fn(torch.autograd.Function):
         return dx, dw, None
 
 
+class _Conv1x1ForkFn(torch.autograd.Function):
+    """``(conv1x1(x, w), x)``: the first convolution of a residual block together with the block's shortcut.  In the
+    backward pass the gradient that arrives through the shortcut is added inside the epilogue of the input-gradient
+    GEMM (fp32, before rounding), instead of autograd adding two full activation tensors in a pass of its own."""
+
+    @staticmethod
+    def forward(ctx, x, weight, col_stats=None):
+        n, c, h, w = x.shape
+        cout = weight.shape[0]
+        ctx.save_for_backward(x, weight)
+        a = x.permute(0, 2, 3, 1).reshape(n * h * w, c)
+        y = _b.native.gemm_bf16_nt(a, weight.reshape(cout, c), None, 0, col_stats)
+        return y.view(n, h, w, cout).permute(0, 3, 1, 2), x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dshortcut):
+        x, weight = ctx.saved_tensors
+        n, c, h, w = x.shape
+        cout = weight.shape[0]
+        C = _b.native
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            d2 = dy.permute(0, 2, 3, 1).reshape(n * h * w, cout)
+            add = None
+            if dshortcut is not None:
+                add = dshortcut.contiguous(memory_format=torch.channels_last).permute(0, 2, 3, 1).reshape(n * h * w, c)
+            dx = C.gemm_bf16_nn(d2, weight.reshape(cout, c).contiguous(), add).view(n, h, w, c).permute(0, 3, 1, 2)
+        if ctx.needs_input_grad[1]:
+            dw = C.conv_wgrad(dy, x, [0], [0], [0], 1, 1, False).view(cout, 1, 1, c).permute(0, 3, 1, 2)
+        return dx, dw, None
+
+
+def conv1x1_fork_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    C = _b.native
+    if not (conv1x1_supported(x, weight) and hasattr(C, "conv_wgrad")):
+        return False
+    n, c, h, w = x.shape
+    return bool(c % 64 == 0 and weight.shape[0] % 8 == 0 and C.conv_wgrad_supported(n, h, w, c, weight.shape[0], 1))
+
+
+def conv1x1_fork(x: torch.Tensor, weight: torch.Tensor, col_stats=None):
+    """Returns ``(conv1x1(x, weight), shortcut)`` where ``shortcut`` equals ``x``; use ``shortcut`` for the residual
+    connection of the block (see ``_Conv1x1ForkFn``).  Only where ``conv1x1_fork_supported``."""
+    return _Conv1x1ForkFn.apply(x, weight, col_stats)
+
+
 def conv1x1_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """Whether ``conv1x1`` runs this input on the tcgen05 GEMM."""
     return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 4

@@ -517,9 +517,13 @@ class _FusedMixin:
                 for p in bk.params:
                     self.state[p]["step"] = torch.tensor(float(bk.steps))
         out = self._base_cls.state_dict(self)
-        # what the flat buffers cannot say by themselves: whether SGD's momentum buffer has been initialised yet
-        out["bluefog_b200"] = {"first_step": [bool(bk.first_step) for bk in self._buckets],
-                               "steps": [int(bk.steps) for bk in self._buckets]}
+        # What the flat buffers cannot say by themselves (whether SGD's momentum buffer has been initialised yet, the
+        # update count) travels as one more entry of the first parameter group, so that the dictionary keeps the two
+        # top-level keys of every torch optimizer.
+        if out["param_groups"]:
+            out["param_groups"][0] = dict(out["param_groups"][0])
+            out["param_groups"][0]["bluefog_b200"] = {"first_step": [bool(bk.first_step) for bk in self._buckets],
+                                                      "steps": [int(bk.steps) for bk in self._buckets]}
         return out
 
     @torch.no_grad()
@@ -536,8 +540,9 @@ class _FusedMixin:
             for old_id, p in zip(sg["params"], g["params"]):
                 by_id[old_id] = p
         loaded = {by_id[k]: v for k, v in state_dict["state"].items() if k in by_id}
+        extra = saved_groups[0].get("bluefog_b200") if saved_groups else None
+        saved_groups = [{k: v for k, v in sg.items() if k != "bluefog_b200"} for sg in saved_groups]
         self._base_cls.load_state_dict(self, {"state": {}, "param_groups": saved_groups})
-        extra = state_dict.get("bluefog_b200")
         for k, bk in enumerate(self._buckets):
             saw_momentum = False
             for i, p in enumerate(bk.params):

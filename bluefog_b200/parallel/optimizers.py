@@ -399,11 +399,69 @@ class _DistributedAdaptThenCombineOptimizer(_CommonMixin):
 # --------------------------------------------------------------------------------------
 # one-sided: win_put / pull-get
 # --------------------------------------------------------------------------------------
+class _WindowBucket:
+    """Parameters that travel as one window: a flat tensor holding them back to back."""
+
+    def __init__(self, name, params):
+        self.name = name
+        self.params = params
+        self.offsets, n = [], 0
+        for p in params:
+            self.offsets.append(n)
+            n += p.numel()
+        self.numel = n
+        self.flat = None
+        self.handle = None
+
+    def views(self, flat):
+        return [flat[o:o + p.numel()].view(p.shape) for o, p in zip(self.offsets, self.params)]
+
+
+def _window_bucket_bytes(bucket_bytes):
+    if bucket_bytes is None:
+        bucket_bytes = int(os.environ.get("BLUEFOG_B200_WINDOW_BUCKET_BYTES", 64 * 1024 * 1024))
+    return int(bucket_bytes)
+
+
+def _make_window_buckets(optimizer, parameter_names, prefix, bucket_bytes):
+    """Groups the optimizer's trainable parameters, in order, into buckets of at most ``bucket_bytes`` with one
+    dtype and device each.  ``bucket_bytes <= 0``: one bucket per parameter, named after it (the layout of the
+    reference, bluefog/torch/optimizers.py:905-922: one window per parameter)."""
+    buckets, cur, cur_bytes, key = [], [], 0, None
+
+    def flush():
+        nonlocal cur, cur_bytes
+        if cur:
+            buckets.append(_WindowBucket("%sbucket.%d" % (prefix, len(buckets)), cur))
+        cur, cur_bytes = [], 0
+
+    for group in optimizer.param_groups:
+        for p in group["params"]:
+            if parameter_names.get(p) is None:
+                raise KeyError("Cannot find parameter in the _parameter_names dictionary")
+            if not p.requires_grad:
+                continue
+            if bucket_bytes <= 0:
+                buckets.append(_WindowBucket(parameter_names[p], [p]))
+                continue
+            nbytes = p.numel() * p.element_size()
+            k = (p.dtype, p.device)
+            if cur and (k != key or cur_bytes + nbytes > bucket_bytes):
+                flush()
+            key = k
+            cur.append(p)
+            cur_bytes += nbytes
+    flush()
+    return buckets
+
+
 class _DistributedWinOptimizer(_CommonMixin):
     """Parameters are windows: a forward hook puts them to (or gets them from) the
-    neighbors without waiting for anybody; ``step()`` folds what has arrived."""
+    neighbors without waiting for anybody; ``step()`` folds what has arrived.  The parameters are packed into
+    buckets (64 MiB by default) and every bucket is ONE window: a step costs one put/get kernel and one update
+    kernel per bucket instead of one pair, one mutex and one handle per parameter."""
 
-    def _bf_init(self, model, num_steps_per_communication, window_prefix, pull_style):
+    def _bf_init(self, model, num_steps_per_communication, window_prefix, pull_style, bucket_bytes=None):
         if pull_style:
             self.src_weights = None   # controls win_get dynamically
         else:
@@ -416,6 +474,9 @@ class _DistributedWinOptimizer(_CommonMixin):
         self._bluefog_delay = {p: num_steps_per_communication for p in self._parameter_names}
         self._windows_registered = False
         self._owned_windows = {}
+        self._bucket_bytes = _window_bucket_bytes(bucket_bytes)
+        self._buckets = []
+        self._bucket_of = {}
         if _b.size() > 1:
             self._register_window()
             for m in self._models:
@@ -429,6 +490,7 @@ class _DistributedWinOptimizer(_CommonMixin):
 
     def _make_hook(self):
         def hook(model, *unused):
+            ready = []
             for _, layer in _named_leaf_module(model):
                 if not layer.training:
                     continue
@@ -439,28 +501,41 @@ class _DistributedWinOptimizer(_CommonMixin):
                         self._warn_once(_WARN_STEPS)
                     self._bluefog_delay[p] -= 1
                     if self._bluefog_delay[p] == 0:
-                        name = self._parameter_names[p]
-                        if self._pull_style:
-                            handle = _win.win_get_nonblocking(name=name, src_weights=self.src_weights,
-                                                              require_mutex=True)
-                        else:
-                            handle = _win.win_put_nonblocking(tensor=p.data, name=name,
-                                                              dst_weights=self.dst_weights, require_mutex=False)
-                        self._handles[p] = handle
+                        bk = self._bucket_of.get(p)
+                        if bk is not None and bk not in ready:
+                            ready.append(bk)
+            for bk in ready:
+                # a bucket goes out when every one of its parameters has been through its forward passes
+                if bk.handle is not None or any(self._bluefog_delay[q] > 0 for q in bk.params):
+                    continue
+                if self._pull_style:
+                    bk.handle = _win.win_get_nonblocking(name=bk.name, src_weights=self.src_weights, require_mutex=True)
+                else:
+                    bk.handle = _win.win_put_nonblocking(tensor=bk.flat.detach(), name=bk.name, dst_weights=self.dst_weights,
+                                                         require_mutex=False)
+                self._handles[bk.params[0]] = bk.handle
         return hook
 
+    @torch.no_grad()
     def _register_window(self):
         if _b.size() <= 1 or self._windows_registered:
             return
-        for group in self.param_groups:
-            for p in group["params"]:
-                name = self._parameter_names.get(p)
-                if name is None:
-                    raise KeyError("Cannot find parameter in the _parameter_names dictionary")
-                with torch.no_grad():
-                    if not _win.win_create(p, name):
-                        raise ValueError("Cannot allocate window for the parameter {}".format(name))
-                self._owned_windows[name] = _win.window_serial(name)
+        self._buckets = _make_window_buckets(self, self._parameter_names, self.window_prefix, self._bucket_bytes)
+        for bk in self._buckets:
+            if len(bk.params) == 1 and self._bucket_bytes <= 0:
+                bk.flat = bk.params[0]                       # the parameter itself is the window tensor
+                if not _win.win_create(bk.flat, bk.name):
+                    raise ValueError("Cannot allocate window for the parameter {}".format(bk.name))
+            else:
+                flat = torch.cat([p.data.reshape(-1) for p in bk.params])
+                if not _win.win_create(flat, bk.name):
+                    raise ValueError("Cannot allocate window for the bucket {}".format(bk.name))
+                bk.flat = flat                               # now aliases the window's memory
+                for p, v in zip(bk.params, bk.views(flat)):
+                    p.data = v
+            for p in bk.params:
+                self._bucket_of[p] = bk
+            self._owned_windows[bk.name] = _win.window_serial(bk.name)
         self._windows_registered = True
 
     def unregister_window(self):
@@ -477,10 +552,14 @@ class _DistributedWinOptimizer(_CommonMixin):
 
     def synchronize(self):
         with torch.no_grad():
-            for p, handle in self._handles.items():
-                _win.win_wait(handle)
-                self._bluefog_delay[p] = self._num_steps_per_communication
-                _win.win_update(name=self._parameter_names[p], require_mutex=True)
+            for bk in self._buckets:
+                if bk.handle is None:
+                    continue
+                _win.win_wait(bk.handle)
+                bk.handle = None
+                for p in bk.params:
+                    self._bluefog_delay[p] = self._num_steps_per_communication
+                _win.win_update(name=bk.name, require_mutex=True)
         self._handles.clear()
         self._synchronized = True
 
@@ -499,21 +578,23 @@ class _DistributedWinOptimizer(_CommonMixin):
 # push-sum
 # --------------------------------------------------------------------------------------
 class _DistributedPushSumOptimizer(_CommonMixin):
-    """Every parameter travels with a scalar weight: ``[x, 1]`` is split between this rank
+    """Every bucket of parameters travels with a scalar weight: ``[x, 1]`` is split between this rank
     (``self_weight``) and its out-neighbors (``dst_weights``, accumulated one-sidedly), the
-    arrived shares are collected, and the parameter becomes ``sum(x) / sum(weight)``."""
+    arrived shares are collected, and the parameters become ``sum(x) / sum(weight)``."""
 
-    def _bf_init(self, model, num_steps_per_communication):
+    def _bf_init(self, model, num_steps_per_communication, bucket_bytes=None):
         outdegree = len(_b.out_neighbor_ranks())
         self.dst_weights = {r: 1.0 / (outdegree + 1) for r in _b.out_neighbor_ranks()}
         self.self_weight = 1.0 / (outdegree + 1)
         self.force_barrier = True
         self._init_common(model)
-        self._extended = {}
         self._num_steps_per_communication = num_steps_per_communication
         self._pushsum_delay = {p: num_steps_per_communication for p in self._parameter_names}
         self._windows_registered = False
         self._owned_windows = {}
+        self._bucket_bytes = _window_bucket_bytes(bucket_bytes)
+        self._buckets = []
+        self._bucket_of = {}
         if _b.size() > 1:
             self._register_window()
             for m in self._models:
@@ -521,14 +602,21 @@ class _DistributedPushSumOptimizer(_CommonMixin):
 
     @torch.no_grad()
     def _register_window(self):
-        for group in self.param_groups:
-            for p in group["params"]:
-                name = self._parameter_names[p]
-                ext = torch.cat((p.data.reshape(-1), torch.ones(1, dtype=p.dtype, device=p.device)), 0)
-                if not _win.win_create(ext, name, zero_init=True):
-                    raise ValueError("Cannot allocate window for the parameter {}".format(name))
-                self._extended[name] = ext
-                self._owned_windows[name] = _win.window_serial(name)
+        self._buckets = _make_window_buckets(self, self._parameter_names, "", self._bucket_bytes)
+        for bk in self._buckets:
+            p0 = bk.params[0]
+            # the window holds [parameters ..., weight]; the parameters themselves become views of one flat tensor
+            # so that filling the window and reading the result back are single copies
+            bk.pflat = torch.cat([p.data.reshape(-1) for p in bk.params])
+            for p, v in zip(bk.params, bk.views(bk.pflat)):
+                p.data = v
+            ext = torch.cat((bk.pflat, torch.ones(1, dtype=p0.dtype, device=p0.device)), 0)
+            if not _win.win_create(ext, bk.name, zero_init=True):
+                raise ValueError("Cannot allocate window for the parameter {}".format(bk.name))
+            bk.flat = ext
+            for p in bk.params:
+                self._bucket_of[p] = bk
+            self._owned_windows[bk.name] = _win.window_serial(bk.name)
         self._windows_registered = True
 
     def unregister_window(self):
@@ -542,6 +630,7 @@ class _DistributedPushSumOptimizer(_CommonMixin):
 
     def _make_hook(self):
         def hook(model, *unused):
+            ready = []
             for _, layer in _named_leaf_module(model):
                 if not layer.training:
                     continue
@@ -552,25 +641,33 @@ class _DistributedPushSumOptimizer(_CommonMixin):
                         self._warn_once(_WARN_STEPS)
                     self._pushsum_delay[p] -= 1
                     if self._pushsum_delay[p] == 0:
-                        name = self._parameter_names[p]
-                        ext = self._extended[name]
-                        with torch.no_grad():
-                            ext[:-1].copy_(p.data.reshape(-1))
-                            ext[-1] = 1.0
-                        # The local share is scaled by self_weight after the shares have left.
-                        self._handles[p] = _win.win_accumulate_nonblocking(
-                            tensor=ext, name=name, self_weight=self.self_weight,
-                            dst_weights=self.dst_weights, require_mutex=True)
+                        bk = self._bucket_of.get(p)
+                        if bk is not None and bk not in ready:
+                            ready.append(bk)
+            for bk in ready:
+                if bk.handle is not None or any(self._pushsum_delay[q] > 0 for q in bk.params):
+                    continue
+                with torch.no_grad():
+                    bk.flat[:-1].copy_(bk.pflat)
+                    bk.flat[-1] = 1.0
+                # The local share is scaled by self_weight after the shares have left.
+                bk.handle = _win.win_accumulate_nonblocking(
+                    tensor=bk.flat, name=bk.name, self_weight=self.self_weight,
+                    dst_weights=self.dst_weights, require_mutex=True)
+                self._handles[bk.params[0]] = bk.handle
         return hook
 
     def synchronize(self):
         with torch.no_grad():
-            for p, handle in self._handles.items():
-                _win.win_wait(handle)
-                name = self._parameter_names[p]
-                self._pushsum_delay[p] = self._num_steps_per_communication
-                ext = _win.win_update_then_collect(name=name)
-                p.data.copy_((ext[:-1] / ext[-1]).reshape(p.shape))
+            for bk in self._buckets:
+                if bk.handle is None:
+                    continue
+                _win.win_wait(bk.handle)
+                bk.handle = None
+                for p in bk.params:
+                    self._pushsum_delay[p] = self._num_steps_per_communication
+                ext = _win.win_update_then_collect(name=bk.name)
+                bk.pflat.copy_(ext[:-1] / ext[-1])
         self._handles.clear()
         self._synchronized = True
 
@@ -602,21 +699,25 @@ def _wrap(optimizer, mixin, *args, **kwargs):
     return obj
 
 
-def DistributedPushSumOptimizer(optimizer, model, num_steps_per_communication=1):
+def DistributedPushSumOptimizer(optimizer, model, num_steps_per_communication=1, bucket_bytes=None):
     """Asynchronous push-sum over one-sided windows (column-stochastic weights; the graph
-    only needs to be strongly connected). Knobs: ``dst_weights``, ``self_weight``, ``force_barrier``."""
-    return _wrap(optimizer, _DistributedPushSumOptimizer, model, num_steps_per_communication)
+    only needs to be strongly connected). Knobs: ``dst_weights``, ``self_weight``, ``force_barrier``.
+    ``bucket_bytes``: parameters per window (default 64 MiB, ``BLUEFOG_B200_WINDOW_BUCKET_BYTES``; 0 = one window
+    per parameter as in the reference)."""
+    return _wrap(optimizer, _DistributedPushSumOptimizer, model, num_steps_per_communication, bucket_bytes)
 
 
-def DistributedPullGetOptimizer(optimizer, model, num_steps_per_communication=1, window_prefix=None):
+def DistributedPullGetOptimizer(optimizer, model, num_steps_per_communication=1, window_prefix=None, bucket_bytes=None):
     """Each step pulls the in-neighbors' parameters with win_get and averages. Knob: ``src_weights``."""
-    return _wrap(optimizer, _DistributedWinOptimizer, model, num_steps_per_communication, window_prefix, True)
+    return _wrap(optimizer, _DistributedWinOptimizer, model, num_steps_per_communication, window_prefix, True,
+                 bucket_bytes)
 
 
-def DistributedWinPutOptimizer(optimizer, model, num_steps_per_communication=1, window_prefix=None):
+def DistributedWinPutOptimizer(optimizer, model, num_steps_per_communication=1, window_prefix=None, bucket_bytes=None):
     """Each step pushes the parameters to the out-neighbors with win_put and averages what has
     arrived. Knob: ``dst_weights``."""
-    return _wrap(optimizer, _DistributedWinOptimizer, model, num_steps_per_communication, window_prefix, False)
+    return _wrap(optimizer, _DistributedWinOptimizer, model, num_steps_per_communication, window_prefix, False,
+                 bucket_bytes)
 
 
 def _maybe_fused(optimizer, model, style, communication_type, steps, fused, **fused_kwargs):

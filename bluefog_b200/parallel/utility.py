@@ -119,11 +119,9 @@ def broadcast_optimizer_state(optimizer, root_rank):
             else:
                 scalars[(pid, key)] = value.item() if isinstance(value, torch.Tensor) else value
     groups = [{k: v for k, v in g.items() if k != "params"} for g in state_dict["param_groups"]]
-    # "bluefog_b200": what a fused optimizer keeps beside its flat buffers (step counts, SGD's first-step flag)
-    scalars, groups, fused_extra = _broadcast_object((scalars, groups, state_dict.get("bluefog_b200")), root_rank,
-                                                     "optimizer.scalars")
-    if fused_extra is not None:
-        state_dict["bluefog_b200"] = fused_extra
+    # (the groups of a fused optimizer also carry what it keeps beside its flat buffers: step counts and SGD's
+    # first-step flag, under the key "bluefog_b200" of the first group)
+    scalars, groups = _broadcast_object((scalars, groups), root_rank, "optimizer.scalars")
     broadcast_parameters(tensors, root_rank)
     for (pid, key), value in scalars.items():
         cur = state_dict["state"][pid].get(key)

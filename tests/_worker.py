@@ -552,7 +552,10 @@ def optimizers():
               ("awc_j2", bf.DistributedAdaptWithCombineOptimizer, {"num_steps_per_communication": 2}),
               ("win_put", bf.DistributedWinPutOptimizer, {}),
               ("pull_get", bf.DistributedPullGetOptimizer, {}),
-              ("push_sum", bf.DistributedPushSumOptimizer, {})]
+              ("push_sum", bf.DistributedPushSumOptimizer, {}),
+              # one window per parameter, the layout of the reference
+              ("win_put", bf.DistributedWinPutOptimizer, {"bucket_bytes": 0}),
+              ("push_sum", bf.DistributedPushSumOptimizer, {"bucket_bytes": 0})]
     for name, factory, kw in styles:
         torch.manual_seed(1)
         model = torch.nn.Linear(16, 3).to(d)
@@ -569,6 +572,10 @@ def optimizers():
                 loss.backward()
             opt.step()
         assert loss.item() < 0.08, (name, loss.item())
+        if name in ("win_put", "pull_get", "push_sum"):
+            windows = bf.get_current_created_window_names()
+            # bias and weight share one bucket window by default; per-parameter mode keeps one window each
+            assert len(windows) == (2 if kw.get("bucket_bytes") == 0 else 1), windows
         sd = opt.state_dict()
         assert set(sd.keys()) == {"state", "param_groups"}
         bf.win_free()
@@ -612,6 +619,78 @@ def checkpoint():
     w0 = bf.broadcast(model2.weight.data, 0)
     assert torch.equal(w0, model2.weight.data) and torch.equal(model2.weight.data, payload["model"]["weight"])
     bf.barrier()
+
+
+@case
+def gpu_fused_wrap_then_broadcast():
+    """The order of the reference's examples: every rank starts from its own random model, wraps the optimizer,
+    THEN broadcasts parameters and optimizer state.  The first combine must see the broadcast values on every
+    neighbor (fp32 compute: the master is written in place; bf16 compute: the shadow is), and after one step with
+    zero gradients every rank must still hold exactly the root's model."""
+    r, n, d = bf.rank(), bf.size(), dev()
+    assert d.type == "cuda"
+    bf.set_topology(tu.RingGraph(n))
+    for compute in (torch.float32, torch.bfloat16):
+        for factory in (bf.DistributedAdaptWithCombineOptimizer, bf.DistributedAdaptThenCombineOptimizer):
+            torch.manual_seed(1000 + r)                      # a different model on every rank
+            model = torch.nn.Sequential(torch.nn.Linear(32, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4)).to(d)
+            opt = factory(torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9), model, compute_dtype=compute)
+            assert hasattr(opt, "master_parameters")
+            bf.broadcast_parameters(model.state_dict(), root_rank=0)
+            bf.broadcast_optimizer_state(opt, root_rank=0)
+            root = torch.cat([v.float().reshape(-1) for v in model.state_dict().values()]).clone()
+            root0 = bf.broadcast(root, 0)
+            assert torch.equal(root, root0), "the broadcast itself did not reach this rank"
+            opt.zero_grad()
+            (model(torch.zeros(2, 32, device=d, dtype=compute)).sum() * 0.0).backward()     # zero gradients
+            opt.step()
+            torch.cuda.synchronize()
+            opt.check()
+            now = torch.cat([v.float().reshape(-1) for v in model.state_dict().values()])
+            tol = 0.0 if compute == torch.float32 else 1e-2
+            assert (now - root0).abs().max().item() <= tol + 1e-6, (compute, factory.__name__, (now - root0).abs().max().item())
+            masters = torch.cat([v.reshape(-1) for v in opt.master_parameters().values()])
+            assert (masters - root0).abs().max().item() <= tol + 1e-6
+            bf.barrier()
+
+
+@case
+def gpu_fused_dst_weights_and_hierarchical():
+    """Fused engine against the per-parameter path (fused=False) with destination weights that change every step,
+    and with hierarchical averaging over two machines."""
+    r, n, d = bf.rank(), bf.size(), dev()
+    assert d.type == "cuda"
+    bf.set_topology(tu.RingGraph(n))
+
+    def run(fused, comm, steps=4):
+        torch.manual_seed(5)
+        model = torch.nn.Linear(24, 6).to(d)
+        with torch.no_grad():
+            for p in model.parameters():
+                p.add_(0.1 * r)
+        factory = bf.DistributedAdaptWithCombineOptimizer if comm[0] == "awc" else bf.DistributedAdaptThenCombineOptimizer
+        ctype = bf.CommunicationType.hierarchical_neighbor_allreduce if comm[1] == "hier" else bf.CommunicationType.neighbor_allreduce
+        opt = factory(torch.optim.SGD(model.parameters(), lr=0.05), model, communication_type=ctype, fused=fused)
+        x = torch.randn(16, 24, generator=torch.Generator().manual_seed(r)).to(d)
+        for t in range(steps):
+            if comm[1] == "dst":
+                opt.self_weight = 0.5
+                opt.src_weights = {(r - 1) % n: 0.5}
+                opt.dst_weights = {(r + 1) % n: 0.5 + 0.25 * ((r + t) % 3)}
+            opt.zero_grad()
+            model(x).pow(2).mean().backward()
+            opt.step()
+        torch.cuda.synchronize()
+        return torch.cat([p.detach().reshape(-1) for p in model.parameters()]).clone()
+
+    kinds = [("awc", "dst"), ("atc", "dst")] if n > 1 else []
+    if bf.local_size() > 1 and bf.machine_size() > 1:
+        bf.set_machine_topology(tu.RingGraph(bf.machine_size()))
+        kinds += [("awc", "hier"), ("atc", "hier")]
+    for comm in kinds:
+        a, b = run(True, comm), run(False, comm)
+        assert (a - b).abs().max().item() < 1e-4, (comm, (a - b).abs().max().item())
+        bf.barrier()
 
 
 @case

@@ -18,14 +18,15 @@ def _need(n):
 
 
 @pytest.mark.parametrize("case", ["collectives", "neighbor_ops", "windows", "optimizers", "gpu_fused_optimizers",
-                                  "gpu_fast_path", "gpu_pair_gossip"])
+                                  "gpu_fast_path", "gpu_pair_gossip", "gpu_fused_wrap_then_broadcast",
+                                  "gpu_fused_dst_weights_and_hierarchical", "neighbor_sweeps", "win_random_p"])
 def test_two_gpus(case):
     _need(2)
     run_ranks(case, 2, gpu=True, env=NVLS_OFF, timeout=600)
 
 
 @pytest.mark.parametrize("case", ["collectives", "neighbor_ops", "windows", "gpu_fused_optimizers",
-                                  "gpu_fast_path", "gpu_pair_gossip"])
+                                  "gpu_fast_path", "gpu_pair_gossip", "gpu_fused_wrap_then_broadcast", "neighbor_sweeps"])
 def test_four_gpus(case):
     _need(4)
     run_ranks(case, 4, gpu=True, env=NVLS_OFF, timeout=600)
@@ -36,9 +37,17 @@ def test_hierarchical_four_gpus():
     run_ranks("hierarchical", 4, gpu=True, env=dict(NVLS_OFF, BLUEFOG_NODES_PER_MACHINE="2"), timeout=600)
 
 
-def test_eight_gpus_neighbor_ops():
+def test_fused_hierarchical_and_destination_weights_four_gpus():
+    _need(4)
+    run_ranks("gpu_fused_dst_weights_and_hierarchical", 4, gpu=True, env=dict(NVLS_OFF, BLUEFOG_NODES_PER_MACHINE="2"),
+              timeout=600)
+
+
+@pytest.mark.parametrize("case", ["neighbor_ops", "collectives", "windows", "gpu_fused_optimizers",
+                                  "gpu_fused_wrap_then_broadcast"])
+def test_eight_gpus(case):
     _need(8)
-    run_ranks("neighbor_ops", 8, gpu=True, env=NVLS_OFF, timeout=600)
+    run_ranks(case, 8, gpu=True, env=NVLS_OFF, timeout=600)
 
 
 def test_pattern_mismatch_times_out_with_an_error_on_gpus():

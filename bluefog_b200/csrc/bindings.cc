@@ -15,6 +15,7 @@
 #include "common/windows.h"
 #include "cuda/bn_kernels.h"
 #include "cuda/bucket.h"
+#include "cuda/combine_noalloc.h"
 #include "cuda/ce_kernels.h"
 #include "cuda/conv_tcgen05.h"
 #include "cuda/gemm_tcgen05.h"
@@ -103,6 +104,8 @@ std::unique_ptr<Channel> MakeIpcChannel(size_t half_bytes) {
   std::shared_ptr<SymmBuffer> ctrl, arena;
   ThrowIfError(AllocateIpc(&rt.control_plane(), kChanUser, rt.device(), sizeof(ChannelCtrl), &ctrl));
   ThrowIfError(AllocateIpc(&rt.control_plane(), kChanUser, rt.device(), half_bytes * 2, &arena));
+  rt.KeepUntilShutdown(ctrl);    // peers' kernels read these: they stay mapped until the barrier in Shutdown
+  rt.KeepUntilShutdown(arena);
   return std::make_unique<Channel>(ctrl, arena, half_bytes);
 }
 
@@ -356,6 +359,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_fusion_threshold", [](int64_t v) { Runtime::Get().set_fusion_threshold(v); });
   m.def("set_stall_warning_seconds", [](double s) { Runtime::Get().set_stall_warning_seconds(s); });
   m.def("kernel_launch_count", [] { return KernelLaunchCount(); });
+  // control words of the allocation-free combine's static scratch on the current device:
+  // (block_counter, calls_done, [done of each source])
+  m.def("noalloc_scratch_words", [](int n_src) {
+    unsigned int block_counter = 0;
+    unsigned long long calls_done = 0;
+    std::vector<unsigned long long> done(static_cast<size_t>(n_src > 0 ? n_src : 0));
+    cudaError_t e = bfb::NoAllocScratchRead(n_src, &block_counter, &calls_done, done.data());
+    if (e != cudaSuccess) throw std::runtime_error(std::string("noalloc_scratch_words: ") + cudaGetErrorString(e));
+    return py::make_tuple(block_counter, calls_done, done);
+  });
 
   // ---- operations --------------------------------------------------------------------------
   m.def("enqueue", [](OpSpec spec) {

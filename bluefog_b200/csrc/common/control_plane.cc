@@ -283,7 +283,8 @@ Status ControlPlane::Exchange(int channel, const std::vector<SendSpec>& sends,
   return Status::OK();
 }
 
-Status ControlPlane::AllgatherBytes(int channel, const std::string& mine, std::vector<std::string>* all) {
+Status ControlPlane::AllgatherBytes(int channel, const std::string& mine, std::vector<std::string>* all,
+                                    double timeout_s) {
   all->assign(size_, std::string());
   (*all)[rank_] = mine;
   if (size_ == 1) return Status::OK();
@@ -297,7 +298,7 @@ Status ControlPlane::AllgatherBytes(int channel, const std::string& mine, std::v
     sends.push_back({p, &my_size, sizeof(my_size)});
     recvs.push_back({p, &sizes[p], sizeof(uint64_t)});
   }
-  Status s = Exchange(channel, sends, recvs);
+  Status s = Exchange(channel, sends, recvs, timeout_s);
   if (!s.ok()) return s;
   sends.clear();
   recvs.clear();
@@ -307,12 +308,12 @@ Status ControlPlane::AllgatherBytes(int channel, const std::string& mine, std::v
     sends.push_back({p, mine.data(), mine.size()});
     recvs.push_back({p, &(*all)[p][0], static_cast<size_t>(sizes[p])});
   }
-  return Exchange(channel, sends, recvs);
+  return Exchange(channel, sends, recvs, timeout_s);
 }
 
-Status ControlPlane::Barrier(int channel) {
+Status ControlPlane::Barrier(int channel, double timeout_s) {
   std::vector<std::string> all;
-  return AllgatherBytes(channel, std::string("b"), &all);
+  return AllgatherBytes(channel, std::string("b"), &all, timeout_s);
 }
 
 Status ControlPlane::BroadcastBytes(int channel, int root, std::string* bytes) {

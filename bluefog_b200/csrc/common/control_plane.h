@@ -58,8 +58,8 @@ class ControlPlane {
                   double timeout_s = -1);
 
   // Collectives on the user/data channel built from Exchange.
-  Status AllgatherBytes(int channel, const std::string& mine, std::vector<std::string>* all);
-  Status Barrier(int channel);
+  Status AllgatherBytes(int channel, const std::string& mine, std::vector<std::string>* all, double timeout_s = -1);
+  Status Barrier(int channel, double timeout_s = -1);
   Status BroadcastBytes(int channel, int root, std::string* bytes);
 
   double default_timeout_s = 300.0;

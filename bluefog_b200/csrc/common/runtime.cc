@@ -175,6 +175,11 @@ void Runtime::Wake() {
   }
 }
 
+void Runtime::KeepUntilShutdown(std::shared_ptr<void> memory) {
+  std::lock_guard<std::mutex> g(keep_mu_);
+  keep_until_shutdown_.push_back(std::move(memory));
+}
+
 void Runtime::Shutdown() {
   if (!initialized_.load()) return;
   {
@@ -195,8 +200,23 @@ void Runtime::Shutdown() {
     cudaSetDevice(device_);
     cudaDeviceSynchronize();
   }
+  if (size_ > 1 && cp_.connected()) {
+    // Every rank's kernels have finished (device synchronised above) once all ranks are here: only then is peer-
+    // mapped memory (windows, channels, bucket arenas) unmapped.  The wait is bounded; a rank that never comes
+    // costs the others this long at exit and nothing else.
+    double limit_s = 10.0;
+    if (const char* v = std::getenv("BLUEFOG_B200_SHUTDOWN_BARRIER_SECONDS")) limit_s = std::atof(v);
+    if (limit_s > 0) {
+      Status s = cp_.Barrier(kChanData, limit_s);
+      if (!s.ok()) BFLOG(WARNING, rank_) << "shutdown barrier not completed (" << s.reason() << "); releasing peer memory anyway";
+    }
+  }
   if (windows_) {
     windows_.reset();
+  }
+  {
+    std::lock_guard<std::mutex> g(keep_mu_);
+    keep_until_shutdown_.clear();
   }
   gpu_channel_.reset();
   gpu_ctrl_.reset();

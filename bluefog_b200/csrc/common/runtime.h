@@ -82,6 +82,9 @@ class Runtime {
   int local_rank() const { return local_rank_; }
   int local_size() const { return local_size_; }
   int device() const { return device_; }
+  // Peer-mapped memory that other ranks' kernels may read (bucket arenas and their control blocks): kept mapped
+  // until Shutdown has met every other rank at a barrier, whatever the owner object's lifetime.
+  void KeepUntilShutdown(std::shared_ptr<void> memory);
   void Suspend() { suspended_.store(true); }
   void Resume() {
     suspended_.store(false);
@@ -193,6 +196,8 @@ class Runtime {
   };
   std::mutex exec_mu_;                                // one executor at a time: background loop or a caller
   std::mutex inline_mu_;
+  std::mutex keep_mu_;
+  std::vector<std::shared_ptr<void>> keep_until_shutdown_;
   std::unordered_map<int, InlineOp> inline_ops_;      // by handle
   std::unordered_map<std::string, int> inline_names_; // names in flight on the fast path
   bool inline_enabled_ = true;

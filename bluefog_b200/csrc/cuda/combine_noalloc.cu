@@ -167,6 +167,22 @@ extern "C" int bfb200_combine_noalloc(const void* self_in, const void* const* sr
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return Fail(err, err_len, 6, cudaGetErrorString(e));
   if (device < 0 || device >= kMaxDevices) return Fail(err, err_len, 6, "bfb200_combine_noalloc: device index out of range");
+  // The kernel runs on the current device with that device's copy of the scratch array: the stream has to be one
+  // of its streams, and self_in/out have to be memory the device can address (not plain host memory).
+  if (stream != nullptr && stream != cudaStreamLegacy && stream != cudaStreamPerThread) {
+    int stream_device = -1;
+    e = cudaStreamGetDevice(static_cast<cudaStream_t>(stream), &stream_device);
+    if (e != cudaSuccess) return Fail(err, err_len, 10, cudaGetErrorString(e));
+    if (stream_device != device)
+      return Fail(err, err_len, 10, "bfb200_combine_noalloc: the stream does not belong to the current device");
+  }
+  for (const void* ptr : {self_in, static_cast<const void*>(out)}) {
+    cudaPointerAttributes attr;
+    e = cudaPointerGetAttributes(&attr, ptr);
+    if (e != cudaSuccess) return Fail(err, err_len, 11, cudaGetErrorString(e));
+    if (attr.type == cudaMemoryTypeUnregistered)
+      return Fail(err, err_len, 11, "bfb200_combine_noalloc: self_in and out must be device-accessible memory");
+  }
   unsigned char* scratch = nullptr;
   {
     // Set-up, once per device, with that device current: resolve the device address of the array.
@@ -214,3 +230,25 @@ extern "C" int bfb200_combine_noalloc(const void* self_in, const void* const* sr
   if (e != cudaSuccess) return Fail(err, err_len, 9, cudaGetErrorString(e));
   return 0;
 }
+
+namespace bfb {
+
+cudaError_t NoAllocScratchRead(int n_src, unsigned int* block_counter, unsigned long long* calls_done,
+                               unsigned long long* done) {
+  if (n_src < 0 || n_src > kMaxSources) return cudaErrorInvalidValue;
+  ScratchHeader hdr;
+  cudaError_t e = cudaMemcpyFromSymbol(&hdr, g_noalloc_scratch, sizeof(hdr), 0, cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return e;
+  *block_counter = hdr.block_counter;
+  *calls_done = hdr.calls_done;
+  for (int j = 0; j < n_src; ++j) {
+    SourceRecord rec;
+    e = cudaMemcpyFromSymbol(&rec, g_noalloc_scratch, sizeof(rec), sizeof(ScratchHeader) + j * sizeof(SourceRecord),
+                             cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return e;
+    done[j] = rec.done;
+  }
+  return cudaSuccess;
+}
+
+}  // namespace bfb

@@ -26,6 +26,10 @@
 //  * all calls on one device share the array, which keeps the previous call's contents; each
 //    call clears what it needs with a stream-ordered memset.  Two calls that overlap on the
 //    GPU (different streams, no ordering between them) race on the array: order them.
+//  * the call works on the CURRENT device: the stream must be a stream of the current device (checked), self_in and
+//    out must be memory that device can address (plain host memory is rejected), and the scratch array used is the
+//    current device's copy.  Source pointers may be peer-mapped memory of other GPUs.  Set the device
+//    (cudaSetDevice) before calling, as for any kernel launch.
 //  * no cudaMalloc, cudaFree or other allocating routine (PyTorch's included) is called.
 #pragma once
 
@@ -47,4 +51,15 @@ int bfb200_combine_noalloc(const void* self_in, const void* const* src_in, const
 
 #ifdef __cplusplus
 }
+#endif
+
+#ifdef __cplusplus
+#include <cuda_runtime.h>
+namespace bfb {
+// Test helper: copies the control words of the current device's scratch array to the host (a blocking copy; it
+// allocates nothing).  After a finished call with n_src sources: block_counter == 0, calls_done == 1 and
+// done[j] == 1 for every j < n_src.
+cudaError_t NoAllocScratchRead(int n_src, unsigned int* block_counter, unsigned long long* calls_done,
+                               unsigned long long* done);
+}  // namespace bfb
 #endif

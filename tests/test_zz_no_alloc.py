@@ -61,6 +61,10 @@ def test_matches_regular_entry_point_twice_in_a_row(dtype):
         assert rc == 0, msg
         torch.cuda.synchronize()
         assert world.status(0)[0] == 0
+        # the static scratch after a finished call: arrival counter re-armed, one call counted (the array is
+        # cleared at the start of every call), every source marked consumed exactly once
+        block_counter, calls_done, done = C.noalloc_scratch_words(W - 1)
+        assert block_counter == 0 and calls_done == 1 and list(done) == [1] * (W - 1), (block_counter, calls_done, done)
         scale = max(1.0, ref.double().abs().max().item())
         assert (out.double() - ref.double()).abs().max().item() <= TOL[dtype] * scale, (dtype, call)
 
@@ -75,7 +79,23 @@ def test_rejects_what_does_not_fit():
     odd = torch.ones(63, device=dev)
     rc, msg = _call(fn, [odd, odd], [1.0], 1.0, 1.0, torch.empty(63, device=dev))
     assert rc != 0 and "multiple of 16" in msg
+    host = torch.ones(64)
+    rc, msg = _call(fn, [host, x], [1.0], 1.0, 1.0, out)
+    assert rc != 0 and "device-accessible" in msg
     # and a valid call still works afterwards
     rc, msg = _call(fn, [x, x], [2.0], 1.0, 1.0, out)
     torch.cuda.synchronize()
     assert rc == 0 and torch.allclose(out, torch.full_like(out, 3.0))
+    assert C.noalloc_scratch_words(1) == (0, 1, [1])
+
+
+def test_stream_of_another_device_is_rejected():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    C, fn = _lib()
+    x = torch.ones(64, device="cuda:0")
+    out = torch.empty(64, device="cuda:0")
+    other = torch.cuda.Stream(device=1)
+    torch.cuda.set_device(0)
+    rc, msg = _call(fn, [x, x], [1.0], 1.0, 1.0, out, other.cuda_stream)
+    assert rc != 0 and "current device" in msg

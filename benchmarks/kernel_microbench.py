@@ -4,6 +4,7 @@
   python benchmarks/kernel_microbench.py --kernel combine --numel 67108864 --dtype bfloat16
   python benchmarks/kernel_microbench.py --kernel gemm --m 8192 --n 8192 --k 8192
   python benchmarks/kernel_microbench.py --kernel conv_layers --batch 64
+  python benchmarks/kernel_microbench.py --kernel bn_layers --batch 64
 
 The multi-rank kernels run on a one-process "local world": the peers' buffers are other
 buffers of the same GPU, so the numbers are HBM-bound, not NVLink-bound; they show how close
@@ -295,15 +296,78 @@ def bench_bn(args):
             "pytorch_fwd_ms (bn, add, relu)": ms_tf}
 
 
+# (count, channels, height = width, relu, residual) of every BatchNorm of ResNet-50 (stride on the 3x3 convolution)
+RESNET50_BNS = [
+    (1, 64, 112, True, False),
+    (6, 64, 56, True, False), (3, 256, 56, True, True), (1, 256, 56, False, False),
+    (1, 128, 56, True, False), (7, 128, 28, True, False), (4, 512, 28, True, True), (1, 512, 28, False, False),
+    (1, 256, 28, True, False), (11, 256, 14, True, False), (6, 1024, 14, True, True), (1, 1024, 14, False, False),
+    (1, 512, 14, True, False), (5, 512, 7, True, False), (3, 2048, 7, True, True), (1, 2048, 7, False, False),
+]
+
+
+def bench_bn_layers(args):
+    """Forward and backward of every BatchNorm(+ReLU, +residual) shape of ResNet-50 at batch --batch, each timed as a
+    CUDA graph of --iters calls (statistics workspace cleared once per graph, as the model clears it once per step).
+    One JSON line per shape with the traffic each pass has to move and the rate it reached, and a last line with the
+    sums weighted by layer count."""
+    n = args.batch
+    tot_f = tot_b = tot_bytes_f = tot_bytes_b = 0.0
+    for count, c, hw, relu, residual in RESNET50_BNS:
+        x = torch.randn(n, c, hw, hw, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        res = torch.randn_like(x) if residual else None
+        dy = torch.randn_like(x)
+        gamma, beta = torch.ones(c, device="cuda"), torch.zeros(c, device="cuda")
+        rm, rv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+        ws = torch.zeros(args.iters + 8, 2 * c if args.bn_two_kernels else _C.bn_workspace_floats(c), device="cuda")
+        y, mean, rstd, mask = _C.bn_forward(x, res, gamma, beta, rm, rv, 1e-5, 0.1, relu)
+        calls = [0]
+
+        def slot():
+            i = calls[0] % (args.iters + 8)
+            if i == 0:
+                ws.zero_()
+            calls[0] += 1
+            return ws[i]
+
+        def fwd():
+            return _C.bn_forward(x, res, gamma, beta, rm, rv, 1e-5, 0.1, relu, slot())
+
+        def bwd():
+            return _C.bn_backward(dy, mask if relu else None, x, mean, rstd, gamma, relu, residual, slot())
+
+        calls[0] = 0
+        ms_f = timed_graph(fwd, args.iters, 0)
+        calls[0] = 0
+        ms_b = timed_graph(bwd, args.iters, 0)
+        nb = x.numel() * 2
+        bits = 1.0 / 16 if relu else 0.0
+        bytes_f = nb * (3 + (1 if residual else 0) + bits)             # read x twice (+ residual), write y (+ bits)
+        bytes_b = nb * (5 + (1 if residual else 0) + 2 * bits)         # read dy, x twice (+ bits), write dx (+ dresidual)
+        tot_f += count * ms_f
+        tot_b += count * ms_b
+        tot_bytes_f += count * bytes_f
+        tot_bytes_b += count * bytes_b
+        print(json.dumps({"bn": [count, c, hw, relu, residual], "mbytes": round(nb / 1e6, 1), "fwd_ms": round(ms_f, 4),
+                          "bwd_ms": round(ms_b, 4), "fwd_gbs": round(bytes_f / ms_f / 1e6), "bwd_gbs": round(bytes_b / ms_b / 1e6),
+                          "fwd_floor_ms": round(bytes_f / PEAKS["hbm_gbs"] / 1e6, 4),
+                          "bwd_floor_ms": round(bytes_b / PEAKS["hbm_gbs"] / 1e6, 4)}), flush=True)
+    return {"kernel": "all ResNet-50 BatchNorm layers, batch %d: sum over layers (ms)" % n, "fwd_ms": round(tot_f, 3),
+            "bwd_ms": round(tot_b, 3), "fwd_floor_ms_at_measured_hbm": round(tot_bytes_f / PEAKS["hbm_gbs"] / 1e6, 3),
+            "bwd_floor_ms_at_measured_hbm": round(tot_bytes_b / PEAKS["hbm_gbs"] / 1e6, 3)}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", required=True, choices=["bucket", "combine", "gemm", "bn", "conv", "conv_layers", "wgrad", "ln"])
+    ap.add_argument("--kernel", required=True, choices=["bucket", "combine", "gemm", "bn", "bn_layers", "conv", "conv_layers", "wgrad", "ln"])
     ap.add_argument("--ksize", type=int, default=3)
     ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--ln-rows", type=int, default=65536)
     ap.add_argument("--conv-shape", type=int, nargs=5, default=[64, 64, 64, 56, 56], metavar=("N", "CIN", "COUT", "H", "W"))
     ap.add_argument("--bn-shape", type=int, nargs=4, default=[64, 256, 56, 56])
+    ap.add_argument("--bn-two-kernels", action="store_true",
+                    help="bn_layers: no barrier word behind the sums, so every pass is statistics kernel + apply kernel")
     ap.add_argument("--numel", type=int, default=64 * 1024 * 1024)
     ap.add_argument("--dtype", default="float32")
     ap.add_argument("--exchange", default="float32", choices=["float32", "bfloat16"])
@@ -316,7 +380,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
     torch.cuda.set_device(0)
-    out = {"bucket": bench_bucket, "combine": bench_combine, "gemm": bench_gemm, "bn": bench_bn, "conv": bench_conv, "conv_layers": bench_conv_layers, "wgrad": bench_wgrad,
+    out = {"bucket": bench_bucket, "combine": bench_combine, "gemm": bench_gemm, "bn": bench_bn, "bn_layers": bench_bn_layers, "conv": bench_conv, "conv_layers": bench_conv_layers, "wgrad": bench_wgrad,
            "ln": bench_ln}[args.kernel](args)
     print(json.dumps(out), flush=True)
 

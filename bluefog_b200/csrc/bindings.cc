@@ -481,6 +481,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            x.is_contiguous(at::MemoryFormat::ChannelsLast) &&
            BnShapeSupported(x.numel() / std::max<int64_t>(x.size(1), 1), static_cast<int>(x.size(1)));
   });
+  // zeroed fp32 words a BatchNorm pass over C channels wants for its one-launch form (accumulator copies + barrier)
+  m.def("bn_workspace_floats", [](int C) { return BnSumCopies(C) * 2 * C + 16; });
   m.def("bn_forward", [](at::Tensor x, c10::optional<at::Tensor> residual, at::Tensor gamma, at::Tensor beta,
                          c10::optional<at::Tensor> running_mean, c10::optional<at::Tensor> running_var, double eps,
                          double momentum, bool relu, c10::optional<at::Tensor> zeroed_sums, bool stats_ready) {
@@ -506,8 +508,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                   zeroed_sums->numel() >= 2 * C, "zeroed_sums must be a contiguous fp32 CUDA tensor of 2*C elements");
       sums = *zeroed_sums;
     } else {
-      sums = at::zeros({2 * C}, fopts);
+      sums = at::zeros({BnSumCopies(C) * 2 * C + 16}, fopts);
     }
+    // room for several sets of accumulators and one more word lets the pass run as a single cooperative launch
+    const int copies = static_cast<int>(std::min<int64_t>(BnSumCopies(C), (sums.numel() - 1) / (2 * C)));
+    at::Tensor& status = GemmStatusWord(x);
     at::Tensor save_mean = at::empty({C}, fopts), save_rstd = at::empty({C}, fopts);
     const void* res = nullptr;
     if (residual.has_value() && residual->defined()) {
@@ -527,7 +532,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                     sums.data_ptr<float>(), gamma.data_ptr(), beta.data_ptr(),
                                     rm, rv, save_mean.data_ptr<float>(), save_rstd.data_ptr<float>(), R, C,
                                     static_cast<float>(eps), static_cast<float>(momentum), relu ? 1 : 0, pbf16 ? 1 : 0,
-                                    CurrentStream(x.get_device()), stats_ready ? 1 : 0);
+                                    CurrentStream(x.get_device()), stats_ready ? 1 : 0, copies,
+                                    reinterpret_cast<unsigned int*>(status.data_ptr<int>()));
     TORCH_CHECK(e == cudaSuccess, "bn_forward launch failed: ", cudaGetErrorString(e));
     return std::make_tuple(y, save_mean, save_rstd, mask);
   }, py::arg("x"), py::arg("residual"), py::arg("gamma"), py::arg("beta"), py::arg("running_mean"),
@@ -544,9 +550,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     at::Tensor dx = at::empty_like(x);
     at::Tensor dres = want_dres ? at::empty_like(x) : at::Tensor();
     at::Tensor sums = (zeroed_sums.has_value() && zeroed_sums->defined())
-                          ? *zeroed_sums : at::zeros({2 * C}, x.options().dtype(at::kFloat));
+                          ? *zeroed_sums : at::zeros({BnSumCopies(C) * 2 * C + 16}, x.options().dtype(at::kFloat));
     TORCH_CHECK(sums.is_cuda() && sums.scalar_type() == at::kFloat && sums.is_contiguous() && sums.numel() >= 2 * C,
                 "zeroed_sums must be a contiguous fp32 CUDA tensor of 2*C elements");
+    const int copies = static_cast<int>(std::min<int64_t>(BnSumCopies(C), (sums.numel() - 1) / (2 * C)));
+    at::Tensor& status = GemmStatusWord(x);
     at::Tensor dgamma = at::empty_like(gamma), dbeta = at::empty_like(gamma);
     const void* mptr = nullptr;
     if (relu) {
@@ -558,7 +566,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                      want_dres ? dres.data_ptr() : nullptr, sums.data_ptr<float>(),
                                      save_mean.data_ptr<float>(), save_rstd.data_ptr<float>(), gamma.data_ptr(),
                                      dgamma.data_ptr(), dbeta.data_ptr(), R, C, relu ? 1 : 0, pbf16 ? 1 : 0,
-                                     CurrentStream(x.get_device()));
+                                     CurrentStream(x.get_device()), copies,
+                                     reinterpret_cast<unsigned int*>(status.data_ptr<int>()));
     TORCH_CHECK(e == cudaSuccess, "bn_backward launch failed: ", cudaGetErrorString(e));
     return std::make_tuple(dx, dres, dgamma, dbeta);
   }, py::arg("dy"), py::arg("mask"), py::arg("x"), py::arg("save_mean"), py::arg("save_rstd"), py::arg("gamma"),

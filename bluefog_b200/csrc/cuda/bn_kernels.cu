@@ -12,6 +12,8 @@
 
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 #include "comm_kernels.h"
 
 namespace bfb {
@@ -60,22 +62,25 @@ __device__ __forceinline__ ReduceGeom reduce_geom(int C) {
   return g;
 }
 
-// Adds the per-thread partials of one block into sums[c] and sums[C + c] (c = channels of this block).
+// Adds the per-thread partials of one block into sums[c] and sums[C + c] (c = channels of this block): every thread
+// parks its 16 values in shared memory, thread c adds up column c over the row lanes and issues one global atomic
+// (shared-memory fp32 atomics are compare-and-swap loops and crawl when many warps add to the same words).
 __device__ __forceinline__ void flush_partials(const float* s1, const float* s2, int lg, int cgb, int c0, int C,
                                                float* sums) {
-  __shared__ float sh[2 * 256];           // 32 groups x 8 channels, two statistics
+  __shared__ float sh[kThreads * 16];
   const int nch = cgb * 8;
-  for (int c = threadIdx.x; c < 2 * nch; c += blockDim.x) sh[c] = 0.f;
-  __syncthreads();
+  const int rl = threadIdx.x / cgb, RL = kThreads / cgb;
+  float* row = sh + size_t(rl) * 2 * nch;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    atomicAdd(&sh[lg * 8 + i], s1[i]);
-    atomicAdd(&sh[nch + lg * 8 + i], s2[i]);
+    row[lg * 8 + i] = s1[i];
+    row[nch + lg * 8 + i] = s2[i];
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < nch; c += blockDim.x) {
-    atomicAdd(&sums[c0 + c], sh[c]);
-    atomicAdd(&sums[C + c0 + c], sh[nch + c]);
+  for (int c = threadIdx.x; c < 2 * nch; c += blockDim.x) {
+    float t = 0.f;
+    for (int r = 0; r < RL; ++r) t += sh[size_t(r) * 2 * nch + c];
+    atomicAdd(&sums[c < nch ? c0 + c : C + c0 + (c - nch)], t);
   }
 }
 
@@ -356,6 +361,353 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(const BnBwdApply
   }
 }
 
+// ------------------------------------------------------------------------------------------------------ //
+// One-launch variants for activations that fit on the chip.
+//
+// Most BatchNorm layers of a ResNet see a few MB: two dependent kernels per pass then cost mostly their launch
+// and a handful of dependent memory round trips each (14 us per pass for a 3 MB tensor, against 1.5 us of
+// traffic).  These kernels do the whole pass in one cooperative launch with one block per SM: phase 1 reads the
+// block's rows once, keeps them in shared memory and adds the block's partial sums to the global accumulators;
+// after a grid-wide barrier phase 2 normalises the rows out of shared memory.  The activation is read once
+// instead of twice and nothing waits for a second launch.  The barrier is a counter in the zeroed workspace
+// (one word after the 2*C sums); its wait is bounded and ends in the caller's status word.
+// ------------------------------------------------------------------------------------------------------ //
+constexpr int kFusedThreads = 512;
+constexpr size_t kFusedStageLimit = 176 * 1024;     // dynamic shared memory for staged rows, per block
+constexpr unsigned long long kBarrierLimitNs = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long bn_now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// All blocks of a cooperative grid meet here once.  Returns false (in every thread of the block) when the wait
+// ran out; the caller then leaves without touching its outputs.
+__device__ __forceinline__ bool grid_barrier_once(unsigned int* counter, unsigned int* status) {
+  __shared__ int ok_s;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    atomicAdd(counter, 1u);
+    bool ok = true;
+    const unsigned long long t0 = bn_now_ns();
+    unsigned spins = 0;
+    for (;;) {
+      unsigned v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+      if (v >= gridDim.x) break;
+      if ((++spins & 63u) == 0 && bn_now_ns() - t0 > kBarrierLimitNs) { ok = false; break; }
+    }
+    if (!ok && status != nullptr) atomicExch(status, 1u);
+    ok_s = ok ? 1 : 0;
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+// Adds the per-thread partials of a block that covers ALL channels into one copy of the accumulators.  Every thread
+// parks its 16 partial sums in shared memory (row lane x channel: kFusedThreads * 16 floats), then thread c adds up
+// column c and issues one global atomic: no shared-memory atomics, whose fp32 form is a compare-and-swap loop that
+// crawls when sixteen warps add to the same words.
+__device__ __forceinline__ void flush_partials_all(const float* s1, const float* s2, int g, int rl, int CG, int C, float* sh,
+                                                   float* sums, int copies) {
+  const int RL = kFusedThreads / CG;
+  float* row = sh + size_t(rl) * 2 * C;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    row[g * 8 + i] = s1[i];
+    row[C + g * 8 + i] = s2[i];
+  }
+  __syncthreads();
+  // blocks spread their additions over `copies` sets of accumulators: same-address atomics serialise in L2
+  float* mine = sums + size_t(blockIdx.x % copies) * 2 * C;
+  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) {
+    float t = 0.f;
+    for (int r = 0; r < RL; ++r) t += sh[size_t(r) * 2 * C + c];
+    atomicAdd(&mine[c], t);
+  }
+}
+
+// After the barrier: totals of all copies into shared memory, once per block (every thread then reads its channels
+// from there instead of all threads of the grid reading the same few lines of L2).
+__device__ __forceinline__ void gather_totals(const float* sums, int C, int copies, float* sh) {
+  __syncthreads();           // the partial sums parked in sh have been consumed by every thread
+  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) {
+    float t = 0.f;
+    for (int k = 0; k < copies; ++k) t += __ldcg(&sums[size_t(k) * 2 * C + c]);
+    sh[c] = t;
+  }
+  __syncthreads();
+}
+
+#ifdef BN_TRACE
+__device__ unsigned long long g_bn_trace[160][8];
+#define BTRACE(i) do { if (threadIdx.x == 0) g_bn_trace[blockIdx.x][i] = bn_now_ns(); } while (0)
+#else
+#define BTRACE(i) do {} while (0)
+#endif
+
+__global__ void __launch_bounds__(kFusedThreads, 1) bn_fwd_fused_kernel(const BnApplyParams p, float* __restrict__ sums,
+                                                                       unsigned int* barrier, unsigned int* status,
+                                                                       int copies) {
+  extern __shared__ uint4 staged[];
+  __shared__ float sh[kFusedThreads * 16];       // partial sums of every thread, later the totals (2*C values)
+  const int C = p.C, CG = C >> 3;
+  const int g = threadIdx.x % CG, rl = threadIdx.x / CG, RL = kFusedThreads / CG;
+  const long long chunk = (p.R + gridDim.x - 1) / gridDim.x;
+  const long long r0 = (long long)blockIdx.x * chunk;
+  const long long r1 = r0 + chunk < p.R ? r0 + chunk : p.R;
+  float pivot[8], s1[8], s2[8], ga[8], be[8];
+  BTRACE(0);
+  unpack8(*reinterpret_cast<const uint4*>(p.x + g * 8), pivot);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {                  // needed after the barrier only: fetched while the rows stream in
+    ga[i] = load_param(p.gamma, g * 8 + i, p.param_bf16);
+    be[i] = load_param(p.beta, g * 8 + i, p.param_bf16);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s1[i] = s2[i] = 0.f;
+  constexpr int U = 4;
+  for (long long r = r0 + rl; r < r1; r += (long long)U * RL) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r + (long long)u * RL;
+      if (row < r1) v[u] = *reinterpret_cast<const uint4*>(p.x + row * C + g * 8);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r + (long long)u * RL;
+      if (row >= r1) continue;
+      staged[(row - r0) * CG + g] = v[u];
+      float f[8];
+      unpack8(v[u], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float d = f[i] - pivot[i];
+        s1[i] += d;
+        s2[i] += d * d;
+      }
+    }
+  }
+  BTRACE(1);
+  flush_partials_all(s1, s2, g, rl, CG, C, sh, sums, copies);
+  BTRACE(2);
+  if (!grid_barrier_once(barrier, status)) return;
+  BTRACE(3);
+  gather_totals(sums, C, copies, sh);
+
+  float scale[8], shift[8];
+  const float inv_r = 1.f / (float)p.R;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = g * 8 + i;
+    const float m1 = sh[c] * inv_r;
+    const float var = fmaxf(sh[C + c] * inv_r - m1 * m1, 0.f);
+    const float mean = pivot[i] + m1;
+    const float rstd = rsqrtf(var + p.eps);
+    scale[i] = ga[i] * rstd;
+    shift[i] = be[i] - mean * scale[i];
+    if (blockIdx.x == 0 && rl == 0) {
+      p.save_mean[c] = mean;
+      p.save_rstd[c] = rstd;
+      if (p.running_mean != nullptr) {
+        const float unbiased = p.R > 1 ? var * (float)p.R / (float)(p.R - 1) : var;
+        p.running_mean[c] = (1.f - p.momentum) * p.running_mean[c] + p.momentum * mean;
+        p.running_var[c] = (1.f - p.momentum) * p.running_var[c] + p.momentum * unbiased;
+      }
+    }
+  }
+  BTRACE(4);
+  for (long long r = r0 + rl; r < r1; r += (long long)U * RL) {
+    uint4 vr[U];
+    if (p.residual != nullptr) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long row = r + (long long)u * RL;
+        if (row < r1) vr[u] = *reinterpret_cast<const uint4*>(p.residual + row * C + g * 8);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r + (long long)u * RL;
+      if (row >= r1) continue;
+      const long long idx = row * CG + g;
+      float f[8];
+      unpack8(staged[(row - r0) * CG + g], f);
+      if (p.residual != nullptr) {
+        float rr[8];
+        unpack8(vr[u], rr);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = f[i] * scale[i] + shift[i] + rr[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = f[i] * scale[i] + shift[i];
+      }
+      if (p.relu) {
+        unsigned bits = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          bits |= (f[i] > 0.f ? 1u : 0u) << i;
+          f[i] = fmaxf(f[i], 0.f);
+        }
+        p.mask[idx] = (unsigned char)bits;
+      }
+      *reinterpret_cast<uint4*>(p.y + idx * 8) = pack8(f);
+    }
+  }
+  BTRACE(5);
+}
+
+// Backward in one launch: phase 1 reads dy, x and the ReLU bits once, keeps x (and, when it fits, the masked
+// gradient dz) in shared memory and reduces sum(dz), sum(dz * xhat); phase 2 writes dx (and dresidual).
+__global__ void __launch_bounds__(kFusedThreads, 1) bn_bwd_fused_kernel(const BnBwdApplyParams p, float* __restrict__ sums,
+                                                                       unsigned int* barrier, unsigned int* status,
+                                                                       int stage_dz, int copies) {
+  extern __shared__ uint4 staged[];
+  __shared__ float sh[kFusedThreads * 16];
+  const int C = p.C, CG = C >> 3;
+  const int g = threadIdx.x % CG, rl = threadIdx.x / CG, RL = kFusedThreads / CG;
+  const long long chunk = (p.R + gridDim.x - 1) / gridDim.x;
+  const long long r0 = (long long)blockIdx.x * chunk;
+  const long long r1 = r0 + chunk < p.R ? r0 + chunk : p.R;
+  uint4* staged_dz = staged + chunk * CG;
+  float mean[8], rstd[8], s1[8], s2[8], ga[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    mean[i] = p.save_mean[g * 8 + i];
+    rstd[i] = p.save_rstd[g * 8 + i];
+    ga[i] = load_param(p.gamma, g * 8 + i, p.param_bf16);
+    s1[i] = s2[i] = 0.f;
+  }
+  constexpr int U = 4;
+  for (long long r = r0 + rl; r < r1; r += (long long)U * RL) {
+    uint4 a[U], b[U];
+    unsigned m[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r + (long long)u * RL;
+      if (row < r1) {
+        const long long off = row * C + g * 8;
+        a[u] = *reinterpret_cast<const uint4*>(p.dy + off);
+        b[u] = *reinterpret_cast<const uint4*>(p.x + off);
+        m[u] = p.relu ? p.mask[row * CG + g] : 0xffu;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r + (long long)u * RL;
+      if (row >= r1) continue;
+      float fd[8], fx[8];
+      unpack8(a[u], fd);
+      unpack8(b[u], fx);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (!((m[u] >> i) & 1u)) fd[i] = 0.f;
+        s1[i] += fd[i];
+        s2[i] += fd[i] * (fx[i] - mean[i]) * rstd[i];
+      }
+      staged[(row - r0) * CG + g] = b[u];
+      if (stage_dz) staged_dz[(row - r0) * CG + g] = pack8(fd);
+    }
+  }
+  flush_partials_all(s1, s2, g, rl, CG, C, sh, sums, copies);
+  if (!grid_barrier_once(barrier, status)) return;
+  gather_totals(sums, C, copies, sh);
+
+  const float inv_r = 1.f / (float)p.R;
+  float k0[8], k1[8], k2[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = g * 8 + i;
+    const float t1 = sh[c], t2 = sh[C + c];
+    k0[i] = ga[i] * rstd[i];         // dx = k0 * (dz - k1 - xhat * k2)
+    k1[i] = t1 * inv_r;
+    k2[i] = t2 * inv_r;
+    if (blockIdx.x == 0 && rl == 0) {
+      store_param(p.dgamma, c, p.param_bf16, t2);
+      store_param(p.dbeta, c, p.param_bf16, t1);
+    }
+  }
+  for (long long r = r0 + rl; r < r1; r += (long long)U * RL) {
+    uint4 a[U];
+    unsigned m[U];
+    if (!stage_dz) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long row = r + (long long)u * RL;
+        if (row < r1) {
+          a[u] = *reinterpret_cast<const uint4*>(p.dy + row * C + g * 8);
+          m[u] = p.relu ? p.mask[row * CG + g] : 0xffu;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long row = r + (long long)u * RL;
+      if (row >= r1) continue;
+      const long long idx = row * CG + g;
+      float fd[8], fx[8], o[8];
+      unpack8(staged[(row - r0) * CG + g], fx);
+      if (stage_dz) {
+        unpack8(staged_dz[(row - r0) * CG + g], fd);
+      } else {
+        unpack8(a[u], fd);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (!((m[u] >> i) & 1u)) fd[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = k0[i] * (fd[i] - k1[i] - (fx[i] - mean[i]) * rstd[i] * k2[i]);
+      *reinterpret_cast<uint4*>(p.dx + idx * 8) = pack8(o);
+      if (p.dres != nullptr) *reinterpret_cast<uint4*>(p.dres + idx * 8) = pack8(fd);
+    }
+  }
+}
+
+int FusedGrid() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0, coop = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (!coop || sms <= 0) sms = -1;
+    static const bool off = [] { const char* e = std::getenv("BLUEFOG_B200_BN_FUSED"); return e != nullptr && e[0] == '0'; }();
+    if (off) sms = -1;
+  }
+  return sms;
+}
+
+// Blocks of the one-launch form: every SM for activations of 7 MB and more, fewer for smaller ones (about 48 KB
+// of rows per block), because what a small pass costs is the barrier and the contention on the accumulators.
+int FusedBlocks(long long R, int C, int sms) {
+  if (sms <= 0) return 0;
+  long long blocks = (R * C * 2 + 48 * 1024 - 1) / (48 * 1024);
+  if (blocks < 8) blocks = 8;
+  if (blocks > sms) blocks = sms;
+  return static_cast<int>(blocks);
+}
+
+// Shared memory one block needs to keep `tensors` copies of its rows; 0 when the one-launch form does not apply.
+size_t FusedStageBytes(long long R, int C, int tensors, int grid) {
+  if (grid <= 0 || (kFusedThreads % (C >> 3)) != 0) return 0;
+  const long long chunk = (R + grid - 1) / grid;
+  const size_t bytes = size_t(chunk) * C * 2 * tensors;
+  return bytes <= kFusedStageLimit ? bytes : 0;
+}
+
+template <typename K>
+cudaError_t LaunchCooperative(K kernel, int grid, size_t smem, void** args, cudaStream_t stream, size_t* attr_bytes) {
+  if (smem > *attr_bytes) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kFusedStageLimit));
+    if (e != cudaSuccess) return e;
+    *attr_bytes = kFusedStageLimit;
+  }
+  return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3(grid), dim3(kFusedThreads), args, smem, stream);
+}
+
 dim3 ReduceGrid(long long R, int C) {
   const int CG = C >> 3;
   const int cgb = CG < 32 ? CG : 32;
@@ -377,6 +729,11 @@ int ApplyGrid(long long R, int C) {
 
 }  // namespace
 
+int BnSumCopies(int C) {
+  int k = 2048 / C;
+  return k < 1 ? 1 : (k > 8 ? 8 : k);
+}
+
 bool BnShapeSupported(long long R, int C) {
   const int CG = C >> 3;
   return R > 0 && C >= 8 && C <= kMaxC && (C % 8) == 0 && (kThreads % CG) == 0;
@@ -385,16 +742,28 @@ bool BnShapeSupported(long long R, int C) {
 cudaError_t LaunchBnForward(const void* x, const void* residual, void* y, void* mask, float* sums, const void* gamma, const void* beta,
                             float* running_mean, float* running_var, float* save_mean, float* save_rstd, long long R,
                             int C, float eps, float momentum, int relu, int param_bf16, cudaStream_t stream,
-                            int stats_ready) {
+                            int stats_ready, int sum_copies, unsigned int* status) {
   if (!BnShapeSupported(R, C) || (relu && mask == nullptr)) return cudaErrorInvalidValue;
-  if (!stats_ready) {
-    bn_stats_kernel<<<ReduceGrid(R, C), kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), R, C, sums);
-    CountKernelLaunch();
-  }
   BnApplyParams p{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
                   static_cast<__nv_bfloat16*>(y), static_cast<unsigned char*>(mask), sums, gamma, beta, running_mean,
                   running_var, save_mean, save_rstd,
                   R, C, relu, param_bf16, eps, momentum, stats_ready};
+  if (!stats_ready && sum_copies >= 1) {
+    const int grid = FusedBlocks(R, C, FusedGrid());
+    const size_t smem = FusedStageBytes(R, C, 1, grid);
+    if (smem != 0) {
+      static size_t attr_bytes = 0;
+      unsigned int* barrier = reinterpret_cast<unsigned int*>(sums + size_t(sum_copies) * 2 * C);
+      void* args[] = {&p, &sums, &barrier, &status, &sum_copies};
+      cudaError_t e = LaunchCooperative(bn_fwd_fused_kernel, grid, smem, args, stream, &attr_bytes);
+      CountKernelLaunch();
+      return e != cudaSuccess ? e : cudaGetLastError();
+    }
+  }
+  if (!stats_ready) {
+    bn_stats_kernel<<<ReduceGrid(R, C), kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), R, C, sums);
+    CountKernelLaunch();
+  }
   bn_apply_kernel<<<ApplyGrid(R, C), kThreads, 0, stream>>>(p);
   CountKernelLaunch();
   return cudaGetLastError();
@@ -402,16 +771,34 @@ cudaError_t LaunchBnForward(const void* x, const void* residual, void* y, void* 
 
 cudaError_t LaunchBnBackward(const void* dy, const void* mask, const void* x, void* dx, void* dres, float* sums,
                              const float* save_mean, const float* save_rstd, const void* gamma, void* dgamma,
-                             void* dbeta, long long R, int C, int relu, int param_bf16, cudaStream_t stream) {
+                             void* dbeta, long long R, int C, int relu, int param_bf16, cudaStream_t stream,
+                             int sum_copies, unsigned int* status) {
   if (!BnShapeSupported(R, C) || (relu && mask == nullptr)) return cudaErrorInvalidValue;
-  bn_bwd_reduce_kernel<<<ReduceGrid(R, C), kThreads, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(dy), static_cast<const unsigned char*>(mask), static_cast<const __nv_bfloat16*>(x),
-      save_mean, save_rstd, R, C, relu, sums);
-  CountKernelLaunch();
   BnBwdApplyParams p{static_cast<const __nv_bfloat16*>(dy), static_cast<const unsigned char*>(mask),
                      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(dx),
                      static_cast<__nv_bfloat16*>(dres), sums, save_mean, save_rstd, gamma, dgamma, dbeta, R, C, relu,
                      param_bf16};
+  if (sum_copies >= 1) {
+    const int grid = FusedBlocks(R, C, FusedGrid());
+    unsigned int* barrier = reinterpret_cast<unsigned int*>(sums + size_t(sum_copies) * 2 * C);
+    int stage_dz = 1;
+    size_t smem = FusedStageBytes(R, C, 2, grid);
+    if (smem == 0) {
+      stage_dz = 0;                      // x stays on the chip, dy and the bits are read again (out of L2)
+      smem = FusedStageBytes(R, C, 1, grid);
+    }
+    if (smem != 0) {
+      static size_t attr_bytes = 0;
+      void* args[] = {&p, &sums, &barrier, &status, &stage_dz, &sum_copies};
+      cudaError_t e = LaunchCooperative(bn_bwd_fused_kernel, grid, smem, args, stream, &attr_bytes);
+      CountKernelLaunch();
+      return e != cudaSuccess ? e : cudaGetLastError();
+    }
+  }
+  bn_bwd_reduce_kernel<<<ReduceGrid(R, C), kThreads, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const unsigned char*>(mask), static_cast<const __nv_bfloat16*>(x),
+      save_mean, save_rstd, R, C, relu, sums);
+  CountKernelLaunch();
   bn_bwd_apply_kernel<<<ApplyGrid(R, C), kThreads, 0, stream>>>(p);
   CountKernelLaunch();
   return cudaGetLastError();

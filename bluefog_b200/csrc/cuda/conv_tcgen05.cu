@@ -638,6 +638,15 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+#ifdef BFB_WGRAD_TRACE
+__device__ unsigned long long g_wgrad_trace[160][16];
+#define WTRACE(i) do { g_wgrad_trace[blockIdx.x][i] = now_ns(); } while (0)
+#define WTRACE_ADD(i, v) do { g_wgrad_trace[blockIdx.x][i] += (v); } while (0)
+#else
+#define WTRACE(i) do {} while (0)
+#define WTRACE_ADD(i, v) do {} while (0)
+#endif
+
 template <int BN_>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_x, const WgradGeom g,
@@ -671,6 +680,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
   const uint32_t box_bytes = uint32_t(positions) * 128u;
 
   if (threadIdx.x == 0) {
+    WTRACE(0);
 #pragma unroll
     for (int i = 0; i < kConvMaxTaps; ++i) {
       tap_dh_s[i] = g.dh[i];
@@ -695,6 +705,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_s;
+  if (threadIdx.x == 0) WTRACE(1);
 
   // item -> output tile (co0, ci0, first tap of its group) and its share of the patches
   auto decode = [&](int item, int& co0, int& ci0, int& t0, int& t1, int& p0, int& p1, int& tile_id) {
@@ -736,7 +747,14 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
           int n0, h0, w0;
           patch_coords(p, n0, h0, w0);
           const int s = it % S;
+#ifdef BFB_WGRAD_TRACE
+          const unsigned long long tw0 = now_ns();
+#endif
           if (!mbar_wait(smem_u32(&empty[s]), ((it / S) & 1) ^ 1, failed)) { ok = false; break; }
+#ifdef BFB_WGRAD_TRACE
+          WTRACE_ADD(10, now_ns() - tw0);
+          if (it == 0) WTRACE(2);
+#endif
           const uint32_t bar = smem_u32(&full[s]);
           unsigned char* stage = smem + size_t(s) * stage_bytes;
           mbar_expect_tx(bar, uint32_t(boxes_a + (t1 - t0) * boxes_b) * box_bytes);
@@ -750,6 +768,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
           armed = it + 1;
         }
       }
+      WTRACE(3);
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -767,7 +786,14 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
                                (uint32_t(BM >> 4) << 24);
         for (int p = p0; p < p1; ++p, ++it) {
           const int s = it % S;
+#ifdef BFB_WGRAD_TRACE
+          const unsigned long long tw0 = now_ns();
+#endif
           if (!mbar_wait(smem_u32(&full[s]), (it / S) & 1, failed)) { ok = false; break; }
+#ifdef BFB_WGRAD_TRACE
+          WTRACE_ADD(11, now_ns() - tw0);
+          if (it == 0) WTRACE(4);
+#endif
           const uint32_t stage = smem_u32(smem + size_t(s) * stage_bytes);
           const uint64_t adesc = make_desc_mn(stage, box_stride, 1024);
           const uint64_t bdesc = make_desc_mn(stage + uint32_t(g.boxes_a) * box_stride, box_stride, 1024);
@@ -777,6 +803,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
           umma_commit(smem_u32(&empty[s]));
         }
         if (ok) umma_commit(smem_u32(acc_full));
+        WTRACE(5);
       }
     }
   } else {
@@ -792,6 +819,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
       epilogue_bar();
       if (!*reinterpret_cast<volatile int*>(&go_s)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (leader) WTRACE(6);
       const int co = co0 + q * 32 + lane;
       const bool row_ok = co < g.Cout;
       for (int t = t0; t < t1; ++t) {
@@ -828,6 +856,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(acc_empty)) : "memory");
+      if (leader) WTRACE(7);
       if (g.splits > 1) {
         // the CTA that adds the last share of this tile turns the fp32 sums into the bf16 filter gradient
         __threadfence();
@@ -871,6 +900,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
           if (leader) counters[tile_id] = 0u;
         }
         epilogue_bar();      // ticket_s is rewritten by the next item
+        if (leader) WTRACE(8);
       }
     }
   }
@@ -886,6 +916,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(g.tmem_cols) : "memory");
   }
+  if (threadIdx.x == 0) WTRACE(9);
   if (threadIdx.x == 0 && failed_s && status != nullptr) atomicExch(status, 1u);
 }
 

@@ -78,7 +78,8 @@ def take_sums(device, channels):
 class _BnActFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu, stats):
-        c2 = 2 * x.shape[1]
+        # accumulators (several copies for few channels) and a zeroed word for the barrier of the one-launch kernels
+        c2 = _b.native.bn_workspace_floats(x.shape[1]) if hasattr(_b.native, "bn_workspace_floats") else 2 * x.shape[1]
         if stats is not None:
             fwd_sums = stats
         else:

@@ -59,10 +59,40 @@ def _case(N, C, H, W, relu, with_res, param_dtype):
     assert int(bn.num_batches_tracked) == 1
 
 
-@pytest.mark.parametrize("N,C,H,W", [(4, 64, 56, 56), (8, 256, 14, 14), (2, 2048, 7, 7), (3, 128, 9, 5), (64, 64, 112, 112)])
+# sizes on both sides of the limits of the one-launch kernels: rows of x (and of dz) kept in shared memory, rows of x
+# only (25.7 MB), and the two-kernel form (102.8 MB)
+@pytest.mark.parametrize("N,C,H,W", [(4, 64, 56, 56), (8, 256, 14, 14), (2, 2048, 7, 7), (3, 128, 9, 5), (64, 64, 112, 112),
+                                     (64, 64, 56, 56), (64, 128, 28, 28), (1, 8, 3, 3)])
 @pytest.mark.parametrize("relu,with_res", [(True, False), (True, True), (False, False)])
 def test_fused_bn_matches_pytorch(N, C, H, W, relu, with_res):
     _case(N, C, H, W, relu, with_res, torch.float32)
+
+
+@pytest.mark.parametrize("N,C,H,W", [(64, 512, 7, 7), (64, 256, 14, 14), (64, 1024, 14, 14)])
+def test_one_launch_and_two_kernel_forms_agree(N, C, H, W):
+    """The same layer with a barrier word behind the sums (one cooperative launch per pass) and without (statistics
+    kernel + apply kernel): same results up to the order of the fp32 sums, and the launch counts say which ran."""
+    from bluefog_b200 import _C
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(C)
+    x = (torch.randn(N, C, H, W, device=dev) + 0.3).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    res = torch.randn_like(x)
+    dy = torch.randn_like(x)
+    gamma, beta = torch.rand(C, device=dev) + 0.5, torch.randn(C, device=dev)
+    outs = []
+    for words in (_C.bn_workspace_floats(C), 2 * C + 1, 2 * C):
+        before = _C.kernel_launch_count()
+        y, mean, rstd, mask = _C.bn_forward(x, res, gamma, beta, None, None, 1e-5, 0.1, True, torch.zeros(words, device=dev))
+        dx, dres, dgamma, dbeta = _C.bn_backward(dy, mask, x, mean, rstd, gamma, True, True, torch.zeros(words, device=dev))
+        torch.cuda.synchronize()
+        assert _C.kernel_launch_count() - before == (2 if words > 2 * C else 4)
+        assert _C.gemm_status() == 0
+        outs.append((y, mean, rstd, dx, dres, dgamma, dbeta))
+    for a, b in list(zip(outs[0], outs[2])) + list(zip(outs[1], outs[2])):
+        # an activation within rounding distance of zero may get a different ReLU bit from differently ordered sums
+        scale = max(1.0, b.float().abs().max().item())
+        bad = ((a.float() - b.float()).abs() > 2e-2 * scale).float().mean().item()
+        assert bad <= 1e-5, bad
 
 
 def test_fused_bn_with_bf16_parameters():

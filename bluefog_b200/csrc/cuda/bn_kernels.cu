@@ -406,36 +406,62 @@ __device__ __forceinline__ bool grid_barrier_once(unsigned int* counter, unsigne
   return ok_s != 0;
 }
 
-// Adds the per-thread partials of a block that covers ALL channels into one copy of the accumulators.  Every thread
-// parks its 16 partial sums in shared memory (row lane x channel: kFusedThreads * 16 floats), then thread c adds up
-// column c and issues one global atomic: no shared-memory atomics, whose fp32 form is a compare-and-swap loop that
-// crawls when sixteen warps add to the same words.
-__device__ __forceinline__ void flush_partials_all(const float* s1, const float* s2, int g, int rl, int CG, int C, float* sh,
+// Work decomposition of the one-launch kernels: like the reduction kernels, a block covers a chunk of at most 256
+// channels (cgb groups of 8) and a chunk of rows; blockIdx.x = row chunk * channel chunks + channel chunk.
+struct FusedGeom {
+  int cgb, nch, cc, rc, nrc, lg, rl, RL, g;
+  long long r0, r1, chunk;
+};
+__device__ __forceinline__ FusedGeom fused_geom(long long R, int C) {
+  FusedGeom f;
+  const int CG = C >> 3;
+  f.cgb = CG < 32 ? CG : 32;
+  f.nch = CG / f.cgb;
+  f.cc = blockIdx.x % f.nch;
+  f.rc = blockIdx.x / f.nch;
+  f.nrc = gridDim.x / f.nch;
+  f.lg = threadIdx.x % f.cgb;
+  f.rl = threadIdx.x / f.cgb;
+  f.RL = kFusedThreads / f.cgb;
+  f.g = f.cc * f.cgb + f.lg;
+  f.chunk = (R + f.nrc - 1) / f.nrc;
+  f.r0 = (long long)f.rc * f.chunk;
+  f.r1 = f.r0 + f.chunk < R ? f.r0 + f.chunk : R;
+  return f;
+}
+
+// Adds the per-thread partials of a block into one copy of the accumulators.  Every thread parks its 16 partial
+// sums in shared memory (row lane x channel: kFusedThreads * 16 floats), then thread c adds up column c and issues
+// one global atomic: no shared-memory atomics, whose fp32 form is a compare-and-swap loop that crawls when sixteen
+// warps add to the same words.  Row chunks spread their additions over `copies` sets of accumulators, because
+// same-address atomics serialise in L2.
+__device__ __forceinline__ void flush_partials_all(const float* s1, const float* s2, const FusedGeom& f, int C, float* sh,
                                                    float* sums, int copies) {
-  const int RL = kFusedThreads / CG;
-  float* row = sh + size_t(rl) * 2 * C;
+  const int nchn = f.cgb * 8;
+  float* row = sh + size_t(f.rl) * 2 * nchn;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    row[g * 8 + i] = s1[i];
-    row[C + g * 8 + i] = s2[i];
+    row[f.lg * 8 + i] = s1[i];
+    row[nchn + f.lg * 8 + i] = s2[i];
   }
   __syncthreads();
-  // blocks spread their additions over `copies` sets of accumulators: same-address atomics serialise in L2
-  float* mine = sums + size_t(blockIdx.x % copies) * 2 * C;
-  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) {
+  float* mine = sums + size_t(f.rc % copies) * 2 * C + f.cc * nchn;
+  for (int c = threadIdx.x; c < 2 * nchn; c += blockDim.x) {
     float t = 0.f;
-    for (int r = 0; r < RL; ++r) t += sh[size_t(r) * 2 * C + c];
-    atomicAdd(&mine[c], t);
+    for (int r = 0; r < f.RL; ++r) t += sh[size_t(r) * 2 * nchn + c];
+    atomicAdd(&mine[c < nchn ? c : C + (c - nchn)], t);
   }
 }
 
-// After the barrier: totals of all copies into shared memory, once per block (every thread then reads its channels
-// from there instead of all threads of the grid reading the same few lines of L2).
-__device__ __forceinline__ void gather_totals(const float* sums, int C, int copies, float* sh) {
+// After the barrier: totals of the block's channels over all copies into shared memory (sh[c] and sh[nchn + c]),
+// once per block, instead of all threads of the grid reading the same few lines of L2.
+__device__ __forceinline__ void gather_totals(const float* sums, const FusedGeom& f, int C, int copies, float* sh) {
   __syncthreads();           // the partial sums parked in sh have been consumed by every thread
-  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) {
+  const int nchn = f.cgb * 8;
+  for (int c = threadIdx.x; c < 2 * nchn; c += blockDim.x) {
+    const int at = f.cc * nchn + (c < nchn ? c : C + (c - nchn));
     float t = 0.f;
-    for (int k = 0; k < copies; ++k) t += __ldcg(&sums[size_t(k) * 2 * C + c]);
+    for (int k = 0; k < copies; ++k) t += __ldcg(&sums[size_t(k) * 2 * C + at]);
     sh[c] = t;
   }
   __syncthreads();
@@ -454,10 +480,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_fwd_fused_kernel(const Bn
   extern __shared__ uint4 staged[];
   __shared__ float sh[kFusedThreads * 16];       // partial sums of every thread, later the totals (2*C values)
   const int C = p.C, CG = C >> 3;
-  const int g = threadIdx.x % CG, rl = threadIdx.x / CG, RL = kFusedThreads / CG;
-  const long long chunk = (p.R + gridDim.x - 1) / gridDim.x;
-  const long long r0 = (long long)blockIdx.x * chunk;
-  const long long r1 = r0 + chunk < p.R ? r0 + chunk : p.R;
+  const FusedGeom f = fused_geom(p.R, C);
+  const int g = f.g, rl = f.rl, RL = f.RL, cgb = f.cgb, lg = f.lg;
+  const long long r0 = f.r0, r1 = f.r1;
   float pivot[8], s1[8], s2[8], ga[8], be[8];
   BTRACE(0);
   unpack8(*reinterpret_cast<const uint4*>(p.x + g * 8), pivot);
@@ -480,7 +505,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_fwd_fused_kernel(const Bn
     for (int u = 0; u < U; ++u) {
       const long long row = r + (long long)u * RL;
       if (row >= r1) continue;
-      staged[(row - r0) * CG + g] = v[u];
+      staged[(row - r0) * cgb + lg] = v[u];
       float f[8];
       unpack8(v[u], f);
 #pragma unroll
@@ -492,24 +517,24 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_fwd_fused_kernel(const Bn
     }
   }
   BTRACE(1);
-  flush_partials_all(s1, s2, g, rl, CG, C, sh, sums, copies);
+  flush_partials_all(s1, s2, f, C, sh, sums, copies);
   BTRACE(2);
   if (!grid_barrier_once(barrier, status)) return;
   BTRACE(3);
-  gather_totals(sums, C, copies, sh);
+  gather_totals(sums, f, C, copies, sh);
 
   float scale[8], shift[8];
   const float inv_r = 1.f / (float)p.R;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int c = g * 8 + i;
-    const float m1 = sh[c] * inv_r;
-    const float var = fmaxf(sh[C + c] * inv_r - m1 * m1, 0.f);
+    const float m1 = sh[lg * 8 + i] * inv_r;
+    const float var = fmaxf(sh[cgb * 8 + lg * 8 + i] * inv_r - m1 * m1, 0.f);
     const float mean = pivot[i] + m1;
     const float rstd = rsqrtf(var + p.eps);
     scale[i] = ga[i] * rstd;
     shift[i] = be[i] - mean * scale[i];
-    if (blockIdx.x == 0 && rl == 0) {
+    if (f.rc == 0 && rl == 0) {
       p.save_mean[c] = mean;
       p.save_rstd[c] = rstd;
       if (p.running_mean != nullptr) {
@@ -535,7 +560,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_fwd_fused_kernel(const Bn
       if (row >= r1) continue;
       const long long idx = row * CG + g;
       float f[8];
-      unpack8(staged[(row - r0) * CG + g], f);
+      unpack8(staged[(row - r0) * cgb + lg], f);
       if (p.residual != nullptr) {
         float rr[8];
         unpack8(vr[u], rr);
@@ -568,11 +593,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_bwd_fused_kernel(const Bn
   extern __shared__ uint4 staged[];
   __shared__ float sh[kFusedThreads * 16];
   const int C = p.C, CG = C >> 3;
-  const int g = threadIdx.x % CG, rl = threadIdx.x / CG, RL = kFusedThreads / CG;
-  const long long chunk = (p.R + gridDim.x - 1) / gridDim.x;
-  const long long r0 = (long long)blockIdx.x * chunk;
-  const long long r1 = r0 + chunk < p.R ? r0 + chunk : p.R;
-  uint4* staged_dz = staged + chunk * CG;
+  const FusedGeom f = fused_geom(p.R, C);
+  const int g = f.g, rl = f.rl, RL = f.RL, cgb = f.cgb, lg = f.lg;
+  const long long r0 = f.r0, r1 = f.r1;
+  uint4* staged_dz = staged + f.chunk * cgb;
   float mean[8], rstd[8], s1[8], s2[8], ga[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -608,24 +632,24 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_bwd_fused_kernel(const Bn
         s1[i] += fd[i];
         s2[i] += fd[i] * (fx[i] - mean[i]) * rstd[i];
       }
-      staged[(row - r0) * CG + g] = b[u];
-      if (stage_dz) staged_dz[(row - r0) * CG + g] = pack8(fd);
+      staged[(row - r0) * cgb + lg] = b[u];
+      if (stage_dz) staged_dz[(row - r0) * cgb + lg] = pack8(fd);
     }
   }
-  flush_partials_all(s1, s2, g, rl, CG, C, sh, sums, copies);
+  flush_partials_all(s1, s2, f, C, sh, sums, copies);
   if (!grid_barrier_once(barrier, status)) return;
-  gather_totals(sums, C, copies, sh);
+  gather_totals(sums, f, C, copies, sh);
 
   const float inv_r = 1.f / (float)p.R;
   float k0[8], k1[8], k2[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int c = g * 8 + i;
-    const float t1 = sh[c], t2 = sh[C + c];
+    const float t1 = sh[lg * 8 + i], t2 = sh[cgb * 8 + lg * 8 + i];
     k0[i] = ga[i] * rstd[i];         // dx = k0 * (dz - k1 - xhat * k2)
     k1[i] = t1 * inv_r;
     k2[i] = t2 * inv_r;
-    if (blockIdx.x == 0 && rl == 0) {
+    if (f.rc == 0 && rl == 0) {
       store_param(p.dgamma, c, p.param_bf16, t2);
       store_param(p.dbeta, c, p.param_bf16, t1);
     }
@@ -649,9 +673,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_bwd_fused_kernel(const Bn
       if (row >= r1) continue;
       const long long idx = row * CG + g;
       float fd[8], fx[8], o[8];
-      unpack8(staged[(row - r0) * CG + g], fx);
+      unpack8(staged[(row - r0) * cgb + lg], fx);
       if (stage_dz) {
-        unpack8(staged_dz[(row - r0) * CG + g], fd);
+        unpack8(staged_dz[(row - r0) * cgb + lg], fd);
       } else {
         unpack8(a[u], fd);
 #pragma unroll
@@ -681,20 +705,29 @@ int FusedGrid() {
 }
 
 // Blocks of the one-launch form: every SM for activations of 7 MB and more, fewer for smaller ones (about 48 KB
-// of rows per block), because what a small pass costs is the barrier and the contention on the accumulators.
+// of rows per block), because what a small pass costs is the barrier and the contention on the accumulators.  The
+// count is a multiple of the number of channel chunks (256 channels each).
 int FusedBlocks(long long R, int C, int sms) {
   if (sms <= 0) return 0;
+  const int CG = C >> 3;
+  const int nch = CG <= 32 ? 1 : CG / 32;
   long long blocks = (R * C * 2 + 48 * 1024 - 1) / (48 * 1024);
   if (blocks < 8) blocks = 8;
   if (blocks > sms) blocks = sms;
-  return static_cast<int>(blocks);
+  long long nrc = blocks / nch;
+  if (nrc < 1) nrc = 1;
+  return nrc * nch <= sms ? static_cast<int>(nrc * nch) : 0;
 }
 
 // Shared memory one block needs to keep `tensors` copies of its rows; 0 when the one-launch form does not apply.
 size_t FusedStageBytes(long long R, int C, int tensors, int grid) {
-  if (grid <= 0 || (kFusedThreads % (C >> 3)) != 0) return 0;
-  const long long chunk = (R + grid - 1) / grid;
-  const size_t bytes = size_t(chunk) * C * 2 * tensors;
+  const int CG = C >> 3;
+  if (grid <= 0 || CG < 1 || (CG < 32 ? (kFusedThreads % CG) != 0 : (CG % 32) != 0)) return 0;
+  const int cgb = CG < 32 ? CG : 32;
+  const int nrc = grid / (CG / cgb);
+  if (nrc < 1) return 0;
+  const long long chunk = (R + nrc - 1) / nrc;
+  const size_t bytes = size_t(chunk) * cgb * 16 * tensors;
   return bytes <= kFusedStageLimit ? bytes : 0;
 }
 
@@ -730,6 +763,8 @@ int ApplyGrid(long long R, int C) {
 }  // namespace
 
 int BnSumCopies(int C) {
+  // row chunks per channel chunk of a full grid: about 148 * 256 / C; eight copies bring the contention per word
+  // below twenty for up to 256 channels, wider layers need fewer
   int k = 2048 / C;
   return k < 1 ? 1 : (k > 8 ? 8 : k);
 }

@@ -63,6 +63,7 @@ using namespace t5;
 constexpr int BM = 128, BK = 64;
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
+constexpr int kWgradMaxCluster = 8;       // portable cluster size
 
 template <int BN_>
 struct ConvCfg {
@@ -617,7 +618,7 @@ struct WgradCfg {
   // flight.  A box holds up to 128 positions x 64 channels.
   static constexpr uint32_t kPoolBytes = 216 * 1024;
   static constexpr int kMaxStages = 8;
-  static constexpr size_t kSmem = 1024 + size_t(kPoolBytes) + (2 * kMaxStages + 2) * 8;
+  static constexpr size_t kSmem = 1024 + size_t(kPoolBytes) + (2 * kMaxStages + 5) * 8;
 };
 
 struct WgradGeom {
@@ -627,6 +628,8 @@ struct WgradGeom {
   signed char dh[kConvMaxTaps], dw[kConvMaxTaps];
   unsigned char wt[kConvMaxTaps];
   int tiles_co, tiles_ci, groups, tg, splits;
+  int cs, gs;                // splits = cs * gs: cs CTAs of one cluster reduce through shared memory, gs such clusters
+                             // per tile add up in the fp32 workspace
   int ldw;                   // elements between filter-gradient rows: w_taps * Cin
   unsigned int tmem_cols;    // power of two >= tg * BN_
   int stages;                // ring depth
@@ -636,6 +639,95 @@ struct WgradGeom {
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// Cluster helpers: the CTAs that share one output tile (different shares of the reduction) form a thread-block
+// cluster and add their partial tiles up through distributed shared memory.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* failed) {
+  if (mbar_try_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (unsigned polls = 1;; ++polls) {
+    if (mbar_try_cluster(bar, parity)) return true;
+    if ((polls & 31u) == 0u) {
+      if (*failed) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *failed = 1;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ float4 ld_cluster_v4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// Last step of the cluster reduction: the CS CTAs of the cluster have pushed their partial sums of this CTA's
+// 128 / CS rows into its shared memory ([sender][row][pitch] floats); add them up and write them out (bf16 filter
+// gradient, or fp32 reductions into the workspace when several clusters share the tile).
+struct ClusterRows {
+  const float* rx;          // receive buffer
+  int n_cols, pitch;        // columns of the tile, floats per row
+  int rank, co0, ci0, t0, te;
+  int Cout, Cin, ldw;
+  bool last;                // true: store bf16; false: reduce into the workspace
+  const int* tap_wt;
+  __nv_bfloat16* dwt;
+  float* ws;
+};
+template <int BN_, int CS>
+__device__ __forceinline__ void cluster_add_rows(const ClusterRows& c) {
+  constexpr int rows_share = BM / CS;
+  const int nf4 = c.n_cols >> 2;
+  const int total = rows_share * nf4;
+  for (int idx = c.te; idx < total; idx += 128) {
+    const int row = idx / nf4, col = (idx % nf4) * 4;
+    const float* at = c.rx + size_t(row) * c.pitch + col;
+    float4 acc = *reinterpret_cast<const float4*>(at);
+#pragma unroll
+    for (int r = 1; r < CS; ++r) {
+      const float4 v = *reinterpret_cast<const float4*>(at + size_t(r) * rows_share * c.pitch);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const int co = c.co0 + c.rank * rows_share + row;
+    const int ci = c.ci0 + col % BN_;
+    if (co >= c.Cout || ci >= c.Cin) continue;
+    const size_t off = size_t(co) * c.ldw + size_t(c.tap_wt[c.t0 + col / BN_]) * c.Cin + ci;
+    if (c.last) {
+      uint2 pk;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+      h[0] = __floats2bfloat162_rn(acc.x, acc.y);
+      h[1] = __floats2bfloat162_rn(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(c.dwt + off) = pk;
+    } else {
+      red_add_v4(c.ws + off, acc.x, acc.y, acc.z, acc.w);
+    }
+  }
 }
 
 #ifdef BFB_WGRAD_TRACE
@@ -663,6 +755,11 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
   uint64_t* empty = bars + S;
   uint64_t* acc_full = bars + 2 * S;
   uint64_t* acc_empty = acc_full + 1;
+  uint64_t* red_full = acc_full + 2;      // every CTA of the cluster is through with its MMAs (cs * 4 warp arrivals)
+  uint64_t* red_done = acc_full + 3;      // every warp of the cluster has pushed its rows (cs * 4 arrivals)
+  uint64_t* rd_done = acc_full + 4;       // this CTA's epilogue warps have read the receive buffer (4 arrivals)
+  const int cs = g.cs;
+  const uint32_t rank = cs > 1 ? cluster_ctarank() : 0u;
   __shared__ uint32_t tmem_base_s;
   __shared__ int failed_s;
   __shared__ int go_s;
@@ -674,7 +771,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
   const int lane = threadIdx.x & 31;
   const int patches = g.tiles_w * g.tiles_h * g.tiles_img;
   const int out_tiles = g.tiles_co * g.tiles_ci * g.groups;
-  const int items = out_tiles * g.splits;
+  const int items = out_tiles * g.gs;
   const int positions = g.bw * g.bh * g.bn;                  // a multiple of 16
   const int ksteps = positions / kUmmaK;
   const uint32_t box_bytes = uint32_t(positions) * 128u;
@@ -694,6 +791,9 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
     }
     mbar_init(smem_u32(acc_full), 1);       // one tcgen05.commit
     mbar_init(smem_u32(acc_empty), 4);      // one arrive per epilogue warp
+    mbar_init(smem_u32(red_full), uint32_t(cs) * 4u);
+    mbar_init(smem_u32(red_done), uint32_t(cs) * 4u);
+    mbar_init(smem_u32(rd_done), 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -706,11 +806,19 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_s;
   if (threadIdx.x == 0) WTRACE(1);
+  if (cs > 1) {
+    // no CTA may signal a peer's barriers before that peer has initialised them
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
 
   // item -> output tile (co0, ci0, first tap of its group) and its share of the patches
+  // CTAs are numbered cluster by cluster; a cluster walks the (tile, share-of-the-clusters) items together and its
+  // CTA `rank` takes share number (item / out_tiles) * cs + rank of the patches
+  const int first_item = int(blockIdx.x) / cs, item_step = int(gridDim.x) / cs;
   auto decode = [&](int item, int& co0, int& ci0, int& t0, int& t1, int& p0, int& p1, int& tile_id) {
     tile_id = item % out_tiles;
-    const int split = item / out_tiles;
+    const int split = (item / out_tiles) * cs + int(rank);
     const int co_t = tile_id % g.tiles_co;
     const int r = tile_id / g.tiles_co;
     const int ci_t = r % g.tiles_ci;
@@ -736,11 +844,17 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
   int armed = 0;
   if (warp == 0) {
     if (lane == 0) {
-      int it = 0;
+      int it = 0, local = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      for (int item = first_item; item < items && ok; item += item_step, ++local) {
         int co0, ci0, t0, t1, p0, p1, tile_id;
         decode(item, co0, ci0, t0, t1, p0, p1, tile_id);
+        // the ring doubles as the receive buffer of the cluster reduction: what the peers pushed for the previous
+        // item must have been read before new patches land on it
+        if (cs > 1 && local > 0) {
+          if (!mbar_wait(smem_u32(rd_done), (local - 1) & 1, failed)) break;
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic accesses before, TMA writes after
+        }
         const int boxes_a = min(g.boxes_a, (g.Cout - co0 + 63) / 64);
         const int boxes_b = min(g.boxes_b, (g.Cin - ci0 + 63) / 64);
         for (int p = p0; p < p1; ++p, ++it) {
@@ -774,7 +888,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
     if (lane == 0) {
       int it = 0, local = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++local) {
+      for (int item = first_item; item < items && ok; item += item_step, ++local) {
         int co0, ci0, t0, t1, p0, p1, tile_id;
         decode(item, co0, ci0, t0, t1, p0, p1, tile_id);
         // the epilogue must have drained the accumulators of the previous item
@@ -810,7 +924,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
     const int q = warp & 3;                  // accumulator lanes [32q, 32q + 32) = output channels co0 + 32q ...
     const bool leader = (warp == 2 && lane == 0);
     int local = 0;
-    for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
+    for (int item = first_item; item < items; item += item_step, ++local) {
       int co0, ci0, t0, t1, p0, p1, tile_id;
       decode(item, co0, ci0, t0, t1, p0, p1, tile_id);
       mbar_wait(smem_u32(acc_full), local & 1, failed);
@@ -820,6 +934,62 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
       if (!*reinterpret_cast<volatile int*>(&go_s)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (leader) WTRACE(6);
+      if (cs > 1) {
+        // ---- cluster reduction.  Rows [j * 128 / cs, (j + 1) * 128 / cs) of the tile belong to CTA j of the cluster.
+        // 1: every CTA announces that its MMAs are done, i.e. that its ring may be overwritten by its peers
+        const int n_cols = (t1 - t0) * BN_;
+        const int pitch = n_cols + 4;       // four extra words keep the 16-byte stores of a warp (one row per lane) off each other's banks
+        float* rx = reinterpret_cast<float*>(smem);
+        __syncwarp();
+        if (lane == 0)
+          for (int r = 0; r < cs; ++r) mbar_arrive_cluster(mapa_u32(smem_u32(red_full), uint32_t(r)));
+        mbar_wait_cluster(smem_u32(red_full), local & 1, failed);
+        epilogue_bar();
+        if (leader) go_s = (*failed == 0);
+        epilogue_bar();
+        if (!*reinterpret_cast<volatile int*>(&go_s)) break;
+        // 2: the accumulator rows go straight from tensor memory into the owner's receive buffer
+        // ([sender][row of the owner's share][pitch] floats) with remote shared-memory stores
+        {
+          const int rows_share = BM / cs;
+          const int row = q * 32 + lane;
+          const uint32_t owner = uint32_t(row / rows_share);
+          const uint32_t dst = mapa_u32(smem_u32(rx + size_t(int(rank) * rows_share + row % rows_share) * pitch), owner);
+#pragma unroll 1
+          for (int c = 0; c < n_cols / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c * 32), r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              st_cluster_v4(dst + uint32_t(c * 32 + j * 4) * 4u, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                            __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        asm volatile("fence.acq_rel.cluster;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(acc_empty)) : "memory");
+          for (int r = 0; r < cs; ++r) mbar_arrive_cluster(mapa_u32(smem_u32(red_done), uint32_t(r)));
+        }
+        // 3: when every warp of the cluster has pushed, this CTA adds up what it received
+        mbar_wait_cluster(smem_u32(red_done), local & 1, failed);
+        epilogue_bar();
+        if (leader) go_s = (*failed == 0);
+        epilogue_bar();
+        if (!*reinterpret_cast<volatile int*>(&go_s)) break;
+        if (leader) WTRACE(7);
+        const int te = int(threadIdx.x) - 64;                    // 0..127 over the four epilogue warps
+        const ClusterRows cr{rx, n_cols, pitch, int(rank), co0, ci0, t0, te, g.Cout, g.Cin, g.ldw, g.gs == 1,
+                             tap_wt_s, dwt, ws};
+        if (cs == 2) cluster_add_rows<BN_, 2>(cr);
+        else if (cs == 4) cluster_add_rows<BN_, 4>(cr);
+        else cluster_add_rows<BN_, 8>(cr);
+        // the ring may take the next item's patches once these reads are over
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(rd_done)) : "memory");
+      } else {
       const int co = co0 + q * 32 + lane;
       const bool row_ok = co < g.Cout;
       for (int t = t0; t < t1; ++t) {
@@ -857,7 +1027,8 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(acc_empty)) : "memory");
       if (leader) WTRACE(7);
-      if (g.splits > 1) {
+      }
+      if (g.gs > 1) {
         // the CTA that adds the last share of this tile turns the fp32 sums into the bf16 filter gradient
         __threadfence();
         epilogue_bar();
@@ -903,6 +1074,8 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
         if (leader) WTRACE(8);
       }
     }
+    // (a CTA leaves only after everything addressed to it has arrived, and nothing is pushed to a CTA that has
+    // not announced its next item, so no shared memory is touched after its owner has gone)
   }
   if (warp == 0 && lane == 0 && *failed) {
     for (int it = armed > S ? armed - S : 0; it < armed; ++it) {
@@ -979,12 +1152,63 @@ cudaError_t LaunchWgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const Wgr
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  const int items = g.tiles_co * g.tiles_ci * g.groups * g.splits;
-  const int sms = SmCount();
-  conv_wgrad_kernel<BN_><<<items < sms ? items : sms, kThreads, Cfg::kSmem, stream>>>(
-      mdy, mx, g, static_cast<__nv_bfloat16*>(p.dw), p.workspace, p.counters, status);
+  const int items = g.tiles_co * g.tiles_ci * g.groups * g.gs;          // each taken by one cluster of cs CTAs
+  cudaLaunchConfig_t cfg{};
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(g.cs);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g.cs > 1 ? 1 : 0;
+  int resident = SmCount();                                             // clusters (or single CTAs) that run at once
+  if (g.cs > 1) {
+    static int max_clusters[kWgradMaxCluster + 1] = {0};
+    if (max_clusters[g.cs] == 0) {
+      cfg.gridDim = dim3(static_cast<unsigned>(g.cs));
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, conv_wgrad_kernel<BN_>, &cfg) != cudaSuccess || n < 1) n = 1;
+      (void)cudaGetLastError();
+      max_clusters[g.cs] = n;
+    }
+    resident = max_clusters[g.cs];
+  }
+  const int clusters = items < resident ? items : resident;
+  cfg.gridDim = dim3(static_cast<unsigned>(clusters * g.cs));
+  cudaError_t e = cudaLaunchKernelEx(&cfg, conv_wgrad_kernel<BN_>, mdy, mx, g, static_cast<__nv_bfloat16*>(p.dw), p.workspace,
+                                     p.counters, status);
   CountKernelLaunch();
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+// Clusters of `cs` CTAs (one CTA per SM) that the device runs at once, for the planner.  A cluster sits inside one
+// GPC, so eight-CTA clusters leave some SMs idle.
+int WgradResidentClusters(int cs) {
+  static int cached[kWgradMaxCluster + 1] = {0};
+  if (cs <= 1) return SmCount();
+  if (cached[cs] == 0) {
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = WgradCfg<64>::kSmem;
+    cfg.gridDim = dim3(static_cast<unsigned>(cs));
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(cs);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaFuncSetAttribute(conv_wgrad_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(WgradCfg<64>::kSmem));
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, conv_wgrad_kernel<64>, &cfg) != cudaSuccess || n < 1) n = SmCount() / cs / 2;
+    (void)cudaGetLastError();
+    cached[cs] = n < 1 ? 1 : n;
+  }
+  return cached[cs];
 }
 
 template <int BN_, int BMODE>
@@ -1181,28 +1405,30 @@ void WgradRings(int cout, int cin, int bn, int tg, int positions, int* boxes_a, 
   *stages = s;
 }
 
-// Tile shape and split of a filter gradient: BN (input channels per tile), taps per group, shares of the patches.
-// The taps of a group are columns of one MMA (N = taps * BN <= 256), so more taps per group cost no extra MMA
-// instructions and share the load of the output gradient; they widen the tile that is reduced at the end.  Every
-// candidate is priced with a small model of one CTA's time line and the cheapest wins:
+// Tile shape and split of a filter gradient: BN (input channels per tile), taps per group, and how the patches are
+// shared out: cs CTAs of one cluster, times gs clusters.  The taps of a group are columns of one MMA (N = taps * BN
+// <= 256), so more taps per group cost no extra MMA instructions and share the load of the output gradient; they
+// widen the tile that is reduced at the end.  Every candidate is priced with a small model of one CTA's time line and
+// the cheapest wins:
 //   main loop   = patches of the CTA x max(bytes per patch / what one SM draws from L2, MMA time, load latency / depth)
-//   reduction   = (more than one share per tile) vector reductions of the partial tile, a fence and a ticket, and the
-//                 last CTA's conversion pass in batches of one L2 round trip each.
-// BLUEFOG_B200_WGRAD_PLAN=bn,tg,splits overrides.
-void WgradPlan(const WgradProblem& p, int patches, int positions, int* bn_tile, int* tg, int* splits) {
+//   reduction   = within a cluster: park the tile in shared memory, add up a 1/cs share of its rows from the peers;
+//                 across clusters (gs > 1): vector reductions of that share into the workspace, a fence and a ticket,
+//                 and the last CTA's conversion pass in batches of one L2 round trip each.
+// BLUEFOG_B200_WGRAD_PLAN=bn,tg,cs,gs overrides.
+void WgradPlan(const WgradProblem& p, int patches, int positions, int* bn_tile, int* tg, int* cs_out, int* gs_out) {
   const int cin = p.x.c, cout = p.dy.c, T = p.taps.T;
-  const int sms = SmCount();
   if (const char* env = std::getenv("BLUEFOG_B200_WGRAD_PLAN")) {
-    int b = 0, t = 0, s = 0;
-    if (std::sscanf(env, "%d,%d,%d", &b, &t, &s) == 3 && (b == 64 || b == 128 || b == 256) && t >= 1 && t <= T &&
-        t * b <= 256 && s >= 1) {
+    int b = 0, t = 0, c = 0, s = 0;
+    if (std::sscanf(env, "%d,%d,%d,%d", &b, &t, &c, &s) == 4 && (b == 64 || b == 128 || b == 256) && t >= 1 && t <= T &&
+        t * b <= 256 && (c == 1 || c == 2 || c == 4 || c == 8) && s >= 1 && c * s <= patches) {
       int ba, bb, st;
       unsigned stride;
       WgradRings(cout, cin, b, t, positions, &ba, &bb, &stride, &st);
       if (st >= 2) {
         *bn_tile = b;
         *tg = t;
-        *splits = s > patches ? patches : s;
+        *cs_out = c;
+        *gs_out = s;
         return;
       }
     }
@@ -1224,32 +1450,48 @@ void WgradPlan(const WgradProblem& p, int patches, int positions, int* bn_tile, 
       const int groups = (T + t - 1) / t;
       const int tiles_co = (cout + BM - 1) / BM, tiles_ci = (cin + b - 1) / b;
       const int tiles = tiles_co * tiles_ci * groups;
-      int s = sms / tiles;
-      if (s < 1) s = 1;
-      if (s > patches) s = patches;
-      const double items_per_cta = double((tiles * s + sms - 1) / sms);
-      const double cta_patches = double((patches + s - 1) / s) * items_per_cta;
-      const double bytes = (ba + double(t) * bb) * box;
-      double mma_clk = double(t) * b / 2.0;                      // one 128 x (t*b) x 16 MMA
-      if (mma_clk < 60.0) mma_clk = 60.0;                        // floor of a small MMA with MN-major operands
-      const double mma_ns = ksteps * mma_clk / kClockGhz;
-      const double load_ns = bytes / kSmBytesPerNs;
-      const double latency_ns = (kLoadLatencyNs + mma_ns) / stages;
-      double per_patch = load_ns > mma_ns ? load_ns : mma_ns;
-      if (latency_ns > per_patch) per_patch = latency_ns;
-      double ns = 3000.0 + cta_patches * per_patch + kRoundTripNs;
-      if (s > 1) {
-        const double reds = double(t) * b / 4.0;                  // 16-byte reductions per epilogue thread
-        const double batches = double((32 * t * ((b + 127) / 128) + 15) / 16);
-        ns += reds * 15.0 + 3.0 * kRoundTripNs + batches * kRoundTripNs;
-      } else {
-        ns += double(t) * b * 2.0;                               // direct bf16 stores
-      }
-      if (best < 0 || ns < best) {
-        best = ns;
-        *bn_tile = b;
-        *tg = t;
-        *splits = s;
+      for (int cs = 1; cs <= kWgradMaxCluster; cs *= 2) {
+        if (cs > patches) break;
+        const int resident = WgradResidentClusters(cs);       // clusters running at once
+        int gs = resident / tiles;
+        if (gs < 1) gs = 1;
+        if (cs * gs > patches) gs = patches / cs;
+        if (gs < 1) continue;
+        // Measured: the cluster form wins where a CTA's share of the reduction is short (at most 16 patches) and the
+        // cluster alone gives all the splits the tile needs; clusters of eight and clusters combined with workspace
+        // splits lost against plain workspace splits on every ResNet-50 and GPT-2 shape tried.
+        if (cs > 1 && (cs > 4 || gs != 1 || (patches + cs - 1) / cs > 16)) continue;
+        const int s = cs * gs;
+        const double rounds = double((tiles * gs + resident - 1) / resident);
+        const double cta_patches = double((patches + s - 1) / s) * rounds;
+        const double bytes = (ba + double(t) * bb) * box;
+        double mma_clk = double(t) * b / 2.0;                      // one 128 x (t*b) x 16 MMA
+        if (mma_clk < 60.0) mma_clk = 60.0;                        // floor of a small MMA
+        const double mma_ns = ksteps * mma_clk / kClockGhz;
+        const double load_ns = bytes / kSmBytesPerNs;
+        const double latency_ns = (kLoadLatencyNs + mma_ns) / stages;
+        double per_patch = load_ns > mma_ns ? load_ns : mma_ns;
+        if (latency_ns > per_patch) per_patch = latency_ns;
+        double ns = 3000.0 + cta_patches * per_patch + kRoundTripNs;
+        const double tile_floats = 128.0 * t * b;
+        // pushing (cs - 1) / cs of the tile through distributed shared memory runs at some 15 bytes/ns per SM in the
+        // all-to-all pattern of this step; the constants are scaled like those of the workspace path below, which
+        // this model prices at about half of what it measures
+        if (cs > 1) ns += 700.0 + tile_floats * 4.0 * (cs - 1) / cs / 32.0 + tile_floats / cs * 0.18;
+        if (gs > 1) {
+          const double reds = tile_floats / cs / 4.0 / 128.0;      // 16-byte reductions per epilogue thread
+          const double batches = double((32 * t * ((b + 127) / 128) + 15) / 16);
+          ns += reds * 15.0 + 3.0 * kRoundTripNs + batches * kRoundTripNs;
+        } else if (cs == 1) {
+          ns += double(t) * b * 2.0;                               // direct bf16 stores
+        }
+        if (best < 0 || ns < best) {
+          best = ns;
+          *bn_tile = b;
+          *tg = t;
+          *cs_out = cs;
+          *gs_out = gs;
+        }
       }
     }
   }
@@ -1283,7 +1525,8 @@ cudaError_t LaunchConvWgrad(const WgradProblem& p, unsigned int* status, cudaStr
   g.tiles_img = (g.N + g.bn - 1) / g.bn;
   const int patches = g.tiles_w * g.tiles_h * g.tiles_img;
   int bn_tile;
-  WgradPlan(p, patches, g.bw * g.bh * g.bn, &bn_tile, &g.tg, &g.splits);
+  WgradPlan(p, patches, g.bw * g.bh * g.bn, &bn_tile, &g.tg, &g.cs, &g.gs);
+  g.splits = g.cs * g.gs;
   g.tiles_co = (g.Cout + BM - 1) / BM;
   g.tiles_ci = (g.Cin + bn_tile - 1) / bn_tile;
   g.groups = (g.T + g.tg - 1) / g.tg;
@@ -1293,7 +1536,7 @@ cudaError_t LaunchConvWgrad(const WgradProblem& p, unsigned int* status, cudaStr
   g.tmem_cols = cols;
   WgradRings(g.Cout, g.Cin, bn_tile, g.tg, g.bw * g.bh * g.bn, &g.boxes_a, &g.boxes_b, &g.box_stride, &g.stages);
   if (g.stages < 2) return cudaErrorInvalidValue;
-  if (g.splits > 1) {
+  if (g.gs > 1) {
     const long long need = (long long)g.Cout * g.ldw;
     if (p.workspace == nullptr || p.counters == nullptr || p.workspace_floats < need ||
         p.n_counters < g.tiles_co * g.tiles_ci * g.groups || (reinterpret_cast<uintptr_t>(p.workspace) & 15))

@@ -540,7 +540,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      py::arg("running_var"), py::arg("eps"), py::arg("momentum"), py::arg("relu"), py::arg("zeroed_sums") = py::none(),
      py::arg("stats_ready") = false);
   m.def("bn_backward", [](at::Tensor dy, c10::optional<at::Tensor> mask, at::Tensor x, at::Tensor save_mean, at::Tensor save_rstd,
-                          at::Tensor gamma, bool relu, bool want_dres, c10::optional<at::Tensor> zeroed_sums) {
+                          at::Tensor gamma, bool relu, bool want_dres, c10::optional<at::Tensor> zeroed_sums,
+                          c10::optional<at::Tensor> dy2) {
+    // dy2: a second addend of the incoming gradient; the kernels use dy + dy2 without a pass that adds them
+    const void* dy2_ptr = nullptr;
+    if (dy2.has_value() && dy2->defined()) {
+      TORCH_CHECK(dy2->is_cuda() && dy2->scalar_type() == at::kBFloat16 && dy2->sizes() == dy.sizes() &&
+                  dy2->is_contiguous(at::MemoryFormat::ChannelsLast), "dy2 must match dy (bf16, channels_last)");
+      dy2_ptr = dy2->data_ptr();
+    }
     TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous(at::MemoryFormat::ChannelsLast) &&
                 dy.sizes() == x.sizes(), "bn_backward expects a bf16 NHWC gradient of the shape of x");
     const int C = static_cast<int>(x.size(1));
@@ -562,7 +570,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                   mask->numel() == R * (C / 8), "bn_backward needs the ReLU bit mask of the forward pass");
       mptr = mask->data_ptr();
     }
-    cudaError_t e = LaunchBnBackward(dy.data_ptr(), mptr, x.data_ptr(), dx.data_ptr(),
+    cudaError_t e = LaunchBnBackward(dy.data_ptr(), dy2_ptr, mptr, x.data_ptr(), dx.data_ptr(),
                                      want_dres ? dres.data_ptr() : nullptr, sums.data_ptr<float>(),
                                      save_mean.data_ptr<float>(), save_rstd.data_ptr<float>(), gamma.data_ptr(),
                                      dgamma.data_ptr(), dbeta.data_ptr(), R, C, relu ? 1 : 0, pbf16 ? 1 : 0,
@@ -571,7 +579,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(e == cudaSuccess, "bn_backward launch failed: ", cudaGetErrorString(e));
     return std::make_tuple(dx, dres, dgamma, dbeta);
   }, py::arg("dy"), py::arg("mask"), py::arg("x"), py::arg("save_mean"), py::arg("save_rstd"), py::arg("gamma"),
-     py::arg("relu"), py::arg("want_dres"), py::arg("zeroed_sums") = py::none());
+     py::arg("relu"), py::arg("want_dres"), py::arg("zeroed_sums") = py::none(), py::arg("dy2") = py::none());
 
   // ---- LayerNorm over the last dimension, bf16 ------------------------------------------------
   m.def("ln_supported", [](at::Tensor x) {

@@ -37,6 +37,26 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
   return v;
 }
+// dy may arrive as two addends (the gradient through a block's shortcut and the gradient through its first
+// convolution): the sum is formed here, in fp32, instead of in a pass of its own.
+__device__ __forceinline__ void unpack8_sum(const uint4& a, const __nv_bfloat16* second, long long off, float* f) {
+  unpack8(a, f);
+  if (second != nullptr) {
+    float g[8];
+    unpack8(*reinterpret_cast<const uint4*>(second + off), g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] += g[i];
+  }
+}
+__device__ __forceinline__ void unpack8_add(const uint4& a, const uint4& b, bool second, float* f) {
+  unpack8(a, f);
+  if (second) {
+    float g[8];
+    unpack8(b, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] += g[i];
+  }
+}
 __device__ __forceinline__ float load_param(const void* p, int i, int is_bf16) {
   return is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]) : static_cast<const float*>(p)[i];
 }
@@ -225,7 +245,8 @@ __global__ void __launch_bounds__(kThreads) bn_apply_kernel(const BnApplyParams 
 }
 
 // sums[c] = sum dz;  sums[C+c] = sum dz * xhat
-__global__ void __launch_bounds__(kThreads, 3) bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dy,
+__global__ void __launch_bounds__(kThreads, 2) bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                                    const __nv_bfloat16* __restrict__ dy2,
                                                                     const unsigned char* __restrict__ mask,
                                                                     const __nv_bfloat16* __restrict__ x,
                                                                     const float* __restrict__ save_mean,
@@ -250,20 +271,21 @@ __global__ void __launch_bounds__(kThreads, 3) bn_bwd_reduce_kernel(const __nv_b
   constexpr int U = 4;
   const int CG = C >> 3;
   for (; r + (long long)(U - 1) * RL < r1; r += (long long)U * RL) {
-    uint4 a[U], b[U];
+    uint4 a[U], a2[U], b[U];
     unsigned m[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const long long row = r + (long long)u * RL;
       const long long off = row * C + g * 8;
       a[u] = *reinterpret_cast<const uint4*>(dy + off);
+      if (dy2 != nullptr) a2[u] = *reinterpret_cast<const uint4*>(dy2 + off);
       b[u] = *reinterpret_cast<const uint4*>(x + off);
       m[u] = relu ? mask[row * CG + g] : 0xffu;
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       float fd[8], fx[8];
-      unpack8(a[u], fd);
+      unpack8_add(a[u], a2[u], dy2 != nullptr, fd);
       unpack8(b[u], fx);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -276,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 3) bn_bwd_reduce_kernel(const __nv_b
   for (; r < r1; r += RL) {
     const long long off = r * C + g * 8;
     float fd[8], fx[8];
-    unpack8(*reinterpret_cast<const uint4*>(dy + off), fd);
+    unpack8_sum(*reinterpret_cast<const uint4*>(dy + off), dy2, off, fd);
     unpack8(*reinterpret_cast<const uint4*>(x + off), fx);
     const unsigned m = relu ? mask[r * CG + g] : 0xffu;
 #pragma unroll
@@ -291,6 +313,7 @@ __global__ void __launch_bounds__(kThreads, 3) bn_bwd_reduce_kernel(const __nv_b
 
 struct BnBwdApplyParams {
   const __nv_bfloat16* dy;
+  const __nv_bfloat16* dy2;        // second addend of the incoming gradient, or null
   const unsigned char* mask;       // bits written by the forward pass (null without ReLU)
   const __nv_bfloat16* x;
   __nv_bfloat16* dx;
@@ -332,13 +355,14 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(const BnBwdApply
   const long long stride = (long long)gridDim.x * blockDim.x;
   constexpr int U = 4;
   for (long long base = gtid; base < total; base += stride * U) {
-    uint4 vd[U], vx[U];
+    uint4 vd[U], vd2[U], vx[U];
     unsigned m[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const long long idx = base + (long long)u * stride;
       if (idx < total) {
         vd[u] = *reinterpret_cast<const uint4*>(p.dy + idx * 8);
+        if (p.dy2 != nullptr) vd2[u] = *reinterpret_cast<const uint4*>(p.dy2 + idx * 8);
         vx[u] = *reinterpret_cast<const uint4*>(p.x + idx * 8);
         m[u] = p.relu ? p.mask[idx] : 0xffu;
       }
@@ -348,7 +372,7 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(const BnBwdApply
       const long long idx = base + (long long)u * stride;
       if (idx >= total) continue;
       float fd[8], fx[8], o[8];
-      unpack8(vd[u], fd);
+      unpack8_add(vd[u], vd2[u], p.dy2 != nullptr, fd);
       unpack8(vx[u], fx);
 #pragma unroll
       for (int i = 0; i < 8; ++i)
@@ -607,7 +631,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_bwd_fused_kernel(const Bn
   }
   constexpr int U = 4;
   for (long long r = r0 + rl; r < r1; r += (long long)U * RL) {
-    uint4 a[U], b[U];
+    uint4 a[U], a2[U], b[U];
     unsigned m[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -615,6 +639,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_bwd_fused_kernel(const Bn
       if (row < r1) {
         const long long off = row * C + g * 8;
         a[u] = *reinterpret_cast<const uint4*>(p.dy + off);
+        if (p.dy2 != nullptr) a2[u] = *reinterpret_cast<const uint4*>(p.dy2 + off);
         b[u] = *reinterpret_cast<const uint4*>(p.x + off);
         m[u] = p.relu ? p.mask[row * CG + g] : 0xffu;
       }
@@ -624,7 +649,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_bwd_fused_kernel(const Bn
       const long long row = r + (long long)u * RL;
       if (row >= r1) continue;
       float fd[8], fx[8];
-      unpack8(a[u], fd);
+      unpack8_add(a[u], a2[u], p.dy2 != nullptr, fd);
       unpack8(b[u], fx);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -655,7 +680,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_bwd_fused_kernel(const Bn
     }
   }
   for (long long r = r0 + rl; r < r1; r += (long long)U * RL) {
-    uint4 a[U];
+    uint4 a[U], a2[U];
     unsigned m[U];
     if (!stage_dz) {
 #pragma unroll
@@ -663,6 +688,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_bwd_fused_kernel(const Bn
         const long long row = r + (long long)u * RL;
         if (row < r1) {
           a[u] = *reinterpret_cast<const uint4*>(p.dy + row * C + g * 8);
+          if (p.dy2 != nullptr) a2[u] = *reinterpret_cast<const uint4*>(p.dy2 + row * C + g * 8);
           m[u] = p.relu ? p.mask[row * CG + g] : 0xffu;
         }
       }
@@ -677,7 +703,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) bn_bwd_fused_kernel(const Bn
       if (stage_dz) {
         unpack8(staged_dz[(row - r0) * cgb + lg], fd);
       } else {
-        unpack8(a[u], fd);
+        unpack8_add(a[u], a2[u], p.dy2 != nullptr, fd);
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           if (!((m[u] >> i) & 1u)) fd[i] = 0.f;
@@ -804,12 +830,13 @@ cudaError_t LaunchBnForward(const void* x, const void* residual, void* y, void* 
   return cudaGetLastError();
 }
 
-cudaError_t LaunchBnBackward(const void* dy, const void* mask, const void* x, void* dx, void* dres, float* sums,
+cudaError_t LaunchBnBackward(const void* dy, const void* dy2, const void* mask, const void* x, void* dx, void* dres, float* sums,
                              const float* save_mean, const float* save_rstd, const void* gamma, void* dgamma,
                              void* dbeta, long long R, int C, int relu, int param_bf16, cudaStream_t stream,
                              int sum_copies, unsigned int* status) {
   if (!BnShapeSupported(R, C) || (relu && mask == nullptr)) return cudaErrorInvalidValue;
-  BnBwdApplyParams p{static_cast<const __nv_bfloat16*>(dy), static_cast<const unsigned char*>(mask),
+  BnBwdApplyParams p{static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(dy2),
+                     static_cast<const unsigned char*>(mask),
                      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(dx),
                      static_cast<__nv_bfloat16*>(dres), sums, save_mean, save_rstd, gamma, dgamma, dbeta, R, C, relu,
                      param_bf16};
@@ -831,7 +858,8 @@ cudaError_t LaunchBnBackward(const void* dy, const void* mask, const void* x, vo
     }
   }
   bn_bwd_reduce_kernel<<<ReduceGrid(R, C), kThreads, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(dy), static_cast<const unsigned char*>(mask), static_cast<const __nv_bfloat16*>(x),
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(dy2), static_cast<const unsigned char*>(mask),
+      static_cast<const __nv_bfloat16*>(x),
       save_mean, save_rstd, R, C, relu, sums);
   CountKernelLaunch();
   bn_bwd_apply_kernel<<<ApplyGrid(R, C), kThreads, 0, stream>>>(p);

@@ -22,7 +22,8 @@ cudaError_t LaunchBnForward(const void* x, const void* residual, void* y, void* 
                             int stats_ready = 0,    // 1: sums already hold sum(x), sum(x^2); no statistics pass
                             int sum_copies = 0, unsigned int* status = nullptr);
 
-cudaError_t LaunchBnBackward(const void* dy, const void* mask, const void* x, void* dx, void* dres, float* sums,
+// dy2: optional second addend of the incoming gradient (same shape as dy): the kernels use dy + dy2.
+cudaError_t LaunchBnBackward(const void* dy, const void* dy2, const void* mask, const void* x, void* dx, void* dres, float* sums,
                              const float* save_mean, const float* save_rstd, const void* gamma, void* dgamma,
                              void* dbeta, long long R, int C, int relu, int param_bf16, cudaStream_t stream,
                              int sum_copies = 0, unsigned int* status = nullptr);

@@ -189,8 +189,9 @@ class BasicBlock(nn.Module):
         self.downsample = downsample
 
     def forward(self, x):
-        identity = x if self.downsample is None else self.downsample(x)
-        out = bn_act(self.conv1(x), self.bn1, relu=True)
+        xa, xb = fused_bn.split_for_two_uses(x)      # see Bottleneck.forward
+        identity = xb if self.downsample is None else self.downsample(xb)
+        out = bn_act(self.conv1(xa), self.bn1, relu=True)
         return bn_act(self.conv2(out), self.bn2, relu=True, residual=identity)
 
 
@@ -209,7 +210,13 @@ class Bottleneck(nn.Module):
         self.downsample = downsample
 
     def forward(self, x):
-        if self.downsample is None:
+        # the block reads x twice (first convolution, shortcut); where x comes from a fused BatchNorm the two
+        # gradients go there as a pair instead of being added by autograd
+        xa, xb = fused_bn.split_for_two_uses(x)
+        if xa is not x:
+            identity = xb if self.downsample is None else self.downsample(xb)
+            out = self.conv1.forward_bn_act(xa, self.bn1, relu=True)
+        elif self.downsample is None:
             out, identity = self.conv1.forward_fork_bn_act(x, self.bn1, relu=True)
         else:
             identity = self.downsample(x)

@@ -5,6 +5,9 @@ streaming kernels forward and two backward (bluefog_b200/csrc/cuda/bn_kernels.cu
 the separate normalisation, add and ReLU passes; it falls back to PyTorch for eval mode and
 for tensors the kernels do not cover (not CUDA, not bf16, not channels_last).
 """
+import os
+import weakref
+
 import torch
 import torch.nn.functional as F
 
@@ -48,9 +51,16 @@ class _Workspace:
 
 _workspaces = {}
 
+# BLUEFOG_B200_PAIR_GRADIENTS=0: the two gradients of a block input are added by autograd as usual
+PAIR_GRADIENTS = os.environ.get("BLUEFOG_B200_PAIR_GRADIENTS", "1") != "0"
+
 
 def begin_step(device):
     """Call once at the start of a training forward pass (the models of this package do)."""
+    if _pending_pairs:
+        _pending_pairs.clear()
+        raise RuntimeError("a gradient pair of split_for_two_uses was never taken by the BatchNorm that produced the "
+                           "tensor; use it only on outputs of bn_act")
     if device.type != "cuda":
         return
     key = device.index if device.index is not None else torch.cuda.current_device()
@@ -75,6 +85,41 @@ def take_sums(device, channels):
     return t if t is not None else torch.zeros(2 * channels, dtype=torch.float32, device=device)
 
 
+# Gradient pairs on their way from _SplitFn.backward to the BatchNorm backward that consumes them:
+# data_ptr of the first addend -> (weak reference to it, second addend)
+_pending_pairs = {}
+
+
+class _SplitFn(torch.autograd.Function):
+    """``x -> (x, x)`` for a tensor with two uses (a residual block reads its input through the first convolution
+    and through the shortcut).  Autograd would add the two gradients in a pass of its own (two reads, one write
+    of a full activation); here they travel as a pair to the BatchNorm kernels that produced ``x``, which read both
+    addends and form the sum in registers."""
+
+    @staticmethod
+    def forward(ctx, x):
+        return x.view_as(x), x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, ga, gb):
+        if ga is None or gb is None:
+            return ga if gb is None else gb
+        if (ga.shape != gb.shape or ga.dtype != torch.bfloat16 or gb.dtype != torch.bfloat16
+                or not ga.is_contiguous(memory_format=torch.channels_last)
+                or not gb.is_contiguous(memory_format=torch.channels_last)):
+            return ga + gb
+        _pending_pairs[ga.data_ptr()] = (weakref.ref(ga), gb)
+        return ga
+
+
+def split_for_two_uses(x):
+    """Two handles of ``x`` whose gradients reach the producer of ``x`` un-added (see ``_SplitFn``).  Only outputs of
+    ``bn_act`` that took the kernel path qualify; any other tensor comes back twice unchanged."""
+    if getattr(x, "_bfb_takes_pairs", False) and x.requires_grad and torch.is_grad_enabled():
+        return _SplitFn.apply(x)
+    return x, x
+
+
 class _BnActFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, residual, gamma, beta, running_mean, running_var, eps, momentum, relu, stats):
@@ -96,11 +141,17 @@ class _BnActFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, mask, mean, rstd, gamma = ctx.saved_tensors
+        dy2 = None
+        pair = _pending_pairs.pop(dy.data_ptr(), None)
+        if pair is not None:
+            if pair[0]() is not dy:
+                raise RuntimeError("gradient pair does not belong to this gradient")
+            dy2 = pair[1]
         dy = dy.contiguous(memory_format=torch.channels_last)
         sums = None
         if ctx.bwd_sums is not None and ctx.ws.generation == ctx.bwd_gen:
             sums, ctx.bwd_sums = ctx.bwd_sums, None    # a slice is clean only once
-        dx, dres, dgamma, dbeta = _b.native.bn_backward(dy, mask, x, mean, rstd, gamma, ctx.relu, ctx.has_res, sums)
+        dx, dres, dgamma, dbeta = _b.native.bn_backward(dy, mask, x, mean, rstd, gamma, ctx.relu, ctx.has_res, sums, dy2)
         return dx, (dres if ctx.has_res else None), dgamma, dbeta, None, None, None, None, None, None
 
 
@@ -119,7 +170,9 @@ def bn_act(x, bn, relu=True, residual=None, count_batches=True, stats=None):
         momentum = 0.1 if bn.momentum is None else bn.momentum
         rm = bn.running_mean if bn.track_running_stats else None
         rv = bn.running_var if bn.track_running_stats else None
-        return _BnActFn.apply(x, residual, bn.weight, bn.bias, rm, rv, bn.eps, momentum, relu, stats)
+        y = _BnActFn.apply(x, residual, bn.weight, bn.bias, rm, rv, bn.eps, momentum, relu, stats)
+        y._bfb_takes_pairs = PAIR_GRADIENTS          # its backward accepts the pairs of split_for_two_uses
+        return y
     out = bn(x)
     if residual is not None:
         out = out + residual

@@ -95,6 +95,41 @@ def test_one_launch_and_two_kernel_forms_agree(N, C, H, W):
         assert bad <= 1e-5, bad
 
 
+@pytest.mark.parametrize("big", [False, True])
+def test_gradient_pairs_equal_autograd_addition(big):
+    """Two bottlenecks in a row: the gradients of the second block's input (through its first convolution and
+    through its shortcut) reach the first block's last BatchNorm as a pair; the result must be what autograd's own
+    addition gives.  ``big`` takes the two-kernel form of the BatchNorm backward (51 MB activations)."""
+    from bluefog_b200.models import resnet
+    from bluefog_b200.ops import fused_bn
+    dev = torch.device("cuda", 0)
+    n, hw = (64, 56) if big else (8, 14)
+    grads = []
+    for pairs in (True, False):
+        torch.manual_seed(3)
+        blocks = torch.nn.Sequential(resnet.Bottleneck(256, 64, 1, resnet.Downsample(256, 256, 1, True), True, True),
+                                     resnet.Bottleneck(256, 64, 1, None, True, True)).to(dev)
+        blocks = blocks.to(memory_format=torch.channels_last).train()
+        for prm in blocks.parameters():                      # bf16 parameters, fp32 running statistics
+            prm.data = prm.data.to(torch.bfloat16)
+        x = torch.randn(n, 256, hw, hw, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        x.requires_grad_(True)
+        fused_bn.PAIR_GRADIENTS = pairs
+        try:
+            fused_bn.begin_step(dev)
+            y = blocks(x)
+            y.float().square().mean().backward()
+        finally:
+            fused_bn.PAIR_GRADIENTS = True
+        torch.cuda.synchronize()
+        assert not fused_bn._pending_pairs
+        grads.append([x.grad.float()] + [p.grad.float() for p in blocks.parameters()])
+    for a, b in zip(*grads):
+        scale = max(b.abs().max().item(), 1e-6)
+        # the pair is added in fp32, autograd's sum is rounded to bf16 first: a few ReLU bits may differ
+        assert ((a - b).abs() > 3e-2 * scale).float().mean().item() <= 1e-3, (a - b).abs().max().item() / scale
+
+
 def test_fused_bn_with_bf16_parameters():
     _case(8, 512, 7, 7, True, True, torch.bfloat16)
 

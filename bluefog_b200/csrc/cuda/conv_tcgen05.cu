@@ -628,6 +628,7 @@ struct WgradGeom {
   signed char dh[kConvMaxTaps], dw[kConvMaxTaps];
   unsigned char wt[kConvMaxTaps];
   int tiles_co, tiles_ci, groups, tg, splits;
+  int spread;                // 1: every CTA of a tile converts a slice of it at the end (cooperative launch, one item per CTA)
   int cs, gs;                // splits = cs * gs: cs CTAs of one cluster reduce through shared memory, gs such clusters
                              // per tile add up in the fp32 workspace
   int ldw;                   // elements between filter-gradient rows: w_taps * Cin
@@ -1029,29 +1030,24 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
       if (leader) WTRACE(7);
       }
       if (g.gs > 1) {
-        // the CTA that adds the last share of this tile turns the fp32 sums into the bf16 filter gradient
-        __threadfence();
-        epilogue_bar();
-        if (leader) ticket_s = atomicAdd(&counters[tile_id], 1u);
-        epilogue_bar();
-        if (*reinterpret_cast<volatile unsigned int*>(&ticket_s) == unsigned(g.splits - 1)) {
-          __threadfence();
-          // Every warp converts its 32 rows; a lane owns four consecutive columns.  The loads of a batch are issued
-          // together: one L2 round trip per batch instead of one per 16 bytes.
+        // fp32 sums of `rows` tile rows from `row_lo` on -> bf16 filter gradient, workspace words back to zero.  The
+        // four warps interleave over (row, tap, 128-column chunk) triples; a lane owns four consecutive columns.
+        // The loads of a batch are issued together: one L2 round trip per batch instead of one per 16 bytes.
+        auto convert_rows = [&](int row_lo, int rows) {
           const int width = min(BN_, g.Cin - ci0);
           const int cchunks = (width + 127) / 128;
           const int ntaps = t1 - t0;
-          const int total = 32 * ntaps * cchunks;              // (row, tap, column chunk) triples of this warp
+          const int total = rows * ntaps * cchunks;
           constexpr int kBatch = 16;
-          for (int base = 0; base < total; base += kBatch) {
+          for (int base = q; base < total; base += 4 * kBatch) {
             float4 v[kBatch];
             size_t off[kBatch];
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
-              const int i = base + u;
+              const int i = base + 4 * u;
               const int cc = i % cchunks;
               const int t = t0 + (i / cchunks) % ntaps;
-              const int row = co0 + q * 32 + i / (cchunks * ntaps);
+              const int row = co0 + row_lo + i / (cchunks * ntaps);
               const int col = cc * 128 + lane * 4;
               const bool ok = i < total && row < g.Cout && col < width;
               off[u] = ok ? size_t(row) * g.ldw + size_t(tap_wt_s[t]) * g.Cin + ci0 + col : size_t(-1);
@@ -1068,6 +1064,48 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
               *reinterpret_cast<uint2*>(dwt + off[u]) = pk;
             }
           }
+        };
+        __threadfence();
+        epilogue_bar();
+        if (leader) ticket_s = atomicAdd(&counters[tile_id], 1u);
+        epilogue_bar();
+        if (g.spread) {
+          // Cooperative launch, one item per CTA: all CTAs that share the tile are running, so each waits (bounded)
+          // until every share has been added and converts its own slice of the rows, instead of the last one
+          // converting the whole tile while the others have gone.
+          if (leader) {
+            bool ok = true;
+            const long long t_start = clock64();
+            unsigned polls = 0;
+            for (;;) {
+              unsigned seen;
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counters + tile_id) : "memory");
+              if (seen >= unsigned(g.splits)) break;
+              if ((++polls & 31u) == 0u && (*failed || clock64() - t_start > kWaitLimitCycles)) {
+                *failed = 1;
+                ok = false;
+                break;
+              }
+            }
+            go_s = ok ? 1 : 0;
+          }
+          epilogue_bar();
+          if (!*reinterpret_cast<volatile int*>(&go_s)) break;
+          __threadfence();
+          const int share = item / out_tiles;
+          const int rows_share = (BM + g.splits - 1) / g.splits;
+          const int row_lo = share * rows_share;
+          convert_rows(row_lo, max(0, min(rows_share, BM - row_lo)));
+          epilogue_bar();
+          if (leader) {
+            // the CTA that finishes its slice last re-arms the tile's counter
+            const unsigned done = atomicAdd(&counters[tile_id], 1u);
+            if (done == unsigned(2 * g.splits - 1)) counters[tile_id] = 0u;
+          }
+        } else if (*reinterpret_cast<volatile unsigned int*>(&ticket_s) == unsigned(g.splits - 1)) {
+          // the CTA that adds the last share of this tile turns the fp32 sums into the bf16 filter gradient
+          __threadfence();
+          convert_rows(0, BM);
           if (leader) counters[tile_id] = 0u;
         }
         epilogue_bar();      // ticket_s is rewritten by the next item
@@ -1164,6 +1202,11 @@ cudaError_t LaunchWgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const Wgr
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = g.cs > 1 ? 1 : 0;
+  if (g.spread) {                                                       // never together with a cluster
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.numAttrs = 1;
+  }
   int resident = SmCount();                                             // clusters (or single CTAs) that run at once
   if (g.cs > 1) {
     static int max_clusters[kWgradMaxCluster + 1] = {0};
@@ -1180,6 +1223,15 @@ cudaError_t LaunchWgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const Wgr
   cfg.gridDim = dim3(static_cast<unsigned>(clusters * g.cs));
   cudaError_t e = cudaLaunchKernelEx(&cfg, conv_wgrad_kernel<BN_>, mdy, mx, g, static_cast<__nv_bfloat16*>(p.dw), p.workspace,
                                      p.counters, status);
+  if (e != cudaSuccess && g.spread) {
+    // the cooperative launch was refused: the same work with the last CTA of a tile converting all of it
+    (void)cudaGetLastError();
+    WgradGeom plain = g;
+    plain.spread = 0;
+    cfg.numAttrs = 0;
+    e = cudaLaunchKernelEx(&cfg, conv_wgrad_kernel<BN_>, mdy, mx, plain, static_cast<__nv_bfloat16*>(p.dw), p.workspace,
+                           p.counters, status);
+  }
   CountKernelLaunch();
   return e != cudaSuccess ? e : cudaGetLastError();
 }
@@ -1480,7 +1532,8 @@ void WgradPlan(const WgradProblem& p, int patches, int positions, int* bn_tile, 
         if (cs > 1) ns += 700.0 + tile_floats * 4.0 * (cs - 1) / cs / 32.0 + tile_floats / cs * 0.18;
         if (gs > 1) {
           const double reds = tile_floats / cs / 4.0 / 128.0;      // 16-byte reductions per epilogue thread
-          const double batches = double((32 * t * ((b + 127) / 128) + 15) / 16);
+          double batches = double((32 * t * ((b + 127) / 128) + 15) / 16);
+          if (cs == 1 && tiles * gs <= SmCount()) batches = double(int(batches) / gs + 1);     // every CTA converts a slice
           ns += reds * 15.0 + 3.0 * kRoundTripNs + batches * kRoundTripNs;
         } else if (cs == 1) {
           ns += double(t) * b * 2.0;                               // direct bf16 stores
@@ -1527,10 +1580,21 @@ cudaError_t LaunchConvWgrad(const WgradProblem& p, unsigned int* status, cudaStr
   int bn_tile;
   WgradPlan(p, patches, g.bw * g.bh * g.bn, &bn_tile, &g.tg, &g.cs, &g.gs);
   g.splits = g.cs * g.gs;
+  g.spread = 0;      // set below
   g.tiles_co = (g.Cout + BM - 1) / BM;
   g.tiles_ci = (g.Cin + bn_tile - 1) / bn_tile;
   g.groups = (g.T + g.tg - 1) / g.tg;
   g.ldw = p.w_taps * g.Cin;
+  {
+    static const bool spread_off = [] { const char* e = std::getenv("BLUEFOG_B200_WGRAD_SPREAD"); return e != nullptr && e[0] == '0'; }();
+    static const bool coop = [] {
+      int dev = 0, v = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&v, cudaDevAttrCooperativeLaunch, dev);
+      return v != 0;
+    }();
+    g.spread = (!spread_off && coop && g.cs == 1 && g.gs > 1 && g.tiles_co * g.tiles_ci * g.groups * g.gs <= SmCount()) ? 1 : 0;
+  }
   unsigned int cols = 32;
   while (cols < unsigned(g.tg * bn_tile)) cols <<= 1;
   g.tmem_cols = cols;

@@ -203,18 +203,25 @@ class _MlpGeluFn(torch.autograd.Function):
         return da, dw1, db1, dw2, db2
 
 
+# Rows up to which a weight gradient with few output tiles takes the split-K kernel of the convolution filter
+# gradients.  With GPT-2 medium's 8192 rows that kernel needs 31 us for 1024 x 1024 and 67 us for 1024 x 3072
+# against 15 and 36 us of the library's split-K product, which cost the step 1.9 ms; those go to the library.
+_SPLITK_MAX_ROWS = 4096
+
+
 def _weight_gradient(dy: torch.Tensor, a: torch.Tensor) -> torch.Tensor:
     """dW[N, K] = dY[M, N]^T @ A[M, K].  Products with many output tiles take the TN kernel (one CTA per tile walks
-    the whole reduction); products with few tiles and a long reduction take the split-K kernel of the convolution
-    filter gradients, which sees the rows as M images of one pixel."""
+    the whole reduction); products with few tiles and a reduction of at most ``_SPLITK_MAX_ROWS`` rows take the
+    split-K kernel of the convolution filter gradients, which sees the rows as M images of one pixel; the rest is
+    the library's."""
     n_out, k_in = dy.shape[1], a.shape[1]
     tiles = ((n_out + 127) // 128) * ((k_in + 255) // 256)
     C = _b.native
     if n_out % 8 == 0 and k_in % 8 == 0 and tiles >= _TN_MIN_TILES:
         return C.gemm_bf16_tn(dy, a)
     m = dy.shape[0]
-    if (hasattr(C, "conv_wgrad") and n_out % 8 == 0 and k_in % 64 == 0 and dy.is_contiguous() and a.is_contiguous()
-            and C.conv_wgrad_supported(m, 1, 1, k_in, n_out, 1)):
+    if (m <= _SPLITK_MAX_ROWS and hasattr(C, "conv_wgrad") and n_out % 8 == 0 and k_in % 64 == 0
+            and dy.is_contiguous() and a.is_contiguous() and C.conv_wgrad_supported(m, 1, 1, k_in, n_out, 1)):
         return C.conv_wgrad(dy.view(m, n_out, 1, 1), a.view(m, k_in, 1, 1), [0], [0], [0], 1, 1, False).view(n_out, k_in)
     return dy.t() @ a
 

@@ -113,6 +113,30 @@ def test_filter_gradient_leaves_its_scratch_clean():
         _close(g, ref, 2e-2)
 
 
+@pytest.mark.parametrize("plan", ["128,1,2,1", "256,1,4,1", "64,1,8,1", "128,1,2,2", "128,1,1,4", "64,3,1,6", "64,2,4,1"])
+@pytest.mark.parametrize("k", [1, 3])
+def test_filter_gradient_plans_cluster_and_workspace_splits(plan, k, monkeypatch):
+    """Every way the reduction over pixels can be shared out - CTAs of one cluster adding up through distributed
+    shared memory (third number), clusters or single CTAs adding up in the fp32 workspace (fourth number), several
+    taps per MMA (second number) - gives the same filter gradient, and leaves the workspace clean."""
+    from bluefog_b200 import _C
+    from bluefog_b200.ops import conv
+    if k == 1 and plan.split(",")[1] != "1":
+        pytest.skip("a 1x1 filter has one tap")
+    torch.manual_seed(11)
+    n, cin, cout, hw = 16, 256, 192, 14
+    x = torch.randn(n, cin, hw, hw, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    dy = torch.randn(n, cout, hw, hw, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    ref = torch.ops.aten.convolution_backward(dy.float(), x.float(), torch.zeros(cout, cin, k, k, device="cuda"), None,
+                                              (1, 1), (k // 2, k // 2), (1, 1), False, (0, 0), 1, (False, True, False))[1]
+    monkeypatch.setenv("BLUEFOG_B200_WGRAD_PLAN", plan)
+    for _ in range(2):                       # twice: the second call finds the workspace as the first one left it
+        g = conv.filter_gradient(dy, x, k, 1, k // 2)
+        torch.cuda.synchronize()
+        assert _C.gemm_status() == 0
+        _close(g, ref, 2e-2)
+
+
 @pytest.mark.parametrize("m,n_out,k_in", [(64, 1000, 2048), (200, 64, 128), (4096, 256, 64), (50, 72, 192)])
 def test_linear_weight_gradient_through_the_split_k_kernel(m, n_out, k_in):
     from bluefog_b200 import _C

@@ -74,3 +74,19 @@ def test_conv1x1_with_batchnorm_statistics_needs_the_kernel_path():
     want = bn_act(conv(x), bn2, relu=True)
     assert torch.allclose(got, want)
     assert torch.allclose(bn.running_mean, bn2.running_mean)
+
+
+def test_split_for_two_uses_leaves_other_tensors_alone():
+    """Gradient pairs are only formed for outputs of the fused BatchNorm kernels; any other tensor comes back twice
+    unchanged and autograd adds its gradients as usual."""
+    import torch
+    from bluefog_b200.ops import fused_bn
+    x = torch.randn(2, 8, 4, 4, requires_grad=True)
+    a, b = fused_bn.split_for_two_uses(x)
+    assert a is x and b is x
+    (a * 2 + b * 3).sum().backward()
+    assert torch.allclose(x.grad, torch.full_like(x, 5.0))
+    bn = torch.nn.BatchNorm2d(8)
+    y = fused_bn.bn_act(x, bn, relu=True)            # CPU: PyTorch fallback, no pairs
+    assert not getattr(y, "_bfb_takes_pairs", False)
+    fused_bn.begin_step(x.device)                    # nothing pending, nothing raised

@@ -174,9 +174,11 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int co0, n0, h0, w0;
         tile_coords(tile, co0, n0, h0, w0);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int tap = kb / cblocks;
-          const int ci0 = (kb % cblocks) * BK;
+        // (tap, 64-channel slice) advance by comparison: cblocks is a run-time value, and a division and a modulo
+        // by it per stage are some fifty instructions in a loop that one thread runs alone
+        int tap = 0, ci0 = 0;
+        for (int kb = 0; kb < num_kb; ++kb, ++it, ci0 += BK) {
+          if (ci0 == g.Cin) { ci0 = 0; ++tap; }
           const int s = it % S;
           if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, failed)) { ok = false; break; }
           const uint32_t full = smem_u32(&bars[s]);
@@ -365,6 +367,15 @@ struct HaloCfg {
   static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN_ >> 3) << 17) | (uint32_t(BM >> 4) << 24);
 };
 
+#ifdef BFB_HALO_TRACE
+__device__ unsigned long long g_halo_trace[160][16];
+#define HTRACE(i) do { g_halo_trace[blockIdx.x][i] = now_ns(); } while (0)
+#define HTRACE_ADD(i, v) do { g_halo_trace[blockIdx.x][i] += (unsigned long long)(v); } while (0)
+#else
+#define HTRACE(i) do {} while (0)
+#define HTRACE_ADD(i, v) do {} while (0)
+#endif
+
 template <int BN_, int BMODE>
 __global__ void __launch_bounds__(kIgemmThreads, 1)
 conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const HaloGeom g,
@@ -396,6 +407,7 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   const int num_tiles = spatial * g.tiles_co;
 
   if (threadIdx.x == 0) {
+    HTRACE(0);
     failed_s = 0;
     for (int s = 0; s < SA; ++s) {
       mbar_init(smem_u32(&full_a[s]), 1);
@@ -445,18 +457,21 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   if (warp == 0) {
     // activation producer: one patch per 64-channel slice
     if (lane == 0) {
-      int it = 0;
+      // ring positions are kept as (slot, phase) pairs that wrap by comparison: the depths are run-time values, and
+      // a modulo and a division by them per step are some fifty instructions in a loop that one thread runs alone
+      int it = 0, s = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int co0, n, h0;
         tile_coords(tile, co0, n, h0);
         for (int cb = 0; cb < cblocks; ++cb, ++it) {
-          const int s = it % SA;
-          if (!mbar_wait(smem_u32(&empty_a[s]), ((it / SA) & 1) ^ 1, failed)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&empty_a[s]), ph ^ 1, failed)) { ok = false; break; }
           const uint32_t full = smem_u32(&full_a[s]);
           mbar_expect_tx(full, g.patch_bytes);
           tma_load_4d(smem_u32(stage_a + size_t(s) * g.slot_bytes_a), &map_x, full, cb * BK, -1, h0 - 1, n);
           armed_a = it + 1;
+          if (++s == SA) { s = 0; ph ^= 1; }
         }
       }
     }
@@ -474,7 +489,8 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             load_filter(smem_u32(stage_b + size_t(t * cblocks + cb) * Cfg::kBytesB), full, g.wt[t], cb * BK, co0);
         armed_b = 1;
       } else {
-        int it = 0;
+        int it = 0, s = 0;
+        uint32_t ph = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
           int co0, n, h0;
@@ -482,12 +498,12 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           for (int cb = 0; cb < cblocks && ok; ++cb) {
 #pragma unroll
             for (int t = 0; t < 9; ++t, ++it) {
-              const int s = it % SB;
-              if (!mbar_wait(smem_u32(&empty_b[s]), ((it / SB) & 1) ^ 1, failed)) { ok = false; break; }
+              if (!mbar_wait(smem_u32(&empty_b[s]), ph ^ 1, failed)) { ok = false; break; }
               const uint32_t full = smem_u32(&full_b[s]);
               mbar_expect_tx(full, Cfg::kBytesB);
               load_filter(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), full, g.wt[t], cb * BK, co0);
               armed_b = it + 1;
+              if (++s == SB) { s = 0; ph ^= 1; }
             }
           }
         }
@@ -495,17 +511,34 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      int ita = 0, itb = 0, local = 0;
+      int ita = 0, sa = 0, sb_next = 0, local = 0;
+      uint32_t pha = 0, phb = 0;
       bool ok = true;
+      // the nine taps' row offsets into the patch, once
+      uint32_t tap_off[9];
+#pragma unroll
+      for (int t = 0; t < 9; ++t) tap_off[t] = uint32_t((g.dh[t] + 1) * g.Wp + (g.dw[t] + 1)) * 128u;
       if (resident) ok = mbar_wait(smem_u32(&full_b[0]), 0, failed);
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
         const int acc = local & 1;
+#ifdef BFB_HALO_TRACE
+        long long c0 = clock64();
+#endif
         if (!mbar_wait(smem_u32(&acc_empty[acc]), ((local >> 1) & 1) ^ 1, failed)) { ok = false; break; }
+#ifdef BFB_HALO_TRACE
+        HTRACE_ADD(8, clock64() - c0);
+#endif
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + uint32_t(acc * BN_);
         for (int cb = 0; cb < cblocks && ok; ++cb, ++ita) {
-          const int sa = ita % SA;
-          if (!mbar_wait(smem_u32(&full_a[sa]), (ita / SA) & 1, failed)) { ok = false; break; }
+#ifdef BFB_HALO_TRACE
+          c0 = clock64();
+#endif
+          if (!mbar_wait(smem_u32(&full_a[sa]), pha, failed)) { ok = false; break; }
+#ifdef BFB_HALO_TRACE
+          HTRACE_ADD(9, clock64() - c0);
+          if (ita == 0) HTRACE(1);
+#endif
           const uint32_t a_base = smem_u32(stage_a + size_t(sa) * g.slot_bytes_a);
           // Nine taps, unrolled: the tap tables are then read at constant indices (kernel parameters) and the
           // loop between two MMAs is a handful of integer instructions.  With a rolled loop the tables live in
@@ -517,13 +550,19 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             if (resident) {
               b_addr = smem_u32(stage_b + size_t(t * cblocks + cb) * Cfg::kBytesB);
             } else {
-              sb = itb % SB;
-              if (!mbar_wait(smem_u32(&full_b[sb]), (itb / SB) & 1, failed)) { ok = false; break; }
-              ++itb;
+              sb = sb_next;
+#ifdef BFB_HALO_TRACE
+              const long long c1 = clock64();
+#endif
+              if (!mbar_wait(smem_u32(&full_b[sb]), phb, failed)) { ok = false; break; }
+#ifdef BFB_HALO_TRACE
+              HTRACE_ADD(10, clock64() - c1);
+#endif
+              if (++sb_next == SB) { sb_next = 0; phb ^= 1; }
               b_addr = smem_u32(stage_b + size_t(sb) * Cfg::kBytesB);
             }
             // the tap's view of the patch: same rows, start moved by (dh + 1) * Wp + (dw + 1) rows of 128 bytes
-            const uint32_t a_addr = a_base + uint32_t((g.dh[t] + 1) * g.Wp + (g.dw[t] + 1)) * 128u;
+            const uint32_t a_addr = a_base + tap_off[t];
             const uint64_t adesc = make_desc(a_addr);
             const uint64_t bdesc = BMODE == 0 ? make_desc(b_addr) : make_desc_mn(b_addr, 8192, 1024);
             constexpr uint32_t idesc = Cfg::kIdesc | (BMODE != 0 ? (1u << 16) : 0u);
@@ -534,9 +573,12 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             if (!resident) umma_commit(smem_u32(&empty_b[sb]));
           }
           if (ok) umma_commit(smem_u32(&empty_a[sa]));
+          if (++sa == SA) { sa = 0; pha ^= 1; }
         }
         if (ok) umma_commit(smem_u32(&acc_full[acc]));
+        if (local < 4) HTRACE(2 + local);
       }
+      HTRACE(6);
     }
   } else if (warp >= 2 && warp <= 5) {
     const int q = warp & 3;
@@ -606,6 +648,7 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kCols) : "memory");
   }
   if (threadIdx.x == 0 && failed_s && status != nullptr) atomicExch(status, 1u);
+  if (threadIdx.x == 0) HTRACE(7);
 }
 
 // ------------------------------------------------------------------------------------------------------ //
@@ -845,7 +888,8 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
   int armed = 0;
   if (warp == 0) {
     if (lane == 0) {
-      int it = 0, local = 0;
+      int it = 0, local = 0, s = 0;       // (slot, phase) wrap by comparison: S is a run-time value, see conv_halo_kernel
+      uint32_t ph = 0;
       bool ok = true;
       for (int item = first_item; item < items && ok; item += item_step, ++local) {
         int co0, ci0, t0, t1, p0, p1, tile_id;
@@ -861,11 +905,10 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
         for (int p = p0; p < p1; ++p, ++it) {
           int n0, h0, w0;
           patch_coords(p, n0, h0, w0);
-          const int s = it % S;
 #ifdef BFB_WGRAD_TRACE
           const unsigned long long tw0 = now_ns();
 #endif
-          if (!mbar_wait(smem_u32(&empty[s]), ((it / S) & 1) ^ 1, failed)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1, failed)) { ok = false; break; }
 #ifdef BFB_WGRAD_TRACE
           WTRACE_ADD(10, now_ns() - tw0);
           if (it == 0) WTRACE(2);
@@ -881,13 +924,15 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
               tma_load_4d(smem_u32(stage_b + size_t((t - t0) * g.boxes_b + j) * box_stride), &map_x, bar, ci0 + j * 64,
                           w0 * g.in_stride + tap_dw_s[t], h0 * g.in_stride + tap_dh_s[t], n0);
           armed = it + 1;
+          if (++s == S) { s = 0; ph ^= 1; }
         }
       }
       WTRACE(3);
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      int it = 0, local = 0;
+      int it = 0, local = 0, s = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int item = first_item; item < items && ok; item += item_step, ++local) {
         int co0, ci0, t0, t1, p0, p1, tile_id;
@@ -900,11 +945,10 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((n_cols >> 3) << 17) |
                                (uint32_t(BM >> 4) << 24);
         for (int p = p0; p < p1; ++p, ++it) {
-          const int s = it % S;
 #ifdef BFB_WGRAD_TRACE
           const unsigned long long tw0 = now_ns();
 #endif
-          if (!mbar_wait(smem_u32(&full[s]), (it / S) & 1, failed)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&full[s]), ph, failed)) { ok = false; break; }
 #ifdef BFB_WGRAD_TRACE
           WTRACE_ADD(11, now_ns() - tw0);
           if (it == 0) WTRACE(4);
@@ -916,6 +960,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
           for (int k = 0; k < ksteps; ++k)
             umma_f16(tmem_base, adesc + uint64_t(k) * 128u, bdesc + uint64_t(k) * 128u, idesc, (p != p0 || k != 0) ? 1u : 0u);
           umma_commit(smem_u32(&empty[s]));
+          if (++s == S) { s = 0; ph ^= 1; }
         }
         if (ok) umma_commit(smem_u32(acc_full));
         WTRACE(5);
@@ -1129,6 +1174,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
   }
   if (threadIdx.x == 0) WTRACE(9);
   if (threadIdx.x == 0 && failed_s && status != nullptr) atomicExch(status, 1u);
+  if (threadIdx.x == 0) HTRACE(7);
 }
 
 // 4-D map over a view [n, h, w, c]; a box of {64, bw, bh, bn} elements taken with traversal stride `stride`
@@ -1271,12 +1317,34 @@ cudaError_t LaunchHalo(const CUtensorMap& mx, const CUtensorMap& mw, HaloGeom g,
   // filter: resident when all taps of the (single) output-channel tile fit beside a useful activation ring
   const size_t resident_bytes = size_t(g.T) * cblocks * Cfg::kBytesB;
   const bool resident = g.tiles_co == 1 && resident_bytes <= 80 * 1024;
-  g.slots_b = resident ? 0 : (BN_ == 64 ? 8 : (BN_ == 128 ? 4 : 3));
+  // Ring depths.  A patch feeds 36 MMAs (nine taps x four K steps), a filter block only four, so at the same
+  // latency of a load the filter ring has to be about nine times as deep in blocks: three patch slots, and all the
+  // rest of the shared memory for filter blocks (with four slots of 16 KB the 128-channel 28x28 layer waited for
+  // filter blocks: 18 blocks per tile at four per load latency).  BLUEFOG_B200_HALO_SLOTS=a,b overrides.
+  int want_a = 3;
+  int want_b = 0;
+  if (const char* env = std::getenv("BLUEFOG_B200_HALO_SLOTS")) {
+    int a = 0, b = 0;
+    if (std::sscanf(env, "%d,%d", &a, &b) == 2 && a >= 2 && a <= 6 && b >= 2 && b <= 16) { want_a = a; want_b = b; }
+  }
+  const size_t bars_bytes = Cfg::kMaxBars * 8;
+  if (resident) {
+    g.slots_b = 0;
+  } else if (want_b > 0) {
+    g.slots_b = want_b;
+  } else {
+    const size_t left = Cfg::kSmemLimit - 1024 - bars_bytes - size_t(want_a) * g.slot_bytes_a;
+    int sb = int(left / Cfg::kBytesB);
+    if (sb > 16) sb = 16;
+    if (sb < 2) sb = 2;
+    g.slots_b = sb;
+  }
+  if (!resident && 2 * (want_a + g.slots_b) + 4 > Cfg::kMaxBars) g.slots_b = (Cfg::kMaxBars - 4) / 2 - want_a;
   const size_t bytes_b = resident ? resident_bytes : size_t(g.slots_b) * Cfg::kBytesB;
-  const size_t fixed = 1024 + bytes_b + Cfg::kMaxBars * 8;
+  const size_t fixed = 1024 + bytes_b + bars_bytes;
   if (fixed + 2 * size_t(g.slot_bytes_a) > Cfg::kSmemLimit) return cudaErrorInvalidValue;
   int sa = int((Cfg::kSmemLimit - fixed) / g.slot_bytes_a);
-  if (sa > 6) sa = 6;
+  if (sa > (resident ? 6 : want_a)) sa = resident ? 6 : want_a;
   g.slots_a = sa;
   const size_t smem = fixed + size_t(sa) * g.slot_bytes_a;
   static size_t attr_bytes = 0;

@@ -511,14 +511,29 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      int ita = 0, sa = 0, sb_next = 0, local = 0;
+      // This loop is run by one thread, and the tensor core idles while it computes: everything that can be is
+      // prepared outside.  Ring positions are (slot, phase) pairs that wrap by comparison; barrier and stage
+      // addresses are 32-bit shared-memory addresses kept incrementally; a descriptor is a constant high word and a
+      // low word = constant + (address >> 4), so moving to the next tap, filter block or K step is one 32-bit add.
+      int ita = 0, sa = 0, sb = 0, local = 0;
       uint32_t pha = 0, phb = 0;
       bool ok = true;
-      // the nine taps' row offsets into the patch, once
-      uint32_t tap_off[9];
+      const uint64_t a_proto = make_desc(0u);
+      const uint64_t b_proto = BMODE == 0 ? make_desc(0u) : make_desc_mn(0u, 8192, 1024);
+      const uint32_t a_hi = uint32_t(a_proto >> 32), b_hi = uint32_t(b_proto >> 32);
+      const uint32_t a_lo0 = uint32_t(a_proto), b_lo0 = uint32_t(b_proto);
+      uint32_t tap16[9];                                       // the nine taps' row offsets into the patch, >> 4
 #pragma unroll
-      for (int t = 0; t < 9; ++t) tap_off[t] = uint32_t((g.dh[t] + 1) * g.Wp + (g.dw[t] + 1)) * 128u;
-      if (resident) ok = mbar_wait(smem_u32(&full_b[0]), 0, failed);
+      for (int t = 0; t < 9; ++t) tap16[t] = uint32_t((g.dh[t] + 1) * g.Wp + (g.dw[t] + 1)) * 8u;
+      const uint32_t stage_a16 = smem_u32(stage_a) >> 4, slot_a16 = g.slot_bytes_a >> 4;
+      const uint32_t stage_b16 = smem_u32(stage_b) >> 4;
+      constexpr uint32_t kB16 = Cfg::kBytesB >> 4;
+      const uint32_t full_a0 = smem_u32(full_a), empty_a0 = smem_u32(empty_a);
+      const uint32_t full_b0 = smem_u32(full_b), empty_b0 = smem_u32(empty_b);
+      uint32_t a_cur16 = stage_a16, b_cur16 = stage_b16;       // follow sa and sb
+      constexpr uint32_t idesc = Cfg::kIdesc | (BMODE != 0 ? (1u << 16) : 0u);
+      constexpr uint32_t b_step = BMODE == 0 ? 2 : (16 * 128) >> 4;
+      if (resident) ok = mbar_wait(full_b0, 0, failed);
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
         const int acc = local & 1;
 #ifdef BFB_HALO_TRACE
@@ -534,46 +549,43 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #ifdef BFB_HALO_TRACE
           c0 = clock64();
 #endif
-          if (!mbar_wait(smem_u32(&full_a[sa]), pha, failed)) { ok = false; break; }
+          if (!mbar_wait(full_a0 + 8u * uint32_t(sa), pha, failed)) { ok = false; break; }
 #ifdef BFB_HALO_TRACE
           HTRACE_ADD(9, clock64() - c0);
           if (ita == 0) HTRACE(1);
 #endif
-          const uint32_t a_base = smem_u32(stage_a + size_t(sa) * g.slot_bytes_a);
-          // Nine taps, unrolled: the tap tables are then read at constant indices (kernel parameters) and the
-          // loop between two MMAs is a handful of integer instructions.  With a rolled loop the tables live in
-          // local memory and their loads leave the tensor core idle between taps.
+          const uint32_t a_lo_patch = a_lo0 + a_cur16;
+          if (resident) b_cur16 = stage_b16 + uint32_t(cb) * kB16;       // block (t, cb) sits at (t * cblocks + cb)
+          // Nine taps, unrolled: the tap tables are then read at constant indices.
 #pragma unroll
           for (int t = 0; t < 9; ++t) {
-            uint32_t b_addr;
-            int sb = 0;
-            if (resident) {
-              b_addr = smem_u32(stage_b + size_t(t * cblocks + cb) * Cfg::kBytesB);
-            } else {
-              sb = sb_next;
+            if (!resident) {
 #ifdef BFB_HALO_TRACE
               const long long c1 = clock64();
 #endif
-              if (!mbar_wait(smem_u32(&full_b[sb]), phb, failed)) { ok = false; break; }
+              if (!mbar_wait(full_b0 + 8u * uint32_t(sb), phb, failed)) { ok = false; break; }
 #ifdef BFB_HALO_TRACE
               HTRACE_ADD(10, clock64() - c1);
 #endif
-              if (++sb_next == SB) { sb_next = 0; phb ^= 1; }
-              b_addr = smem_u32(stage_b + size_t(sb) * Cfg::kBytesB);
             }
             // the tap's view of the patch: same rows, start moved by (dh + 1) * Wp + (dw + 1) rows of 128 bytes
-            const uint32_t a_addr = a_base + tap_off[t];
-            const uint64_t adesc = make_desc(a_addr);
-            const uint64_t bdesc = BMODE == 0 ? make_desc(b_addr) : make_desc_mn(b_addr, 8192, 1024);
-            constexpr uint32_t idesc = Cfg::kIdesc | (BMODE != 0 ? (1u << 16) : 0u);
-            constexpr uint64_t b_step = BMODE == 0 ? 2 : (16 * 128) >> 4;
+            const uint32_t a_lo = a_lo_patch + tap16[t];
+            const uint32_t b_lo = b_lo0 + b_cur16;
 #pragma unroll
             for (int k = 0; k < BK / kUmmaK; ++k)
-              umma_f16(tmem_d, adesc + uint64_t(2 * k), bdesc + b_step * uint64_t(k), idesc, (cb | t | k) != 0 ? 1u : 0u);
-            if (!resident) umma_commit(smem_u32(&empty_b[sb]));
+              umma_f16_split(tmem_d, a_lo + uint32_t(2 * k), a_hi, b_lo + b_step * uint32_t(k), b_hi, idesc,
+                             (cb | t | k) != 0 ? 1u : 0u);
+            if (resident) {
+              b_cur16 += uint32_t(cblocks) * kB16;
+            } else {
+              umma_commit(empty_b0 + 8u * uint32_t(sb));
+              b_cur16 += kB16;
+              if (++sb == SB) { sb = 0; phb ^= 1; b_cur16 = stage_b16; }
+            }
           }
-          if (ok) umma_commit(smem_u32(&empty_a[sa]));
-          if (++sa == SA) { sa = 0; pha ^= 1; }
+          if (ok) umma_commit(empty_a0 + 8u * uint32_t(sa));
+          a_cur16 += slot_a16;
+          if (++sa == SA) { sa = 0; pha ^= 1; a_cur16 = stage_a16; }
         }
         if (ok) umma_commit(smem_u32(&acc_full[acc]));
         if (local < 4) HTRACE(2 + local);

@@ -661,6 +661,238 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
   if (threadIdx.x == 0 && failed_s && status != nullptr) atomicExch(status, 1u);
 }
 
+// ------------------------------------------------------------------------------------------ //
+// Two-SM variant (tcgen05 cta_group::2): a cluster of two CTAs owns a 256 x 256 output tile.  Each CTA loads its
+// own 128 rows of A and HALF of B (128 of the 256 columns) per ring stage; one thread of the leader CTA issues
+// 256 x 256 x 16 MMAs that read A from each CTA's own shared memory and both halves of B, and leave 128 rows of
+// the accumulator in each CTA's tensor memory.  Per SM and MMA that is 4 KB of A and 4 KB of B out of shared
+// memory instead of 4 + 8: a 128 x 256 tile on one SM reads (and TMA writes) more than the 128 bytes per clock an
+// SM's shared memory has, which is what held the one-SM kernel at 0.84 of the library on large products.
+//   loads     : cp.async.bulk.tensor with .cta_group::2 (no multicast): data lands in the issuing CTA, the byte
+//               count is signalled on the LEADER's full barrier, which expects both CTAs' bytes;
+//   empty/acc : tcgen05.commit.cta_group::2 ... multicast::cluster arrives on the barrier at the same offset in
+//               both CTAs (ring slots free, accumulator complete);
+//   acc_empty : the four epilogue warps of both CTAs arrive on the leader's barrier (count 8, remote arrive).
+// Every wait is bounded.  Epilogue: plain product with optional bias and activation, leaving through TMA stores.
+// BMODE as in the one-SM kernel (1: B is [K, N] row-major, consumed MN-major).
+// ------------------------------------------------------------------------------------------ //
+struct PairCfg {
+  static constexpr int kBN = 256, kHalfN = 128, kStages = 6;
+  static constexpr uint32_t kBytesA = BM * BK * 2;
+  static constexpr uint32_t kBytesB = kHalfN * BK * 2;
+  static constexpr uint32_t kBytesStage = kBytesA + kBytesB;
+  static constexpr uint32_t kCols = 2 * kBN;
+  static constexpr uint32_t kBytesOutBox = 32 * 64 * 2;
+  static constexpr uint32_t kBytesOut = 4 * 2 * kBytesOutBox;
+  static constexpr size_t kSmem = 1024 + size_t(kStages) * kBytesStage + kBytesOut + 256;
+  // D fp32, A and B bf16, N = 256, M = 256 (the pair's tile)
+  static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kBN >> 3) << 17) | (uint32_t(256 >> 4) << 24);
+};
+
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((unsigned short)3)
+      : "memory");
+}
+
+template <int BMODE>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const __grid_constant__ CUtensorMap map_c, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
+                      int act, unsigned int* __restrict__ status) {
+  using Cfg = PairCfg;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* stage_a = smem;
+  unsigned char* stage_b = smem + size_t(S) * Cfg::kBytesA;
+  unsigned char* stage_out = smem + size_t(S) * Cfg::kBytesStage;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + Cfg::kBytesOut);
+  // bars[0..S): full (used in the leader), [S..2S): empty, [2S..2S+2): acc_full, [2S+2..2S+4): acc_empty (leader)
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int failed_s;
+  volatile int* failed = &failed_s;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int tiles_n = (N + Cfg::kBN - 1) / Cfg::kBN;
+  const int tiles_m = (M + 255) / 256;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+  const int first_tile = int(blockIdx.x >> 1), tile_step = int(gridDim.x >> 1);
+
+  if (threadIdx.x == 0) {
+    failed_s = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&bars[s]), 1);            // the leader's producer arrives once and expects both CTAs' bytes
+      mbar_init(smem_u32(&bars[S + s]), 1);        // one tcgen05.commit (multicast to both CTAs)
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bars[2 * S + a]), 1);        // one tcgen05.commit
+      mbar_init(smem_u32(&bars[2 * S + 2 + a]), 8);    // four epilogue warps of each CTA
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(Cfg::kCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  // nobody signals a peer's barrier before the peer has initialised it
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+
+  int armed = 0;
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * 256 + int(rank) * BM;
+        const int nb0 = tn * Cfg::kBN + int(rank) * Cfg::kHalfN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % S;
+          if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, failed)) { ok = false; break; }
+          if (leader) mbar_expect_tx(smem_u32(&bars[s]), 2 * Cfg::kBytesStage);
+          const uint32_t full = mapa_u32(smem_u32(&bars[s]), 0u);
+          tma_load_2d_pair(smem_u32(stage_a + size_t(s) * Cfg::kBytesA), &map_a, full, kb * BK, m0);
+          if (BMODE == 0) {
+            tma_load_2d_pair(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), &map_b, full, kb * BK, nb0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < Cfg::kHalfN / 64; ++j)
+              tma_load_2d_pair(smem_u32(stage_b + size_t(s) * Cfg::kBytesB + size_t(j) * 8192), &map_b, full, nb0 + j * 64, kb * BK);
+          }
+          armed = it + 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local) {
+        const int acc = local & 1;
+        // both CTAs' epilogues must have drained this accumulator buffer
+        if (!mbar_wait_cluster(smem_u32(&bars[2 * S + 2 + acc]), ((local >> 1) & 1) ^ 1, failed)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + uint32_t(acc * Cfg::kBN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % S;
+          if (!mbar_wait(smem_u32(&bars[s]), (it / S) & 1, failed)) { ok = false; break; }
+          const uint64_t adesc = make_desc(smem_u32(stage_a + size_t(s) * Cfg::kBytesA));
+          const uint32_t b_addr = smem_u32(stage_b + size_t(s) * Cfg::kBytesB);
+          const uint64_t bdesc = BMODE == 0 ? make_desc(b_addr) : make_desc_mn(b_addr, 8192, 1024);
+          constexpr uint32_t idesc = Cfg::kIdesc | (BMODE != 0 ? (1u << 16) : 0u);
+          constexpr uint64_t b_step = BMODE == 0 ? 2 : (16 * 128) >> 4;
+#pragma unroll
+          for (int k = 0; k < BK / kUmmaK; ++k) {
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "setp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+                ::"r"(tmem_d), "l"(adesc + uint64_t(2 * k)), "l"(bdesc + b_step * uint64_t(k)), "r"(idesc),
+                  "r"((kb | k) != 0 ? 1u : 0u), "r"(0u)
+                : "memory");
+          }
+          umma_commit_pair(smem_u32(&bars[S + s]));
+        }
+        if (ok) umma_commit_pair(smem_u32(&bars[2 * S + acc]));
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    unsigned char* my_out = stage_out + size_t(q) * 2 * Cfg::kBytesOutBox;
+    int local = 0;
+    int boxes = 0;
+    for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++local) {
+      const int acc = local & 1;
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * 256 + int(rank) * BM;
+      const int n0 = tn * Cfg::kBN;
+      if (!mbar_wait(smem_u32(&bars[2 * S + acc]), (local >> 1) & 1, failed)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int c = 0; c < Cfg::kBN / 64; ++c) {
+        const int nbase = n0 + c * 64;
+        if (nbase >= N || m0 + q * 32 >= M) break;           // warp-uniform
+        uint32_t r[64];
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * Cfg::kBN + c * 64);
+        tmem_ld32(taddr, r);
+        tmem_ld32(taddr + 32, r + 32);
+        if (lane == 0) tma_store_wait_read<1>();
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        __syncwarp();
+        unsigned char* box = my_out + size_t(boxes & 1) * Cfg::kBytesOutBox;
+        unsigned char* row = box + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float x = __uint_as_float(r[j * 8 + i]);
+            if (bias != nullptr) {
+              const int n = nbase + j * 8 + i;
+              x += n < N ? __bfloat162float(bias[n]) : 0.f;
+            }
+            v[i] = act_fn(x, act);
+          }
+          uint4 pk;
+          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+          *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = pk;      // 128-byte swizzle
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&map_c, smem_u32(box), nbase, m0 + q * 32);
+          tma_store_commit();
+        }
+        ++boxes;
+      }
+      // hand the accumulator buffer back: the leader's MMA thread waits for all eight epilogue warps of the pair
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars[2 * S + 2 + acc]), 0u));
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+  if (warp == 0 && lane == 0 && *failed && leader) {
+    const int first = armed > S ? armed - S : 0;
+    for (int it = first; it < armed; ++it) {
+      const unsigned long long t0 = now_ns();
+      while (!mbar_try(smem_u32(&bars[it % S]), (it / S) & 1) && now_ns() - t0 < kWaitLimitNs) {}
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  // neither CTA leaves (or frees tensor memory) while the other may still read its shared memory or signal it
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kCols) : "memory");
+  }
+  if (threadIdx.x == 0 && failed_s && status != nullptr) atomicExch(status, 1u);
+}
+
 bool MakeMap(CUtensorMap* map, const void* base, int rows, int cols /*K*/, int box_rows) {
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
@@ -686,6 +918,51 @@ cudaError_t LaunchPersistent(const CUtensorMap& map_a, const CUtensorMap& map_b,
   kernel<<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(map_a, map_b, map_c, out, bias, M, N, K, act,
                                                                              tma_out, status, map_aux, aux_in, col_stats);
   return cudaSuccess;
+}
+
+// Launches the two-SM kernel on clusters of two CTAs, one cluster per 256 x 256 output tile at a time.
+template <int BMODE>
+cudaError_t LaunchPair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const __nv_bfloat16* bias,
+                       int M, int N, int K, int act, int sm_count, unsigned int* status, cudaStream_t stream) {
+  auto kernel = gemm_bf16_pair_kernel<BMODE>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PairCfg::kSmem));
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const int tiles = ((M + 255) / 256) * ((N + PairCfg::kBN - 1) / PairCfg::kBN);
+  const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = PairCfg::kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, bias, M, N, K, act, status);
+}
+
+// Whether a plain product goes to the two-SM kernel: TMA-storable output, at least one full pair tile in each
+// direction, enough tiles to occupy the pairs, and a reduction long enough for the main loop to matter (measured:
+// +8 % at 8192^3, +11 % on 8192 x 50304 x 1024, +4-5 % on GPT-2's 8192 x {1024, 3072, 4096} x {1024, 4096}; with
+// K <= 256 the product is bound by its epilogue and the larger tile is 20-30 % slower).
+// BLUEFOG_B200_GEMM_PAIR=0 keeps everything on the one-SM kernel, =1 sends every eligible shape to the pair.
+bool UsePair(int M, int N, int K, int sm_count) {
+  static const int mode = [] {
+    const char* v = std::getenv("BLUEFOG_B200_GEMM_PAIR");
+    return v == nullptr ? -1 : std::atoi(v);
+  }();
+  if (mode == 0) return false;
+  if ((N % 8) != 0 || N < 256 || M < 256) return false;
+  if (mode > 0) return true;
+  const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+  return K >= 1024 && tiles >= sm_count / 4;
 }
 
 int SmCount() {
@@ -750,6 +1027,9 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     gemm_bf16_nt_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, o, bp, M, N, K, act, status);
+  } else if (!preact && tma_out && UsePair(M, N, K, sm_count)) {
+    if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, PairCfg::kHalfN)) return cudaErrorInvalidValue;
+    e = LaunchPair<0>(map_a, map_b, map_c, bp, M, N, K, act, sm_count, status, stream);
   } else if (N > 128) {
     if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, 256)) return cudaErrorInvalidValue;
     e = preact ? LaunchPersistent<256, 0, 0, kEpiStorePreact>(map_a, map_b, map_c, map_aux, o, bp, nullptr, M, N, K, act, tma_out,
@@ -787,7 +1067,9 @@ cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
   const __nv_bfloat16* aux = static_cast<const __nv_bfloat16*>(gelu_preact);
   cudaError_t e;
-  if (addend != nullptr) {
+  if (addend == nullptr && aux == nullptr && UsePair(M, N, K, sm_count)) {
+    e = LaunchPair<1>(map_a, map_b, map_c, nullptr, M, N, K, 0, sm_count, status, stream);
+  } else if (addend != nullptr) {
     const __nv_bfloat16* add = static_cast<const __nv_bfloat16*>(addend);
     e = N > 128 ? LaunchPersistent<256, 1, 0, kEpiAddAux>(map_a, map_b, map_c, map_c, o, nullptr, add, M, N, K, 0, 1, sm_count,
                                                           status, stream)

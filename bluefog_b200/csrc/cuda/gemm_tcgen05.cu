@@ -239,6 +239,33 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 
 // ------------------------------------------------------------------------------------------ //
+// Two-SM variant (tcgen05 cta_group::2): a cluster of two CTAs owns a 256 x 256 output tile.  Each CTA loads its
+// own 128 rows of A and HALF of B (128 of the 256 columns) per ring stage; one thread of the leader CTA issues
+// 256 x 256 x 16 MMAs that read A from each CTA's own shared memory and both halves of B, and leave 128 rows of
+// the accumulator in each CTA's tensor memory.  Per SM and MMA that is 4 KB of A and 4 KB of B out of shared
+// memory instead of 4 + 8: a 128 x 256 tile on one SM reads (and TMA writes) more than the 128 bytes per clock an
+// SM's shared memory has, which is what held the one-SM kernel at 0.84 of the library on large products.
+//   loads     : cp.async.bulk.tensor with .cta_group::2 (no multicast): data lands in the issuing CTA, the byte
+//               count is signalled on the LEADER's full barrier, which expects both CTAs' bytes;
+//   empty/acc : tcgen05.commit.cta_group::2 ... multicast::cluster arrives on the barrier at the same offset in
+//               both CTAs (ring slots free, accumulator complete);
+//   acc_empty : the four epilogue warps of both CTAs arrive on the leader's barrier (count 8, remote arrive).
+// Every wait is bounded.  It is the PAIR mode of the persistent kernel below, so every operand mode and epilogue has it.
+// ------------------------------------------------------------------------------------------ //
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((unsigned short)3)
+      : "memory");
+}
+
+// ------------------------------------------------------------------------------------------ //
 // Persistent variant: one CTA per SM walks over output tiles of 128 x BN_; the accumulator is
 // double-buffered in tensor memory (2 x BN_ columns) so that the epilogue of tile i runs while
 // the MMAs of tile i+1 are issued.  Ring-stage and accumulator hand-over use four kinds of
@@ -249,21 +276,25 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // tile edges are clipped by the tensor map.  Row pitches that TMA cannot address (N % 8 != 0)
 // take the direct-store epilogue.
 // ------------------------------------------------------------------------------------------ //
-template <int BN_, int EPI = 0>
+template <int BN_, int EPI = 0, int PAIR = 0>
 struct PersistentCfg {
+  // PAIR: two CTAs of a cluster share a (2 * BM) x BN_ tile (tcgen05 cta_group::2); each holds its 128 rows of A and
+  // half of B, so a stage is smaller and the ring deeper.
   // the column-statistics epilogue gives one ring stage up for its per-warp partial sums
-  static constexpr int kStagesP = ((BN_ == 256) ? 4 : 6) - (EPI == kEpiColumnStats ? 1 : 0);
+  static constexpr int kStagesP = (PAIR ? 6 : ((BN_ == 256) ? 4 : 6)) - (EPI == kEpiColumnStats ? 1 : 0);
   // per epilogue warp: BN_ column sums and BN_ sums of squares
   static constexpr uint32_t kStatBytes = EPI == kEpiColumnStats ? 4 * 2 * BN_ * 4 : 0;
+  static constexpr int kRowsB = PAIR ? BN_ / 2 : BN_;          // rows (output columns) of B one CTA loads
+  static constexpr int kTileM = PAIR ? 2 * BM : BM;
   static constexpr uint32_t kBytesA = BM * BK * 2;
-  static constexpr uint32_t kBytesB = BN_ * BK * 2;
+  static constexpr uint32_t kBytesB = kRowsB * BK * 2;
   static constexpr uint32_t kBytesStage = kBytesA + kBytesB;
   static constexpr uint32_t kCols = 2 * BN_;
   // output staging: per epilogue warp two [32 rows x 64 columns] bf16 boxes (4 KiB each, 1024-byte aligned)
   static constexpr uint32_t kBytesOutBox = 32 * 64 * 2;
   static constexpr uint32_t kBytesOut = 4 * 2 * kBytesOutBox;
   static constexpr size_t kSmem = 1024 + size_t(kStagesP) * kBytesStage + kBytesOut + 256 + kStatBytes;
-  static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN_ >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+  static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN_ >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
 };
 
 // BMODE 0: B is [N, K] row-major (K-major operand).  BMODE 1: B is [K, N] row-major and is consumed as an
@@ -274,14 +305,17 @@ struct PersistentCfg {
 // consumed MN-major in the same way: two boxes of [64 K-rows x 64 M-columns] per stage, bit 15 of the
 // instruction descriptor.
 // EPI (GemmEpi) is a template parameter so that the plain epilogue keeps its small register footprint.
-template <int BN_, int BMODE = 0, int AMODE = 0, int EPI = 0>
+// PAIR 1: launched as clusters of two CTAs (see the two-SM notes above): loads signal the
+// leader's full barrier, commits are multicast to both CTAs, the leader's MMA thread issues cta_group::2 MMAs and
+// waits for the epilogue warps of both CTAs.
+template <int BN_, int BMODE = 0, int AMODE = 0, int EPI = 0, int PAIR = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ out,
                                const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int act, int tma_out,
                                unsigned int* __restrict__ status, const __grid_constant__ CUtensorMap map_aux,
                                const __nv_bfloat16* __restrict__ aux_in, float* __restrict__ col_stats) {
-  using Cfg = PersistentCfg<BN_, EPI>;
+  using Cfg = PersistentCfg<BN_, EPI, PAIR>;
   constexpr int S = Cfg::kStagesP;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -296,10 +330,14 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
   const int tiles_n = (N + BN_ - 1) / BN_;
-  const int tiles_m = (M + BM - 1) / BM;
+  const int tiles_m = (M + Cfg::kTileM - 1) / Cfg::kTileM;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
+  const int first_tile = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x);
+  const int tile_step = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);
 
   if (threadIdx.x == 0) {
     failed_s = 0;
@@ -309,17 +347,27 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bars[2 * S + a]), 1);        // one tcgen05.commit
-      mbar_init(smem_u32(&bars[2 * S + 2 + a]), 4);    // one arrive per epilogue warp
+      mbar_init(smem_u32(&bars[2 * S + 2 + a]), PAIR ? 8 : 4);    // one arrive per epilogue warp (of both CTAs)
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(Cfg::kCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(Cfg::kCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(Cfg::kCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (PAIR) {
+    // nobody signals a peer's barrier before the peer has initialised it
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_s;
 
@@ -328,42 +376,48 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
-        const int m0 = tm * BM;
-        const int n0 = tn * BN_;
+        const int m0 = tm * Cfg::kTileM + int(rank) * BM;
+        const int n0 = tn * BN_ + int(rank) * Cfg::kRowsB;          // PAIR: this CTA's half of the tile's columns
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % S;
           if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, failed)) { ok = false; break; }
-          const uint32_t full = smem_u32(&bars[s]);
-          mbar_expect_tx(full, Cfg::kBytesStage);
+          // PAIR: the leader's barrier counts the bytes of both CTAs; the leader arms it
+          if (leader) mbar_expect_tx(smem_u32(&bars[s]), (PAIR ? 2u : 1u) * Cfg::kBytesStage);
+          const uint32_t full = PAIR ? mapa_u32(smem_u32(&bars[s]), 0u) : smem_u32(&bars[s]);
+          auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y) {
+            if (PAIR) tma_load_2d_pair(dst, map, full, x, y);
+            else tma_load_2d(dst, map, full, x, y);
+          };
           if (AMODE == 0) {
-            tma_load_2d(smem_u32(stage_a + size_t(s) * Cfg::kBytesA), &map_a, full, kb * BK, m0);
+            load(smem_u32(stage_a + size_t(s) * Cfg::kBytesA), &map_a, kb * BK, m0);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d(smem_u32(stage_a + size_t(s) * Cfg::kBytesA + size_t(j) * 8192), &map_a, full, m0 + j * 64, kb * BK);
+              load(smem_u32(stage_a + size_t(s) * Cfg::kBytesA + size_t(j) * 8192), &map_a, m0 + j * 64, kb * BK);
           }
           if (BMODE == 0) {
-            tma_load_2d(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), &map_b, full, kb * BK, n0);
+            load(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), &map_b, kb * BK, n0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN_ / 64; ++j)
-              tma_load_2d(smem_u32(stage_b + size_t(s) * Cfg::kBytesB + size_t(j) * 8192), &map_b, full, n0 + j * 64, kb * BK);
+            for (int j = 0; j < Cfg::kRowsB / 64; ++j)
+              load(smem_u32(stage_b + size_t(s) * Cfg::kBytesB + size_t(j) * 8192), &map_b, n0 + j * 64, kb * BK);
           }
           armed = it + 1;
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       int it = 0, local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local) {
         const int acc = local & 1;
-        // the epilogue must have drained this accumulator buffer (tile local-2)
-        if (!mbar_wait(smem_u32(&bars[2 * S + 2 + acc]), ((local >> 1) & 1) ^ 1, failed)) { ok = false; break; }
+        // the epilogue (of both CTAs) must have drained this accumulator buffer (tile local-2)
+        if (!(PAIR ? mbar_wait_cluster(smem_u32(&bars[2 * S + 2 + acc]), ((local >> 1) & 1) ^ 1, failed)
+                   : mbar_wait(smem_u32(&bars[2 * S + 2 + acc]), ((local >> 1) & 1) ^ 1, failed))) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + uint32_t(acc * BN_);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -381,17 +435,31 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
           constexpr uint64_t b_step = BMODE == 0 ? 2 : (16 * 128) >> 4;
 #pragma unroll
           for (int k = 0; k < BK / kUmmaK; ++k) {
-            asm volatile(
-                "{\n\t.reg .pred p;\n\t"
-                "setp.ne.b32 p, %4, 0;\n\t"
-                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                ::"r"(tmem_d), "l"(adesc + a_step * uint64_t(k)), "l"(bdesc + b_step * uint64_t(k)), "r"(idesc),
-                  "r"((kb | k) != 0 ? 1u : 0u)
-                : "memory");
+            if (PAIR) {
+              asm volatile(
+                  "{\n\t.reg .pred p;\n\t"
+                  "setp.ne.b32 p, %4, 0;\n\t"
+                  "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+                  ::"r"(tmem_d), "l"(adesc + a_step * uint64_t(k)), "l"(bdesc + b_step * uint64_t(k)), "r"(idesc),
+                    "r"((kb | k) != 0 ? 1u : 0u), "r"(0u)
+                  : "memory");
+            } else {
+              asm volatile(
+                  "{\n\t.reg .pred p;\n\t"
+                  "setp.ne.b32 p, %4, 0;\n\t"
+                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                  ::"r"(tmem_d), "l"(adesc + a_step * uint64_t(k)), "l"(bdesc + b_step * uint64_t(k)), "r"(idesc),
+                    "r"((kb | k) != 0 ? 1u : 0u)
+                  : "memory");
+            }
           }
-          umma_commit(smem_u32(&bars[S + s]));
+          if (PAIR) umma_commit_pair(smem_u32(&bars[S + s]));
+          else umma_commit(smem_u32(&bars[S + s]));
         }
-        if (ok) umma_commit(smem_u32(&bars[2 * S + acc]));
+        if (ok) {
+          if (PAIR) umma_commit_pair(smem_u32(&bars[2 * S + acc]));
+          else umma_commit(smem_u32(&bars[2 * S + acc]));
+        }
       }
     }
   } else {
@@ -428,11 +496,11 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
       for (int i = lane; i < 2 * BN_; i += 32) wstat[i] = 0.f;
       __syncwarp();
     }
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+    for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++local) {
       const int acc = local & 1;
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
-      const int m0 = tm * BM;
+      const int m0 = tm * Cfg::kTileM + int(rank) * BM;         // this CTA's 128 rows, all BN_ columns
       const int n0 = tn * BN_;
       if (!mbar_wait(smem_u32(&bars[2 * S + acc]), (local >> 1) & 1, failed)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -639,239 +707,13 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
       // hand the accumulator buffer back to the MMA warp
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars[2 * S + 2 + acc])) : "memory");
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&bars[2 * S + 2 + acc]), 0u));
+        else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars[2 * S + 2 + acc])) : "memory");
+      }
     }
     if constexpr (EPI == kEpiColumnStats) flush_stats();
     // the stores of this warp must be complete before its shared memory goes away
-    if (lane == 0) tma_store_wait_all();
-  }
-  if (warp == 0 && lane == 0 && *failed) {
-    const int first = armed > S ? armed - S : 0;
-    for (int it = first; it < armed; ++it) {
-      const unsigned long long t0 = now_ns();
-      while (!mbar_try(smem_u32(&bars[it % S]), (it / S) & 1) && now_ns() - t0 < kWaitLimitNs) {}
-    }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 1) {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kCols) : "memory");
-  }
-  if (threadIdx.x == 0 && failed_s && status != nullptr) atomicExch(status, 1u);
-}
-
-// ------------------------------------------------------------------------------------------ //
-// Two-SM variant (tcgen05 cta_group::2): a cluster of two CTAs owns a 256 x 256 output tile.  Each CTA loads its
-// own 128 rows of A and HALF of B (128 of the 256 columns) per ring stage; one thread of the leader CTA issues
-// 256 x 256 x 16 MMAs that read A from each CTA's own shared memory and both halves of B, and leave 128 rows of
-// the accumulator in each CTA's tensor memory.  Per SM and MMA that is 4 KB of A and 4 KB of B out of shared
-// memory instead of 4 + 8: a 128 x 256 tile on one SM reads (and TMA writes) more than the 128 bytes per clock an
-// SM's shared memory has, which is what held the one-SM kernel at 0.84 of the library on large products.
-//   loads     : cp.async.bulk.tensor with .cta_group::2 (no multicast): data lands in the issuing CTA, the byte
-//               count is signalled on the LEADER's full barrier, which expects both CTAs' bytes;
-//   empty/acc : tcgen05.commit.cta_group::2 ... multicast::cluster arrives on the barrier at the same offset in
-//               both CTAs (ring slots free, accumulator complete);
-//   acc_empty : the four epilogue warps of both CTAs arrive on the leader's barrier (count 8, remote arrive).
-// Every wait is bounded.  Epilogue: plain product with optional bias and activation, leaving through TMA stores.
-// BMODE as in the one-SM kernel (1: B is [K, N] row-major, consumed MN-major).
-// ------------------------------------------------------------------------------------------ //
-struct PairCfg {
-  static constexpr int kBN = 256, kHalfN = 128, kStages = 6;
-  static constexpr uint32_t kBytesA = BM * BK * 2;
-  static constexpr uint32_t kBytesB = kHalfN * BK * 2;
-  static constexpr uint32_t kBytesStage = kBytesA + kBytesB;
-  static constexpr uint32_t kCols = 2 * kBN;
-  static constexpr uint32_t kBytesOutBox = 32 * 64 * 2;
-  static constexpr uint32_t kBytesOut = 4 * 2 * kBytesOutBox;
-  static constexpr size_t kSmem = 1024 + size_t(kStages) * kBytesStage + kBytesOut + 256;
-  // D fp32, A and B bf16, N = 256, M = 256 (the pair's tile)
-  static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kBN >> 3) << 17) | (uint32_t(256 >> 4) << 24);
-};
-
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-      ::"r"(bar), "h"((unsigned short)3)
-      : "memory");
-}
-
-template <int BMODE>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                      const __grid_constant__ CUtensorMap map_c, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
-                      int act, unsigned int* __restrict__ status) {
-  using Cfg = PairCfg;
-  constexpr int S = Cfg::kStages;
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* stage_a = smem;
-  unsigned char* stage_b = smem + size_t(S) * Cfg::kBytesA;
-  unsigned char* stage_out = smem + size_t(S) * Cfg::kBytesStage;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + Cfg::kBytesOut);
-  // bars[0..S): full (used in the leader), [S..2S): empty, [2S..2S+2): acc_full, [2S+2..2S+4): acc_empty (leader)
-  __shared__ uint32_t tmem_base_s;
-  __shared__ int failed_s;
-  volatile int* failed = &failed_s;
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();
-  const bool leader = rank == 0;
-  const int tiles_n = (N + Cfg::kBN - 1) / Cfg::kBN;
-  const int tiles_m = (M + 255) / 256;
-  const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (K + BK - 1) / BK;
-  const int first_tile = int(blockIdx.x >> 1), tile_step = int(gridDim.x >> 1);
-
-  if (threadIdx.x == 0) {
-    failed_s = 0;
-    for (int s = 0; s < S; ++s) {
-      mbar_init(smem_u32(&bars[s]), 1);            // the leader's producer arrives once and expects both CTAs' bytes
-      mbar_init(smem_u32(&bars[S + s]), 1);        // one tcgen05.commit (multicast to both CTAs)
-    }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(smem_u32(&bars[2 * S + a]), 1);        // one tcgen05.commit
-      mbar_init(smem_u32(&bars[2 * S + 2 + a]), 8);    // four epilogue warps of each CTA
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(Cfg::kCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  // nobody signals a peer's barrier before the peer has initialised it
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = tmem_base_s;
-
-  int armed = 0;
-  if (warp == 0) {
-    if (lane == 0) {
-      int it = 0;
-      bool ok = true;
-      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-        int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
-        const int m0 = tm * 256 + int(rank) * BM;
-        const int nb0 = tn * Cfg::kBN + int(rank) * Cfg::kHalfN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % S;
-          if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, failed)) { ok = false; break; }
-          if (leader) mbar_expect_tx(smem_u32(&bars[s]), 2 * Cfg::kBytesStage);
-          const uint32_t full = mapa_u32(smem_u32(&bars[s]), 0u);
-          tma_load_2d_pair(smem_u32(stage_a + size_t(s) * Cfg::kBytesA), &map_a, full, kb * BK, m0);
-          if (BMODE == 0) {
-            tma_load_2d_pair(smem_u32(stage_b + size_t(s) * Cfg::kBytesB), &map_b, full, kb * BK, nb0);
-          } else {
-#pragma unroll
-            for (int j = 0; j < Cfg::kHalfN / 64; ++j)
-              tma_load_2d_pair(smem_u32(stage_b + size_t(s) * Cfg::kBytesB + size_t(j) * 8192), &map_b, full, nb0 + j * 64, kb * BK);
-          }
-          armed = it + 1;
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0 && leader) {
-      int it = 0, local = 0;
-      bool ok = true;
-      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local) {
-        const int acc = local & 1;
-        // both CTAs' epilogues must have drained this accumulator buffer
-        if (!mbar_wait_cluster(smem_u32(&bars[2 * S + 2 + acc]), ((local >> 1) & 1) ^ 1, failed)) { ok = false; break; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t tmem_d = tmem_base + uint32_t(acc * Cfg::kBN);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % S;
-          if (!mbar_wait(smem_u32(&bars[s]), (it / S) & 1, failed)) { ok = false; break; }
-          const uint64_t adesc = make_desc(smem_u32(stage_a + size_t(s) * Cfg::kBytesA));
-          const uint32_t b_addr = smem_u32(stage_b + size_t(s) * Cfg::kBytesB);
-          const uint64_t bdesc = BMODE == 0 ? make_desc(b_addr) : make_desc_mn(b_addr, 8192, 1024);
-          constexpr uint32_t idesc = Cfg::kIdesc | (BMODE != 0 ? (1u << 16) : 0u);
-          constexpr uint64_t b_step = BMODE == 0 ? 2 : (16 * 128) >> 4;
-#pragma unroll
-          for (int k = 0; k < BK / kUmmaK; ++k) {
-            asm volatile(
-                "{\n\t.reg .pred p;\n\t"
-                "setp.ne.b32 p, %4, 0;\n\t"
-                "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
-                ::"r"(tmem_d), "l"(adesc + uint64_t(2 * k)), "l"(bdesc + b_step * uint64_t(k)), "r"(idesc),
-                  "r"((kb | k) != 0 ? 1u : 0u), "r"(0u)
-                : "memory");
-          }
-          umma_commit_pair(smem_u32(&bars[S + s]));
-        }
-        if (ok) umma_commit_pair(smem_u32(&bars[2 * S + acc]));
-      }
-    }
-  } else {
-    const int q = warp & 3;
-    unsigned char* my_out = stage_out + size_t(q) * 2 * Cfg::kBytesOutBox;
-    int local = 0;
-    int boxes = 0;
-    for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++local) {
-      const int acc = local & 1;
-      int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
-      const int m0 = tm * 256 + int(rank) * BM;
-      const int n0 = tn * Cfg::kBN;
-      if (!mbar_wait(smem_u32(&bars[2 * S + acc]), (local >> 1) & 1, failed)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-      for (int c = 0; c < Cfg::kBN / 64; ++c) {
-        const int nbase = n0 + c * 64;
-        if (nbase >= N || m0 + q * 32 >= M) break;           // warp-uniform
-        uint32_t r[64];
-        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * Cfg::kBN + c * 64);
-        tmem_ld32(taddr, r);
-        tmem_ld32(taddr + 32, r + 32);
-        if (lane == 0) tma_store_wait_read<1>();
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        __syncwarp();
-        unsigned char* box = my_out + size_t(boxes & 1) * Cfg::kBytesOutBox;
-        unsigned char* row = box + lane * 128;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float v[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float x = __uint_as_float(r[j * 8 + i]);
-            if (bias != nullptr) {
-              const int n = nbase + j * 8 + i;
-              x += n < N ? __bfloat162float(bias[n]) : 0.f;
-            }
-            v[i] = act_fn(x, act);
-          }
-          uint4 pk;
-          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-          *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = pk;      // 128-byte swizzle
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_2d(&map_c, smem_u32(box), nbase, m0 + q * 32);
-          tma_store_commit();
-        }
-        ++boxes;
-      }
-      // hand the accumulator buffer back: the leader's MMA thread waits for all eight epilogue warps of the pair
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars[2 * S + 2 + acc]), 0u));
-    }
     if (lane == 0) tma_store_wait_all();
   }
   if (warp == 0 && lane == 0 && *failed && leader) {
@@ -883,12 +725,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  // neither CTA leaves (or frees tensor memory) while the other may still read its shared memory or signal it
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (PAIR) {
+    // neither CTA leaves (or frees tensor memory) while the other may still read its shared memory or signal it
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kCols) : "memory");
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kCols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kCols) : "memory");
   }
   if (threadIdx.x == 0 && failed_s && status != nullptr) atomicExch(status, 1u);
 }
@@ -900,43 +745,32 @@ bool MakeMap(CUtensorMap* map, const void* base, int rows, int cols /*K*/, int b
   return EncodeTiled(map, 2, base, dims, strides, box);
 }
 
-// Launches one instantiation of the persistent kernel on min(tiles, SMs) CTAs.
-template <int BN_, int BMODE, int AMODE, int EPI>
+// Launches one instantiation of the persistent kernel on min(tiles, SMs) CTAs; PAIR: on clusters of two CTAs, one
+// cluster per (2 * BM) x BN_ tile at a time.
+template <int BN_, int BMODE, int AMODE, int EPI, int PAIR = 0>
 cudaError_t LaunchPersistent(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
                              const CUtensorMap& map_aux, __nv_bfloat16* out, const __nv_bfloat16* bias,
                              const __nv_bfloat16* aux_in, int M, int N, int K, int act, int tma_out, int sm_count,
                              unsigned int* status, cudaStream_t stream, float* col_stats = nullptr) {
-  using Cfg = PersistentCfg<BN_, EPI>;
-  auto kernel = gemm_bf16_nt_persistent_kernel<BN_, BMODE, AMODE, EPI>;
+  using Cfg = PersistentCfg<BN_, EPI, PAIR>;
+  auto kernel = gemm_bf16_nt_persistent_kernel<BN_, BMODE, AMODE, EPI, PAIR>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem));
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN_ - 1) / BN_);
-  kernel<<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(map_a, map_b, map_c, out, bias, M, N, K, act,
-                                                                             tma_out, status, map_aux, aux_in, col_stats);
-  return cudaSuccess;
-}
-
-// Launches the two-SM kernel on clusters of two CTAs, one cluster per 256 x 256 output tile at a time.
-template <int BMODE>
-cudaError_t LaunchPair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const __nv_bfloat16* bias,
-                       int M, int N, int K, int act, int sm_count, unsigned int* status, cudaStream_t stream) {
-  auto kernel = gemm_bf16_pair_kernel<BMODE>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PairCfg::kSmem));
-    if (e != cudaSuccess) return e;
-    attr_set = true;
+  const int tiles = ((M + Cfg::kTileM - 1) / Cfg::kTileM) * ((N + BN_ - 1) / BN_);
+  if (!PAIR) {
+    kernel<<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(map_a, map_b, map_c, out, bias, M, N, K, act,
+                                                                               tma_out, status, map_aux, aux_in, col_stats);
+    return cudaSuccess;
   }
-  const int tiles = ((M + 255) / 256) * ((N + PairCfg::kBN - 1) / PairCfg::kBN);
   const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = PairCfg::kSmem;
+  cfg.dynamicSmemBytes = Cfg::kSmem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -945,7 +779,7 @@ cudaError_t LaunchPair(const CUtensorMap& map_a, const CUtensorMap& map_b, const
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, bias, M, N, K, act, status);
+  return cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, out, bias, M, N, K, act, tma_out, status, map_aux, aux_in, col_stats);
 }
 
 // Whether a plain product goes to the two-SM kernel: TMA-storable output, at least one full pair tile in each
@@ -1027,9 +861,12 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     gemm_bf16_nt_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, o, bp, M, N, K, act, status);
-  } else if (!preact && tma_out && UsePair(M, N, K, sm_count)) {
-    if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, PairCfg::kHalfN)) return cudaErrorInvalidValue;
-    e = LaunchPair<0>(map_a, map_b, map_c, bp, M, N, K, act, sm_count, status, stream);
+  } else if (tma_out && UsePair(M, N, K, sm_count)) {
+    if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, 128)) return cudaErrorInvalidValue;
+    e = preact ? LaunchPersistent<256, 0, 0, kEpiStorePreact, 1>(map_a, map_b, map_c, map_aux, o, bp, nullptr, M, N, K, act, 1,
+                                                                 sm_count, status, stream)
+               : LaunchPersistent<256, 0, 0, kEpiNone, 1>(map_a, map_b, map_c, map_aux, o, bp, nullptr, M, N, K, act, 1, sm_count,
+                                                          status, stream);
   } else if (N > 128) {
     if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, 256)) return cudaErrorInvalidValue;
     e = preact ? LaunchPersistent<256, 0, 0, kEpiStorePreact>(map_a, map_b, map_c, map_aux, o, bp, nullptr, M, N, K, act, tma_out,
@@ -1067,8 +904,16 @@ cudaError_t LaunchGemmBf16NN(const void* a, const void* b, void* out, int M, int
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
   const __nv_bfloat16* aux = static_cast<const __nv_bfloat16*>(gelu_preact);
   cudaError_t e;
-  if (addend == nullptr && aux == nullptr && UsePair(M, N, K, sm_count)) {
-    e = LaunchPair<1>(map_a, map_b, map_c, nullptr, M, N, K, 0, sm_count, status, stream);
+  if (UsePair(M, N, K, sm_count)) {
+    const __nv_bfloat16* add = static_cast<const __nv_bfloat16*>(addend);
+    if (add != nullptr)
+      e = LaunchPersistent<256, 1, 0, kEpiAddAux, 1>(map_a, map_b, map_c, map_c, o, nullptr, add, M, N, K, 0, 1, sm_count, status, stream);
+    else if (aux != nullptr)
+      e = LaunchPersistent<256, 1, 0, kEpiMulGeluGrad, 1>(map_a, map_b, map_c, map_c, o, nullptr, aux, M, N, K, 0, 1, sm_count, status,
+                                                          stream);
+    else
+      e = LaunchPersistent<256, 1, 0, kEpiNone, 1>(map_a, map_b, map_c, map_c, o, nullptr, nullptr, M, N, K, 0, 1, sm_count, status,
+                                                   stream);
   } else if (addend != nullptr) {
     const __nv_bfloat16* add = static_cast<const __nv_bfloat16*>(addend);
     e = N > 128 ? LaunchPersistent<256, 1, 0, kEpiAddAux>(map_a, map_b, map_c, map_c, o, nullptr, add, M, N, K, 0, 1, sm_count,
@@ -1106,7 +951,10 @@ cudaError_t LaunchGemmBf16TN(const void* a, const void* b, void* out, int M, int
     return cudaErrorInvalidValue;
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
   const cudaError_t e =
-      N > 128 ? LaunchPersistent<256, 1, 1, kEpiNone>(map_a, map_b, map_c, map_c, o, nullptr, nullptr, M, N, K, 0, 1, sm_count,
+      UsePair(M, N, K, sm_count)
+          ? LaunchPersistent<256, 1, 1, kEpiNone, 1>(map_a, map_b, map_c, map_c, o, nullptr, nullptr, M, N, K, 0, 1, sm_count, status,
+                                                     stream)
+      : N > 128 ? LaunchPersistent<256, 1, 1, kEpiNone>(map_a, map_b, map_c, map_c, o, nullptr, nullptr, M, N, K, 0, 1, sm_count,
                                                       status, stream)
               : LaunchPersistent<128, 1, 1, kEpiNone>(map_a, map_b, map_c, map_c, o, nullptr, nullptr, M, N, K, 0, 1, sm_count,
                                                       status, stream);

@@ -200,3 +200,36 @@ def test_batchnorm_fed_by_the_gemm_statistics_matches_its_own_pass():
                         bn.running_mean.clone(), bn.running_var.clone()))
     for got, want in zip(*results):
         assert (got - want).norm().item() <= 2e-2 * want.norm().item() + 1e-3
+
+
+def test_two_sm_mode_on_ragged_shapes_in_a_process_of_its_own():
+    """BLUEFOG_B200_GEMM_PAIR=1 sends every eligible product (M, N >= 256) to the cta_group::2 mode, also shapes
+    whose edges fall inside a 256 x 256 pair tile; the switch is read once per process, hence the child process."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import torch
+from bluefog_b200 import _C
+torch.manual_seed(5)
+for M, N, K in [(304, 264, 72), (1000, 520, 200), (520, 1032, 1024)]:
+    a = (torch.randn(M, K) * 0.5).cuda().to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.5).cuda().to(torch.bfloat16)
+    b = (torch.randn(K, N) * 0.5).cuda().to(torch.bfloat16)
+    bias = torch.randn(N).cuda().to(torch.bfloat16)
+    at = (torch.randn(K, M) * 0.5).cuda().to(torch.bfloat16)
+    cases = [(_C.gemm_bf16_nt(a, w, bias, 1), torch.relu(a.float() @ w.float().t() + bias.float())),
+             (_C.gemm_bf16_nn(a, b), a.float() @ b.float()),
+             (_C.gemm_bf16_tn(at, b), at.float().t() @ b.float())]
+    torch.cuda.synchronize()
+    assert _C.gemm_status() == 0
+    for out, ref in cases:
+        err = (out.float() - ref).abs().max().item()
+        assert err <= 1e-2 * ref.abs().max().item() + 1e-2, (M, N, K, err)
+print("ok")
+'''
+    env = dict(os.environ, BLUEFOG_B200_GEMM_PAIR="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stdout[-500:] + out.stderr[-1500:]

@@ -710,7 +710,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   // col_stats (optional, >= 2*N zero-initialised or running fp32 values): receives the column sums and sums of
   // squares of the rounded output, added by the GEMM epilogue (needs N % 8 == 0, no bias, act == 0)
   m.def("gemm_bf16_nt", [](at::Tensor a, at::Tensor w, c10::optional<at::Tensor> bias, int act,
-                           c10::optional<at::Tensor> col_stats) {
+                           c10::optional<at::Tensor> col_stats, c10::optional<at::Tensor> addend) {
     TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2, "gemm_bf16_nt expects 2-D CUDA tensors");
     TORCH_CHECK(a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "gemm_bf16_nt expects bf16");
     TORCH_CHECK(a.is_contiguous() && w.is_contiguous(), "gemm_bf16_nt expects contiguous tensors");
@@ -732,13 +732,22 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                   "col_stats needs 2*N 16-byte aligned fp32 values, N % 8 == 0, no bias and no activation");
       stats = col_stats->data_ptr<float>();
     }
+    const void* add = nullptr;
+    if (addend.has_value() && addend->defined()) {
+      // out = a w^T + bias + addend, the addend read in the epilogue
+      TORCH_CHECK(addend->is_cuda() && addend->scalar_type() == at::kBFloat16 && addend->is_contiguous() &&
+                  addend->dim() == 2 && addend->size(0) == a.size(0) && addend->size(1) == w.size(0) && w.size(0) % 8 == 0 &&
+                  act == 0 && stats == nullptr, "addend must be a contiguous bf16 [M, N] matrix, N % 8 == 0, no activation");
+      add = addend->data_ptr();
+    }
     cudaError_t e = LaunchGemmBf16NT(a.data_ptr(), w.data_ptr(), out.data_ptr(), bptr, static_cast<int>(a.size(0)),
                                      static_cast<int>(w.size(0)), static_cast<int>(a.size(1)), act,
                                      reinterpret_cast<unsigned int*>(status.data_ptr()), CurrentStream(a.get_device()),
-                                     nullptr, stats);
+                                     nullptr, stats, add);
     TORCH_CHECK(e == cudaSuccess, "gemm_bf16_nt launch failed: ", cudaGetErrorString(e));
     return out;
-  }, py::arg("a"), py::arg("w"), py::arg("bias") = py::none(), py::arg("act") = 0, py::arg("col_stats") = py::none());
+  }, py::arg("a"), py::arg("w"), py::arg("bias") = py::none(), py::arg("act") = 0, py::arg("col_stats") = py::none(),
+     py::arg("addend") = py::none());
 
   // ---- tcgen05 implicit-GEMM 3x3 convolution (stride 1, pad 1), NHWC bf16 ---------------------
   m.def("conv3x3_supported", [](int64_t n, int64_t h, int64_t w, int64_t cin, int64_t cout) {

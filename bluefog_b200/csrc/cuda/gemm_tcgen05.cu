@@ -608,8 +608,14 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
               for (int i = 0; i < 4; ++i) {
                 const float2 t2 = __bfloat1622float2(ah[i]);
                 if constexpr (EPI == kEpiAddAux) {
-                  v[2 * i] = __uint_as_float(r[j * 8 + 2 * i]) + t2.x;
-                  v[2 * i + 1] = __uint_as_float(r[j * 8 + 2 * i + 1]) + t2.y;
+                  float b0 = 0.f, b1 = 0.f;
+                  if (bias != nullptr) {                       // out = accumulator + bias + aux (a layer with a residual)
+                    const int n = nbase + j * 8 + 2 * i;
+                    b0 = n < N ? __bfloat162float(bias[n]) : 0.f;
+                    b1 = n + 1 < N ? __bfloat162float(bias[n + 1]) : 0.f;
+                  }
+                  v[2 * i] = __uint_as_float(r[j * 8 + 2 * i]) + b0 + t2.x;
+                  v[2 * i + 1] = __uint_as_float(r[j * 8 + 2 * i + 1]) + b1 + t2.y;
                 } else {
                   v[2 * i] = __uint_as_float(r[j * 8 + 2 * i]) * gelu_tanh_grad(t2.x);
                   v[2 * i + 1] = __uint_as_float(r[j * 8 + 2 * i + 1]) * gelu_tanh_grad(t2.y);
@@ -815,7 +821,8 @@ int SmCount() {
 bool GemmSupported() { return GetEncodeFn() != nullptr; }
 
 cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void* bias, int M, int N, int K, int act,
-                             unsigned int* status, cudaStream_t stream, void* preact_out, float* col_stats) {
+                             unsigned int* status, cudaStream_t stream, void* preact_out, float* col_stats,
+                             const void* addend) {
   (void)cudaGetLastError();   // the value returned below must be this launch's own, not an older error of the calling thread
   if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
   // TMA needs 16-byte aligned bases and row pitches: K must be a multiple of 8 bf16 elements.
@@ -842,7 +849,22 @@ cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void
     if (!MakeMap(&map_aux, preact_out, M, N, 32)) return cudaErrorInvalidValue;
   }
   cudaError_t e = cudaSuccess;
-  if (col_stats != nullptr) {
+  if (addend != nullptr) {
+    // out = a b^T + bias + addend (a layer whose output joins a residual stream): the addend is read in the epilogue
+    if (variant == 0 || !tma_out || preact || col_stats != nullptr || act != 0 || (reinterpret_cast<uintptr_t>(addend) & 15))
+      return cudaErrorInvalidValue;
+    const __nv_bfloat16* add = static_cast<const __nv_bfloat16*>(addend);
+    if (UsePair(M, N, K, sm_count)) {
+      if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, 128)) return cudaErrorInvalidValue;
+      e = LaunchPersistent<256, 0, 0, kEpiAddAux, 1>(map_a, map_b, map_c, map_c, o, bp, add, M, N, K, 0, 1, sm_count, status, stream);
+    } else if (N > 128) {
+      if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, 256)) return cudaErrorInvalidValue;
+      e = LaunchPersistent<256, 0, 0, kEpiAddAux>(map_a, map_b, map_c, map_c, o, bp, add, M, N, K, 0, 1, sm_count, status, stream);
+    } else {
+      if (!MakeMap(&map_a, a, M, K, BM) || !MakeMap(&map_b, b, N, K, 128)) return cudaErrorInvalidValue;
+      e = LaunchPersistent<128, 0, 0, kEpiAddAux>(map_a, map_b, map_c, map_c, o, bp, add, M, N, K, 0, 1, sm_count, status, stream);
+    }
+  } else if (col_stats != nullptr) {
     // column statistics of the plain product only: the kernel relies on rows past M being exact zeros
     if (variant == 0 || !tma_out || preact || bias != nullptr || act != 0) return cudaErrorInvalidValue;
     const int bn = N > 128 ? 256 : 128;

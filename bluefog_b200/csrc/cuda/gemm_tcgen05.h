@@ -22,7 +22,9 @@ bool GemmSupported();
 // normalisation layer, taken while the tile is still on chip).
 cudaError_t LaunchGemmBf16NT(const void* a, const void* b, void* out, const void* bias, int M, int N, int K, int act,
                              unsigned int* status, cudaStream_t stream, void* preact_out = nullptr,
-                             float* col_stats = nullptr);
+                             float* col_stats = nullptr, const void* addend = nullptr);
+// addend: bf16 [M, N] added to the product (and the bias) in the epilogue, e.g. the residual stream a layer's output
+// joins; needs act == 0, N % 8 == 0, no preact_out and no col_stats.
 
 // out[M,N] = a[M,K] * b[K,N] with b row-major (consumed as an MN-major operand); K % 8 == 0, N % 8 == 0.
 // gelu_preact (optional, [M,N] bf16): the result is multiplied elementwise by GELU'(gelu_preact).

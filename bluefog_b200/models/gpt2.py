@@ -25,13 +25,16 @@ class B200Linear(nn.Linear):
         super().__init__(in_features, out_features, bias=bias)
         self.use_b200_gemm = use_b200_gemm
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        """``residual`` (same shape as the output) is added to the result; on the kernel path inside the GEMM epilogue."""
         if self.use_b200_gemm and x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
             from bluefog_b200.ops import gemm
             if gemm.available() and self.in_features % 8 == 0:
-                y = gemm.linear(x.reshape(-1, self.in_features), self.weight, self.bias)
+                res2d = None if residual is None else residual.reshape(-1, self.out_features)
+                y = gemm.linear(x.reshape(-1, self.in_features), self.weight, self.bias, res2d)
                 return y.view(*x.shape[:-1], self.out_features)
-        return F.linear(x, self.weight, self.bias)
+        y = F.linear(x, self.weight, self.bias)
+        return y if residual is None else y + residual
 
 
 class Attention(nn.Module):
@@ -41,13 +44,13 @@ class Attention(nn.Module):
         self.c_attn = B200Linear(d_model, 3 * d_model, use_b200_gemm=use_b200_gemm)
         self.c_proj = B200Linear(d_model, d_model, use_b200_gemm=use_b200_gemm)
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
         b, t, c = x.shape
         q, k, v = self.c_attn(x).split(c, dim=2)
         shape = (b, t, self.n_head, c // self.n_head)
         q, k, v = (z.view(shape).transpose(1, 2) for z in (q, k, v))
         y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        return self.c_proj(y.transpose(1, 2).reshape(b, t, c))
+        return self.c_proj(y.transpose(1, 2).reshape(b, t, c), residual)
 
 
 class MLP(nn.Module):
@@ -56,15 +59,16 @@ class MLP(nn.Module):
         self.c_fc = B200Linear(d_model, 4 * d_model, use_b200_gemm=use_b200_gemm)
         self.c_proj = B200Linear(4 * d_model, d_model, use_b200_gemm=use_b200_gemm)
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
         # BLUEFOG_B200_MLP_FUSION=0 keeps the GELU a kernel of its own between the two GEMMs
         if (self.c_fc.use_b200_gemm and x.is_cuda and x.dtype == torch.bfloat16
                 and os.environ.get("BLUEFOG_B200_MLP_FUSION", "1") != "0"):
             from bluefog_b200.ops import gemm
+            res2d = None if residual is None else residual.reshape(-1, residual.shape[-1])
             y = gemm.mlp_gelu(x.reshape(-1, x.shape[-1]), self.c_fc.weight, self.c_fc.bias, self.c_proj.weight,
-                              self.c_proj.bias)
+                              self.c_proj.bias, res2d)
             return y.view(*x.shape[:-1], y.shape[-1])
-        return self.c_proj(F.gelu(self.c_fc(x), approximate="tanh"))
+        return self.c_proj(F.gelu(self.c_fc(x), approximate="tanh"), residual)
 
 
 class Block(nn.Module):
@@ -76,8 +80,9 @@ class Block(nn.Module):
         self.mlp = MLP(d_model, use_b200_gemm)
 
     def forward(self, x):
-        x = x + self.attn(self.ln_1(x))
-        return x + self.mlp(self.ln_2(x))
+        # the residual stream joins each sub-layer's output inside the last GEMM's epilogue
+        x = self.attn(self.ln_1(x), x)
+        return self.mlp(self.ln_2(x), x)
 
 
 class GPT2(nn.Module):

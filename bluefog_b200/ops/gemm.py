@@ -38,10 +38,11 @@ _TN_MIN_TILES = 120
 
 class _LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, a, w, bias):
+    def forward(ctx, a, w, bias, residual=None):
         ctx.save_for_backward(a, w)
         ctx.has_bias = bias is not None
-        return _b.native.gemm_bf16_nt(a, w, bias, 0)
+        # residual: added in the GEMM epilogue (out = a w^T + bias + residual) instead of by a pass of its own
+        return _b.native.gemm_bf16_nt(a, w, bias, 0, None, residual)
 
     @staticmethod
     def backward(ctx, dy):
@@ -64,14 +65,18 @@ class _LinearFn(torch.autograd.Function):
                 db = _b.native.column_sum(dy).to(dy.dtype)       # fp32 sums of the bf16 gradient in one pass
             else:
                 db = dy.sum(0, dtype=torch.float32).to(dy.dtype)
-        return da, dw, db
+        return da, dw, db, (dy if ctx.needs_input_grad[3] else None)
 
 
-def linear(a: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
-    """``a @ w.T (+ bias)`` on the tcgen05 kernel; a: [M, K] bf16, w: [N, K] bf16."""
+def linear(a: torch.Tensor, w: torch.Tensor, bias=None, residual=None) -> torch.Tensor:
+    """``a @ w.T (+ bias) (+ residual)`` on the tcgen05 kernel; a: [M, K] bf16, w: [N, K] bf16, residual: [M, N] bf16
+    (added in the epilogue when N is a multiple of 8)."""
     if a.shape[-1] % 8 != 0:
-        return torch.nn.functional.linear(a, w, bias)
-    return _LinearFn.apply(a.contiguous(), w.contiguous(), bias)
+        y = torch.nn.functional.linear(a, w, bias)
+        return y if residual is None else y + residual
+    if residual is not None and (w.shape[0] % 8 != 0 or residual.dtype != torch.bfloat16):
+        return _LinearFn.apply(a.contiguous(), w.contiguous(), bias) + residual
+    return _LinearFn.apply(a.contiguous(), w.contiguous(), bias, None if residual is None else residual.contiguous())
 
 
 class _Conv1x1Fn(torch.autograd.Function):
@@ -182,9 +187,9 @@ class _MlpGeluFn(torch.autograd.Function):
     multiplied by GELU'(pre-activation) before it is written."""
 
     @staticmethod
-    def forward(ctx, a, w1, b1, w2, b2):
+    def forward(ctx, a, w1, b1, w2, b2, residual=None):
         g, u = _b.native.gemm_bf16_nt_gelu(a, w1, b1)
-        y = _b.native.gemm_bf16_nt(g, w2, b2, 0)
+        y = _b.native.gemm_bf16_nt(g, w2, b2, 0, None, residual)        # residual joins in the epilogue
         ctx.save_for_backward(a, w1, w2, u, g)
         ctx.has_bias = (b1 is not None, b2 is not None)
         return y
@@ -200,7 +205,7 @@ class _MlpGeluFn(torch.autograd.Function):
         da = _input_gradient(du, w1) if ctx.needs_input_grad[0] else None
         dw1 = _weight_gradient(du, a)
         db1 = C.column_sum(du).to(du.dtype) if ctx.has_bias[0] else None
-        return da, dw1, db1, dw2, db2
+        return da, dw1, db1, dw2, db2, (dy if ctx.needs_input_grad[5] else None)
 
 
 # Rows up to which a weight gradient with few output tiles takes the split-K kernel of the convolution filter
@@ -226,14 +231,17 @@ def _weight_gradient(dy: torch.Tensor, a: torch.Tensor) -> torch.Tensor:
     return dy.t() @ a
 
 
-def mlp_gelu(a: torch.Tensor, w1: torch.Tensor, b1, w2: torch.Tensor, b2) -> torch.Tensor:
-    """``F.linear(F.gelu(F.linear(a, w1, b1), approximate="tanh"), w2, b2)`` for a bf16 CUDA matrix ``a`` [M, K]
-    on the tcgen05 kernels with the GELU folded into the GEMM epilogues; other inputs take PyTorch's ops."""
+def mlp_gelu(a: torch.Tensor, w1: torch.Tensor, b1, w2: torch.Tensor, b2, residual=None) -> torch.Tensor:
+    """``F.linear(F.gelu(F.linear(a, w1, b1), approximate="tanh"), w2, b2) (+ residual)`` for a bf16 CUDA matrix ``a``
+    [M, K] on the tcgen05 kernels with the GELU (and the residual add) folded into the GEMM epilogues; other inputs
+    take PyTorch's ops."""
     ok = (a.is_cuda and a.dim() == 2 and all(t.dtype == torch.bfloat16 for t in (a, w1, w2))
           and a.shape[1] % 8 == 0 and w1.shape[0] % 8 == 0 and w2.shape[0] % 8 == 0 and a.numel() > 0
           and (b1 is None or b1.dtype == torch.bfloat16) and (b2 is None or b2.dtype == torch.bfloat16)
           and available() and hasattr(_b.native, "gemm_bf16_nt_gelu"))
-    if ok:
-        return _MlpGeluFn.apply(a.contiguous(), w1.contiguous(), b1, w2.contiguous(), b2)
+    if ok and (residual is None or (residual.dtype == torch.bfloat16 and residual.shape == (a.shape[0], w2.shape[0]))):
+        return _MlpGeluFn.apply(a.contiguous(), w1.contiguous(), b1, w2.contiguous(), b2,
+                                None if residual is None else residual.contiguous())
     h = torch.nn.functional.gelu(torch.nn.functional.linear(a, w1, b1), approximate="tanh")
-    return torch.nn.functional.linear(h, w2, b2)
+    y = torch.nn.functional.linear(h, w2, b2)
+    return y if residual is None else y + residual

@@ -233,3 +233,28 @@ print("ok")
     env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and "ok" in out.stdout, out.stdout[-500:] + out.stderr[-1500:]
+
+
+@pytest.mark.parametrize("M,K,N", [(512, 256, 384), (8192, 1024, 1024), (300, 72, 136)])
+def test_linear_with_the_residual_added_in_the_epilogue(M, K, N):
+    """out = a w^T + bias + residual from one kernel; gradients of all four inputs against fp32 autograd."""
+    from bluefog_b200 import _C
+    from bluefog_b200.ops import gemm
+    torch.manual_seed(M + N)
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(N, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    r = torch.randn(M, N, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    before = _C.kernel_launch_count()
+    y = gemm.linear(a, w, b, r)
+    assert _C.kernel_launch_count() == before + 1            # no separate addition
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    a2, w2, b2, r2 = (t.detach().float().requires_grad_(True) for t in (a, w, b, r))
+    y2 = a2 @ w2.t() + b2 + r2
+    y2.backward(gy.float())
+    torch.cuda.synchronize()
+    assert _C.gemm_status() == 0
+    for got, ref in [(y, y2), (a.grad, a2.grad), (w.grad, w2.grad), (b.grad, b2.grad), (r.grad, r2.grad)]:
+        err = (got.float() - ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item() + 2e-2, err

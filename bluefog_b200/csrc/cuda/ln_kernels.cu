@@ -18,6 +18,8 @@
 #include "comm_kernels.h"
 #include "ln_kernels.h"
 
+#include <cstdlib>
+
 namespace bfb {
 namespace {
 
@@ -197,13 +199,130 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_kernel(const __nv_bfloat16* _
   }
 }
 
+// Backward with several warps per row.  The one-warp-per-row kernel above keeps a whole row of dy and x-hat in the
+// registers of 32 threads (212 registers at 1024 columns), which leaves one block of eight warps per SM and eight
+// rows in flight: the pass is then bound by the latency of one row after the other (34 us for 8192 x 1024, where the
+// traffic takes 8).  Here a row belongs to `tpr` threads (the columns / 8, rounded up to warps; one 16-byte vector
+// per thread), a block holds 256 / tpr rows side by side and every thread walks two rows per step, so that an SM has
+// a dozen rows in flight; the two row sums cross the warps of a row through shared memory (double-buffered, one
+// named barrier per step).  Column sums stay in registers per thread and leave through shared memory with one
+// vector reduction per four columns and block (no shared-memory atomics: their fp32 form is a CAS loop).
+__device__ __forceinline__ void row_bar(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 3) ln_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                                  const __nv_bfloat16* __restrict__ x,
+                                                                  const void* __restrict__ gamma,
+                                                                  const float* __restrict__ mean_in,
+                                                                  const float* __restrict__ rstd_in,
+                                                                  __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
+                                                                  float* __restrict__ dbeta, long long R, int C, int param_bf16,
+                                                                  int tpr) {
+  __shared__ float red[2][8][8][4];              // [buffer][row group][warp of the group][s1, s2 of two rows]
+  __shared__ float park[kThreads * 16];          // column sums of every thread on their way out
+  const int CG = C >> 3;
+  const int G = kThreads / tpr;                  // row groups per block
+  const int grp = threadIdx.x / tpr, t = threadIdx.x % tpr;
+  const int lane = threadIdx.x & 31, wig = t >> 5, nw = tpr >> 5;
+  const bool active = grp < G && t < CG;         // threads past the last column group only take part in barriers
+  const float inv_c = 1.f / (float)C;
+  float ga[8], sg[8], sb[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ga[i] = sg[i] = sb[i] = 0.f;
+  if (active) load_param8(gamma, t * 8, param_bf16, ga);
+  const long long step = (long long)gridDim.x * G * 2;
+  int buf = 0;
+  if (grp < G) {
+    for (long long r0 = ((long long)blockIdx.x * G + grp) * 2; r0 < R; r0 += step) {
+      const bool two = r0 + 1 < R;
+      float fd[2][8], xh[2][8];
+      float s[4] = {0.f, 0.f, 0.f, 0.f};
+      if (active) {
+        const uint4 d0 = *reinterpret_cast<const uint4*>(dy + r0 * C + t * 8);
+        const uint4 x0 = *reinterpret_cast<const uint4*>(x + r0 * C + t * 8);
+        uint4 d1 = make_uint4(0u, 0u, 0u, 0u), x1 = make_uint4(0u, 0u, 0u, 0u);
+        if (two) {
+          d1 = *reinterpret_cast<const uint4*>(dy + (r0 + 1) * C + t * 8);
+          x1 = *reinterpret_cast<const uint4*>(x + (r0 + 1) * C + t * 8);
+        }
+        unpack8(d0, fd[0]); unpack8(x0, xh[0]); unpack8(d1, fd[1]); unpack8(x1, xh[1]);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          if (k == 1 && !two) break;
+          const float mean = mean_in[r0 + k], rstd = rstd_in[r0 + k];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            xh[k][i] = (xh[k][i] - mean) * rstd;
+            sg[i] += fd[k][i] * xh[k][i];
+            sb[i] += fd[k][i];
+            fd[k][i] *= ga[i];
+            s[2 * k] += fd[k][i];
+            s[2 * k + 1] += fd[k][i] * xh[k][i];
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[j] = warp_sum(s[j]);
+      if (nw > 1) {
+        if (lane == 0) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) red[buf][grp][wig][j] = s[j];
+        }
+        row_bar(1 + grp, tpr);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float tsum = 0.f;
+          for (int w = 0; w < nw; ++w) tsum += red[buf][grp][w][j];
+          s[j] = tsum;
+        }
+        buf ^= 1;
+      }
+      if (active) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          if (k == 1 && !two) break;
+          const float rstd = rstd_in[r0 + k];
+          const float m1 = s[2 * k] * inv_c, m2 = s[2 * k + 1] * inv_c;
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = rstd * (fd[k][i] - m1 - xh[k][i] * m2);
+          *reinterpret_cast<uint4*>(dx + (r0 + k) * C + t * 8) = pack8(o);
+        }
+      }
+    }
+  }
+  // column sums: every thread parks its 16 values, thread (column quad) adds up the row groups and issues one
+  // vector reduction per four columns
+  {
+    float* mine = park + size_t(threadIdx.x) * 16;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      mine[i] = (grp < G) ? sg[i] : 0.f;
+      mine[8 + i] = (grp < G) ? sb[i] : 0.f;
+    }
+  }
+  __syncthreads();
+  // quads: CG column groups x 2 quads x {dgamma, dbeta}
+  for (int qd = threadIdx.x; qd < CG * 4; qd += kThreads) {
+    const int g8 = qd >> 2, half = (qd >> 1) & 1, which = qd & 1;      // which: 0 dgamma, 1 dbeta
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int gg = 0; gg < G; ++gg) {
+      const float* src = park + size_t(gg * tpr + g8) * 16 + which * 8 + half * 4;
+      acc.x += src[0]; acc.y += src[1]; acc.z += src[2]; acc.w += src[3];
+    }
+    float* dst = (which ? dbeta : dgamma) + g8 * 8 + half * 4;
+    asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
+  }
+}
+
 // out[c] += sum over rows of x[r, c]  (bf16 [R, C] row-major, fp32 sums; out holds zeros on entry).
 // The bias gradient of a linear layer.  A block owns 256 consecutive columns (one 16-byte vector per lane
-// and row) and a slice of the rows; its warps stride over the rows, fold through shared memory and add
-// each column once to the global sums.
+// and row) and a slice of the rows; its warps stride over the rows, park their partial sums in shared memory and
+// one thread per column adds them to the global sums.
 __global__ void __launch_bounds__(kThreads) column_sum_kernel(const __nv_bfloat16* __restrict__ x,
                                                               float* __restrict__ out, long long R, int C) {
-  __shared__ float fold[256];
+  __shared__ float fold[kWarps][256];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int c0 = blockIdx.x * 256 + lane * 8;
@@ -235,14 +354,19 @@ __global__ void __launch_bounds__(kThreads) column_sum_kernel(const __nv_bfloat1
       for (int i = 0; i < 8; ++i) acc[i] += f[i];
     }
   }
-  for (int i = threadIdx.x; i < 256; i += kThreads) fold[i] = 0.f;
-  __syncthreads();
+  // every warp parks its 256 partial sums; one thread per column adds the eight warps up (fp32 atomics on shared
+  // memory are a CAS loop, eight-way contended here)
 #pragma unroll
-  for (int i = 0; i < 8; ++i) atomicAdd(&fold[lane * 8 + i], acc[i]);
+  for (int i = 0; i < 8; ++i) fold[warp][lane * 8 + i] = acc[i];
   __syncthreads();
   for (int i = threadIdx.x; i < 256; i += kThreads) {
     const int c = blockIdx.x * 256 + i;
-    if (c < C) atomicAdd(&out[c], fold[i]);
+    if (c < C) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) t += fold[w][i];
+      atomicAdd(&out[c], t);
+    }
   }
 }
 
@@ -302,6 +426,23 @@ cudaError_t LaunchLnBackward(const void* dy, const void* x, const void* gamma, c
                              void* dx, float* dgamma_zeroed, float* dbeta_zeroed, long long R, int C, int param_bf16,
                              cudaStream_t stream) {
   if (!LnShapeSupported(R, C)) return cudaErrorInvalidValue;
+  const int CG = C >> 3;
+  static const bool rows_off = [] { const char* e = std::getenv("BLUEFOG_B200_LN_ROWS"); return e != nullptr && e[0] == '0'; }();
+  // the sums are reduced as 16-byte vectors: dgamma and dbeta have to be 16-byte aligned for the row-group kernel
+  if (!rows_off && CG <= kThreads && (reinterpret_cast<uintptr_t>(dgamma_zeroed) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(dbeta_zeroed) & 15) == 0) {
+    const int tpr = ((CG + 31) / 32) * 32;                     // threads per row, whole warps
+    const int G = kThreads / tpr;
+    long long blocks = (R + 2 * G - 1) / (2 * G);
+    const long long cap = (long long)SmCount() * 3;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    ln_bwd_rows_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), gamma, mean, rstd,
+        static_cast<__nv_bfloat16*>(dx), dgamma_zeroed, dbeta_zeroed, R, C, param_bf16, tpr);
+    CountKernelLaunch();
+    return cudaGetLastError();
+  }
   const int nv = ((C >> 3) + 31) / 32;
   BFB_LN_DISPATCH(nv, (ln_bwd_kernel<NV><<<GridForBackward(R), kThreads, 0, stream>>>(
                           static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), gamma, mean,

@@ -74,6 +74,8 @@ def bench_bucket(args):
     master = [torch.randn(n, device="cuda") for _ in range(W)]
     grad = [torch.randn(n, device="cuda").to(torch.bfloat16) for _ in range(W)]
     mom = [torch.zeros(n, device="cuda") for _ in range(W)]
+    adam = args.bucket_opt == "adamw"
+    second = [torch.zeros(n, device="cuda") for _ in range(W)] if adam else None
     shadow = [torch.zeros(n, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
     for r in range(W):
         a = _C.BucketStepArgs()
@@ -87,6 +89,9 @@ def bench_bucket(args):
             a.mode, a.opt = 0, 1
             a.master, a.grad, a.state1, a.shadow = master[r], grad[r], mom[r], shadow[r]
             a.lr, a.momentum, a.first_step = 0.01, 0.9, state["first"]
+            if adam:
+                a.opt, a.adamw, a.state2 = 2, True, second[r]
+                a.beta1, a.beta2, a.eps, a.bias1, a.bias2, a.weight_decay = 0.9, 0.999, 1e-8, 0.5, 0.1, 0.01
             a.self_weight, a.src_ranks, a.src_weights, a.n_readers = 0.5, [1 - r], [0.5], 1
             buckets[r].step(a)
         state["first"] = False
@@ -94,8 +99,9 @@ def bench_bucket(args):
     ms = timed(step, args.iters, args.warmup) / W
     pub = 4 if args.exchange == "float32" else 2
     # per element: master r+w (8), peer published copy r, own published copy w, grad r (2), momentum r+w (8), shadow w (2)
-    bytes_per_launch = n * (8 + 2 * pub + 2 + 8 + 2)
-    return {"kernel": "bucket_step_kernel (AWC, SGD momentum, bf16 grad+shadow)", "numel": n, "ms": ms,
+    bytes_per_launch = n * (8 + 2 * pub + 2 + 8 + 2 + (8 if adam else 0))             # AdamW: second moment r+w
+    return {"kernel": "bucket_step_kernel (AWC, %s, bf16 grad+shadow)" % ("AdamW" if adam else "SGD momentum"),
+            "numel": n, "ms": ms,
             "gbs": bytes_per_launch / ms / 1e6, "frac_of_measured_hbm": bytes_per_launch / ms / 1e6 / PEAKS["hbm_gbs"]}
 
 
@@ -363,6 +369,7 @@ def main():
     ap.add_argument("--ksize", type=int, default=3)
     ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--bucket-opt", choices=["sgd", "adamw"], default="sgd")
     ap.add_argument("--ln-rows", type=int, default=65536)
     ap.add_argument("--conv-shape", type=int, nargs=5, default=[64, 64, 64, 56, 56], metavar=("N", "CIN", "COUT", "H", "W"))
     ap.add_argument("--bn-shape", type=int, nargs=4, default=[64, 256, 56, 56])

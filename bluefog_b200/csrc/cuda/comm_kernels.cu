@@ -433,32 +433,71 @@ struct OptConst {
   float lr, momentum, dampening, wd, beta1, beta2, eps, bias1, bias2;
 };
 
-// Applies one optimizer update to parameter value c with gradient g. Returns the new value.
-__device__ __forceinline__ float opt_update(const OptConst& o, float c, float g, float* s1, float* s2, float* s3,
-                                            unsigned long long i) {
+// Applies one optimizer update to parameter value c with gradient g. Returns the new value.  The optimizer state of
+// the element (s1: momentum buffer or first moment, s2: second moment, s3: running maximum of the second moment)
+// lives in registers: the caller moves it as 16-byte vectors.  Through pointers every store of an element's state
+// would order the loads of the next element behind it, four dependent memory round trips per 16 bytes.
+__device__ __forceinline__ float opt_update(const OptConst& o, float c, float g, float& s1, float& s2, float& s3) {
   if (o.maximize) g = -g;
   if (o.opt == kOptSGD) {
     float d = g + o.wd * c;
     if (o.momentum != 0.f) {
-      float buf = o.first_step ? d : o.momentum * s1[i] + (1.f - o.dampening) * d;
-      s1[i] = buf;
+      float buf = o.first_step ? d : o.momentum * s1 + (1.f - o.dampening) * d;
+      s1 = buf;
       d = o.nesterov ? d + o.momentum * buf : buf;
     }
     return c - o.lr * d;
   }
   if (o.opt == kOptAdam) {
     if (o.adamw) c = c * (1.f - o.lr * o.wd); else g = g + o.wd * c;
-    float m = o.beta1 * s1[i] + (1.f - o.beta1) * g;
-    float v = o.beta2 * s2[i] + (1.f - o.beta2) * g * g;
-    s1[i] = m;
-    s2[i] = v;
+    float m = o.beta1 * s1 + (1.f - o.beta1) * g;
+    float v = o.beta2 * s2 + (1.f - o.beta2) * g * g;
+    s1 = m;
+    s2 = v;
     float vhat = v;
-    if (o.amsgrad) { vhat = fmaxf(s3[i], v); s3[i] = vhat; }
+    if (o.amsgrad) { vhat = fmaxf(s3, v); s3 = vhat; }
     // correctly rounded square root and division whatever the build's fast-math setting: v is tiny early in training
     const float denom = __fdiv_rn(__fsqrt_rn(vhat), __fsqrt_rn(o.bias2)) + o.eps;
     return c - __fdiv_rn(o.lr, o.bias1) * __fdiv_rn(m, denom);
   }
   return c;
+}
+
+// Four consecutive floats starting at a 16-byte boundary; `cnt` < 4 only in the last step of a buffer.
+__device__ __forceinline__ void load4f(const float* __restrict__ p, int cnt, float* v) {
+  if (cnt == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = i < cnt ? p[i] : 0.f;
+  }
+}
+__device__ __forceinline__ void store4f(float* __restrict__ p, int cnt, const float* v) {
+  if (cnt == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (i < cnt) p[i] = v[i];
+  }
+}
+// Up to four gradient elements, scaled; one vector load when all four exist and the address allows it.
+template <typename GradT>
+__device__ __forceinline__ void load4g(const GradT* __restrict__ gp, unsigned long long have, float scale, float* g) {
+  if (have >= 4 && (reinterpret_cast<uintptr_t>(gp) & (4 * sizeof(GradT) - 1)) == 0) {
+    if (sizeof(GradT) == 4) {
+      const float4 t = *reinterpret_cast<const float4*>(gp);
+      g[0] = t.x * scale; g[1] = t.y * scale; g[2] = t.z * scale; g[3] = t.w * scale;
+    } else {
+      const uint2 t = *reinterpret_cast<const uint2*>(gp);
+      g[0] = __uint_as_float(t.x << 16) * scale; g[1] = __uint_as_float(t.x & 0xffff0000u) * scale;
+      g[2] = __uint_as_float(t.y << 16) * scale; g[3] = __uint_as_float(t.y & 0xffff0000u) * scale;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) g[i] = (unsigned long long)i < have ? Elem<GradT>::load(gp + i) * scale : 0.f;
+  }
 }
 
 template <typename PubT, typename GradT>
@@ -505,6 +544,11 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
     const bool any_grad = p.grad != nullptr || p.grad_ptrs != nullptr;
     const bool has_grad = any_grad && p.opt != kOptNone;
     const bool wants_grad = any_grad && (has_grad || mode == kModeGradReduce || mode == kModePublishOnly);
+    // which state arrays the optimizer reads (ld) and writes (st)
+    const bool st1 = (o.opt == kOptSGD && o.momentum != 0.f) || o.opt == kOptAdam;
+    const bool ld1 = st1 && !(o.opt == kOptSGD && o.first_step);
+    const bool st2 = o.opt == kOptAdam;
+    const bool st3 = o.opt == kOptAdam && o.amsgrad;
     // Main loop: 4 elements per thread per step; published/grad buffers are padded to 16 bytes.
     for (unsigned long long q = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; q * 4 < p.numel; q += stride) {
       const unsigned long long i0 = q * 4;
@@ -525,8 +569,7 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
       for (int i = 0; i < 4; ++i) g[i] = 0.f;
       if (wants_grad) {
         if (p.grad != nullptr) {
-          const GradT* gp = static_cast<const GradT*>(p.grad) + i0;
-          for (int i = 0; i < 4; ++i) g[i] = i < cnt ? GE::load(gp + i) * p.grad_scale : 0.f;
+          load4g<GradT>(static_cast<const GradT*>(p.grad) + i0, (unsigned long long)cnt, p.grad_scale, g);
         } else {
           // per-parameter gradients: parameters start at multiples of 4 elements, so the four
           // elements of this step belong to one parameter (or to the padding behind it)
@@ -539,10 +582,20 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
           const unsigned long long local = i0 - p.seg_start[lo];
           const unsigned long long n = p.seg_numel[lo];
           if (gp != nullptr)
-            for (int i = 0; i < 4; ++i) g[i] = (local + i < n) ? GE::load(gp + local + i) * p.grad_scale : 0.f;
+            load4g<GradT>(gp + local, local < n ? n - local : 0ull, p.grad_scale, g);
           else
             seg_has_grad = false;
         }
+      }
+      // optimizer state of these four elements, requested before the peers' terms so that all loads of the step
+      // are in flight together
+      const bool upd = has_grad && seg_has_grad;
+      const bool touch = (mode == kModeGradReduce) ? true : (upd && (mode == kModeAWC || mode == kModeAdaptPublish));
+      float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f}, s3[4] = {0.f, 0.f, 0.f, 0.f};
+      if (touch) {
+        if (ld1) load4f(p.state1 + i0, cnt, s1);
+        if (st2) load4f(p.state2 + i0, cnt, s2);
+        if (st3) load4f(p.state3 + i0, cnt, s3);
       }
       // remote terms
       if (mode == kModeAWC || mode == kModeCombineOnly) {
@@ -570,17 +623,21 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
         }
       }
       float y[4];
-      const bool upd = has_grad && seg_has_grad;
       if (mode == kModeAWC) {
-        for (int i = 0; i < 4; ++i) y[i] = (upd && i < cnt) ? opt_update(o, acc[i], g[i], p.state1, p.state2, p.state3, i0 + i) : acc[i];
+        for (int i = 0; i < 4; ++i) y[i] = (upd && i < cnt) ? opt_update(o, acc[i], g[i], s1[i], s2[i], s3[i]) : acc[i];
       } else if (mode == kModeAdaptPublish) {
-        for (int i = 0; i < 4; ++i) y[i] = (upd && i < cnt) ? opt_update(o, x[i], g[i], p.state1, p.state2, p.state3, i0 + i) : x[i];
+        for (int i = 0; i < 4; ++i) y[i] = (upd && i < cnt) ? opt_update(o, x[i], g[i], s1[i], s2[i], s3[i]) : x[i];
       } else if (mode == kModeCombineOnly) {
         for (int i = 0; i < 4; ++i) y[i] = acc[i];
       } else if (mode == kModeGradReduce) {
-        for (int i = 0; i < 4; ++i) y[i] = i < cnt ? opt_update(o, x[i], acc[i] * p.post_scale, p.state1, p.state2, p.state3, i0 + i) : 0.f;
+        for (int i = 0; i < 4; ++i) y[i] = i < cnt ? opt_update(o, x[i], acc[i] * p.post_scale, s1[i], s2[i], s3[i]) : 0.f;
       } else {  // publish only: payload is the master (or the gradient when grad != null and opt == none)
         for (int i = 0; i < 4; ++i) y[i] = any_grad ? g[i] : x[i];
+      }
+      if (touch) {
+        if (st1) store4f(p.state1 + i0, cnt, s1);
+        if (st2) store4f(p.state2 + i0, cnt, s2);
+        if (st3) store4f(p.state3 + i0, cnt, s3);
       }
       const bool writes_master = (mode == kModeAWC || mode == kModeCombineOnly || mode == kModeGradReduce ||
                                   (mode == kModeAdaptPublish && p.master != nullptr));

@@ -267,6 +267,7 @@ def bench_ln(args):
     nb = x.numel() * 2
     ms_f = timed(lambda: _C.ln_forward(x, w, b, 1e-5), args.iters, args.warmup)
     ms_b = timed(lambda: _C.ln_backward(dy, x, w, mean, rstd), args.iters, args.warmup)
+    ms_b2 = timed(lambda: _C.ln_backward(dy, x, w, mean, rstd, y), args.iters, args.warmup)     # + residual term, + column sums
     ms_c = timed(lambda: _C.column_sum(wide), args.iters, args.warmup)
     ms_t = timed(lambda: wide.sum(0, dtype=torch.float32), args.iters, args.warmup)
     ms_tf = timed(lambda: torch.nn.functional.layer_norm(x, (1024,), w.bfloat16(), b.bfloat16()), args.iters, args.warmup)
@@ -274,6 +275,7 @@ def bench_ln(args):
     return {"kernel": "ln_fwd_kernel / ln_bwd_kernel / column_sum_kernel", "rows": rows,
             "ln_fwd_ms": ms_f, "ln_fwd_frac_of_measured_hbm": 2 * nb / ms_f / 1e6 / peak,       # read x, write y
             "ln_bwd_ms": ms_b, "ln_bwd_frac_of_measured_hbm": 3 * nb / ms_b / 1e6 / peak,       # read dy, x, write dx
+            "ln_bwd_residual_ms": ms_b2, "ln_bwd_residual_frac_of_measured_hbm": 4 * nb / ms_b2 / 1e6 / peak,
             "column_sum_ms": ms_c, "column_sum_frac_of_measured_hbm": wide.numel() * 2 / ms_c / 1e6 / peak,
             "pytorch_layer_norm_fwd_ms": ms_tf, "pytorch_sum_ms": ms_t}
 

@@ -605,22 +605,39 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(e == cudaSuccess, "ln_forward launch failed: ", cudaGetErrorString(e));
     return std::make_tuple(y, mean, rstd);
   });
-  m.def("ln_backward", [](at::Tensor dy, at::Tensor x, at::Tensor gamma, at::Tensor mean, at::Tensor rstd) {
+  // addend (optional, same shape as x): dx = LN'(dy) + addend, and a fourth result holds the fp32 column sums of dx.
+  m.def("ln_backward", [](at::Tensor dy, at::Tensor x, at::Tensor gamma, at::Tensor mean, at::Tensor rstd,
+                          c10::optional<at::Tensor> addend) {
     TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && dy.sizes() == x.sizes() &&
                 x.scalar_type() == at::kBFloat16 && x.is_contiguous(), "ln_backward expects contiguous bf16 dy and x");
     const int C = static_cast<int>(x.size(-1));
     const long long R = x.numel() / C;
     TORCH_CHECK(LnShapeSupported(R, C) && mean.numel() == R && rstd.numel() == R && mean.scalar_type() == at::kFloat &&
                 rstd.scalar_type() == at::kFloat, "ln_backward: statistics do not match x");
+    const bool extra = addend.has_value() && addend->defined();
+    if (extra)
+      TORCH_CHECK(addend->is_cuda() && addend->scalar_type() == at::kBFloat16 && addend->is_contiguous() &&
+                  addend->sizes() == x.sizes(), "ln_backward: the second gradient term has to be contiguous bf16 of x's shape");
     const bool pbf16 = gamma.scalar_type() == at::kBFloat16;
+    c10::cuda::CUDAGuard g(x.get_device());
     at::Tensor dx = at::empty_like(x);
-    at::Tensor sums = at::zeros({2, static_cast<int64_t>(C)}, x.options().dtype(at::kFloat));
+    at::Tensor sums = at::zeros({extra ? 3 : 2, static_cast<int64_t>(C)}, x.options().dtype(at::kFloat));
+    float* sp = sums.data_ptr<float>();
+    cudaStream_t stream = CurrentStream(x.get_device());
     cudaError_t e = LaunchLnBackward(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr<float>(),
-                                     rstd.data_ptr<float>(), dx.data_ptr(), sums.data_ptr<float>(),
-                                     sums.data_ptr<float>() + C, R, C, pbf16 ? 1 : 0, CurrentStream(x.get_device()));
+                                     rstd.data_ptr<float>(), dx.data_ptr(), sp, sp + C, R, C, pbf16 ? 1 : 0, stream,
+                                     extra ? addend->data_ptr() : nullptr, extra ? sp + 2 * C : nullptr);
+    if (extra && e == cudaErrorNotSupported) {
+      (void)cudaGetLastError();
+      e = LaunchLnBackward(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                           dx.data_ptr(), sp, sp + C, R, C, pbf16 ? 1 : 0, stream);
+      TORCH_CHECK(e == cudaSuccess, "ln_backward launch failed: ", cudaGetErrorString(e));
+      dx.add_(*addend);
+      e = LaunchColumnSum(dx.data_ptr(), sp + 2 * C, R, C, stream);
+    }
     TORCH_CHECK(e == cudaSuccess, "ln_backward launch failed: ", cudaGetErrorString(e));
-    return std::make_tuple(dx, sums.select(0, 0), sums.select(0, 1));
-  });
+    return std::make_tuple(dx, sums.select(0, 0), sums.select(0, 1), extra ? sums.select(0, 2) : at::Tensor());
+  }, py::arg("dy"), py::arg("x"), py::arg("gamma"), py::arg("mean"), py::arg("rstd"), py::arg("addend") = py::none());
 
   m.def("column_sum", [](at::Tensor x) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous() &&

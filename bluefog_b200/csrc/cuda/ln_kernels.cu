@@ -211,25 +211,30 @@ __device__ __forceinline__ void row_bar(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-__global__ void __launch_bounds__(kThreads, 3) ln_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy,
-                                                                  const __nv_bfloat16* __restrict__ x,
-                                                                  const void* __restrict__ gamma,
-                                                                  const float* __restrict__ mean_in,
-                                                                  const float* __restrict__ rstd_in,
-                                                                  __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
-                                                                  float* __restrict__ dbeta, long long R, int C, int param_bf16,
-                                                                  int tpr) {
+//
+// EXTRA: the row's gradient has a second term that skips the normalisation (the residual stream of a transformer
+// block: x feeds the LayerNorm and the addition behind the sub-layer), dx = LN'(dy) + addend, and the column sums of
+// that total leave with it (the bias gradient of the linear layer whose output, plus residual, was x).
+template <bool EXTRA>
+__global__ void __launch_bounds__(kThreads, EXTRA ? 2 : 3) ln_bwd_rows_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const void* __restrict__ gamma,
+    const float* __restrict__ mean_in, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+    float* __restrict__ dgamma, float* __restrict__ dbeta, const __nv_bfloat16* __restrict__ addend,
+    float* __restrict__ colsum, long long R, int C, int param_bf16, int tpr) {
+  constexpr int kPark = EXTRA ? 24 : 16;
   __shared__ float red[2][8][8][4];              // [buffer][row group][warp of the group][s1, s2 of two rows]
-  __shared__ float park[kThreads * 16];          // column sums of every thread on their way out
+  __shared__ float park[kThreads * kPark];       // column sums of every thread on their way out
   const int CG = C >> 3;
   const int G = kThreads / tpr;                  // row groups per block
   const int grp = threadIdx.x / tpr, t = threadIdx.x % tpr;
   const int lane = threadIdx.x & 31, wig = t >> 5, nw = tpr >> 5;
   const bool active = grp < G && t < CG;         // threads past the last column group only take part in barriers
   const float inv_c = 1.f / (float)C;
-  float ga[8], sg[8], sb[8];
+  float ga[8], sg[8], sb[8], sc[EXTRA ? 8 : 1];
 #pragma unroll
   for (int i = 0; i < 8; ++i) ga[i] = sg[i] = sb[i] = 0.f;
+#pragma unroll
+  for (int i = 0; i < (EXTRA ? 8 : 1); ++i) sc[i] = 0.f;
   if (active) load_param8(gamma, t * 8, param_bf16, ga);
   const long long step = (long long)gridDim.x * G * 2;
   int buf = 0;
@@ -238,6 +243,11 @@ __global__ void __launch_bounds__(kThreads, 3) ln_bwd_rows_kernel(const __nv_bfl
       const bool two = r0 + 1 < R;
       float fd[2][8], xh[2][8];
       float s[4] = {0.f, 0.f, 0.f, 0.f};
+      uint4 ad[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+      if (EXTRA && active) {
+        ad[0] = *reinterpret_cast<const uint4*>(addend + r0 * C + t * 8);
+        if (two) ad[1] = *reinterpret_cast<const uint4*>(addend + (r0 + 1) * C + t * 8);
+      }
       if (active) {
         const uint4 d0 = *reinterpret_cast<const uint4*>(dy + r0 * C + t * 8);
         const uint4 x0 = *reinterpret_cast<const uint4*>(x + r0 * C + t * 8);
@@ -287,31 +297,41 @@ __global__ void __launch_bounds__(kThreads, 3) ln_bwd_rows_kernel(const __nv_bfl
           float o[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) o[i] = rstd * (fd[k][i] - m1 - xh[k][i] * m2);
+          if (EXTRA) {
+            float a[8];
+            unpack8(ad[k], a);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              o[i] += a[i];
+              sc[i] += o[i];
+            }
+          }
           *reinterpret_cast<uint4*>(dx + (r0 + k) * C + t * 8) = pack8(o);
         }
       }
     }
   }
-  // column sums: every thread parks its 16 values, thread (column quad) adds up the row groups and issues one
+  // column sums: every thread parks its values, one thread per column quad adds up the row groups and issues one
   // vector reduction per four columns
   {
-    float* mine = park + size_t(threadIdx.x) * 16;
+    float* mine = park + size_t(threadIdx.x) * kPark;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       mine[i] = (grp < G) ? sg[i] : 0.f;
       mine[8 + i] = (grp < G) ? sb[i] : 0.f;
+      if (EXTRA) mine[16 + i] = (grp < G) ? sc[i] : 0.f;
     }
   }
   __syncthreads();
-  // quads: CG column groups x 2 quads x {dgamma, dbeta}
-  for (int qd = threadIdx.x; qd < CG * 4; qd += kThreads) {
-    const int g8 = qd >> 2, half = (qd >> 1) & 1, which = qd & 1;      // which: 0 dgamma, 1 dbeta
+  constexpr int kSums = EXTRA ? 3 : 2;           // dgamma, dbeta(, column sums of dx)
+  for (int qd = threadIdx.x; qd < CG * 2 * kSums; qd += kThreads) {
+    const int g8 = qd / (2 * kSums), rem = qd % (2 * kSums), which = rem >> 1, half = rem & 1;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int gg = 0; gg < G; ++gg) {
-      const float* src = park + size_t(gg * tpr + g8) * 16 + which * 8 + half * 4;
+      const float* src = park + size_t(gg * tpr + g8) * kPark + which * 8 + half * 4;
       acc.x += src[0]; acc.y += src[1]; acc.z += src[2]; acc.w += src[3];
     }
-    float* dst = (which ? dbeta : dgamma) + g8 * 8 + half * 4;
+    float* dst = (which == 0 ? dgamma : which == 1 ? dbeta : colsum) + g8 * 8 + half * 4;
     asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
   }
 }
@@ -424,25 +444,33 @@ cudaError_t LaunchLnForward(const void* x, const void* gamma, const void* beta, 
 
 cudaError_t LaunchLnBackward(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
                              void* dx, float* dgamma_zeroed, float* dbeta_zeroed, long long R, int C, int param_bf16,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, const void* addend, float* colsum_zeroed) {
   if (!LnShapeSupported(R, C)) return cudaErrorInvalidValue;
+  if ((addend == nullptr) != (colsum_zeroed == nullptr)) return cudaErrorInvalidValue;
   const int CG = C >> 3;
   static const bool rows_off = [] { const char* e = std::getenv("BLUEFOG_B200_LN_ROWS"); return e != nullptr && e[0] == '0'; }();
   // the sums are reduced as 16-byte vectors: dgamma and dbeta have to be 16-byte aligned for the row-group kernel
   if (!rows_off && CG <= kThreads && (reinterpret_cast<uintptr_t>(dgamma_zeroed) & 15) == 0 &&
-      (reinterpret_cast<uintptr_t>(dbeta_zeroed) & 15) == 0) {
+      (reinterpret_cast<uintptr_t>(dbeta_zeroed) & 15) == 0 && (reinterpret_cast<uintptr_t>(colsum_zeroed) & 15) == 0) {
     const int tpr = ((CG + 31) / 32) * 32;                     // threads per row, whole warps
     const int G = kThreads / tpr;
     long long blocks = (R + 2 * G - 1) / (2 * G);
-    const long long cap = (long long)SmCount() * 3;
+    const long long cap = (long long)SmCount() * (addend != nullptr ? 2 : 3);
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    ln_bwd_rows_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), gamma, mean, rstd,
-        static_cast<__nv_bfloat16*>(dx), dgamma_zeroed, dbeta_zeroed, R, C, param_bf16, tpr);
+    if (addend != nullptr)
+      ln_bwd_rows_kernel<true><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(
+          static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), gamma, mean, rstd,
+          static_cast<__nv_bfloat16*>(dx), dgamma_zeroed, dbeta_zeroed, static_cast<const __nv_bfloat16*>(addend),
+          colsum_zeroed, R, C, param_bf16, tpr);
+    else
+      ln_bwd_rows_kernel<false><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(
+          static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), gamma, mean, rstd,
+          static_cast<__nv_bfloat16*>(dx), dgamma_zeroed, dbeta_zeroed, nullptr, nullptr, R, C, param_bf16, tpr);
     CountKernelLaunch();
     return cudaGetLastError();
   }
+  if (addend != nullptr) return cudaErrorNotSupported;       // only the row-group kernel takes the second term
   const int nv = ((C >> 3) + 31) / 32;
   BFB_LN_DISPATCH(nv, (ln_bwd_kernel<NV><<<GridForBackward(R), kThreads, 0, stream>>>(
                           static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), gamma, mean,

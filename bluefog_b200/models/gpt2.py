@@ -81,8 +81,11 @@ class Block(nn.Module):
 
     def forward(self, x):
         # the residual stream joins each sub-layer's output inside the last GEMM's epilogue
-        x = self.attn(self.ln_1(x), x)
-        return self.mlp(self.ln_2(x), x)
+        # and its two gradients (through the LayerNorm, and past it) meet inside the LayerNorm backward kernel
+        h, x = self.ln_1.with_residual(x)
+        x = self.attn(h, x)
+        h, x = self.ln_2.with_residual(x)
+        return self.mlp(h, x)
 
 
 class GPT2(nn.Module):

@@ -9,6 +9,7 @@ MN-major (products with too few output tiles for a kernel without split-K go to 
 import torch
 
 from bluefog_b200.common.basics import get_basics
+from bluefog_b200.ops import fused_ln
 
 _b = get_basics()
 
@@ -61,7 +62,10 @@ class _LinearFn(torch.autograd.Function):
             # for that product and the kernels read them in place.
             dw = _weight_gradient(dy, a)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            if dy.shape[1] % 8 == 0 and hasattr(_b.native, "column_sum"):
+            sums = fused_ln.take_column_sums(dy)                  # summed on the way by the kernel that made dy
+            if sums is not None:
+                db = sums.to(dy.dtype)
+            elif dy.shape[1] % 8 == 0 and hasattr(_b.native, "column_sum"):
                 db = _b.native.column_sum(dy).to(dy.dtype)       # fp32 sums of the bf16 gradient in one pass
             else:
                 db = dy.sum(0, dtype=torch.float32).to(dy.dtype)
@@ -201,7 +205,10 @@ class _MlpGeluFn(torch.autograd.Function):
         C = _b.native
         du = C.gemm_bf16_nn_gelu_grad(dy, w2, u)                  # (dY W2) * GELU'(u)
         dw2 = _weight_gradient(dy, g)
-        db2 = C.column_sum(dy).to(dy.dtype) if ctx.has_bias[1] else None
+        db2 = None
+        if ctx.has_bias[1]:
+            sums = fused_ln.take_column_sums(dy)
+            db2 = (sums if sums is not None else C.column_sum(dy)).to(dy.dtype)
         da = _input_gradient(du, w1) if ctx.needs_input_grad[0] else None
         dw1 = _weight_gradient(du, a)
         db1 = C.column_sum(du).to(du.dtype) if ctx.has_bias[0] else None

@@ -90,3 +90,19 @@ def test_split_for_two_uses_leaves_other_tensors_alone():
     y = fused_bn.bn_act(x, bn, relu=True)            # CPU: PyTorch fallback, no pairs
     assert not getattr(y, "_bfb_takes_pairs", False)
     fused_bn.begin_step(x.device)                    # nothing pending, nothing raised
+
+
+def test_layer_norm_residual_falls_back_on_cpu():
+    """Off the kernels, ``layer_norm_residual`` is ``(F.layer_norm(x), x)`` and autograd adds the two gradients."""
+    import torch
+    import torch.nn.functional as F
+    from bluefog_b200.ops import fused_ln
+    x = torch.randn(3, 5, 16, requires_grad=True)
+    w, b = torch.rand(16) + 0.5, torch.randn(16)
+    y, r = fused_ln.layer_norm_residual(x, w, b)
+    assert r is x and torch.allclose(y, F.layer_norm(x, (16,), w, b))
+    (y.sum() + 2 * r.sum()).backward()
+    ref = x.detach().clone().requires_grad_(True)
+    (F.layer_norm(ref, (16,), w, b).sum() + 2 * ref.sum()).backward()
+    assert torch.allclose(x.grad, ref.grad)
+    assert fused_ln.take_column_sums(x.grad.reshape(-1, 16)) is None

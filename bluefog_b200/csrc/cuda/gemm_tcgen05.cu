@@ -249,7 +249,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 //               count is signalled on the LEADER's full barrier, which expects both CTAs' bytes;
 //   empty/acc : tcgen05.commit.cta_group::2 ... multicast::cluster arrives on the barrier at the same offset in
 //               both CTAs (ring slots free, accumulator complete);
-//   acc_empty : the four epilogue warps of both CTAs arrive on the leader's barrier (count 8, remote arrive).
+//   acc_empty : the eight epilogue warps of both CTAs arrive on the leader's barrier (count 16, remote arrive).
 // Every wait is bounded.  It is the PAIR mode of the persistent kernel below, so every operand mode and epilogue has it.
 // ------------------------------------------------------------------------------------------ //
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
@@ -281,9 +281,15 @@ struct PersistentCfg {
   // PAIR: two CTAs of a cluster share a (2 * BM) x BN_ tile (tcgen05 cta_group::2); each holds its 128 rows of A and
   // half of B, so a stage is smaller and the ring deeper.
   // the column-statistics epilogue gives one ring stage up for its per-warp partial sums
-  static constexpr int kStagesP = (PAIR ? 6 : ((BN_ == 256) ? 4 : 6)) - (EPI == kEpiColumnStats ? 1 : 0);
+  // PAIR runs eight epilogue warps, two per 32-lane quarter of tensor memory, each on half of the tile's columns:
+  // with a reduction of 1024 the main loop of a 256 x 256 tile takes 4.3 us, and four warps that convert, activate
+  // and store 256 columns each (and wait for their own TMA stores and auxiliary loads in turn) took three times
+  // that on the GELU epilogues.  Their staging boxes cost one of the six ring stages.
+  static constexpr int kEpiWarps = PAIR ? 8 : 4;
+  static constexpr int kThreadsP = 64 + 32 * kEpiWarps;
+  static constexpr int kStagesP = (PAIR ? 5 : ((BN_ == 256) ? 4 : 6)) - (EPI == kEpiColumnStats ? 1 : 0);
   // per epilogue warp: BN_ column sums and BN_ sums of squares
-  static constexpr uint32_t kStatBytes = EPI == kEpiColumnStats ? 4 * 2 * BN_ * 4 : 0;
+  static constexpr uint32_t kStatBytes = EPI == kEpiColumnStats ? kEpiWarps * 2 * BN_ * 4 : 0;
   static constexpr int kRowsB = PAIR ? BN_ / 2 : BN_;          // rows (output columns) of B one CTA loads
   static constexpr int kTileM = PAIR ? 2 * BM : BM;
   static constexpr uint32_t kBytesA = BM * BK * 2;
@@ -292,7 +298,7 @@ struct PersistentCfg {
   static constexpr uint32_t kCols = 2 * BN_;
   // output staging: per epilogue warp two [32 rows x 64 columns] bf16 boxes (4 KiB each, 1024-byte aligned)
   static constexpr uint32_t kBytesOutBox = 32 * 64 * 2;
-  static constexpr uint32_t kBytesOut = 4 * 2 * kBytesOutBox;
+  static constexpr uint32_t kBytesOut = kEpiWarps * 2 * kBytesOutBox;
   static constexpr size_t kSmem = 1024 + size_t(kStagesP) * kBytesStage + kBytesOut + 256 + kStatBytes;
   static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BN_ >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
 };
@@ -309,7 +315,7 @@ struct PersistentCfg {
 // leader's full barrier, commits are multicast to both CTAs, the leader's MMA thread issues cta_group::2 MMAs and
 // waits for the epilogue warps of both CTAs.
 template <int BN_, int BMODE = 0, int AMODE = 0, int EPI = 0, int PAIR = 0>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((PersistentCfg<BN_, EPI, PAIR>::kThreadsP), 1)
 gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ out,
                                const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int act, int tma_out,
@@ -347,7 +353,7 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bars[2 * S + a]), 1);        // one tcgen05.commit
-      mbar_init(smem_u32(&bars[2 * S + 2 + a]), PAIR ? 8 : 4);    // one arrive per epilogue warp (of both CTAs)
+      mbar_init(smem_u32(&bars[2 * S + 2 + a]), (PAIR ? 2 : 1) * Cfg::kEpiWarps);    // one arrive per epilogue warp (of both CTAs)
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -463,21 +469,26 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
       }
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3;                // the quarter of tensor memory (32 lanes = 32 rows) this warp can read
+    const int ew = warp - 2;               // epilogue warp index
+    // eight warps: warps 2-5 take the first half of the columns, warps 6-9 the second
+    constexpr int kChunks = BN_ / 64;
+    constexpr int kChunksW = Cfg::kEpiWarps == 8 ? kChunks / 2 : kChunks;
+    const int c_first = Cfg::kEpiWarps == 8 ? (ew >> 2) * kChunksW : 0;
     const bool vec_ok = (N % 8) == 0;
-    unsigned char* my_out = stage_out + size_t(q) * 2 * Cfg::kBytesOutBox;
+    unsigned char* my_out = stage_out + size_t(ew) * 2 * Cfg::kBytesOutBox;
     int local = 0;
     int boxes = 0;                       // TMA stores issued by this warp
     // kEpiColumnStats: this warp's partial column sums [BN_] and sums of squares [BN_] of the current column
     // block live in shared memory (lanes 0-7 each own eight columns of every 64-column chunk, so no atomics)
     // and go to col_stats with vector reductions when the column block changes and at the end: adding every
     // box to global memory directly serialises thousands of reductions per address.
-    float* wstat = reinterpret_cast<float*>(stage_out + Cfg::kBytesOut + 256) + (EPI == kEpiColumnStats ? q * 2 * BN_ : 0);
+    float* wstat = reinterpret_cast<float*>(stage_out + Cfg::kBytesOut + 256) + (EPI == kEpiColumnStats ? ew * 2 * BN_ : 0);
     int stat_n0 = -1;
     auto flush_stats = [&]() {
       if (stat_n0 >= 0 && lane < 8) {
 #pragma unroll 1
-        for (int c = 0; c < BN_ / 64; ++c) {
+        for (int c = c_first; c < c_first + kChunksW; ++c) {
           const int col = c * 64 + lane * 8;
           const int n = stat_n0 + col;
           float4* ws = reinterpret_cast<float4*>(wstat + col);
@@ -513,7 +524,7 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
       }
       if (tma_out) {
 #pragma unroll 1
-        for (int c = 0; c < BN_ / 64; ++c) {
+        for (int c = c_first; c < c_first + kChunksW; ++c) {
           const int nbase = n0 + c * 64;
           if (nbase >= N || m0 + q * 32 >= M) break;           // warp-uniform
           uint32_t r[64];
@@ -678,7 +689,7 @@ gemm_bf16_nt_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < BN_ / 32; ++c) {
+        for (int c = 2 * c_first; c < 2 * (c_first + kChunksW); ++c) {
           uint32_t r[32];
           tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN_ + c * 32), r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -768,14 +779,14 @@ cudaError_t LaunchPersistent(const CUtensorMap& map_a, const CUtensorMap& map_b,
   }
   const int tiles = ((M + Cfg::kTileM - 1) / Cfg::kTileM) * ((N + BN_ - 1) / BN_);
   if (!PAIR) {
-    kernel<<<tiles < sm_count ? tiles : sm_count, kThreads, Cfg::kSmem, stream>>>(map_a, map_b, map_c, out, bias, M, N, K, act,
+    kernel<<<tiles < sm_count ? tiles : sm_count, Cfg::kThreadsP, Cfg::kSmem, stream>>>(map_a, map_b, map_c, out, bias, M, N, K, act,
                                                                                tma_out, status, map_aux, aux_in, col_stats);
     return cudaSuccess;
   }
   const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(Cfg::kThreadsP);
   cfg.dynamicSmemBytes = Cfg::kSmem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

@@ -605,7 +605,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(e == cudaSuccess, "ln_forward launch failed: ", cudaGetErrorString(e));
     return std::make_tuple(y, mean, rstd);
   });
-  // addend (optional, same shape as x): dx = LN'(dy) + addend, and a fourth result holds the fp32 column sums of dx.
+  // addend (optional, same shape as x): dx = LN'(dy) + addend, and a third row of the sums holds the fp32 column sums of dx.
   m.def("ln_backward", [](at::Tensor dy, at::Tensor x, at::Tensor gamma, at::Tensor mean, at::Tensor rstd,
                           c10::optional<at::Tensor> addend) {
     TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && dy.sizes() == x.sizes() &&
@@ -636,7 +636,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       e = LaunchColumnSum(dx.data_ptr(), sp + 2 * C, R, C, stream);
     }
     TORCH_CHECK(e == cudaSuccess, "ln_backward launch failed: ", cudaGetErrorString(e));
-    return std::make_tuple(dx, sums.select(0, 0), sums.select(0, 1), extra ? sums.select(0, 2) : at::Tensor());
+    // rows of sums: dgamma, dbeta(, column sums of dx); one tensor so that a caller converts them in one pass
+    return std::make_tuple(dx, sums);
   }, py::arg("dy"), py::arg("x"), py::arg("gamma"), py::arg("mean"), py::arg("rstd"), py::arg("addend") = py::none());
 
   m.def("column_sum", [](at::Tensor x) {

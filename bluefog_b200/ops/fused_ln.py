@@ -37,8 +37,9 @@ class _LayerNormFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, weight, mean, rstd = ctx.saved_tensors
-        dx, dgamma, dbeta, _ = _b.native.ln_backward(dy.contiguous(), x, weight, mean, rstd)
-        return dx, dgamma.to(weight.dtype), dbeta.to(weight.dtype), None
+        dx, sums = _b.native.ln_backward(dy.contiguous(), x, weight, mean, rstd)
+        sums = sums.to(weight.dtype)                  # [dgamma, dbeta], one conversion for both
+        return dx, sums[0], sums[1], None
 
 
 # Column sums that left a backward kernel together with a gradient: data_ptr of the gradient -> (weak reference to
@@ -56,7 +57,8 @@ def _offer_column_sums(grad, sums):
 
 
 def take_column_sums(dy):
-    """fp32 column sums of the 2-D gradient ``dy`` if the kernel that produced it summed them on its way, else None."""
+    """Column sums of the 2-D gradient ``dy`` (fp32, or already converted to the gradient's dtype) if the kernel that
+    produced it summed them on its way, else None."""
     global column_sum_hits
     entry = _column_sums.pop(dy.data_ptr(), None) if _column_sums else None
     if entry is None:
@@ -85,11 +87,14 @@ class _LayerNormResidualFn(torch.autograd.Function):
         if dy is None:
             return dres, None, None, None
         if dres is None:
-            dx, dgamma, dbeta, _ = _b.native.ln_backward(dy.contiguous(), x, weight, mean, rstd)
-            return dx, dgamma.to(weight.dtype), dbeta.to(weight.dtype), None
-        dx, dgamma, dbeta, sums = _b.native.ln_backward(dy.contiguous(), x, weight, mean, rstd, dres.contiguous())
-        _offer_column_sums(dx, sums)
-        return dx, dgamma.to(weight.dtype), dbeta.to(weight.dtype), None
+            dx, sums = _b.native.ln_backward(dy.contiguous(), x, weight, mean, rstd)
+            sums = sums.to(weight.dtype)
+            return dx, sums[0], sums[1], None
+        dx, sums = _b.native.ln_backward(dy.contiguous(), x, weight, mean, rstd, dres.contiguous())
+        if weight.dtype == dx.dtype:
+            sums = sums.to(weight.dtype)              # the bias gradient wants the activation dtype: one conversion for all three
+        _offer_column_sums(dx, sums[2])
+        return dx, sums[0].to(weight.dtype), sums[1].to(weight.dtype), None
 
 
 def layer_norm_residual(x, weight, bias, eps=1e-5):

@@ -70,6 +70,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--out", default="")
     ap.add_argument("--skip-nccl", action="store_true")
+    ap.add_argument("--registered", action="store_true",
+                    help="also time neighbor_allreduce on tensors of bf.symmetric_empty (published in place)")
+    ap.add_argument("--registered-min-bytes", type=int, default=0)
     ap.add_argument("--ops", default="neighbor,windows,collectives",
                     help="comma-separated: neighbor (neighbor_allreduce), windows (win_put/accumulate/get/update), "
                          "collectives (allreduce/broadcast/allgather against NCCL)")
@@ -129,6 +132,17 @@ def main():
                        "mode": mode, "ms": ms, "gbs": indeg * nbytes / ms / 1e6,
                        "roofline_frac": indeg * nbytes / ms / 1e6 / NVLINK_GBS}
                 results.append(row)
+                if args.registered and nbytes >= args.registered_min_bytes:
+                    # the same operation on a tensor in symmetric memory: published in place, no copy into the arena
+                    xr = bf.symmetric_empty(numel, dtype=dtype)
+                    xr.copy_(x)
+                    keep, x = x, xr
+                    ms_r = device_time_ms(ours, args.iters, args.warmup)
+                    x = keep
+                    results.append({"op": "neighbor_allreduce", "impl": "ours-registered", "dtype": row["dtype"],
+                                    "bytes": nbytes, "mode": mode, "ms": ms_r, "gbs": indeg * nbytes / ms_r / 1e6,
+                                    "roofline_frac": indeg * nbytes / ms_r / 1e6 / NVLINK_GBS})
+                    del xr
                 # the same operations issued back to back through the nonblocking API and waited for at the
                 # end, which is how the NCCL arm below runs (its wait() only orders streams)
                 ms_nb = pipelined_time_ms(ours_nonblocking, args.iters, args.warmup)

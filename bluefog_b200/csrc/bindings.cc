@@ -82,6 +82,49 @@ class LocalWorld {
       copies.push_back({copy_src[i], static_cast<uint64_t>(arena_off[i]), static_cast<uint64_t>(outs[i].nbytes()), outs[i].data_ptr()});
     ThrowIfError(chans_[rank]->PullGather(rounds_[round_id], src_ranks, copies, CurrentStream(device_)));
   }
+  // Registered tensors: one buffer of `nbytes` per rank, every rank's registry knows all of them.  Returns the
+  // ranks' buffers as uint8 tensors.
+  std::vector<at::Tensor> alloc_symmetric(int64_t nbytes) {
+    c10::cuda::CUDAGuard g(device_);
+    std::vector<std::shared_ptr<SymmBuffer>> bufs;
+    ThrowIfError(AllocateLocal(world_, device_, static_cast<size_t>((nbytes + 255) & ~int64_t(255)), &bufs));
+    if (regs_.empty()) regs_.resize(world_);
+    std::vector<at::Tensor> out;
+    for (int r = 0; r < world_; ++r) {
+      regs_[r].Add(bufs[r]);
+      std::shared_ptr<SymmBuffer> keep = bufs[r];
+      out.push_back(at::from_blob(bufs[r]->local(), {nbytes}, [keep](void*) {},
+                                  at::TensorOptions().dtype(at::kByte).device(at::kCUDA, device_)));
+    }
+    return out;
+  }
+  // Publishes `x` (a tensor inside rank's registered buffer) in place; a tensor elsewhere is copied into the arena.
+  int publish_in_place(int rank, at::Tensor x, c10::optional<std::vector<double>> dst_weight, int n_readers) {
+    c10::cuda::CUDAGuard g(device_);
+    RegisteredLoc reg;
+    const bool found = !regs_.empty() && regs_[rank].Find(x.data_ptr(), static_cast<uint64_t>(x.nbytes()), &reg);
+    std::vector<SegSpec> segs{{x.data_ptr(), nullptr, static_cast<uint64_t>(x.nbytes()), static_cast<uint64_t>(x.numel())}};
+    Round round;
+    ThrowIfError(chans_[rank]->Publish(segs, dst_weight ? dst_weight->data() : nullptr, n_readers, CurrentStream(device_), &round,
+                                       found ? reg.key : 0));
+    rounds_.push_back(round);
+    return static_cast<int>(rounds_.size()) - 1;
+  }
+  // The pull of a rank that published `x` with publish_in_place.
+  void combine_in_place(int rank, int round_id, at::Tensor x, at::Tensor out, double self_w, std::vector<int> src_ranks,
+                        std::vector<double> src_w, bool use_dst_weight, double post_scale) {
+    c10::cuda::CUDAGuard g(device_);
+    RegisteredLoc reg;
+    const bool found = !regs_.empty() && regs_[rank].Find(x.data_ptr(), static_cast<uint64_t>(x.nbytes()), &reg);
+    std::vector<SegSpec> segs{{nullptr, out.data_ptr(), static_cast<uint64_t>(out.nbytes()), static_cast<uint64_t>(out.numel())}};
+    ThrowIfError(chans_[rank]->PullCombine(rounds_[round_id], segs, ElemOf(out), self_w, src_ranks, src_w, use_dst_weight,
+                                           post_scale, CurrentStream(device_), found ? &reg : nullptr));
+  }
+  // Launch only after the pulls of every reader have been launched: ranks of this world share one GPU.
+  void wait_readers(int rank, int round_id) {
+    c10::cuda::CUDAGuard g(device_);
+    ThrowIfError(chans_[rank]->WaitReaders(rounds_[round_id], CurrentStream(device_)));
+  }
   // Rounds published by different ranks in the same position share version and layout.
   std::vector<int64_t> round_offsets(int round_id) {
     return std::vector<int64_t>(rounds_[round_id].offsets.begin(), rounds_[round_id].offsets.end());
@@ -96,6 +139,7 @@ class LocalWorld {
   int world_, device_;
   std::vector<std::unique_ptr<Channel>> chans_;
   std::vector<Round> rounds_;
+  std::vector<SymmRegistry> regs_;       // per rank
 };
 
 std::unique_ptr<Channel> MakeIpcChannel(size_t half_bytes) {
@@ -351,6 +395,23 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("size", [] { return Runtime::Get().size(); });
   m.def("local_rank", [] { return Runtime::Get().local_rank(); });
   m.def("local_size", [] { return Runtime::Get().local_size(); });
+  // Collective: `nbytes` of this rank's device memory, mapped into every rank (see Runtime::SymmetricAlloc); a uint8
+  // tensor that Python views as the dtype and shape it wants.
+  m.def("symmetric_alloc", [](int64_t nbytes) {
+    Runtime& rt = Runtime::Get();
+    std::shared_ptr<SymmBuffer> buf;
+    {
+      py::gil_scoped_release nogil;
+      ThrowIfError(rt.SymmetricAlloc(static_cast<size_t>(nbytes), &buf));
+    }
+    std::shared_ptr<SymmBuffer> keep = buf;
+    return at::from_blob(buf->local(), {nbytes}, [keep](void*) {},
+                         at::TensorOptions().dtype(at::kByte).device(at::kCUDA, rt.device()));
+  });
+  m.def("is_symmetric", [](at::Tensor t) {
+    RegisteredLoc loc;
+    return t.is_cuda() && Runtime::Get().FindRegistered(t.data_ptr(), static_cast<uint64_t>(t.nbytes()), &loc);
+  });
   m.def("set_skip_negotiate_stage", [](bool v) { Runtime::Get().set_skip_negotiate(v); });
   m.def("get_skip_negotiate_stage", [] { return Runtime::Get().skip_negotiate(); });
   m.def("suspend", [] { Runtime::Get().Suspend(); });
@@ -1006,6 +1067,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("publish", &LocalWorld::publish, py::arg("rank"), py::arg("tensors"), py::arg("dst_weight") = py::none(), py::arg("n_readers") = 0)
       .def("combine", &LocalWorld::combine)
       .def("gather", &LocalWorld::gather)
+      .def("alloc_symmetric", &LocalWorld::alloc_symmetric)
+      .def("publish_in_place", &LocalWorld::publish_in_place, py::arg("rank"), py::arg("x"), py::arg("dst_weight") = py::none(),
+           py::arg("n_readers") = 0)
+      .def("combine_in_place", &LocalWorld::combine_in_place)
+      .def("wait_readers", &LocalWorld::wait_readers)
       .def("round_offsets", &LocalWorld::round_offsets)
       .def("status", &LocalWorld::status)
       .def("clear_status", &LocalWorld::clear_status);

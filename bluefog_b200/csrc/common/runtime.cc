@@ -180,6 +180,25 @@ void Runtime::KeepUntilShutdown(std::shared_ptr<void> memory) {
   keep_until_shutdown_.push_back(std::move(memory));
 }
 
+Status Runtime::SymmetricAlloc(size_t bytes, std::shared_ptr<SymmBuffer>* out) {
+  if (!initialized_.load()) return Status::PreconditionError("bluefog is not initialized");
+  if (device_ < 0) return Status::PreconditionError("symmetric memory needs a CUDA device");
+  if (bytes == 0) return Status::InvalidArgument("symmetric allocation of zero bytes");
+  c10::cuda::CUDAGuard guard(device_);
+  Status s = AllocateIpc(&cp_, kChanUser, device_, (bytes + 255) & ~size_t(255), out);
+  if (!s.ok()) return s;
+  KeepUntilShutdown(*out);
+  std::lock_guard<std::mutex> g(reg_mu_);
+  if (!registered_) registered_ = std::make_unique<SymmRegistry>();
+  registered_->Add(*out);
+  return Status::OK();
+}
+
+bool Runtime::FindRegistered(const void* p, uint64_t nbytes, RegisteredLoc* loc) {
+  std::lock_guard<std::mutex> g(reg_mu_);
+  return registered_ != nullptr && registered_->Find(p, nbytes, loc);
+}
+
 void Runtime::Shutdown() {
   if (!initialized_.load()) return;
   {
@@ -213,6 +232,10 @@ void Runtime::Shutdown() {
   }
   if (windows_) {
     windows_.reset();
+  }
+  {
+    std::lock_guard<std::mutex> g(reg_mu_);
+    registered_.reset();
   }
   {
     std::lock_guard<std::mutex> g(keep_mu_);
@@ -1364,7 +1387,14 @@ Status Runtime::ExecuteGpu(std::vector<Entry>& entries, const Response& resp) {
     std::vector<double> dstw(size_, 1.0);
     if (first.dst_weights.size() == first.dst_ranks.size())
       for (size_t i = 0; i < first.dst_ranks.size(); ++i) dstw[first.dst_ranks[i]] = first.dst_weights[i];
-    s = gpu_channel_->Publish(segs, dstw.data(), static_cast<int>(first.dst_ranks.size()), stream, &round);
+    // A tensor in registered symmetric memory is published in place: no copy into the arena, neighbors pull it from
+    // where it is, and the operation ends with a wait for those neighbors (the tensor is the caller's to overwrite
+    // again only when nobody reads it any more).  One tensor per operation, not the output of the same call.
+    RegisteredLoc reg;
+    const bool in_place = type == OpType::NEIGHBOR_ALLREDUCE && entries.size() == 1 && !first.is_hierarchical &&
+                          first.output->data_ptr() != segs[0].in && FindRegistered(segs[0].in, segs[0].nbytes, &reg);
+    s = gpu_channel_->Publish(segs, dstw.data(), static_cast<int>(first.dst_ranks.size()), stream, &round,
+                              in_place ? reg.key : 0);
     if (s.ok()) {
       for (size_t i = 0; i < entries.size(); ++i) {
         at::Tensor& out = *entries[i].spec.output;
@@ -1378,7 +1408,9 @@ Status Runtime::ExecuteGpu(std::vector<Entry>& entries, const Response& resp) {
       std::vector<double> w = first.src_weights;
       if (integral) w.assign(first.src_ranks.size(), 1.0);
       s = gpu_channel_->PullCombine(round, segs, elem, integral ? 1.0 : first.self_weight, first.src_ranks, w,
-                                    /*use_dst_weight=*/!integral, integral ? 1.0 : first.post_scale, stream);
+                                    /*use_dst_weight=*/!integral, integral ? 1.0 : first.post_scale, stream,
+                                    in_place ? &reg : nullptr);
+      if (s.ok() && in_place) s = gpu_channel_->WaitReaders(round, stream);
     }
     end_act();
     return s;

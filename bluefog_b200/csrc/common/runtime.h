@@ -39,6 +39,8 @@ namespace bfb {
 class Channel;
 class WindowManager;
 struct SymmBuffer;
+struct RegisteredLoc;
+class SymmRegistry;
 
 // Everything one operation needs; filled by the Python layer after argument validation.
 struct OpSpec {
@@ -85,6 +87,11 @@ class Runtime {
   // Peer-mapped memory that other ranks' kernels may read (bucket arenas and their control blocks): kept mapped
   // until Shutdown has met every other rank at a barrier, whatever the owner object's lifetime.
   void KeepUntilShutdown(std::shared_ptr<void> memory);
+  // Collective (every rank, same size): device memory of this rank that is mapped into every rank's address space.
+  // A tensor placed in it is published in place by neighbor_allreduce - neighbors pull it from where it is instead
+  // of from a copy in the channel arena.  The memory stays allocated until Shutdown.
+  Status SymmetricAlloc(size_t bytes, std::shared_ptr<SymmBuffer>* out);
+  bool FindRegistered(const void* p, uint64_t nbytes, RegisteredLoc* loc);
   void Suspend() { suspended_.store(true); }
   void Resume() {
     suspended_.store(false);
@@ -198,6 +205,8 @@ class Runtime {
   std::mutex inline_mu_;
   std::mutex keep_mu_;
   std::vector<std::shared_ptr<void>> keep_until_shutdown_;
+  std::mutex reg_mu_;
+  std::unique_ptr<SymmRegistry> registered_;          // buffers of SymmetricAlloc, in allocation order
   std::unordered_map<int, InlineOp> inline_ops_;      // by handle
   std::unordered_map<std::string, int> inline_names_; // names in flight on the fast path
   bool inline_enabled_ = true;

@@ -281,6 +281,7 @@ __global__ void __launch_bounds__(kThreads) pack_publish_kernel(const __grid_con
         for (int r = threadIdx.x; r < p.world; r += blockDim.x) p.ctrl->dst_weight[p.half][r] = p.dst_weight[r];
       if (threadIdx.x == 0) {
         p.ctrl->payload_bytes[p.half] = p.payload_bytes;
+        p.ctrl->payload_loc[p.half] = p.loc;
         // a version that was not written completely is still announced (nobody may hang on it), but marked
         if (*reinterpret_cast<volatile unsigned int*>(&p.ctrl->launch_failed) != 0u) {
           p.ctrl->failed_epoch = p.publish_epoch;
@@ -309,7 +310,27 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(const __grid_constant
   for (int j = threadIdx.x; j < p.sync.n_src; j += blockDim.x) w_host[j] = (W)p.src_w[j];
   for (int i = threadIdx.x; i <= p.n_seg; i += blockDim.x) starts[i] = p.chunk_start[i];
   __syncthreads();
-  const bool ok = pull_prologue<W>(p.sync, w_host, p.sync.n_src, w_s);
+  bool ok = pull_prologue<W>(p.sync, w_host, p.sync.n_src, w_s);
+  // where each source keeps this version: in its arena, or in place in registered memory
+  __shared__ const unsigned char* base_s[kMaxSrc];
+  __shared__ int layout_ok;
+  if (threadIdx.x == 0) layout_ok = 1;
+  __syncthreads();
+  if (ok) {
+    for (int j = threadIdx.x; j < p.sync.n_src; j += blockDim.x) {
+      const unsigned long long loc = ld_acquire_sys(&p.sync.src_ctrl[j]->payload_loc[p.sync.half]);
+      if (loc == 0ull) {
+        base_s[j] = p.sync.src_arena[j];
+      } else if (loc == p.my_loc) {
+        base_s[j] = p.alt_src[j];
+      } else {
+        report_error(p.sync.status, kCommLayoutMismatch, (unsigned)p.sync.src_rank[j], p.my_loc, loc);
+        layout_ok = 0;
+      }
+    }
+  }
+  __syncthreads();
+  ok = ok && layout_ok != 0;
   if (ok) {
     const W self_w = (W)p.self_w;
     const W post = (W)p.post_scale;
@@ -353,7 +374,7 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(const __grid_constant
         }
       }
       for (int j = 0; j < n_src; ++j) {
-        const unsigned char* base = p.sync.src_arena[j];
+        const unsigned char* base = base_s[j];
         const W w = w_s[j];
         uint4 v[kUnroll];
 #pragma unroll
@@ -753,6 +774,20 @@ void CountKernelLaunch() { g_launches.fetch_add(1); }
 cudaError_t LaunchPack(const PackParams& p, cudaStream_t stream) {
   const unsigned long long total = p.chunk_start[p.n_seg];
   pack_publish_kernel<<<GridFor(total), kThreads, 0, stream>>>(p);
+  CountKernelLaunch();
+  return cudaGetLastError();
+}
+
+__global__ void wait_readers_kernel(ChannelCtrl* ctrl, int half, unsigned long long need, unsigned long long timeout_ns,
+                                    CommStatus* status, int my_rank) {
+  unsigned long long seen = 0;
+  if (!wait_ge(&ctrl->done[half], need, timeout_ns, &seen))
+    report_error(status, kCommTimeoutDone, (unsigned)my_rank, need, seen);
+}
+
+cudaError_t LaunchWaitReaders(ChannelCtrl* ctrl, int half, unsigned long long need, unsigned long long timeout_ns,
+                              CommStatus* status, int my_rank, cudaStream_t stream) {
+  wait_readers_kernel<<<1, 1, 0, stream>>>(ctrl, half, need, timeout_ns, status, my_rank);
   CountKernelLaunch();
   return cudaGetLastError();
 }

@@ -34,6 +34,7 @@ enum CommError : uint32_t {
   kCommBadArgument = 3,
   kCommPeerFailed = 4,     // a source published a version it could not complete (its own wait had expired)
   kCommTimeoutLock = 5,    // a window mutex word stayed taken for longer than the limit
+  kCommLayoutMismatch = 6, // a source published from registered memory that this reader has no matching pointer for
 };
 
 struct alignas(256) ChannelCtrl {
@@ -50,6 +51,10 @@ struct alignas(256) ChannelCtrl {
   // that nobody hangs, but marked; readers report kCommPeerFailed and leave their outputs alone.
   unsigned long long failed_epoch;
   unsigned int launch_failed;           // set by any block of the owner's launches of the current version
+  // Where the payload of each half's version lives: 0 = in the arena half; otherwise the key of a registered
+  // tensor (symmetric buffer id and byte offset, see RegisteredLoc) that the owner published in place, without a
+  // copy into the arena.  Written with the header of every version.
+  unsigned long long payload_loc[2];
 };
 
 // Host-visible status block (pinned, mapped): kernels write, the host reads after the
@@ -74,6 +79,7 @@ struct PackParams {
   unsigned long long publish_epoch;  // value stored to ctrl->epoch when publish != 0
   unsigned long long timeout_ns;
   unsigned long long payload_bytes;
+  unsigned long long loc;       // ChannelCtrl::payload_loc of this version
   int half;
   int wait_done;                // 1: perform the done-wait (first launch of a version)
   int publish;                  // 1: store the header and the epoch (last launch of a version)
@@ -117,7 +123,13 @@ struct CombineParams {
   unsigned long long off[kMaxSeg];      // byte offset of the segment inside every arena half
   unsigned long long numel[kMaxSeg];
   unsigned long long chunk_start[kMaxSeg + 1];
+  // Registered payloads (one tensor, published in place): my_loc is the key this rank published with (0 = arena)
+  // and alt_src[j] the address of the same tensor in source j's registered buffer.  A source whose version says
+  // "arena" is read from its arena, one that says my_loc from alt_src[j]; anything else is kCommLayoutMismatch.
+  unsigned long long my_loc;
+  const unsigned char* alt_src[kMaxSrc];
 };
+static_assert(sizeof(CombineParams) <= 4000, "kernel parameters are limited to 4 KB");
 
 // Plain copies out of sources' arenas (allgather / neighbor_allgather / broadcast).
 struct GatherParams {
@@ -193,6 +205,11 @@ struct BucketParams {
 cudaError_t LaunchPack(const PackParams& p, cudaStream_t stream);
 cudaError_t LaunchCombine(const CombineParams& p, cudaStream_t stream);
 cudaError_t LaunchGather(const GatherParams& p, cudaStream_t stream);
+// One thread waits (bounded) until ctrl->done[half] >= need: every reader of the versions published so far in that
+// half has finished.  A rank that published a tensor in place runs it behind its own pull, so that the operation is
+// complete - and the tensor the caller's again - only when no neighbor still reads it.
+cudaError_t LaunchWaitReaders(ChannelCtrl* ctrl, int half, unsigned long long need, unsigned long long timeout_ns,
+                              CommStatus* status, int my_rank, cudaStream_t stream);
 cudaError_t LaunchBucketStep(const BucketParams& p, cudaStream_t stream);
 // buf[i] *= s for any supported element type (K1/K2 of the reference, kept as a utility).
 cudaError_t LaunchScale(void* buf, unsigned long long numel, double s, int elem_type, cudaStream_t stream);

@@ -44,14 +44,45 @@ Status Channel::StatusToError() const {
                          : st.error == kCommTimeoutDone
                                ? "timed out waiting for the readers of an earlier version (need " +
                                      std::to_string(st.want) + ", saw " + std::to_string(st.seen) + ")"
-                               : "invalid kernel argument";
+                               : st.error == kCommLayoutMismatch
+                                     ? "rank " + std::to_string(st.peer) + " published a tensor in registered memory that this "
+                                       "rank did not pass as the same registered tensor (pass tensors of bf.symmetric_empty "
+                                       "on every rank of an operation, or on none)"
+                                     : "invalid kernel argument";
   return Status::Aborted("peer-memory channel on rank " + std::to_string(rank()) + ": " + what +
                          ". The send/recv pattern of the ranks probably does not match.");
 }
 
+int SymmRegistry::Add(std::shared_ptr<SymmBuffer> buf) {
+  bufs_.push_back(std::move(buf));
+  return static_cast<int>(bufs_.size()) - 1;
+}
+
+bool SymmRegistry::Find(const void* p, uint64_t nbytes, RegisteredLoc* loc) const {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  if (p == nullptr || (a & 15) != 0) return false;
+  for (size_t id = 0; id < bufs_.size(); ++id) {
+    const SymmBuffer& b = *bufs_[id];
+    const uintptr_t base = reinterpret_cast<uintptr_t>(b.local());
+    if (a < base || a + nbytes > base + b.bytes) continue;
+    const uint64_t off = a - base;
+    loc->key = (static_cast<uint64_t>(id + 1) << 40) | off;
+    loc->ptrs.resize(b.world);
+    for (int r = 0; r < b.world; ++r) loc->ptrs[r] = static_cast<const unsigned char*>(b.ptrs[r]) + off;
+    return true;
+  }
+  return false;
+}
+
+Status Channel::WaitReaders(const Round& round, cudaStream_t stream) {
+  BFB_CUDA_OK(LaunchWaitReaders(ctrl_ptr(rank()), round.half, readers_cum_[round.half], timeout_ns_, status_, rank(), stream));
+  return Status::OK();
+}
+
 Status Channel::Publish(const std::vector<SegSpec>& segs, const double* dst_weight, int n_readers,
-                        cudaStream_t stream, Round* round) {
-  if (RequiredBytes(segs) > half_bytes_)
+                        cudaStream_t stream, Round* round, uint64_t loc) {
+  if (loc != 0 && segs.size() != 1) return Status::InvalidArgument("a registered payload is one tensor");
+  if (loc == 0 && RequiredBytes(segs) > half_bytes_)
     return Status::PreconditionError("channel arena too small for this payload");
   uint64_t need_done = 0;
   round->version = TakeVersion(n_readers, &need_done);
@@ -76,6 +107,7 @@ Status Channel::Publish(const std::vector<SegSpec>& segs, const double* dst_weig
     p.publish_epoch = round->version + 1;
     p.timeout_ns = timeout_ns_;
     p.payload_bytes = off;
+    p.loc = loc;
     p.half = round->half;
     p.wait_done = first ? 1 : 0;
     p.publish = end == n ? 1 : 0;
@@ -92,7 +124,7 @@ Status Channel::Publish(const std::vector<SegSpec>& segs, const double* dst_weig
       p.dst_off[k] = round->offsets[i];
       p.nbytes[k] = segs[i].nbytes;
       p.chunk_start[k] = chunks;
-      chunks += (segs[i].nbytes + 15) / 16;
+      if (loc == 0) chunks += (segs[i].nbytes + 15) / 16;          // registered: the header alone is published
     }
     p.chunk_start[p.n_seg] = chunks;
     BFB_CUDA_OK(LaunchPack(p, stream));
@@ -121,8 +153,10 @@ void Channel::FillSync(PullSync* s, const Round& round, const std::vector<int>& 
 
 Status Channel::PullCombine(const Round& round, const std::vector<SegSpec>& segs, int elem_type, double self_w,
                             const std::vector<int>& src_ranks, const std::vector<double>& src_w,
-                            bool use_dst_weight, double post_scale, cudaStream_t stream) {
+                            bool use_dst_weight, double post_scale, cudaStream_t stream, const RegisteredLoc* reg) {
   if (src_ranks.size() > static_cast<size_t>(kMaxSrc)) return Status::InvalidArgument("too many source ranks");
+  if (reg != nullptr && (segs.size() != 1 || reg->key == 0 || reg->ptrs.size() != static_cast<size_t>(world())))
+    return Status::InvalidArgument("a registered payload is one tensor with one address per rank");
   if (src_ranks.size() != src_w.size()) return Status::InvalidArgument("source ranks and weights differ in length");
   for (int r : src_ranks)
     if (r < 0 || r >= world() || r == rank()) return Status::InvalidArgument("invalid source rank " + std::to_string(r));
@@ -137,6 +171,13 @@ Status Channel::PullCombine(const Round& round, const std::vector<SegSpec>& segs
     FillSync(&p.sync, round, src_ranks, /*signal_done=*/end == n);
     p.sync.use_dst_weight = use_dst_weight ? 1 : 0;
     p.self_arena = arena_ptr(rank(), round.half);
+    if (reg != nullptr) {
+      // the own term and the sources that published the same registered tensor are read in place (offset 0 of the
+      // round's layout); a source that copied into its arena is read from there
+      p.self_arena = static_cast<const unsigned char*>(reg->ptrs[rank()]);
+      p.my_loc = reg->key;
+      for (size_t j = 0; j < src_ranks.size(); ++j) p.alt_src[j] = static_cast<const unsigned char*>(reg->ptrs[src_ranks[j]]);
+    }
     p.self_w = self_w;
     p.post_scale = post_scale;
     for (size_t j = 0; j < src_w.size(); ++j) p.src_w[j] = src_w[j];

@@ -25,6 +25,26 @@ struct Round {
   std::vector<uint64_t> offsets;  // per tensor, byte offset inside the arena half
 };
 
+// A tensor that lives in registered symmetric memory (the same allocation on every rank, all of them mapped into
+// this process): it is published in place - no copy into the arena - and neighbors pull it from where it is.
+struct RegisteredLoc {
+  uint64_t key = 0;                // (buffer id + 1) << 40 | byte offset inside the buffer; 0 = not registered
+  std::vector<const void*> ptrs;   // ptrs[r]: the tensor's address in rank r's buffer
+};
+
+// The registered buffers of one rank, in allocation order (allocation is collective, so ids agree across ranks).
+class SymmRegistry {
+ public:
+  int Add(std::shared_ptr<SymmBuffer> buf);
+  // Whether [p, p + nbytes) lies inside one of this rank's registered buffers and starts on a 16-byte boundary.
+  bool Find(const void* p, uint64_t nbytes, RegisteredLoc* loc) const;
+  size_t size() const { return bufs_.size(); }
+  void Clear() { bufs_.clear(); }
+
+ private:
+  std::vector<std::shared_ptr<SymmBuffer>> bufs_;
+};
+
 class Channel {
  public:
   Channel(std::shared_ptr<SymmBuffer> ctrl, std::shared_ptr<SymmBuffer> arena, size_t half_bytes);
@@ -42,12 +62,16 @@ class Channel {
 
   // Publishes one version holding the given tensors (possibly none). n_readers = how many
   // ranks will pull this version. dst_weight: world entries or nullptr.
+  // loc != 0: the (single) tensor of this version stays where it is, in registered memory with that key; segs
+  // still describes it (sizes and layout are the same on every rank) but nothing is copied.
   Status Publish(const std::vector<SegSpec>& segs, const double* dst_weight, int n_readers,
-                 cudaStream_t stream, Round* round);
+                 cudaStream_t stream, Round* round, uint64_t loc = 0);
   // out = post_scale * (self_w * mine + sum_j w_j * [dstw_j] * src_j) for every tensor of the round.
   Status PullCombine(const Round& round, const std::vector<SegSpec>& segs, int elem_type, double self_w,
                      const std::vector<int>& src_ranks, const std::vector<double>& src_w,
-                     bool use_dst_weight, double post_scale, cudaStream_t stream);
+                     bool use_dst_weight, double post_scale, cudaStream_t stream, const RegisteredLoc* reg = nullptr);
+  // Returns (on the stream) once every reader of the versions published so far in the round's half has finished.
+  Status WaitReaders(const Round& round, cudaStream_t stream);
   // Copies: for each item, nbytes from rank src's (or my own) version of tensor `seg_index`
   // starting at src_byte_off into out.
   struct CopySpec {

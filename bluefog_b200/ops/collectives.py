@@ -346,6 +346,40 @@ def neighbor_allreduce(tensor: torch.Tensor, *,
 
 
 # --------------------------------------------------------------------------------------
+# registered tensors
+# --------------------------------------------------------------------------------------
+def symmetric_empty(*shape, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """An uninitialised CUDA tensor in symmetric memory: memory of this rank's GPU that is mapped into every other
+    rank of the machine.  ``neighbor_allreduce`` publishes such a tensor in place - it raises a flag instead of copying
+    the tensor into its staging arena, and the neighbors pull it from where it is - and returns once they have.
+
+    Collective: every rank calls it, in the same order, with the same shape and dtype; every rank then passes its tensor
+    (or the same slice of it) to an operation, or none does.  The memory is released at ``shutdown()``.  Without a GPU
+    (CPU ranks, a single process) the result is an ordinary ``torch.empty`` and nothing changes.
+    The reference has no counterpart: its GPU path hands every tensor to NCCL or copies it into a fusion buffer first
+    (bluefog/common/nccl_controller.cc:1013-1204)."""
+    if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)):
+        shape = tuple(shape[0])
+    native = _b.native
+    if (native is None or not hasattr(native, "symmetric_alloc") or not torch.cuda.is_available()
+            or not _b.is_initialized() or _b.size() == 1 or _b.device() < 0):
+        device = "cuda" if torch.cuda.is_available() and _b.is_initialized() and _b.device() >= 0 else "cpu"
+        return torch.empty(*shape, dtype=dtype, device=device)
+    numel = int(np.prod(shape)) if len(shape) else 1
+    nbytes = max(numel * torch.empty((), dtype=dtype).element_size(), 16)
+    raw = native.symmetric_alloc(nbytes)
+    return raw[:numel * torch.empty((), dtype=dtype).element_size()].view(dtype).view(*shape)
+
+
+def is_symmetric(tensor: torch.Tensor) -> bool:
+    """Whether ``tensor`` lies in memory of ``symmetric_empty`` (and starts on a 16-byte boundary), i.e. whether
+    ``neighbor_allreduce`` will publish it in place."""
+    native = _b.native
+    return bool(native is not None and hasattr(native, "is_symmetric") and tensor.is_cuda and _b.is_initialized()
+                and native.is_symmetric(tensor))
+
+
+# --------------------------------------------------------------------------------------
 # hierarchical_neighbor_allreduce
 # --------------------------------------------------------------------------------------
 def _resolve_machine_weights(self_weight, src_machine_weights, dst_machine_weights):

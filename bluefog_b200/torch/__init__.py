@@ -44,6 +44,7 @@ from bluefog_b200.ops.collectives import (  # noqa: E402
     hierarchical_neighbor_allreduce, hierarchical_neighbor_allreduce_nonblocking,
     pair_gossip, pair_gossip_nonblocking,
     poll, synchronize, wait, barrier,
+    symmetric_empty, is_symmetric,
 )
 from bluefog_b200.ops.windows import (  # noqa: E402
     win_create, win_free, win_update, win_update_then_collect,

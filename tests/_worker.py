@@ -735,6 +735,50 @@ def gpu_fused_optimizers():
 
 
 @case
+def gpu_registered_tensors():
+    """neighbor_allreduce of tensors in symmetric memory (published in place), with and without negotiation, static
+    and per-call weights, a slice of a registered tensor, and the same values as the copying path."""
+    r, n = bf.rank(), bf.size()
+    d = dev()
+    bf.set_topology(bf.RingGraph(n))
+    nb = bf.in_neighbor_ranks()
+    w = 1.0 / (len(nb) + 1)
+    numel = 3 * 1024 * 1024 + 77
+    x = bf.symmetric_empty(numel, dtype=torch.float32)
+    assert bf.is_symmetric(x) and x.is_cuda and x.shape == (numel,)
+    assert not bf.is_symmetric(torch.empty(16, device=d))
+    base = torch.arange(numel, device=d, dtype=torch.float32) % 11.0
+    for skip in (False, True):
+        bf.set_skip_negotiate_stage(skip)
+        for it in range(3):
+            x.copy_(base + r + it)
+            out = bf.neighbor_allreduce(x, name=f"reg.{int(skip)}.{it}")
+            ref = w * ((base + r + it) + sum(base + q + it for q in nb))
+            assert torch.allclose(out, ref, atol=1e-5), (out[:4], ref[:4])
+            # the tensor is the caller's again when the call returns: overwrite it right away
+            x.zero_()
+        bf.barrier()
+    bf.set_skip_negotiate_stage(False)
+    # a 16-byte aligned slice, bf16, explicit weights; the copying path on an ordinary tensor gives the same values
+    xb = bf.symmetric_empty(2, 70000, dtype=torch.bfloat16)
+    xb.copy_(((torch.arange(140000, device=d) % 13).float() + r).view(2, 70000))
+    part = xb[1, 8:60008]
+    assert bf.is_symmetric(part)
+    sw = {q: 0.5 / len(nb) for q in nb}
+    got = bf.neighbor_allreduce(part, self_weight=0.5, src_weights=sw, name="reg.slice")
+    want = bf.neighbor_allreduce(part.clone(), self_weight=0.5, src_weights=sw, name="reg.slice.copy")
+    assert torch.equal(got, want)
+    # nonblocking series on registered tensors
+    ys = [bf.symmetric_empty(5000 + k) for k in range(4)]
+    for k, y in enumerate(ys):
+        y.fill_(float(r + k))
+    hs = [bf.neighbor_allreduce_nonblocking(y, name=f"reg.series.{k}") for k, y in enumerate(ys)]
+    for k, h in enumerate(hs):
+        close(bf.synchronize(h), w * ((r + k) + sum(q + k for q in nb)), 1e-5)
+    bf.barrier()
+
+
+@case
 def gpu_fast_path():
     """Negotiation-free GPU collectives issued on the calling thread: blocking, nonblocking series, mixed
     with queued operations, and large tensors right before small ones."""

@@ -138,3 +138,55 @@ def test_scale_kernel():
         C.scale_(x, 3.0)
         torch.cuda.synchronize()
         assert torch.equal(x, ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_registered_tensors_are_published_in_place(dtype):
+    """Tensors in registered symmetric memory: the publish is a header and a flag, the pull reads the neighbors'
+    tensors where they are, and a closing wait returns once every reader is done.  Ring of three ranks, several
+    versions (both arena halves), a tensor that starts inside its buffer."""
+    from bluefog_b200 import _C
+    W, n = 3, 100003
+    es = torch.empty((), dtype=dtype).element_size()
+    world = _C.LocalWorld(W, 4096, 0)                     # an arena far too small for the tensors: they never go there
+    bufs = world.alloc_symmetric(n * es + 64)
+    xs = [bufs[r][32:32 + n * es].view(dtype) for r in range(W)]
+    outs = [torch.empty(n, device="cuda", dtype=dtype) for _ in range(W)]
+    for it in range(4):
+        for r in range(W):
+            xs[r].copy_(torch.randn(n, device="cuda").to(dtype))
+        rounds = [world.publish_in_place(r, xs[r], None, 1) for r in range(W)]
+        for r in range(W):
+            world.combine_in_place(r, rounds[r], xs[r], outs[r], 0.25, [(r - 1) % W], [0.75], False, 1.0)
+        for r in range(W):
+            world.wait_readers(r, rounds[r])
+        torch.cuda.synchronize()
+        for r in range(W):
+            assert world.status(r)[0] == 0, world.status(r)
+            ref = 0.25 * xs[r].float() + 0.75 * xs[(r - 1) % W].float()
+            assert torch.allclose(outs[r].float(), ref, atol=2e-2 if dtype == torch.bfloat16 else 1e-6)
+
+
+def test_registered_and_copied_payloads_mix_and_mismatches_are_reported():
+    """A reader follows what each source announces: a source that copied into its arena is read there even by a rank
+    that published in place; a source that published in place towards a rank without the matching registered tensor
+    makes that rank report a layout mismatch (and nobody waits for ever)."""
+    from bluefog_b200 import _C
+    W, n = 2, 4096
+    world = _C.LocalWorld(W, n * 4 + 4096, 0)
+    bufs = world.alloc_symmetric(n * 4)
+    x0 = torch.randn(n, device="cuda")                   # rank 0: an ordinary tensor -> arena
+    x1 = bufs[1].view(torch.float32)                     # rank 1: registered -> in place
+    x1.copy_(torch.randn(n, device="cuda"))
+    outs = [torch.zeros(n, device="cuda") for _ in range(W)]
+    r0 = world.publish_in_place(0, x0, None, 1)
+    r1 = world.publish_in_place(1, x1, None, 1)
+    world.combine_in_place(0, r0, x0, outs[0], 0.5, [1], [0.5], False, 1.0)
+    world.combine_in_place(1, r1, x1, outs[1], 0.5, [0], [0.5], False, 1.0)
+    world.wait_readers(1, r1)
+    torch.cuda.synchronize()
+    assert world.status(1)[0] == 0, world.status(1)
+    assert torch.allclose(outs[1], 0.5 * x1 + 0.5 * x0, atol=1e-6)
+    err, peer, _, _ = world.status(0)
+    assert err == 6 and peer == 1, world.status(0)       # kCommLayoutMismatch, reported about rank 1
+    assert torch.count_nonzero(outs[0]) == 0             # nothing was combined

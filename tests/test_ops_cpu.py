@@ -106,3 +106,12 @@ def test_layer_norm_residual_falls_back_on_cpu():
     (F.layer_norm(ref, (16,), w, b).sum() + 2 * ref.sum()).backward()
     assert torch.allclose(x.grad, ref.grad)
     assert fused_ln.take_column_sums(x.grad.reshape(-1, 16)) is None
+
+
+def test_symmetric_empty_without_a_gpu_world_is_an_ordinary_tensor():
+    import torch
+    import bluefog_b200.torch as bf
+    x = bf.symmetric_empty(3, 5, dtype=torch.bfloat16)
+    assert x.shape == (3, 5) and x.dtype == torch.bfloat16
+    assert bf.symmetric_empty((4,)).shape == (4,)
+    assert not bf.is_symmetric(x)

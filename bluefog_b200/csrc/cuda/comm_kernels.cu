@@ -319,7 +319,11 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(const __grid_constant
   if (ok) {
     for (int j = threadIdx.x; j < p.sync.n_src; j += blockDim.x) {
       const unsigned long long loc = ld_acquire_sys(&p.sync.src_ctrl[j]->payload_loc[p.sync.half]);
-      if (loc == 0ull) {
+      const unsigned long long have = ld_acquire_sys(&p.sync.src_ctrl[j]->payload_bytes[p.sync.half]);
+      if (have < p.need_bytes) {
+        report_error(p.sync.status, kCommLayoutMismatch, (unsigned)p.sync.src_rank[j], p.need_bytes, have);
+        layout_ok = 0;
+      } else if (loc == 0ull) {
         base_s[j] = p.sync.src_arena[j];
       } else if (loc == p.my_loc) {
         base_s[j] = p.alt_src[j];

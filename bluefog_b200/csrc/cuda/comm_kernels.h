@@ -128,6 +128,10 @@ struct CombineParams {
   // "arena" is read from its arena, one that says my_loc from alt_src[j]; anything else is kCommLayoutMismatch.
   unsigned long long my_loc;
   const unsigned char* alt_src[kMaxSrc];
+  // Bytes of a source's payload this launch reads (largest segment end).  A source whose version is shorter than that
+  // was published with another layout (ranks that disagree about sizes while negotiation is skipped): the reader
+  // reports kCommLayoutMismatch instead of reading past what was written.
+  unsigned long long need_bytes;
 };
 static_assert(sizeof(CombineParams) <= 4000, "kernel parameters are limited to 4 KB");
 

@@ -45,9 +45,10 @@ Status Channel::StatusToError() const {
                                ? "timed out waiting for the readers of an earlier version (need " +
                                      std::to_string(st.want) + ", saw " + std::to_string(st.seen) + ")"
                                : st.error == kCommLayoutMismatch
-                                     ? "rank " + std::to_string(st.peer) + " published a tensor in registered memory that this "
-                                       "rank did not pass as the same registered tensor (pass tensors of bf.symmetric_empty "
-                                       "on every rank of an operation, or on none)"
+                                     ? "the version rank " + std::to_string(st.peer) + " published does not have the layout this "
+                                       "rank reads (expected " + std::to_string(st.want) + ", found " + std::to_string(st.seen) +
+                                       "): tensor sizes differ between the ranks, or only some ranks passed a tensor of "
+                                       "bf.symmetric_empty"
                                      : "invalid kernel argument";
   return Status::Aborted("peer-memory channel on rank " + std::to_string(rank()) + ": " + what +
                          ". The send/recv pattern of the ranks probably does not match.");
@@ -191,6 +192,8 @@ Status Channel::PullCombine(const Round& round, const std::vector<SegSpec>& segs
       p.numel[k] = segs[i].numel;
       p.chunk_start[k] = chunks;
       chunks += (segs[i].numel + per_vec - 1) / per_vec;
+      const uint64_t end_byte = p.off[k] + segs[i].numel * static_cast<uint64_t>(esize);
+      if (end_byte > p.need_bytes) p.need_bytes = end_byte;
     }
     p.chunk_start[p.n_seg] = chunks;
     BFB_CUDA_OK(LaunchCombine(p, stream));

@@ -29,14 +29,22 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr", "--use_fast_math", "-Xptxas", "-v",
 ]
 
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-sign-compare", "-Wno-unused-function"]
+LINK_FLAGS = ["-Wl,--strip-debug"]
+if os.environ.get("BLUEFOG_B200_TSAN") == "1":
+    # ThreadSanitizer build of the host runtime (the .cc files; device code is not instrumented).  Build it beside the
+    # regular library, not over it, and load it with BLUEFOG_B200_NATIVE (see `make tsan`):
+    #   CC=/usr/bin/gcc CXX=/usr/bin/g++ BLUEFOG_B200_TSAN=1 python setup.py build_ext --build-lib build/tsan --build-temp build/tsan_tmp
+    CXX_FLAGS = ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=thread", "-std=c++17", "-fPIC", "-Wno-sign-compare"]
+    LINK_FLAGS = ["-fsanitize=thread"]
+
 ext = CUDAExtension(
     name="bluefog_b200._C",
     sources=sources(),
     include_dirs=[os.path.join(ROOT, CSRC)],
-    extra_compile_args={"cxx": ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-sign-compare", "-Wno-unused-function"],
-                        "nvcc": NVCC_FLAGS},
+    extra_compile_args={"cxx": CXX_FLAGS, "nvcc": NVCC_FLAGS},
     libraries=["rt"],
-    extra_link_args=["-Wl,--strip-debug"],
+    extra_link_args=LINK_FLAGS,
 )
 
 setup(

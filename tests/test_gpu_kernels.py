@@ -190,3 +190,22 @@ def test_registered_and_copied_payloads_mix_and_mismatches_are_reported():
     err, peer, _, _ = world.status(0)
     assert err == 6 and peer == 1, world.status(0)       # kCommLayoutMismatch, reported about rank 1
     assert torch.count_nonzero(outs[0]) == 0             # nothing was combined
+
+
+def test_reader_reports_a_source_whose_payload_is_shorter_than_what_it_reads():
+    """Ranks that disagree about a tensor's size (possible when negotiation is skipped): the rank that expects more
+    than its source published reports a layout mismatch and combines nothing; the other direction is unaffected."""
+    from bluefog_b200 import _C
+    world = _C.LocalWorld(2, 1 << 20, 0)
+    small, large = torch.randn(1000, device="cuda"), torch.randn(5000, device="cuda")
+    out0, out1 = torch.zeros(1000, device="cuda"), torch.zeros(5000, device="cuda")
+    r0 = world.publish(0, [small], None, 1)
+    r1 = world.publish(1, [large], None, 1)
+    world.combine(0, r0, [out0], 0.5, [1], [0.5], False, 1.0)
+    world.combine(1, r1, [out1], 0.5, [0], [0.5], False, 1.0)
+    torch.cuda.synchronize()
+    assert world.status(0)[0] == 0
+    assert torch.allclose(out0, 0.5 * small + 0.5 * large[:1000], atol=1e-6)
+    err, peer, want, seen = world.status(1)
+    assert err == 6 and peer == 0 and want == 20000 and seen < want, world.status(1)
+    assert torch.count_nonzero(out1) == 0

@@ -53,6 +53,17 @@ Status Bucket::Step(const BucketStepArgs& a, cudaStream_t stream) {
   p.state2 = static_cast<float*>(a.state2);
   p.state3 = static_cast<float*>(a.state3);
   p.shadow = a.shadow;
+  {
+    // the state arrays the chosen optimizer reads and writes (the same table as in bucket_step_kernel) have to exist
+    const bool updates = (a.mode == kModeAWC || a.mode == kModeAdaptPublish || a.mode == kModeGradReduce) &&
+                         (a.grad != nullptr || a.grad_ptrs != nullptr);
+    if (a.opt < kOptNone || a.opt > kOptAdadelta) return Status::InvalidArgument("bucket step: unknown optimizer");
+    const bool need1 = (a.opt == kOptSGD && a.momentum != 0.0) || a.opt >= kOptAdam;
+    const bool need2 = a.opt == kOptAdam || a.opt == kOptAdadelta || (a.opt == kOptRMSprop && a.momentum > 0.0);
+    const bool need3 = (a.opt == kOptAdam || a.opt == kOptRMSprop) && a.amsgrad;
+    if (updates && ((need1 && p.state1 == nullptr) || (need2 && p.state2 == nullptr) || (need3 && p.state3 == nullptr)))
+      return Status::InvalidArgument("bucket step: an optimizer state buffer is missing");
+  }
 
   PullSync& s = p.sync;
   s.my_rank = ch.rank();

@@ -485,6 +485,40 @@ __device__ __forceinline__ float opt_update(const OptConst& o, float c, float g,
     const float denom = __fdiv_rn(__fsqrt_rn(vhat), __fsqrt_rn(o.bias2)) + o.eps;
     return c - __fdiv_rn(o.lr, o.bias1) * __fdiv_rn(m, denom);
   }
+  if (o.opt == kOptRMSprop) {                       // torch.optim.RMSprop: beta2 = alpha, amsgrad = centered
+    g = g + o.wd * c;
+    const float sq = o.beta2 * s1 + (1.f - o.beta2) * g * g;
+    s1 = sq;
+    float avg;
+    if (o.amsgrad) {
+      const float ga = o.beta2 * s3 + (1.f - o.beta2) * g;
+      s3 = ga;
+      avg = __fsqrt_rn(sq - ga * ga);
+    } else {
+      avg = __fsqrt_rn(sq);
+    }
+    avg += o.eps;
+    if (o.momentum > 0.f) {
+      const float buf = o.momentum * s2 + __fdiv_rn(g, avg);
+      s2 = buf;
+      return c - o.lr * buf;
+    }
+    return c - o.lr * __fdiv_rn(g, avg);
+  }
+  if (o.opt == kOptAdagrad) {                       // torch.optim.Adagrad: lr is the decayed rate of this step
+    g = g + o.wd * c;
+    const float sum = s1 + g * g;
+    s1 = sum;
+    return c - o.lr * __fdiv_rn(g, __fsqrt_rn(sum) + o.eps);
+  }
+  if (o.opt == kOptAdadelta) {                      // torch.optim.Adadelta: beta2 = rho
+    g = g + o.wd * c;
+    const float sq = o.beta2 * s1 + (1.f - o.beta2) * g * g;
+    s1 = sq;
+    const float delta = __fdiv_rn(__fsqrt_rn(s2 + o.eps), __fsqrt_rn(sq + o.eps)) * g;
+    s2 = o.beta2 * s2 + (1.f - o.beta2) * delta * delta;
+    return c - o.lr * delta;
+  }
   return c;
 }
 
@@ -570,10 +604,10 @@ __global__ void __launch_bounds__(kThreads) bucket_step_kernel(const __grid_cons
     const bool has_grad = any_grad && p.opt != kOptNone;
     const bool wants_grad = any_grad && (has_grad || mode == kModeGradReduce || mode == kModePublishOnly);
     // which state arrays the optimizer reads (ld) and writes (st)
-    const bool st1 = (o.opt == kOptSGD && o.momentum != 0.f) || o.opt == kOptAdam;
+    const bool st1 = (o.opt == kOptSGD && o.momentum != 0.f) || o.opt >= kOptAdam;
     const bool ld1 = st1 && !(o.opt == kOptSGD && o.first_step);
-    const bool st2 = o.opt == kOptAdam;
-    const bool st3 = o.opt == kOptAdam && o.amsgrad;
+    const bool st2 = o.opt == kOptAdam || o.opt == kOptAdadelta || (o.opt == kOptRMSprop && o.momentum > 0.f);
+    const bool st3 = (o.opt == kOptAdam || o.opt == kOptRMSprop) && o.amsgrad;
     // Main loop: 4 elements per thread per step; published/grad buffers are padded to 16 bytes.
     for (unsigned long long q = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; q * 4 < p.numel; q += stride) {
       const unsigned long long i0 = q * 4;

@@ -147,7 +147,9 @@ struct GatherParams {
   unsigned long long chunk_start[kMaxSeg + 1];
 };
 
-enum BucketOpt : int { kOptNone = 0, kOptSGD = 1, kOptAdam = 2 };
+// kOptRMSprop: beta2 = alpha, amsgrad = centered; state1 square_avg, state2 momentum_buffer, state3 grad_avg.
+// kOptAdagrad: lr = the step's decayed rate; state1 sum.  kOptAdadelta: beta2 = rho; state1 square_avg, state2 acc_delta.
+enum BucketOpt : int { kOptNone = 0, kOptSGD = 1, kOptAdam = 2, kOptRMSprop = 3, kOptAdagrad = 4, kOptAdadelta = 5 };
 enum BucketMode : int {
   // c = self_w*P + sum_j w_j*pub_j(v);  P' = c - step(g, c);  pub(v+1) = P'   (adapt-with-combine)
   kModeAWC = 0,

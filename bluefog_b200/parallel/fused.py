@@ -9,7 +9,7 @@ shadow that ``p.data`` aliases (bf16 compute with fp32 master weights), and a na
 
 One kernel launch per bucket and step (two for adapt-then-combine and gradient allreduce)
 pulls the in-neighbors' published copies over NVLink, forms the weighted combine, applies
-SGD(momentum/nesterov/weight decay) or Adam/AdamW(amsgrad), and writes master, published copy
+SGD(momentum/nesterov/weight decay), Adam/AdamW(amsgrad), RMSprop(momentum, centered), Adagrad or Adadelta, and writes master, published copy
 and shadow in the same pass.  The maths of the three styles is that of the reference
 wrappers (bluefog/torch/optimizers.py:297-319, 485-841, 166-294).
 """
@@ -27,7 +27,10 @@ from bluefog_b200.ops import collectives as _ops
 _b = get_basics()
 
 MODE_AWC, MODE_ADAPT_PUBLISH, MODE_COMBINE_ONLY, MODE_GRAD_REDUCE, MODE_PUBLISH_ONLY = 0, 1, 2, 3, 4
-OPT_NONE, OPT_SGD, OPT_ADAM = 0, 1, 2
+OPT_NONE, OPT_SGD, OPT_ADAM, OPT_RMSPROP, OPT_ADAGRAD, OPT_ADADELTA = 0, 1, 2, 3, 4, 5
+_KINDS = ((torch.optim.SGD, OPT_SGD), (torch.optim.Adam, OPT_ADAM), (torch.optim.AdamW, OPT_ADAM),
+          (torch.optim.RMSprop, OPT_RMSPROP), (torch.optim.Adagrad, OPT_ADAGRAD), (torch.optim.Adadelta, OPT_ADADELTA))
+
 _ALIGN = 64  # elements; keeps every parameter view 128-byte aligned even in bf16
 
 
@@ -45,10 +48,10 @@ def republish_live():
 
 def supported(optimizer, model, communication_type) -> bool:
     """True when the bucket engine can take over: initialised runtime on a GPU, every
-    parameter on that GPU in fp32, optimizer exactly SGD, Adam or AdamW."""
+    parameter on that GPU in fp32, optimizer exactly SGD, Adam, AdamW, RMSprop, Adagrad or Adadelta."""
     if not _b.is_initialized() or _b.device() < 0:
         return False
-    if type(optimizer) not in (torch.optim.SGD, torch.optim.Adam, torch.optim.AdamW):
+    if type(optimizer) not in tuple(cls for cls, _ in _KINDS):
         return False
     for g in optimizer.param_groups:
         if g.get("capturable") or g.get("differentiable"):
@@ -95,6 +98,18 @@ class _BucketState:
             self.state2 = torch.zeros(n, dtype=torch.float32, device=device)
             if group.get("amsgrad", False):
                 self.state3 = torch.zeros(n, dtype=torch.float32, device=device)
+        if opt_kind == OPT_RMSPROP:                  # square_avg, momentum_buffer, grad_avg
+            self.state1 = torch.zeros(n, dtype=torch.float32, device=device)
+            if group.get("momentum", 0) > 0:
+                self.state2 = torch.zeros(n, dtype=torch.float32, device=device)
+            if group.get("centered", False):
+                self.state3 = torch.zeros(n, dtype=torch.float32, device=device)
+        if opt_kind == OPT_ADAGRAD:                  # sum
+            self.state1 = torch.full((n,), float(group.get("initial_accumulator_value", 0.0)), dtype=torch.float32,
+                                     device=device)
+        if opt_kind == OPT_ADADELTA:                 # square_avg, acc_delta
+            self.state1 = torch.zeros(n, dtype=torch.float32, device=device)
+            self.state2 = torch.zeros(n, dtype=torch.float32, device=device)
         self.steps = 0            # optimizer updates applied to this bucket
         self.first_step = True    # SGD momentum buffer not initialised yet
         self.native = _b.native.Bucket.create(n, "bfloat16" if pub_dtype == torch.bfloat16 else "float32")
@@ -148,7 +163,7 @@ class _FusedMixin:
         self._compute_dtype = compute_dtype
         if bucket_bytes is None:
             bucket_bytes = int(os.environ.get("BLUEFOG_B200_BUCKET_BYTES", 64 * 1024 * 1024))
-        self._opt_kind = OPT_SGD if isinstance(self, torch.optim.SGD) else OPT_ADAM
+        self._opt_kind = next(kind for cls, kind in _KINDS if isinstance(self, cls))
         self._adamw = isinstance(self, torch.optim.AdamW)
         device = torch.device("cuda", _b.device())
         self._buckets = []
@@ -193,7 +208,7 @@ class _FusedMixin:
                         bk.first_step = False
                     st["momentum_buffer"] = bk.view(bk.state1, i)
             else:
-                for key, flat in (("exp_avg", bk.state1), ("exp_avg_sq", bk.state2), ("max_exp_avg_sq", bk.state3)):
+                for key, flat in self._state_pairs(bk):
                     if flat is None:
                         continue
                     old = st.get(key)
@@ -227,6 +242,18 @@ class _FusedMixin:
             a.nesterov = bool(g.get("nesterov", False))
             a.first_step = bk.first_step
             a.state1 = bk.state1
+        elif self._opt_kind == OPT_RMSPROP:
+            a.beta2, a.eps = float(g["alpha"]), float(g["eps"])
+            a.momentum = float(g.get("momentum", 0.0))
+            a.amsgrad = bool(g.get("centered", False))          # the kernel's flag for the third state array
+            a.state1, a.state2, a.state3 = bk.state1, bk.state2, bk.state3
+        elif self._opt_kind == OPT_ADAGRAD:
+            a.lr = float(g["lr"]) / (1.0 + bk.steps * float(g.get("lr_decay", 0.0)))
+            a.eps = float(g["eps"])
+            a.state1 = bk.state1
+        elif self._opt_kind == OPT_ADADELTA:
+            a.beta2, a.eps = float(g["rho"]), float(g["eps"])
+            a.state1, a.state2 = bk.state1, bk.state2
         else:
             b1, b2 = g["betas"]
             step = bk.steps + 1
@@ -509,10 +536,16 @@ class _FusedMixin:
     def _state_pairs(self, bk):
         if self._opt_kind == OPT_SGD:
             return (("momentum_buffer", bk.state1),)
+        if self._opt_kind == OPT_RMSPROP:
+            return (("square_avg", bk.state1), ("momentum_buffer", bk.state2), ("grad_avg", bk.state3))
+        if self._opt_kind == OPT_ADAGRAD:
+            return (("sum", bk.state1),)
+        if self._opt_kind == OPT_ADADELTA:
+            return (("square_avg", bk.state1), ("acc_delta", bk.state2))
         return (("exp_avg", bk.state1), ("exp_avg_sq", bk.state2), ("max_exp_avg_sq", bk.state3))
 
     def state_dict(self):
-        if self._opt_kind == OPT_ADAM:
+        if self._opt_kind != OPT_SGD:
             for bk in self._buckets:
                 for p in bk.params:
                     self.state[p]["step"] = torch.tensor(float(bk.steps))
@@ -558,7 +591,7 @@ class _FusedMixin:
                     st[key] = bk.view(flat, i)
                 if "step" in src:
                     bk.steps = int(float(src["step"]))
-                if self._opt_kind == OPT_ADAM:
+                if self._opt_kind != OPT_SGD:
                     st["step"] = torch.tensor(float(bk.steps))
             if extra is not None and k < len(extra.get("first_step", [])):
                 bk.first_step = bool(extra["first_step"][k])

@@ -13,7 +13,7 @@ bluefog/torch/optimizers.py:1180-1554).  Update styles:
   the gradient exists and then launches the exchange:  w+ = Combine(w - lr * g(w)).
 * gradient allreduce (Horovod style), one-sided win_put / pull-get, and push-sum.
 
-On CUDA with SGD or Adam/AdamW the AWC, ATC and gradient-allreduce styles run on the
+On CUDA with SGD, Adam/AdamW, RMSprop, Adagrad or Adadelta the AWC, ATC and gradient-allreduce styles run on the
 fused bucket engine (``bluefog_b200.parallel.fused``): parameters live in flat peer-mapped
 buckets and one kernel per bucket does combine + update + casts.  Everything else uses the
 per-parameter path below, which works for any optimizer class and any device.
@@ -733,7 +733,7 @@ def DistributedAdaptWithCombineOptimizer(optimizer, model,
                                          communication_type=CommunicationType.neighbor_allreduce,
                                          num_steps_per_communication=1, fused=None, **fused_kwargs):
     """w+ = Combine(w) - lr * g(w). ``fused=None`` picks the bucket engine when it applies
-    (CUDA parameters, SGD/Adam/AdamW, not hierarchical); ``fused_kwargs``: ``compute_dtype``,
+    (CUDA parameters, SGD/Adam/AdamW/RMSprop/Adagrad/Adadelta, not hierarchical); ``fused_kwargs``: ``compute_dtype``,
     ``exchange_dtype``, ``bucket_bytes``."""
     obj = _maybe_fused(optimizer, model, "awc", communication_type, num_steps_per_communication, fused, **fused_kwargs)
     if obj is not None:

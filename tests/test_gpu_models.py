@@ -252,3 +252,45 @@ def test_resnet50_on_own_kernels_matches_the_library_routing():
     assert rel(ga["fc.bias"].grad, gb["fc.bias"].grad) < 2e-2
     assert rel(ga["fc.weight"].grad, gb["fc.weight"].grad) < 0.25
     assert all(p.grad is not None and torch.isfinite(p.grad.float()).all() for p in a.parameters())
+
+
+@pytest.mark.parametrize("make", [
+    lambda ps: torch.optim.RMSprop(ps, lr=1e-3, alpha=0.95, weight_decay=1e-4),
+    lambda ps: torch.optim.RMSprop(ps, lr=1e-3, momentum=0.9, centered=True),
+    lambda ps: torch.optim.Adagrad(ps, lr=0.05, lr_decay=0.01, initial_accumulator_value=0.1, weight_decay=1e-4),
+    lambda ps: torch.optim.Adadelta(ps, lr=1.0, rho=0.9, weight_decay=1e-4),
+    lambda ps: torch.optim.Adam(ps, lr=1e-3, amsgrad=True),
+], ids=["rmsprop", "rmsprop-centered-momentum", "adagrad", "adadelta", "adam-amsgrad"])
+def test_fused_update_of_every_supported_optimizer_matches_torch(bf, make):
+    """The bucket kernel's update arithmetic against torch.optim on the same gradients, four steps, and the state
+    dictionary under torch's own key names."""
+    torch.manual_seed(1)
+    dev = torch.device("cuda", 0)
+    m1 = torch.nn.Sequential(torch.nn.Linear(37, 64), torch.nn.Tanh(), torch.nn.Linear(64, 10)).to(dev)
+    m2 = torch.nn.Sequential(torch.nn.Linear(37, 64), torch.nn.Tanh(), torch.nn.Linear(64, 10)).to(dev)
+    m2.load_state_dict(m1.state_dict())
+    o1 = make(m1.parameters())
+    o2 = bf.DistributedNeighborAllreduceOptimizer(make(m2.parameters()), m2)
+    assert hasattr(o2, "master_parameters"), "the bucket engine did not take this optimizer"
+    x = torch.randn(16, 37, device=dev)
+    y = torch.randint(0, 10, (16,), device=dev)
+    for _ in range(4):
+        o1.zero_grad()
+        o2.zero_grad()
+        torch.nn.functional.cross_entropy(m2(x), y).backward()
+        for p1, p2 in zip(m1.parameters(), m2.parameters()):
+            p1.grad = p2.grad.detach().clone()
+        o1.step()
+        o2.step()
+        torch.cuda.synchronize()
+        o2.check()
+        for p1, p2 in zip(m1.parameters(), m2.parameters()):
+            assert torch.allclose(p1, p2, rtol=2e-5, atol=2e-6), (p1 - p2).abs().max().item()
+    s1, s2 = o1.state_dict()["state"], o2.state_dict()["state"]
+    for k in s1:
+        assert set(s1[k]) == set(s2[k]), (set(s1[k]), set(s2[k]))
+        for name, v in s1[k].items():
+            if name != "step":
+                assert torch.allclose(v, s2[k][name].to(v.dtype), rtol=1e-4, atol=1e-7), name
+            else:
+                assert float(v) == float(s2[k][name])

@@ -18,6 +18,7 @@
 #include "cuda/combine_noalloc.h"
 #include "cuda/ce_kernels.h"
 #include "cuda/conv_tcgen05.h"
+#include "cuda/embed_kernels.h"
 #include "cuda/gemm_tcgen05.h"
 #include "cuda/gpu_channel.h"
 #include "cuda/ln_kernels.h"
@@ -700,6 +701,42 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     // rows of sums: dgamma, dbeta(, column sums of dx); one tensor so that a caller converts them in one pass
     return std::make_tuple(dx, sums);
   }, py::arg("dy"), py::arg("x"), py::arg("gamma"), py::arg("mean"), py::arg("rstd"), py::arg("addend") = py::none());
+
+  // ---- token + position embedding (GPT-2) ------------------------------------------------------
+  m.def("embed_forward", [](at::Tensor idx, at::Tensor wte, at::Tensor wpe) {
+    TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kLong && idx.dim() == 2 && idx.is_contiguous(),
+                "embed_forward: idx has to be a contiguous int64 CUDA matrix [batch, positions]");
+    TORCH_CHECK(wte.is_cuda() && wpe.is_cuda() && wte.scalar_type() == at::kBFloat16 && wpe.scalar_type() == at::kBFloat16 &&
+                wte.dim() == 2 && wpe.dim() == 2 && wte.is_contiguous() && wpe.is_contiguous() && wte.size(1) == wpe.size(1) &&
+                wte.size(1) % 8 == 0 && idx.size(1) <= wpe.size(0) && idx.numel() > 0,
+                "embed_forward: bf16 tables [V, C] and [P, C] with C % 8 == 0 and at most P positions");
+    c10::cuda::CUDAGuard g(idx.get_device());
+    const int C = static_cast<int>(wte.size(1));
+    at::Tensor out = at::empty({idx.size(0), idx.size(1), wte.size(1)}, wte.options());
+    at::Tensor bad = at::zeros({1}, idx.options().dtype(at::kInt));
+    cudaError_t e = LaunchEmbedForward(reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()), wte.data_ptr(), wpe.data_ptr(), out.data_ptr(), idx.numel(), static_cast<int>(idx.size(1)),
+                                       C, wte.size(0), bad.data_ptr<int>(), CurrentStream(idx.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "embed_forward launch failed: ", cudaGetErrorString(e));
+    return std::make_tuple(out, bad);
+  });
+  // slot: int32 [V] filled with INT_MAX, acc: fp32 [N, C] zeros; both come back in that state
+  m.def("embed_backward", [](at::Tensor idx, at::Tensor dx, int64_t vocab, at::Tensor slot, at::Tensor acc) {
+    TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kLong && idx.dim() == 2 && idx.is_contiguous() && dx.is_cuda() &&
+                dx.scalar_type() == at::kBFloat16 && dx.is_contiguous() && dx.dim() == 3 && dx.size(0) == idx.size(0) &&
+                dx.size(1) == idx.size(1) && dx.size(2) % 8 == 0, "embed_backward: dx has to be contiguous bf16 [batch, positions, C]");
+    TORCH_CHECK(slot.is_cuda() && slot.scalar_type() == at::kInt && slot.numel() >= vocab && acc.is_cuda() &&
+                acc.scalar_type() == at::kFloat && acc.numel() >= dx.numel() && slot.is_contiguous() && acc.is_contiguous(),
+                "embed_backward: scratch buffers too small");
+    c10::cuda::CUDAGuard g(idx.get_device());
+    const int C = static_cast<int>(dx.size(2));
+    at::Tensor d_wte = at::empty({vocab, dx.size(2)}, dx.options());
+    at::Tensor d_wpe = at::empty({idx.size(1), dx.size(2)}, dx.options());
+    cudaError_t e = LaunchEmbedBackward(reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()), dx.data_ptr(), d_wte.data_ptr(),
+                                        d_wpe.data_ptr(), slot.data_ptr<int>(), acc.data_ptr<float>(), idx.numel(),
+                                        static_cast<int>(idx.size(1)), C, vocab, CurrentStream(idx.get_device()));
+    TORCH_CHECK(e == cudaSuccess, "embed_backward launch failed: ", cudaGetErrorString(e));
+    return std::make_tuple(d_wte, d_wpe);
+  });
 
   m.def("column_sum", [](at::Tensor x) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.is_contiguous() &&

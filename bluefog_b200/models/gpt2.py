@@ -15,6 +15,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from bluefog_b200.ops import fused_embedding
 from bluefog_b200.ops.fused_ln import LayerNorm
 
 
@@ -113,8 +114,7 @@ class GPT2(nn.Module):
 
     def forward(self, idx, targets=None):
         b, t = idx.shape
-        pos = torch.arange(t, device=idx.device)
-        x = self.wte(idx) + self.wpe(pos)
+        x = fused_embedding.token_position_embedding(idx, self.wte.weight, self.wpe.weight)   # wte[idx] + wpe[:t]
         for block in self.h:
             x = block(x)
         x = self.ln_f(x)

@@ -52,3 +52,41 @@ def test_fused_cross_entropy_matches_fp32(R, C, pad):
     assert err <= 1e-2 * max(b.grad.abs().max().item(), 1e-6), err
     if pad:
         assert a.grad[:, C - pad:].abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("B,T,V,C,P", [(8, 128, 1000, 256, 128), (3, 17, 50, 64, 40), (4, 64, 20, 1024, 64), (1, 1, 5, 8, 1)])
+def test_token_position_embedding_matches_pytorch(B, T, V, C, P):
+    """wte[idx] + wpe[:T] and both table gradients (repeated tokens summed in fp32) against fp32 PyTorch; twice, so that
+    the scratch buffers are seen to come back clean."""
+    from bluefog_b200.ops import fused_embedding
+    torch.manual_seed(B * T + V)
+    idx = torch.randint(0, V, (B, T), device="cuda")
+    wte = torch.randn(V, C, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    wpe = torch.randn(P, C, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    assert fused_embedding._eligible(idx, wte, wpe)
+    for _ in range(2):
+        wte.grad = wpe.grad = None
+        out = fused_embedding.token_position_embedding(idx, wte, wpe)
+        ref = wte.detach().float()[idx] + wpe.detach().float()[:T]
+        assert out.shape == (B, T, C) and torch.allclose(out.float(), ref, atol=2e-2, rtol=1e-2)
+        dy = torch.randn(B, T, C, device="cuda").to(torch.bfloat16)
+        out.backward(dy)
+        fused_embedding.check_indices()
+        ref_wte = torch.zeros(V, C, device="cuda").index_add_(0, idx.reshape(-1), dy.float().reshape(-1, C))
+        ref_wpe = torch.zeros(P, C, device="cuda")
+        ref_wpe[:T] = dy.float().sum(0)
+        for got, want in ((wte.grad, ref_wte), (wpe.grad, ref_wpe)):
+            assert got.shape == want.shape
+            err = (got.float() - want).abs().max().item()
+            assert err <= 1e-2 * max(1.0, want.abs().max().item()), err
+
+
+def test_token_outside_the_table_is_skipped_and_reported():
+    from bluefog_b200.ops import fused_embedding
+    wte = torch.randn(10, 16, device="cuda").to(torch.bfloat16)
+    wpe = torch.randn(4, 16, device="cuda").to(torch.bfloat16)
+    idx = torch.tensor([[1, 2, 12, 3]], device="cuda")
+    out = fused_embedding.token_position_embedding(idx, wte, wpe)
+    assert torch.equal(out[0, 2], wpe[2])                  # the position term alone
+    with pytest.raises(IndexError):
+        fused_embedding.check_indices()

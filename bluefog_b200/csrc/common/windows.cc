@@ -83,6 +83,34 @@ unsigned char* Window::self_ptr(int rank) const { return data_base(rank) + sizeo
 unsigned char* Window::slot_ptr(int rank, int k) const {
   return data_base(rank) + sizeof(WinHeader) + padded * static_cast<size_t>(1 + k);
 }
+namespace {
+const unsigned char kGuardPattern[Window::kGuardBytes] = {0xB1, 0xFE, 0x06, 0x20, 0xB2, 0x00, 0x5A, 0xA5,
+                                                          0xC3, 0x3C, 0x96, 0x69, 0x0F, 0xF0, 0x77, 0x88};
+}
+
+void Window::WriteGuards(int rank) const {
+  for (int k = -1; k < num_slots; ++k) {
+    unsigned char* g = (k < 0 ? self_ptr(rank) : slot_ptr(rank, k)) + padded - kGuardBytes;
+    if (on_gpu) cudaMemcpy(g, kGuardPattern, kGuardBytes, cudaMemcpyHostToDevice);
+    else std::memcpy(g, kGuardPattern, kGuardBytes);
+  }
+}
+
+int Window::DamagedGuards(int rank) const {
+  int damaged = 0;
+  for (int k = -1; k < num_slots; ++k) {
+    const unsigned char* g = (k < 0 ? self_ptr(rank) : slot_ptr(rank, k)) + padded - kGuardBytes;
+    unsigned char seen[kGuardBytes];
+    if (on_gpu) {
+      if (cudaMemcpy(seen, g, kGuardBytes, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    } else {
+      std::memcpy(seen, g, kGuardBytes);
+    }
+    if (std::memcmp(seen, kGuardPattern, kGuardBytes) != 0) ++damaged;
+  }
+  return damaged;
+}
+
 std::atomic<int>* Window::mutex_word(int owner, int source) const {
   return &static_cast<HostHeader*>(shm[owner]->base)->mutex[source];
 }
@@ -128,7 +156,7 @@ Status WindowManager::Create(const OpSpec& spec, int channel) {
   w->shape = t.sizes().vec();
   w->numel = static_cast<uint64_t>(t.numel());
   w->nbytes = w->numel * t.element_size();
-  w->padded = (w->nbytes + 255) & ~uint64_t(255);
+  w->padded = (w->nbytes + Window::kGuardBytes + 255) & ~uint64_t(255);     // room for the guard words behind the tensor
   w->num_slots = spec.num_slots;
   w->in_neighbors = spec.in_neighbors;
   if (static_cast<int>(w->in_neighbors.size()) > w->num_slots)
@@ -169,6 +197,7 @@ Status WindowManager::Create(const OpSpec& spec, int channel) {
     double one = 1.0;
     WinHeader* h = reinterpret_cast<WinHeader*>(w->data_base(rank_));
     cudaMemcpy(&h->p[rank_], &one, sizeof(double), cudaMemcpyHostToDevice);
+    w->WriteGuards(rank_);
     cudaDeviceSynchronize();
   } else {
     w->self_view = at::from_blob(w->self_ptr(rank_), w->shape, [keep](void*) {}, opts);
@@ -178,6 +207,7 @@ Status WindowManager::Create(const OpSpec& spec, int channel) {
       if (spec.zero_init) slot.zero_(); else slot.copy_(t);
     }
     reinterpret_cast<WinHeader*>(w->data_base(rank_))->p[rank_] = 1.0;
+    w->WriteGuards(rank_);
   }
   s = cp_->Barrier(channel);   // every rank has mapped and initialised
   if (!s.ok()) return s;
@@ -216,7 +246,19 @@ Status WindowManager::Free(const std::string& name, int channel) {
     }
   // Nobody may unmap while a peer could still be writing into it.
   Status s = cp_->Barrier(channel);
+  // every writer is done: the guard words behind the regions of my blocks must be as win_create left them
+  std::string overrun;
+  for (auto& w : victims) {
+    c10::cuda::OptionalCUDAGuard guard;
+    if (w->on_gpu) guard.set_index(w->device);
+    const int damaged = w->DamagedGuards(rank_);
+    if (damaged != 0)
+      overrun += (overrun.empty() ? "" : ", ") + w->name + " (" + (damaged < 0 ? std::string("unreadable") : std::to_string(damaged)) + ")";
+  }
   for (auto& w : victims) FreeOne(w);
+  if (s.ok() && !overrun.empty())
+    return Status::UnknownError("window memory was written past the end of a tensor on rank " + std::to_string(rank_) +
+                                ": " + overrun + " region(s) with a damaged guard");
   return s;
 }
 

@@ -60,6 +60,12 @@ struct Window {
   unsigned char* self_ptr(int rank) const;
   unsigned char* slot_ptr(int rank, int k) const;
   std::atomic<int>* mutex_word(int owner, int source) const;
+  // Guard words: the last 16 bytes of every region (self and each slot) of this rank's block lie behind the tensor
+  // and behind anything a kernel may write for it (whole 16-byte vectors); they hold a fixed pattern from win_create
+  // to win_free, where a changed pattern means that some rank wrote past the end of a region.
+  static constexpr size_t kGuardBytes = 16;
+  void WriteGuards(int rank) const;
+  int DamagedGuards(int rank) const;          // how many regions of the rank's block have a changed guard
 };
 
 class WindowManager {

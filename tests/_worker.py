@@ -735,6 +735,36 @@ def gpu_fused_optimizers():
 
 
 @case
+def win_guard():
+    """Guard words behind every region of a window: untouched by put / accumulate / get / update of ragged sizes, and
+    a byte written past the end of the tensor is reported when the window is freed."""
+    import ctypes
+    r, n = bf.rank(), bf.size()
+    d = dev()
+    bf.set_topology(bf.RingGraph(n))
+    for numel in (1, 100, 64, 4099):
+        x = torch.full((numel,), float(r), device=d)
+        assert bf.win_create(x, f"guard.{numel}", zero_init=True)
+        bf.win_put(x, f"guard.{numel}")
+        bf.win_accumulate(x, f"guard.{numel}")
+        bf.barrier()
+        bf.win_update(f"guard.{numel}")
+        bf.win_get(f"guard.{numel}")
+        bf.barrier()
+        assert bf.win_free(f"guard.{numel}"), "guard words damaged by regular operations"
+    if d.type == "cpu":
+        # 100 floats = 400 bytes in a region of 512: the guard is its last 16 bytes
+        y = torch.zeros(100)
+        assert bf.win_create(y, "guard.hit")
+        bf.barrier()
+        if r == 0:
+            ctypes.memset(y.data_ptr() + 500, 0x11, 1)
+        ok = bf.win_free("guard.hit")
+        assert ok == (r != 0), (r, ok)
+    bf.barrier()
+
+
+@case
 def gpu_registered_tensors():
     """neighbor_allreduce of tensors in symmetric memory (published in place), with and without negotiation, static
     and per-call weights, a slice of a registered tensor, and the same values as the copying path."""

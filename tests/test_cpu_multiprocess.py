@@ -67,3 +67,7 @@ def test_rank_that_leaves_is_detected():
 def test_stall_warning_names_missing_rank():
     out = run_ranks("stall_warning", 2, timeout=120)
     assert "late.tensor" in out[0][1] and "missing ranks: 1" in out[0][1]
+
+
+def test_window_guard_words_detect_a_write_past_the_tensor():
+    run_ranks("win_guard", 2, timeout=300)

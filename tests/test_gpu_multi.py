@@ -20,7 +20,7 @@ def _need(n):
 @pytest.mark.parametrize("case", ["collectives", "neighbor_ops", "windows", "optimizers", "gpu_fused_optimizers",
                                   "gpu_fast_path", "gpu_pair_gossip", "gpu_fused_wrap_then_broadcast",
                                   "gpu_fused_dst_weights_and_hierarchical", "neighbor_sweeps", "win_random_p",
-                                  "gpu_registered_tensors"])
+                                  "gpu_registered_tensors", "win_guard"])
 def test_two_gpus(case):
     _need(2)
     run_ranks(case, 2, gpu=True, env=NVLS_OFF, timeout=600)

@@ -108,6 +108,14 @@ def collectives():
 @case
 def neighbor_ops():
     r, n, d = bf.rank(), bf.size(), dev()
+    # symmetric_empty is collective and usable everywhere: registered GPU memory on GPU ranks, an ordinary tensor on
+    # CPU ranks; the operation gives the same values either way
+    bf.set_topology(tu.RingGraph(n))
+    sym = bf.symmetric_empty(7, 5)
+    sym.fill_(float(r))
+    assert sym.shape == (7, 5) and sym.device.type == d.type and bf.is_symmetric(sym) == (d.type == "cuda" and n > 1)
+    ring_nb = bf.in_neighbor_ranks()
+    close(bf.neighbor_allreduce(sym, name="sym.ring"), (r + sum(ring_nb)) / (len(ring_nb) + 1), 1e-6)
     for graph_fn in (tu.ExponentialTwoGraph, tu.RingGraph, tu.StarGraph, tu.MeshGrid2DGraph):
         graph = graph_fn(n)
         bf.set_topology(graph)

@@ -115,3 +115,31 @@ def test_symmetric_empty_without_a_gpu_world_is_an_ordinary_tensor():
     assert x.shape == (3, 5) and x.dtype == torch.bfloat16
     assert bf.symmetric_empty((4,)).shape == (4,)
     assert not bf.is_symmetric(x)
+
+
+def test_column_sums_offered_with_a_gradient_are_taken_once_and_only_for_that_tensor():
+    """The hand-over of bias-gradient sums between two backward passes: keyed by the gradient's address, honoured only
+    while the tensor it was made for is alive and has the same extent, and only once."""
+    import gc
+    import torch
+    from bluefog_b200.ops import fused_ln
+    g = torch.randn(6, 8)
+    sums = g.sum(0)
+    fused_ln._offer_column_sums(g, sums)
+    assert fused_ln.take_column_sums(torch.randn(6, 8)) is None          # another tensor
+    view = g.reshape(2, 3, 8).reshape(-1, 8)                              # same memory, seen through views
+    assert fused_ln.take_column_sums(view) is sums
+    assert fused_ln.take_column_sums(view) is None                        # taken
+    # an entry whose tensor has died is not honoured, even if the address comes back
+    h = torch.randn(6, 8)
+    fused_ln._offer_column_sums(h, h.sum(0))
+    addr = h.data_ptr()
+    del h
+    gc.collect()
+    again = torch.randn(6, 8)
+    if again.data_ptr() == addr:                                          # the allocator usually hands the block back
+        assert fused_ln.take_column_sums(again) is None
+    # a different extent at the same address does not match either
+    k = torch.randn(6, 8)
+    fused_ln._offer_column_sums(k, k.sum(0))
+    assert fused_ln.take_column_sums(k[:3]) is None

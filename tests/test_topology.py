@@ -132,3 +132,57 @@ def test_every_public_name_of_the_reference_package_exists():
     missing = [n for n in names if not hasattr(bf, n)]
     assert not missing, missing
     bf.check_extension("bluefog_b200")          # the extension of this checkout is built
+
+
+# ---- randomised properties (hypothesis) ---------------------------------------------------------------------------
+from hypothesis import given, settings, strategies as st  # noqa: E402
+
+_STATIC = [tu.ExponentialTwoGraph, tu.ExponentialGraph, tu.SymmetricExponentialGraph, tu.MeshGrid2DGraph, tu.StarGraph,
+           tu.RingGraph, tu.FullyConnectedGraph]
+
+
+@settings(max_examples=60, deadline=None)
+@given(n=st.integers(min_value=1, max_value=48), which=st.integers(min_value=0, max_value=len(_STATIC) - 1))
+def test_any_static_graph_gives_every_rank_weights_that_sum_to_one(n, which):
+    topo = _STATIC[which](n)
+    assert topo.number_of_nodes() == n and tu.IsTopologyEquivalent(topo, topo)
+    for r in range(n):
+        self_w, src = tu.GetRecvWeights(topo, r)
+        assert abs(self_w + sum(src.values()) - 1.0) < 1e-9, (which, n, r)
+        assert r not in src and all(0 <= s < n for s in src)
+        _, dst = tu.GetSendWeights(topo, r)
+        # what r says it sends to d is what d says it receives from r
+        for d in dst:
+            assert r in tu.GetRecvWeights(topo, d)[1]
+
+
+@settings(max_examples=40, deadline=None)
+@given(n=st.integers(min_value=2, max_value=24), which=st.integers(min_value=0, max_value=len(_STATIC) - 1),
+       rounds=st.integers(min_value=1, max_value=12))
+def test_one_peer_schedule_is_a_matching_of_sends_and_receives_on_any_graph(n, which, rounds):
+    topo = _STATIC[which](n)
+    gens = [tu.GetDynamicOnePeerSendRecvRanks(topo, r) for r in range(n)]
+    for _ in range(rounds):
+        step = [next(g) for g in gens]
+        for r, (send, recv) in enumerate(step):
+            assert len(send) == 1 and topo.has_edge(r, send[0])
+            assert r in step[send[0]][1]                      # my destination expects me
+            for s in recv:
+                assert step[s][0] == [r]                      # everyone I expect sends to me
+        # averaging with these lists preserves the mean when every rank weighs what it has uniformly only on
+        # regular patterns; what always holds is that nothing is sent twice or dropped:
+        assert sum(len(recv) for _, recv in step) == n
+
+
+@settings(max_examples=30, deadline=None)
+@given(machines=st.integers(min_value=2, max_value=6), local=st.integers(min_value=3, max_value=6),
+       rounds=st.integers(min_value=1, max_value=10))
+def test_inner_outer_schedules_pair_every_send_with_a_receive(machines, local, rounds):
+    world = machines * local
+    for gen_fn in (tu.GetInnerOuterRingDynamicSendRecvRanks, tu.GetInnerOuterExpo2DynamicSendRecvRanks):
+        gens = [gen_fn(world, local, r) for r in range(world)]
+        for _ in range(rounds):
+            step = [next(g) for g in gens]
+            for r, (send, recv) in enumerate(step):
+                assert len(send) == 1 and len(recv) == 1 and send[0] != r
+                assert step[send[0]][1] == [r], (gen_fn.__name__, machines, local, r)

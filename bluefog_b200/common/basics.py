@@ -307,6 +307,15 @@ class BlueFogBasics:
         finally:
             self.timeline_end_activity(tensor_name)
 
+    def runtime_stats(self) -> dict:
+        """Counters of this rank since ``init()``: operations enqueued per type (``enqueued.NEIGHBOR_ALLREDUCE``, ...),
+        ``input_bytes``, ``issued_on_calling_thread`` (operations that skipped the background loop),
+        ``responses_executed`` and ``tensors_in_fused_responses`` (negotiated path), ``operations_failed`` and
+        ``kernel_launches`` of this library's kernels.  The reference has no counterpart (its observability is the
+        log and the timeline)."""
+        self._require_init()
+        return dict(self.native.runtime_stats())
+
 
 _basics = BlueFogBasics()
 

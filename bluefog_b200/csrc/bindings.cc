@@ -413,6 +413,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     RegisteredLoc loc;
     return t.is_cuda() && Runtime::Get().FindRegistered(t.data_ptr(), static_cast<uint64_t>(t.nbytes()), &loc);
   });
+  // Counters of this rank's runtime since init, plus the kernel launches of this library (see Runtime::StatsSnapshot).
+  m.def("runtime_stats", [] {
+    py::dict d;
+    for (const auto& kv : Runtime::Get().StatsSnapshot()) d[py::str(kv.first)] = kv.second;
+    d["kernel_launches"] = KernelLaunchCount();
+    return d;
+  });
   m.def("set_skip_negotiate_stage", [](bool v) { Runtime::Get().set_skip_negotiate(v); });
   m.def("get_skip_negotiate_stage", [] { return Runtime::Get().skip_negotiate(); });
   m.def("suspend", [] { Runtime::Get().Suspend(); });

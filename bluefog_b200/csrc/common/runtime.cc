@@ -262,7 +262,22 @@ void Runtime::Shutdown() {
 // ----------------------------------------------------------------------------------------
 // handles
 // ----------------------------------------------------------------------------------------
+std::map<std::string, uint64_t> Runtime::StatsSnapshot() const {
+  std::map<std::string, uint64_t> out;
+  for (int t = 0; t < kStatOpTypes; ++t) {
+    const uint64_t n = stats_.enqueued[t].load();
+    if (n != 0) out[std::string("enqueued.") + OpTypeName(static_cast<OpType>(t))] = n;
+  }
+  out["input_bytes"] = stats_.input_bytes.load();
+  out["issued_on_calling_thread"] = stats_.inline_issued.load();
+  out["responses_executed"] = stats_.responses.load();
+  out["tensors_in_fused_responses"] = stats_.fused_tensors.load();
+  out["operations_failed"] = stats_.errors.load();
+  return out;
+}
+
 void Runtime::MarkDone(int handle, const Status& s) {
+  if (!s.ok() && !s.in_progress()) stats_.errors.fetch_add(1);
   {
     std::lock_guard<std::mutex> g(handle_mu_);
     auto it = handles_.find(handle);
@@ -412,6 +427,8 @@ int Runtime::Enqueue(OpSpec spec) {
     MarkDone(handle, Status::PreconditionError(kSuspendError()));
     return handle;
   }
+  if (spec.type >= 0 && spec.type < kStatOpTypes) stats_.enqueued[spec.type].fetch_add(1);
+  if (spec.input.has_value() && spec.input->defined()) stats_.input_bytes.fetch_add(static_cast<uint64_t>(spec.input->nbytes()));
   Entry e;
   e.handle = handle;
   e.enqueued = Clock::now();
@@ -426,7 +443,10 @@ int Runtime::Enqueue(OpSpec spec) {
   }
   timeline_.ActivityStart(spec.name, std::string("ENQUEUE_") + OpTypeName(static_cast<OpType>(spec.type)));
   e.spec = std::move(spec);
-  if (InlineEligible(e.spec) && TryRunInline(e)) return handle;
+  if (InlineEligible(e.spec) && TryRunInline(e)) {
+    stats_.inline_issued.fetch_add(1);
+    return handle;
+  }
   {
     std::lock_guard<std::mutex> g(queue_mu_);
     queue_.push_back(std::move(e));
@@ -806,6 +826,8 @@ void Runtime::ExecuteResponse(const Response& resp) {
     }
   }
   if (entries.empty()) return;
+  stats_.responses.fetch_add(1);
+  if (entries.size() > 1) stats_.fused_tensors.fetch_add(entries.size());
   if (resp.type == OpType::ERROR) {
     FinishEntries(entries, Status::PreconditionError(resp.error_message), nullptr);
     return;

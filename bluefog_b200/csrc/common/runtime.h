@@ -111,6 +111,11 @@ class Runtime {
   // Collective byte exchange on the calling thread (bootstrap helpers for Python).
   Status AllgatherBytesNow(const std::string& mine, std::vector<std::string>* all);
 
+  // Counters of this rank since init (monotonic; read without stopping anything): operations enqueued per type,
+  // payload bytes of their inputs, operations issued on the calling thread, responses executed by the background
+  // loop and the tensors fused into them, operations that ended in an error.
+  std::map<std::string, uint64_t> StatsSnapshot() const;
+
   Timeline& timeline() { return timeline_; }
   ControlPlane& control_plane() { return cp_; }
   WindowManager* windows() { return windows_.get(); }
@@ -205,6 +210,13 @@ class Runtime {
   std::mutex inline_mu_;
   std::mutex keep_mu_;
   std::vector<std::shared_ptr<void>> keep_until_shutdown_;
+  static constexpr int kStatOpTypes = 16;
+  struct Stats {
+    std::atomic<uint64_t> enqueued[kStatOpTypes];
+    std::atomic<uint64_t> input_bytes{0}, inline_issued{0}, responses{0}, fused_tensors{0}, errors{0};
+    Stats() { for (auto& e : enqueued) e.store(0); }
+  };
+  Stats stats_;
   std::mutex reg_mu_;
   std::unique_ptr<SymmRegistry> registered_;          // buffers of SymmetricAlloc, in allocation order
   std::unordered_map<int, InlineOp> inline_ops_;      // by handle

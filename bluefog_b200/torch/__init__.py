@@ -34,6 +34,7 @@ get_skip_negotiate_stage = _b.get_skip_negotiate_stage
 timeline_start_activity = _b.timeline_start_activity
 timeline_end_activity = _b.timeline_end_activity
 timeline_context = _b.timeline_context
+runtime_stats = _b.runtime_stats
 
 from bluefog_b200.ops.collectives import (  # noqa: E402
     allreduce, allreduce_nonblocking, allreduce_, allreduce_nonblocking_,

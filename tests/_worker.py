@@ -743,6 +743,51 @@ def gpu_fused_optimizers():
 
 
 @case
+def runtime_stats():
+    """Counters of the runtime: per-type operation counts, payload bytes, failures, and the Prometheus view of them."""
+    r, n = bf.rank(), bf.size()
+    d = dev()
+    bf.set_topology(bf.RingGraph(n))
+    before = bf.runtime_stats()
+    x = torch.full((1000,), float(r), device=d)
+    for k in range(5):
+        bf.neighbor_allreduce(x, name=f"stats.na.{k}")
+    bf.allreduce(x, name="stats.ar")
+    hs = [bf.neighbor_allreduce_nonblocking(torch.full((10,), 1.0, device=d), name=f"stats.small.{k}") for k in range(6)]
+    for h in hs:
+        bf.synchronize(h)
+    after = bf.runtime_stats()
+
+    def delta(key):
+        return after.get(key, 0) - before.get(key, 0)
+
+    assert delta("enqueued.NEIGHBOR_ALLREDUCE") == 11 and delta("enqueued.ALLREDUCE") == 1, after
+    assert delta("input_bytes") == 6 * 4000 + 6 * 40
+    assert delta("operations_failed") == 0
+    if d.type == "cpu":
+        assert delta("responses_executed") >= 1 and delta("issued_on_calling_thread") == 0
+    # a failing operation is counted
+    try:
+        bf.neighbor_allreduce(x, self_weight=0.5, name="stats.bad")           # src_weights missing
+    except ValueError:
+        pass
+    from bluefog_b200.utils import metrics
+    snap = metrics.snapshot()
+    assert snap["rank"] == r and snap["size"] == n and snap["enqueued.NEIGHBOR_ALLREDUCE"] >= 11
+    try:
+        import prometheus_client
+    except ImportError:
+        prometheus_client = None
+    if prometheus_client is not None:
+        reg = prometheus_client.CollectorRegistry()
+        reg.register(metrics._Collector())
+        text = prometheus_client.generate_latest(reg).decode()
+        assert f'bluefog_b200_operations_enqueued_total{{rank="{r}",type="neighbor_allreduce"}}' in text, text[:600]
+        assert "bluefog_b200_input_bytes_total" in text
+    bf.barrier()
+
+
+@case
 def win_guard():
     """Guard words behind every region of a window: untouched by put / accumulate / get / update of ragged sizes, and
     a byte written past the end of the tensor is reported when the window is freed."""

@@ -71,3 +71,7 @@ def test_stall_warning_names_missing_rank():
 
 def test_window_guard_words_detect_a_write_past_the_tensor():
     run_ranks("win_guard", 2, timeout=300)
+
+
+def test_runtime_counters_and_their_prometheus_view():
+    run_ranks("runtime_stats", 3, timeout=300)

@@ -108,3 +108,130 @@ def test_host_parsing(tmp_path):
     assert network_util.is_local_host("localhost") and network_util.is_local_host("127.0.0.1")
     env = env_util.rank_environment({"A": "1", "RANK": "5", "BASH_FUNC_x%%": "y"}, timeline="p", verbose=True)
     assert env == {"A": "1", "BLUEFOG_TIMELINE": "p", "BLUEFOG_LOG_LEVEL": "debug"}
+
+
+_FAKE_CONTROLLER = """
+import os, signal, sys, time
+out = os.environ["IBF_TEST_OUT"]
+with open(os.path.join(out, "controller"), "w") as f:
+    f.write(" ".join(sys.argv[1:]))
+signal.signal(signal.SIGINT, lambda *_: sys.exit(0))
+signal.signal(signal.SIGTERM, lambda *_: sys.exit(0))
+while True:
+    time.sleep(0.1)
+"""
+
+_FAKE_ENGINE = """
+import os, signal, sys, time
+e, out = os.environ, os.environ["IBF_TEST_OUT"]
+with open(os.path.join(out, "engine_" + e["RANK"]), "w") as f:
+    f.write("%s %s %s %d %s" % (e["RANK"], e["WORLD_SIZE"], e["LOCAL_RANK"], os.getpid(), " ".join(sys.argv[1:])))
+signal.signal(signal.SIGINT, lambda *_: sys.exit(0))
+signal.signal(signal.SIGTERM, lambda *_: sys.exit(0))
+while True:
+    time.sleep(0.1)
+"""
+
+
+def _alive(pid):
+    try:
+        os.kill(pid, 0)
+        return True
+    except OSError:
+        return False
+
+
+def test_ibfrun_starts_a_controller_and_engines_as_ranks_and_stops_them(tmp_path):
+    """The whole start / status / stop cycle of the interactive launcher against a stand-in for the optional
+    ipyparallel package (a controller and engines that only record how they were started): the engines come up as ranks
+    of one job, a second start is refused while the cluster lives, stop ends exactly the processes that were started."""
+    import time
+    fake = tmp_path / "fake" / "ipyparallel"
+    fake.mkdir(parents=True)
+    (fake / "__init__.py").write_text("")
+    (fake / "controller.py").write_text(_FAKE_CONTROLLER)
+    (fake / "engine.py").write_text(_FAKE_ENGINE)
+    out = tmp_path / "out"
+    out.mkdir()
+    env = dict(ENV, PYTHONPATH=str(tmp_path / "fake") + os.pathsep + ENV["PYTHONPATH"], HOME=str(tmp_path),
+               IBF_TEST_OUT=str(out))
+
+    def ibfrun(*args):
+        return subprocess.run([sys.executable, "-m", "bluefog_b200.run.interactive_run", *args], env=env,
+                              capture_output=True, text=True, timeout=120)
+
+    assert ibfrun("status").returncode == 1                         # nothing yet
+    started = ibfrun("start", "-np", "2", "--ipython-profile", "t")
+    assert started.returncode == 0, started.stderr
+    try:
+        deadline = time.time() + 30
+        while time.time() < deadline and not ((out / "engine_0").exists() and (out / "engine_1").exists()):
+            time.sleep(0.2)
+        engines = [(out / f"engine_{r}").read_text().split() for r in range(2)]
+        assert [e[:3] for e in engines] == [["0", "2", "0"], ["1", "2", "1"]]
+        assert all("--profile=t" in e and "--IPEngine.max_heartbeat_misses=0" in e for e in engines)
+        assert "--profile=t" in (out / "controller").read_text()
+        pids = [int(e[3]) for e in engines]
+        assert all(_alive(p) for p in pids)
+        assert ibfrun("status").returncode == 0
+        again = ibfrun("start", "-np", "2", "--ipython-profile", "t")
+        assert again.returncode != 0 and "already running" in again.stderr
+    finally:
+        stopped = ibfrun("stop")
+    assert stopped.returncode == 0 and "stopped" in stopped.stdout
+    deadline = time.time() + 10
+    while time.time() < deadline and any(_alive(p) for p in pids):
+        time.sleep(0.2)
+    assert not any(_alive(p) for p in pids)
+    assert ibfrun("status").returncode == 1
+    assert "nothing to stop" in ibfrun("stop").stdout
+
+
+def test_interrupt_hanged_processes_signals_only_the_engines_that_do_not_answer(tmp_path):
+    """Engines stuck in a collective do not answer a ping: they, and only they, get SIGINT."""
+    import time
+    from bluefog_b200.run import interactive_run
+    code = ("import os, signal, sys, time\n"
+            "signal.signal(signal.SIGINT, lambda *_: (open(sys.argv[1], 'w').write('interrupted'), sys.exit(0)))\n"
+            "open(sys.argv[1] + '.up', 'w').write('up')\n"
+            "while True: time.sleep(0.05)\n")
+    procs = [subprocess.Popen([sys.executable, "-c", code, str(tmp_path / f"e{k}")]) for k in range(2)]
+    try:
+        deadline = time.time() + 20
+        while time.time() < deadline and not all((tmp_path / f"e{k}.up").exists() for k in range(2)):
+            time.sleep(0.05)
+
+        class Result:
+            def __init__(self, value, ready=True):
+                self.value, self._ready = value, ready
+
+            def get_dict(self):
+                return self.value
+
+            def ready(self):
+                return self._ready
+
+        class View:
+            def __init__(self, client, eid=None):
+                self.client, self.eid = client, eid
+
+            def apply_async(self, fn):
+                if self.eid is None:
+                    return Result({k: p.pid for k, p in enumerate(procs)})
+                return Result(0, ready=self.client.answers[self.eid])
+
+        class Client:
+            ids = [0, 1]
+            answers = {0: True, 1: False}        # engine 1 hangs
+
+            def __getitem__(self, key):
+                return View(self, None if isinstance(key, slice) else key)
+
+        interactive_run.interrupt_hanged_processes(Client(), timeout=0.05)
+        procs[1].wait(timeout=10)
+        assert (tmp_path / "e1").read_text() == "interrupted"
+        assert procs[0].poll() is None and not (tmp_path / "e0").exists()
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()

@@ -18,7 +18,7 @@ import sys
 import tempfile
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-DEFAULT_CASES = "collectives,neighbor_ops,windows,errors,skip_negotiate,optimizers"
+DEFAULT_CASES = "collectives,neighbor_ops,windows,errors,skip_negotiate,optimizers,runtime_stats,win_guard"
 
 
 def find_libtsan():
